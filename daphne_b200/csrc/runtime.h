@@ -1,0 +1,95 @@
+// Internal C++ view of the runtime objects behind the opaque handles of the C-ABI.
+#pragma once
+
+#include "common.cuh"
+
+#include <memory>
+#include <mutex>
+#include <stdexcept>
+#include <string>
+#include <vector>
+
+struct db2_context {
+    int device = 0;
+    cudaStream_t stream = nullptr;
+    cudaMemPool_t pool = nullptr;
+    // reusable scratch for two-stage reductions (grown on demand, stream-ordered reuse)
+    void *scratch = nullptr;
+    size_t scratch_bytes = 0;
+    // device status word for domain errors + pinned host mirror
+    int32_t *dev_status = nullptr;
+    int32_t *host_status = nullptr;
+    std::mutex mu;
+    db2_stats stats{};
+};
+
+namespace db2 {
+
+struct Error : std::runtime_error {
+    int code;
+    Error(int c, const std::string &m) : std::runtime_error(m), code(c) {}
+};
+
+// RAII device buffer from the context's pool (or borrowed from the caller)
+struct DevBuf {
+    db2_context *ctx;
+    void *ptr;
+    size_t bytes;
+    bool owned;
+    ~DevBuf();
+};
+
+struct HostBuf {
+    void *ptr;
+    size_t bytes;
+    bool owned; // owned buffers are pinned (cudaMallocHost)
+    ~HostBuf();
+};
+
+int ctx_alloc(db2_context *ctx, size_t bytes, void **out);
+int ctx_free(db2_context *ctx, void *ptr, size_t bytes);
+int ctx_scratch(db2_context *ctx, size_t bytes, void **out);
+std::shared_ptr<DevBuf> make_devbuf(db2_context *ctx, size_t bytes); // throws Error
+
+inline void bind_device(const db2_context *ctx) {
+    int cur = -1;
+    if (cudaGetDevice(&cur) != cudaSuccess || cur != ctx->device)
+        cudaSetDevice(ctx->device);
+}
+
+} // namespace db2
+
+struct db2_matrix {
+    std::atomic<int> refs{1};
+    db2_context *ctx = nullptr;
+    int dtype = DB2_F64;
+    int64_t rows = 0, cols = 0;
+    // device placement
+    std::shared_ptr<db2::DevBuf> dev;
+    int64_t dev_off = 0; // element offset of (0,0) inside dev
+    int64_t dev_ld = 0;
+    bool dev_valid = false;
+    // host placement
+    std::shared_ptr<db2::HostBuf> host;
+    int64_t host_off = 0;
+    int64_t host_ld = 0;
+    bool host_valid = false;
+
+    size_t esize() const { return db2::dtype_size(dtype); }
+    void *dev_ptr() const { return static_cast<char *>(dev->ptr) + dev_off * (int64_t)esize(); }
+    void *host_ptr() const { return static_cast<char *>(host->ptr) + host_off * (int64_t)esize(); }
+};
+
+namespace db2 {
+// makes the device placement current (allocation + async H2D when only the host copy is valid)
+int ensure_device(db2_matrix *m);
+// result allocation following the reference's "*res == nullptr means allocate" convention; checks shape/type otherwise
+int prepare_result(db2_context *ctx, db2_matrix **res, int dtype, int64_t rows, int64_t cols);
+} // namespace db2
+
+#define DB2_API_BEGIN try {
+#define DB2_API_END                                                                                                    \
+    }                                                                                                                  \
+    catch (const ::db2::Error &e) { return ::db2::set_error(e.code, "%s", e.what()); }                                 \
+    catch (const std::bad_alloc &) { return ::db2::set_error(DB2_ENOMEM, "out of host memory"); }                      \
+    catch (const std::exception &e) { return ::db2::set_error(DB2_EINVAL, "%s", e.what()); }

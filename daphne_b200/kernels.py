@@ -1,0 +1,206 @@
+"""Host-side mirror of the reference's kernel interface for the hot path.
+
+Function names, argument order and error behaviour follow the convenience functions of
+src/runtime/local/kernels/*.h (ewBinaryMat, ewBinaryObjSca, ewUnaryMat, aggRow, aggCol, aggAll, ...), so the parity
+tests read like the reference's own unit tests.  Everything here is a thin ctypes call into the C-ABI runtime
+(include/daphne_b200.h); numpy is only used to hand host buffers in and out."""
+from __future__ import annotations
+
+import ctypes as C
+import enum
+from typing import Optional
+
+import numpy as np
+
+from . import lib as _l
+from .lib import Db2Error, check, lib
+
+_NP2DT = {np.dtype(np.float64): _l.F64, np.dtype(np.float32): _l.F32, np.dtype(np.int64): _l.I64,
+          np.dtype(np.uint64): _l.U64}
+_DT2NP = {v: k for k, v in _NP2DT.items()}
+
+
+class BinaryOpCode(enum.IntEnum):  # BinaryOpCode.h:29-56
+    ADD = 0; SUB = 1; MUL = 2; DIV = 3; POW = 4; MOD = 5; LOG = 6; EQ = 7; NEQ = 8; LT = 9; LE = 10; GT = 11
+    GE = 12; MIN = 13; MAX = 14; AND = 15; OR = 16; BITWISE_AND = 17
+
+
+class UnaryOpCode(enum.IntEnum):  # UnaryOpCode.h:26-56
+    MINUS = 0; ABS = 1; SIGN = 2; SQRT = 3; EXP = 4; LN = 5; SIN = 6; COS = 7; TAN = 8; ASIN = 9; ACOS = 10
+    ATAN = 11; SINH = 12; COSH = 13; TANH = 14; FLOOR = 15; CEIL = 16; ROUND = 17; ISNAN = 18
+
+
+class AggOpCode(enum.IntEnum):  # AggOpCode.h:25-35
+    SUM = 0; PROD = 1; MIN = 2; MAX = 3; IDXMIN = 4; IDXMAX = 5; MEAN = 6; STDDEV = 7; VAR = 8
+
+
+class Context:
+    """One per device (db2_context): stream, pooled device memory, counters."""
+
+    def __init__(self, device: int = 0):
+        self._h = C.c_void_p()
+        check(lib.db2_context_create(int(device), C.byref(self._h)))
+        self.device = int(device)
+
+    @property
+    def handle(self):
+        return self._h
+
+    @property
+    def stream(self) -> int:
+        return lib.db2_context_stream(self._h) or 0
+
+    def sync(self) -> None:
+        check(lib.db2_context_sync(self._h))
+
+    def stats(self) -> dict:
+        s = _l.Stats()
+        check(lib.db2_context_stats(self._h, C.byref(s)))
+        return {f: getattr(s, f) for f, _ in s._fields_}
+
+    def close(self) -> None:
+        if self._h:
+            lib.db2_context_destroy(self._h)
+            self._h = C.c_void_p()
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *exc):
+        self.close()
+
+
+class DenseMatrix:
+    """Handle to a db2_matrix.  `from_numpy` makes the array the host placement (no copy); the device placement is
+    created when a kernel first needs it."""
+
+    def __init__(self, ctx: Context, handle, keep=None):
+        self.ctx = ctx
+        self._h = handle
+        self._keep = keep  # host array backing a borrowed host placement
+        dt, r, c = C.c_int(), C.c_int64(), C.c_int64()
+        check(lib.db2_matrix_info(self._h, C.byref(dt), C.byref(r), C.byref(c)))
+        self.dtype_code, self.rows, self.cols = dt.value, r.value, c.value
+
+    @property
+    def handle(self):
+        return self._h
+
+    @property
+    def shape(self):
+        return (self.rows, self.cols)
+
+    @property
+    def dtype(self):
+        return _DT2NP[self.dtype_code]
+
+    @staticmethod
+    def from_numpy(ctx: Context, a: np.ndarray) -> "DenseMatrix":
+        if a.ndim == 1:
+            a = a.reshape(-1, 1)
+        if a.ndim != 2 or a.dtype not in _NP2DT:
+            raise Db2Error(1, f"unsupported array: ndim {a.ndim}, dtype {a.dtype}")
+        if a.size and (a.strides[1] != a.itemsize or a.strides[0] % a.itemsize):
+            a = np.ascontiguousarray(a)
+        ld = a.strides[0] // a.itemsize if a.shape[0] > 1 and a.size else a.shape[1]
+        ld = max(ld, a.shape[1])
+        h = C.c_void_p()
+        check(lib.db2_matrix_wrap_host(ctx.handle, _NP2DT[a.dtype], a.shape[0], a.shape[1], ld,
+                                       C.c_void_p(a.ctypes.data), C.byref(h)))
+        return DenseMatrix(ctx, h, keep=a)
+
+    @staticmethod
+    def empty(ctx: Context, rows: int, cols: int, dtype=np.float64, zero: bool = False) -> "DenseMatrix":
+        h = C.c_void_p()
+        check(lib.db2_matrix_create(ctx.handle, _NP2DT[np.dtype(dtype)], rows, cols, int(zero), C.byref(h)))
+        return DenseMatrix(ctx, h)
+
+    @staticmethod
+    def wrap_device(ctx: Context, ptr: int, rows: int, cols: int, ld: int, dtype=np.float64, keep=None):
+        h = C.c_void_p()
+        check(lib.db2_matrix_wrap_device(ctx.handle, _NP2DT[np.dtype(dtype)], rows, cols, ld, C.c_void_p(ptr),
+                                         C.byref(h)))
+        return DenseMatrix(ctx, h, keep=keep)
+
+    def slice_rows(self, r0: int, r1: int) -> "DenseMatrix":
+        h = C.c_void_p()
+        check(lib.db2_matrix_slice_rows(self._h, r0, r1, C.byref(h)))
+        return DenseMatrix(self.ctx, h, keep=self._keep)
+
+    def device_ptr(self):
+        p, ld = C.c_void_p(), C.c_int64()
+        check(lib.db2_matrix_device_ptr(self._h, C.byref(p), C.byref(ld)))
+        return (p.value or 0), ld.value
+
+    def to_numpy(self) -> np.ndarray:
+        out = np.empty((self.rows, self.cols), dtype=self.dtype)
+        check(lib.db2_matrix_to_host(self._h, C.c_void_p(out.ctypes.data), max(self.cols, 1)))
+        return out
+
+    def free(self) -> None:
+        if self._h:
+            lib.db2_matrix_decref(self._h)
+            self._h = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.free()
+        except Exception:
+            pass
+
+
+def _res(ctx: Context, h) -> DenseMatrix:
+    return DenseMatrix(ctx, h)
+
+
+def _scalar(dtype_code: int, value):
+    return np.array([value], dtype=_DT2NP[dtype_code])
+
+
+def ewBinaryMat(op, lhs: DenseMatrix, rhs: DenseMatrix, ctx: Optional[Context] = None) -> DenseMatrix:
+    """EwBinaryMat.h:44-47: res = lhs op rhs, rhs may be a row or column vector."""
+    ctx = ctx or lhs.ctx
+    h = C.c_void_p()
+    check(lib.db2_ewBinaryMat(ctx.handle, int(op), C.byref(h), lhs.handle, rhs.handle))
+    return _res(ctx, h)
+
+
+def ewBinaryObjSca(op, lhs: DenseMatrix, rhs, ctx: Optional[Context] = None) -> DenseMatrix:
+    """EwBinaryObjSca.h:47-50: res = lhs op scalar."""
+    ctx = ctx or lhs.ctx
+    s = _scalar(lhs.dtype_code, rhs)
+    h = C.c_void_p()
+    check(lib.db2_ewBinaryObjSca(ctx.handle, int(op), C.byref(h), lhs.handle, C.c_void_p(s.ctypes.data)))
+    return _res(ctx, h)
+
+
+def ewUnaryMat(op, arg: DenseMatrix, ctx: Optional[Context] = None) -> DenseMatrix:
+    """EwUnaryMat.h:46-48."""
+    ctx = ctx or arg.ctx
+    h = C.c_void_p()
+    check(lib.db2_ewUnaryMat(ctx.handle, int(op), C.byref(h), arg.handle))
+    return _res(ctx, h)
+
+
+def aggRow(op, arg: DenseMatrix, ctx: Optional[Context] = None) -> DenseMatrix:
+    """AggRow.h:49-51: rows x 1 result; IDXMIN/IDXMAX give uint64 positions."""
+    ctx = ctx or arg.ctx
+    h = C.c_void_p()
+    check(lib.db2_aggRow(ctx.handle, int(op), C.byref(h), arg.handle))
+    return _res(ctx, h)
+
+
+def aggCol(op, arg: DenseMatrix, ctx: Optional[Context] = None) -> DenseMatrix:
+    """AggCol.h:47-49: 1 x cols result."""
+    ctx = ctx or arg.ctx
+    h = C.c_void_p()
+    check(lib.db2_aggCol(ctx.handle, int(op), C.byref(h), arg.handle))
+    return _res(ctx, h)
+
+
+def aggAll(op, arg: DenseMatrix, ctx: Optional[Context] = None):
+    """AggAll.h:49-51: scalar result."""
+    ctx = ctx or arg.ctx
+    out = np.zeros(1, dtype=arg.dtype)
+    check(lib.db2_aggAll(ctx.handle, int(op), C.c_void_p(out.ctypes.data), arg.handle))
+    return out[0]

@@ -1,0 +1,132 @@
+"""ctypes binding of libdaphne_b200.so (the C-ABI declared in include/daphne_b200.h).
+
+There is no CPU fallback: if the shared library is missing the import fails with a message that says how to build it,
+and every compute call needs a CUDA device."""
+from __future__ import annotations
+
+import ctypes as C
+from pathlib import Path
+
+_PKG = Path(__file__).resolve().parent
+LIB_PATH = _PKG / "libdaphne_b200.so"
+
+# value type codes (include/daphne_b200.h)
+F64, F32, I64, U64 = 0, 1, 2, 3
+
+
+class Db2Error(RuntimeError):
+    """A non-zero status from the C-ABI; mirrors the std::runtime_error the reference's kernels throw."""
+
+    def __init__(self, code: int, msg: str):
+        super().__init__(msg)
+        self.code = code
+
+
+def _load() -> C.CDLL:
+    if not LIB_PATH.exists():
+        raise ImportError(
+            f"{LIB_PATH} is missing: build it with `python -m daphne_b200.build` "
+            "(needs nvcc; daphne_b200 has no CPU fallback)")
+    return C.CDLL(str(LIB_PATH), mode=C.RTLD_GLOBAL)
+
+
+lib = _load()
+
+i32, i64, u64, sz, vp = C.c_int, C.c_int64, C.c_uint64, C.c_size_t, C.c_void_p
+_P = C.POINTER
+
+_SIGS = {
+    # name: (restype, argtypes)
+    "db2_last_error": (C.c_char_p, []),
+    "db2_version": (C.c_char_p, []),
+    "db2_device_count": (i32, [_P(i32)]),
+    "db2_set_device": (i32, [i32]),
+    "db2_sm_count": (i32, [_P(i32)]),
+    "db2_malloc": (i32, [_P(vp), sz]),
+    "db2_free": (i32, [vp]),
+    "db2_malloc_host": (i32, [_P(vp), sz]),
+    "db2_free_host": (i32, [vp]),
+    "db2_memcpy_h2d": (i32, [vp, vp, sz, vp]),
+    "db2_memcpy_d2h": (i32, [vp, vp, sz, vp]),
+    "db2_memcpy_d2d": (i32, [vp, vp, sz, vp]),
+    "db2_memset": (i32, [vp, i32, sz, vp]),
+    "db2_stream_create": (i32, [_P(vp)]),
+    "db2_stream_destroy": (i32, [vp]),
+    "db2_stream_sync": (i32, [vp]),
+    "db2_device_sync": (i32, []),
+    "db2_event_create": (i32, [_P(vp)]),
+    "db2_event_destroy": (i32, [vp]),
+    "db2_event_record": (i32, [vp, vp]),
+    "db2_event_elapsed_ms": (i32, [vp, vp, _P(C.c_float)]),
+    "db2_launch_count": (u64, []),
+    "db2k_ew_binary": (i32, [i32, i32, vp, i64, i64, i64, vp, i64, i64, i64, vp, i64, vp]),
+    "db2k_ew_binary_sca": (i32, [i32, i32, vp, i64, i64, i64, vp, vp, i64, vp]),
+    "db2k_ew_unary": (i32, [i32, i32, vp, i64, i64, i64, vp, i64, vp, vp]),
+    "db2k_agg_row": (i32, [i32, i32, vp, i64, i64, i64, vp, i64, vp]),
+    "db2k_agg_col_scratch_bytes": (sz, [i32, i32, i64, i64]),
+    "db2k_agg_col": (i32, [i32, i32, vp, i64, i64, i64, vp, vp, sz, vp]),
+    "db2k_agg_all_scratch_bytes": (sz, [i32, i32, i64, i64]),
+    "db2k_agg_all": (i32, [i32, i32, vp, i64, i64, i64, vp, vp, sz, vp]),
+    # runtime
+    "db2_context_create": (i32, [i32, _P(vp)]),
+    "db2_context_destroy": (i32, [vp]),
+    "db2_context_device": (i32, [vp, _P(i32)]),
+    "db2_context_stream": (vp, [vp]),
+    "db2_context_sync": (i32, [vp]),
+    "db2_context_stats": (i32, [vp, vp]),
+    "db2_matrix_create": (i32, [vp, i32, i64, i64, i32, _P(vp)]),
+    "db2_matrix_wrap_host": (i32, [vp, i32, i64, i64, i64, vp, _P(vp)]),
+    "db2_matrix_wrap_device": (i32, [vp, i32, i64, i64, i64, vp, _P(vp)]),
+    "db2_matrix_slice_rows": (i32, [vp, i64, i64, _P(vp)]),
+    "db2_matrix_incref": (i32, [vp]),
+    "db2_matrix_decref": (i32, [vp]),
+    "db2_matrix_info": (i32, [vp, _P(i32), _P(i64), _P(i64)]),
+    "db2_matrix_device_ptr": (i32, [vp, _P(vp), _P(i64)]),
+    "db2_matrix_to_host": (i32, [vp, vp, i64]),
+    "db2_ewBinaryMat": (i32, [vp, i32, _P(vp), vp, vp]),
+    "db2_ewBinaryObjSca": (i32, [vp, i32, _P(vp), vp, vp]),
+    "db2_ewUnaryMat": (i32, [vp, i32, _P(vp), vp]),
+    "db2_aggRow": (i32, [vp, i32, _P(vp), vp]),
+    "db2_aggCol": (i32, [vp, i32, _P(vp), vp]),
+    "db2_aggAll": (i32, [vp, i32, vp, vp]),
+}
+
+
+class Stats(C.Structure):
+    """db2_stats (include/daphne_b200.h)."""
+    _fields_ = [(n, C.c_uint64) for n in ("h2d_bytes", "d2h_bytes", "d2d_bytes", "allocs", "alloc_bytes", "frees",
+                                          "launches", "live_bytes", "peak_bytes")]
+
+
+def declare(sigs: dict) -> None:
+    for name, (res, args) in sigs.items():
+        fn = getattr(lib, name)  # AttributeError here = the library does not export a declared symbol
+        fn.restype = res
+        fn.argtypes = args
+
+
+declare(_SIGS)
+
+
+def exported_symbols() -> list[str]:
+    return sorted(_SIGS)
+
+
+def last_error() -> str:
+    return (lib.db2_last_error() or b"").decode("utf-8", "replace")
+
+
+def check(rc: int) -> None:
+    if rc != 0:
+        raise Db2Error(rc, last_error())
+
+
+def device_count() -> int:
+    n = i32(0)
+    rc = lib.db2_device_count(C.byref(n))
+    return n.value if rc == 0 else 0
+
+
+def require_device() -> None:
+    if device_count() < 1:
+        raise Db2Error(2, "daphne_b200 needs a CUDA device (there is no CPU fallback)")

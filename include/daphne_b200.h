@@ -1,0 +1,206 @@
+/*
+ * daphne_b200 -- B200-native (sm_100a) runtime kernel library for the kernels
+ * that DAPHNE's vectorized pipelines execute.
+ *
+ * This header is the C-ABI boundary: plain pointers and sizes, no C++ or torch
+ * types.  It has three layers:
+ *
+ *   db2k_*  kernel launchers on DEVICE pointers (one per reference kernel
+ *           template registered in src/runtime/local/kernels/kernels.json),
+ *   db2_*   the runtime: context (device, stream, pooled device memory),
+ *           matrix handles with host/device residency, operator calls on
+ *           handles, and the row-partition pipeline scheduler,
+ *   db2h_*  host-buffer conveniences (copy in, run, copy out) used by the
+ *           end-to-end measurement.
+ *
+ * The DAPHNE-named entry points (CUDA_sumRow__DenseMatrix_double__... etc.),
+ * which take DAPHNE's C++ data objects, live in the adapter library built from
+ * daphne_b200/csrc/daphne_abi/ against a DAPHNE source tree; they forward to
+ * the functions declared here.
+ *
+ * Conventions
+ *   - every function returns 0 on success, a DB2_E* code otherwise;
+ *     db2_last_error() returns the message of the calling thread's last error
+ *     (the reference reports errors as C++ exceptions: the adapter rethrows the
+ *     message as std::runtime_error, like
+ *     src/runtime/local/kernels/CUDA/HostUtils.h:37-80 does for CUDA errors);
+ *   - matrices are row-major with a leading dimension `ld` in ELEMENTS
+ *     (DenseMatrix::getRowSkip(), src/runtime/local/datastructures/DenseMatrix.h:42-62);
+ *   - `stream` is a cudaStream_t passed as void* (NULL = legacy default stream);
+ *   - op codes are the reference's enum values
+ *     (BinaryOpCode.h:29-56, UnaryOpCode.h:26-56, AggOpCode.h:25-35).
+ */
+#ifndef DAPHNE_B200_H
+#define DAPHNE_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ------------------------------------------------------------------------- */
+/* enums                                                                      */
+/* ------------------------------------------------------------------------- */
+
+enum { DB2_OK = 0, DB2_EINVAL = 1, DB2_ECUDA = 2, DB2_ENOMEM = 3, DB2_EUNSUPPORTED = 4, DB2_EDOMAIN = 5,
+       DB2_ENCCL = 6, DB2_ETIMEOUT = 7 };
+
+/* value types (kernels.json instantiates the hot kernels for double, float, int64_t;
+ * size_t is the value type of idxMin/idxMax results, AggRow.h:71-96) */
+enum { DB2_F64 = 0, DB2_F32 = 1, DB2_I64 = 2, DB2_U64 = 3 };
+
+/* BinaryOpCode (src/runtime/local/kernels/BinaryOpCode.h:29-56) */
+enum { DB2_ADD = 0, DB2_SUB, DB2_MUL, DB2_DIV, DB2_POW, DB2_MOD, DB2_LOG, DB2_EQ, DB2_NEQ, DB2_LT, DB2_LE, DB2_GT,
+       DB2_GE, DB2_MIN, DB2_MAX, DB2_AND, DB2_OR, DB2_BITWISE_AND };
+
+/* UnaryOpCode (src/runtime/local/kernels/UnaryOpCode.h:26-56) */
+enum { DB2_U_MINUS = 0, DB2_U_ABS, DB2_U_SIGN, DB2_U_SQRT, DB2_U_EXP, DB2_U_LN, DB2_U_SIN, DB2_U_COS, DB2_U_TAN,
+       DB2_U_ASIN, DB2_U_ACOS, DB2_U_ATAN, DB2_U_SINH, DB2_U_COSH, DB2_U_TANH, DB2_U_FLOOR, DB2_U_CEIL,
+       DB2_U_ROUND, DB2_U_ISNAN };
+
+/* AggOpCode (src/runtime/local/kernels/AggOpCode.h:25-35) */
+enum { DB2_AGG_SUM = 0, DB2_AGG_PROD, DB2_AGG_MIN, DB2_AGG_MAX, DB2_AGG_IDXMIN, DB2_AGG_IDXMAX, DB2_AGG_MEAN,
+       DB2_AGG_STDDEV, DB2_AGG_VAR };
+
+/* VectorSplit / VectorCombine (src/ir/daphneir/DaphneVectorizableOpInterface.td:23-36) */
+enum { DB2_SPLIT_NONE = 0, DB2_SPLIT_ROWS = 1 };
+enum { DB2_COMBINE_ROWS = 1, DB2_COMBINE_COLS = 2, DB2_COMBINE_ADD = 3, DB2_COMBINE_MIN = 4, DB2_COMBINE_MAX = 5 };
+
+/* ------------------------------------------------------------------------- */
+/* errors, device memory helpers                                              */
+/* ------------------------------------------------------------------------- */
+
+const char *db2_last_error(void);
+const char *db2_version(void);
+int db2_device_count(int *count);
+int db2_set_device(int device);
+int db2_sm_count(int *count);
+
+int db2_malloc(void **dptr, size_t bytes);                /* cudaMalloc                    */
+int db2_free(void *dptr);                                 /* cudaFree                      */
+int db2_malloc_host(void **hptr, size_t bytes);           /* pinned host memory            */
+int db2_free_host(void *hptr);
+int db2_memcpy_h2d(void *dst, const void *src, size_t bytes, void *stream);
+int db2_memcpy_d2h(void *dst, const void *src, size_t bytes, void *stream);
+int db2_memcpy_d2d(void *dst, const void *src, size_t bytes, void *stream);
+int db2_memset(void *dst, int byte, size_t bytes, void *stream);
+int db2_stream_create(void **stream);
+int db2_stream_destroy(void *stream);
+int db2_stream_sync(void *stream);
+int db2_device_sync(void);
+/* CUDA-event timing on a stream (used by the measurement harness). */
+int db2_event_create(void **event);
+int db2_event_destroy(void *event);
+int db2_event_record(void *event, void *stream);
+int db2_event_elapsed_ms(void *start, void *stop, float *ms); /* synchronises on `stop` */
+/* number of kernels this library launched since load (all threads) */
+uint64_t db2_launch_count(void);
+
+/* ------------------------------------------------------------------------- */
+/* db2k_*: kernel launchers on device pointers                                */
+/* ------------------------------------------------------------------------- */
+
+/* res = lhs op rhs.  rhs has the shape of lhs, or is a 1 x cols row vector, or a rows x 1 column vector;
+ * the result has the shape of lhs.  Replaces EwBinaryMat<Dense,Dense,Dense>
+ * (src/runtime/local/kernels/EwBinaryMat.h:54-108; CUDA twin kernels/CUDA/EwBinaryMat.cu:97-263).
+ * Comparison results are 0/1 in the value type. */
+int db2k_ew_binary(int dtype, int op, const void *lhs, int64_t lhs_rows, int64_t lhs_cols, int64_t lhs_ld,
+                   const void *rhs, int64_t rhs_rows, int64_t rhs_cols, int64_t rhs_ld, void *res, int64_t res_ld,
+                   void *stream);
+
+/* res = lhs op scalar; `scalar` is a HOST pointer to one value of `dtype`.  Replaces EwBinaryObjSca<Dense,Dense,VT>
+ * (src/runtime/local/kernels/EwBinaryObjSca.h:58-79; CUDA twin kernels/CUDA/EwBinaryObjSca.cu:31-88). */
+int db2k_ew_binary_sca(int dtype, int op, const void *lhs, int64_t rows, int64_t cols, int64_t ld,
+                       const void *scalar, void *res, int64_t res_ld, void *stream);
+
+/* res = f(arg).  Replaces EwUnaryMat<Dense,Dense> (src/runtime/local/kernels/EwUnaryMat.h:57-77; scalar functions
+ * EwUnarySca.h:182-206).  SQRT/LN of a negative value and ASIN/ACOS outside [-1,1] are domain errors in the
+ * reference (EwUnarySca.h:134-156): the kernel then sets *dev_status (a device int32, may be NULL) to 1 and the
+ * caller reports DB2_EDOMAIN after synchronising. */
+int db2k_ew_unary(int dtype, int op, const void *arg, int64_t rows, int64_t cols, int64_t ld, void *res,
+                  int64_t res_ld, int32_t *dev_status, void *stream);
+
+/* Row aggregation -> rows x 1 (ld = res_ld).  SUM/PROD/MIN/MAX/MEAN/STDDEV/VAR results have value type `dtype`;
+ * IDXMIN/IDXMAX results are uint64 and ties go to the lowest index.  Replaces AggRow<Dense,Dense>
+ * (src/runtime/local/kernels/AggRow.h:60-161; CUDA twin kernels/CUDA/AggRow.cu:108-143). */
+int db2k_agg_row(int dtype, int op, const void *arg, int64_t rows, int64_t cols, int64_t ld, void *res,
+                 int64_t res_ld, void *stream);
+
+/* Column aggregation -> 1 x cols.  Same result types as db2k_agg_row.  VAR/STDDEV are the population two-pass
+ * form of the reference.  `scratch` is device memory of at least db2k_agg_col_scratch_bytes() bytes.
+ * Replaces AggCol<Dense,Dense> (src/runtime/local/kernels/AggCol.h:58-178; CUDA twin kernels/CUDA/AggCol.cu:45-86). */
+size_t db2k_agg_col_scratch_bytes(int dtype, int op, int64_t rows, int64_t cols);
+int db2k_agg_col(int dtype, int op, const void *arg, int64_t rows, int64_t cols, int64_t ld, void *res,
+                 void *scratch, size_t scratch_bytes, void *stream);
+
+/* Full aggregation -> one DEVICE scalar of `dtype`.  Replaces AggAll<VT,Dense>
+ * (src/runtime/local/kernels/AggAll.h:124-193; CUDA twin kernels/CUDA/AggAll.cu:109-151). */
+size_t db2k_agg_all_scratch_bytes(int dtype, int op, int64_t rows, int64_t cols);
+int db2k_agg_all(int dtype, int op, const void *arg, int64_t rows, int64_t cols, int64_t ld, void *res,
+                 void *scratch, size_t scratch_bytes, void *stream);
+
+/* ------------------------------------------------------------------------- */
+/* db2_*: runtime -- context, matrix handles with residency, operator calls   */
+/* ------------------------------------------------------------------------- */
+
+/* One context per device: a compute stream, stream-ordered pooled device memory, reusable scratch, transfer and
+ * launch counters.  Replaces CUDAContext (src/runtime/local/context/CUDAContext.h:29-114, .cpp:41-137), which is
+ * created by CUDA::createCUDAContext (src/runtime/local/kernels/CUDA/CreateCUDAContext.cpp:4-9) for device 0 only,
+ * allocates with one cudaMalloc per object and runs everything on the default stream. */
+typedef struct db2_context db2_context;
+
+/* A dense row-major matrix with up to two placements (host, device) and "latest" tracking, plus zero-copy row
+ * views that keep their row offset on the device.  Replaces the residency part of DenseMatrix
+ * (src/runtime/local/datastructures/DenseMatrix.cpp:126-237), MetaDataObject/DataPlacement
+ * (MetaDataObject.h:39-57, DataPlacement.h:29-42) and AllocationDescriptorCUDA (AllocationDescriptorCUDA.h:24-75). */
+typedef struct db2_matrix db2_matrix;
+
+typedef struct db2_stats {
+    uint64_t h2d_bytes, d2h_bytes, d2d_bytes; /* transfers issued by the residency layer            */
+    uint64_t allocs, alloc_bytes, frees;      /* pooled device allocations                          */
+    uint64_t launches;                        /* kernels launched through this context              */
+    uint64_t live_bytes, peak_bytes;          /* device bytes held by matrices / scratch            */
+} db2_stats;
+
+int db2_context_create(int device, db2_context **ctx);
+int db2_context_destroy(db2_context *ctx);
+int db2_context_device(const db2_context *ctx, int *device);
+void *db2_context_stream(db2_context *ctx);
+int db2_context_sync(db2_context *ctx);
+int db2_context_stats(db2_context *ctx, db2_stats *out);
+
+/* device-only matrix (DataObjectFactory::create<DenseMatrix<VT>>(rows, cols, zero, &alloc_desc)) */
+int db2_matrix_create(db2_context *ctx, int dtype, int64_t rows, int64_t cols, int zero, db2_matrix **out);
+/* matrix whose host placement is the caller's buffer (borrowed, must outlive the handle); the device placement is
+ * created on first use by a kernel, with one asynchronous copy (pinned staging is the caller's choice). */
+int db2_matrix_wrap_host(db2_context *ctx, int dtype, int64_t rows, int64_t cols, int64_t ld, void *host,
+                         db2_matrix **out);
+/* matrix whose device placement is the caller's device buffer (borrowed) */
+int db2_matrix_wrap_device(db2_context *ctx, int dtype, int64_t rows, int64_t cols, int64_t ld, void *dptr,
+                           db2_matrix **out);
+/* zero-copy view of rows [r0, r1) (DenseMatrix view constructor, DenseMatrix.cpp:98-115) */
+int db2_matrix_slice_rows(db2_matrix *m, int64_t r0, int64_t r1, db2_matrix **view);
+int db2_matrix_incref(db2_matrix *m);
+int db2_matrix_decref(db2_matrix *m); /* frees at zero (DataObjectFactory::destroy) */
+int db2_matrix_info(const db2_matrix *m, int *dtype, int64_t *rows, int64_t *cols);
+/* device pointer of element (0,0) and leading dimension; makes the device placement current first */
+int db2_matrix_device_ptr(db2_matrix *m, void **dptr, int64_t *ld);
+/* copies the latest values into dst (rows x cols, leading dimension dst_ld); synchronises the stream */
+int db2_matrix_to_host(db2_matrix *m, void *dst, int64_t dst_ld);
+
+/* Operator calls.  *res == NULL on entry means "the kernel allocates the result" (the reference's convention,
+ * e.g. kernels/CUDA/AggRow.cu:121-122); otherwise the given matrix is overwritten. */
+int db2_ewBinaryMat(db2_context *ctx, int op, db2_matrix **res, db2_matrix *lhs, db2_matrix *rhs);
+int db2_ewBinaryObjSca(db2_context *ctx, int op, db2_matrix **res, db2_matrix *lhs, const void *scalar);
+int db2_ewUnaryMat(db2_context *ctx, int op, db2_matrix **res, db2_matrix *arg);
+int db2_aggRow(db2_context *ctx, int op, db2_matrix **res, db2_matrix *arg);
+int db2_aggCol(db2_context *ctx, int op, db2_matrix **res, db2_matrix *arg);
+/* res_host: host pointer to one value of the matrix's value type; synchronises */
+int db2_aggAll(db2_context *ctx, int op, void *res_host, db2_matrix *arg);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* DAPHNE_B200_H */

@@ -1,0 +1,359 @@
+/*
+ * TEST INFRASTRUCTURE -- not part of the product.
+ *
+ * Plain-C restatement of the CPU kernels of DAPHNE (daphne-eu/daphne, src/runtime/local/kernels) that the CUDA
+ * library in daphne_b200/ replaces.  It exists only as the checker for tests/, for __graft_entry__.smoke() and for
+ * the cpu_baseline leg of bench.py; nothing in daphne_b200/ may call it.
+ *
+ * Every function walks the data in the same order and with the same scalar expressions as the reference function it
+ * cites, so that floating-point results carry the same rounding as the reference's CPU kernels built with gcc at
+ * -O2 without -ffast-math (this file must be compiled with -ffp-contract=off so that no a*b+c is fused).
+ * Pinned against: the literal expected values of the reference's unit tests (tests/golden/*.json, taken from
+ * test/runtime/local/kernels/{AggRow,AggCol,AggAll,EwBinaryMat,EwBinaryObjSca,EwUnaryMat,Syrk,MatMul,Gemv,Solve,
+ * CTable,Transpose}Test.cpp) and against the reference's own kernels compiled from its sources (oracle/_ref,
+ * tests/test_oracle_vs_ref.py).
+ *
+ * Conventions: row-major, leading dimension in elements, op codes = the reference's enum values
+ * (BinaryOpCode.h:29-56, UnaryOpCode.h:26-56, AggOpCode.h:25-35).  Return 0 = ok, 1 = invalid argument
+ * (the reference throws std::runtime_error), 5 = domain error (std::domain_error).
+ */
+#include <math.h>
+#include <stddef.h>
+#include <stdint.h>
+#include <stdlib.h>
+#include <string.h>
+
+enum { ADD = 0, SUB, MUL, DIV, POW, MOD, LOG, EQ, NEQ, LT, LE, GT, GE, MIN, MAX, AND, OR, BITWISE_AND };
+enum { U_MINUS = 0, U_ABS, U_SIGN, U_SQRT, U_EXP, U_LN, U_SIN, U_COS, U_TAN, U_ASIN, U_ACOS, U_ATAN, U_SINH, U_COSH,
+       U_TANH, U_FLOOR, U_CEIL, U_ROUND, U_ISNAN };
+enum { A_SUM = 0, A_PROD, A_MIN, A_MAX, A_IDXMIN, A_IDXMAX, A_MEAN, A_STDDEV, A_VAR };
+
+/* ------------------------------------------------------------------------------------------------------------- */
+/* scalar ops: EwBinarySca.h:138-166 (MAKE_EW_BINARY_SCA lines)                                                   */
+/* ------------------------------------------------------------------------------------------------------------- */
+#define DEF_BIN(NAME, VT)                                                                                              \
+    static VT bin_##NAME(int op, VT a, VT b) {                                                                         \
+        switch (op) {                                                                                                  \
+        case ADD: return a + b;                                                                                        \
+        case SUB: return a - b;                                                                                        \
+        case MUL: return a * b;                                                                                        \
+        case DIV: return a / b;                                                                                        \
+        case POW: return (VT)pow((double)a, (double)b);                                                                \
+        case MOD: return (VT)fmod((double)a, (double)b);                                                               \
+        case LOG: return (VT)(log((double)a) / log((double)b));                                                        \
+        case EQ: return (VT)(a == b);                                                                                  \
+        case NEQ: return (VT)(a != b);                                                                                 \
+        case LT: return (VT)(a < b);                                                                                   \
+        case LE: return (VT)(a <= b);                                                                                  \
+        case GT: return (VT)(a > b);                                                                                   \
+        case GE: return (VT)(a >= b);                                                                                  \
+        case MIN: return (b < a) ? b : a; /* std::min */                                                               \
+        case MAX: return (a < b) ? b : a; /* std::max */                                                               \
+        case AND: return (VT)(a && b);                                                                                 \
+        case OR: return (VT)(a || b);                                                                                  \
+        case BITWISE_AND: return (VT)((int64_t)a & (int64_t)b);                                                        \
+        default: return a;                                                                                             \
+        }                                                                                                              \
+    }
+DEF_BIN(f64, double)
+DEF_BIN(i64, int64_t)
+/* float: fmodf / logf are what std::fmod(float,float) and std::log(float) resolve to */
+static float bin_f32(int op, float a, float b) {
+    switch (op) {
+    case ADD: return a + b;
+    case SUB: return a - b;
+    case MUL: return a * b;
+    case DIV: return a / b;
+    case POW: return (float)pow((double)a, (double)b);
+    case MOD: return fmodf(a, b);
+    case LOG: return logf(a) / logf(b);
+    case EQ: return (float)(a == b);
+    case NEQ: return (float)(a != b);
+    case LT: return (float)(a < b);
+    case LE: return (float)(a <= b);
+    case GT: return (float)(a > b);
+    case GE: return (float)(a >= b);
+    case MIN: return (b < a) ? b : a;
+    case MAX: return (a < b) ? b : a;
+    case AND: return (float)(a && b);
+    case OR: return (float)(a || b);
+    default: return a;
+    }
+}
+
+/* EwUnarySca.h:182-206; *bad is set where the reference throws std::domain_error (:134-156) */
+static double un_f64(int op, double x, int *bad) {
+    switch (op) {
+    case U_MINUS: return -x;
+    case U_ABS: return fabs(x);
+    case U_SIGN: return (x == 0) ? 0 : ((x < 0) ? -1 : ((x > 0) ? 1 : NAN));
+    case U_SQRT: if (-0.0 > x) *bad = 1; return sqrt(x);
+    case U_EXP: return exp(x);
+    case U_LN: if (-0.0 > x) *bad = 1; return log(x);
+    case U_SIN: return sin(x);
+    case U_COS: return cos(x);
+    case U_TAN: return tan(x);
+    case U_ASIN: if (-1.0 > x || x > 1.0) *bad = 1; return asin(x);
+    case U_ACOS: if (-1.0 > x || x > 1.0) *bad = 1; return acos(x);
+    case U_ATAN: return atan(x);
+    case U_SINH: return sinh(x);
+    case U_COSH: return cosh(x);
+    case U_TANH: return tanh(x);
+    case U_FLOOR: return floor(x);
+    case U_CEIL: return ceil(x);
+    case U_ROUND: return round(x);
+    case U_ISNAN: return (double)(x != x);
+    default: return x;
+    }
+}
+static float un_f32(int op, float x, int *bad) {
+    switch (op) {
+    case U_MINUS: return -x;
+    case U_ABS: return fabsf(x);
+    case U_SIGN: return (x == 0) ? 0 : ((x < 0) ? -1 : ((x > 0) ? 1 : NAN));
+    case U_SQRT: if (-0.0 > x) *bad = 1; return sqrtf(x);
+    case U_EXP: return expf(x);
+    case U_LN: if (-0.0 > x) *bad = 1; return logf(x);
+    case U_SIN: return sinf(x);
+    case U_COS: return cosf(x);
+    case U_TAN: return tanf(x);
+    case U_ASIN: if (-1.0 > x || x > 1.0) *bad = 1; return asinf(x);
+    case U_ACOS: if (-1.0 > x || x > 1.0) *bad = 1; return acosf(x);
+    case U_ATAN: return atanf(x);
+    case U_SINH: return sinhf(x);
+    case U_COSH: return coshf(x);
+    case U_TANH: return tanhf(x);
+    case U_FLOOR: return floorf(x);
+    case U_CEIL: return ceilf(x);
+    case U_ROUND: return roundf(x);
+    case U_ISNAN: return (float)(x != x);
+    default: return x;
+    }
+}
+static int64_t un_i64(int op, int64_t x, int *bad) {
+    switch (op) {
+    case U_MINUS: return -x;
+    case U_ABS: return x < 0 ? -x : x;
+    case U_SIGN: return (x == 0) ? 0 : ((x < 0) ? -1 : 1);
+    case U_FLOOR: case U_CEIL: case U_ROUND: return x;
+    case U_ISNAN: return 0;
+    default: return (int64_t)un_f64(op, (double)x, bad);
+    }
+}
+
+/* ------------------------------------------------------------------------------------------------------------- */
+/* EwBinaryMat<Dense,Dense,Dense>  (EwBinaryMat.h:54-108)                                                         */
+/* ------------------------------------------------------------------------------------------------------------- */
+#define DEF_EW_BINARY(NAME, VT)                                                                                        \
+    int orc_ew_binary_##NAME(int op, const VT *lhs, int64_t lr, int64_t lc, int64_t lld, const VT *rhs, int64_t rr,    \
+                             int64_t rc, int64_t rld, VT *res, int64_t res_ld) {                                       \
+        if (lr == rr && lc == rc) {                                                                                    \
+            for (int64_t r = 0; r < lr; r++)                                                                           \
+                for (int64_t c = 0; c < lc; c++)                                                                       \
+                    res[r * res_ld + c] = bin_##NAME(op, lhs[r * lld + c], rhs[r * rld + c]);                          \
+        } else if (lc == rc && (rr == 1 || lr == 1)) {                                                                 \
+            for (int64_t r = 0; r < lr; r++)                                                                           \
+                for (int64_t c = 0; c < lc; c++)                                                                       \
+                    res[r * res_ld + c] = bin_##NAME(op, lhs[r * lld + c], rhs[c]);                                    \
+        } else if (lr == rr && (rc == 1 || lc == 1)) {                                                                 \
+            for (int64_t r = 0; r < lr; r++)                                                                           \
+                for (int64_t c = 0; c < lc; c++)                                                                       \
+                    res[r * res_ld + c] = bin_##NAME(op, lhs[r * lld + c], rhs[r * rld]);                              \
+        } else                                                                                                         \
+            return 1;                                                                                                  \
+        return 0;                                                                                                      \
+    }                                                                                                                  \
+    /* EwBinaryObjSca<Dense,Dense,VT> (EwBinaryObjSca.h:58-79) */                                                      \
+    int orc_ew_binary_sca_##NAME(int op, const VT *lhs, int64_t rows, int64_t cols, int64_t ld, VT s, VT *res,         \
+                                 int64_t res_ld) {                                                                     \
+        for (int64_t r = 0; r < rows; r++)                                                                             \
+            for (int64_t c = 0; c < cols; c++)                                                                         \
+                res[r * res_ld + c] = bin_##NAME(op, lhs[r * ld + c], s);                                              \
+        return 0;                                                                                                      \
+    }                                                                                                                  \
+    /* EwUnaryMat<Dense,Dense> (EwUnaryMat.h:57-77) */                                                                 \
+    int orc_ew_unary_##NAME(int op, const VT *arg, int64_t rows, int64_t cols, int64_t ld, VT *res, int64_t res_ld) {  \
+        int bad = 0;                                                                                                   \
+        for (int64_t r = 0; r < rows; r++)                                                                             \
+            for (int64_t c = 0; c < cols; c++)                                                                         \
+                res[r * res_ld + c] = un_##NAME(op, arg[r * ld + c], &bad);                                            \
+        return bad ? 5 : 0;                                                                                            \
+    }
+DEF_EW_BINARY(f64, double)
+DEF_EW_BINARY(f32, float)
+DEF_EW_BINARY(i64, int64_t)
+
+/* ------------------------------------------------------------------------------------------------------------- */
+/* aggregations                                                                                                   */
+/* ------------------------------------------------------------------------------------------------------------- */
+#define NEUTRAL_MIN_f64 INFINITY
+#define NEUTRAL_MAX_f64 (-INFINITY)
+#define NEUTRAL_MIN_f32 INFINITY
+#define NEUTRAL_MAX_f32 (-INFINITY)
+#define NEUTRAL_MIN_i64 INT64_MAX
+#define NEUTRAL_MAX_i64 INT64_MIN
+#define SQRT_f64(x) sqrt(x)
+#define SQRT_f32(x) ((float)sqrt(x)) /* unqualified sqrt(float) in the reference binds to the double overload set */
+#define SQRT_i64(x) ((int64_t)sqrt((double)(x)))
+
+static int agg_bin_op(int op) {
+    switch (op) {
+    case A_SUM: case A_MEAN: case A_STDDEV: case A_VAR: return ADD;
+    case A_PROD: return MUL;
+    case A_MIN: return MIN;
+    case A_MAX: return MAX;
+    default: return -1;
+    }
+}
+
+#define DEF_AGG(NAME, VT)                                                                                              \
+    /* AggRow<Dense,Dense> (AggRow.h:60-161).  idx results go to res_idx (uint64), others to res. */                   \
+    int orc_agg_row_##NAME(int op, const VT *arg, int64_t rows, int64_t cols, int64_t ld, VT *res, uint64_t *res_idx,  \
+                           int64_t res_ld) {                                                                           \
+        if (op == A_IDXMIN || op == A_IDXMAX) {                                                                        \
+            for (int64_t r = 0; r < rows; r++) {                                                                       \
+                const VT *row = arg + r * ld;                                                                          \
+                VT best = row[0];                                                                                      \
+                uint64_t idx = 0;                                                                                      \
+                for (int64_t c = 1; c < cols; c++)                                                                     \
+                    if (op == A_IDXMIN ? (row[c] < best) : (row[c] > best)) {                                          \
+                        best = row[c];                                                                                 \
+                        idx = (uint64_t)c;                                                                             \
+                    }                                                                                                  \
+                res_idx[r * res_ld] = idx;                                                                             \
+            }                                                                                                          \
+            return 0;                                                                                                  \
+        }                                                                                                              \
+        const int bop = agg_bin_op(op);                                                                                \
+        if (bop < 0)                                                                                                   \
+            return 1;                                                                                                  \
+        for (int64_t r = 0; r < rows; r++) {                                                                           \
+            const VT *row = arg + r * ld;                                                                              \
+            VT agg = row[0];                                                                                           \
+            for (int64_t c = 1; c < cols; c++)                                                                         \
+                agg = bin_##NAME(bop, agg, row[c]);                                                                    \
+            res[r * res_ld] = agg;                                                                                     \
+        }                                                                                                              \
+        if (op == A_SUM || op == A_PROD || op == A_MIN || op == A_MAX)                                                 \
+            return 0;                                                                                                  \
+        for (int64_t r = 0; r < rows; r++)                                                                             \
+            res[r * res_ld] = (VT)(res[r * res_ld] / (size_t)cols);                                                    \
+        if (op == A_MEAN)                                                                                              \
+            return 0;                                                                                                  \
+        for (int64_t r = 0; r < rows; r++) {                                                                           \
+            const VT *row = arg + r * ld;                                                                              \
+            VT t = 0;                                                                                                  \
+            for (int64_t c = 0; c < cols; c++) {                                                                       \
+                VT val = row[c] - res[r * res_ld];                                                                     \
+                t = t + val * val;                                                                                     \
+            }                                                                                                          \
+            t = (VT)(t / (size_t)cols);                                                                                \
+            res[r * res_ld] = (op == A_STDDEV) ? SQRT_##NAME(t) : t;                                                   \
+        }                                                                                                              \
+        return 0;                                                                                                      \
+    }                                                                                                                  \
+    /* AggCol<Dense,Dense> (AggCol.h:58-178) */                                                                        \
+    int orc_agg_col_##NAME(int op, const VT *arg, int64_t rows, int64_t cols, int64_t ld, VT *res,                     \
+                           uint64_t *res_idx) {                                                                        \
+        if (op == A_IDXMIN || op == A_IDXMAX) {                                                                        \
+            VT *tmp = (VT *)malloc(sizeof(VT) * (size_t)(cols ? cols : 1));                                            \
+            memcpy(tmp, arg, sizeof(VT) * (size_t)cols);                                                               \
+            for (int64_t c = 0; c < cols; c++)                                                                         \
+                res_idx[c] = 0;                                                                                        \
+            for (int64_t r = 1; r < rows; r++)                                                                         \
+                for (int64_t c = 0; c < cols; c++) {                                                                   \
+                    const VT x = arg[r * ld + c];                                                                      \
+                    if (op == A_IDXMIN ? (x < tmp[c]) : (x > tmp[c])) {                                                \
+                        tmp[c] = x;                                                                                    \
+                        res_idx[c] = (uint64_t)r;                                                                      \
+                    }                                                                                                  \
+                }                                                                                                      \
+            free(tmp);                                                                                                 \
+            return 0;                                                                                                  \
+        }                                                                                                              \
+        const int bop = agg_bin_op(op);                                                                                \
+        if (bop < 0)                                                                                                   \
+            return 1;                                                                                                  \
+        for (int64_t c = 0; c < cols; c++)                                                                             \
+            res[c] = arg[c];                                                                                           \
+        for (int64_t r = 1; r < rows; r++)                                                                             \
+            for (int64_t c = 0; c < cols; c++)                                                                         \
+                res[c] = bin_##NAME(bop, res[c], arg[r * ld + c]);                                                     \
+        if (op == A_SUM || op == A_PROD || op == A_MIN || op == A_MAX)                                                 \
+            return 0;                                                                                                  \
+        for (int64_t c = 0; c < cols; c++)                                                                             \
+            res[c] = (VT)(res[c] / (size_t)rows);                                                                      \
+        if (op == A_MEAN)                                                                                              \
+            return 0;                                                                                                  \
+        VT *t = (VT *)calloc((size_t)(cols ? cols : 1), sizeof(VT));                                                   \
+        for (int64_t r = 0; r < rows; r++)                                                                             \
+            for (int64_t c = 0; c < cols; c++) {                                                                       \
+                VT val = arg[r * ld + c] - res[c];                                                                     \
+                t[c] = t[c] + val * val;                                                                               \
+            }                                                                                                          \
+        for (int64_t c = 0; c < cols; c++) {                                                                           \
+            t[c] = (VT)(t[c] / (size_t)rows);                                                                          \
+            if (op == A_STDDEV)                                                                                        \
+                t[c] = SQRT_##NAME(t[c]);                                                                              \
+        }                                                                                                              \
+        memcpy(res, t, sizeof(VT) * (size_t)cols);                                                                     \
+        free(t);                                                                                                       \
+        return 0;                                                                                                      \
+    }                                                                                                                  \
+    /* aggAllArray (AggAll.h:64-96): four interleaved accumulators, pairwise fold, then the tail */                    \
+    static VT agg_all_array_##NAME(int bop, const VT *v, size_t n, VT neutral) {                                       \
+        VT agg;                                                                                                        \
+        if (n) {                                                                                                       \
+            VT a0 = neutral, a1 = neutral, a2 = neutral, a3 = neutral;                                                 \
+            for (size_t i = 0; i < n / 4 * 4; i += 4) {                                                                \
+                a0 = bin_##NAME(bop, a0, v[i]);                                                                        \
+                a1 = bin_##NAME(bop, a1, v[i + 1]);                                                                    \
+                a2 = bin_##NAME(bop, a2, v[i + 2]);                                                                    \
+                a3 = bin_##NAME(bop, a3, v[i + 3]);                                                                    \
+            }                                                                                                          \
+            agg = bin_##NAME(bop, bin_##NAME(bop, a0, a1), bin_##NAME(bop, a2, a3));                                   \
+            for (size_t i = 0; i < n % 4; i++)                                                                         \
+                agg = bin_##NAME(bop, agg, v[n / 4 * 4 + i]);                                                          \
+        } else                                                                                                         \
+            agg = neutral;                                                                                             \
+        return agg;                                                                                                    \
+    }                                                                                                                  \
+    /* AggAll<VT,Dense> (AggAll.h:124-193) */                                                                          \
+    int orc_agg_all_##NAME(int op, const VT *arg, int64_t rows, int64_t cols, int64_t ld, VT *res) {                   \
+        const int bop = agg_bin_op(op);                                                                                \
+        if (bop < 0)                                                                                                   \
+            return 1;                                                                                                  \
+        VT neutral = 0;                                                                                                \
+        if (op == A_PROD) neutral = 1;                                                                                 \
+        if (op == A_MIN) neutral = NEUTRAL_MIN_##NAME;                                                                 \
+        if (op == A_MAX) neutral = NEUTRAL_MAX_##NAME;                                                                 \
+        VT agg;                                                                                                        \
+        if (cols == ld || rows == 1)                                                                                   \
+            agg = agg_all_array_##NAME(bop, arg, (size_t)(rows * cols), neutral);                                      \
+        else {                                                                                                         \
+            agg = neutral;                                                                                             \
+            for (int64_t r = 0; r < rows; r++)                                                                         \
+                agg = bin_##NAME(bop, agg, agg_all_array_##NAME(bop, arg + r * ld, (size_t)cols, neutral));            \
+        }                                                                                                              \
+        if (op == A_SUM || op == A_PROD || op == A_MIN || op == A_MAX) {                                               \
+            *res = agg;                                                                                                \
+            return 0;                                                                                                  \
+        }                                                                                                              \
+        agg = (VT)(agg / ((size_t)cols * (size_t)rows));                                                               \
+        if (op == A_MEAN) {                                                                                            \
+            *res = agg;                                                                                                \
+            return 0;                                                                                                  \
+        }                                                                                                              \
+        VT sd = 0;                                                                                                     \
+        for (int64_t r = 0; r < rows; r++)                                                                             \
+            for (int64_t c = 0; c < cols; c++) {                                                                       \
+                VT val = arg[r * ld + c] - agg;                                                                        \
+                sd = sd + val * val;                                                                                   \
+            }                                                                                                          \
+        sd = (VT)(sd / ((size_t)cols * (size_t)rows));                                                                 \
+        *res = (op == A_VAR) ? sd : SQRT_##NAME(sd);                                                                   \
+        return 0;                                                                                                      \
+    }
+DEF_AGG(f64, double)
+DEF_AGG(f32, float)
+DEF_AGG(i64, int64_t)

@@ -1,0 +1,186 @@
+"""Parity of the elementwise CUDA kernels with the CPU oracle (EwBinaryMat / EwBinaryObjSca / EwUnaryMat)."""
+import numpy as np
+import pytest
+
+from tests.util import (RTOL_TRANSCENDENTAL_F32, RTOL_TRANSCENDENTAL_F64, assert_bits_equal, assert_close_rel,
+                        rng_matrix)
+
+pytestmark = pytest.mark.gpu
+
+EXACT_BIN = ["ADD", "SUB", "MUL", "DIV", "EQ", "NEQ", "LT", "LE", "GT", "GE", "MIN", "MAX", "AND", "OR"]
+SHAPES = [(1, 1), (3, 5), (7, 32), (257, 33), (1000, 64), (4099, 50), (1, 100003), (100003, 1), (513, 1024)]
+
+
+def _k():
+    import daphne_b200.kernels as k
+    from oracle import pyoracle as o
+    return k, o
+
+
+@pytest.mark.parametrize("dtype", [np.float64, np.float32, np.int64])
+@pytest.mark.parametrize("opname", EXACT_BIN)
+def test_binary_same_shape_bit_exact(ctx, dtype, opname):
+    k, o = _k()
+    op = k.BinaryOpCode[opname]
+    for i, (r, c) in enumerate(SHAPES):
+        a = rng_matrix(10 + i, r, c, dtype)
+        b = rng_matrix(20 + i, r, c, dtype)
+        if np.dtype(dtype) == np.int64 and opname == "DIV":
+            b[b == 0] = 7
+        if opname in ("EQ", "NEQ", "LE", "GE", "AND", "OR"):
+            b[::2] = a[::2]  # make ties / equalities happen
+            a[1::3] = 0
+        got = k.ewBinaryMat(op, k.DenseMatrix.from_numpy(ctx, a), k.DenseMatrix.from_numpy(ctx, b)).to_numpy()
+        assert_bits_equal(got, o.ewBinaryMat(op, a, b), f"{opname} {dtype.__name__} {r}x{c}")
+
+
+@pytest.mark.parametrize("dtype", [np.float64, np.float32, np.int64])
+@pytest.mark.parametrize("opname", ["ADD", "SUB", "MUL", "DIV", "MAX", "MIN", "NEQ", "LE"])
+def test_binary_broadcast_bit_exact(ctx, dtype, opname):
+    k, o = _k()
+    op = k.BinaryOpCode[opname]
+    for i, (r, c) in enumerate(SHAPES):
+        a = rng_matrix(30 + i, r, c, dtype)
+        rv = rng_matrix(40 + i, 1, c, dtype)
+        cv = rng_matrix(50 + i, r, 1, dtype)
+        if np.dtype(dtype) == np.int64:
+            rv[rv == 0] = 3
+            cv[cv == 0] = 3
+        A = k.DenseMatrix.from_numpy(ctx, a)
+        got_r = k.ewBinaryMat(op, A, k.DenseMatrix.from_numpy(ctx, rv)).to_numpy()
+        assert_bits_equal(got_r, o.ewBinaryMat(op, a, rv), f"{opname} rowvec {r}x{c}")
+        got_c = k.ewBinaryMat(op, A, k.DenseMatrix.from_numpy(ctx, cv)).to_numpy()
+        assert_bits_equal(got_c, o.ewBinaryMat(op, a, cv), f"{opname} colvec {r}x{c}")
+
+
+def test_binary_special_values_bit_exact(ctx):
+    k, o = _k()
+    sp = np.array([0.0, -0.0, 1.0, -1.0, np.inf, -np.inf, np.nan, 5e-324, 1.7976931348623157e308, 1e-310, 3.0, 0.1])
+    a = np.repeat(sp, len(sp)).reshape(len(sp), len(sp)).copy()
+    b = np.tile(sp, len(sp)).reshape(len(sp), len(sp)).copy()
+    for opname in ["ADD", "SUB", "MUL", "DIV", "MIN", "MAX", "EQ", "NEQ", "LT", "GE", "AND", "OR"]:
+        op = k.BinaryOpCode[opname]
+        got = k.ewBinaryMat(op, k.DenseMatrix.from_numpy(ctx, a), k.DenseMatrix.from_numpy(ctx, b)).to_numpy()
+        exp = o.ewBinaryMat(op, a, b)
+        # NaN payload/sign of a produced NaN is not defined by IEEE; compare NaN-ness there and bits elsewhere
+        nan = np.isnan(exp)
+        assert np.array_equal(np.isnan(got), nan), opname
+        assert_bits_equal(np.where(nan, 0.0, got), np.where(nan, 0.0, exp), f"special {opname}")
+
+
+def test_binary_shape_mismatch_raises(ctx):
+    k, o = _k()
+    a = k.DenseMatrix.from_numpy(ctx, np.ones((4, 5)))
+    b = k.DenseMatrix.from_numpy(ctx, np.ones((3, 2)))
+    with pytest.raises(k.Db2Error, match="lhs and rhs must either have the same dimensions"):
+        k.ewBinaryMat(k.BinaryOpCode.ADD, a, b)
+    with pytest.raises(o.OracleError):
+        o.ewBinaryMat(0, np.ones((4, 5)), np.ones((3, 2)))
+
+
+def test_binary_row_views_keep_their_offset(ctx):
+    """A row view of a device-resident matrix must address its own rows (the reference's view returns the parent's
+    base pointer, src/runtime/local/datastructures/DenseMatrix.cpp:98-115,235-236)."""
+    k, o = _k()
+    a = rng_matrix(1, 1000, 32)
+    b = rng_matrix(2, 1000, 32)
+    A, B = k.DenseMatrix.from_numpy(ctx, a), k.DenseMatrix.from_numpy(ctx, b)
+    A.device_ptr()
+    got = k.ewBinaryMat(k.BinaryOpCode.SUB, A.slice_rows(100, 613), B.slice_rows(300, 813)).to_numpy()
+    assert_bits_equal(got, a[100:613] - b[300:813], "views")
+
+
+def test_binary_strided_and_unaligned_host_layouts(ctx):
+    k, o = _k()
+    big = rng_matrix(3, 300, 40)
+    a = big[:, 3:36]  # ld 40, cols 33, first element not 16-byte aligned
+    b = rng_matrix(4, 300, 33)
+    got = k.ewBinaryMat(k.BinaryOpCode.MUL, k.DenseMatrix.from_numpy(ctx, a), k.DenseMatrix.from_numpy(ctx, b))
+    assert_bits_equal(got.to_numpy(), a * b, "strided")
+
+
+@pytest.mark.parametrize("dtype", [np.float64, np.float32, np.int64])
+@pytest.mark.parametrize("opname", ["ADD", "SUB", "MUL", "DIV", "MAX", "MIN", "NEQ", "GT", "EQ"])
+def test_binary_scalar_bit_exact(ctx, dtype, opname):
+    k, o = _k()
+    op = k.BinaryOpCode[opname]
+    for i, (r, c) in enumerate(SHAPES):
+        a = rng_matrix(60 + i, r, c, dtype)
+        s = 3 if np.dtype(dtype) == np.int64 else 2.5
+        got = k.ewBinaryObjSca(op, k.DenseMatrix.from_numpy(ctx, a), s).to_numpy()
+        assert_bits_equal(got, o.ewBinaryObjSca(op, a, s), f"{opname} scalar {r}x{c}")
+
+
+def test_pow_log_mod_within_ulps(ctx):
+    k, o = _k()
+    a = np.abs(rng_matrix(70, 513, 37)) + 0.1
+    b = rng_matrix(71, 513, 37, kind="uniform") * 3 + 0.5
+    A, B = k.DenseMatrix.from_numpy(ctx, a), k.DenseMatrix.from_numpy(ctx, b)
+    for opname in ["POW", "LOG"]:
+        op = k.BinaryOpCode[opname]
+        assert_close_rel(k.ewBinaryMat(op, A, B).to_numpy(), o.ewBinaryMat(op, a, b), RTOL_TRANSCENDENTAL_F64, opname)
+    assert_bits_equal(k.ewBinaryMat(k.BinaryOpCode.MOD, A, B).to_numpy(), o.ewBinaryMat(k.BinaryOpCode.MOD, a, b),
+                      "MOD")
+    # x^2 (the form the standardisation and k-means scripts use) is a single rounding on both sides
+    z = rng_matrix(72, 1000, 32)
+    got = k.ewBinaryObjSca(k.BinaryOpCode.POW, k.DenseMatrix.from_numpy(ctx, z), 2.0).to_numpy()
+    assert_bits_equal(got, o.ewBinaryObjSca(k.BinaryOpCode.POW, z, 2.0), "POW 2")
+    got = k.ewBinaryObjSca(k.BinaryOpCode.POW, k.DenseMatrix.from_numpy(ctx, np.abs(z)), 1.7).to_numpy()
+    assert_close_rel(got, o.ewBinaryObjSca(k.BinaryOpCode.POW, np.abs(z), 1.7), RTOL_TRANSCENDENTAL_F64, "POW 1.7")
+
+
+@pytest.mark.parametrize("dtype", [np.float64, np.float32])
+def test_unary(ctx, dtype):
+    k, o = _k()
+    exact = ["MINUS", "ABS", "SIGN", "SQRT", "FLOOR", "CEIL", "ROUND", "ISNAN"]
+    approx = ["EXP", "LN", "SIN", "COS", "TAN", "ATAN", "SINH", "COSH", "TANH"]
+    rt = RTOL_TRANSCENDENTAL_F64 if dtype == np.float64 else RTOL_TRANSCENDENTAL_F32
+    for i, (r, c) in enumerate(SHAPES[:6]):
+        a = np.abs(rng_matrix(80 + i, r, c, dtype, kind="uniform")) * 4 + 0.01
+        a.reshape(-1)[::7] = 0.0
+        a.reshape(-1)[3::11] += 0.5
+        A = k.DenseMatrix.from_numpy(ctx, a)
+        for name in exact:
+            op = k.UnaryOpCode[name]
+            src = a if name in ("SQRT",) else (a - 2.0).astype(dtype)
+            S = A if name in ("SQRT",) else k.DenseMatrix.from_numpy(ctx, src)
+            assert_bits_equal(k.ewUnaryMat(op, S).to_numpy(), o.ewUnaryMat(op, src), f"{name} {r}x{c}")
+        for name in approx:
+            op = k.UnaryOpCode[name]
+            src = (a + 0.5).astype(dtype) if name == "LN" else (a - 2.0).astype(dtype)
+            got = k.ewUnaryMat(op, k.DenseMatrix.from_numpy(ctx, src)).to_numpy()
+            assert_close_rel(got, o.ewUnaryMat(op, src), rt, f"{name} {r}x{c}", scale=1e-3)
+        u = (rng_matrix(90 + i, r, c, dtype, kind="uniform") * 2 - 1).astype(dtype)
+        for name in ["ASIN", "ACOS"]:
+            op = k.UnaryOpCode[name]
+            got = k.ewUnaryMat(op, k.DenseMatrix.from_numpy(ctx, u)).to_numpy()
+            assert_close_rel(got, o.ewUnaryMat(op, u), rt, name, scale=1e-3)
+
+
+def test_unary_domain_error(ctx):
+    """sqrt/ln of a negative value and asin/acos outside [-1,1] throw std::domain_error in the reference
+    (EwUnarySca.h:134-156,186-195)."""
+    k, o = _k()
+    a = np.ones((50, 7))
+    a[33, 4] = -1e-3
+    for name in ["SQRT", "LN"]:
+        with pytest.raises(k.Db2Error, match="invalid argument"):
+            k.ewUnaryMat(k.UnaryOpCode[name], k.DenseMatrix.from_numpy(ctx, a))
+        with pytest.raises(o.OracleError):
+            o.ewUnaryMat(k.UnaryOpCode[name], a)
+    b = np.zeros((5, 5))
+    b[2, 2] = 1.5
+    with pytest.raises(k.Db2Error):
+        k.ewUnaryMat(k.UnaryOpCode.ASIN, k.DenseMatrix.from_numpy(ctx, b))
+    # the context stays usable, -0.0 is inside the domain
+    z = np.array([[-0.0, 0.0, 4.0]])
+    assert_bits_equal(k.ewUnaryMat(k.UnaryOpCode.SQRT, k.DenseMatrix.from_numpy(ctx, z)).to_numpy(),
+                      o.ewUnaryMat(k.UnaryOpCode.SQRT, z), "sqrt after error")
+
+
+def test_empty_matrices(ctx):
+    k, o = _k()
+    e = k.DenseMatrix.from_numpy(ctx, np.zeros((0, 5)))
+    assert k.ewBinaryMat(k.BinaryOpCode.ADD, e, e).to_numpy().shape == (0, 5)
+    assert k.ewBinaryObjSca(k.BinaryOpCode.MUL, e, 2.0).to_numpy().shape == (0, 5)
+    assert k.ewUnaryMat(k.UnaryOpCode.ABS, e).to_numpy().shape == (0, 5)
