@@ -153,8 +153,9 @@ template <typename VT> __device__ __forceinline__ VT binary_op_rt(int op, VT a, 
 
 // Unary ops.  `bad` is set when the reference would throw std::domain_error (EwUnarySca.h:134-156,186-195).
 template <int OP, typename VT> __device__ __forceinline__ VT unary_op(VT x, bool &bad) {
-    // integer value types: rounding/identity-like ops are exact, the rest evaluates in double and casts back
-    using FT = std::conditional_t<std::is_same_v<VT, float>, float, double>;
+    // The reference spells the math functions unqualified (sqrt(arg), exp(arg), ...; EwUnarySca.h:186-202), which
+    // for float and integer arguments evaluates the C double function and converts the result back; same here.
+    using FT = double;
     if constexpr (OP == DB2_U_MINUS) {
         if constexpr (std::is_integral_v<VT>)
             return (VT)(0 - (uint64_t)x);
@@ -196,10 +197,7 @@ template <int OP, typename VT> __device__ __forceinline__ VT unary_op(VT x, bool
         if constexpr (OP == DB2_U_SQRT) {
             if (a < (FT)0)
                 bad = true;
-            if constexpr (std::is_same_v<FT, float>)
-                r = __fsqrt_rn(a);
-            else
-                r = __dsqrt_rn(a);
+            r = __dsqrt_rn(a);
         } else if constexpr (OP == DB2_U_EXP)
             r = exp(a);
         else if constexpr (OP == DB2_U_LN) {

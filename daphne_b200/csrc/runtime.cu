@@ -5,8 +5,25 @@
 namespace db2 {
 
 DevBuf::~DevBuf() {
-    if (owned && ptr)
-        ctx_free(ctx, ptr, bytes);
+    if (owned) {
+        if (ptr)
+            ctx_free(ctx, ptr, bytes);
+        ctx_release(ctx);
+    }
+}
+
+void ctx_release(db2_context *ctx) {
+    if (ctx->refs.fetch_sub(1) != 1)
+        return;
+    bind_device(ctx);
+    cudaStreamSynchronize(ctx->stream);
+    if (ctx->scratch)
+        cudaFreeAsync(ctx->scratch, ctx->stream);
+    cudaStreamSynchronize(ctx->stream);
+    cudaFree(ctx->dev_status);
+    cudaFreeHost(ctx->host_status);
+    cudaStreamDestroy(ctx->stream);
+    delete ctx;
 }
 HostBuf::~HostBuf() {
     if (owned && ptr)
@@ -73,6 +90,7 @@ std::shared_ptr<DevBuf> make_devbuf(db2_context *ctx, size_t bytes) {
     int rc = ctx_alloc(ctx, bytes, &p);
     if (rc != DB2_OK)
         throw Error(rc, err_buf());
+    ctx->refs.fetch_add(1);
     return std::shared_ptr<DevBuf>(new DevBuf{ctx, p, bytes, true});
 }
 
@@ -84,9 +102,7 @@ int ensure_device(db2_matrix *m) {
     bind_device(ctx);
     const size_t es = m->esize();
     if (!m->dev) {
-        void *p = nullptr;
-        DB2_TRY(ctx_alloc(ctx, (size_t)m->rows * m->cols * es, &p));
-        m->dev = std::shared_ptr<DevBuf>(new DevBuf{ctx, p, (size_t)m->rows * m->cols * es, true});
+        m->dev = make_devbuf(ctx, (size_t)m->rows * m->cols * es);
         m->dev_off = 0;
         m->dev_ld = m->cols;
     }
@@ -166,13 +182,7 @@ int db2_context_destroy(db2_context *ctx) {
         return DB2_OK;
     bind_device(ctx);
     cudaStreamSynchronize(ctx->stream);
-    if (ctx->scratch)
-        cudaFreeAsync(ctx->scratch, ctx->stream);
-    cudaStreamSynchronize(ctx->stream);
-    cudaFree(ctx->dev_status);
-    cudaFreeHost(ctx->host_status);
-    cudaStreamDestroy(ctx->stream);
-    delete ctx;
+    ctx_release(ctx);
     return DB2_OK;
 }
 

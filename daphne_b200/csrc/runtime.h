@@ -21,6 +21,9 @@ struct db2_context {
     int32_t *host_status = nullptr;
     std::mutex mu;
     db2_stats stats{};
+    // the handle returned by db2_context_create holds one reference, every pooled buffer another: a context is torn
+    // down when the last of them goes, so matrices may outlive db2_context_destroy
+    std::atomic<int> refs{1};
 };
 
 namespace db2 {
@@ -49,6 +52,7 @@ struct HostBuf {
 int ctx_alloc(db2_context *ctx, size_t bytes, void **out);
 int ctx_free(db2_context *ctx, void *ptr, size_t bytes);
 int ctx_scratch(db2_context *ctx, size_t bytes, void **out);
+void ctx_release(db2_context *ctx);
 std::shared_ptr<DevBuf> make_devbuf(db2_context *ctx, size_t bytes); // throws Error
 
 inline void bind_device(const db2_context *ctx) {

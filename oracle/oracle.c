@@ -106,28 +106,16 @@ static double un_f64(int op, double x, int *bad) {
     default: return x;
     }
 }
+/* float: the reference spells most functions unqualified (sqrt(arg), exp(arg), sin(arg), ...), which binds to the C
+ * double functions, and rounds the double result to float; only std::abs and std::ceil use the float overloads. */
 static float un_f32(int op, float x, int *bad) {
     switch (op) {
     case U_MINUS: return -x;
     case U_ABS: return fabsf(x);
     case U_SIGN: return (x == 0) ? 0 : ((x < 0) ? -1 : ((x > 0) ? 1 : NAN));
-    case U_SQRT: if (-0.0 > x) *bad = 1; return sqrtf(x);
-    case U_EXP: return expf(x);
-    case U_LN: if (-0.0 > x) *bad = 1; return logf(x);
-    case U_SIN: return sinf(x);
-    case U_COS: return cosf(x);
-    case U_TAN: return tanf(x);
-    case U_ASIN: if (-1.0 > x || x > 1.0) *bad = 1; return asinf(x);
-    case U_ACOS: if (-1.0 > x || x > 1.0) *bad = 1; return acosf(x);
-    case U_ATAN: return atanf(x);
-    case U_SINH: return sinhf(x);
-    case U_COSH: return coshf(x);
-    case U_TANH: return tanhf(x);
-    case U_FLOOR: return floorf(x);
     case U_CEIL: return ceilf(x);
-    case U_ROUND: return roundf(x);
     case U_ISNAN: return (float)(x != x);
-    default: return x;
+    default: return (float)un_f64(op, (double)x, bad);
     }
 }
 static int64_t un_i64(int op, int64_t x, int *bad) {

@@ -1,0 +1,92 @@
+"""TEST INFRASTRUCTURE: numpy-facing wrappers over oracle/_ref/libdaphne_ref.so, i.e. the reference's own CPU kernels
+compiled from a DAPHNE source tree by oracle/Makefile.  `available()` is False when that library was not built (for
+instance on a machine without the source tree); callers then fall back to the restatement in oracle.c."""
+from __future__ import annotations
+
+import ctypes as C
+from pathlib import Path
+
+import numpy as np
+
+from . import pyoracle as _o
+
+_PATH = Path(__file__).resolve().parent / "_ref" / "libdaphne_ref.so"
+_lib = None
+
+
+def available() -> bool:
+    global _lib
+    if _lib is None and _PATH.exists():
+        try:
+            _lib = C.CDLL(str(_PATH))
+        except OSError:
+            _lib = False
+    return bool(_lib)
+
+
+def _f(name, argtypes):
+    fn = getattr(_lib, name)
+    fn.argtypes = argtypes
+    fn.restype = C.c_int
+    return fn
+
+
+i64, vp = C.c_int64, C.c_void_p
+_mat, _ld, _p, _SUF, _CT, _chk = _o._mat, _o._ld, _o._p, _o._SUF, _o._CT, _o._chk
+
+
+def set_blas_threads(n: int) -> None:
+    _lib.ref_set_blas_threads(C.c_int(n))
+
+
+def ewBinaryMat(op, lhs, rhs):
+    lhs, rhs = _mat(lhs), _mat(rhs)
+    res = np.empty(lhs.shape, dtype=lhs.dtype)
+    f = _f(f"ref_ew_binary_{_SUF[lhs.dtype]}", [C.c_int, vp, i64, i64, i64, vp, i64, i64, i64, vp, i64])
+    _chk(f(int(op), _p(lhs), lhs.shape[0], lhs.shape[1], _ld(lhs), _p(rhs), rhs.shape[0], rhs.shape[1], _ld(rhs),
+           _p(res), max(res.shape[1], 1)))
+    return res
+
+
+def ewBinaryObjSca(op, lhs, scalar):
+    lhs = _mat(lhs)
+    s = _SUF[lhs.dtype]
+    res = np.empty(lhs.shape, dtype=lhs.dtype)
+    f = _f(f"ref_ew_binary_sca_{s}", [C.c_int, vp, i64, i64, i64, _CT[s], vp, i64])
+    _chk(f(int(op), _p(lhs), lhs.shape[0], lhs.shape[1], _ld(lhs), lhs.dtype.type(scalar).item(), _p(res),
+           max(res.shape[1], 1)))
+    return res
+
+
+def ewUnaryMat(op, arg):
+    arg = _mat(arg)
+    res = np.empty(arg.shape, dtype=arg.dtype)
+    f = _f(f"ref_ew_unary_{_SUF[arg.dtype]}", [C.c_int, vp, i64, i64, i64, vp, i64])
+    _chk(f(int(op), _p(arg), arg.shape[0], arg.shape[1], _ld(arg), _p(res), max(res.shape[1], 1)))
+    return res
+
+
+def aggRow(op, arg):
+    arg = _mat(arg)
+    res = np.empty((arg.shape[0], 1), dtype=arg.dtype)
+    idx = np.empty((arg.shape[0], 1), dtype=np.uint64)
+    f = _f(f"ref_agg_row_{_SUF[arg.dtype]}", [C.c_int, vp, i64, i64, i64, vp, vp, i64])
+    _chk(f(int(op), _p(arg), arg.shape[0], arg.shape[1], _ld(arg), _p(res), _p(idx), 1))
+    return idx if _o._is_idx(op) else res
+
+
+def aggCol(op, arg):
+    arg = _mat(arg)
+    res = np.empty((1, arg.shape[1]), dtype=arg.dtype)
+    idx = np.empty((1, arg.shape[1]), dtype=np.uint64)
+    f = _f(f"ref_agg_col_{_SUF[arg.dtype]}", [C.c_int, vp, i64, i64, i64, vp, vp])
+    _chk(f(int(op), _p(arg), arg.shape[0], arg.shape[1], _ld(arg), _p(res), _p(idx)))
+    return idx if _o._is_idx(op) else res
+
+
+def aggAll(op, arg):
+    arg = _mat(arg)
+    res = np.zeros(1, dtype=arg.dtype)
+    f = _f(f"ref_agg_all_{_SUF[arg.dtype]}", [C.c_int, vp, i64, i64, i64, vp])
+    _chk(f(int(op), _p(arg), arg.shape[0], arg.shape[1], _ld(arg), _p(res)))
+    return res[0]

@@ -1,0 +1,140 @@
+"""Extracts the known-answer cases of the reference's own kernel unit tests into tests/golden/reference_cases.json.
+
+The reference's tests build literal matrices with genGivenVals<DT>(numRows, {values...}) and compare a kernel's result
+with a literal expected matrix (test/runtime/local/kernels/*Test.cpp).  This script reads those C++ files AS TEXT
+(nothing is compiled or executed), pairs every check call with the literals it names, and writes them out as JSON with
+the source file and line of each check.  The JSON is the committed fixture; the script is kept so the fixture can be
+regenerated from a DAPHNE checkout:
+
+    python tests/golden/extract_reference_cases.py /path/to/daphne > tests/golden/reference_cases.json
+"""
+from __future__ import annotations
+
+import json
+import math
+import re
+import sys
+from pathlib import Path
+
+FILES = ["AggRowTest.cpp", "AggColTest.cpp", "AggAllTest.cpp", "EwBinaryMatTest.cpp", "EwBinaryObjScaTest.cpp",
+         "EwUnaryMatTest.cpp", "SyrkTest.cpp", "GemvTest.cpp", "MatMulTest.cpp", "SolveTest.cpp", "CTableTest.cpp",
+         "TransposeTest.cpp"]
+
+SCOPE_RE = re.compile(r"^\s*(TEMPLATE_PRODUCT_TEST_CASE|TEMPLATE_TEST_CASE|TEST_CASE|#define\s+\w+TEST_CASE\w*)\b")
+GEN_RE = re.compile(r"(?:auto|\w+\s*\*)\s*(\w+)\s*=\s*genGivenVals<([^>]*(?:<[^>]*>)?[^>]*)>\(\s*(\w+)\s*,\s*\{(.*?)\}\s*\)\s*;",
+                    re.S)
+CHECK_RE = re.compile(r"\b(check\w+)\(\s*(?:(\w+OpCode)::(\w+)\s*,\s*)?([^;]*?)\)\s*;")
+
+_ENV = {"sqrt": math.sqrt, "exp": math.exp, "log": math.log, "sin": math.sin, "cos": math.cos, "tan": math.tan,
+        "asin": math.asin, "acos": math.acos, "atan": math.atan, "sinh": math.sinh, "cosh": math.cosh,
+        "tanh": math.tanh, "pow": math.pow, "M_PI": math.pi, "M_E": math.e, "inf": math.inf, "nan": math.nan,
+        "true": 1, "false": 0}
+
+
+def _clean(text: str) -> str:
+    text = re.sub(r"//[^\n]*", "", text)
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return text.replace("\\\n", "\n")
+
+
+def _value(tok: str):
+    t = tok.strip()
+    if not t:
+        return None
+    t = re.sub(r"std::numeric_limits<[^>]*>::infinity\(\)", "inf", t)
+    t = re.sub(r"std::numeric_limits<[^>]*>::quiet_NaN\(\)", "nan", t)
+    t = re.sub(r"\b(?:VT|VTRes|VTArg|typename\s+\w+::VT|double|float|int64_t|size_t|uint32_t)\s*\(([^()]*)\)", r"(\1)", t)
+    t = re.sub(r"\((?:VT|VTRes|VTArg|typename\s+\w+::VT|double|float|int64_t|size_t)\)", "", t)
+    t = re.sub(r"static_cast<[^>]*>", "", t)
+    t = re.sub(r"\bstd::", "", t)
+    t = re.sub(r"(?<=[0-9.])[fFlLuU]+\b", "", t)
+    try:
+        v = eval(t, {"__builtins__": {}}, _ENV)  # literals and a few math calls only
+    except Exception:
+        raise ValueError(tok)
+    if isinstance(v, bool) or not isinstance(v, (int, float)):
+        raise ValueError(tok)
+    return float(v) if isinstance(v, float) else int(v)
+
+
+def _split_values(body: str):
+    out, depth, cur = [], 0, ""
+    for ch in body:
+        if ch in "([":
+            depth += 1
+        elif ch in ")]":
+            depth -= 1
+        if ch == "," and depth == 0:
+            out.append(cur)
+            cur = ""
+        else:
+            cur += ch
+    out.append(cur)
+    return [v for v in (_value(x) for x in out) if v is not None]
+
+
+def _enc(v):
+    if isinstance(v, float) and (math.isnan(v) or math.isinf(v)):
+        return "nan" if math.isnan(v) else ("inf" if v > 0 else "-inf")
+    return v
+
+
+def extract(root: Path):
+    cases, skipped = [], 0
+    for fname in FILES:
+        path = root / "test" / "runtime" / "local" / "kernels" / fname
+        if not path.exists():
+            continue
+        raw = path.read_text()
+        # keep line numbers: work on the raw text for positions, on a cleaned copy (same length) for parsing
+        text = re.sub(r"//[^\n]*", lambda m: " " * len(m.group()), raw)
+        text = text.replace("\\\n", " \n")
+        lines = text.split("\n")
+        starts = [i for i, ln in enumerate(lines) if SCOPE_RE.match(ln)] + [len(lines)]
+        offs = [0]
+        for ln in lines:
+            offs.append(offs[-1] + len(ln) + 1)
+        for si in range(len(starts) - 1):
+            a, b = offs[starts[si]], offs[starts[si + 1]]
+            scope = text[a:b]
+            header = lines[starts[si]].strip()
+            mats = {}
+            for m in GEN_RE.finditer(scope):
+                name, dt, nrows, body = m.groups()
+                try:
+                    vals = _split_values(body)
+                    nr = int(nrows) if nrows.isdigit() else None
+                except ValueError:
+                    continue
+                mats[name] = {"dt": re.sub(r"\s+", "", dt), "rows": nr, "values": [_enc(v) for v in vals]}
+            for m in CHECK_RE.finditer(scope):
+                fn, enum, op, rest = m.groups()
+                if fn in ("checkEqApprox", "checkEq"):
+                    continue
+                line = text.count("\n", 0, a + m.start()) + 1
+                args = []
+                ok = True
+                for tok in [t.strip() for t in re.split(r",(?![^()]*\))", rest) if t.strip()]:
+                    if tok in mats and mats[tok]["rows"] is not None:
+                        args.append({"matrix": tok, **mats[tok]})
+                    elif tok in ("nullptr",):
+                        continue
+                    else:
+                        try:
+                            args.append({"scalar": _enc(_value(tok))})
+                        except ValueError:
+                            ok = False
+                if not ok or not args:
+                    skipped += 1
+                    continue
+                cases.append({"file": f"test/runtime/local/kernels/{fname}", "line": line, "test": header[:120],
+                              "check": fn, "op": op, "args": args})
+    return cases, skipped
+
+
+if __name__ == "__main__":
+    root = Path(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    cases, skipped = extract(root)
+    json.dump({"source": "daphne-eu/daphne test/runtime/local/kernels (literals of the reference's unit tests)",
+               "skipped_unparsed_checks": skipped, "cases": cases}, sys.stdout, indent=None, separators=(",", ":"))
+    sys.stderr.write(f"{len(cases)} cases, {skipped} skipped\n")

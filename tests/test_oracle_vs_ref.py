@@ -1,0 +1,102 @@
+"""The C restatement (oracle/oracle.c) against the reference's own CPU kernels compiled from its sources
+(oracle/_ref).  Bit-exact: both run the same scalar expressions in the same order.  Skipped where oracle/_ref was not
+built (no DAPHNE source tree on this machine)."""
+import numpy as np
+import pytest
+
+from oracle import pyoracle as o
+from oracle import refkernels as ref
+from tests.util import assert_bits_equal, rng_matrix
+
+pytestmark = pytest.mark.skipif(not ref.available(), reason="oracle/_ref not built")
+
+SHAPES = [(1, 1), (3, 5), (64, 32), (257, 33), (1, 1003), (1003, 1), (130, 70)]
+DTYPES = [np.float64, np.float32, np.int64]
+
+
+def _nanfix(a, b):
+    if a.dtype.kind == "f":
+        nan = np.isnan(b)
+        assert np.array_equal(np.isnan(a), nan)
+        return np.where(nan, 0, a), np.where(nan, 0, b)
+    return a, b
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_ew_binary(dtype):
+    for i, (r, c) in enumerate(SHAPES):
+        a, b = rng_matrix(i, r, c, dtype), rng_matrix(50 + i, r, c, dtype)
+        rv, cv = rng_matrix(70 + i, 1, c, dtype), rng_matrix(90 + i, r, 1, dtype)
+        for m in (b, rv, cv):
+            m[m == 0] = 3
+        a.reshape(-1)[::5] = b.reshape(-1)[::5]
+        for op in range(17):
+            if np.dtype(dtype) == np.int64 and op in (4, 5, 6):
+                x, y, z, w = np.abs(a) % 7 + 1, np.abs(b) % 4 + 1, np.abs(rv) % 4 + 1, np.abs(cv) % 4 + 1
+            elif op in (4, 6):
+                x, y, z, w = np.abs(a) + 1, np.abs(b) % 3 + 1.5, np.abs(rv) % 3 + 1.5, np.abs(cv) % 3 + 1.5
+                x, y, z, w = (t.astype(dtype) for t in (x, y, z, w))
+            else:
+                x, y, z, w = a, b, rv, cv
+            for rhs in (y, z, w):
+                assert_bits_equal(*_nanfix(o.ewBinaryMat(op, x, rhs), ref.ewBinaryMat(op, x, rhs)),
+                                  f"op {op} {dtype.__name__} {x.shape} {rhs.shape}")
+            s = 3 if np.dtype(dtype) == np.int64 else 2.5
+            assert_bits_equal(*_nanfix(o.ewBinaryObjSca(op, x, s), ref.ewBinaryObjSca(op, x, s)), f"sca op {op}")
+
+
+def test_ew_binary_shape_error_matches():
+    with pytest.raises(o.OracleError):
+        o.ewBinaryMat(0, np.ones((4, 5)), np.ones((3, 2)))
+    with pytest.raises(o.OracleError):
+        ref.ewBinaryMat(0, np.ones((4, 5)), np.ones((3, 2)))
+
+
+@pytest.mark.parametrize("dtype", [np.float64, np.float32])
+def test_ew_unary(dtype):
+    for i, (r, c) in enumerate(SHAPES):
+        a = (rng_matrix(i, r, c, dtype, kind="uniform") * 0.9 + 0.05).astype(dtype)
+        for op in range(19):
+            assert_bits_equal(*_nanfix(o.ewUnaryMat(op, a), ref.ewUnaryMat(op, a)), f"unary {op} {dtype.__name__}")
+        neg = (a - 0.5).astype(dtype)
+        for op in (0, 1, 2, 4, 6, 7, 8, 11, 12, 13, 14, 15, 16, 17, 18):
+            assert_bits_equal(*_nanfix(o.ewUnaryMat(op, neg), ref.ewUnaryMat(op, neg)), f"unary {op} neg")
+    bad = np.array([[1.0, -1.0]])
+    for op in (3, 5):
+        with pytest.raises(o.OracleError) as e1:
+            o.ewUnaryMat(op, bad)
+        with pytest.raises(o.OracleError) as e2:
+            ref.ewUnaryMat(op, bad)
+        assert e1.value.code == e2.value.code == 5
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_aggregations(dtype):
+    ops = range(9) if np.dtype(dtype) != np.int64 else (0, 1, 2, 3, 4, 5)
+    for i, (r, c) in enumerate(SHAPES):
+        a = rng_matrix(i, r, c, dtype)
+        if np.dtype(dtype) == np.int64:
+            a = a % 5
+        a.reshape(-1)[::3] = a.reshape(-1)[0]
+        for op in ops:
+            assert_bits_equal(o.aggRow(op, a), ref.aggRow(op, a), f"aggRow {op} {dtype.__name__} {r}x{c}")
+            assert_bits_equal(o.aggCol(op, a), ref.aggCol(op, a), f"aggCol {op} {dtype.__name__} {r}x{c}")
+            if op not in (4, 5):
+                x, y = o.aggAll(op, a), ref.aggAll(op, a)
+                assert x == y or (x != x and y != y), f"aggAll {op} {dtype.__name__} {r}x{c}: {x} {y}"
+    # strided input (rowSkip > numCols) takes the per-row branch of AggAll (AggAll.h:147-163)
+    big = rng_matrix(7, 50, 40, np.float64)
+    v = big[:, 3:30]
+    for op in (0, 2, 3, 6, 7, 8):
+        assert o.aggAll(op, v) == ref.aggAll(op, v)
+        assert_bits_equal(o.aggRow(op, v), ref.aggRow(op, v), "strided row")
+        assert_bits_equal(o.aggCol(op, v), ref.aggCol(op, v), "strided col")
+
+
+def test_nan_and_signed_zero_cases():
+    rows = np.array([[np.nan, 1.0, 2.0], [1.0, np.nan, 2.0], [0.0, -0.0, 0.0], [-0.0, 0.0, -0.0],
+                     [np.inf, np.nan, np.inf]])
+    for a in (rows, np.ascontiguousarray(rows.T)):
+        for op in (2, 3, 4, 5):
+            assert_bits_equal(*_nanfix(o.aggRow(op, a), ref.aggRow(op, a)), f"row {op}")
+            assert_bits_equal(*_nanfix(o.aggCol(op, a), ref.aggCol(op, a)), f"col {op}")
