@@ -1,0 +1,298 @@
+#!/usr/bin/env python
+"""Benchmark of the vectorized-pipeline hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--rows R]
+
+One "step" = one pass of the column standardisation + aggregation pipeline (16,777,216 x 32 f64 = 4 GiB per GPU) over
+a seeded synthetic N(5,2) matrix; with N > 1 every rank owns its own 4 GiB row block (weak scaling) and the column
+statistics are combined across ranks.  Prints ONE JSON line (rank 0).  `value` is rows/s with the input resident in
+HBM; `e2e` is the same pipeline through the host-buffer API (H2D of the input and D2H of every result inside the timed
+region).  `--impl reference` times the reference's CPU kernels on the host cores on a bounded sample."""
+from __future__ import annotations
+
+import argparse
+import ctypes as C
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+import numpy as np
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+ROWS_PER_GPU = 16_777_216
+COLS = 32
+SEED = 2
+# algorithmic bytes per row of the whole pipeline with nothing materialised: statistics passes read the row twice,
+# the normalise+aggregate pass once more is folded in the survey's minimum of 2 reads + 3 results = 536 B/row
+PIPELINE_MIN_BYTES_PER_ROW = 2 * COLS * 8 + 24
+
+
+def measured_peaks():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        d = json.loads(p.read_text())
+        return float(d["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu = gpu_index
+        self.proc = None
+        self.lines = []
+        self.t = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                          "-lms", "100", "-i", str(self.gpu)], stdout=subprocess.PIPE,
+                                         stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+            return
+        self.t = threading.Thread(target=self._read, daemon=True)
+        self.t.start()
+
+    def _read(self):
+        for ln in self.proc.stdout:
+            self.lines.append(ln.strip())
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=2)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        for ln in self.lines:
+            f = [x.strip() for x in ln.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def make_input(rows: int, cols: int, seed: int, out: np.ndarray) -> None:
+    """N(5, 2) entries, seeded; filled in chunks so that no second 4 GiB temporary is needed."""
+    rng = np.random.default_rng(seed)
+    step = 1 << 20
+    for lo in range(0, rows, step):
+        hi = min(rows, lo + step)
+        blk = rng.standard_normal((hi - lo, cols))
+        blk *= 2.0
+        blk += 5.0
+        out[lo:hi] = blk
+
+
+def pinned_array(lib, rows: int, cols: int):
+    from daphne_b200.lib import check
+    p = C.c_void_p()
+    nbytes = rows * cols * 8
+    check(lib.db2_malloc_host(C.byref(p), nbytes))
+    buf = (C.c_double * (rows * cols)).from_address(p.value)
+    return np.frombuffer(buf, dtype=np.float64).reshape(rows, cols), p
+
+
+def run_ours(args) -> dict:
+    import daphne_b200.kernels as K
+    from daphne_b200 import pipelines
+    from daphne_b200.dist import Comm
+    from daphne_b200.lib import check, lib, require_device
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus and world > 1:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}")
+    require_device()
+    if world > 1:
+        import torch
+        torch.cuda.set_device(local_rank)
+    comm = Comm.from_env("nccl")
+    ctx = K.Context(local_rank)
+    rows, cols = args.rows, COLS
+    n_total = rows * world
+
+    host, host_ptr = pinned_array(lib, rows, cols)
+    make_input(rows, cols, SEED + rank, host)
+
+    def ev():
+        e = C.c_void_p()
+        check(lib.db2_event_create(C.byref(e)))
+        return e
+
+    stream = C.c_void_p(ctx.stream)
+
+    def sync_all():
+        comm.barrier()
+        check(lib.db2_device_sync())
+
+    probe = pipelines.Probe(lib, stream) if hasattr(pipelines, "Probe") else None
+
+    # ---- device-resident timing (`value`) ----
+    Xd = K.DenseMatrix.from_numpy(ctx, host)
+    Xd.device_ptr()  # H2D once, outside the timed region
+    ctx.sync()
+    for _ in range(args.warmup):
+        res = pipelines.standardise_aggregate(ctx, Xd, n_total, comm)
+    sync_all()
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    launches0 = lib.db2_launch_count()
+    e0, e1 = ev(), ev()
+    if probe:
+        probe.reset()
+    check(lib.db2_event_record(e0, stream))
+    for _ in range(args.steps):
+        res = pipelines.standardise_aggregate(ctx, Xd, n_total, comm, probe=probe) if probe else \
+            pipelines.standardise_aggregate(ctx, Xd, n_total, comm)
+    check(lib.db2_event_record(e1, stream))
+    sync_all()
+    ms = C.c_float()
+    check(lib.db2_event_elapsed_ms(e0, e1, C.byref(ms)))
+    launches = lib.db2_launch_count() - launches0
+    clocks = sampler.stop()
+    ms_step = comm.max_float(ms.value / args.steps)
+    s_value = res.s
+    dom = probe.summary() if probe else None
+    del res
+
+    # ---- end to end through host buffers (`e2e`) ----
+    out_r = np.empty((rows, 1))
+    out_m = np.empty((rows, 1))
+    out_i = np.empty((rows, 1), dtype=np.uint64)
+    Xd.free()
+    e2e_steps = max(1, min(args.steps, 3))
+
+    def e2e_step():
+        Xh = K.DenseMatrix.from_numpy(ctx, host)  # host placement only; the first kernel triggers the H2D copy
+        r = pipelines.standardise_aggregate(ctx, Xh, n_total, comm)
+        check(lib.db2_matrix_to_host(r.r.handle, C.c_void_p(out_r.ctypes.data), 1))
+        check(lib.db2_matrix_to_host(r.row_max.handle, C.c_void_p(out_m.ctypes.data), 1))
+        check(lib.db2_matrix_to_host(r.row_idx_max.handle, C.c_void_p(out_i.ctypes.data), 1))
+        mu, sd = r.mu.to_numpy(), r.sd.to_numpy()
+        Xh.free()
+        return r.s, mu, sd
+
+    e2e_step()
+    sync_all()
+    t0 = time.perf_counter()
+    e2, e3 = ev(), ev()
+    check(lib.db2_event_record(e2, stream))
+    for _ in range(e2e_steps):
+        e2e_step()
+    check(lib.db2_event_record(e3, stream))
+    sync_all()
+    wall_ms = (time.perf_counter() - t0) * 1e3 / e2e_steps
+    check(lib.db2_event_elapsed_ms(e2, e3, C.byref(ms)))
+    e2e_ms = comm.max_float(max(ms.value / e2e_steps, wall_ms))
+
+    peak, peak_kind = measured_peaks()
+    line = {
+        "metric": "pipeline_rows_per_s", "value": n_total / (ms_step * 1e-3), "unit": "rows/s", "n_gpus": world,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f64", "data": "synthetic",
+        "config": {"workload": "cfg2 column standardisation + aggregation (mean, sd, Z=(X-mu)/sd, rowSums(Z^2), "
+                               "sum, rowMaxs, idxMax) on f64 %d x %d per GPU, N(5,2) seed %d" % (rows, cols, SEED),
+                   "rows_per_gpu": rows, "cols": cols, "parallelism": f"rows{world}",
+                   "l2": "input (4 GiB) larger than L2, no flush needed"},
+        "clocks": clocks,
+        "e2e": {"value": n_total / (e2e_ms * 1e-3), "unit": "rows/s", "ms_per_step": e2e_ms,
+                "h2d_bytes_per_step": rows * cols * 8, "d2h_bytes_per_step": rows * 24 + 2 * cols * 8 + 8,
+                "steps": e2e_steps},
+        "gpu_launches": int(launches),
+        "pipeline_hbm_gbs": n_total / world * PIPELINE_MIN_BYTES_PER_ROW / (ms_step * 1e-3) / 1e9,
+        "pipeline_hbm_frac_of_" + peak_kind: (rows * PIPELINE_MIN_BYTES_PER_ROW / (ms_step * 1e-3) / 1e9) / peak,
+        "checksum_s": s_value,
+    }
+    if dom:
+        line["roofline"] = {"bound": "hbm", "kernel": dom["name"], "achieved": dom["gbs"], "peak": peak,
+                            "unit": "GB/s", "frac": dom["gbs"] / peak, "traffic": dom.get("traffic"),
+                            "peak_kind": peak_kind, "launches_timed": dom["launches"],
+                            "avg_ms": dom["avg_ms"], "algorithmic_bytes_per_launch": dom["bytes"]}
+    if rank == 0:
+        line["cpu_baseline"] = cpu_baseline(min(rows, args.cpu_rows), cols)
+    lib.db2_free_host(host_ptr)
+    return line if rank == 0 else {}
+
+
+def cpu_baseline(rows: int, cols: int, steps: int = 3, threads: int | None = None) -> dict:
+    from oracle import cpu_pipelines
+    k, kind = cpu_pipelines.backend()
+    threads = threads or cpu_pipelines.host_threads()
+    X = np.empty((rows, cols))
+    make_input(rows, cols, SEED, X)
+    cpu_pipelines.standardise_aggregate(X, threads, k)
+    ts = []
+    for _ in range(steps):
+        t0 = time.perf_counter()
+        cpu_pipelines.standardise_aggregate(X, threads, k)
+        ts.append(time.perf_counter() - t0)
+    t = float(np.median(ts))
+    return {"value": rows / t, "unit": "rows/s", "cores": threads, "kind": kind,
+            "sample": f"first {rows} rows x {cols} cols of the same N(5,2) input, {steps} runs after 1 warm-up, median; "
+                      f"reference CPU kernels row-partitioned over {threads} threads (STATIC)",
+            "ms_per_step": t * 1e3}
+
+
+def run_reference(args) -> dict:
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return {}
+    rows = min(args.rows, args.cpu_rows)
+    b = cpu_baseline(rows, COLS, steps=max(1, args.steps), threads=None)
+    return {
+        "impl": "reference", "metric": "pipeline_rows_per_s", "value": b["value"], "unit": "rows/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": b["ms_per_step"],
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f64", "data": "synthetic",
+        "config": {"workload": "cfg2 column standardisation + aggregation on f64 %d x %d (bounded sample of the "
+                               "%d-row workload), CPU" % (rows, COLS, args.rows), "rows": rows, "cols": COLS},
+        "cpu_baseline": b,
+        "e2e": {"value": b["value"], "unit": "rows/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--rows", type=int, default=ROWS_PER_GPU, help="rows per GPU (default: the 4 GiB configuration)")
+    ap.add_argument("--cpu-rows", type=int, default=1 << 20, help="rows of the bounded CPU-baseline sample")
+    args = ap.parse_args()
+    if args.warmup < 3 and args.impl == "ours":
+        args.warmup = 3
+    line = run_reference(args) if args.impl == "reference" else run_ours(args)
+    if line:
+        print(json.dumps(line), flush=True)
+    if int(os.environ.get("WORLD_SIZE", "1")) > 1:
+        import torch.distributed as dist
+        if dist.is_initialized():
+            dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

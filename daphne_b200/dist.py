@@ -1,0 +1,84 @@
+"""Row-sharded multi-GPU plumbing: one process per GPU, torch.distributed for rendezvous and collectives.
+
+The path shards by rows (the reference's VectorSplit::ROWS contract, src/runtime/local/vectorized/Tasks.h:85-110):
+rank g owns the contiguous row block [g*n/G, (g+1)*n/G).  ROWS/COLS outputs stay sharded; ADD/MIN/MAX partials
+(VectorCombine, src/runtime/local/vectorized/Tasks.cpp:51-82) are combined with one all-reduce per pipeline."""
+from __future__ import annotations
+
+import os
+from typing import Optional
+
+import numpy as np
+
+COMBINE_ROWS, COMBINE_COLS, COMBINE_ADD, COMBINE_MIN, COMBINE_MAX = 1, 2, 3, 4, 5
+
+
+def row_block(n_rows: int, rank: int, world: int) -> tuple[int, int]:
+    """Contiguous row block of `rank`; the first n_rows % world ranks get one extra row."""
+    base, extra = divmod(n_rows, world)
+    lo = rank * base + min(rank, extra)
+    return lo, lo + base + (1 if rank < extra else 0)
+
+
+class Comm:
+    """Collectives over the row shards.  world == 1 needs no torch at all."""
+
+    def __init__(self, rank: int = 0, world: int = 1, backend: Optional[str] = None):
+        self.rank, self.world, self.backend = rank, world, backend
+        self._dist = None
+        if world > 1:
+            import torch.distributed as dist
+            if not dist.is_initialized():
+                raise RuntimeError("torch.distributed must be initialised before creating a Comm with world > 1")
+            self._dist = dist
+
+    @staticmethod
+    def from_env(device_backend: str = "nccl") -> "Comm":
+        world = int(os.environ.get("WORLD_SIZE", "1"))
+        rank = int(os.environ.get("RANK", "0"))
+        if world > 1:
+            import torch.distributed as dist
+            if not dist.is_initialized():
+                dist.init_process_group(backend=device_backend, rank=rank, world_size=world)
+        return Comm(rank, world, device_backend if world > 1 else None)
+
+    def _op(self, combine: int):
+        d = self._dist
+        return {COMBINE_ADD: d.ReduceOp.SUM, COMBINE_MIN: d.ReduceOp.MIN, COMBINE_MAX: d.ReduceOp.MAX}[combine]
+
+    def allreduce_tensor(self, t, combine: int = COMBINE_ADD):
+        """In-place all-reduce of a torch tensor (CUDA tensor under nccl, CPU tensor under gloo)."""
+        if self.world > 1:
+            self._dist.all_reduce(t, op=self._op(combine))
+        return t
+
+    def allreduce_numpy(self, a: np.ndarray, combine: int = COMBINE_ADD) -> np.ndarray:
+        if self.world == 1:
+            return a
+        import torch
+        t = torch.from_numpy(np.ascontiguousarray(a))
+        if self.backend == "nccl":
+            t = t.cuda()
+        self._dist.all_reduce(t, op=self._op(combine))
+        return t.cpu().numpy()
+
+    def allgather_numpy(self, a: np.ndarray) -> np.ndarray:
+        """Concatenates equally shaped row shards in rank order."""
+        if self.world == 1:
+            return a
+        import torch
+        t = torch.from_numpy(np.ascontiguousarray(a))
+        if self.backend == "nccl":
+            t = t.cuda()
+        out = [torch.empty_like(t) for _ in range(self.world)]
+        self._dist.all_gather(out, t)
+        return torch.cat(out, dim=0).cpu().numpy()
+
+    def barrier(self):
+        if self.world > 1:
+            self._dist.barrier()
+
+    def max_float(self, x: float) -> float:
+        if self.world == 1:
+            return x
+        return float(self.allreduce_numpy(np.array([x], dtype=np.float64), COMBINE_MAX)[0])
