@@ -16,6 +16,8 @@
 // AggAll.h:161-192).
 #include "ops.cuh"
 
+#include <mutex>
+
 namespace db2 {
 
 constexpr int AGG_THREADS = 256;
@@ -755,6 +757,53 @@ extern "C" int db2k_agg_col(int dtype, int op, const void *arg, int64_t rows, in
     DB2_CHECK((arg && res) || cols == 0, DB2_EINVAL, "null operand");
     DB2_DISPATCH_DTYPE(dtype, VT, return (agg_col_impl<VT>(op, (const VT *)arg, rows, cols, ld, res, scratch,
                                                            scratch_bytes, as_stream(stream))));
+    return DB2_OK;
+}
+
+// ---------------------------------------------------------------------------
+// column aggregation without any allocation
+// ---------------------------------------------------------------------------
+// Scratch for db2k_agg_col_static: one fixed array in device memory per GPU that loads this library.  Host code only
+// ever uses its address as returned by cudaGetSymbolAddress (the bare name is a host-side stand-in for the symbol).
+#define DB2_STATIC_SCRATCH_BYTES (4u << 20)
+static __device__ __align__(256) unsigned char g_agg_col_static_scratch[DB2_STATIC_SCRATCH_BYTES];
+
+namespace {
+std::mutex g_static_mu;
+void *g_static_ptr[64] = {nullptr};
+
+// Looks the array's device address up once per device (with that device current) and remembers it.
+int static_scratch(void **out) {
+    int dev = -1;
+    DB2_CUDA(cudaGetDevice(&dev));
+    DB2_CHECK(dev >= 0 && dev < 64, DB2_EINVAL, "device index %d out of range", dev);
+    std::lock_guard<std::mutex> lock(g_static_mu);
+    if (!g_static_ptr[dev]) {
+        void *p = nullptr;
+        DB2_CUDA(cudaGetSymbolAddress(&p, g_agg_col_static_scratch));
+        DB2_CHECK(p != nullptr, DB2_ECUDA, "cudaGetSymbolAddress returned a null address");
+        g_static_ptr[dev] = p;
+    }
+    *out = g_static_ptr[dev];
+    return DB2_OK;
+}
+} // namespace
+
+extern "C" size_t db2k_agg_col_static_max_bytes(void) { return DB2_STATIC_SCRATCH_BYTES; }
+
+extern "C" int db2k_agg_col_static(int dtype, int op, const void *arg, int64_t rows, int64_t cols, int64_t ld,
+                                   void *res, void *stream) {
+    DB2_CHECK(rows >= 0 && cols >= 0, DB2_EINVAL, "negative dimension");
+    DB2_CHECK((arg && res) || cols == 0, DB2_EINVAL, "null operand");
+    const size_t need = col_scratch_bytes(cols, dtype_size(dtype));
+    DB2_CHECK(need <= (size_t)DB2_STATIC_SCRATCH_BYTES, DB2_EINVAL,
+              "db2k_agg_col_static: %lld columns need %zu bytes of scratch, the built-in array holds %zu; use "
+              "db2k_agg_col with caller-provided scratch for wider matrices",
+              (long long)cols, need, (size_t)DB2_STATIC_SCRATCH_BYTES);
+    void *scratch = nullptr;
+    DB2_TRY(static_scratch(&scratch));
+    DB2_DISPATCH_DTYPE(dtype, VT, return (agg_col_impl<VT>(op, (const VT *)arg, rows, cols, ld, res, scratch,
+                                                           (size_t)DB2_STATIC_SCRATCH_BYTES, as_stream(stream))));
     return DB2_OK;
 }
 

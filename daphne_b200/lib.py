@@ -65,6 +65,8 @@ _SIGS = {
     "db2k_agg_row": (i32, [i32, i32, vp, i64, i64, i64, vp, i64, vp]),
     "db2k_agg_col_scratch_bytes": (sz, [i32, i32, i64, i64]),
     "db2k_agg_col": (i32, [i32, i32, vp, i64, i64, i64, vp, vp, sz, vp]),
+    "db2k_agg_col_static_max_bytes": (sz, []),
+    "db2k_agg_col_static": (i32, [i32, i32, vp, i64, i64, i64, vp, vp]),
     "db2k_agg_all_scratch_bytes": (sz, [i32, i32, i64, i64]),
     "db2k_agg_all": (i32, [i32, i32, vp, i64, i64, i64, vp, vp, sz, vp]),
     # runtime

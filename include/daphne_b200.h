@@ -135,6 +135,26 @@ size_t db2k_agg_col_scratch_bytes(int dtype, int op, int64_t rows, int64_t cols)
 int db2k_agg_col(int dtype, int op, const void *arg, int64_t rows, int64_t cols, int64_t ld, void *res,
                  void *scratch, size_t scratch_bytes, void *stream);
 
+/* Column aggregation that allocates nothing (no counterpart in the reference).
+ *
+ * For callers that are not allowed to allocate device memory at the point of the call: code running inside a
+ * host callback or another context where cudaMalloc is forbidden or would synchronise the device, latency-critical
+ * loops that must not touch the allocator, and embedders that hand this library a fixed memory budget up front.
+ * The scratch that db2k_agg_col takes from the caller lives here in one fixed array of
+ * db2k_agg_col_static_max_bytes() (4 MiB) in device memory, which every GPU that loads the library holds until the
+ * process exits.  Inputs and outputs are still the caller's.
+ *   - Limit: db2k_agg_col_scratch_bytes(dtype, op, rows, cols) must fit the array (about 220 f64 columns on a
+ *     148-SM device); wider matrices are rejected with DB2_EINVAL and a message, nothing is launched.
+ *   - The first call on each device looks up the array's device address (cudaGetSymbolAddress, with that device
+ *     current); make that first call before starting any stream capture.
+ *   - All calls share the one array and it keeps the previous call's contents (every partial is rewritten before
+ *     it is read, so nothing needs clearing); two calls that may overlap on the GPU (different streams without
+ *     ordering) race on it -- serialise them.
+ *   - Calls no cudaMalloc/cudaFree and no allocating library routine.  Same kernels and results as db2k_agg_col. */
+size_t db2k_agg_col_static_max_bytes(void);
+int db2k_agg_col_static(int dtype, int op, const void *arg, int64_t rows, int64_t cols, int64_t ld, void *res,
+                        void *stream);
+
 /* Full aggregation -> one DEVICE scalar of `dtype`.  Replaces AggAll<VT,Dense>
  * (src/runtime/local/kernels/AggAll.h:124-193; CUDA twin kernels/CUDA/AggAll.cu:109-151). */
 size_t db2k_agg_all_scratch_bytes(int dtype, int op, int64_t rows, int64_t cols);
