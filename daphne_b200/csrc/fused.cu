@@ -1,0 +1,579 @@
+// Kernels that evaluate a deferred elementwise chain inside a consumer (see fused.cuh).
+//
+// Row pass (materialisation and/or up to FUSED_MAX_AGGS row aggregations in one sweep):
+//   a CTA of 128 threads stages a tile of 128 rows x 32 columns in shared memory with coalesced 128-bit loads
+//   (16 loads in flight per thread), then every thread walks ONE row of the tile (row pitch 33 doubles: conflict
+//   free), evaluates the chain on 8 values at a time (one interpreter dispatch per step and 8 values) and feeds the
+//   row trackers, so no cross-lane reduction is needed at all; results are written one row per thread (coalesced).
+//   HBM traffic = every base element once + 8 or 16 bytes per row and aggregation.
+// Column pass: threadIdx.x owns a packet of columns, threadIdx.y strides over rows (the mapping of agg.cu), the chain
+//   is evaluated on the packet right after its load; per-CTA partials are folded by agg.cu's second stage.
+//
+// Division by a broadcast divisor (row vector or scalar) is the one expensive FP64 operation of the standardisation
+// pipeline (B200 issues 64 FP64 instructions per SM and clock, a generic IEEE division costs about 20 of them), so it
+// is computed from the divisor's correctly rounded reciprocal y = RN(1/d), staged once per column:
+//   q = RN(a*y); r = a - q*d (exact, FMA); result = RN(q + r*y),
+// which is the correctly rounded quotient a/d when nothing over/underflows (Markstein's theorem).  Operands outside
+// a conservative exponent window, zeros, infinities, NaNs and divisors whose significand is all ones take the
+// generic IEEE division instead, so the result always has the bits of a/d.
+#include "fused.cuh"
+#include "ops.cuh"
+
+namespace db2 {
+
+constexpr int RT = 128;          // threads per CTA = rows per tile
+constexpr int CK = 32;           // columns per chunk
+constexpr int PITCH = CK + 1;    // doubles per tile row in shared memory
+constexpr int GV = 8;            // values per interpreter dispatch
+constexpr int NO_COL = 0x7fffffff;
+
+__device__ __forceinline__ bool safe_divisor(double d) {
+    const unsigned hi = (unsigned)__double2hiint(d), lo = (unsigned)__double2loint(d);
+    const int e = (hi >> 20) & 0x7ff;
+    const bool all_ones = ((hi & 0xfffffu) == 0xfffffu) && (lo == 0xffffffffu);
+    return e > 923 && e < 1123 && !all_ones; // |d| in (2^-100, 2^100)
+}
+// reciprocal used by fast_div, or 0.0 = "take the generic division"
+__device__ __forceinline__ double div_helper(double d) { return safe_divisor(d) ? __drcp_rn(d) : 0.0; }
+
+__device__ __forceinline__ double fast_div(double a, double d, double y) {
+    const int ea = (__double2hiint(a) >> 20) & 0x7ff;
+    if (y != 0.0) {
+        if (ea > 123 && ea < 1923) { // |a| in (2^-900, 2^900): no intermediate can over- or underflow
+            const double q = __dmul_rn(a, y);
+            const double r = __fma_rn(-q, d, a);
+            return __fma_rn(r, y, q);
+        }
+        if (a == 0.0)
+            return __dmul_rn(a, y); // signed zero
+    }
+    return __ddiv_rn(a, d);
+}
+
+// value (op) operand on GV values; `o` holds the operand, `y` the division helper (only read for FO_DIV)
+template <int N>
+__device__ __forceinline__ void apply_step(int op, bool reversed, double (&v)[N], const double (&o)[N],
+                                           const double (&y)[N]) {
+#define DB2_FSTEP(EXPR_FWD, EXPR_REV)                                                                                  \
+    if (!reversed) {                                                                                                   \
+        _Pragma("unroll") for (int i = 0; i < N; i++) { const double a = v[i], b = o[i]; (void)b; v[i] = (EXPR_FWD); } \
+    } else {                                                                                                           \
+        _Pragma("unroll") for (int i = 0; i < N; i++) { const double a = v[i], b = o[i]; (void)b; v[i] = (EXPR_REV); } \
+    }                                                                                                                  \
+    break;
+    switch (op) {
+    case FO_ADD: DB2_FSTEP(__dadd_rn(a, b), __dadd_rn(b, a))
+    case FO_SUB: DB2_FSTEP(__dsub_rn(a, b), __dsub_rn(b, a))
+    case FO_MUL: DB2_FSTEP(__dmul_rn(a, b), __dmul_rn(b, a))
+    case FO_DIV:
+        if (!reversed) {
+#pragma unroll
+            for (int i = 0; i < N; i++)
+                v[i] = fast_div(v[i], o[i], y[i]);
+        } else {
+#pragma unroll
+            for (int i = 0; i < N; i++)
+                v[i] = __ddiv_rn(o[i], v[i]);
+        }
+        break;
+    case FO_SQUARE: DB2_FSTEP(__dmul_rn(a, a), __dmul_rn(a, a))
+    case FO_EQ: DB2_FSTEP((double)(a == b), (double)(b == a))
+    case FO_NEQ: DB2_FSTEP((double)(a != b), (double)(b != a))
+    case FO_LT: DB2_FSTEP((double)(a < b), (double)(b < a))
+    case FO_LE: DB2_FSTEP((double)(a <= b), (double)(b <= a))
+    case FO_GT: DB2_FSTEP((double)(a > b), (double)(b > a))
+    case FO_GE: DB2_FSTEP((double)(a >= b), (double)(b >= a))
+    case FO_MIN: DB2_FSTEP(((b < a) ? b : a), ((a < b) ? a : b))
+    case FO_MAX: DB2_FSTEP(((a < b) ? b : a), ((b < a) ? a : b))
+    case FO_AND: DB2_FSTEP((double)((a != 0.0) && (b != 0.0)), (double)((b != 0.0) && (a != 0.0)))
+    case FO_OR: DB2_FSTEP((double)((a != 0.0) || (b != 0.0)), (double)((b != 0.0) || (a != 0.0)))
+    case FO_NEG: DB2_FSTEP(-a, -a)
+    case FO_ABS: DB2_FSTEP(fabs(a), fabs(a))
+    case FO_SIGN:
+        DB2_FSTEP(((a == 0) ? 0.0 : ((a < 0) ? -1.0 : ((a > 0) ? 1.0 : (double)NAN))),
+                  ((a == 0) ? 0.0 : ((a < 0) ? -1.0 : ((a > 0) ? 1.0 : (double)NAN))))
+    case FO_FLOOR: DB2_FSTEP(floor(a), floor(a))
+    case FO_CEIL: DB2_FSTEP(ceil(a), ceil(a))
+    case FO_ROUND: DB2_FSTEP(round(a), round(a))
+    case FO_ISNAN: DB2_FSTEP((double)(a != a), (double)(a != a))
+    default: break;
+    }
+#undef DB2_FSTEP
+}
+
+// One row tracker per tap: running value, column of the extremum, "first element was NaN".
+struct RowTracker {
+    double v;
+    int c;
+    bool first_nan;
+};
+__device__ __forceinline__ void tracker_init(RowTracker &t, int op) {
+    t.c = NO_COL;
+    t.first_nan = false;
+    switch (op) {
+    case DB2_AGG_PROD: t.v = 1.0; break;
+    case DB2_AGG_MIN:
+    case DB2_AGG_IDXMIN: t.v = INFINITY; break;
+    case DB2_AGG_MAX:
+    case DB2_AGG_IDXMAX: t.v = -INFINITY; break;
+    default: t.v = 0.0; break;
+    }
+}
+template <int N>
+__device__ __forceinline__ void tracker_feed(RowTracker &t, int op, const double (&v)[N], int c0, int nv) {
+    switch (op) {
+    case DB2_AGG_SUM:
+    case DB2_AGG_MEAN:
+#pragma unroll
+        for (int i = 0; i < N; i++)
+            if (i < nv)
+                t.v = __dadd_rn(t.v, v[i]);
+        break;
+    case DB2_AGG_PROD:
+#pragma unroll
+        for (int i = 0; i < N; i++)
+            if (i < nv)
+                t.v = __dmul_rn(t.v, v[i]);
+        break;
+    case DB2_AGG_MIN:
+    case DB2_AGG_IDXMIN:
+        if (c0 == 0 && v[0] != v[0])
+            t.first_nan = true;
+#pragma unroll
+        for (int i = 0; i < N; i++)
+            if (i < nv && (v[i] < t.v || (t.c == NO_COL && v[i] == t.v))) {
+                t.v = v[i];
+                t.c = c0 + i;
+            }
+        break;
+    case DB2_AGG_MAX:
+    case DB2_AGG_IDXMAX:
+        if (c0 == 0 && v[0] != v[0])
+            t.first_nan = true;
+#pragma unroll
+        for (int i = 0; i < N; i++)
+            if (i < nv && (v[i] > t.v || (t.c == NO_COL && v[i] == t.v))) {
+                t.v = v[i];
+                t.c = c0 + i;
+            }
+        break;
+    default: break;
+    }
+}
+
+template <bool ALIGNED>
+__global__ void __launch_bounds__(RT)
+    fused_row_kernel(const __grid_constant__ FusedProgram P) {
+    extern __shared__ __align__(16) double smem[];
+    double *tile = smem;             // [RT][PITCH]
+    double *rvs = smem + RT * PITCH; // staged row-vector operands (+ division helpers)
+    const int tid = threadIdx.x;
+    const int64_t rows = P.rows, cols = P.cols;
+
+    // stage the row-vector operands once per CTA
+    for (int s = 0; s < P.nsteps; s++) {
+        const FusedStep &st = P.steps[s];
+        if (st.kind == FK_ROWVEC && st.smem_off >= 0) {
+            const double *src = static_cast<const double *>(st.ptr);
+            const bool helper = (st.op == FO_DIV && !st.reversed);
+            for (int64_t c = tid; c < cols; c += RT) {
+                const double d = src[c];
+                rvs[st.smem_off + c] = d;
+                if (helper)
+                    rvs[st.smem_off + cols + c] = div_helper(d);
+            }
+        }
+    }
+    __syncthreads();
+
+    const double *base = static_cast<const double *>(P.base);
+    const int64_t ntiles = (rows + RT - 1) / RT;
+    for (int64_t tile_i = blockIdx.x; tile_i < ntiles; tile_i += gridDim.x) {
+        const int64_t row0 = tile_i * RT;
+        const int64_t row = row0 + tid;
+        const bool live = row < rows;
+        const int64_t rows_here = (rows - row0 < RT) ? (rows - row0) : RT;
+        RowTracker trk[FUSED_MAX_AGGS];
+#pragma unroll
+        for (int a = 0; a < FUSED_MAX_AGGS; a++)
+            if (a < P.ntaps)
+                tracker_init(trk[a], P.taps[a].op);
+
+        for (int64_t cc = 0; cc < cols; cc += CK) {
+            const int cw = (cols - cc < CK) ? (int)(cols - cc) : CK;
+            __syncthreads(); // the previous chunk's readers are done with the tile
+            if (ALIGNED && cw == CK) {
+                // 16 packets of 16 bytes per row, 128 rows: 16 coalesced loads in flight per thread
+                Pack<double> p[CK / 2 * RT / RT];
+#pragma unroll
+                for (int i = 0; i < CK / 2; i++) {
+                    const int idx = tid + i * RT;
+                    const int r = idx >> 4, k = idx & 15;
+                    if (r < rows_here)
+                        p[i] = ld_pack_stream(base + (row0 + r) * P.base_ld + cc + 2 * k);
+                    else
+                        p[i].v[0] = p[i].v[1] = 0.0;
+                }
+#pragma unroll
+                for (int i = 0; i < CK / 2; i++) {
+                    const int idx = tid + i * RT;
+                    const int r = idx >> 4, k = idx & 15;
+                    tile[r * PITCH + 2 * k] = p[i].v[0];
+                    tile[r * PITCH + 2 * k + 1] = p[i].v[1];
+                }
+            } else {
+                for (int idx = tid; idx < RT * cw; idx += RT) {
+                    const int r = idx / cw, k = idx - r * cw;
+                    tile[r * PITCH + k] = (r < rows_here) ? base[(row0 + r) * P.base_ld + cc + k] : 0.0;
+                }
+            }
+            __syncthreads();
+
+            double *myrow = tile + tid * PITCH;
+            for (int k0 = 0; k0 < cw; k0 += GV) {
+                const int nv = (cw - k0 < GV) ? (cw - k0) : GV;
+                const int64_t c0 = cc + k0;
+                double v[GV];
+#pragma unroll
+                for (int i = 0; i < GV; i++)
+                    v[i] = (i < nv) ? myrow[k0 + i] : 0.0;
+#pragma unroll
+                for (int a = 0; a < FUSED_MAX_AGGS; a++)
+                    if (a < P.ntaps && P.taps[a].after_step == 0)
+                        tracker_feed(trk[a], P.taps[a].op, v, (int)c0, nv);
+                for (int s = 0; s < P.nsteps; s++) {
+                    const FusedStep &st = P.steps[s];
+                    double o[GV], y[GV];
+                    if (st.kind == FK_ROWVEC) {
+                        if (st.smem_off >= 0) {
+                            const double *sv = rvs + st.smem_off + c0;
+#pragma unroll
+                            for (int i = 0; i < GV; i++)
+                                o[i] = (i < nv) ? sv[i] : 1.0;
+                            if (st.op == FO_DIV && !st.reversed) {
+#pragma unroll
+                                for (int i = 0; i < GV; i++)
+                                    y[i] = (i < nv) ? sv[cols + i] : 0.0;
+                            }
+                        } else {
+                            const double *gv = static_cast<const double *>(st.ptr) + c0;
+#pragma unroll
+                            for (int i = 0; i < GV; i++) {
+                                o[i] = (i < nv) ? __ldg(gv + i) : 1.0;
+                                y[i] = 0.0;
+                            }
+                        }
+                    } else if (st.kind == FK_SCALAR) {
+                        const double yy = (st.op == FO_DIV && !st.reversed) ? div_helper(st.imm) : 0.0;
+#pragma unroll
+                        for (int i = 0; i < GV; i++) {
+                            o[i] = st.imm;
+                            y[i] = yy;
+                        }
+                    } else if (st.kind == FK_COLVEC) {
+                        const double x = live ? __ldg(static_cast<const double *>(st.ptr) + row * st.ld) : 1.0;
+#pragma unroll
+                        for (int i = 0; i < GV; i++) {
+                            o[i] = x;
+                            y[i] = 0.0;
+                        }
+                    } else if (st.kind == FK_MATRIX) {
+                        const double *mp = static_cast<const double *>(st.ptr) + (live ? row : 0) * st.ld + c0;
+#pragma unroll
+                        for (int i = 0; i < GV; i++) {
+                            o[i] = (i < nv && live) ? __ldg(mp + i) : 1.0;
+                            y[i] = 0.0;
+                        }
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < GV; i++) {
+                            o[i] = 0.0;
+                            y[i] = 0.0;
+                        }
+                    }
+                    apply_step<GV>(st.op, st.reversed != 0, v, o, y);
+#pragma unroll
+                    for (int a = 0; a < FUSED_MAX_AGGS; a++)
+                        if (a < P.ntaps && P.taps[a].after_step == s + 1)
+                            tracker_feed(trk[a], P.taps[a].op, v, (int)c0, nv);
+                }
+                if (P.ew_out) {
+#pragma unroll
+                    for (int i = 0; i < GV; i++)
+                        if (i < nv)
+                            myrow[k0 + i] = v[i];
+                }
+            }
+            if (P.ew_out) {
+                __syncthreads();
+                double *out = static_cast<double *>(P.ew_out);
+                const bool out_vec = ALIGNED && cw == CK && ((P.ew_out_ld & 1) == 0) &&
+                                     ((reinterpret_cast<uintptr_t>(out) & 15u) == 0);
+                if (out_vec) {
+#pragma unroll
+                    for (int i = 0; i < CK / 2; i++) {
+                        const int idx = tid + i * RT;
+                        const int r = idx >> 4, k = idx & 15;
+                        if (r < rows_here) {
+                            Pack<double> q;
+                            q.v[0] = tile[r * PITCH + 2 * k];
+                            q.v[1] = tile[r * PITCH + 2 * k + 1];
+                            st_pack_stream(out + (row0 + r) * P.ew_out_ld + cc + 2 * k, q);
+                        }
+                    }
+                } else {
+                    for (int idx = tid; idx < RT * cw; idx += RT) {
+                        const int r = idx / cw, k = idx - r * cw;
+                        if (r < rows_here)
+                            out[(row0 + r) * P.ew_out_ld + cc + k] = tile[r * PITCH + k];
+                    }
+                }
+            }
+        }
+        // one row per thread: results of consecutive rows are written by consecutive threads
+        if (live) {
+#pragma unroll
+            for (int a = 0; a < FUSED_MAX_AGGS; a++) {
+                if (a < P.ntaps) {
+                    const FusedTap &tp = P.taps[a];
+                    RowTracker t = trk[a];
+                    const bool ext = tp.op == DB2_AGG_MIN || tp.op == DB2_AGG_MAX || tp.op == DB2_AGG_IDXMIN ||
+                                     tp.op == DB2_AGG_IDXMAX;
+                    if (ext && (t.first_nan || t.c == NO_COL)) {
+                        t.v = NAN; // only reachable when the first element is NaN (or every element is)
+                        t.c = 0;
+                    }
+                    if (tp.op == DB2_AGG_IDXMIN || tp.op == DB2_AGG_IDXMAX)
+                        static_cast<uint64_t *>(tp.out)[row * tp.out_ld] = (uint64_t)t.c;
+                    else if (tp.op == DB2_AGG_MEAN)
+                        static_cast<double *>(tp.out)[row * tp.out_ld] = __ddiv_rn(t.v, (double)cols);
+                    else
+                        static_cast<double *>(tp.out)[row * tp.out_ld] = t.v;
+                }
+            }
+        }
+    }
+}
+
+int fused_row_pass_f64(const FusedProgram &prog, cudaStream_t st) {
+    if (prog.rows == 0 || prog.cols == 0)
+        return DB2_OK;
+    const size_t smem = (size_t)(RT * PITCH + prog.smem_elems) * sizeof(double);
+    bool aligned = aligned16(prog.base) && (prog.base_ld % 2 == 0);
+    const int64_t ntiles = (prog.rows + RT - 1) / RT;
+    // resident CTAs per SM are bounded by shared memory (about 34 KB each) and registers; 6 is a safe upper bound
+    const int64_t cap = (int64_t)sm_count() * 6;
+    const int grid = (int)(ntiles < cap ? ntiles : cap);
+    static bool attr_set[2] = {false, false};
+    if (smem > 48 * 1024 && !attr_set[aligned]) {
+        if (aligned)
+            DB2_CUDA(cudaFuncSetAttribute(fused_row_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                          100 * 1024));
+        else
+            DB2_CUDA(cudaFuncSetAttribute(fused_row_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                          100 * 1024));
+        attr_set[aligned] = true;
+    }
+    if (aligned)
+        fused_row_kernel<true><<<grid, RT, smem, st>>>(prog);
+    else
+        fused_row_kernel<false><<<grid, RT, smem, st>>>(prog);
+    return after_launch("fused_row_kernel");
+}
+
+// ---------------------------------------------------------------------------
+// column pass
+// ---------------------------------------------------------------------------
+constexpr int CT = 256;
+enum { CK_SUM = 0, CK_PROD = 1, CK_MIN = 2, CK_MAX = 3 };
+constexpr int64_t POS_NONE = INT64_MAX; // no element seen yet
+constexpr int64_t POS_FIRST_NAN = -1;   // row 0 holds a NaN: the sequential scan of the reference never leaves it
+
+// does candidate (b at row q) replace the current extremum (a at row p)?  Lowest row wins ties.
+template <int KIND> __device__ __forceinline__ bool col_better(double b, int64_t q, double a, int64_t p) {
+    if (q == POS_NONE || p == POS_FIRST_NAN)
+        return false;
+    if (p == POS_NONE || q == POS_FIRST_NAN)
+        return true;
+    return (KIND == CK_MIN) ? (b < a || (b == a && q < p)) : (b > a || (b == a && q < p));
+}
+
+template <int KIND>
+__global__ void __launch_bounds__(CT)
+    fused_col_kernel(const __grid_constant__ FusedProgram P, double *__restrict__ part_v,
+                     int64_t *__restrict__ part_i) {
+    extern __shared__ __align__(16) double csm[];
+    double *sv = csm;                                          // [TY][TX*2]
+    int64_t *si = reinterpret_cast<int64_t *>(csm + CT * 2);   // same shape
+    const int tx = threadIdx.x, ty = threadIdx.y, TX = blockDim.x, TY = blockDim.y;
+    const int64_t rows = P.rows, cols = P.cols;
+    const int64_t c0 = ((int64_t)blockIdx.y * TX + tx) * 2;
+    const int nv = (c0 + 2 <= cols) ? 2 : ((c0 < cols) ? 1 : 0);
+    double acc[2];
+    int64_t pos[2];
+#pragma unroll
+    for (int k = 0; k < 2; k++) {
+        acc[k] = (KIND == CK_SUM) ? 0.0 : (KIND == CK_PROD) ? 1.0 : (KIND == CK_MIN) ? INFINITY : -INFINITY;
+        pos[k] = POS_NONE;
+    }
+    const double *base = static_cast<const double *>(P.base);
+    const bool vec = (P.base_ld % 2 == 0) && aligned16(base) && nv == 2;
+    if (nv > 0) {
+        // row-vector operands are invariant per thread (fixed columns): fetched through L1 on every use
+        const int64_t row_stride = (int64_t)gridDim.x * TY;
+        for (int64_t r = (int64_t)blockIdx.x * TY + ty; r < rows; r += row_stride) {
+            double v[2];
+            if (vec) {
+                const Pack<double> p = ld_pack_stream(base + r * P.base_ld + c0);
+                v[0] = p.v[0];
+                v[1] = p.v[1];
+            } else {
+                v[0] = base[r * P.base_ld + c0];
+                v[1] = (nv == 2) ? base[r * P.base_ld + c0 + 1] : 0.0;
+            }
+            for (int s = 0; s < P.nsteps; s++) {
+                const FusedStep &st = P.steps[s];
+                double o[2], y[2];
+                if (st.kind == FK_ROWVEC) {
+                    const double *gv = static_cast<const double *>(st.ptr) + c0;
+                    o[0] = __ldg(gv);
+                    o[1] = (nv == 2) ? __ldg(gv + 1) : 1.0;
+                    if (st.op == FO_DIV && !st.reversed) {
+                        y[0] = div_helper(o[0]);
+                        y[1] = div_helper(o[1]);
+                    } else
+                        y[0] = y[1] = 0.0;
+                } else if (st.kind == FK_SCALAR) {
+                    o[0] = o[1] = st.imm;
+                    y[0] = y[1] = (st.op == FO_DIV && !st.reversed) ? div_helper(st.imm) : 0.0;
+                } else if (st.kind == FK_COLVEC) {
+                    o[0] = o[1] = __ldg(static_cast<const double *>(st.ptr) + r * st.ld);
+                    y[0] = y[1] = 0.0;
+                } else if (st.kind == FK_MATRIX) {
+                    const double *mp = static_cast<const double *>(st.ptr) + r * st.ld + c0;
+                    o[0] = __ldg(mp);
+                    o[1] = (nv == 2) ? __ldg(mp + 1) : 1.0;
+                    y[0] = y[1] = 0.0;
+                } else {
+                    o[0] = o[1] = y[0] = y[1] = 0.0;
+                }
+                apply_step<2>(st.op, st.reversed != 0, v, o, y);
+            }
+#pragma unroll
+            for (int k = 0; k < 2; k++) {
+                if (KIND == CK_SUM)
+                    acc[k] = __dadd_rn(acc[k], v[k]);
+                else if (KIND == CK_PROD)
+                    acc[k] = __dmul_rn(acc[k], v[k]);
+                else {
+                    if (r == 0 && v[k] != v[k]) {
+                        acc[k] = v[k];
+                        pos[k] = POS_FIRST_NAN;
+                    } else if (v[k] == v[k] && col_better<KIND>(v[k], r, acc[k], pos[k])) {
+                        acc[k] = v[k];
+                        pos[k] = r;
+                    }
+                }
+            }
+        }
+    }
+#pragma unroll
+    for (int k = 0; k < 2; k++) {
+        sv[(ty * TX + tx) * 2 + k] = acc[k];
+        si[(ty * TX + tx) * 2 + k] = pos[k];
+    }
+    __syncthreads();
+    for (int k = ty; k < 2; k += TY) {
+        if (c0 + k < cols) {
+            double a = sv[tx * 2 + k];
+            int64_t p = si[tx * 2 + k];
+            for (int yv = 1; yv < TY; yv++) {
+                const double b = sv[(yv * TX + tx) * 2 + k];
+                const int64_t q = si[(yv * TX + tx) * 2 + k];
+                if (KIND == CK_SUM)
+                    a = __dadd_rn(a, b);
+                else if (KIND == CK_PROD)
+                    a = __dmul_rn(a, b);
+                else if (col_better<KIND>(b, q, a, p)) {
+                    a = b;
+                    p = q;
+                }
+            }
+            part_v[(int64_t)blockIdx.x * cols + c0 + k] = a;
+            part_i[(int64_t)blockIdx.x * cols + c0 + k] = p;
+        }
+    }
+}
+
+// second stage for the chain column pass: folds the per-CTA partials in order and applies the epilogue
+template <int KIND>
+__global__ void fused_col_final_kernel(const double *__restrict__ part_v, const int64_t *__restrict__ part_i,
+                                       int nparts, int64_t cols, int64_t count, int out_mode, void *__restrict__ res) {
+    const int64_t c = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= cols)
+        return;
+    double a = part_v[c];
+    int64_t p = part_i[c];
+    for (int i = 1; i < nparts; i++) {
+        const double b = part_v[(int64_t)i * cols + c];
+        const int64_t q = part_i[(int64_t)i * cols + c];
+        if (KIND == CK_SUM)
+            a = __dadd_rn(a, b);
+        else if (KIND == CK_PROD)
+            a = __dmul_rn(a, b);
+        else if (col_better<KIND>(b, q, a, p)) {
+            a = b;
+            p = q;
+        }
+    }
+    if (out_mode == 1)
+        static_cast<uint64_t *>(res)[c] = (p == POS_NONE || p == POS_FIRST_NAN) ? 0 : (uint64_t)p;
+    else if (out_mode == 2)
+        static_cast<double *>(res)[c] = __ddiv_rn(a, (double)count);
+    else
+        static_cast<double *>(res)[c] = ((KIND == CK_MIN || KIND == CK_MAX) && p == POS_NONE) ? (double)NAN : a;
+}
+
+size_t fused_col_scratch_bytes(int64_t cols) { return (size_t)sm_count() * 8 * cols * 16 + 256; }
+
+template <int KIND>
+static int fused_col_launch(const FusedProgram &prog, int out_mode, void *res, void *scratch, cudaStream_t st) {
+    const int64_t packets = (prog.cols + 1) / 2;
+    int tx = next_pow2(packets);
+    if (tx > 32)
+        tx = 32;
+    const int ty = CT / tx;
+    const int gy = (int)((packets + tx - 1) / tx);
+    int64_t cap = ((int64_t)sm_count() * 8 + gy - 1) / gy;
+    int64_t want = (prog.rows + (int64_t)ty * 4 - 1) / ((int64_t)ty * 4);
+    if (want < 1)
+        want = 1;
+    const int gx = (int)(want < cap ? want : cap);
+    double *part_v = static_cast<double *>(scratch);
+    int64_t *part_i = reinterpret_cast<int64_t *>(part_v + (size_t)gx * prog.cols);
+    fused_col_kernel<KIND><<<dim3(gx, gy), dim3(tx, ty), CT * 2 * 16, st>>>(prog, part_v, part_i);
+    DB2_TRY(after_launch("fused_col_kernel"));
+    fused_col_final_kernel<KIND>
+        <<<(unsigned)((prog.cols + 127) / 128), 128, 0, st>>>(part_v, part_i, gx, prog.cols, prog.rows, out_mode, res);
+    return after_launch("fused_col_final_kernel");
+}
+
+int fused_col_pass_f64(const FusedProgram &prog, int agg_op, void *res, void *scratch, size_t scratch_bytes,
+                       cudaStream_t st) {
+    if (prog.cols == 0)
+        return DB2_OK;
+    DB2_CHECK(prog.rows > 0, DB2_EINVAL, "aggCol on a matrix without rows");
+    DB2_CHECK(scratch && scratch_bytes >= fused_col_scratch_bytes(prog.cols), DB2_EINVAL, "scratch too small");
+    switch (agg_op) {
+    case DB2_AGG_SUM: return fused_col_launch<CK_SUM>(prog, 0, res, scratch, st);
+    case DB2_AGG_MEAN: return fused_col_launch<CK_SUM>(prog, 2, res, scratch, st);
+    case DB2_AGG_PROD: return fused_col_launch<CK_PROD>(prog, 0, res, scratch, st);
+    case DB2_AGG_MIN: return fused_col_launch<CK_MIN>(prog, 0, res, scratch, st);
+    case DB2_AGG_MAX: return fused_col_launch<CK_MAX>(prog, 0, res, scratch, st);
+    case DB2_AGG_IDXMIN: return fused_col_launch<CK_MIN>(prog, 1, res, scratch, st);
+    case DB2_AGG_IDXMAX: return fused_col_launch<CK_MAX>(prog, 1, res, scratch, st);
+    default: return set_error(DB2_EUNSUPPORTED, "AggOpCode %d has no fused column pass", agg_op);
+    }
+}
+
+} // namespace db2

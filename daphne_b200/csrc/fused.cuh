@@ -1,0 +1,73 @@
+// Fused evaluation of deferred elementwise chains.
+//
+// DAPHNE's compiled pipelines call one kernel per operator, so a chain such as  Z = (X - mu) / sd;  r = sum(Z^2, 0);
+// m = aggMax(Z, 0);  i = idxMax(Z, 0)  would move the 4 GiB operand through HBM once per call.  The runtime therefore
+// records cheap elementwise operators as a CHAIN on their (materialised) base operand instead of running them, and
+// the consumers -- row aggregations, column aggregations, or a plain materialisation -- evaluate the chain inside
+// their own load loop: value = base[r][c]; for each step: value = op(value, operand) with the operand a same-shape
+// matrix, a row vector, a column vector or an immediate.  Several row aggregations whose chains are prefixes of one
+// another are served by ONE pass ("taps" after the step where their chain ends).
+//
+// The step list is a tiny interpreted program (uniform control flow: every thread executes the same step), passed to
+// the kernel as a __grid_constant__ parameter; there is no run-time code generation.
+#pragma once
+
+#include "common.cuh"
+
+namespace db2 {
+
+constexpr int FUSED_MAX_STEPS = 10;
+constexpr int FUSED_MAX_AGGS = 4;
+
+enum FusedOperandKind : int32_t {
+    FK_MATRIX = 0, // same shape as the base operand
+    FK_ROWVEC = 1, // 1 x cols
+    FK_COLVEC = 2, // rows x 1
+    FK_SCALAR = 3, // immediate
+    FK_UNARY = 4,  // no operand
+};
+
+// internal opcode of a fused step (a subset of the binary/unary op codes: the cheap, exactly rounded ones)
+enum FusedOp : int32_t {
+    FO_ADD = 0, FO_SUB, FO_MUL, FO_DIV, FO_SQUARE, FO_EQ, FO_NEQ, FO_LT, FO_LE, FO_GT, FO_GE, FO_MIN, FO_MAX, FO_AND,
+    FO_OR, FO_NEG, FO_ABS, FO_SIGN, FO_FLOOR, FO_CEIL, FO_ROUND, FO_ISNAN, FO_COUNT
+};
+
+struct FusedStep {
+    int32_t kind;     // FusedOperandKind
+    int32_t op;       // FusedOp
+    int32_t reversed; // operand (op) value instead of value (op) operand
+    int32_t smem_off; // ROWVEC operands staged in shared memory: element offset of this step's copy, else -1
+    const void *ptr;  // operand (device) for MATRIX / ROWVEC / COLVEC
+    int64_t ld;       // leading dimension of a MATRIX / COLVEC operand
+    double imm;       // SCALAR operand
+};
+
+struct FusedTap {
+    int32_t after_step; // the aggregation sees the value after this many steps (0 = the base operand itself)
+    int32_t op;         // AggOpCode: SUM, PROD, MIN, MAX, IDXMIN, IDXMAX, MEAN
+    void *out;          // rows x 1 result (value type, or uint64 for IDXMIN/IDXMAX)
+    int64_t out_ld;
+};
+
+struct FusedProgram {
+    const void *base;
+    int64_t base_ld;
+    int64_t rows, cols;
+    int32_t nsteps, ntaps;
+    int32_t smem_elems; // total elements of staged row-vector operands (2 per column and step: value, reciprocal)
+    int32_t pad;
+    void *ew_out; // if set: the value after all steps is stored here (materialisation)
+    int64_t ew_out_ld;
+    FusedStep steps[FUSED_MAX_STEPS];
+    FusedTap taps[FUSED_MAX_AGGS];
+};
+
+// host side launchers (fused.cu)
+int fused_row_pass_f64(const FusedProgram &prog, cudaStream_t st);
+// column aggregation of a chain: kind = K_SUM / K_MIN / K_MAX / K_PROD of agg.cu, epilogue like db2k_agg_col
+int fused_col_pass_f64(const FusedProgram &prog, int agg_op, void *res, void *scratch, size_t scratch_bytes,
+                       cudaStream_t st);
+size_t fused_col_scratch_bytes(int64_t cols);
+
+} // namespace db2

@@ -1,0 +1,358 @@
+// Deferred evaluation: cheap elementwise operator calls on large f64 matrices are recorded as a chain on their base
+// operand; row aggregations of such chains (or of plain matrices) are parked as "pending" results; the first time a
+// pending or deferred value is actually needed, one fused pass (fused.cu) produces it together with every pending
+// sibling whose chain is a prefix-compatible view of the same base operand.
+//
+// Why this is safe: DAPHNE's data objects are immutable values (the compiler's SSA form; results are fresh objects),
+// so a chain may keep reading its operands until it is evaluated; every operand's buffer is kept alive by the chain.
+// Callers that wrap their own device buffers must not overwrite them while results derived from them are alive.
+// A context and its matrices are driven by one host thread at a time (the reference runs one WorkerGPU thread per
+// CUDA context, src/runtime/local/vectorized/WorkerGPU.h:38-52).
+#include "fused.cuh"
+#include "runtime.h"
+
+#include <algorithm>
+#include <cmath>
+
+namespace db2 {
+
+static constexpr int64_t LAZY_MIN_ELEMS = 1 << 16; // below this an immediate kernel is cheaper than bookkeeping
+
+static int fused_binary_op(int op) {
+    switch (op) {
+    case DB2_ADD: return FO_ADD;
+    case DB2_SUB: return FO_SUB;
+    case DB2_MUL: return FO_MUL;
+    case DB2_DIV: return FO_DIV;
+    case DB2_EQ: return FO_EQ;
+    case DB2_NEQ: return FO_NEQ;
+    case DB2_LT: return FO_LT;
+    case DB2_LE: return FO_LE;
+    case DB2_GT: return FO_GT;
+    case DB2_GE: return FO_GE;
+    case DB2_MIN: return FO_MIN;
+    case DB2_MAX: return FO_MAX;
+    case DB2_AND: return FO_AND;
+    case DB2_OR: return FO_OR;
+    default: return -1;
+    }
+}
+static int fused_unary_op(int op) {
+    switch (op) {
+    case DB2_U_MINUS: return FO_NEG;
+    case DB2_U_ABS: return FO_ABS;
+    case DB2_U_SIGN: return FO_SIGN;
+    case DB2_U_FLOOR: return FO_FLOOR;
+    case DB2_U_CEIL: return FO_CEIL;
+    case DB2_U_ROUND: return FO_ROUND;
+    case DB2_U_ISNAN: return FO_ISNAN;
+    default: return -1;
+    }
+}
+
+static bool lazy_candidate(const db2_context *ctx, const db2_matrix *m) {
+    return !ctx->eager && m->dtype == DB2_F64 && m->rows * m->cols >= LAZY_MIN_ELEMS && m->cols < (1 << 30);
+}
+
+static int operand_of(db2_matrix *m, Operand *out) {
+    DB2_TRY(ensure_device(m)); // materialises deferred operands
+    out->buf = m->dev;
+    out->off = m->dev_off;
+    out->ld = m->dev_ld;
+    out->rows = m->rows;
+    out->cols = m->cols;
+    return DB2_OK;
+}
+
+// the chain that `m` stands for: its own when deferred, else a fresh chain on the matrix itself
+static int chain_of(db2_matrix *m, std::shared_ptr<Expr> *out) {
+    auto e = std::make_shared<Expr>();
+    if (m->lazy) {
+        *e = *m->lazy;
+    } else {
+        e->dtype = m->dtype;
+        e->rows = m->rows;
+        e->cols = m->cols;
+        DB2_TRY(operand_of(m, &e->base));
+    }
+    *out = e;
+    return DB2_OK;
+}
+
+static db2_matrix *new_deferred(db2_context *ctx, int dtype, int64_t rows, int64_t cols) {
+    db2_matrix *m = new db2_matrix();
+    m->ctx = ctx;
+    m->dtype = dtype;
+    m->rows = rows;
+    m->cols = cols;
+    return m;
+}
+
+int lazy_try_binary(db2_context *ctx, int op, db2_matrix **res, db2_matrix *lhs, db2_matrix *rhs, bool *handled) {
+    *handled = false;
+    const int fop = fused_binary_op(op);
+    if (*res != nullptr || fop < 0 || !lazy_candidate(ctx, lhs) || rhs->dtype != DB2_F64)
+        return DB2_OK;
+    if (lhs->pend_src || rhs->pend_src) // pending aggregates are column vectors that have to exist first
+        return DB2_OK;
+    int kind;
+    if (lhs->rows == rhs->rows && lhs->cols == rhs->cols)
+        kind = FK_MATRIX;
+    else if (lhs->cols == rhs->cols && rhs->rows == 1 && lhs->rows > 1)
+        kind = FK_ROWVEC;
+    else if (lhs->rows == rhs->rows && rhs->cols == 1 && lhs->cols > 1)
+        kind = FK_COLVEC;
+    else
+        return DB2_OK; // unusual broadcast forms run immediately
+    std::shared_ptr<Expr> e;
+    ExprStep st;
+    st.kind = kind;
+    st.op = fop;
+    if (kind == FK_MATRIX && rhs->lazy && !lhs->lazy) {
+        // the deferred side is the right operand: continue ITS chain with the operands swapped
+        DB2_TRY(chain_of(rhs, &e));
+        st.reversed = true;
+        DB2_TRY(operand_of(lhs, &st.operand));
+    } else {
+        DB2_TRY(chain_of(lhs, &e));
+        DB2_TRY(operand_of(rhs, &st.operand)); // a deferred rhs is produced first
+    }
+    if ((int)e->steps.size() >= FUSED_MAX_STEPS)
+        return DB2_OK; // chain full: run this operator immediately (its inputs are materialised on demand)
+    e->steps.push_back(st);
+    db2_matrix *r = new_deferred(ctx, DB2_F64, lhs->rows, lhs->cols);
+    r->lazy = e;
+    *res = r;
+    *handled = true;
+    return DB2_OK;
+}
+
+int lazy_try_scalar(db2_context *ctx, int op, db2_matrix **res, db2_matrix *lhs, const void *scalar, bool *handled) {
+    *handled = false;
+    if (*res != nullptr || !lazy_candidate(ctx, lhs) || lhs->pend_src)
+        return DB2_OK;
+    const double s = *static_cast<const double *>(scalar);
+    int fop = fused_binary_op(op);
+    if (op == DB2_POW && s == 2.0)
+        fop = FO_SQUARE;
+    if (fop < 0)
+        return DB2_OK;
+    std::shared_ptr<Expr> e;
+    DB2_TRY(chain_of(lhs, &e));
+    if ((int)e->steps.size() >= FUSED_MAX_STEPS)
+        return DB2_OK;
+    ExprStep st;
+    st.kind = FK_SCALAR;
+    st.op = fop;
+    st.imm = s;
+    e->steps.push_back(st);
+    db2_matrix *r = new_deferred(ctx, DB2_F64, lhs->rows, lhs->cols);
+    r->lazy = e;
+    *res = r;
+    *handled = true;
+    return DB2_OK;
+}
+
+int lazy_try_unary(db2_context *ctx, int op, db2_matrix **res, db2_matrix *arg, bool *handled) {
+    *handled = false;
+    const int fop = fused_unary_op(op);
+    if (*res != nullptr || fop < 0 || !lazy_candidate(ctx, arg) || arg->pend_src)
+        return DB2_OK;
+    std::shared_ptr<Expr> e;
+    DB2_TRY(chain_of(arg, &e));
+    if ((int)e->steps.size() >= FUSED_MAX_STEPS)
+        return DB2_OK;
+    ExprStep st;
+    st.kind = FK_UNARY;
+    st.op = fop;
+    e->steps.push_back(st);
+    db2_matrix *r = new_deferred(ctx, DB2_F64, arg->rows, arg->cols);
+    r->lazy = e;
+    *res = r;
+    *handled = true;
+    return DB2_OK;
+}
+
+static bool row_agg_fusable(int op) {
+    return op == DB2_AGG_SUM || op == DB2_AGG_PROD || op == DB2_AGG_MIN || op == DB2_AGG_MAX ||
+           op == DB2_AGG_IDXMIN || op == DB2_AGG_IDXMAX || op == DB2_AGG_MEAN;
+}
+
+int lazy_try_agg_row(db2_context *ctx, int op, db2_matrix **res, db2_matrix *arg, bool *handled) {
+    *handled = false;
+    if (*res != nullptr || !row_agg_fusable(op) || !lazy_candidate(ctx, arg) || arg->pend_src || arg->cols < 2)
+        return DB2_OK;
+    std::shared_ptr<Expr> e;
+    if (arg->lazy)
+        e = std::const_pointer_cast<Expr>(arg->lazy); // shared, never modified
+    else
+        DB2_TRY(chain_of(arg, &e));
+    const bool idx = op == DB2_AGG_IDXMIN || op == DB2_AGG_IDXMAX;
+    db2_matrix *r = new_deferred(ctx, idx ? DB2_U64 : DB2_F64, arg->rows, 1);
+    r->pend_src = e;
+    r->pend_op = op;
+    ctx->pending.push_back(r);
+    *res = r;
+    *handled = true;
+    // bound the backlog: a full group is produced right away
+    int same_base = 0;
+    for (db2_matrix *p : ctx->pending)
+        if (p->pend_src->base.same(e->base))
+            same_base++;
+    if (same_base >= FUSED_MAX_AGGS)
+        return lazy_force(r);
+    return DB2_OK;
+}
+
+// fills the device-side program from a chain; returns false if the chain cannot be expressed (never for chains
+// built above)
+static void build_program(const Expr &e, size_t nsteps, FusedProgram *P) {
+    memset(P, 0, sizeof(*P));
+    P->base = e.base.ptr(8);
+    P->base_ld = e.base.ld;
+    P->rows = e.rows;
+    P->cols = e.cols;
+    P->nsteps = (int)nsteps;
+    int smem = 0;
+    const int smem_budget = (56 * 1024) / 8; // doubles, on top of the 33 KB tile
+    for (size_t i = 0; i < nsteps; i++) {
+        const ExprStep &s = e.steps[i];
+        FusedStep &d = P->steps[i];
+        d.kind = s.kind;
+        d.op = s.op;
+        d.reversed = s.reversed ? 1 : 0;
+        d.smem_off = -1;
+        d.imm = s.imm;
+        if (s.kind == FK_MATRIX || s.kind == FK_ROWVEC || s.kind == FK_COLVEC) {
+            d.ptr = s.operand.ptr(8);
+            d.ld = s.operand.ld;
+        }
+        if (s.kind == FK_ROWVEC) {
+            const int need = (int)e.cols * ((s.op == FO_DIV && !s.reversed) ? 2 : 1);
+            if (smem + need <= smem_budget) {
+                d.smem_off = smem;
+                smem += need;
+            }
+        }
+    }
+    P->smem_elems = smem;
+}
+
+static bool is_prefix(const Expr &a, const Expr &b) { // a's chain is a prefix of b's (same base)
+    if (!a.base.same(b.base) || a.rows != b.rows || a.cols != b.cols || a.steps.size() > b.steps.size())
+        return false;
+    for (size_t i = 0; i < a.steps.size(); i++)
+        if (!a.steps[i].same(b.steps[i]))
+            return false;
+    return true;
+}
+
+static void unpend(db2_context *ctx, db2_matrix *m) {
+    auto &v = ctx->pending;
+    v.erase(std::remove(v.begin(), v.end(), m), v.end());
+}
+
+// One fused pass over `longest`: materialises `ew_target` (may be null) and every pending aggregation in `group`.
+static int run_row_pass(db2_context *ctx, const Expr &longest, db2_matrix *ew_target,
+                        const std::vector<db2_matrix *> &group) {
+    FusedProgram P;
+    build_program(longest, longest.steps.size(), &P);
+    if (ew_target) {
+        ew_target->dev = make_devbuf(ctx, (size_t)longest.rows * longest.cols * 8);
+        ew_target->dev_off = 0;
+        ew_target->dev_ld = longest.cols;
+        P.ew_out = ew_target->dev->ptr;
+        P.ew_out_ld = longest.cols;
+    }
+    P.ntaps = (int)group.size();
+    for (size_t i = 0; i < group.size(); i++) {
+        db2_matrix *g = group[i];
+        g->dev = make_devbuf(ctx, (size_t)g->rows * 8);
+        g->dev_off = 0;
+        g->dev_ld = 1;
+        P.taps[i].after_step = (int)g->pend_src->steps.size();
+        P.taps[i].op = g->pend_op;
+        P.taps[i].out = g->dev->ptr;
+        P.taps[i].out_ld = 1;
+    }
+    DB2_TRY(fused_row_pass_f64(P, ctx->stream));
+    if (ew_target) {
+        ew_target->dev_valid = true;
+        ew_target->lazy.reset();
+    }
+    for (db2_matrix *g : group) {
+        g->dev_valid = true;
+        g->pend_src.reset();
+        g->pend_op = -1;
+        unpend(ctx, g);
+    }
+    return DB2_OK;
+}
+
+int lazy_force(db2_matrix *m) {
+    db2_context *ctx = m->ctx;
+    bind_device(ctx);
+    const uint64_t before = g_launches.load();
+    int rc = DB2_OK;
+    if (m->lazy) {
+        // materialisation; pending aggregations of prefixes of this chain ride along
+        std::shared_ptr<const Expr> e = m->lazy;
+        std::vector<db2_matrix *> group;
+        for (db2_matrix *p : ctx->pending)
+            if ((int)group.size() < FUSED_MAX_AGGS && is_prefix(*p->pend_src, *e))
+                group.push_back(p);
+        rc = run_row_pass(ctx, *e, m, group);
+    } else if (m->pend_src) {
+        std::shared_ptr<const Expr> longest = m->pend_src;
+        std::vector<db2_matrix *> group{m};
+        for (db2_matrix *p : ctx->pending) {
+            if (p == m || (int)group.size() >= FUSED_MAX_AGGS)
+                continue;
+            if (is_prefix(*p->pend_src, *longest)) {
+                group.push_back(p);
+            } else if (is_prefix(*longest, *p->pend_src)) {
+                longest = p->pend_src;
+                group.push_back(p);
+            }
+        }
+        rc = run_row_pass(ctx, *longest, nullptr, group);
+    }
+    {
+        std::lock_guard<std::mutex> lock(ctx->mu);
+        ctx->stats.launches += g_launches.load() - before;
+    }
+    return rc;
+}
+
+int lazy_flush_all(db2_context *ctx) {
+    while (!ctx->pending.empty())
+        DB2_TRY(lazy_force(ctx->pending.front()));
+    return DB2_OK;
+}
+
+void lazy_forget(db2_matrix *m) {
+    if (m->pend_src && m->ctx)
+        unpend(m->ctx, m);
+}
+
+int lazy_try_agg_col(db2_context *ctx, int op, db2_matrix **res, db2_matrix *arg, bool *handled) {
+    *handled = false;
+    if (!arg->lazy || ctx->eager)
+        return DB2_OK; // plain matrices use the dedicated column kernels
+    const bool ok = op == DB2_AGG_SUM || op == DB2_AGG_PROD || op == DB2_AGG_MIN || op == DB2_AGG_MAX ||
+                    op == DB2_AGG_IDXMIN || op == DB2_AGG_IDXMAX || op == DB2_AGG_MEAN;
+    if (!ok)
+        return DB2_OK; // VAR/STDDEV: the argument is materialised and the two-pass kernels run
+    std::shared_ptr<const Expr> e = arg->lazy;
+    const bool idx = op == DB2_AGG_IDXMIN || op == DB2_AGG_IDXMAX;
+    DB2_TRY(prepare_result(ctx, res, idx ? DB2_U64 : DB2_F64, 1, arg->cols));
+    FusedProgram P;
+    build_program(*e, e->steps.size(), &P);
+    void *scratch = nullptr;
+    DB2_TRY(ctx_scratch(ctx, fused_col_scratch_bytes(arg->cols), &scratch));
+    DB2_TRY(fused_col_pass_f64(P, op, (*res)->dev_ptr(), scratch, ctx->scratch_bytes, ctx->stream));
+    *handled = true;
+    return DB2_OK;
+}
+
+} // namespace db2

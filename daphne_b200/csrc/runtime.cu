@@ -97,6 +97,8 @@ std::shared_ptr<DevBuf> make_devbuf(db2_context *ctx, size_t bytes) {
 int ensure_device(db2_matrix *m) {
     if (m->dev_valid)
         return DB2_OK;
+    if (m->deferred())
+        return lazy_force(m);
     DB2_CHECK(m->host_valid && m->host, DB2_EINVAL, "matrix has no valid placement");
     db2_context *ctx = m->ctx;
     bind_device(ctx);
@@ -128,7 +130,15 @@ int prepare_result(db2_context *ctx, db2_matrix **res, int dtype, int64_t rows, 
     DB2_CHECK(r->dtype == dtype && r->rows == rows && r->cols == cols, DB2_EINVAL,
               "pre-allocated result has shape (%lld x %lld) / type %d, expected (%lld x %lld) / type %d",
               (long long)r->rows, (long long)r->cols, r->dtype, (long long)rows, (long long)cols, dtype);
-    if (!r->dev) {
+    if (r->deferred()) {
+        lazy_forget(r);
+        r->lazy.reset();
+        r->pend_src.reset();
+        r->pend_op = -1;
+    }
+    // a buffer that deferred chains (or other handles) still read is not overwritten: the result gets a fresh one.
+    // Row views are the exception: writing through a view is how results are placed into a larger matrix.
+    if (!r->dev || (!r->is_view && r->dev.use_count() > 1)) {
         r->dev = make_devbuf(ctx, (size_t)rows * cols * r->esize());
         r->dev_off = 0;
         r->dev_ld = cols;
@@ -164,6 +174,8 @@ int db2_context_create(int device, db2_context **out) {
     DB2_CUDA(cudaSetDevice(device));
     std::unique_ptr<db2_context> ctx(new db2_context());
     ctx->device = device;
+    const char *eager = getenv("DB2_EAGER");
+    ctx->eager = eager && eager[0] == '1';
     DB2_CUDA(cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking));
     DB2_CUDA(cudaDeviceGetDefaultMemPool(&ctx->pool, device));
     uint64_t threshold = UINT64_MAX; // keep freed blocks cached in the pool instead of returning them to the driver
@@ -195,6 +207,7 @@ void *db2_context_stream(db2_context *ctx) { return ctx ? ctx->stream : nullptr;
 int db2_context_sync(db2_context *ctx) {
     DB2_CHECK(ctx, DB2_EINVAL, "null context");
     bind_device(ctx);
+    DB2_TRY(lazy_flush_all(ctx));
     DB2_CUDA(cudaStreamSynchronize(ctx->stream));
     return DB2_OK;
 }
@@ -276,9 +289,10 @@ int db2_matrix_slice_rows(db2_matrix *src, int64_t r0, int64_t r1, db2_matrix **
     m->dtype = src->dtype;
     m->rows = r1 - r0;
     m->cols = src->cols;
+    m->is_view = true;
     // a view shares the parent's buffers; make the parent's device placement current first so that all views of a
-    // host matrix share one transfer
-    if (src->host_valid && !src->dev_valid && src->ctx)
+    // host matrix share one transfer (and a deferred parent is produced once)
+    if (!src->dev_valid && src->ctx)
         DB2_TRY(ensure_device(src));
     if (src->dev) {
         m->dev = src->dev;
@@ -305,8 +319,11 @@ int db2_matrix_incref(db2_matrix *m) {
 int db2_matrix_decref(db2_matrix *m) {
     if (!m)
         return DB2_OK;
-    if (m->refs.fetch_sub(1) == 1)
+    if (m->refs.fetch_sub(1) == 1) {
+        if (m->deferred())
+            lazy_forget(m);
         delete m;
+    }
     return DB2_OK;
 }
 int db2_matrix_info(const db2_matrix *m, int *dtype, int64_t *rows, int64_t *cols) {
@@ -337,6 +354,8 @@ int db2_matrix_to_host(db2_matrix *m, void *dst, int64_t dst_ld) {
     const size_t es = m->esize();
     if (m->rows * m->cols == 0)
         return DB2_OK;
+    if (m->deferred())
+        DB2_TRY(lazy_force(m));
     if (m->dev_valid) {
         db2_context *ctx = m->ctx;
         bind_device(ctx);
@@ -374,6 +393,13 @@ int db2_ewBinaryMat(db2_context *ctx, int op, db2_matrix **res, db2_matrix *lhs,
               (long long)lhs->rows, (long long)lhs->cols, (long long)rhs->rows, (long long)rhs->cols);
     bind_device(ctx);
     const uint64_t before = g_launches.load();
+    DB2_CHECK(res, DB2_EINVAL, "null result slot");
+    bool handled = false;
+    DB2_TRY(lazy_try_binary(ctx, op, res, lhs, rhs, &handled));
+    if (handled) {
+        count_launches(ctx, before);
+        return DB2_OK;
+    }
     DB2_TRY(ensure_device(lhs));
     DB2_TRY(ensure_device(rhs));
     DB2_TRY(prepare_result(ctx, res, lhs->dtype, lhs->rows, lhs->cols));
@@ -390,6 +416,13 @@ int db2_ewBinaryObjSca(db2_context *ctx, int op, db2_matrix **res, db2_matrix *l
     DB2_CHECK(ctx && lhs && scalar, DB2_EINVAL, "null argument");
     bind_device(ctx);
     const uint64_t before = g_launches.load();
+    DB2_CHECK(res, DB2_EINVAL, "null result slot");
+    bool handled = false;
+    DB2_TRY(lazy_try_scalar(ctx, op, res, lhs, scalar, &handled));
+    if (handled) {
+        count_launches(ctx, before);
+        return DB2_OK;
+    }
     DB2_TRY(ensure_device(lhs));
     DB2_TRY(prepare_result(ctx, res, lhs->dtype, lhs->rows, lhs->cols));
     db2_matrix *r = *res;
@@ -409,6 +442,13 @@ int db2_ewUnaryMat(db2_context *ctx, int op, db2_matrix **res, db2_matrix *arg) 
     DB2_CHECK(ctx && arg, DB2_EINVAL, "null argument");
     bind_device(ctx);
     const uint64_t before = g_launches.load();
+    DB2_CHECK(res, DB2_EINVAL, "null result slot");
+    bool handled = false;
+    DB2_TRY(lazy_try_unary(ctx, op, res, arg, &handled));
+    if (handled) {
+        count_launches(ctx, before);
+        return DB2_OK;
+    }
     DB2_TRY(ensure_device(arg));
     DB2_TRY(prepare_result(ctx, res, arg->dtype, arg->rows, arg->cols));
     db2_matrix *r = *res;
@@ -442,6 +482,13 @@ int db2_aggRow(db2_context *ctx, int op, db2_matrix **res, db2_matrix *arg) {
     DB2_CHECK(ctx && arg, DB2_EINVAL, "null argument");
     bind_device(ctx);
     const uint64_t before = g_launches.load();
+    DB2_CHECK(res, DB2_EINVAL, "null result slot");
+    bool handled = false;
+    DB2_TRY(lazy_try_agg_row(ctx, op, res, arg, &handled));
+    if (handled) {
+        count_launches(ctx, before);
+        return DB2_OK;
+    }
     DB2_TRY(ensure_device(arg));
     DB2_TRY(prepare_result(ctx, res, agg_result_dtype(op, arg->dtype), arg->rows, 1));
     db2_matrix *r = *res;
@@ -457,6 +504,13 @@ int db2_aggCol(db2_context *ctx, int op, db2_matrix **res, db2_matrix *arg) {
     DB2_CHECK(ctx && arg, DB2_EINVAL, "null argument");
     bind_device(ctx);
     const uint64_t before = g_launches.load();
+    DB2_CHECK(res, DB2_EINVAL, "null result slot");
+    bool handled = false;
+    DB2_TRY(lazy_try_agg_col(ctx, op, res, arg, &handled));
+    if (handled) {
+        count_launches(ctx, before);
+        return DB2_OK;
+    }
     DB2_TRY(ensure_device(arg));
     DB2_TRY(prepare_result(ctx, res, agg_result_dtype(op, arg->dtype), 1, arg->cols));
     db2_matrix *r = *res;

@@ -9,8 +9,16 @@
 #include <string>
 #include <vector>
 
+struct db2_matrix;
+namespace db2 {
+struct Expr;
+}
+
 struct db2_context {
     int device = 0;
+    // deferred evaluation (lazy.cu): row aggregations waiting to be served by one fused pass
+    std::vector<db2_matrix *> pending;
+    bool eager = false; // DB2_EAGER=1: run every operator call immediately (no fusion)
     cudaStream_t stream = nullptr;
     cudaMemPool_t pool = nullptr;
     // reusable scratch for two-stage reductions (grown on demand, stream-ordered reuse)
@@ -78,13 +86,62 @@ struct db2_matrix {
     int64_t host_off = 0;
     int64_t host_ld = 0;
     bool host_valid = false;
+    // deferred elementwise chain: the values are expr(base operand) and no placement is valid yet
+    std::shared_ptr<const db2::Expr> lazy;
+    // pending row aggregation `pend_op` of `pend_src`, produced together with its siblings when first needed
+    std::shared_ptr<const db2::Expr> pend_src;
+    int pend_op = -1;
 
+    bool is_view = false; // shares its buffers with a parent (row slice): results written through it stay in place
+
+    bool deferred() const { return (bool)lazy || (bool)pend_src; }
     size_t esize() const { return db2::dtype_size(dtype); }
     void *dev_ptr() const { return static_cast<char *>(dev->ptr) + dev_off * (int64_t)esize(); }
     void *host_ptr() const { return static_cast<char *>(host->ptr) + host_off * (int64_t)esize(); }
 };
 
 namespace db2 {
+
+// ---- deferred evaluation (lazy.cu) ----
+struct Operand { // a materialised device operand; holds its buffer alive
+    std::shared_ptr<DevBuf> buf;
+    int64_t off = 0, ld = 0, rows = 0, cols = 0;
+    const void *ptr(size_t es) const { return static_cast<const char *>(buf->ptr) + off * (int64_t)es; }
+    bool same(const Operand &o) const {
+        return buf.get() == o.buf.get() && off == o.off && ld == o.ld && rows == o.rows && cols == o.cols;
+    }
+};
+struct ExprStep {
+    int kind = 0, op = 0; // FusedOperandKind, FusedOp
+    bool reversed = false;
+    Operand operand;
+    double imm = 0.0;
+    bool same(const ExprStep &o) const {
+        if (kind != o.kind || op != o.op || reversed != o.reversed)
+            return false;
+        if (kind == 3)
+            return memcmp(&imm, &o.imm, sizeof(double)) == 0;
+        if (kind == 4)
+            return true;
+        return operand.same(o.operand);
+    }
+};
+struct Expr {
+    int dtype = DB2_F64;
+    int64_t rows = 0, cols = 0;
+    Operand base;
+    std::vector<ExprStep> steps;
+};
+// Each returns DB2_OK and sets *handled when the call was recorded instead of executed.
+int lazy_try_binary(db2_context *ctx, int op, db2_matrix **res, db2_matrix *lhs, db2_matrix *rhs, bool *handled);
+int lazy_try_scalar(db2_context *ctx, int op, db2_matrix **res, db2_matrix *lhs, const void *scalar, bool *handled);
+int lazy_try_unary(db2_context *ctx, int op, db2_matrix **res, db2_matrix *arg, bool *handled);
+int lazy_try_agg_row(db2_context *ctx, int op, db2_matrix **res, db2_matrix *arg, bool *handled);
+int lazy_try_agg_col(db2_context *ctx, int op, db2_matrix **res, db2_matrix *arg, bool *handled);
+int lazy_force(db2_matrix *m);          // materialises a deferred matrix (and the pending siblings it can serve)
+int lazy_flush_all(db2_context *ctx);   // produces every pending aggregation
+void lazy_forget(db2_matrix *m);        // a deferred matrix is being destroyed
+
 // makes the device placement current (allocation + async H2D when only the host copy is valid)
 int ensure_device(db2_matrix *m);
 // result allocation following the reference's "*res == nullptr means allocate" convention; checks shape/type otherwise

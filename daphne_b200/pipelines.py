@@ -112,17 +112,19 @@ def standardise_aggregate(ctx: K.Context, X: K.DenseMatrix, n_total: Optional[in
     d2.free()
     var = K.ewBinaryObjSca(B.DIV, v, float(n))
     sd = K.ewUnaryMat(U.SQRT, var)
-    with probe.section("ew_2d_kernel<SUB,row-vector> (X - mu)", 2 * X.rows * X.cols * 8):
-        xc = K.ewBinaryMat(B.SUB, X, mu)
+    xc = K.ewBinaryMat(B.SUB, X, mu)
     Z = K.ewBinaryMat(B.DIV, xc, sd)
     xc.free()
     z2 = K.ewBinaryObjSca(B.POW, Z, 2.0)
     r = K.aggRow(A.SUM, z2)
     z2.free()
-    s_local = K.aggAll(A.SUM, r)
-    s = float(s_local) if comm is None or comm.world == 1 else float(
-        comm.allreduce_numpy(np.array([s_local], dtype=np.float64))[0])
     m = K.aggRow(A.MAX, Z)
     i = K.aggRow(A.IDXMAX, Z)
     Z.free()
+    with probe.section("fused_row_kernel (Z=(X-mu)/sd; rowSums(Z^2), rowMaxs(Z), idxMax(Z))",
+                       X.rows * (X.cols * 8 + 24)):
+        r.device_ptr()  # the three row aggregations are produced by one pass over X
+    s_local = K.aggAll(A.SUM, r)
+    s = float(s_local) if comm is None or comm.world == 1 else float(
+        comm.allreduce_numpy(np.array([s_local], dtype=np.float64))[0])
     return StandardiseResult(mu, sd, r, s, m, i)
