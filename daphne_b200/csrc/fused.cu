@@ -107,36 +107,33 @@ struct RowTracker {
     int c;
     bool first_nan;
 };
-__device__ __forceinline__ void tracker_init(RowTracker &t, int op) {
+__device__ __forceinline__ void tracker_init(RowTracker &t, int kind) {
     t.c = NO_COL;
     t.first_nan = false;
-    switch (op) {
-    case DB2_AGG_PROD: t.v = 1.0; break;
-    case DB2_AGG_MIN:
-    case DB2_AGG_IDXMIN: t.v = INFINITY; break;
-    case DB2_AGG_MAX:
-    case DB2_AGG_IDXMAX: t.v = -INFINITY; break;
+    switch (kind) {
+    case FT_PROD: t.v = 1.0; break;
+    case FT_MIN: t.v = INFINITY; break;
+    case FT_MAX: t.v = -INFINITY; break;
     default: t.v = 0.0; break;
     }
 }
 template <int N>
 __device__ __forceinline__ void tracker_feed(RowTracker &t, int op, const double (&v)[N], int c0, int nv) {
     switch (op) {
-    case DB2_AGG_SUM:
-    case DB2_AGG_MEAN:
+    case FT_SUM:
+    case FT_MEAN:
 #pragma unroll
         for (int i = 0; i < N; i++)
             if (i < nv)
                 t.v = __dadd_rn(t.v, v[i]);
         break;
-    case DB2_AGG_PROD:
+    case FT_PROD:
 #pragma unroll
         for (int i = 0; i < N; i++)
             if (i < nv)
                 t.v = __dmul_rn(t.v, v[i]);
         break;
-    case DB2_AGG_MIN:
-    case DB2_AGG_IDXMIN:
+    case FT_MIN:
         if (c0 == 0 && v[0] != v[0])
             t.first_nan = true;
 #pragma unroll
@@ -146,8 +143,7 @@ __device__ __forceinline__ void tracker_feed(RowTracker &t, int op, const double
                 t.c = c0 + i;
             }
         break;
-    case DB2_AGG_MAX:
-    case DB2_AGG_IDXMAX:
+    case FT_MAX:
         if (c0 == 0 && v[0] != v[0])
             t.first_nan = true;
 #pragma unroll
@@ -197,7 +193,7 @@ __global__ void __launch_bounds__(RT)
 #pragma unroll
         for (int a = 0; a < FUSED_MAX_AGGS; a++)
             if (a < P.ntaps)
-                tracker_init(trk[a], P.taps[a].op);
+                tracker_init(trk[a], P.taps[a].kind);
 
         for (int64_t cc = 0; cc < cols; cc += CK) {
             const int cw = (cols - cc < CK) ? (int)(cols - cc) : CK;
@@ -240,7 +236,7 @@ __global__ void __launch_bounds__(RT)
 #pragma unroll
                 for (int a = 0; a < FUSED_MAX_AGGS; a++)
                     if (a < P.ntaps && P.taps[a].after_step == 0)
-                        tracker_feed(trk[a], P.taps[a].op, v, (int)c0, nv);
+                        tracker_feed(trk[a], P.taps[a].kind, v, (int)c0, nv);
                 for (int s = 0; s < P.nsteps; s++) {
                     const FusedStep &st = P.steps[s];
                     double o[GV], y[GV];
@@ -295,7 +291,7 @@ __global__ void __launch_bounds__(RT)
 #pragma unroll
                     for (int a = 0; a < FUSED_MAX_AGGS; a++)
                         if (a < P.ntaps && P.taps[a].after_step == s + 1)
-                            tracker_feed(trk[a], P.taps[a].op, v, (int)c0, nv);
+                            tracker_feed(trk[a], P.taps[a].kind, v, (int)c0, nv);
                 }
                 if (P.ew_out) {
 #pragma unroll
@@ -337,18 +333,15 @@ __global__ void __launch_bounds__(RT)
                 if (a < P.ntaps) {
                     const FusedTap &tp = P.taps[a];
                     RowTracker t = trk[a];
-                    const bool ext = tp.op == DB2_AGG_MIN || tp.op == DB2_AGG_MAX || tp.op == DB2_AGG_IDXMIN ||
-                                     tp.op == DB2_AGG_IDXMAX;
-                    if (ext && (t.first_nan || t.c == NO_COL)) {
+                    if ((tp.kind == FT_MIN || tp.kind == FT_MAX) && (t.first_nan || t.c == NO_COL)) {
                         t.v = NAN; // only reachable when the first element is NaN (or every element is)
                         t.c = 0;
                     }
-                    if (tp.op == DB2_AGG_IDXMIN || tp.op == DB2_AGG_IDXMAX)
-                        static_cast<uint64_t *>(tp.out)[row * tp.out_ld] = (uint64_t)t.c;
-                    else if (tp.op == DB2_AGG_MEAN)
-                        static_cast<double *>(tp.out)[row * tp.out_ld] = __ddiv_rn(t.v, (double)cols);
-                    else
-                        static_cast<double *>(tp.out)[row * tp.out_ld] = t.v;
+                    if (tp.out_idx)
+                        static_cast<uint64_t *>(tp.out_idx)[row] = (uint64_t)t.c;
+                    if (tp.out)
+                        static_cast<double *>(tp.out)[row] =
+                            (tp.kind == FT_MEAN) ? __ddiv_rn(t.v, (double)cols) : t.v;
                 }
             }
         }

@@ -43,11 +43,14 @@ struct FusedStep {
     double imm;       // SCALAR operand
 };
 
+// kinds of row trackers; MIN/MAX trackers can deliver the extremum (out) and its position (out_idx) together
+enum FusedTapKind : int32_t { FT_SUM = 0, FT_PROD = 1, FT_MIN = 2, FT_MAX = 3, FT_MEAN = 4 };
+
 struct FusedTap {
     int32_t after_step; // the aggregation sees the value after this many steps (0 = the base operand itself)
-    int32_t op;         // AggOpCode: SUM, PROD, MIN, MAX, IDXMIN, IDXMAX, MEAN
-    void *out;          // rows x 1 result (value type, or uint64 for IDXMIN/IDXMAX)
-    int64_t out_ld;
+    int32_t kind;       // FusedTapKind
+    void *out;          // rows x 1 values (may be null for MIN/MAX when only the position is wanted)
+    void *out_idx;      // rows x 1 uint64 positions of the extremum (MIN/MAX only, may be null)
 };
 
 struct FusedProgram {
@@ -65,6 +68,11 @@ struct FusedProgram {
 
 // host side launchers (fused.cu)
 int fused_row_pass_f64(const FusedProgram &prog, cudaStream_t st);
+// Specialised (compile-time) versions of frequent chains (fused_ct.cu).  `signature` spells the chain and its taps,
+// e.g. "SUB.R|DIV.R|SQ.S#MAX@2,SUM@3"; returns true when a specialised kernel was launched.
+bool fused_row_pass_ct(const FusedProgram &prog, const char *signature, cudaStream_t st, int *rc);
+bool fused_col_pass_ct(const FusedProgram &prog, const char *signature, int agg_op, void *res, void *scratch,
+                       size_t scratch_bytes, cudaStream_t st, int *rc);
 // column aggregation of a chain: kind = K_SUM / K_MIN / K_MAX / K_PROD of agg.cu, epilogue like db2k_agg_col
 int fused_col_pass_f64(const FusedProgram &prog, int agg_op, void *res, void *scratch, size_t scratch_bytes,
                        cudaStream_t st);

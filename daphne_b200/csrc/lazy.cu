@@ -13,6 +13,7 @@
 
 #include <algorithm>
 #include <cmath>
+#include <string>
 
 namespace db2 {
 
@@ -252,7 +253,52 @@ static void unpend(db2_context *ctx, db2_matrix *m) {
     v.erase(std::remove(v.begin(), v.end(), m), v.end());
 }
 
-// One fused pass over `longest`: materialises `ew_target` (may be null) and every pending aggregation in `group`.
+static const char *fused_op_name(int op) {
+    static const char *n[] = {"ADD", "SUB", "MUL", "DIV", "SQ", "EQ", "NEQ", "LT", "LE", "GT", "GE", "MIN", "MAX", "AND",
+                              "OR", "NEG", "ABS", "SIGN", "FLOOR", "CEIL", "ROUND", "ISNAN"};
+    return (op >= 0 && op < FO_COUNT) ? n[op] : "?";
+}
+
+// Spells a program: "SUB.R|DIV.R|SQ.S#MAX@2,SUM@3+EW" (operand kinds M/R/C/S/U, a trailing r = reversed operands).
+static std::string signature_of(const FusedProgram &P) {
+    std::string sig;
+    for (int i = 0; i < P.nsteps; i++) {
+        if (i)
+            sig += "|";
+        sig += fused_op_name(P.steps[i].op);
+        sig += ".";
+        sig += "MRCSU"[P.steps[i].kind];
+        if (P.steps[i].reversed)
+            sig += "r";
+    }
+    sig += "#";
+    static const char *tk[] = {"SUM", "PROD", "MIN", "MAX", "MEAN"};
+    for (int i = 0; i < P.ntaps; i++) {
+        if (i)
+            sig += ",";
+        sig += tk[P.taps[i].kind];
+        sig += "@" + std::to_string(P.taps[i].after_step);
+    }
+    if (P.ew_out)
+        sig += "+EW";
+    return sig;
+}
+
+static int tap_kind_of(int agg_op) {
+    switch (agg_op) {
+    case DB2_AGG_SUM: return FT_SUM;
+    case DB2_AGG_PROD: return FT_PROD;
+    case DB2_AGG_MIN:
+    case DB2_AGG_IDXMIN: return FT_MIN;
+    case DB2_AGG_MAX:
+    case DB2_AGG_IDXMAX: return FT_MAX;
+    default: return FT_MEAN;
+    }
+}
+
+// One fused pass over `longest`: materialises `ew_target` (may be null) and every pending aggregation in `group`
+// (members that do not fit the tap slots stay pending).  MIN/IDXMIN and MAX/IDXMAX of the same chain position share
+// one tracker.
 static int run_row_pass(db2_context *ctx, const Expr &longest, db2_matrix *ew_target,
                         const std::vector<db2_matrix *> &group) {
     FusedProgram P;
@@ -264,23 +310,45 @@ static int run_row_pass(db2_context *ctx, const Expr &longest, db2_matrix *ew_ta
         P.ew_out = ew_target->dev->ptr;
         P.ew_out_ld = longest.cols;
     }
-    P.ntaps = (int)group.size();
-    for (size_t i = 0; i < group.size(); i++) {
-        db2_matrix *g = group[i];
+    // canonical order: by chain position, then tracker kind
+    std::vector<db2_matrix *> sorted(group);
+    std::stable_sort(sorted.begin(), sorted.end(), [](const db2_matrix *a, const db2_matrix *b) {
+        const size_t pa = a->pend_src->steps.size(), pb = b->pend_src->steps.size();
+        if (pa != pb)
+            return pa < pb;
+        return tap_kind_of(a->pend_op) < tap_kind_of(b->pend_op);
+    });
+    std::vector<db2_matrix *> served;
+    for (db2_matrix *g : sorted) {
+        const int after = (int)g->pend_src->steps.size(), kind = tap_kind_of(g->pend_op);
+        const bool idx = g->pend_op == DB2_AGG_IDXMIN || g->pend_op == DB2_AGG_IDXMAX;
+        int slot = -1;
+        for (int t = 0; t < P.ntaps; t++)
+            if (P.taps[t].after_step == after && P.taps[t].kind == kind && (idx ? !P.taps[t].out_idx : !P.taps[t].out))
+                slot = t;
+        if (slot < 0) {
+            if (P.ntaps >= FUSED_MAX_AGGS)
+                continue; // stays pending
+            slot = P.ntaps++;
+            P.taps[slot].after_step = after;
+            P.taps[slot].kind = kind;
+        }
         g->dev = make_devbuf(ctx, (size_t)g->rows * 8);
         g->dev_off = 0;
         g->dev_ld = 1;
-        P.taps[i].after_step = (int)g->pend_src->steps.size();
-        P.taps[i].op = g->pend_op;
-        P.taps[i].out = g->dev->ptr;
-        P.taps[i].out_ld = 1;
+        (idx ? P.taps[slot].out_idx : P.taps[slot].out) = g->dev->ptr;
+        served.push_back(g);
     }
-    DB2_TRY(fused_row_pass_f64(P, ctx->stream));
+    int rc = DB2_OK;
+    const std::string sig = signature_of(P);
+    if (!fused_row_pass_ct(P, sig.c_str(), ctx->stream, &rc))
+        rc = fused_row_pass_f64(P, ctx->stream);
+    DB2_TRY(rc);
     if (ew_target) {
         ew_target->dev_valid = true;
         ew_target->lazy.reset();
     }
-    for (db2_matrix *g : group) {
+    for (db2_matrix *g : served) {
         g->dev_valid = true;
         g->pend_src.reset();
         g->pend_op = -1;
@@ -316,6 +384,8 @@ int lazy_force(db2_matrix *m) {
             }
         }
         rc = run_row_pass(ctx, *longest, nullptr, group);
+        if (rc == DB2_OK && m->pend_src) // more distinct trackers than one pass holds: serve m on its own
+            rc = run_row_pass(ctx, *std::shared_ptr<const Expr>(m->pend_src), nullptr, {m});
     }
     {
         std::lock_guard<std::mutex> lock(ctx->mu);
@@ -350,7 +420,11 @@ int lazy_try_agg_col(db2_context *ctx, int op, db2_matrix **res, db2_matrix *arg
     build_program(*e, e->steps.size(), &P);
     void *scratch = nullptr;
     DB2_TRY(ctx_scratch(ctx, fused_col_scratch_bytes(arg->cols), &scratch));
-    DB2_TRY(fused_col_pass_f64(P, op, (*res)->dev_ptr(), scratch, ctx->scratch_bytes, ctx->stream));
+    int rc = DB2_OK;
+    const std::string sig = signature_of(P);
+    if (!fused_col_pass_ct(P, sig.c_str(), op, (*res)->dev_ptr(), scratch, ctx->scratch_bytes, ctx->stream, &rc))
+        rc = fused_col_pass_f64(P, op, (*res)->dev_ptr(), scratch, ctx->scratch_bytes, ctx->stream);
+    DB2_TRY(rc);
     *handled = true;
     return DB2_OK;
 }

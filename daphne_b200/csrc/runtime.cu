@@ -12,14 +12,16 @@ DevBuf::~DevBuf() {
     }
 }
 
+static void release_cached(db2_context *ctx);
+
 void ctx_release(db2_context *ctx) {
     if (ctx->refs.fetch_sub(1) != 1)
         return;
     bind_device(ctx);
     cudaStreamSynchronize(ctx->stream);
     if (ctx->scratch)
-        cudaFreeAsync(ctx->scratch, ctx->stream);
-    cudaStreamSynchronize(ctx->stream);
+        ctx_free(ctx, ctx->scratch, ctx->scratch_bytes);
+    release_cached(ctx);
     cudaFree(ctx->dev_status);
     cudaFreeHost(ctx->host_status);
     cudaStreamDestroy(ctx->stream);
@@ -30,27 +32,56 @@ HostBuf::~HostBuf() {
         cudaFreeHost(ptr);
 }
 
+static size_t round_block(size_t bytes) {
+    if (bytes <= (1u << 20)) {
+        size_t p = 512;
+        while (p < bytes)
+            p <<= 1;
+        return p;
+    }
+    const size_t g = 2u << 20;
+    return (bytes + g - 1) / g * g;
+}
+
+static void release_cached(db2_context *ctx) {
+    for (auto &kv : ctx->free_blocks) {
+        cudaFree(kv.second);
+        ctx->block_size.erase(kv.second);
+    }
+    ctx->free_blocks.clear();
+    ctx->cached_bytes = 0;
+}
+
 int ctx_alloc(db2_context *ctx, size_t bytes, void **out) {
     *out = nullptr;
     if (bytes == 0)
         return DB2_OK;
     bind_device(ctx);
-    cudaError_t e = cudaMallocFromPoolAsync(out, bytes, ctx->pool, ctx->stream);
-    if (e == cudaErrorMemoryAllocation) {
-        cudaGetLastError();
-        // give cached blocks back to the driver once and retry
-        cudaStreamSynchronize(ctx->stream);
-        cudaMemPoolTrimTo(ctx->pool, 0);
-        e = cudaMallocFromPoolAsync(out, bytes, ctx->pool, ctx->stream);
+    const size_t want = round_block(bytes);
+    std::lock_guard<std::mutex> lock(ctx->mu);
+    auto it = ctx->free_blocks.lower_bound(want);
+    if (it != ctx->free_blocks.end() && it->first <= want + want / 4) {
+        *out = it->second;
+        ctx->cached_bytes -= it->first;
+        ctx->free_blocks.erase(it);
+    } else {
+        cudaError_t e = cudaMalloc(out, want);
         if (e == cudaErrorMemoryAllocation) {
             cudaGetLastError();
-            return set_error(DB2_ENOMEM, "out of device memory allocating %zu bytes on device %d", bytes, ctx->device);
+            cudaStreamSynchronize(ctx->stream);
+            release_cached(ctx); // hand the cached blocks back to the driver once and retry
+            e = cudaMalloc(out, want);
+            if (e == cudaErrorMemoryAllocation) {
+                cudaGetLastError();
+                return set_error(DB2_ENOMEM, "out of device memory allocating %zu bytes on device %d", want,
+                                 ctx->device);
+            }
         }
+        DB2_CUDA(e);
+        ctx->block_size[*out] = want;
+        ctx->stats.allocs++;
+        ctx->stats.alloc_bytes += want;
     }
-    DB2_CUDA(e);
-    std::lock_guard<std::mutex> lock(ctx->mu);
-    ctx->stats.allocs++;
-    ctx->stats.alloc_bytes += bytes;
     ctx->stats.live_bytes += bytes;
     if (ctx->stats.live_bytes > ctx->stats.peak_bytes)
         ctx->stats.peak_bytes = ctx->stats.live_bytes;
@@ -60,14 +91,14 @@ int ctx_alloc(db2_context *ctx, size_t bytes, void **out) {
 int ctx_free(db2_context *ctx, void *ptr, size_t bytes) {
     if (!ptr)
         return DB2_OK;
-    bind_device(ctx);
-    cudaError_t e = cudaFreeAsync(ptr, ctx->stream);
-    {
-        std::lock_guard<std::mutex> lock(ctx->mu);
-        ctx->stats.frees++;
-        ctx->stats.live_bytes -= bytes;
-    }
-    DB2_CUDA(e);
+    std::lock_guard<std::mutex> lock(ctx->mu);
+    ctx->stats.frees++;
+    ctx->stats.live_bytes -= bytes;
+    auto it = ctx->block_size.find(ptr);
+    if (it == ctx->block_size.end())
+        return set_error(DB2_EINVAL, "freeing a block this context did not allocate");
+    ctx->free_blocks.emplace(it->second, ptr);
+    ctx->cached_bytes += it->second;
     return DB2_OK;
 }
 
@@ -177,9 +208,6 @@ int db2_context_create(int device, db2_context **out) {
     const char *eager = getenv("DB2_EAGER");
     ctx->eager = eager && eager[0] == '1';
     DB2_CUDA(cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking));
-    DB2_CUDA(cudaDeviceGetDefaultMemPool(&ctx->pool, device));
-    uint64_t threshold = UINT64_MAX; // keep freed blocks cached in the pool instead of returning them to the driver
-    DB2_CUDA(cudaMemPoolSetAttribute(ctx->pool, cudaMemPoolAttrReleaseThreshold, &threshold));
     DB2_CUDA(cudaMalloc(&ctx->dev_status, 256));
     DB2_CUDA(cudaMemset(ctx->dev_status, 0, 256));
     DB2_CUDA(cudaMallocHost(&ctx->host_status, 256));

@@ -3,7 +3,9 @@
 
 #include "common.cuh"
 
+#include <map>
 #include <memory>
+#include <unordered_map>
 #include <mutex>
 #include <stdexcept>
 #include <string>
@@ -20,7 +22,11 @@ struct db2_context {
     std::vector<db2_matrix *> pending;
     bool eager = false; // DB2_EAGER=1: run every operator call immediately (no fusion)
     cudaStream_t stream = nullptr;
-    cudaMemPool_t pool = nullptr;
+    // caching device allocator: freed blocks are kept by size and handed out again without calling the driver; all
+    // work of a context is ordered on its one stream, so a freed block may be reused immediately
+    std::multimap<size_t, void *> free_blocks;
+    std::unordered_map<void *, size_t> block_size;
+    size_t cached_bytes = 0;
     // reusable scratch for two-stage reductions (grown on demand, stream-ordered reuse)
     void *scratch = nullptr;
     size_t scratch_bytes = 0;
