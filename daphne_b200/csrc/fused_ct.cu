@@ -463,6 +463,7 @@ struct ColEntry {
 static const ColEntry COL_TABLE[] = {
     {"SUB.R|SQ.S#", &launch_col_sum<Chain<SubR, SqS>>}, // column sums of squared deviations (variance)
     {"SQ.S#", &launch_col_sum<Chain<SqS>>},
+    {"MUL.C#", &launch_col_sum<Chain<S<FO_MUL, FK_COLVEC>>>}, // t(X) y as column sums of X .* y
     {"#", &launch_col_sum<Chain<>>},
 };
 

@@ -204,3 +204,83 @@ def aggAll(op, arg: DenseMatrix, ctx: Optional[Context] = None):
     out = np.zeros(1, dtype=arg.dtype)
     check(lib.db2_aggAll(ctx.handle, int(op), C.c_void_p(out.ctypes.data), arg.handle))
     return out[0]
+
+
+def matMul(lhs: DenseMatrix, rhs: DenseMatrix, transa: bool = False, transb: bool = False,
+           ctx: Optional[Context] = None) -> DenseMatrix:
+    """MatMul.h:44-47: res = op(lhs) @ op(rhs)."""
+    ctx = ctx or lhs.ctx
+    h = C.c_void_p()
+    check(lib.db2_matMul(ctx.handle, C.byref(h), lhs.handle, rhs.handle, int(transa), int(transb)))
+    return _res(ctx, h)
+
+
+def syrk(arg: DenseMatrix, transLeft: bool = True, ctx: Optional[Context] = None) -> DenseMatrix:
+    """Syrk.h:40-43: t(arg) @ arg if transLeft else arg @ t(arg); full symmetric result."""
+    ctx = ctx or arg.ctx
+    h = C.c_void_p()
+    check(lib.db2_syrk(ctx.handle, C.byref(h), arg.handle, int(transLeft)))
+    return _res(ctx, h)
+
+
+def gemv(mat: DenseMatrix, vec: DenseMatrix, ctx: Optional[Context] = None) -> DenseMatrix:
+    """Gemv.h:40-43: t(mat) @ vec (cols x 1)."""
+    ctx = ctx or mat.ctx
+    h = C.c_void_p()
+    check(lib.db2_gemv(ctx.handle, C.byref(h), mat.handle, vec.handle))
+    return _res(ctx, h)
+
+
+def solve(lhs: DenseMatrix, rhs: DenseMatrix, ctx: Optional[Context] = None) -> DenseMatrix:
+    """Solve.h:40-43: x with lhs @ x = rhs (one right-hand side)."""
+    ctx = ctx or lhs.ctx
+    h = C.c_void_p()
+    check(lib.db2_solve(ctx.handle, C.byref(h), lhs.handle, rhs.handle))
+    return _res(ctx, h)
+
+
+def transpose(arg: DenseMatrix, ctx: Optional[Context] = None) -> DenseMatrix:
+    ctx = ctx or arg.ctx
+    h = C.c_void_p()
+    check(lib.db2_transpose(ctx.handle, C.byref(h), arg.handle))
+    return _res(ctx, h)
+
+
+def fill(ctx: Context, value, rows: int, cols: int, dtype=np.float64) -> DenseMatrix:
+    v = np.array([value], dtype=dtype)
+    h = C.c_void_p()
+    check(lib.db2_fill(ctx.handle, C.byref(h), _NP2DT[np.dtype(dtype)], C.c_void_p(v.ctypes.data), rows, cols))
+    return _res(ctx, h)
+
+
+def seq(ctx: Context, start, end, inc, dtype=np.float64) -> DenseMatrix:
+    """Seq.h:36-38."""
+    a = np.array([start, end, inc], dtype=dtype)
+    h = C.c_void_p()
+    base = a.ctypes.data
+    check(lib.db2_seq(ctx.handle, C.byref(h), _NP2DT[np.dtype(dtype)], C.c_void_p(base), C.c_void_p(base + 8),
+                      C.c_void_p(base + 16)))
+    return _res(ctx, h)
+
+
+def diagMatrix(arg: DenseMatrix, ctx: Optional[Context] = None) -> DenseMatrix:
+    ctx = ctx or arg.ctx
+    h = C.c_void_p()
+    check(lib.db2_diagMatrix(ctx.handle, C.byref(h), arg.handle))
+    return _res(ctx, h)
+
+
+def ctable(lhs: DenseMatrix, rhs: DenseMatrix, weight: float = 1.0, resNumRows: int = -1, resNumCols: int = -1,
+           ctx: Optional[Context] = None) -> DenseMatrix:
+    """CTable.h:44-48: res[lhs[i], rhs[i]] += weight."""
+    ctx = ctx or lhs.ctx
+    h = C.c_void_p()
+    check(lib.db2_ctable(ctx.handle, C.byref(h), lhs.handle, rhs.handle, float(weight), resNumRows, resNumCols))
+    return _res(ctx, h)
+
+
+def castObj(arg: DenseMatrix, dtype, ctx: Optional[Context] = None) -> DenseMatrix:
+    ctx = ctx or arg.ctx
+    h = C.c_void_p()
+    check(lib.db2_castObj(ctx.handle, C.byref(h), arg.handle, _NP2DT[np.dtype(dtype)]))
+    return _res(ctx, h)

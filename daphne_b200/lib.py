@@ -69,6 +69,17 @@ _SIGS = {
     "db2k_agg_col_static": (i32, [i32, i32, vp, i64, i64, i64, vp, vp]),
     "db2k_agg_all_scratch_bytes": (sz, [i32, i32, i64, i64]),
     "db2k_agg_all": (i32, [i32, i32, vp, i64, i64, i64, vp, vp, sz, vp]),
+    "db2k_matmul_scratch_bytes": (sz, [i32, i64, i64, i64]),
+    "db2k_matmul": (i32, [i32, vp, i64, i64, i64, vp, i64, i64, i64, i32, i32, vp, i64, vp, sz, vp]),
+    "db2k_syrk_scratch_bytes": (sz, [i32, i64, i64, i32]),
+    "db2k_syrk": (i32, [i32, vp, i64, i64, i64, i32, vp, i64, vp, sz, vp]),
+    "db2k_transpose": (i32, [i32, vp, i64, i64, i64, vp, i64, vp]),
+    "db2k_fill": (i32, [i32, vp, i64, i64, i64, vp, vp]),
+    "db2k_seq": (i32, [i32, vp, i64, vp, vp, vp]),
+    "db2k_diag_matrix": (i32, [i32, vp, i64, i64, vp, i64, vp]),
+    "db2k_max_i64": (i32, [vp, i64, i64, vp, vp]),
+    "db2k_ctable": (i32, [vp, i64, vp, i64, i64, C.c_double, vp, i64, i64, i64, i32, vp]),
+    "db2k_solve": (i32, [i32, vp, i64, vp, vp, vp]),
     # runtime
     "db2_context_create": (i32, [i32, _P(vp)]),
     "db2_context_destroy": (i32, [vp]),
@@ -91,6 +102,16 @@ _SIGS = {
     "db2_aggRow": (i32, [vp, i32, _P(vp), vp]),
     "db2_aggCol": (i32, [vp, i32, _P(vp), vp]),
     "db2_aggAll": (i32, [vp, i32, vp, vp]),
+    "db2_matMul": (i32, [vp, _P(vp), vp, vp, i32, i32]),
+    "db2_syrk": (i32, [vp, _P(vp), vp, i32]),
+    "db2_gemv": (i32, [vp, _P(vp), vp, vp]),
+    "db2_solve": (i32, [vp, _P(vp), vp, vp]),
+    "db2_transpose": (i32, [vp, _P(vp), vp]),
+    "db2_fill": (i32, [vp, _P(vp), i32, vp, i64, i64]),
+    "db2_seq": (i32, [vp, _P(vp), i32, vp, vp, vp]),
+    "db2_diagMatrix": (i32, [vp, _P(vp), vp]),
+    "db2_ctable": (i32, [vp, _P(vp), vp, vp, C.c_double, i64, i64]),
+    "db2_castObj": (i32, [vp, _P(vp), vp, i32]),
 }
 
 

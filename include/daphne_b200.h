@@ -161,6 +161,45 @@ size_t db2k_agg_all_scratch_bytes(int dtype, int op, int64_t rows, int64_t cols)
 int db2k_agg_all(int dtype, int op, const void *arg, int64_t rows, int64_t cols, int64_t ld, void *res,
                  void *scratch, size_t scratch_bytes, void *stream);
 
+/* res (m x n) = op(lhs) op(rhs), op = transpose iff the flag is set; double only.  FP64 tensor-core (DMMA) kernel;
+ * contractions over a long row range (t(A) B with tall operands) are split over the grid and reduced in a fixed
+ * order through `scratch` (db2k_matmul_scratch_bytes(dtype, m, n, k) bytes, m/n/k = the product's dimensions).
+ * Replaces MatMul<Dense,Dense,Dense> (src/runtime/local/kernels/MatMul.cpp:248-290: cblas_ddot / dgemv / dgemm;
+ * CUDA twin kernels/CUDA/MatMul.cpp:45-91: cuBLAS gemm). */
+size_t db2k_matmul_scratch_bytes(int dtype, int64_t m, int64_t n, int64_t k);
+int db2k_matmul(int dtype, const void *lhs, int64_t lhs_rows, int64_t lhs_cols, int64_t lhs_ld, const void *rhs,
+                int64_t rhs_rows, int64_t rhs_cols, int64_t rhs_ld, int transa, int transb, void *res,
+                int64_t res_ld, void *scratch, size_t scratch_bytes, void *stream);
+
+/* res (n x n, full symmetric) = t(arg) arg if trans_left else arg t(arg).  Only the tiles on and above the diagonal
+ * are computed, the rest is mirrored.  Replaces Syrk<Dense,Dense> (src/runtime/local/kernels/Syrk.h:51-71:
+ * cblas_dsyrk + mirror loop; CUDA twin kernels/CUDA/Syrk.cu:54-87). */
+size_t db2k_syrk_scratch_bytes(int dtype, int64_t rows, int64_t cols, int trans_left);
+int db2k_syrk(int dtype, const void *arg, int64_t rows, int64_t cols, int64_t ld, int trans_left, void *res,
+              int64_t res_ld, void *scratch, size_t scratch_bytes, void *stream);
+
+/* Out-of-place transpose (any 4- or 8-byte value type).  Replaces Transpose<Dense,Dense>
+ * (src/runtime/local/kernels/Transpose.h:51-76; CUDA twin kernels/CUDA/Transpose.cpp:70-90: cuBLAS geam). */
+int db2k_transpose(int dtype, const void *arg, int64_t rows, int64_t cols, int64_t ld, void *res, int64_t res_ld,
+                   void *stream);
+/* Constant fill; `value` is a host pointer to one element.  Replaces Fill (kernels/Fill.h; CUDA/Fill.cu:29-42). */
+int db2k_fill(int dtype, void *res, int64_t rows, int64_t cols, int64_t ld, const void *value, void *stream);
+/* res[i] = start + i * inc for i < n (Seq, src/runtime/local/kernels/Seq.h:49-99; n is computed by the caller). */
+int db2k_seq(int dtype, void *res, int64_t n, const void *start, const void *inc, void *stream);
+/* n x n matrix with vec on its diagonal (DiagMatrix<Dense,Dense>, src/runtime/local/kernels/DiagMatrix.h:55-78). */
+int db2k_diag_matrix(int dtype, const void *vec, int64_t vec_ld, int64_t n, void *res, int64_t res_ld, void *stream);
+/* maximum of an int64 vector into a device int64 (used to size ctable results like CTable.h:79-84 does) */
+int db2k_max_i64(const void *vec, int64_t ld, int64_t n, void *dev_out, void *stream);
+/* Contingency table res[lhs[i], rhs[i]] += weight over int64 coordinate vectors (f64 result, overwritten).
+ * Coordinates outside res are ignored.  lhs_is_row_index != 0 promises lhs = 0,1,..,n-1 (the one-hot use).
+ * Replaces CTable<Dense<double>,Dense<int64>,Dense<int64>,double> (src/runtime/local/kernels/CTable.h:55-106). */
+int db2k_ctable(const void *lhs, int64_t lhs_ld, const void *rhs, int64_t rhs_ld, int64_t n, double weight, void *res,
+                int64_t res_rows, int64_t res_cols, int64_t res_ld, int lhs_is_row_index, void *stream);
+/* Solves A x = b by LU with partial pivoting.  a_work: n x n row-major COPY of A (destroyed); x_inout: b on entry,
+ * x on exit; *dev_status (device int32) = 0, or k+1 if U(k,k) is exactly zero.  Replaces Solve<Dense,Dense,Dense>
+ * (src/runtime/local/kernels/Solve.h:86-116: LAPACKE_dgesv; CUDA twin kernels/CUDA/Solve.cpp:75-151). */
+int db2k_solve(int dtype, void *a_work, int64_t n, void *x_inout, int32_t *dev_status, void *stream);
+
 /* ------------------------------------------------------------------------- */
 /* db2_*: runtime -- context, matrix handles with residency, operator calls   */
 /* ------------------------------------------------------------------------- */
@@ -219,6 +258,21 @@ int db2_aggRow(db2_context *ctx, int op, db2_matrix **res, db2_matrix *arg);
 int db2_aggCol(db2_context *ctx, int op, db2_matrix **res, db2_matrix *arg);
 /* res_host: host pointer to one value of the matrix's value type; synchronises */
 int db2_aggAll(db2_context *ctx, int op, void *res_host, db2_matrix *arg);
+int db2_matMul(db2_context *ctx, db2_matrix **res, db2_matrix *lhs, db2_matrix *rhs, int transa, int transb);
+int db2_syrk(db2_context *ctx, db2_matrix **res, db2_matrix *arg, int trans_left);
+/* res (cols x 1) = t(mat) vec (Gemv<Dense,Dense,Dense>, src/runtime/local/kernels/Gemv.h:51-63) */
+int db2_gemv(db2_context *ctx, db2_matrix **res, db2_matrix *mat, db2_matrix *vec);
+int db2_solve(db2_context *ctx, db2_matrix **res, db2_matrix *lhs, db2_matrix *rhs);
+/* vectors are reshaped without moving data, like the reference (Transpose.h:57-58) */
+int db2_transpose(db2_context *ctx, db2_matrix **res, db2_matrix *arg);
+int db2_fill(db2_context *ctx, db2_matrix **res, int dtype, const void *value, int64_t rows, int64_t cols);
+int db2_seq(db2_context *ctx, db2_matrix **res, int dtype, const void *start, const void *end, const void *inc);
+int db2_diagMatrix(db2_context *ctx, db2_matrix **res, db2_matrix *arg);
+/* res_rows / res_cols < 0: derived from the largest coordinate (synchronises) */
+int db2_ctable(db2_context *ctx, db2_matrix **res, db2_matrix *lhs, db2_matrix *rhs, double weight,
+               int64_t res_rows, int64_t res_cols);
+/* value-type cast between f64 / i64 / u64 (CastObj, used for idxMin results feeding ctable) */
+int db2_castObj(db2_context *ctx, db2_matrix **res, db2_matrix *arg, int dtype);
 
 #ifdef __cplusplus
 }

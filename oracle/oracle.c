@@ -345,3 +345,163 @@ static int agg_bin_op(int op) {
 DEF_AGG(f64, double)
 DEF_AGG(f32, float)
 DEF_AGG(i64, int64_t)
+
+/* ------------------------------------------------------------------------------------------------------------- */
+/* contractions and helpers                                                                                       */
+/* ------------------------------------------------------------------------------------------------------------- */
+/* MatMul<Dense,Dense,Dense> (MatMul.cpp:248-290).  The reference hands the arithmetic to OpenBLAS (cblas_ddot /
+ * cblas_dgemv / cblas_dgemm, a third-party dependency pinned to 0.3.23 in software-package-versions.txt:27 and not
+ * part of the reference tree); BLAS fixes no summation order, so this restatement is the textbook triple loop and
+ * parity for the contractions is a tolerance statement (relative to the largest entry of the result), pinned by the
+ * exact small integer cases of MatMulTest.cpp / SyrkTest.cpp. */
+int orc_matmul_f64(const double *a, int64_t ar, int64_t ac, int64_t lda, const double *b, int64_t br, int64_t bc,
+                   int64_t ldb, int transa, int transb, double *res, int64_t ldc) {
+    const int64_t m = transa ? ac : ar, k = transa ? ar : ac, k2 = transb ? bc : br, n = transb ? br : bc;
+    if (k != k2)
+        return 1;
+    for (int64_t i = 0; i < m; i++)
+        for (int64_t j = 0; j < n; j++) {
+            double s = 0.0;
+            for (int64_t l = 0; l < k; l++) {
+                const double x = transa ? a[l * lda + i] : a[i * lda + l];
+                const double y = transb ? b[j * ldb + l] : b[l * ldb + j];
+                s = s + x * y;
+            }
+            res[i * ldc + j] = s;
+        }
+    return 0;
+}
+/* Syrk<Dense,Dense> (Syrk.h:51-71): cblas_dsyrk on the upper triangle, then the mirror loop (:65-69) */
+int orc_syrk_f64(const double *arg, int64_t rows, int64_t cols, int64_t ld, int trans_left, double *res) {
+    const int64_t n = trans_left ? cols : rows, k = trans_left ? rows : cols;
+    for (int64_t i = 0; i < n; i++)
+        for (int64_t j = i; j < n; j++) {
+            double s = 0.0;
+            for (int64_t l = 0; l < k; l++) {
+                const double x = trans_left ? arg[l * ld + i] : arg[i * ld + l];
+                const double y = trans_left ? arg[l * ld + j] : arg[j * ld + l];
+                s = s + x * y;
+            }
+            res[i * n + j] = s;
+        }
+    for (int64_t r = 0; r < n; r++)
+        for (int64_t c = r + 1; c < n; c++)
+            res[c * n + r] = res[r * n + c];
+    return 0;
+}
+/* Gemv<Dense,Dense,Dense> (Gemv.h:51-63): res = t(mat) vec */
+int orc_gemv_f64(const double *mat, int64_t rows, int64_t cols, int64_t ld, const double *vec, int64_t vec_ld,
+                 double *res) {
+    for (int64_t c = 0; c < cols; c++)
+        res[c] = 0.0;
+    for (int64_t r = 0; r < rows; r++)
+        for (int64_t c = 0; c < cols; c++)
+            res[c] = res[c] + mat[r * ld + c] * vec[r * vec_ld];
+    return 0;
+}
+/* Solve<Dense,Dense,Dense> (Solve.h:86-116): LAPACKE_dgesv = LU with partial pivoting (first largest |a_ik| as
+ * pivot, like idamax) followed by forward and back substitution.  Returns 1 when a pivot is exactly zero (the
+ * reference throws "A factor Ui is exactly singular"). */
+int orc_solve_f64(const double *a, int64_t n, const double *b, double *x) {
+    double *w = (double *)malloc(sizeof(double) * (size_t)(n * n ? n * n : 1));
+    memcpy(w, a, sizeof(double) * (size_t)(n * n));
+    memcpy(x, b, sizeof(double) * (size_t)n);
+    for (int64_t k = 0; k < n; k++) {
+        int64_t piv = k;
+        double best = fabs(w[k * n + k]);
+        for (int64_t i = k + 1; i < n; i++)
+            if (fabs(w[i * n + k]) > best) {
+                best = fabs(w[i * n + k]);
+                piv = i;
+            }
+        if (best == 0.0) {
+            free(w);
+            return 1;
+        }
+        if (piv != k) {
+            for (int64_t c = 0; c < n; c++) {
+                double t = w[k * n + c];
+                w[k * n + c] = w[piv * n + c];
+                w[piv * n + c] = t;
+            }
+            double t = x[k];
+            x[k] = x[piv];
+            x[piv] = t;
+        }
+        for (int64_t i = k + 1; i < n; i++) {
+            const double l = w[i * n + k] / w[k * n + k];
+            w[i * n + k] = l;
+            for (int64_t j = k + 1; j < n; j++)
+                w[i * n + j] = w[i * n + j] - l * w[k * n + j];
+            x[i] = x[i] - l * x[k];
+        }
+    }
+    for (int64_t k = n - 1; k >= 0; k--) {
+        x[k] = x[k] / w[k * n + k];
+        for (int64_t i = 0; i < k; i++)
+            x[i] = x[i] - w[i * n + k] * x[k];
+    }
+    free(w);
+    return 0;
+}
+/* Transpose<Dense,Dense> (Transpose.h:51-76) */
+int orc_transpose_f64(const double *arg, int64_t rows, int64_t cols, int64_t ld, double *res) {
+    for (int64_t r = 0; r < rows; r++)
+        for (int64_t c = 0; c < cols; c++)
+            res[c * rows + r] = arg[r * ld + c];
+    return 0;
+}
+/* CTable<Dense<double>,Dense<int64>,Dense<int64>,double> (CTable.h:55-106).  res_rows / res_cols < 0: derived from the
+ * largest coordinate; res must then be sized by the caller after a first call with res == NULL. */
+int orc_ctable_f64(const int64_t *lhs, const int64_t *rhs, int64_t n, double weight, int64_t res_rows,
+                   int64_t res_cols, double *res, int64_t *out_rows, int64_t *out_cols) {
+    const int rows_from_lhs = res_rows < 0, cols_from_rhs = res_cols < 0;
+    if (rows_from_lhs) {
+        int64_t m = lhs[0];
+        for (int64_t i = 1; i < n; i++)
+            if (lhs[i] > m) m = lhs[i];
+        res_rows = m + 1;
+    }
+    if (cols_from_rhs) {
+        int64_t m = rhs[0];
+        for (int64_t i = 1; i < n; i++)
+            if (rhs[i] > m) m = rhs[i];
+        res_cols = m + 1;
+    }
+    *out_rows = res_rows;
+    *out_cols = res_cols;
+    if (!res)
+        return 0;
+    memset(res, 0, sizeof(double) * (size_t)(res_rows * res_cols));
+    for (int64_t i = 0; i < n; i++) {
+        const int64_t r = lhs[i], c = rhs[i];
+        if ((rows_from_lhs && cols_from_rhs) || (r < res_rows && c < res_cols))
+            res[r * res_cols + c] += weight;
+    }
+    return 0;
+}
+/* Seq<Dense<double>> (Seq.h:49-99): repeated addition of inc, then the end-point trim */
+int orc_seq_f64(double start, double end, double inc, double *res, int64_t cap, int64_t *n_out) {
+    if (inc != inc || start != start || end != end || inc == 0)
+        return 1;
+    if ((start < end && inc < 0) || (start > end && inc > 0)) {
+        *n_out = 0;
+        return 0;
+    }
+    const int64_t expected = (int64_t)ceil(fabs(end - start) / fabs(inc)) + 1;
+    double acc = start, last = start;
+    for (int64_t i = 0; i < expected; i++) {
+        if (res && i < cap)
+            res[i] = acc;
+        last = acc;
+        acc += inc;
+    }
+    int64_t n = expected;
+    const double eps = 1.0e-13;
+    if ((end < start) && end - last > eps)
+        n--;
+    else if ((end > start) && last - end > eps)
+        n--;
+    *n_out = n;
+    return 0;
+}

@@ -112,3 +112,105 @@ def aggAll(op, arg):
     f.argtypes = [C.c_int, C.c_void_p, i64, i64, i64, C.c_void_p]
     _chk(f(int(op), _p(arg), arg.shape[0], arg.shape[1], _ld(arg), _p(res)))
     return res[0]
+
+
+def _la_lib(prefix):
+    return _lib, prefix
+
+
+def _matmul(lib, prefix, lhs, rhs, transa=False, transb=False):
+    lhs, rhs = _mat(np.asarray(lhs, dtype=np.float64)), _mat(np.asarray(rhs, dtype=np.float64))
+    m = lhs.shape[1] if transa else lhs.shape[0]
+    n = rhs.shape[0] if transb else rhs.shape[1]
+    res = np.empty((m, n))
+    f = getattr(lib, f"{prefix}_matmul_f64")
+    if prefix == "orc":
+        f.argtypes = [C.c_void_p, i64, i64, i64, C.c_void_p, i64, i64, i64, C.c_int, C.c_int, C.c_void_p, i64]
+        _chk(f(_p(lhs), lhs.shape[0], lhs.shape[1], _ld(lhs), _p(rhs), rhs.shape[0], rhs.shape[1], _ld(rhs),
+               int(transa), int(transb), _p(res), max(n, 1)))
+    else:
+        f.argtypes = [C.c_void_p, i64, i64, i64, C.c_void_p, i64, i64, i64, C.c_int, C.c_int, C.c_void_p]
+        _chk(f(_p(lhs), lhs.shape[0], lhs.shape[1], _ld(lhs), _p(rhs), rhs.shape[0], rhs.shape[1], _ld(rhs),
+               int(transa), int(transb), _p(res)))
+    return res
+
+
+def matMul(lhs, rhs, transa=False, transb=False):
+    return _matmul(_lib, "orc", lhs, rhs, transa, transb)
+
+
+def _syrk(lib, prefix, arg, transLeft=True):
+    arg = _mat(np.asarray(arg, dtype=np.float64))
+    n = arg.shape[1] if transLeft else arg.shape[0]
+    res = np.empty((n, n))
+    f = getattr(lib, f"{prefix}_syrk_f64")
+    f.argtypes = [C.c_void_p, i64, i64, i64, C.c_int, C.c_void_p]
+    _chk(f(_p(arg), arg.shape[0], arg.shape[1], _ld(arg), int(transLeft), _p(res)))
+    return res
+
+
+def syrk(arg, transLeft=True):
+    return _syrk(_lib, "orc", arg, transLeft)
+
+
+def gemv(mat, vec):
+    mat = _mat(np.asarray(mat, dtype=np.float64))
+    vec = np.ascontiguousarray(np.asarray(vec, dtype=np.float64).reshape(-1, 1))
+    res = np.empty((mat.shape[1], 1))
+    f = _lib.orc_gemv_f64
+    f.argtypes = [C.c_void_p, i64, i64, i64, C.c_void_p, i64, C.c_void_p]
+    _chk(f(_p(mat), mat.shape[0], mat.shape[1], _ld(mat), _p(vec), 1, _p(res)))
+    return res
+
+
+def _solve(lib, prefix, a, b):
+    a = np.ascontiguousarray(np.asarray(a, dtype=np.float64))
+    b = np.ascontiguousarray(np.asarray(b, dtype=np.float64).reshape(-1, 1))
+    x = np.empty((a.shape[0], 1))
+    f = getattr(lib, f"{prefix}_solve_f64")
+    f.argtypes = [C.c_void_p, i64, C.c_void_p, C.c_void_p]
+    _chk(f(_p(a), a.shape[0], _p(b), _p(x)))
+    return x
+
+
+def solve(a, b):
+    return _solve(_lib, "orc", a, b)
+
+
+def transpose(arg):
+    arg = _mat(np.asarray(arg, dtype=np.float64))
+    res = np.empty((arg.shape[1], arg.shape[0]))
+    f = _lib.orc_transpose_f64
+    f.argtypes = [C.c_void_p, i64, i64, i64, C.c_void_p]
+    _chk(f(_p(arg), arg.shape[0], arg.shape[1], _ld(arg), _p(res)))
+    return res
+
+
+def _ctable(lib, prefix, lhs, rhs, weight=1.0, resNumRows=-1, resNumCols=-1):
+    lhs = np.ascontiguousarray(np.asarray(lhs, dtype=np.int64).reshape(-1))
+    rhs = np.ascontiguousarray(np.asarray(rhs, dtype=np.int64).reshape(-1))
+    f = getattr(lib, f"{prefix}_ctable_f64")
+    f.argtypes = [C.c_void_p, C.c_void_p, i64, C.c_double, i64, i64, C.c_void_p, C.c_void_p, C.c_void_p]
+    r, c = C.c_int64(), C.c_int64()
+    _chk(f(_p(lhs), _p(rhs), lhs.size, float(weight), resNumRows, resNumCols, None, C.byref(r), C.byref(c)))
+    res = np.empty((r.value, c.value))
+    _chk(f(_p(lhs), _p(rhs), lhs.size, float(weight), resNumRows, resNumCols, _p(res), C.byref(r), C.byref(c)))
+    return res
+
+
+def ctable(lhs, rhs, weight=1.0, resNumRows=-1, resNumCols=-1):
+    return _ctable(_lib, "orc", lhs, rhs, weight, resNumRows, resNumCols)
+
+
+def _seq(lib, prefix, start, end, inc):
+    f = getattr(lib, f"{prefix}_seq_f64")
+    f.argtypes = [C.c_double, C.c_double, C.c_double, C.c_void_p, i64, C.c_void_p]
+    n = C.c_int64()
+    _chk(f(float(start), float(end), float(inc), None, 0, C.byref(n)))
+    res = np.empty((n.value + 1, 1))
+    _chk(f(float(start), float(end), float(inc), _p(res), res.shape[0], C.byref(n)))
+    return res[:n.value].copy()
+
+
+def seq(start, end, inc):
+    return _seq(_lib, "orc", start, end, inc)

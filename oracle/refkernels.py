@@ -90,3 +90,48 @@ def aggAll(op, arg):
     f = _f(f"ref_agg_all_{_SUF[arg.dtype]}", [C.c_int, vp, i64, i64, i64, vp])
     _chk(f(int(op), _p(arg), arg.shape[0], arg.shape[1], _ld(arg), _p(res)))
     return res[0]
+
+
+def matMul(lhs, rhs, transa=False, transb=False):
+    return _o._matmul(_lib, "ref", lhs, rhs, transa, transb)
+
+
+def syrk(arg, transLeft=True):
+    return _o._syrk(_lib, "ref", arg, transLeft)
+
+
+def gemv(mat, vec):
+    mat = _mat(np.asarray(mat, dtype=np.float64))
+    vec = np.ascontiguousarray(np.asarray(vec, dtype=np.float64).reshape(-1, 1))
+    res = np.empty((mat.shape[1], 1))
+    f = _f("ref_gemv_f64", [vp, i64, i64, i64, vp, vp])
+    _chk(f(_p(mat), mat.shape[0], mat.shape[1], _ld(mat), _p(vec), _p(res)))
+    return res
+
+
+def solve(a, b):
+    return _o._solve(_lib, "ref", a, b)
+
+
+def transpose(arg):
+    arg = _mat(np.asarray(arg, dtype=np.float64))
+    res = np.empty((arg.shape[1], arg.shape[0]))
+    f = _f("ref_transpose_f64", [vp, i64, i64, i64, vp])
+    _chk(f(_p(arg), arg.shape[0], arg.shape[1], _ld(arg), _p(res)))
+    return res
+
+
+def ctable(lhs, rhs, weight=1.0, resNumRows=-1, resNumCols=-1):
+    return _o._ctable(_lib, "ref", lhs, rhs, weight, resNumRows, resNumCols)
+
+
+def seq(start, end, inc):
+    return _o._seq(_lib, "ref", start, end, inc)
+
+
+def rand(rows, cols, lo, hi, sparsity, seed):
+    """The reference's RandMatrix kernel = DaphneDSL rand(rows, cols, lo, hi, sparsity, seed)."""
+    res = np.empty((rows, cols))
+    f = _f("ref_rand_f64", [i64, i64, C.c_double, C.c_double, C.c_double, i64, vp])
+    _chk(f(rows, cols, float(lo), float(hi), float(sparsity), int(seed), _p(res)))
+    return res

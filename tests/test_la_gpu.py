@@ -1,0 +1,178 @@
+"""Contractions and helper kernels (matMul, syrk, gemv, solve, transpose, fill, seq, diagMatrix, ctable, castObj)
+against the CPU oracle.
+
+Tolerance for the contractions: |got - ref| <= 1e-12 * max|ref| per result (relative to the largest entry: the
+reference computes them with OpenBLAS, which fixes no summation order, so entries that cancel to nearly zero cannot be
+compared relative to themselves).  Integer-valued inputs, as in the reference's MatMulTest/SyrkTest, must match
+exactly."""
+import numpy as np
+import pytest
+
+from tests.util import assert_bits_equal
+
+pytestmark = pytest.mark.gpu
+RTOL = 1e-12
+
+
+def _k():
+    import daphne_b200.kernels as k
+    from oracle import pyoracle as o
+    return k, o
+
+
+def _close(got, exp, what):
+    assert got.shape == exp.shape, what
+    scale = max(np.abs(exp).max(), 1e-300)
+    err = np.abs(got - exp).max() / scale
+    assert err <= RTOL, f"{what}: {err:.3e}"
+
+
+@pytest.mark.parametrize("ta,tb", [(False, False), (False, True), (True, False), (True, True)])
+def test_matmul_all_transpose_combinations(ctx, ta, tb):
+    k, o = _k()
+    rng = np.random.default_rng(1)
+    for (m, n, kk) in [(1, 1, 1), (5, 7, 3), (64, 64, 16), (130, 70, 37), (257, 50, 64), (33, 129, 1000), (8, 8, 5000),
+                       (300, 200, 150)]:
+        a = rng.standard_normal((kk, m) if ta else (m, kk))
+        b = rng.standard_normal((n, kk) if tb else (kk, n))
+        got = k.matMul(k.DenseMatrix.from_numpy(ctx, a), k.DenseMatrix.from_numpy(ctx, b), ta, tb).to_numpy()
+        _close(got, o.matMul(a, b, ta, tb), f"matMul {m}x{n}x{kk} ta={ta} tb={tb}")
+
+
+def test_matmul_integer_valued_inputs_are_exact(ctx):
+    k, o = _k()
+    rng = np.random.default_rng(2)
+    a = rng.integers(-9, 10, size=(77, 130)).astype(np.float64)
+    b = rng.integers(-9, 10, size=(130, 41)).astype(np.float64)
+    got = k.matMul(k.DenseMatrix.from_numpy(ctx, a), k.DenseMatrix.from_numpy(ctx, b)).to_numpy()
+    assert_bits_equal(got, a @ b, "integer matMul")
+    got = k.syrk(k.DenseMatrix.from_numpy(ctx, a)).to_numpy()
+    assert_bits_equal(got, a.T @ a, "integer syrk")
+
+
+def test_matmul_on_views_and_odd_leading_dimensions(ctx):
+    k, o = _k()
+    rng = np.random.default_rng(3)
+    big = rng.standard_normal((500, 71))
+    a = big[:, 3:60]           # ld 71 (odd), offset 3
+    b = rng.standard_normal((57, 29))
+    got = k.matMul(k.DenseMatrix.from_numpy(ctx, a), k.DenseMatrix.from_numpy(ctx, b)).to_numpy()
+    _close(got, o.matMul(np.ascontiguousarray(a), b), "strided lhs")
+    A = k.DenseMatrix.from_numpy(ctx, rng.standard_normal((4000, 64)))
+    v = A.slice_rows(1000, 3001)
+    c = rng.standard_normal((50, 64))
+    got = k.matMul(v, k.DenseMatrix.from_numpy(ctx, c), False, True).to_numpy()
+    _close(got, o.matMul(A.to_numpy()[1000:3001], c, False, True), "row view x t(C)")
+
+
+def test_matmul_shape_mismatch_raises(ctx):
+    k, o = _k()
+    a, b = np.ones((4, 5)), np.ones((4, 5))
+    with pytest.raises(k.Db2Error, match="#cols of lhs and #rows of rhs must be the same"):
+        k.matMul(k.DenseMatrix.from_numpy(ctx, a), k.DenseMatrix.from_numpy(ctx, b))
+    with pytest.raises(o.OracleError):
+        o.matMul(a, b)
+
+
+@pytest.mark.parametrize("n,d", [(1000, 1), (5000, 7), (20000, 33), (100000, 100), (40000, 512), (300, 700)])
+def test_syrk_and_gemv_tall_skinny(ctx, n, d):
+    k, o = _k()
+    rng = np.random.default_rng(4)
+    x = rng.random((n, d))
+    y = rng.standard_normal((n, 1))
+    X, Y = k.DenseMatrix.from_numpy(ctx, x), k.DenseMatrix.from_numpy(ctx, y)
+    a = k.syrk(X, True).to_numpy()
+    ref = x.T @ x  # same tolerance class as the oracle's triple loop; the oracle itself is checked below for small d
+    _close(a, ref, f"syrk {n}x{d}")
+    assert_bits_equal(a, a.T.copy(), "syrk result is exactly symmetric")
+    if n * d * d <= 4e8:
+        _close(a, o.syrk(x, True), f"syrk vs oracle {n}x{d}")
+    _close(k.gemv(X, Y).to_numpy(), o.gemv(x, y), f"gemv {n}x{d}")
+    if n <= 5000:
+        _close(k.syrk(X, False).to_numpy(), o.syrk(x, False), f"syrk X t(X) {n}x{d}")
+
+
+def test_syrk_equals_transpose_then_matmul(ctx):
+    """The reference's SyrkTest checks syrk against transpose followed by matMul (SyrkTest.cpp:32-58)."""
+    k, o = _k()
+    x = np.random.default_rng(5).integers(-5, 6, size=(300, 40)).astype(np.float64)
+    X = k.DenseMatrix.from_numpy(ctx, x)
+    assert_bits_equal(k.syrk(X).to_numpy(), k.matMul(k.transpose(X), X).to_numpy(), "syrk == t(X) @ X")
+
+
+def test_normal_equations_solve(ctx):
+    k, o = _k()
+    rng = np.random.default_rng(6)
+    for n, d in [(2000, 5), (20000, 100), (30000, 512)]:
+        x = rng.random((n, d))
+        w = rng.standard_normal((d, 1))
+        y = x @ w + 0.01 * rng.standard_normal((n, 1))
+        X, Y = k.DenseMatrix.from_numpy(ctx, x), k.DenseMatrix.from_numpy(ctx, y)
+        lam = k.fill(ctx, 0.001, d, 1)
+        A = k.ewBinaryMat(k.BinaryOpCode.ADD, k.syrk(X), k.diagMatrix(lam))
+        b = k.gemv(X, Y)
+        beta = k.solve(A, b).to_numpy()
+        a_cpu = x.T @ x + 0.001 * np.eye(d)
+        ref = o.solve(a_cpu, x.T @ y)
+        # the normal equations are ill-conditioned (cond ~ 1e3..1e5): compare through the residual and loosely on beta
+        assert np.abs(beta - ref).max() <= 1e-7 * np.abs(ref).max(), f"beta {n}x{d}"
+        res = np.abs(a_cpu @ beta - x.T @ y).max() / np.abs(x.T @ y).max()
+        assert res <= 1e-12, f"residual {res:.2e}"
+        assert np.abs(beta - w).max() < 0.05
+
+
+def test_solve_general_and_singular(ctx):
+    k, o = _k()
+    rng = np.random.default_rng(7)
+    for n in (1, 2, 17, 100, 300):
+        a = rng.standard_normal((n, n)) + n * np.eye(n)
+        a[[0, n - 1]] = a[[n - 1, 0]]  # force row exchanges
+        b = rng.standard_normal((n, 1))
+        got = k.solve(k.DenseMatrix.from_numpy(ctx, a), k.DenseMatrix.from_numpy(ctx, b)).to_numpy()
+        ref = o.solve(a, b)
+        assert np.abs(got - ref).max() <= 1e-10 * np.abs(ref).max(), n
+    sing = np.zeros((3, 3))
+    sing[0, 0] = 1.0
+    with pytest.raises(k.Db2Error, match="exactly singular"):
+        k.solve(k.DenseMatrix.from_numpy(ctx, sing), k.DenseMatrix.from_numpy(ctx, np.ones((3, 1))))
+    with pytest.raises(o.OracleError):
+        o.solve(sing, np.ones((3, 1)))
+    with pytest.raises(k.Db2Error, match="#rows and #cols of lhs must be the same"):
+        k.solve(k.DenseMatrix.from_numpy(ctx, np.ones((3, 2))), k.DenseMatrix.from_numpy(ctx, np.ones((3, 1))))
+
+
+def test_transpose_fill_seq_diag_cast(ctx):
+    k, o = _k()
+    rng = np.random.default_rng(8)
+    for r, c in [(1, 1), (3, 5), (33, 65), (1000, 50), (70, 1)]:
+        a = rng.standard_normal((r, c))
+        assert_bits_equal(k.transpose(k.DenseMatrix.from_numpy(ctx, a)).to_numpy(), o.transpose(a), f"t {r}x{c}")
+    vec = k.DenseMatrix.from_numpy(ctx, rng.standard_normal((1000, 1)))
+    t = k.transpose(vec)
+    assert t.shape == (1, 1000) and t.device_ptr()[0] == vec.device_ptr()[0], "vectors are reshaped in place"
+    assert_bits_equal(k.fill(ctx, 2.5, 7, 9).to_numpy(), np.full((7, 9), 2.5), "fill")
+    for s, e, i in [(1.0, 100000.0, 1.0), (0.0, 9.0, 3.0), (10.0, 1.0, -3.0), (5.0, 5.0, 1.0), (1.0, 10.0, -1.0)]:
+        assert_bits_equal(k.seq(ctx, s, e, i).to_numpy(), o.seq(s, e, i), f"seq {s} {e} {i}")
+    with pytest.raises(k.Db2Error, match="inc should not be zero"):
+        k.seq(ctx, 1.0, 2.0, 0.0)
+    d = rng.standard_normal((37, 1))
+    assert_bits_equal(k.diagMatrix(k.DenseMatrix.from_numpy(ctx, d)).to_numpy(), np.diag(d[:, 0]), "diagMatrix")
+    u = np.arange(50, dtype=np.uint64).reshape(-1, 1)
+    assert_bits_equal(k.castObj(k.DenseMatrix.from_numpy(ctx, u), np.int64).to_numpy(), u.astype(np.int64), "cast")
+
+
+def test_ctable(ctx):
+    k, o = _k()
+    rng = np.random.default_rng(9)
+    n = 100000
+    lhs = np.arange(n, dtype=np.int64).reshape(-1, 1)
+    rhs = rng.integers(0, 50, size=(n, 1), dtype=np.int64)
+    L, R = k.DenseMatrix.from_numpy(ctx, lhs), k.DenseMatrix.from_numpy(ctx, rhs)
+    assert_bits_equal(k.ctable(L, R, 1.0, n, 50).to_numpy(), o.ctable(lhs, rhs, 1.0, n, 50), "one-hot ctable")
+    a = rng.integers(0, 9, size=(5000, 1), dtype=np.int64)
+    b = rng.integers(0, 13, size=(5000, 1), dtype=np.int64)
+    A, B = k.DenseMatrix.from_numpy(ctx, a), k.DenseMatrix.from_numpy(ctx, b)
+    assert_bits_equal(k.ctable(A, B).to_numpy(), o.ctable(a, b), "ctable, derived shape")
+    assert_bits_equal(k.ctable(A, B, 3.0, 5, 20).to_numpy(), o.ctable(a, b, 3.0, 5, 20), "ctable, given shape")
+    with pytest.raises(k.Db2Error, match="same number of rows"):
+        k.ctable(A, R)

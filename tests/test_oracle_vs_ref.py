@@ -100,3 +100,29 @@ def test_nan_and_signed_zero_cases():
         for op in (2, 3, 4, 5):
             assert_bits_equal(*_nanfix(o.aggRow(op, a), ref.aggRow(op, a)), f"row {op}")
             assert_bits_equal(*_nanfix(o.aggCol(op, a), ref.aggCol(op, a)), f"col {op}")
+
+
+def test_contractions_and_helpers():
+    """BLAS-backed kernels fix no summation order: tolerance 1e-12 relative to the largest entry; the rest is exact."""
+    rng = np.random.default_rng(5)
+    a, y = rng.random((300, 40)), rng.standard_normal((300, 1))
+    for ta, tb, x, z in ((0, 0, a, rng.random((40, 17))), (1, 0, a, rng.random((300, 9))),
+                         (0, 1, a, rng.random((11, 40))), (1, 1, a, rng.random((7, 300)))):
+        g, e = o.matMul(x, z, ta, tb), ref.matMul(x, z, ta, tb)
+        assert np.abs(g - e).max() <= 1e-12 * np.abs(e).max()
+    for tl in (True, False):
+        g, e = o.syrk(a, tl), ref.syrk(a, tl)
+        assert np.abs(g - e).max() <= 1e-12 * np.abs(e).max()
+    assert np.abs(o.gemv(a, y) - ref.gemv(a, y)).max() <= 1e-12 * np.abs(ref.gemv(a, y)).max()
+    s = o.syrk(a) + 0.001 * np.eye(40)
+    b = o.gemv(a, y)
+    assert np.abs(o.solve(s, b) - ref.solve(s, b)).max() <= 1e-9 * np.abs(ref.solve(s, b)).max()
+    ints = rng.integers(-5, 6, size=(30, 12)).astype(np.float64)
+    assert_bits_equal(o.syrk(ints), ref.syrk(ints), "integer syrk")
+    assert_bits_equal(o.matMul(ints, ints, True, False), ref.matMul(ints, ints, True, False), "integer matMul")
+    assert_bits_equal(o.transpose(a), ref.transpose(a), "transpose")
+    l, r = rng.integers(0, 5, 200), rng.integers(0, 7, 200)
+    assert_bits_equal(o.ctable(l, r), ref.ctable(l, r), "ctable")
+    assert_bits_equal(o.ctable(l, r, 2.0, 3, 4), ref.ctable(l, r, 2.0, 3, 4), "ctable given shape")
+    for args in ((1, 10, 1), (0, 1, 0.1), (10, 1, -3), (5, 5, 1), (1, 1000, 7)):
+        assert_bits_equal(o.seq(*args), ref.seq(*args), f"seq {args}")
