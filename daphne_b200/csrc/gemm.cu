@@ -1,10 +1,10 @@
 // FP64 contractions on the tensor cores: MatMul (all four transpose combinations) and Syrk (t(X) X / X t(X)).
 //
 // Blackwell's tcgen05 tensor path has no FP64 kind, so the FP64 contraction is the warp-level DMMA
-// (mma.sync.aligned.m8n8k4.f64), fed from shared memory tiles that are filled with 16-byte cp.async copies in a
+// (mma.sync.aligned.m16n8k16.f64), fed from shared memory tiles that are filled with 16-byte cp.async copies in a
 // 4-stage ring.  Tile layouts are chosen so that every fragment load is one conflict-free 64-bit shared load per
 // thread: an operand whose contraction index is contiguous in memory is stored [row][KC + 4], the other kind is stored
-// [k][tile + 4]; both pitches are 4 mod 16 doubles, which spreads the 8 x 4 fragment of a half warp over all banks.
+// [k][tile + 4]; both pitches are 4 mod 16 doubles, which spreads every fragment access of a half warp over all banks.
 //
 // The tall-skinny products of the workloads (t(X) X with 8.4 M x 512, t(P) X with 1 M x 50) contract over the ROWS:
 // the row range is split over gridDim.z, each split accumulates a private tile and writes it to scratch, and a second
@@ -15,14 +15,25 @@
 namespace db2 {
 
 constexpr int KC = 16;     // contraction depth per stage
-constexpr int BN = 64;     // tile columns
-constexpr int STAGES = 4;
 constexpr int PK = KC + 4; // pitch of a [row][k] tile (doubles)
+// CTA tiles: BM x BN in {64,128}^2 with (BM / 32) x (BN / 32) warps of 32 x 32.  128 x 128 (16 warps) gives 16 flop
+// per byte fetched from L2, which is what keeps the FP64 tensor pipe busy (a 64 x 64 tile needs twice the L2 traffic
+// and stalls at about half of peak on this part).
+template <int BM, int BN> struct TileCfg {
+    static constexpr int WN = 32;
+    static constexpr int THREADS = (BM / 32) * (BN / 32) * 32;
+    static constexpr int STAGES = (BM == 128 && BN == 128) ? 5 : 4;
+};
 
-__device__ __forceinline__ void dmma8x8x4(double &c0, double &c1, double a, double b) {
-    asm volatile("mma.sync.aligned.m8n8k4.row.col.f64.f64.f64.f64 {%0,%1}, {%2}, {%3}, {%0,%1};\n"
-                 : "+d"(c0), "+d"(c1)
-                 : "d"(a), "d"(b));
+// D (16 x 8) += A (16 x 16, row) * B (16 x 8, col).  With g = lane / 4, t = lane % 4:
+//   a[i]: row g + 8 * (i & 1), k = t + 4 * (i >> 1);   b[i]: k = t + 4 * i, column g;
+//   c[i]: row g + 8 * (i >> 1), column 2 * t + (i & 1).
+__device__ __forceinline__ void dmma16x8x16(double (&c)[4], const double (&a)[8], const double (&b)[4]) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f64.f64.f64.f64 {%0,%1,%2,%3}, {%4,%5,%6,%7,%8,%9,%10,%11}, "
+                 "{%12,%13,%14,%15}, {%0,%1,%2,%3};\n"
+                 : "+d"(c[0]), "+d"(c[1]), "+d"(c[2]), "+d"(c[3])
+                 : "d"(a[0]), "d"(a[1]), "d"(a[2]), "d"(a[3]), "d"(a[4]), "d"(a[5]), "d"(a[6]), "d"(a[7]), "d"(b[0]),
+                   "d"(b[1]), "d"(b[2]), "d"(b[3]));
 }
 // 16-byte async copy with zero fill: `bytes` (0, 8 or 16) are read from global, the rest of the slot is zeroed
 __device__ __forceinline__ void cp_async16_zfill(void *smem_dst, const void *gsrc, int bytes) {
@@ -47,9 +58,9 @@ struct GemmArgs {
 };
 
 // Loads one stage.  TA: A is stored K x M (contraction index = row);  !TA: A is M x K.  Same for TB with N.
-template <bool TA, bool TB, int BM>
+template <bool TA, bool TB, int BM, int BN>
 __device__ __forceinline__ void load_stage(const GemmArgs &g, double *As, double *Bs, int64_t m0, int64_t n0,
-                                           int64_t k0, int64_t k_end, int tid, int nthreads) {
+                                           int64_t k0, int64_t k_end, int tid, int nthreads, bool load_b) {
     constexpr int PA = BM + 4, PB = BN + 4;
     if (g.aligned) {
         if constexpr (TA) { // [KC][BM]: KC rows of BM contiguous doubles
@@ -71,7 +82,8 @@ __device__ __forceinline__ void load_stage(const GemmArgs &g, double *As, double
                 cp_async16_zfill(As + r * PK + 2 * p, bytes ? (g.A + m * g.lda + k) : g.A, bytes);
             }
         }
-        if constexpr (!TB) { // B is K x N: [KC][BN]
+        if (!load_b) {
+        } else if constexpr (!TB) { // B is K x N: [KC][BN]
             for (int idx = tid; idx < KC * (BN / 2); idx += nthreads) {
                 const int kk = idx / (BN / 2), p = idx % (BN / 2);
                 const int64_t k = k0 + kk, n = n0 + 2 * p;
@@ -105,7 +117,8 @@ __device__ __forceinline__ void load_stage(const GemmArgs &g, double *As, double
                 As[r * PK + c] = (m < g.M && k < k_end) ? g.A[m * g.lda + k] : 0.0;
             }
         }
-        if constexpr (!TB) {
+        if (!load_b) {
+        } else if constexpr (!TB) {
             for (int idx = tid; idx < KC * BN; idx += nthreads) {
                 const int kk = idx / BN, c = idx % BN;
                 const int64_t k = k0 + kk, n = n0 + c;
@@ -122,37 +135,48 @@ __device__ __forceinline__ void load_stage(const GemmArgs &g, double *As, double
 }
 
 // C (M x N) = op(A) op(B).  blockIdx.x = tile_n (fastest), blockIdx.y = tile_m, blockIdx.z = split of the
-// contraction range.  BM x BN tile, (BM / 32) x 2 warps of 32 x 32.
-template <bool TA, bool TB, int BM>
-__global__ void __launch_bounds__(BM * 2) gemm_f64_kernel(const __grid_constant__ GemmArgs g) {
-    constexpr int NT = BM * 2;
+// contraction range.  With `syrk`, warps whose 32 x 32 sub-tile lies strictly below the diagonal do no arithmetic
+// (the reduce step mirrors those entries), and a tile on the diagonal loads its operand once.
+template <bool TA, bool TB, int BM, int BN>
+__global__ void __launch_bounds__(TileCfg<BM, BN>::THREADS) gemm_f64_kernel(const __grid_constant__ GemmArgs ga) {
+    using Cfg = TileCfg<BM, BN>;
+    constexpr int NT = Cfg::THREADS, WN = Cfg::WN, STAGES = Cfg::STAGES, NTILES = WN / 8;
     constexpr int PA = BM + 4, PB = BN + 4;
     constexpr int A_ELEMS = TA ? KC * PA : BM * PK;
     constexpr int B_ELEMS = TB ? BN * PK : KC * PB;
     extern __shared__ __align__(16) double gsm[];
     const int tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
-    const int wm = warp / 2, wn = warp % 2;
+    // warp -> sub-tile: rotating the column by the row spreads the warps that stay active in a diagonal syrk tile
+    // (column block >= row block) evenly over the four scheduler partitions (warp id mod 4)
+    constexpr int WCOLS = BN / 32;
+    const int wm = warp / WCOLS, wn = (warp % WCOLS + WCOLS - wm % WCOLS) % WCOLS;
     const int64_t m0 = (int64_t)blockIdx.y * BM, n0 = (int64_t)blockIdx.x * BN;
-    if (g.syrk && n0 + BN <= m0)
+    if (ga.syrk && n0 + BN <= m0)
         return; // strictly below the diagonal: mirrored by the reduce step
-    const int64_t k_begin = (int64_t)blockIdx.z * g.k_per_split;
-    const int64_t k_end = (k_begin + g.k_per_split < g.K) ? k_begin + g.k_per_split : g.K;
+    const bool warp_active = !ga.syrk || (n0 + wn * WN + WN > m0 + wm * 32);
+    const bool same_tile = ga.syrk && BM == BN && m0 == n0 && (TA != TB);
+    const int64_t k_begin = (int64_t)blockIdx.z * ga.k_per_split;
+    const int64_t k_end = (k_begin + ga.k_per_split < ga.K) ? k_begin + ga.k_per_split : ga.K;
     const int64_t nchunks = (k_end > k_begin) ? (k_end - k_begin + KC - 1) / KC : 0;
 
-    double acc[4][4][2];
+    double acc[2][NTILES][4];
 #pragma unroll
-    for (int i = 0; i < 4; i++)
+    for (int i = 0; i < 2; i++)
 #pragma unroll
-        for (int j = 0; j < 4; j++)
-            acc[i][j][0] = acc[i][j][1] = 0.0;
+        for (int j = 0; j < NTILES; j++)
+#pragma unroll
+            for (int e = 0; e < 4; e++)
+                acc[i][j][e] = 0.0;
+    const int g = lane / 4, t = lane % 4;
 
     auto stage_a = [&](int s) { return gsm + (size_t)s * (A_ELEMS + B_ELEMS); };
-    auto stage_b = [&](int s) { return gsm + (size_t)s * (A_ELEMS + B_ELEMS) + A_ELEMS; };
+    auto stage_b = [&](int s) { return same_tile ? stage_a(s) : gsm + (size_t)s * (A_ELEMS + B_ELEMS) + A_ELEMS; };
 
 #pragma unroll
     for (int s = 0; s < STAGES - 1; s++) {
         if (s < nchunks)
-            load_stage<TA, TB, BM>(g, stage_a(s), stage_b(s), m0, n0, k_begin + (int64_t)s * KC, k_end, tid, NT);
+            load_stage<TA, TB, BM, BN>(ga, stage_a(s), stage_b(s), m0, n0, k_begin + (int64_t)s * KC, k_end, tid, NT,
+                                       !same_tile);
         cp_async_commit();
     }
     for (int64_t ch = 0; ch < nchunks; ch++) {
@@ -161,70 +185,82 @@ __global__ void __launch_bounds__(BM * 2) gemm_f64_kernel(const __grid_constant_
         {
             const int64_t nx = ch + STAGES - 1;
             if (nx < nchunks)
-                load_stage<TA, TB, BM>(g, stage_a((int)(nx % STAGES)), stage_b((int)(nx % STAGES)), m0, n0,
-                                       k_begin + nx * KC, k_end, tid, NT);
+                load_stage<TA, TB, BM, BN>(ga, stage_a((int)(nx % STAGES)), stage_b((int)(nx % STAGES)), m0, n0,
+                                           k_begin + nx * KC, k_end, tid, NT, !same_tile);
             cp_async_commit();
         }
+        if (!warp_active)
+            continue;
         const double *As = stage_a((int)(ch % STAGES));
         const double *Bs = stage_b((int)(ch % STAGES));
+        static_assert(KC == 16, "one m16n8k16 step per stage");
+        double af[2][8];
 #pragma unroll
-        for (int kk = 0; kk < KC; kk += 4) {
-            double a[4], b[4];
+        for (int mt = 0; mt < 2; mt++)
 #pragma unroll
-            for (int mt = 0; mt < 4; mt++) {
-                const int m = wm * 32 + mt * 8 + lane / 4;
-                a[mt] = TA ? As[(kk + lane % 4) * PA + m] : As[m * PK + kk + lane % 4];
+            for (int i = 0; i < 8; i++) {
+                const int m = wm * 32 + mt * 16 + g + 8 * (i & 1), k = t + 4 * (i >> 1);
+                af[mt][i] = TA ? As[k * PA + m] : As[m * PK + k];
             }
 #pragma unroll
-            for (int nt = 0; nt < 4; nt++) {
-                const int n = wn * 32 + nt * 8 + lane / 4;
-                b[nt] = TB ? Bs[n * PK + kk + lane % 4] : Bs[(kk + lane % 4) * PB + n];
+        for (int nt = 0; nt < NTILES; nt++) {
+            double bf[4];
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                const int n = wn * WN + nt * 8 + g, k = t + 4 * i;
+                bf[i] = TB ? Bs[n * PK + k] : Bs[k * PB + n];
             }
-#pragma unroll
-            for (int mt = 0; mt < 4; mt++)
-#pragma unroll
-                for (int nt = 0; nt < 4; nt++)
-                    dmma8x8x4(acc[mt][nt][0], acc[mt][nt][1], a[mt], b[nt]);
+            dmma16x8x16(acc[0][nt], af[0], bf);
+            dmma16x8x16(acc[1][nt], af[1], bf);
         }
     }
     cp_async_wait<0>();
+    if (!warp_active)
+        return;
 
-    if (g.splits > 1) {
-        double *tile = g.part + (((size_t)blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x) * (BM * BN);
+    if (ga.splits > 1) {
+        double *tile =
+            ga.part + (((size_t)blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x) * (BM * BN);
 #pragma unroll
-        for (int mt = 0; mt < 4; mt++)
+        for (int mt = 0; mt < 2; mt++)
 #pragma unroll
-            for (int nt = 0; nt < 4; nt++) {
-                const int r = wm * 32 + mt * 8 + lane / 4, c = wn * 32 + nt * 8 + (lane % 4) * 2;
-                *reinterpret_cast<double2 *>(tile + r * BN + c) = make_double2(acc[mt][nt][0], acc[mt][nt][1]);
-            }
+            for (int nt = 0; nt < NTILES; nt++)
+#pragma unroll
+                for (int h = 0; h < 2; h++) {
+                    const int r = wm * 32 + mt * 16 + g + 8 * h, c = wn * WN + nt * 8 + 2 * t;
+                    *reinterpret_cast<double2 *>(tile + r * BN + c) =
+                        make_double2(acc[mt][nt][2 * h], acc[mt][nt][2 * h + 1]);
+                }
     } else {
 #pragma unroll
-        for (int mt = 0; mt < 4; mt++)
+        for (int mt = 0; mt < 2; mt++)
 #pragma unroll
-            for (int nt = 0; nt < 4; nt++) {
-                const int64_t r = m0 + wm * 32 + mt * 8 + lane / 4, c = n0 + wn * 32 + nt * 8 + (lane % 4) * 2;
-                if (r < g.M) {
-                    if (c < g.N)
-                        g.C[r * g.ldc + c] = acc[mt][nt][0];
-                    if (c + 1 < g.N)
-                        g.C[r * g.ldc + c + 1] = acc[mt][nt][1];
+            for (int nt = 0; nt < NTILES; nt++)
+#pragma unroll
+                for (int h = 0; h < 2; h++) {
+                    const int64_t r = m0 + wm * 32 + mt * 16 + g + 8 * h, c = n0 + wn * WN + nt * 8 + 2 * t;
+                    if (r < ga.M) {
+                        if (c < ga.N)
+                            ga.C[r * ga.ldc + c] = acc[mt][nt][2 * h];
+                        if (c + 1 < ga.N)
+                            ga.C[r * ga.ldc + c + 1] = acc[mt][nt][2 * h + 1];
+                    }
                 }
-            }
     }
 }
 
-// Adds the per-split tiles in split order; with `syrk` the strictly lower part is the mirror of the upper one, and
-// when splits == 1 only the mirroring is done (the tiles were written to C directly).
-template <int BM>
+// Adds the per-split tiles in split order; with `syrk` the entries of the skipped 32 x 32 sub-tiles are the mirror
+// of computed ones, and when splits == 1 only the mirroring is done (the tiles were written to C directly).
+template <int BM, int BN>
 __global__ void gemm_reduce_kernel(const double *__restrict__ part, double *__restrict__ C, int64_t ldc, int64_t M,
                                    int64_t N, int tiles_m, int tiles_n, int splits, int syrk) {
+    constexpr int WN = 32;
     const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= M * N)
         return;
     const int64_t i = idx / N, j = idx % N;
     int64_t si = i, sj = j;
-    if (syrk && (j / BN) * BN + BN <= (i / BM) * BM) { // (i, j) lies in a tile that was skipped: take (j, i)
+    if (syrk && (j / WN) * WN + WN <= (i / 32) * 32) { // (i, j) was skipped: take (j, i)
         si = j;
         sj = i;
     }
@@ -242,32 +278,40 @@ __global__ void gemm_reduce_kernel(const double *__restrict__ part, double *__re
 }
 
 struct GemmPlan {
-    int bm, tiles_m, tiles_n, splits;
+    int bm, bn, tiles_m, tiles_n, splits;
     int64_t k_per_split;
     size_t scratch;
 };
 
-static GemmPlan plan_gemm(int64_t M, int64_t N, int64_t K, bool syrk) {
+static size_t tile_smem(int bm, int bn, bool ta, bool tb) {
+    const size_t a = ta ? (size_t)KC * (bm + 4) : (size_t)bm * PK;
+    const size_t b = tb ? (size_t)bn * PK : (size_t)KC * (bn + 4);
+    const int stages = (bm == 128 && bn == 128) ? 5 : 4;
+    return stages * (a + b) * 8;
+}
+
+static GemmPlan plan_gemm(int64_t M, int64_t N, int64_t K, bool syrk, bool ta, bool tb) {
     GemmPlan p;
-    // tall-skinny contractions (K much larger than the output) use the smaller tile and split the contraction range
-    const bool tall = K >= 64 * (M > N ? M : N) || M * N <= (int64_t)BN * 64 * 148;
-    p.bm = (M <= 64 || (tall && K > 8 * M)) ? 64 : 128;
+    p.bm = M > 64 ? 128 : 64;
+    p.bn = N > 64 ? 128 : 64;
     p.tiles_m = (int)((M + p.bm - 1) / p.bm);
-    p.tiles_n = (int)((N + BN - 1) / BN);
+    p.tiles_n = (int)((N + p.bn - 1) / p.bn);
     int64_t tiles = (int64_t)p.tiles_m * p.tiles_n;
     if (syrk) { // tiles on or above the diagonal
         tiles = 0;
         for (int tm = 0; tm < p.tiles_m; tm++)
             for (int tn = 0; tn < p.tiles_n; tn++)
-                if ((int64_t)tn * BN + BN > (int64_t)tm * p.bm)
+                if ((int64_t)tn * p.bn + p.bn > (int64_t)tm * p.bm)
                     tiles++;
     }
-    const size_t smem = (size_t)STAGES * ((size_t)KC * (p.bm + 4) + (size_t)KC * (BN + 4)) * 8; // upper bound
-    int per_sm = (int)((200 * 1024) / smem);
+    int per_sm = (int)((220 * 1024) / tile_smem(p.bm, p.bn, ta, tb));
     if (per_sm < 1)
         per_sm = 1;
-    if (per_sm > (p.bm == 64 ? 4 : 2))
-        per_sm = (p.bm == 64 ? 4 : 2);
+    const int max_per_sm = 2048 / ((p.bm / 32) * (p.bn / 32) * 32);
+    if (per_sm > max_per_sm)
+        per_sm = max_per_sm;
+    if (per_sm > 4)
+        per_sm = 4;
     const int64_t slots = (int64_t)sm_count() * per_sm;
     const int64_t chunks = (K + KC - 1) / KC;
     int64_t splits = slots / (tiles > 0 ? tiles : 1);
@@ -280,51 +324,58 @@ static GemmPlan plan_gemm(int64_t M, int64_t N, int64_t K, bool syrk) {
     const int64_t cps = (chunks + splits - 1) / splits;
     p.k_per_split = cps * KC;
     p.splits = (int)((chunks + cps - 1) / cps);
-    p.scratch = p.splits > 1 ? (size_t)p.splits * p.tiles_m * p.tiles_n * p.bm * BN * 8 : 0;
+    p.scratch = p.splits > 1 ? (size_t)p.splits * p.tiles_m * p.tiles_n * p.bm * p.bn * 8 : 0;
     return p;
 }
 
-template <bool TA, bool TB, int BM> static int launch_gemm(const GemmArgs &g, const GemmPlan &p, cudaStream_t st) {
-    constexpr int A_ELEMS = TA ? KC * (BM + 4) : BM * PK;
-    constexpr int B_ELEMS = TB ? BN * PK : KC * (BN + 4);
-    const size_t smem = (size_t)STAGES * (A_ELEMS + B_ELEMS) * sizeof(double);
+template <bool TA, bool TB, int BM, int BN>
+static int launch_gemm(const GemmArgs &g, const GemmPlan &p, cudaStream_t st) {
+    const size_t smem = tile_smem(BM, BN, TA, TB);
     static bool attr = false;
     if (!attr) {
-        DB2_CUDA(cudaFuncSetAttribute(gemm_f64_kernel<TA, TB, BM>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        DB2_CUDA(cudaFuncSetAttribute(gemm_f64_kernel<TA, TB, BM, BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                       (int)smem));
         attr = true;
     }
     dim3 grid(p.tiles_n, p.tiles_m, p.splits);
-    gemm_f64_kernel<TA, TB, BM><<<grid, BM * 2, smem, st>>>(g);
+    gemm_f64_kernel<TA, TB, BM, BN><<<grid, TileCfg<BM, BN>::THREADS, smem, st>>>(g);
     DB2_TRY(after_launch("gemm_f64_kernel"));
     if (p.splits > 1 || g.syrk) {
         const int64_t total = g.M * g.N;
-        gemm_reduce_kernel<BM><<<(unsigned)((total + 255) / 256), 256, 0, st>>>(g.part, g.C, g.ldc, g.M, g.N,
-                                                                                p.tiles_m, p.tiles_n, p.splits, g.syrk);
+        gemm_reduce_kernel<BM, BN><<<(unsigned)((total + 255) / 256), 256, 0, st>>>(
+            g.part, g.C, g.ldc, g.M, g.N, p.tiles_m, p.tiles_n, p.splits, g.syrk);
         DB2_TRY(after_launch("gemm_reduce_kernel"));
     }
     return DB2_OK;
 }
 
+template <bool TA, bool TB> static int dispatch_tiles(const GemmArgs &g, const GemmPlan &p, cudaStream_t st) {
+    if (p.bm == 128 && p.bn == 128)
+        return launch_gemm<TA, TB, 128, 128>(g, p, st);
+    if (p.bm == 128)
+        return launch_gemm<TA, TB, 128, 64>(g, p, st);
+    if (p.bn == 128)
+        return launch_gemm<TA, TB, 64, 128>(g, p, st);
+    return launch_gemm<TA, TB, 64, 64>(g, p, st);
+}
+
 static int run_gemm(bool ta, bool tb, GemmArgs g, cudaStream_t st, void *scratch, size_t scratch_bytes) {
     if (g.M == 0 || g.N == 0)
         return DB2_OK;
-    const GemmPlan p = plan_gemm(g.M, g.N, g.K, g.syrk != 0);
+    const GemmPlan p = plan_gemm(g.M, g.N, g.K, g.syrk != 0, ta, tb);
     DB2_CHECK(p.scratch == 0 || (scratch && scratch_bytes >= p.scratch), DB2_EINVAL,
               "matMul/syrk scratch too small: %zu < %zu", scratch_bytes, p.scratch);
     g.part = static_cast<double *>(scratch);
     g.splits = p.splits;
     g.k_per_split = p.k_per_split;
     g.aligned = aligned16(g.A) && aligned16(g.B) && (g.lda % 2 == 0) && (g.ldb % 2 == 0);
-#define DB2_GEMM_CASE(TA_, TB_)                                                                                        \
-    if (ta == TA_ && tb == TB_)                                                                                        \
-        return p.bm == 64 ? launch_gemm<TA_, TB_, 64>(g, p, st) : launch_gemm<TA_, TB_, 128>(g, p, st);
-    DB2_GEMM_CASE(false, false)
-    DB2_GEMM_CASE(false, true)
-    DB2_GEMM_CASE(true, false)
-    DB2_GEMM_CASE(true, true)
-#undef DB2_GEMM_CASE
-    return DB2_OK;
+    if (!ta && !tb)
+        return dispatch_tiles<false, false>(g, p, st);
+    if (!ta && tb)
+        return dispatch_tiles<false, true>(g, p, st);
+    if (ta && !tb)
+        return dispatch_tiles<true, false>(g, p, st);
+    return dispatch_tiles<true, true>(g, p, st);
 }
 
 } // namespace db2
@@ -333,7 +384,12 @@ using namespace db2;
 
 extern "C" size_t db2k_matmul_scratch_bytes(int dtype, int64_t m, int64_t n, int64_t k) {
     (void)dtype;
-    return plan_gemm(m, n, k, false).scratch + 256;
+    size_t worst = 0;
+    for (int c = 0; c < 4; c++) {
+        const size_t b = plan_gemm(m, n, k, false, c & 1, c & 2).scratch;
+        worst = b > worst ? b : worst;
+    }
+    return worst + 256;
 }
 
 extern "C" int db2k_matmul(int dtype, const void *lhs, int64_t lhs_rows, int64_t lhs_cols, int64_t lhs_ld,
@@ -362,7 +418,7 @@ extern "C" int db2k_matmul(int dtype, const void *lhs, int64_t lhs_rows, int64_t
 extern "C" size_t db2k_syrk_scratch_bytes(int dtype, int64_t rows, int64_t cols, int trans_left) {
     (void)dtype;
     const int64_t n = trans_left ? cols : rows, k = trans_left ? rows : cols;
-    return plan_gemm(n, n, k, true).scratch + 256;
+    return plan_gemm(n, n, k, true, trans_left != 0, trans_left == 0).scratch + 256;
 }
 
 extern "C" int db2k_syrk(int dtype, const void *arg, int64_t rows, int64_t cols, int64_t ld, int trans_left, void *res,
