@@ -284,3 +284,90 @@ def castObj(arg: DenseMatrix, dtype, ctx: Optional[Context] = None) -> DenseMatr
     h = C.c_void_p()
     check(lib.db2_castObj(ctx.handle, C.byref(h), arg.handle, _NP2DT[np.dtype(dtype)]))
     return _res(ctx, h)
+
+
+class CSRMatrix:
+    """Handle to a db2_csr.  The host arrays follow the reference's CSRMatrix layout (values, colIdxs and rowOffsets
+    with 64-bit indices)."""
+
+    def __init__(self, ctx: Context, handle, keep=None):
+        self.ctx, self._h, self._keep = ctx, handle, keep
+        r, c = C.c_int64(), C.c_int64()
+        check(lib.db2_csr_info(self._h, C.byref(r), C.byref(c), None))
+        self.rows, self.cols = r.value, c.value
+
+    @property
+    def handle(self):
+        return self._h
+
+    @property
+    def shape(self):
+        return (self.rows, self.cols)
+
+    @staticmethod
+    def from_arrays(ctx: Context, rows: int, cols: int, values, col_idx, row_off) -> "CSRMatrix":
+        values = np.ascontiguousarray(values, dtype=np.float64)
+        col_idx = np.ascontiguousarray(col_idx, dtype=np.uint64)
+        row_off = np.ascontiguousarray(row_off, dtype=np.uint64)
+        h = C.c_void_p()
+        check(lib.db2_csr_wrap_host(ctx.handle, _l.F64, rows, cols, C.c_void_p(values.ctypes.data),
+                                    C.c_void_p(col_idx.ctypes.data), C.c_void_p(row_off.ctypes.data), C.byref(h)))
+        return CSRMatrix(ctx, h, keep=(values, col_idx, row_off))
+
+    @staticmethod
+    def from_scipy(ctx: Context, m) -> "CSRMatrix":
+        m = m.tocsr()
+        m.sort_indices()
+        return CSRMatrix.from_arrays(ctx, m.shape[0], m.shape[1], m.data, m.indices, m.indptr)
+
+    def nnz(self) -> int:
+        n = C.c_int64()
+        check(lib.db2_csr_info(self._h, None, None, C.byref(n)))
+        return n.value
+
+    def slice_rows(self, r0: int, r1: int) -> "CSRMatrix":
+        h = C.c_void_p()
+        check(lib.db2_csr_slice_rows(self._h, r0, r1, C.byref(h)))
+        return CSRMatrix(self.ctx, h, keep=self._keep)
+
+    def to_arrays(self):
+        n = self.nnz()
+        vals, cols, offs = np.empty(n), np.empty(n, dtype=np.uint64), np.empty(self.rows + 1, dtype=np.uint64)
+        check(lib.db2_csr_to_host(self._h, C.c_void_p(vals.ctypes.data), C.c_void_p(cols.ctypes.data),
+                                  C.c_void_p(offs.ctypes.data)))
+        return vals, cols, offs
+
+    def free(self):
+        if self._h:
+            lib.db2_csr_decref(self._h)
+            self._h = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.free()
+        except Exception:
+            pass
+
+
+def ewMulCsrDense(lhs: CSRMatrix, rhs: DenseMatrix, ctx: Optional[Context] = None) -> CSRMatrix:
+    """EwBinaryMat<CSR,CSR,Dense> with MUL (EwBinaryMat.h:254-317)."""
+    ctx = ctx or lhs.ctx
+    h = C.c_void_p()
+    check(lib.db2_ewMulCsrDense(ctx.handle, C.byref(h), lhs.handle, rhs.handle))
+    return CSRMatrix(ctx, h, keep=(lhs, rhs))
+
+
+def aggRowCsr(op, arg: CSRMatrix, ctx: Optional[Context] = None) -> DenseMatrix:
+    """AggRow<Dense,CSR> (AggRow.h:178-238)."""
+    ctx = ctx or arg.ctx
+    h = C.c_void_p()
+    check(lib.db2_aggRowCsr(ctx.handle, int(op), C.byref(h), arg.handle))
+    return _res(ctx, h)
+
+
+def matMulCsrDense(lhs: CSRMatrix, rhs: DenseMatrix, ctx: Optional[Context] = None) -> DenseMatrix:
+    """Gemv<Dense,CSR,Dense> / MatMul<Dense,CSR,Dense>."""
+    ctx = ctx or lhs.ctx
+    h = C.c_void_p()
+    check(lib.db2_matMulCsrDense(ctx.handle, C.byref(h), lhs.handle, rhs.handle))
+    return _res(ctx, h)

@@ -112,6 +112,15 @@ _SIGS = {
     "db2_diagMatrix": (i32, [vp, _P(vp), vp]),
     "db2_ctable": (i32, [vp, _P(vp), vp, vp, C.c_double, i64, i64]),
     "db2_castObj": (i32, [vp, _P(vp), vp, i32]),
+    "db2_csr_wrap_host": (i32, [vp, i32, i64, i64, vp, vp, vp, _P(vp)]),
+    "db2_csr_slice_rows": (i32, [vp, i64, i64, _P(vp)]),
+    "db2_csr_incref": (i32, [vp]),
+    "db2_csr_decref": (i32, [vp]),
+    "db2_csr_info": (i32, [vp, _P(i64), _P(i64), _P(i64)]),
+    "db2_csr_to_host": (i32, [vp, vp, vp, vp]),
+    "db2_ewMulCsrDense": (i32, [vp, _P(vp), vp, vp]),
+    "db2_aggRowCsr": (i32, [vp, i32, _P(vp), vp]),
+    "db2_matMulCsrDense": (i32, [vp, _P(vp), vp, vp]),
 }
 
 

@@ -128,3 +128,101 @@ def standardise_aggregate(ctx: K.Context, X: K.DenseMatrix, n_total: Optional[in
     s = float(s_local) if comm is None or comm.world == 1 else float(
         comm.allreduce_numpy(np.array([s_local], dtype=np.float64))[0])
     return StandardiseResult(mu, sd, r, s, m, i)
+
+
+@dataclass
+class NormalEquationsResult:
+    A: K.DenseMatrix      # d x d   t(X) X + lambda I (global)
+    b: K.DenseMatrix      # d x 1   t(X) y (global)
+    beta: K.DenseMatrix   # d x 1   solve(A, b)
+
+
+def normal_equations(ctx: K.Context, X: K.DenseMatrix, y: K.DenseMatrix, lam: float = 0.001,
+                     comm: Optional[Comm] = None, probe=None) -> NormalEquationsResult:
+    """Linear regression by the normal equations (lmDS, scripts/algorithms/lmDS_.daph:98-112):
+
+        A = t(X) @ X + diagMatrix(fill(lambda, ncol(X), 1));  b = t(X) @ y;  beta = solve(A, b);
+
+    t(X) @ X lowers to syrk and t(X) @ y to gemv (PhyOperatorSelectionPass.cpp:54-71); both are ADD-combined over the
+    row shards."""
+    probe = probe or _NoProbe()
+    d = X.cols
+    with probe.section("gemm_f64_kernel syrk t(X)X", X.rows * d * 8):
+        xtx = K.syrk(X, True)
+    xty = K.gemv(X, y)
+    xtx = _allreduce_matrix(ctx, xtx, comm)
+    xty = _allreduce_matrix(ctx, xty, comm)
+    A = K.ewBinaryMat(B.ADD, xtx, K.diagMatrix(K.fill(ctx, lam, d, 1)))
+    beta = K.solve(A, xty)
+    return NormalEquationsResult(A, xty, beta)
+
+
+@dataclass
+class KMeansResult:
+    C: K.DenseMatrix        # k x d centroids after the last update (global)
+    assign: K.DenseMatrix   # n x 1 (int64) cluster of every local row in the last iteration
+
+
+def kmeans(ctx: K.Context, X: K.DenseMatrix, C0: K.DenseMatrix, iterations: int = 10,
+           comm: Optional[Comm] = None) -> KMeansResult:
+    """K-means assignment + update:
+
+        xs = sum(X ^ 2, 0);
+        for i: D = (X @ t(C)) * -2.0 + xs + t(sum(C ^ 2, 0));  a = idxMin(D, 0);
+               P = ctable(seq(0, n - 1), a, 1.0, n, k);  C = (t(P) @ X) / t(sum(P, 1));
+
+    Ties in idxMin go to the lowest index (AggRow.h:71-83).  The centroid sums t(P) @ X and the counts sum(P, 1) are
+    ADD-combined over the row shards."""
+    n, k = X.rows, C0.rows
+    xs = K.aggRow(A.SUM, K.ewBinaryObjSca(B.POW, X, 2.0))
+    rows = K.seq(ctx, 0, n - 1, 1, dtype=np.int64)
+    Cm, assign = C0, None
+    for _ in range(iterations):
+        cs = K.transpose(K.aggRow(A.SUM, K.ewBinaryObjSca(B.POW, Cm, 2.0)))
+        xc = K.matMul(X, Cm, False, True)
+        D = K.ewBinaryMat(B.ADD, K.ewBinaryMat(B.ADD, K.ewBinaryObjSca(B.MUL, xc, -2.0), xs), cs)
+        assign = K.castObj(K.aggRow(A.IDXMIN, D), np.int64)
+        D.free()
+        xc.free()
+        P = K.ctable(rows, assign, 1.0, n, k)
+        sums = _allreduce_matrix(ctx, K.matMul(P, X, True, False), comm)
+        counts = _allreduce_matrix(ctx, K.aggCol(A.SUM, P), comm)
+        P.free()
+        Cm = K.ewBinaryMat(B.DIV, sums, K.transpose(counts))
+    return KMeansResult(Cm, assign)
+
+
+@dataclass
+class ComponentsResult:
+    c: K.DenseMatrix    # n_local x 1 component label of every local vertex
+    iterations: int
+
+
+def connected_components(ctx: K.Context, G: K.CSRMatrix, maxi: int = 1000, comm: Optional[Comm] = None,
+                         row_block: Optional[tuple] = None) -> ComponentsResult:
+    """Connected components by label propagation (test/api/cli/algorithms/components.daphne:14-26):
+
+        c = seq(1, n, 1);  while (diff > 0 && iter <= maxi):
+            u = max(aggMax(G * t(c), 0), c);  diff = sum(u != c);  c = u;
+
+    G is the row shard [row_block) of the symmetric 0/1 adjacency matrix (all n columns); every rank needs the whole
+    label vector for the gather G * t(c), so the updated shard is all-gathered each iteration and the change count is
+    ADD-combined."""
+    n = G.cols
+    lo, hi = row_block if row_block is not None else (0, G.rows)
+    c_full = K.seq(ctx, 1.0, float(n), 1.0)
+    it, diff = 1, 1.0
+    c_loc = c_full.slice_rows(lo, hi)
+    while diff > 0.0 and it <= maxi:
+        prod = K.ewMulCsrDense(G, K.transpose(c_full))
+        u = K.ewBinaryMat(B.MAX, K.aggRowCsr(A.MAX, prod), c_loc)
+        diff = float(K.aggAll(A.SUM, K.ewBinaryMat(B.NEQ, u, c_loc)))
+        if comm is not None and comm.world > 1:
+            diff = float(comm.allreduce_numpy(np.array([diff]))[0])
+            c_full = K.DenseMatrix.from_numpy(ctx, comm.allgather_numpy(u.to_numpy()))
+            c_loc = c_full.slice_rows(lo, hi)
+        else:
+            c_full = u
+            c_loc = u
+        it += 1
+    return ComponentsResult(c_loc, it - 1)

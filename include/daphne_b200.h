@@ -274,6 +274,34 @@ int db2_ctable(db2_context *ctx, db2_matrix **res, db2_matrix *lhs, db2_matrix *
 /* value-type cast between f64 / i64 / u64 (CastObj, used for idxMin results feeding ctable) */
 int db2_castObj(db2_context *ctx, db2_matrix **res, db2_matrix *arg, int dtype);
 
+/* ------------------------------------------------------------------------- */
+/* CSR matrices                                                               */
+/* ------------------------------------------------------------------------- */
+
+/* A CSR matrix with a device placement (32-bit column indices where the column count allows, 64-bit row offsets)
+ * and zero-copy row views.  The host layout handed in and out is the reference's: values[VT], colIdxs[size_t],
+ * rowOffsets[size_t, rows + 1] (src/runtime/local/datastructures/CSRMatrix.h:70-72); the reference has no device
+ * residency for CSRMatrix at all. */
+typedef struct db2_csr db2_csr;
+
+int db2_csr_wrap_host(db2_context *ctx, int dtype, int64_t rows, int64_t cols, const void *values,
+                      const uint64_t *col_idx, const uint64_t *row_off, db2_csr **out);
+/* rows [r0, r1) sharing the arrays (CSRMatrix view constructor, CSRMatrix.h:131-148) */
+int db2_csr_slice_rows(db2_csr *m, int64_t r0, int64_t r1, db2_csr **view);
+int db2_csr_incref(db2_csr *m);
+int db2_csr_decref(db2_csr *m);
+int db2_csr_info(db2_csr *m, int64_t *rows, int64_t *cols, int64_t *nnz);
+int db2_csr_to_host(db2_csr *m, void *values, uint64_t *col_idx, uint64_t *row_off);
+/* res = lhs (.) rhs, rhs of the same shape or a row/column vector; entries meeting an exactly zero rhs are dropped.
+ * The product is deferred until its arrays are needed.  Replaces EwBinaryMat<CSR,CSR,Dense> for MUL
+ * (src/runtime/local/kernels/EwBinaryMat.h:254-317; no CUDA twin in the reference). */
+int db2_ewMulCsrDense(db2_context *ctx, db2_csr **res, db2_csr *lhs, db2_matrix *rhs);
+/* SUM/PROD/MIN/MAX per row with the implicit zeros taking part where the reference lets them
+ * (AggRow<Dense,CSR>, src/runtime/local/kernels/AggRow.h:178-238).  A deferred product is aggregated in one pass. */
+int db2_aggRowCsr(db2_context *ctx, int op, db2_matrix **res, db2_csr *arg);
+/* res = lhs @ rhs, dense rhs (Gemv<Dense,CSR,Dense>, src/runtime/local/kernels/Gemv.h:79-117) */
+int db2_matMulCsrDense(db2_context *ctx, db2_matrix **res, db2_csr *lhs, db2_matrix *rhs);
+
 #ifdef __cplusplus
 }
 #endif

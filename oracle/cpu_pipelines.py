@@ -77,3 +77,43 @@ def standardise_aggregate(X: np.ndarray, threads: int = 1, k=None):
         for p in run(tail):
             s = s + float(p)
     return mu, sd, r, s, m, idx
+
+
+def normal_equations(X: np.ndarray, y: np.ndarray, lam: float = 0.001, k=None):
+    """CPU twin of daphne_b200.pipelines.normal_equations: (A, b, beta)."""
+    k = k or backend()[0]
+    d = X.shape[1]
+    A = k.ewBinaryMat(0, k.syrk(X, True), np.diag(np.full(d, lam)))
+    b = k.gemv(X, y)
+    return A, b, k.solve(A, b)
+
+
+def kmeans(X: np.ndarray, C0: np.ndarray, iterations: int = 10, k=None):
+    """CPU twin of daphne_b200.pipelines.kmeans: (C, assign)."""
+    k = k or backend()[0]
+    n, kk = X.shape[0], C0.shape[0]
+    xs = k.aggRow(SUM, k.ewBinaryObjSca(POW, X, 2.0))
+    rows = np.arange(n, dtype=np.int64)
+    C, a = C0, None
+    for _ in range(iterations):
+        cs = k.transpose(k.aggRow(SUM, k.ewBinaryObjSca(POW, C, 2.0)))
+        D = k.ewBinaryMat(0, k.ewBinaryMat(0, k.ewBinaryObjSca(2, k.matMul(X, C, False, True), -2.0), xs), cs)
+        a = k.aggRow(4, D).astype(np.int64)
+        P = k.ctable(rows, a, 1.0, n, kk)
+        C = k.ewBinaryMat(DIV, k.matMul(P, X, True, False), k.transpose(k.aggCol(SUM, P)))
+    return C, a
+
+
+def connected_components(G, maxi: int = 1000, k=None):
+    """CPU twin of daphne_b200.pipelines.connected_components on a scipy CSR matrix: (c, iterations)."""
+    k = k or backend()[0]
+    n = G.shape[0]
+    c = k.seq(1.0, float(n), 1.0)
+    it, diff = 1, 1.0
+    while diff > 0.0 and it <= maxi:
+        prod = k.ewMulCsrDense(G, k.transpose(c))
+        u = k.ewBinaryMat(14, k.aggRowCsr(MAX, prod), c)
+        diff = float(k.aggAll(SUM, k.ewBinaryMat(8, u, c)))
+        c = u
+        it += 1
+    return c, it - 1

@@ -505,3 +505,62 @@ int orc_seq_f64(double start, double end, double inc, double *res, int64_t cap, 
     *n_out = n;
     return 0;
 }
+
+/* ------------------------------------------------------------------------------------------------------------- */
+/* CSR kernels (values double, indices size_t as in CSRMatrix.h:70-72)                                            */
+/* ------------------------------------------------------------------------------------------------------------- */
+/* EwBinaryMat<CSR,CSR,Dense> for MUL (EwBinaryMat.h:254-317): rhs has the shape of lhs or is a row/column vector;
+ * entries where rhs is exactly 0 are dropped.  Outputs sized for nnz(lhs). */
+int orc_csr_ewmul_dense_f64(const double *vals, const uint64_t *cidx, const uint64_t *roff, int64_t rows, int64_t cols,
+                            const double *rhs, int64_t rr, int64_t rc, double *ovals, uint64_t *ocidx, uint64_t *oroff,
+                            int64_t *out_nnz) {
+    if ((rows != rr && rr != 1) || (cols != rc && rc != 1))
+        return 1;
+    oroff[0] = 0;
+    for (int64_t r = 0; r < rows; r++) {
+        uint64_t pos = oroff[r];
+        const int64_t rhs_row = (rr == 1) ? 0 : r;
+        for (uint64_t i = roff[r]; i < roff[r + 1]; i++) {
+            const int64_t rhs_col = (rc == 1) ? 0 : (int64_t)cidx[i];
+            const double rv = rhs[rhs_row * rc + rhs_col];
+            if (rv != 0) {
+                ovals[pos] = vals[i] * rv;
+                ocidx[pos] = cidx[i];
+                pos++;
+            }
+        }
+        oroff[r + 1] = pos;
+    }
+    *out_nnz = (int64_t)oroff[rows];
+    return 0;
+}
+/* AggRow<Dense,CSR> (AggRow.h:178-238) for the pure reductions: aggAllArray over the row's stored values, then one
+ * implicit zero if the op is not sparse-safe and the row is not full (AggOpCode.h:84-100). */
+int orc_csr_agg_row_f64(int op, const double *vals, const uint64_t *roff, int64_t rows, int64_t cols, double *res) {
+    const int bop = agg_bin_op(op);
+    if (bop < 0 || op == A_MEAN || op == A_STDDEV || op == A_VAR)
+        return 1;
+    double neutral = 0;
+    if (op == A_PROD) neutral = 1;
+    if (op == A_MIN) neutral = INFINITY;
+    if (op == A_MAX) neutral = -INFINITY;
+    const int sparse_safe = (op == A_SUM);
+    for (int64_t r = 0; r < rows; r++) {
+        const size_t n = (size_t)(roff[r + 1] - roff[r]);
+        double agg = agg_all_array_f64(bop, vals + roff[r], n, neutral);
+        if (!sparse_safe && (int64_t)n < cols)
+            agg = bin_f64(bop, agg, 0);
+        res[r] = agg;
+    }
+    return 0;
+}
+/* Gemv<Dense,CSR,Dense> (Gemv.h:79-117): res = mat @ vec for a dense vec with vcols columns */
+int orc_csr_gemv_f64(const double *vals, const uint64_t *cidx, const uint64_t *roff, int64_t rows, const double *vec,
+                     int64_t vcols, double *res) {
+    memset(res, 0, sizeof(double) * (size_t)(rows * vcols));
+    for (int64_t r = 0; r < rows; r++)
+        for (uint64_t i = roff[r]; i < roff[r + 1]; i++)
+            for (int64_t j = 0; j < vcols; j++)
+                res[r * vcols + j] += vals[i] * vec[(int64_t)cidx[i] * vcols + j];
+    return 0;
+}

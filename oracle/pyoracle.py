@@ -214,3 +214,57 @@ def _seq(lib, prefix, start, end, inc):
 
 def seq(start, end, inc):
     return _seq(_lib, "orc", start, end, inc)
+
+
+def _csr_arrays(m):
+    """(values f64, colIdxs u64, rowOffsets u64, rows, cols) from a scipy CSR matrix or an equivalent tuple."""
+    if isinstance(m, tuple):
+        vals, cols_, offs, rows, cols = m
+    else:
+        m = m.tocsr()
+        m.sort_indices()
+        vals, cols_, offs, (rows, cols) = m.data, m.indices, m.indptr, m.shape
+    return (np.ascontiguousarray(vals, dtype=np.float64), np.ascontiguousarray(cols_, dtype=np.uint64),
+            np.ascontiguousarray(offs, dtype=np.uint64), int(rows), int(cols))
+
+
+def _csr_ewmul(lib, prefix, m, rhs):
+    vals, cidx, roff, rows, cols = _csr_arrays(m)
+    rhs = _mat(np.ascontiguousarray(rhs, dtype=np.float64))
+    ov, oc, oo = np.empty_like(vals), np.empty_like(cidx), np.empty_like(roff)
+    n = C.c_int64()
+    f = getattr(lib, f"{prefix}_csr_ewmul_dense_f64")
+    if prefix == "orc":
+        f.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, i64, i64, C.c_void_p, i64, i64, C.c_void_p, C.c_void_p,
+                      C.c_void_p, C.c_void_p]
+        _chk(f(_p(vals), _p(cidx), _p(roff), rows, cols, _p(rhs), rhs.shape[0], rhs.shape[1], _p(ov), _p(oc), _p(oo),
+               C.byref(n)))
+    else:
+        f.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, i64, i64, i64, C.c_void_p, i64, i64, C.c_void_p, C.c_void_p,
+                      C.c_void_p, C.c_void_p]
+        _chk(f(_p(vals), _p(cidx), _p(roff), rows, cols, vals.size, _p(rhs), rhs.shape[0], rhs.shape[1], _p(ov),
+               _p(oc), _p(oo), C.byref(n)))
+    return (ov[:n.value].copy(), oc[:n.value].copy(), oo, rows, cols)
+
+
+def ewMulCsrDense(m, rhs):
+    return _csr_ewmul(_lib, "orc", m, rhs)
+
+
+def aggRowCsr(op, m):
+    vals, cidx, roff, rows, cols = _csr_arrays(m)
+    res = np.empty((rows, 1))
+    f = _lib.orc_csr_agg_row_f64
+    f.argtypes = [C.c_int, C.c_void_p, C.c_void_p, i64, i64, C.c_void_p]
+    _chk(f(int(op), _p(vals), _p(roff), rows, cols, _p(res)))
+    return res
+
+
+def matMulCsrDense(m, rhs):
+    vals, cidx, roff, rows, cols = _csr_arrays(m)
+    rhs = np.ascontiguousarray(_mat(np.asarray(rhs, dtype=np.float64)))
+    res = np.empty((rows, rhs.shape[1]))
+    f = _lib.orc_csr_gemv_f64
+    f.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, i64, C.c_void_p, i64, C.c_void_p]
+    _chk(f(_p(vals), _p(cidx), _p(roff), rows, _p(rhs), rhs.shape[1], _p(res)))
+    return res

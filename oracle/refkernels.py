@@ -135,3 +135,27 @@ def rand(rows, cols, lo, hi, sparsity, seed):
     f = _f("ref_rand_f64", [i64, i64, C.c_double, C.c_double, C.c_double, i64, vp])
     _chk(f(rows, cols, float(lo), float(hi), float(sparsity), int(seed), _p(res)))
     return res
+
+
+def ewMulCsrDense(m, rhs):
+    return _o._csr_ewmul(_lib, "ref", m, rhs)
+
+
+def aggRowCsr(op, m):
+    vals, cidx, roff, rows, cols = _o._csr_arrays(m)
+    res = np.empty((rows, 1))
+    f = _f("ref_csr_agg_row_f64", [C.c_int, vp, vp, vp, i64, i64, i64, vp])
+    _chk(f(int(op), _p(vals), _p(cidx), _p(roff), rows, cols, vals.size, _p(res)))
+    return res
+
+
+def matMulCsrDense(m, rhs):
+    vals, cidx, roff, rows, cols = _o._csr_arrays(m)
+    rhs = np.ascontiguousarray(_mat(np.asarray(rhs, dtype=np.float64)))
+    res = np.empty((rows, rhs.shape[1]))
+    f = _f("ref_csr_gemv_f64", [vp, vp, vp, i64, i64, i64, vp, i64, vp])
+    _chk(f(_p(vals), _p(cidx), _p(roff), rows, cols, vals.size, _p(rhs), rhs.shape[1], _p(res)))
+    return res
+
+
+available()  # load the library at import when it exists
