@@ -131,6 +131,7 @@ def run_ours(args) -> dict:
         torch.cuda.set_device(local_rank)
     comm = Comm.from_env("nccl")
     ctx = K.Context(local_rank)
+    comm.init_device(ctx)  # NCCL communicator inside the runtime: partials are combined on the device
     rows, cols = args.rows, COLS
     n_total = rows * world
 

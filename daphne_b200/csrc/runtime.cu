@@ -18,6 +18,7 @@ void ctx_release(db2_context *ctx) {
     if (ctx->refs.fetch_sub(1) != 1)
         return;
     bind_device(ctx);
+    db2_comm_destroy(ctx);
     cudaStreamSynchronize(ctx->stream);
     if (ctx->scratch)
         ctx_free(ctx, ctx->scratch, ctx->scratch_bytes);

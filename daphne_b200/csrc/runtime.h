@@ -33,6 +33,9 @@ struct db2_context {
     // device status word for domain errors + pinned host mirror
     int32_t *dev_status = nullptr;
     int32_t *host_status = nullptr;
+    // cross-GPU combine (comm.cu): this context's rank among `world` row shards and its NCCL communicator
+    int rank = 0, world = 1;
+    void *comm = nullptr;
     std::mutex mu;
     db2_stats stats{};
     // the handle returned by db2_context_create holds one reference, every pooled buffer another: a context is torn

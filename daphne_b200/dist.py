@@ -74,6 +74,55 @@ class Comm:
         self._dist.all_gather(out, t)
         return torch.cat(out, dim=0).cpu().numpy()
 
+    def allgather_ragged(self, a: np.ndarray) -> np.ndarray:
+        """Concatenates row shards of possibly different heights in rank order (host side, for results)."""
+        if self.world == 1:
+            return a
+        gathered = [None] * self.world
+        self._dist.all_gather_object(gathered, np.ascontiguousarray(a))
+        return np.concatenate(gathered, axis=0)
+
+    # ---- device-resident collectives through the runtime's NCCL communicator ----
+    def init_device(self, ctx) -> None:
+        """Gives the runtime context an NCCL communicator; the 128-byte id travels over torch.distributed."""
+        import ctypes as C
+
+        import torch
+
+        from .lib import check, lib
+        if self.world == 1:
+            return
+        ident = torch.zeros(128, dtype=torch.uint8)
+        if self.rank == 0:
+            buf = (C.c_ubyte * 128)()
+            check(lib.db2_comm_unique_id(buf))
+            ident = torch.tensor(list(buf), dtype=torch.uint8)
+        if self.backend == "nccl":
+            ident = ident.cuda()
+        self._dist.broadcast(ident, src=0)
+        raw = bytes(ident.cpu().tolist())
+        check(lib.db2_comm_init(ctx.handle, self.rank, self.world, raw))
+        self._device_ctx = ctx
+
+    def device_collectives(self, ctx) -> bool:
+        return ctx is not None and getattr(self, "_device_ctx", None) is ctx
+
+    def allreduce_device(self, ctx, m, combine: int = COMBINE_ADD) -> None:
+        from .lib import check, lib
+        check(lib.db2_allreduce(ctx.handle, m.handle, int(combine)))
+
+    def allgather_rows(self, ctx, m, k=None):
+        """Concatenates equally sized row shards in rank order."""
+        if self.device_collectives(ctx):
+            import ctypes as C
+
+            from . import kernels as K
+            from .lib import check, lib
+            h = C.c_void_p()
+            check(lib.db2_allgather_rows(ctx.handle, m.handle, C.byref(h)))
+            return K.DenseMatrix(ctx, h)
+        return k.DenseMatrix.from_numpy(ctx, self.allgather_numpy(m.to_numpy()))
+
     def barrier(self):
         if self.world > 1:
             self._dist.barrier()

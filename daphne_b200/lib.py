@@ -87,6 +87,12 @@ _SIGS = {
     "db2_context_stream": (vp, [vp]),
     "db2_context_sync": (i32, [vp]),
     "db2_context_stats": (i32, [vp, vp]),
+    "db2_comm_unique_id": (i32, [vp]),
+    "db2_comm_init": (i32, [vp, i32, i32, vp]),
+    "db2_comm_destroy": (i32, [vp]),
+    "db2_comm_info": (i32, [vp, _P(i32), _P(i32)]),
+    "db2_allreduce": (i32, [vp, vp, i32]),
+    "db2_allgather_rows": (i32, [vp, vp, _P(vp)]),
     "db2_matrix_create": (i32, [vp, i32, i64, i64, i32, _P(vp)]),
     "db2_matrix_wrap_host": (i32, [vp, i32, i64, i64, i64, vp, _P(vp)]),
     "db2_matrix_wrap_device": (i32, [vp, i32, i64, i64, i64, vp, _P(vp)]),
@@ -127,7 +133,8 @@ _SIGS = {
 class Stats(C.Structure):
     """db2_stats (include/daphne_b200.h)."""
     _fields_ = [(n, C.c_uint64) for n in ("h2d_bytes", "d2h_bytes", "d2d_bytes", "allocs", "alloc_bytes", "frees",
-                                          "launches", "live_bytes", "peak_bytes")]
+                                          "launches", "live_bytes", "peak_bytes", "collectives",
+                                          "collective_bytes")]
 
 
 def declare(sigs: dict) -> None:

@@ -73,26 +73,36 @@ class _NoProbe:
         return contextlib.nullcontext()
 
 
-def _allreduce_matrix(ctx: K.Context, m: K.DenseMatrix, comm: Optional[Comm], combine=COMBINE_ADD) -> K.DenseMatrix:
-    """Combines a small ADD/MIN/MAX partial (1 x c, c x c, 1 x 1) across the row shards."""
+def _allreduce_matrix(ctx, m, comm: Optional[Comm], combine=COMBINE_ADD, k=None):
+    """Combines a small ADD/MIN/MAX partial (1 x c, c x c, 1 x 1) across the row shards: in place on the device with
+    NCCL when the context has a communicator, through the host otherwise (CPU tests of the sharding logic)."""
     if comm is None or comm.world == 1:
         return m
+    if comm.device_collectives(ctx):
+        comm.allreduce_device(ctx, m, combine)
+        return m
     host = comm.allreduce_numpy(m.to_numpy(), combine)
-    return K.DenseMatrix.from_numpy(ctx, host)
+    return (k or K).DenseMatrix.from_numpy(ctx, host)
+
+
+def _allreduce_scalar(ctx, x: float, comm: Optional[Comm], combine=COMBINE_ADD) -> float:
+    if comm is None or comm.world == 1:
+        return float(x)
+    return float(comm.allreduce_numpy(np.array([x], dtype=np.float64), combine)[0])
 
 
 @dataclass
 class StandardiseResult:
-    mu: K.DenseMatrix        # 1 x c   column means
-    sd: K.DenseMatrix        # 1 x c   column standard deviations (population)
-    r: K.DenseMatrix         # n x 1   rowSums(Z^2)
+    mu: object        # 1 x c   column means
+    sd: object        # 1 x c   column standard deviations (population)
+    r: object         # n x 1   rowSums(Z^2)
     s: float                 #         sum(r) over ALL shards
-    row_max: K.DenseMatrix   # n x 1   rowMaxs(Z)
-    row_idx_max: K.DenseMatrix  # n x 1 (uint64) idxMax per row of Z
+    row_max: object   # n x 1   rowMaxs(Z)
+    row_idx_max: object  # n x 1 (uint64) idxMax per row of Z
 
 
-def standardise_aggregate(ctx: K.Context, X: K.DenseMatrix, n_total: Optional[int] = None,
-                          comm: Optional[Comm] = None, probe=None) -> StandardiseResult:
+def standardise_aggregate(ctx, X, n_total: Optional[int] = None, comm: Optional[Comm] = None, probe=None,
+                          kernels=None) -> StandardiseResult:
     """Column standardisation and aggregation:
 
         mu = mean(X, 1); sd = sqrt(var(X, 1)); Z = (X - mu) / sd;
@@ -101,14 +111,15 @@ def standardise_aggregate(ctx: K.Context, X: K.DenseMatrix, n_total: Optional[in
     mean/var are issued as their ADD-combinable forms (column sums divided by the global row count, then column sums
     of squared deviations from the global mean) so that row shards on several GPUs produce the global statistics;
     on one GPU this is the arithmetic of AggCol's MEAN/VAR (src/runtime/local/kernels/AggCol.h:146-173)."""
+    K = kernels or globals()["K"]
     n = X.rows if n_total is None else n_total
     probe = probe or _NoProbe()
-    s1 = _allreduce_matrix(ctx, K.aggCol(A.SUM, X), comm)
+    s1 = _allreduce_matrix(ctx, K.aggCol(A.SUM, X), comm, k=K)
     mu = K.ewBinaryObjSca(B.DIV, s1, float(n))
     d = K.ewBinaryMat(B.SUB, X, mu)
     d2 = K.ewBinaryObjSca(B.POW, d, 2.0)
     d.free()
-    v = _allreduce_matrix(ctx, K.aggCol(A.SUM, d2), comm)
+    v = _allreduce_matrix(ctx, K.aggCol(A.SUM, d2), comm, k=K)
     d2.free()
     var = K.ewBinaryObjSca(B.DIV, v, float(n))
     sd = K.ewUnaryMat(U.SQRT, var)
@@ -124,34 +135,33 @@ def standardise_aggregate(ctx: K.Context, X: K.DenseMatrix, n_total: Optional[in
     with probe.section("fused_row_kernel (Z=(X-mu)/sd; rowSums(Z^2), rowMaxs(Z), idxMax(Z))",
                        X.rows * (X.cols * 8 + 24)):
         r.device_ptr()  # the three row aggregations are produced by one pass over X
-    s_local = K.aggAll(A.SUM, r)
-    s = float(s_local) if comm is None or comm.world == 1 else float(
-        comm.allreduce_numpy(np.array([s_local], dtype=np.float64))[0])
+    s = _allreduce_scalar(ctx, K.aggAll(A.SUM, r), comm)
     return StandardiseResult(mu, sd, r, s, m, i)
 
 
 @dataclass
 class NormalEquationsResult:
-    A: K.DenseMatrix      # d x d   t(X) X + lambda I (global)
-    b: K.DenseMatrix      # d x 1   t(X) y (global)
-    beta: K.DenseMatrix   # d x 1   solve(A, b)
+    A: object      # d x d   t(X) X + lambda I (global)
+    b: object      # d x 1   t(X) y (global)
+    beta: object   # d x 1   solve(A, b)
 
 
-def normal_equations(ctx: K.Context, X: K.DenseMatrix, y: K.DenseMatrix, lam: float = 0.001,
-                     comm: Optional[Comm] = None, probe=None) -> NormalEquationsResult:
+def normal_equations(ctx, X, y, lam: float = 0.001, comm: Optional[Comm] = None, probe=None,
+                     kernels=None) -> NormalEquationsResult:
     """Linear regression by the normal equations (lmDS, scripts/algorithms/lmDS_.daph:98-112):
 
         A = t(X) @ X + diagMatrix(fill(lambda, ncol(X), 1));  b = t(X) @ y;  beta = solve(A, b);
 
     t(X) @ X lowers to syrk and t(X) @ y to gemv (PhyOperatorSelectionPass.cpp:54-71); both are ADD-combined over the
     row shards."""
+    K = kernels or globals()["K"]
     probe = probe or _NoProbe()
     d = X.cols
     with probe.section("gemm_f64_kernel syrk t(X)X", X.rows * d * 8):
         xtx = K.syrk(X, True)
     xty = K.gemv(X, y)
-    xtx = _allreduce_matrix(ctx, xtx, comm)
-    xty = _allreduce_matrix(ctx, xty, comm)
+    xtx = _allreduce_matrix(ctx, xtx, comm, k=K)
+    xty = _allreduce_matrix(ctx, xty, comm, k=K)
     A = K.ewBinaryMat(B.ADD, xtx, K.diagMatrix(K.fill(ctx, lam, d, 1)))
     beta = K.solve(A, xty)
     return NormalEquationsResult(A, xty, beta)
@@ -159,12 +169,11 @@ def normal_equations(ctx: K.Context, X: K.DenseMatrix, y: K.DenseMatrix, lam: fl
 
 @dataclass
 class KMeansResult:
-    C: K.DenseMatrix        # k x d centroids after the last update (global)
-    assign: K.DenseMatrix   # n x 1 (int64) cluster of every local row in the last iteration
+    C: object        # k x d centroids after the last update (global)
+    assign: object   # n x 1 (int64) cluster of every local row in the last iteration
 
 
-def kmeans(ctx: K.Context, X: K.DenseMatrix, C0: K.DenseMatrix, iterations: int = 10,
-           comm: Optional[Comm] = None) -> KMeansResult:
+def kmeans(ctx, X, C0, iterations: int = 10, comm: Optional[Comm] = None, kernels=None) -> KMeansResult:
     """K-means assignment + update:
 
         xs = sum(X ^ 2, 0);
@@ -173,6 +182,7 @@ def kmeans(ctx: K.Context, X: K.DenseMatrix, C0: K.DenseMatrix, iterations: int 
 
     Ties in idxMin go to the lowest index (AggRow.h:71-83).  The centroid sums t(P) @ X and the counts sum(P, 1) are
     ADD-combined over the row shards."""
+    K = kernels or globals()["K"]
     n, k = X.rows, C0.rows
     xs = K.aggRow(A.SUM, K.ewBinaryObjSca(B.POW, X, 2.0))
     rows = K.seq(ctx, 0, n - 1, 1, dtype=np.int64)
@@ -185,8 +195,8 @@ def kmeans(ctx: K.Context, X: K.DenseMatrix, C0: K.DenseMatrix, iterations: int 
         D.free()
         xc.free()
         P = K.ctable(rows, assign, 1.0, n, k)
-        sums = _allreduce_matrix(ctx, K.matMul(P, X, True, False), comm)
-        counts = _allreduce_matrix(ctx, K.aggCol(A.SUM, P), comm)
+        sums = _allreduce_matrix(ctx, K.matMul(P, X, True, False), comm, k=K)
+        counts = _allreduce_matrix(ctx, K.aggCol(A.SUM, P), comm, k=K)
         P.free()
         Cm = K.ewBinaryMat(B.DIV, sums, K.transpose(counts))
     return KMeansResult(Cm, assign)
@@ -194,12 +204,12 @@ def kmeans(ctx: K.Context, X: K.DenseMatrix, C0: K.DenseMatrix, iterations: int 
 
 @dataclass
 class ComponentsResult:
-    c: K.DenseMatrix    # n_local x 1 component label of every local vertex
+    c: object    # n_local x 1 component label of every local vertex
     iterations: int
 
 
-def connected_components(ctx: K.Context, G: K.CSRMatrix, maxi: int = 1000, comm: Optional[Comm] = None,
-                         row_block: Optional[tuple] = None) -> ComponentsResult:
+def connected_components(ctx, G, maxi: int = 1000, comm: Optional[Comm] = None, row_block: Optional[tuple] = None,
+                         kernels=None) -> ComponentsResult:
     """Connected components by label propagation (test/api/cli/algorithms/components.daphne:14-26):
 
         c = seq(1, n, 1);  while (diff > 0 && iter <= maxi):
@@ -208,6 +218,7 @@ def connected_components(ctx: K.Context, G: K.CSRMatrix, maxi: int = 1000, comm:
     G is the row shard [row_block) of the symmetric 0/1 adjacency matrix (all n columns); every rank needs the whole
     label vector for the gather G * t(c), so the updated shard is all-gathered each iteration and the change count is
     ADD-combined."""
+    K = kernels or globals()["K"]
     n = G.cols
     lo, hi = row_block if row_block is not None else (0, G.rows)
     c_full = K.seq(ctx, 1.0, float(n), 1.0)
@@ -216,10 +227,9 @@ def connected_components(ctx: K.Context, G: K.CSRMatrix, maxi: int = 1000, comm:
     while diff > 0.0 and it <= maxi:
         prod = K.ewMulCsrDense(G, K.transpose(c_full))
         u = K.ewBinaryMat(B.MAX, K.aggRowCsr(A.MAX, prod), c_loc)
-        diff = float(K.aggAll(A.SUM, K.ewBinaryMat(B.NEQ, u, c_loc)))
+        diff = _allreduce_scalar(ctx, K.aggAll(A.SUM, K.ewBinaryMat(B.NEQ, u, c_loc)), comm)
         if comm is not None and comm.world > 1:
-            diff = float(comm.allreduce_numpy(np.array([diff]))[0])
-            c_full = K.DenseMatrix.from_numpy(ctx, comm.allgather_numpy(u.to_numpy()))
+            c_full = comm.allgather_rows(ctx, u, k=K)
             c_loc = c_full.slice_rows(lo, hi)
         else:
             c_full = u

@@ -221,6 +221,7 @@ typedef struct db2_stats {
     uint64_t allocs, alloc_bytes, frees;      /* pooled device allocations                          */
     uint64_t launches;                        /* kernels launched through this context              */
     uint64_t live_bytes, peak_bytes;          /* device bytes held by matrices / scratch            */
+    uint64_t collectives, collective_bytes;   /* cross-GPU combines issued through this context     */
 } db2_stats;
 
 int db2_context_create(int device, db2_context **ctx);
@@ -229,6 +230,20 @@ int db2_context_device(const db2_context *ctx, int *device);
 void *db2_context_stream(db2_context *ctx);
 int db2_context_sync(db2_context *ctx);
 int db2_context_stats(db2_context *ctx, db2_stats *out);
+
+/* Row-sharded multi-GPU execution: one process (and context) per GPU.  rank 0 creates an id with
+ * db2_comm_unique_id, every rank passes the same 128 bytes to db2_comm_init (exchange them with any host-side
+ * mechanism).  The reference has no multi-GPU path (device 0 is hard-coded, e.g. kernels/CUDA/AggRow.cu:113) and
+ * combines ADD/MIN/MAX partials on the host under a mutex (src/runtime/local/vectorized/Tasks.cpp:51-82); here they
+ * are combined on the device with one NCCL all-reduce on the context's stream. */
+int db2_comm_unique_id(void *id128);
+int db2_comm_init(db2_context *ctx, int rank, int world, const void *id128);
+int db2_comm_destroy(db2_context *ctx);
+int db2_comm_info(const db2_context *ctx, int *rank, int *world);
+/* in-place combine of a small contiguous partial over all ranks; combine = DB2_COMBINE_ADD / MIN / MAX */
+int db2_allreduce(db2_context *ctx, db2_matrix *m, int combine);
+/* concatenation of equally shaped row shards in rank order */
+int db2_allgather_rows(db2_context *ctx, db2_matrix *local, db2_matrix **full);
 
 /* device-only matrix (DataObjectFactory::create<DenseMatrix<VT>>(rows, cols, zero, &alloc_desc)) */
 int db2_matrix_create(db2_context *ctx, int dtype, int64_t rows, int64_t cols, int zero, db2_matrix **out);
