@@ -31,6 +31,9 @@ SEED = 2
 # algorithmic bytes per row of the whole pipeline with nothing materialised: statistics passes read the row twice,
 # the normalise+aggregate pass once more is folded in the survey's minimum of 2 reads + 3 results = 536 B/row
 PIPELINE_MIN_BYTES_PER_ROW = 2 * COLS * 8 + 24
+# DRAM traffic of the dominant kernel per row, from the ncu capture of the 2,097,152-row case
+# (dram__bytes_read.sum + dram__bytes_write.sum = 536.92 MB + 44.38 MB; profiles/fused_row_ct_kernel_*.md)
+DOMINANT_TRAFFIC_BYTES_PER_ROW = (536.92e6 + 44.38e6) / 2_097_152
 
 
 def measured_peaks():
@@ -52,11 +55,12 @@ class ClockSampler:
         self.proc = None
         self.lines = []
         self.t = None
+        self.t0 = self.t1 = None
 
     def start(self):
         try:
             self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
-                                          "-lms", "100", "-i", str(self.gpu)], stdout=subprocess.PIPE,
+                                          "-lms", "20", "-i", str(self.gpu)], stdout=subprocess.PIPE,
                                          stderr=subprocess.DEVNULL, text=True)
         except OSError:
             self.proc = None
@@ -66,7 +70,13 @@ class ClockSampler:
 
     def _read(self):
         for ln in self.proc.stdout:
-            self.lines.append(ln.strip())
+            self.lines.append((time.perf_counter(), ln.strip()))
+
+    def mark_start(self):
+        self.t0 = time.perf_counter()
+
+    def mark_stop(self):
+        self.t1 = time.perf_counter()
 
     def stop(self) -> dict:
         if self.proc is None:
@@ -77,7 +87,12 @@ class ClockSampler:
         except subprocess.TimeoutExpired:
             self.proc.kill()
         sm, mx, reasons = [], [], set()
-        for ln in self.lines:
+        inside = [ln for (t, ln) in self.lines if self.t0 is not None and self.t0 <= t <= (self.t1 or t)]
+        window = "timed region"
+        if len(inside) < 3:  # a timed region of a few ms holds fewer than three 20 ms samples: add the warm-up
+            inside = [ln for (_, ln) in self.lines]
+            window = "warm-up + timed region"
+        for ln in inside:
             f = [x.strip() for x in ln.split(",")]
             if len(f) < 9:
                 continue
@@ -90,7 +105,7 @@ class ClockSampler:
                 if v.lower().startswith("active"):
                     reasons.add(name)
         return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
-                "reasons": sorted(reasons), "samples": len(sm)}
+                "reasons": sorted(reasons), "samples": len(sm), "window": window}
 
 
 def make_input(rows: int, cols: int, seed: int, out: np.ndarray) -> None:
@@ -155,11 +170,13 @@ def run_ours(args) -> dict:
     Xd = K.DenseMatrix.from_numpy(ctx, host)
     Xd.device_ptr()  # H2D once, outside the timed region
     ctx.sync()
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    time.sleep(0.3)  # nvidia-smi needs a moment before its first sample
     for _ in range(args.warmup):
         res = pipelines.standardise_aggregate(ctx, Xd, n_total, comm)
     sync_all()
-    sampler = ClockSampler(local_rank)
-    sampler.start()
+    sampler.mark_start()
     launches0 = lib.db2_launch_count()
     e0, e1 = ev(), ev()
     if probe:
@@ -170,6 +187,7 @@ def run_ours(args) -> dict:
             pipelines.standardise_aggregate(ctx, Xd, n_total, comm)
     check(lib.db2_event_record(e1, stream))
     sync_all()
+    sampler.mark_stop()
     ms = C.c_float()
     check(lib.db2_event_elapsed_ms(e0, e1, C.byref(ms)))
     launches = lib.db2_launch_count() - launches0
@@ -229,7 +247,8 @@ def run_ours(args) -> dict:
     }
     if dom:
         line["roofline"] = {"bound": "hbm", "kernel": dom["name"], "achieved": dom["gbs"], "peak": peak,
-                            "unit": "GB/s", "frac": dom["gbs"] / peak, "traffic": dom.get("traffic"),
+                            "unit": "GB/s", "frac": dom["gbs"] / peak,
+                            "traffic": rows * DOMINANT_TRAFFIC_BYTES_PER_ROW if cols == COLS else None,
                             "peak_kind": peak_kind, "launches_timed": dom["launches"],
                             "avg_ms": dom["avg_ms"], "algorithmic_bytes_per_launch": dom["bytes"]}
     if rank == 0:
@@ -278,8 +297,8 @@ def run_reference(args) -> dict:
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=10)
-    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--rows", type=int, default=ROWS_PER_GPU, help="rows per GPU (default: the 4 GiB configuration)")
     ap.add_argument("--cpu-rows", type=int, default=1 << 20, help="rows of the bounded CPU-baseline sample")

@@ -409,18 +409,24 @@ template <typename VT, int KIND>
 __global__ void agg_col_final_kernel(const VT *__restrict__ part_v, const int64_t *__restrict__ part_i, int nparts,
                                      int64_t cols, int64_t count, const VT *__restrict__ first_row, int out_mode,
                                      void *__restrict__ res) {
-    const int64_t c = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    // one warp per column: lane l folds partials l, l + 32, ... in order, then a fixed shuffle tree
+    const int lane = threadIdx.x % 32;
+    const int64_t c = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) / 32;
     if (c >= cols)
         return;
     Acc<VT, KIND> t;
-    t.v = part_v[c];
-    t.i = (KIND == K_MIN || KIND == K_MAX) ? part_i[c] : NO_IDX;
-    for (int p = 1; p < nparts; p++) {
+    t.init();
+    for (int p = lane; p < nparts; p += 32) {
         Acc<VT, KIND> o;
         o.v = part_v[(int64_t)p * cols + c];
         o.i = (KIND == K_MIN || KIND == K_MAX) ? part_i[(int64_t)p * cols + c] : NO_IDX;
-        t.merge(o);
+        t.merge(o); // lanes start from the neutral element
     }
+#pragma unroll
+    for (int m = 16; m >= 1; m >>= 1)
+        t.merge(shfl_xor_acc<VT, KIND>(t, m));
+    if (lane != 0)
+        return;
     if constexpr (KIND == K_MIN || KIND == K_MAX) {
         const VT first = first_row[c];
         if (first != first || t.i == NO_IDX) {
@@ -481,9 +487,9 @@ static int agg_col_pass(const VT *arg, int64_t rows, int64_t cols, int64_t ld, c
     else
         agg_col_partial_kernel<VT, KIND, 1><<<grid, block, p.smem, st>>>(arg, rows, cols, ld, mean, part_v, part_i);
     DB2_TRY(after_launch("agg_col_partial_kernel"));
-    const int fb = 128;
+    const int fb = 256; // 8 columns (warps) per block
     agg_col_final_kernel<VT, KIND>
-        <<<(unsigned)((cols + fb - 1) / fb), fb, 0, st>>>(part_v, part_i, p.gx, cols, count, arg, out_mode, res);
+        <<<(unsigned)((cols * 32 + fb - 1) / fb), fb, 0, st>>>(part_v, part_i, p.gx, cols, count, arg, out_mode, res);
     return after_launch("agg_col_final_kernel");
 }
 

@@ -392,13 +392,19 @@ __global__ void __launch_bounds__(CT_THREADS)
 
 __global__ void col_sum_final_kernel(const double *__restrict__ part, int nparts, int64_t cols, int64_t count,
                                      int mean, double *__restrict__ res) {
-    const int64_t c = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    // one warp per column: lane l adds partials l, l + 32, ... in order, then a fixed shuffle tree (deterministic)
+    const int lane = threadIdx.x % 32;
+    const int64_t c = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) / 32;
     if (c >= cols)
         return;
-    double a = part[c];
-    for (int i = 1; i < nparts; i++)
-        a = __dadd_rn(a, part[(int64_t)i * cols + c]);
-    res[c] = mean ? __ddiv_rn(a, (double)count) : a;
+    double a = 0.0;
+    for (int i = lane; i < nparts; i += 32)
+        a = (i == lane) ? part[(int64_t)i * cols + c] : __dadd_rn(a, part[(int64_t)i * cols + c]);
+#pragma unroll
+    for (int m = 16; m >= 1; m >>= 1)
+        a = __dadd_rn(a, shfl_xor(a, m));
+    if (lane == 0)
+        res[c] = mean ? __ddiv_rn(a, (double)count) : a;
 }
 
 template <typename ChainT>
@@ -417,7 +423,7 @@ static int launch_col_sum(const FusedProgram &prog, int mean, void *res, void *s
     double *part = static_cast<double *>(scratch);
     fused_col_sum_ct_kernel<ChainT><<<dim3(gx, gy), dim3(tx, ty), 0, st>>>(prog, part);
     DB2_TRY(after_launch("fused_col_sum_ct_kernel"));
-    col_sum_final_kernel<<<(unsigned)((prog.cols + 127) / 128), 128, 0, st>>>(part, gx, prog.cols, prog.rows, mean,
+    col_sum_final_kernel<<<(unsigned)((prog.cols * 32 + 255) / 256), 256, 0, st>>>(part, gx, prog.cols, prog.rows, mean,
                                                                             static_cast<double *>(res));
     return after_launch("col_sum_final_kernel");
 }
