@@ -388,8 +388,12 @@ int db2_matrix_to_host(db2_matrix *m, void *dst, int64_t dst_ld) {
     if (m->dev_valid) {
         db2_context *ctx = m->ctx;
         bind_device(ctx);
-        DB2_CUDA(cudaMemcpy2DAsync(dst, (size_t)dst_ld * es, m->dev_ptr(), (size_t)m->dev_ld * es, (size_t)m->cols * es,
-                                   (size_t)m->rows, cudaMemcpyDeviceToHost, ctx->stream));
+        if ((dst_ld == m->cols && m->dev_ld == m->cols) || m->rows == 1) // contiguous: one linear copy
+            DB2_CUDA(cudaMemcpyAsync(dst, m->dev_ptr(), (size_t)m->rows * m->cols * es, cudaMemcpyDeviceToHost,
+                                     ctx->stream));
+        else
+            DB2_CUDA(cudaMemcpy2DAsync(dst, (size_t)dst_ld * es, m->dev_ptr(), (size_t)m->dev_ld * es,
+                                       (size_t)m->cols * es, (size_t)m->rows, cudaMemcpyDeviceToHost, ctx->stream));
         DB2_CUDA(cudaStreamSynchronize(ctx->stream));
         std::lock_guard<std::mutex> lock(ctx->mu);
         ctx->stats.d2h_bytes += (uint64_t)m->rows * m->cols * es;
