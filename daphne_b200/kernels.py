@@ -371,3 +371,36 @@ def matMulCsrDense(lhs: CSRMatrix, rhs: DenseMatrix, ctx: Optional[Context] = No
     h = C.c_void_p()
     check(lib.db2_matMulCsrDense(ctx.handle, C.byref(h), lhs.handle, rhs.handle))
     return _res(ctx, h)
+
+
+PIPELINE_FN = C.CFUNCTYPE(None, C.POINTER(C.POINTER(C.c_void_p)), C.POINTER(C.c_void_p), C.c_void_p)
+
+
+def vectorizedPipeline(ctx: Context, inputs, splits, combines, body, batch_rows: int = 0):
+    """VectorizedPipeline.h:35-69.  `body(ins) -> outs` receives DenseMatrix handles for the (row slices of the)
+    inputs and returns one DenseMatrix per output; like the compiled body of the reference it owns its inputs (they
+    are released when the handles go out of scope) and hands its results over to the scheduler."""
+    n_in, n_out = len(inputs), len(combines)
+    keep = []
+
+    def trampoline(outs_pp, ins_p, _ctx):
+        ins = [DenseMatrix(ctx, C.c_void_p(ins_p[i])) for i in range(n_in)]
+        outs = body(ins)
+        assert len(outs) == n_out
+        for o, m in enumerate(outs):
+            outs_pp[o][0] = m.handle.value
+            m._h = C.c_void_p()  # ownership moves to the scheduler
+        for m in ins:
+            m.free()
+        keep.append(outs)
+
+    cb = PIPELINE_FN(trampoline)
+    out_h = (C.c_void_p * n_out)()
+    in_h = (C.c_void_p * n_in)(*[m.handle.value for m in inputs])
+    sp = (C.c_int64 * n_in)(*[int(x) for x in splits])
+    cm = (C.c_int64 * n_out)(*[int(x) for x in combines])
+    neg = (C.c_int64 * n_out)(*([-1] * n_out))
+    scal = (C.c_int * n_in)(*([0] * n_in))
+    check(lib.db2_vectorizedPipeline(ctx.handle, out_h, n_out, scal, in_h, n_in, neg, neg, sp, cm,
+                                     C.cast(cb, C.c_void_p), int(batch_rows)))
+    return [DenseMatrix(ctx, C.c_void_p(out_h[o])) for o in range(n_out)]

@@ -290,6 +290,26 @@ int db2_ctable(db2_context *ctx, db2_matrix **res, db2_matrix *lhs, db2_matrix *
 int db2_castObj(db2_context *ctx, db2_matrix **res, db2_matrix *arg, int dtype);
 
 /* ------------------------------------------------------------------------- */
+/* row-partition scheduler                                                    */
+/* ------------------------------------------------------------------------- */
+
+/* The compiled body of a vectorized pipeline: a chain of operator calls on (row slices of) the inputs that leaves its
+ * results in *outputs[i] (lowered `_vect_cudaN`, src/compiler/lowering/LowerToLLVMPass.cpp:575-726). */
+typedef void (*db2_pipeline_fn)(db2_matrix ***outputs, db2_matrix **inputs, db2_context *ctx);
+
+/* Runs `fun` over the row range of the ROWS-split inputs on this context's GPU and combines the results:
+ * splits[i] = DB2_SPLIT_NONE / DB2_SPLIT_ROWS (a 1-row ROWS input is broadcast), combines[o] = DB2_COMBINE_ROWS /
+ * COLS / ADD / MIN / MAX; scalar inputs travel in the pointer slot with isScalar[i] != 0; batch_rows <= 0 picks the
+ * batch from the memory budget (normally the whole range).  ADD/MIN/MAX results are also combined over the row
+ * shards of all ranks of the communicator.  Mirrors
+ * _vectorizedPipeline__DenseMatrix_double_variadic__size_t__bool__Structure_variadic__size_t__int64_t__int64_t__
+ * int64_t__int64_t__size_t__void_variadic (src/runtime/local/kernels/VectorizedPipeline.h:35-69 ->
+ * vectorized/MTWrapper_dense.cpp:203-336, vectorized/TasksCUDA.cpp:21-123). */
+int db2_vectorizedPipeline(db2_context *ctx, db2_matrix **outputs, size_t numOutputs, const int *isScalar,
+                           db2_matrix **inputs, size_t numInputs, const int64_t *outRows, const int64_t *outCols,
+                           const int64_t *splits, const int64_t *combines, db2_pipeline_fn fun, int64_t batch_rows);
+
+/* ------------------------------------------------------------------------- */
 /* CSR matrices                                                               */
 /* ------------------------------------------------------------------------- */
 
