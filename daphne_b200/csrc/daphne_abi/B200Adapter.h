@@ -1,0 +1,187 @@
+// Glue between DAPHNE's C++ data objects and the daphne_b200 C-ABI (include/daphne_b200.h).
+//
+// DAPHNE's kernels receive DenseMatrix<VT>* objects whose per-memory-space copies are tracked by a MetaDataObject
+// (src/runtime/local/datastructures/MetaDataObject.h:39-57); the reference's CUDA kernels ask for a device pointer
+// with getValues(&AllocationDescriptorCUDA) (datastructures/AllocationDescriptorCUDA.h:24-75).  This adapter plugs
+// into the same mechanism with its own IAllocationDescriptor: the placement carries a db2_matrix handle, so a result
+// of one kernel reaches the next kernel as a HANDLE (possibly still deferred) and the elementwise chains of a
+// pipeline body are fused exactly as through the C-ABI; raw values are only produced when somebody calls getData()
+// or the host asks for the values (transferFrom).
+#pragma once
+
+#include <runtime/local/context/DaphneContext.h>
+#include <runtime/local/datastructures/DataObjectFactory.h>
+#include <runtime/local/datastructures/DataPlacement.h>
+#include <runtime/local/datastructures/DenseMatrix.h>
+#include <runtime/local/datastructures/IAllocationDescriptor.h>
+
+#include <daphne_b200.h>
+
+#include <memory>
+#include <stdexcept>
+#include <string>
+#include <type_traits>
+#include <vector>
+
+namespace b200 {
+
+// Structure keeps the offsets of a view protected and DenseMatrix::offset() is private; a pointer to member formed in
+// a derived class reads them without touching the reference's headers (a public accessor upstream would replace this).
+struct ViewOffsets : Structure {
+    static size_t row(const Structure *s) { return s->*(&ViewOffsets::row_offset); }
+    static size_t col(const Structure *s) { return s->*(&ViewOffsets::col_offset); }
+};
+
+inline void check(int rc) {
+    if (rc != DB2_OK)
+        throw std::runtime_error(db2_last_error());
+}
+
+// value type -> db2 code (-1: not implemented on the device)
+template <typename VT> constexpr int dtype_of() {
+    if (std::is_same_v<VT, double>)
+        return DB2_F64;
+    if (std::is_same_v<VT, float>)
+        return DB2_F32;
+    if (std::is_same_v<VT, int64_t> || std::is_same_v<VT, long long>)
+        return DB2_I64;
+    if (std::is_same_v<VT, uint64_t> || std::is_same_v<VT, size_t>)
+        return DB2_U64;
+    return -1;
+}
+template <typename VT> void require_supported(const char *kernel) {
+    if (dtype_of<VT>() < 0)
+        throw std::runtime_error(std::string(kernel) + ": this value type is not implemented by the B200 kernel library");
+}
+
+// the device context of a DaphneContext (created by CUDA::createCUDAContext, or on first use)
+db2_context *context(DaphneContext *ctx);
+void create_context(DaphneContext *ctx);
+
+struct HandleBox {
+    db2_matrix *m = nullptr;
+    ~HandleBox() {
+        if (m)
+            db2_matrix_decref(m);
+    }
+};
+
+} // namespace b200
+
+class AllocationDescriptorB200 : public IAllocationDescriptor {
+    db2_context *dctx;
+    int dtype;
+    int64_t rows, cols;
+    std::shared_ptr<b200::HandleBox> box;
+
+  public:
+    AllocationDescriptorB200(db2_context *c, int dtype, int64_t rows, int64_t cols, db2_matrix *preset = nullptr)
+        : dctx(c), dtype(dtype), rows(rows), cols(cols), box(std::make_shared<b200::HandleBox>()) {
+        box->m = preset; // takes over the caller's reference
+    }
+    [[nodiscard]] ALLOCATION_TYPE getType() const override { return ALLOCATION_TYPE::GPU_CUDA; }
+    [[nodiscard]] std::string getLocation() const override {
+        int dev = 0;
+        db2_context_device(dctx, &dev);
+        return std::to_string(dev);
+    }
+    void createAllocation(size_t size, bool zero) override {
+        if (box->m)
+            return; // the placement was created around an existing (possibly deferred) result
+        const size_t es = dtype == DB2_F32 ? 4 : 8;
+        if ((size_t)rows * cols * es != size) { // a caller that only knows bytes
+            rows = 1;
+            cols = (int64_t)(size / es);
+        }
+        b200::check(db2_matrix_create(dctx, dtype, rows, cols, zero ? 1 : 0, &box->m));
+    }
+    std::shared_ptr<std::byte> getData() override {
+        void *p = nullptr;
+        b200::check(db2_matrix_device_ptr(box->m, &p, nullptr));
+        return std::shared_ptr<std::byte>(box, static_cast<std::byte *>(p)); // keeps the handle alive
+    }
+    void transferTo(std::byte *src, size_t size) override {
+        if (!src)
+            throw std::runtime_error("src ptr requested for transfer to device is null");
+        void *p = nullptr;
+        b200::check(db2_matrix_device_ptr(box->m, &p, nullptr));
+        b200::check(db2_memcpy_h2d(p, src, size, db2_context_stream(dctx)));
+        b200::check(db2_context_sync(dctx)); // the source may be pageable memory that the caller reuses
+    }
+    void transferFrom(std::byte *dst, size_t size) override {
+        (void)size;
+        b200::check(db2_matrix_to_host(box->m, dst, cols));
+    }
+    [[nodiscard]] std::unique_ptr<IAllocationDescriptor> clone() const override {
+        return std::make_unique<AllocationDescriptorB200>(*this);
+    }
+    bool operator==(const IAllocationDescriptor *other) const override {
+        return getType() == other->getType() && getLocation() == other->getLocation();
+    }
+    [[nodiscard]] db2_matrix *handle() const { return box->m; }
+};
+
+namespace b200 {
+
+// Collects the handles a kernel call borrows or creates and releases the temporary ones at scope exit.
+class Call {
+    std::vector<db2_matrix *> temps;
+
+  public:
+    DaphneContext *dctx;
+    db2_context *c;
+    explicit Call(DaphneContext *ctx) : dctx(ctx), c(context(ctx)) {}
+    ~Call() {
+        for (db2_matrix *t : temps)
+            db2_matrix_decref(t);
+    }
+    Call(const Call &) = delete;
+
+    // device handle of an argument: the handle of its (latest) device placement, else a new placement filled from
+    // the host copy.  A row view of a device-resident parent becomes a row slice of the parent's handle.
+    template <typename VT> db2_matrix *in(const DenseMatrix<VT> *m) {
+        require_supported<VT>("kernel argument");
+        AllocationDescriptorB200 probe(c, dtype_of<VT>(), (int64_t)m->getNumRows(), (int64_t)m->getNumCols());
+        auto *mdo = m->getMetaDataObject();
+        const DataPlacement *dp = mdo->findDataPlacementByType(&probe, nullptr);
+        if (!dp || !mdo->isLatestVersion(dp->dp_id)) {
+            m->getValues(&probe); // creates/refreshes the placement through AllocationDescriptorB200
+            dp = mdo->findDataPlacementByType(&probe, nullptr);
+        }
+        auto *desc = dynamic_cast<AllocationDescriptorB200 *>(dp ? dp->allocation.get() : nullptr);
+        if (!desc || !desc->handle())
+            throw std::runtime_error("no B200 device placement for a kernel argument");
+        db2_matrix *h = desc->handle();
+        int64_t hr = 0, hc = 0;
+        check(db2_matrix_info(h, nullptr, &hr, &hc));
+        if (hr == (int64_t)m->getNumRows() && hc == (int64_t)m->getNumCols())
+            return h;
+        // placement inherited from the parent of a view
+        const size_t r0 = ViewOffsets::row(m);
+        if (hc != (int64_t)m->getNumCols() || ViewOffsets::col(m) != 0)
+            throw std::runtime_error("column views of device-resident matrices are not supported");
+        db2_matrix *v = nullptr;
+        check(db2_matrix_slice_rows(h, (int64_t)r0, (int64_t)(r0 + m->getNumRows()), &v));
+        temps.push_back(v);
+        return v;
+    }
+    // handle of a pre-allocated result (the kernel overwrites it)
+    template <typename VT> db2_matrix *out(DenseMatrix<VT> *m) {
+        AllocationDescriptorB200 probe(c, dtype_of<VT>(), (int64_t)m->getNumRows(), (int64_t)m->getNumCols());
+        m->getValues(&probe); // non-const access: the device placement becomes the only latest version
+        const DataPlacement *dp = m->getMetaDataObject()->findDataPlacementByType(&probe, nullptr);
+        auto *desc = dynamic_cast<AllocationDescriptorB200 *>(dp ? dp->allocation.get() : nullptr);
+        if (!desc || !desc->handle())
+            throw std::runtime_error("no B200 device placement for a kernel result");
+        return desc->handle();
+    }
+    // new device-only DenseMatrix around a result handle (takes over the reference)
+    template <typename VT> DenseMatrix<VT> *wrap(db2_matrix *h) {
+        int64_t r = 0, cc = 0;
+        check(db2_matrix_info(h, nullptr, &r, &cc));
+        AllocationDescriptorB200 desc(c, dtype_of<VT>(), r, cc, h);
+        return DataObjectFactory::create<DenseMatrix<VT>>((size_t)r, (size_t)cc, false, &desc);
+    }
+};
+
+} // namespace b200

@@ -1,0 +1,154 @@
+// TEST DRIVER for the adapter: plays the role of DAPHNE's JIT-compiled code.  It owns real DenseMatrix objects, looks
+// the kernels up BY SYMBOL NAME in the adapter library (dlsym) and calls them with the (results..., args..., kId, ctx)
+// convention of the generated wrappers (src/runtime/local/kernels/genKernelInst.py:183-262), then reads the results
+// back through DenseMatrix::getValues() -- i.e. through the residency layer.
+#include <B200Adapter.h>
+
+#include <dlfcn.h>
+
+#include <cstring>
+
+namespace {
+DaphneContext g_ctx;
+void *sym(const char *name) {
+    void *p = dlsym(RTLD_DEFAULT, name);
+    if (!p)
+        throw std::runtime_error(std::string("symbol not found: ") + name);
+    return p;
+}
+DenseMatrix<double> *host_matrix(const double *v, int64_t r, int64_t c) {
+    auto *m = DataObjectFactory::create<DenseMatrix<double>>((size_t)r, (size_t)c, false);
+    memcpy(m->getValues(), v, sizeof(double) * r * c);
+    return m;
+}
+int copy_out(DenseMatrix<double> *m, double *out, int64_t cap, int64_t *r, int64_t *c) {
+    *r = (int64_t)m->getNumRows();
+    *c = (int64_t)m->getNumCols();
+    if (*r * *c > cap)
+        return 3;
+    const double *v = static_cast<const DenseMatrix<double> *>(m)->getValues(); // device -> host through the MDO
+    for (int64_t i = 0; i < *r; i++)
+        memcpy(out + i * *c, v + i * m->getRowSkip(), sizeof(double) * *c);
+    return 0;
+}
+char g_err[1024];
+template <typename F> int guarded(F &&f) {
+    try {
+        return f();
+    } catch (const std::exception &e) {
+        snprintf(g_err, sizeof(g_err), "%s", e.what());
+        return 1;
+    }
+}
+} // namespace
+
+extern "C" {
+const char *drv_last_error() { return g_err; }
+
+int drv_init() {
+    return guarded([] {
+        reinterpret_cast<void (*)(int, DaphneContext *)>(sym("CUDA_createCUDAContext"))(0, &g_ctx);
+        return 0;
+    });
+}
+// res = kernel(arg): aggRow / aggCol / transpose style
+int drv_unary(const char *name, const double *a, int64_t ar, int64_t ac, double *out, int64_t cap, int64_t *r,
+              int64_t *c) {
+    return guarded([&] {
+        auto *A = host_matrix(a, ar, ac);
+        DenseMatrix<double> *R = nullptr;
+        reinterpret_cast<void (*)(DenseMatrix<double> **, const DenseMatrix<double> *, int, DaphneContext *)>(
+            sym(name))(&R, A, 1, &g_ctx);
+        int rc = copy_out(R, out, cap, r, c);
+        DataObjectFactory::destroy(A, R);
+        return rc;
+    });
+}
+// scalar = kernel(arg): aggAll style
+int drv_scalar(const char *name, const double *a, int64_t ar, int64_t ac, double *out) {
+    return guarded([&] {
+        auto *A = host_matrix(a, ar, ac);
+        reinterpret_cast<void (*)(double *, const DenseMatrix<double> *, int, DaphneContext *)>(sym(name))(out, A, 2,
+                                                                                                      &g_ctx);
+        DataObjectFactory::destroy(A);
+        return 0;
+    });
+}
+// res = kernel(lhs, rhs): ewBinaryMat / gemv / solve style
+int drv_binary(const char *name, const double *a, int64_t ar, int64_t ac, const double *b, int64_t br, int64_t bc,
+               double *out, int64_t cap, int64_t *r, int64_t *c) {
+    return guarded([&] {
+        auto *A = host_matrix(a, ar, ac);
+        auto *B = host_matrix(b, br, bc);
+        DenseMatrix<double> *R = nullptr;
+        reinterpret_cast<void (*)(DenseMatrix<double> **, const DenseMatrix<double> *, const DenseMatrix<double> *,
+                                  int, DaphneContext *)>(sym(name))(&R, A, B, 3, &g_ctx);
+        int rc = copy_out(R, out, cap, r, c);
+        DataObjectFactory::destroy(A, B, R);
+        return rc;
+    });
+}
+int drv_binary_sca(const char *name, const double *a, int64_t ar, int64_t ac, double s, double *out, int64_t cap,
+                   int64_t *r, int64_t *c) {
+    return guarded([&] {
+        auto *A = host_matrix(a, ar, ac);
+        DenseMatrix<double> *R = nullptr;
+        reinterpret_cast<void (*)(DenseMatrix<double> **, const DenseMatrix<double> *, double, int, DaphneContext *)>(
+            sym(name))(&R, A, s, 4, &g_ctx);
+        int rc = copy_out(R, out, cap, r, c);
+        DataObjectFactory::destroy(A, R);
+        return rc;
+    });
+}
+int drv_matmul(const double *a, int64_t ar, int64_t ac, const double *b, int64_t br, int64_t bc, int ta, int tb,
+               double *out, int64_t cap, int64_t *r, int64_t *c) {
+    return guarded([&] {
+        auto *A = host_matrix(a, ar, ac);
+        auto *B = host_matrix(b, br, bc);
+        DenseMatrix<double> *R = nullptr;
+        reinterpret_cast<void (*)(DenseMatrix<double> **, const DenseMatrix<double> *, const DenseMatrix<double> *,
+                                  bool, bool, int, DaphneContext *)>(
+            sym("CUDA_matMul__DenseMatrix_double__DenseMatrix_double__DenseMatrix_double__bool__bool"))(
+            &R, A, B, ta != 0, tb != 0, 5, &g_ctx);
+        int rc = copy_out(R, out, cap, r, c);
+        DataObjectFactory::destroy(A, B, R);
+        return rc;
+    });
+}
+int drv_syrk(const double *a, int64_t ar, int64_t ac, int trans_left, double *out, int64_t cap, int64_t *r,
+             int64_t *c) {
+    return guarded([&] {
+        auto *A = host_matrix(a, ar, ac);
+        DenseMatrix<double> *R = nullptr;
+        reinterpret_cast<void (*)(DenseMatrix<double> **, const DenseMatrix<double> *, bool, int, DaphneContext *)>(
+            sym("CUDA_syrk__DenseMatrix_double__DenseMatrix_double__bool"))(&R, A, trans_left != 0, 6, &g_ctx);
+        int rc = copy_out(R, out, cap, r, c);
+        DataObjectFactory::destroy(A, R);
+        return rc;
+    });
+}
+// A chained call sequence whose intermediates never visit the host, including a row VIEW of a device-resident
+// matrix: r = sumRow((X[r0:r1, ] - mu) * s) -- exercises handle passing, deferred chains and view offsets.
+int drv_chain(const double *x, int64_t xr, int64_t xc, const double *mu, double s, int64_t r0, int64_t r1, double *out,
+              int64_t cap, int64_t *r, int64_t *c) {
+    return guarded([&] {
+        using DM = DenseMatrix<double>;
+        auto *X = host_matrix(x, xr, xc);
+        auto *MU = host_matrix(mu, 1, xc);
+        DM *X2 = nullptr, *D = nullptr, *S = nullptr, *R = nullptr;
+        // X2 = X + 0 lives on the device only; the view below inherits its device placement
+        reinterpret_cast<void (*)(DM **, const DM *, double, int, DaphneContext *)>(
+            sym("CUDA_ewAdd__DenseMatrix_double__DenseMatrix_double__double"))(&X2, X, 0.0, 7, &g_ctx);
+        auto *V = DataObjectFactory::create<DM>(X2, r0, r1);
+        reinterpret_cast<void (*)(DM **, const DM *, const DM *, int, DaphneContext *)>(
+            sym("CUDA_ewSub__DenseMatrix_double__DenseMatrix_double__DenseMatrix_double"))(&D, V, MU, 8, &g_ctx);
+        reinterpret_cast<void (*)(DM **, const DM *, double, int, DaphneContext *)>(
+            sym("CUDA_ewMul__DenseMatrix_double__DenseMatrix_double__double"))(&S, D, s, 9, &g_ctx);
+        reinterpret_cast<void (*)(DM **, const DM *, int, DaphneContext *)>(
+            sym("CUDA_sumRow__DenseMatrix_double__DenseMatrix_double"))(&R, S, 10, &g_ctx);
+        int rc = copy_out(R, out, cap, r, c);
+        DataObjectFactory::destroy(X, MU, X2, V, D, S, R);
+        return rc;
+    });
+}
+}

@@ -1,0 +1,93 @@
+"""Builds the DAPHNE-facing adapter library from a DAPHNE source tree.
+
+    python daphne_b200/csrc/daphne_abi/build_adapter.py [DAPHNE_SRC]      (default /root/reference)
+
+Steps:
+  1. the tree's own kernels.json is filtered to the kernel templates this library implements for the CUDA backend
+     (the DNN operators and extractCol/colBind are left to DAPHNE's own library);
+  2. the tree's own generator (src/runtime/local/kernels/genKernelInst.py) emits the extern "C" wrappers and the
+     catalog JSON for backend "CUDA" -- names, argument order and the kId/ctx tail are therefore exactly DAPHNE's;
+  3. the wrappers are compiled against the tree's data-structure headers and the headers in include/ here, which carry
+     the reference's header names (runtime/local/kernels/CUDA/AggRow.h, ...) and forward to libdaphne_b200.so.
+Nothing of the tree is copied; generated sources and the outputs live in daphne_b200/_abi_build/ (git-ignored):
+    libCUDAKernels.so   CUDAcatalog.json   (+ libabi_driver.so, the JIT stand-in used by the tests)
+Outside a DAPHNE build tree (as here) DaphneContext.h / ErrorHandler.h / KernelInstrumentation.h come from shim/."""
+from __future__ import annotations
+
+import json
+import subprocess
+import sys
+import sysconfig
+from pathlib import Path
+
+HERE = Path(__file__).resolve().parent
+PKG = HERE.parents[1]
+OUT = PKG / "_abi_build"
+SUPPORTED_HEADERS = {"AggAll.h", "AggCol.h", "AggRow.h", "EwBinaryMat.h", "EwBinaryObjSca.h", "MatMul.h", "Syrk.h",
+                     "Gemv.h", "Solve.h", "Transpose.h", "Fill.h", "CreateCUDAContext.h"}
+
+
+def _is_cuda(api) -> bool:
+    names = api["name"] if isinstance(api["name"], list) else [api["name"]]
+    return "CUDA" in names
+
+
+def filtered_spec(daphne_src: Path) -> list:
+    spec = json.loads((daphne_src / "src/runtime/local/kernels/kernels.json").read_text())
+    keep = []
+    for k in spec:
+        t = k["kernelTemplate"]
+        if t["header"] not in SUPPORTED_HEADERS:
+            continue
+        apis = [a for a in k.get("api", []) if _is_cuda(a)]
+        if not apis:
+            continue
+        k = dict(k)
+        k["api"] = [dict(a, name=["CUDA"]) for a in apis]
+        keep.append(k)
+    return keep
+
+
+def build(daphne_src: str | Path = "/root/reference") -> Path:
+    daphne_src = Path(daphne_src)
+    if not (daphne_src / "src/runtime/local/kernels/genKernelInst.py").exists():
+        raise RuntimeError(f"no DAPHNE source tree at {daphne_src}")
+    from daphne_b200 import build as core
+    core.build()
+    OUT.mkdir(exist_ok=True)
+    for old in OUT.glob("CUDAkernels*.cpp"):
+        old.unlink()
+    spec_path = OUT / "kernels_b200.json"
+    spec_path.write_text(json.dumps(filtered_spec(daphne_src)))
+    r = subprocess.run([sys.executable, str(daphne_src / "src/runtime/local/kernels/genKernelInst.py"), str(spec_path),
+                        str(OUT / "CUDAkernels"), str(OUT / "CUDAcatalog.json"), "CUDA"],
+                       capture_output=True, text=True)
+    if r.returncode != 0:
+        raise RuntimeError("genKernelInst.py failed:\n" + r.stdout + r.stderr)
+    site = Path(sysconfig.get_paths()["purelib"])
+    ds = daphne_src / "src/runtime/local/datastructures"
+    inc = ["-I", str(HERE / "include"), "-I", str(HERE), "-I", str(HERE / "shim"), "-I", str(daphne_src / "src"),
+           "-I", str(site / "flashinfer/data/spdlog/include"), "-I", str(PKG.parent / "include")]
+    flags = ["-std=c++20", "-O2", "-fPIC", "-pthread", "-DFMT_HEADER_ONLY", "-w"]
+    gen = sorted(OUT.glob("CUDAkernels*.cpp"))
+    ref_srcs = [ds / n for n in ("Structure.cpp", "MetaDataObject.cpp", "DenseMatrix.cpp", "DataPlacement.cpp",
+                                 "ValueTypeUtils.cpp")]
+    lib = OUT / "libCUDAKernels.so"
+    cmd = ["g++", *flags, "-shared", "-o", str(lib), *inc, *map(str, gen), str(HERE / "adapter.cpp"),
+           *map(str, ref_srcs), "-L", str(PKG), "-ldaphne_b200", f"-Wl,-rpath,{PKG}", "-Wl,-rpath,$ORIGIN/.."]
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    if r.returncode != 0:
+        raise RuntimeError("compiling the adapter failed:\n" + r.stdout[-4000:] + r.stderr[-8000:])
+    drv = OUT / "libabi_driver.so"
+    cmd = ["g++", *flags, "-shared", "-o", str(drv), *inc, str(HERE / "abi_driver.cpp"), "-L", str(OUT),
+           "-lCUDAKernels", "-L", str(PKG), "-ldaphne_b200", "-ldl", f"-Wl,-rpath,{OUT}", f"-Wl,-rpath,{PKG}",
+           "-Wl,-rpath,$ORIGIN", "-Wl,-rpath,$ORIGIN/.."]
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    if r.returncode != 0:
+        raise RuntimeError("compiling the ABI driver failed:\n" + r.stdout[-4000:] + r.stderr[-8000:])
+    return lib
+
+
+if __name__ == "__main__":
+    sys.path.insert(0, str(PKG.parent))
+    print(build(sys.argv[1] if len(sys.argv) > 1 else "/root/reference"))

@@ -1,0 +1,15 @@
+// B200 implementation behind the name and signature of the reference header of the same path
+// (src/runtime/local/kernels/CUDA/EwBinaryMat.h): the generated extern "C" wrappers include it unchanged.
+#pragma once
+#include <B200Adapter.h>
+#include <runtime/local/kernels/BinaryOpCode.h>
+namespace CUDA {
+template <class DTRes, class DTLhs, class DTRhs>
+void ewBinaryMat(BinaryOpCode opCode, DTRes *&res, const DTLhs *lhs, const DTRhs *rhs, DCTX(ctx)) {
+    b200::Call call(ctx);
+    db2_matrix *r = res ? call.out(res) : nullptr;
+    b200::check(db2_ewBinaryMat(call.c, static_cast<int>(opCode), &r, call.in(lhs), call.in(rhs)));
+    if (!res)
+        res = call.template wrap<typename DTRes::VT>(r);
+}
+} // namespace CUDA

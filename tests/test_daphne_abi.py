@@ -1,0 +1,135 @@
+"""The DAPHNE-facing adapter (daphne_b200/_abi_build/libCUDAKernels.so): the library DAPHNE's kernel catalog would
+load in place of its own libCUDAKernels.so.  Built by daphne_b200/csrc/daphne_abi/build_adapter.py from a DAPHNE
+source tree; skipped where it was not built.
+
+CPU: every function of the generated catalog is an exported symbol, and the names are the reference's.
+GPU: a driver that plays the JIT (owns real DenseMatrix objects, resolves kernels by symbol name, reads results back
+through DenseMatrix::getValues()) against the CPU oracle."""
+import ctypes as C
+import json
+import subprocess
+from pathlib import Path
+
+import numpy as np
+import pytest
+
+ROOT = Path(__file__).resolve().parents[1]
+ABI = ROOT / "daphne_b200" / "_abi_build"
+pytestmark = pytest.mark.skipif(not (ABI / "libCUDAKernels.so").exists(), reason="adapter library not built")
+
+
+def test_catalog_symbols_are_exported_with_the_reference_names():
+    cat = json.loads((ABI / "CUDAcatalog.json").read_text())
+    out = subprocess.run(["nm", "-D", "--defined-only", str(ABI / "libCUDAKernels.so")], capture_output=True,
+                         text=True, check=True).stdout
+    syms = {ln.split()[-1] for ln in out.splitlines() if " T " in ln}
+    names = {e["kernelFuncName"] for e in cat}
+    assert len(names) >= 250
+    assert not (names - syms)
+    for must in ("CUDA_sumRow__DenseMatrix_double__DenseMatrix_double", "CUDA_sumAll__double__DenseMatrix_double",
+                 "CUDA_ewAdd__DenseMatrix_double__DenseMatrix_double__double",
+                 "CUDA_matMul__DenseMatrix_double__DenseMatrix_double__DenseMatrix_double__bool__bool",
+                 "CUDA_syrk__DenseMatrix_double__DenseMatrix_double__bool", "CUDA_createCUDAContext",
+                 "CUDA_gemv__DenseMatrix_double__DenseMatrix_double__DenseMatrix_double",
+                 "CUDA_solve__DenseMatrix_double__DenseMatrix_double__DenseMatrix_double",
+                 "CUDA_transpose__DenseMatrix_double__DenseMatrix_double",
+                 "CUDA_fill__DenseMatrix_double__double__size_t__size_t"):
+        assert must in syms, must
+    assert all(e["backend"] == "CUDA" and e["libPath"] == "libCUDAKernels.so" for e in cat)
+
+
+@pytest.fixture(scope="module")
+def drv():
+    C.CDLL(str(ROOT / "daphne_b200" / "libdaphne_b200.so"), mode=C.RTLD_GLOBAL)
+    C.CDLL(str(ABI / "libCUDAKernels.so"), mode=C.RTLD_GLOBAL)
+    d = C.CDLL(str(ABI / "libabi_driver.so"), mode=C.RTLD_GLOBAL)
+    d.drv_last_error.restype = C.c_char_p
+    assert d.drv_init() == 0, d.drv_last_error()
+    return d
+
+
+def _p(a):
+    return C.c_void_p(a.ctypes.data)
+
+
+def _call(d, fn, *args, cap=1 << 22):
+    out = np.empty(cap)
+    r, c = C.c_int64(), C.c_int64()
+    rc = fn(*args, _p(out), C.c_int64(cap), C.byref(r), C.byref(c))
+    if rc != 0:
+        raise RuntimeError(d.drv_last_error().decode())
+    return out[: r.value * c.value].reshape(r.value, c.value).copy()
+
+
+i64 = C.c_int64
+
+
+@pytest.mark.gpu
+def test_kernels_called_by_symbol_through_daphne_objects(drv):
+    from oracle import pyoracle as o
+    rng = np.random.default_rng(0)
+    a = np.ascontiguousarray(rng.standard_normal((3000, 40)))
+    b = np.ascontiguousarray(rng.standard_normal((3000, 40)))
+    for name, f, op in (("sumRow", o.aggRow, 0), ("minRow", o.aggRow, 2), ("maxRow", o.aggRow, 3),
+                        ("sumCol", o.aggCol, 0), ("minCol", o.aggCol, 2), ("maxCol", o.aggCol, 3)):
+        got = _call(drv, drv.drv_unary, f"CUDA_{name}__DenseMatrix_double__DenseMatrix_double".encode(), _p(a),
+                    i64(3000), i64(40))
+        np.testing.assert_allclose(got, f(op, a), rtol=1e-12)
+    for name, op in (("sumAll", 0), ("minAll", 2), ("maxAll", 3)):
+        v = C.c_double()
+        assert drv.drv_scalar(f"CUDA_{name}__double__DenseMatrix_double".encode(), _p(a), i64(3000), i64(40),
+                              C.byref(v)) == 0, drv.drv_last_error()
+        assert abs(v.value - o.aggAll(op, a)) <= 1e-12 * abs(o.aggAll(op, a))
+    for name, op in (("ewAdd", 0), ("ewSub", 1), ("ewMul", 2), ("ewDiv", 3), ("ewMax", 14), ("ewNeq", 8)):
+        sym = f"CUDA_{name}__DenseMatrix_double__DenseMatrix_double__DenseMatrix_double".encode()
+        got = _call(drv, drv.drv_binary, sym, _p(a), i64(3000), i64(40), _p(b), i64(3000), i64(40))
+        assert np.array_equal(got, o.ewBinaryMat(op, a, b)), name
+        rv = np.ascontiguousarray(b[:1])
+        got = _call(drv, drv.drv_binary, sym, _p(a), i64(3000), i64(40), _p(rv), i64(1), i64(40))
+        assert np.array_equal(got, o.ewBinaryMat(op, a, rv)), name + " row vector"
+        sym = f"CUDA_{name}__DenseMatrix_double__DenseMatrix_double__double".encode()
+        got = _call(drv, drv.drv_binary_sca, sym, _p(a), i64(3000), i64(40), C.c_double(1.5))
+        assert np.array_equal(got, o.ewBinaryObjSca(op, a, 1.5)), name + " scalar"
+    got = _call(drv, drv.drv_unary, b"CUDA_transpose__DenseMatrix_double__DenseMatrix_double", _p(a), i64(3000),
+                i64(40))
+    assert np.array_equal(got, a.T)
+    for ta, tb, x, y in ((0, 0, a, np.ascontiguousarray(b[:40, :17])), (1, 0, a, b), (0, 1, a, b[:50].copy())):
+        got = _call(drv, drv.drv_matmul, _p(x), i64(x.shape[0]), i64(x.shape[1]), _p(y), i64(y.shape[0]),
+                    i64(y.shape[1]), C.c_int(ta), C.c_int(tb))
+        exp = o.matMul(x, y, ta, tb)
+        assert np.abs(got - exp).max() <= 1e-12 * np.abs(exp).max()
+    got = _call(drv, drv.drv_syrk, _p(a), i64(3000), i64(40), C.c_int(1))
+    assert np.abs(got - o.syrk(a)).max() <= 1e-12 * np.abs(o.syrk(a)).max()
+    y = np.ascontiguousarray(rng.standard_normal((3000, 1)))
+    got = _call(drv, drv.drv_binary, b"CUDA_gemv__DenseMatrix_double__DenseMatrix_double__DenseMatrix_double", _p(a),
+                i64(3000), i64(40), _p(y), i64(3000), i64(1))
+    assert np.abs(got - o.gemv(a, y)).max() <= 1e-12 * np.abs(o.gemv(a, y)).max()
+    s = o.syrk(a) + 0.001 * np.eye(40)
+    rhs = o.gemv(a, y)
+    got = _call(drv, drv.drv_binary, b"CUDA_solve__DenseMatrix_double__DenseMatrix_double__DenseMatrix_double", _p(s),
+                i64(40), i64(40), _p(rhs), i64(40), i64(1))
+    assert np.abs(got - o.solve(s, rhs)).max() <= 1e-9 * np.abs(o.solve(s, rhs)).max()
+
+
+@pytest.mark.gpu
+def test_chained_calls_keep_intermediates_on_the_device_and_views_keep_their_offset(drv):
+    rng = np.random.default_rng(1)
+    x = np.ascontiguousarray(rng.standard_normal((80000, 16)))
+    mu = np.ascontiguousarray(x.mean(axis=0, keepdims=True))
+    got = _call(drv, drv.drv_chain, _p(x), i64(80000), i64(16), _p(mu), C.c_double(3.0), i64(1000), i64(71000))
+    exp = (((x + 0.0)[1000:71000] - mu) * 3.0)
+    seq = np.zeros((70000, 1))
+    for c in range(16):  # the fused row pass adds left to right like the reference
+        seq[:, 0] += exp[:, c]
+    assert np.array_equal(got, seq)
+
+
+@pytest.mark.gpu
+def test_errors_surface_as_exceptions_with_the_reference_message(drv):
+    a, b = np.ones((4, 5)), np.ones((3, 2))
+    out = np.empty(100)
+    r, c = C.c_int64(), C.c_int64()
+    rc = drv.drv_binary(b"CUDA_ewAdd__DenseMatrix_double__DenseMatrix_double__DenseMatrix_double", _p(a), i64(4),
+                        i64(5), _p(b), i64(3), i64(2), _p(out), i64(100), C.byref(r), C.byref(c))
+    assert rc == 1
+    assert b"lhs and rhs must either have the same dimensions" in drv.drv_last_error()
