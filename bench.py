@@ -33,6 +33,8 @@ SEED = 2
 PIPELINE_MIN_BYTES_PER_ROW = 2 * COLS * 8 + 24
 # DRAM traffic of the dominant kernel per row, from the ncu capture of the 2,097,152-row case
 # (dram__bytes_read.sum + dram__bytes_write.sum = 536.92 MB + 44.38 MB; profiles/fused_row_ct_kernel_*.md)
+# FP64 peak of this pool's B200: cuBLAS DGEMM 8192^3 through torch.mm, measured twice on the GPU box (35.4 / 35.5)
+FP64_PEAK_TFLOPS = 35.4
 DOMINANT_TRAFFIC_BYTES_PER_ROW = (536.92e6 + 44.38e6) / 2_097_152
 
 
@@ -227,6 +229,10 @@ def run_ours(args) -> dict:
     check(lib.db2_event_elapsed_ms(e2, e3, C.byref(ms)))
     e2e_ms = comm.max_float(max(ms.value / e2e_steps, wall_ms))
 
+    extra = {}
+    if not args.no_extra:
+        extra["normal_equations_shard"] = normal_equations_leg(ctx, comm, lib, host, world, args)
+
     peak, peak_kind = measured_peaks()
     line = {
         "metric": "pipeline_rows_per_s", "value": n_total / (ms_step * 1e-3), "unit": "rows/s", "n_gpus": world,
@@ -244,6 +250,7 @@ def run_ours(args) -> dict:
         "pipeline_hbm_gbs": n_total / world * PIPELINE_MIN_BYTES_PER_ROW / (ms_step * 1e-3) / 1e9,
         "pipeline_hbm_frac_of_" + peak_kind: (rows * PIPELINE_MIN_BYTES_PER_ROW / (ms_step * 1e-3) / 1e9) / peak,
         "checksum_s": s_value,
+        "extra": extra,
     }
     if dom:
         line["roofline"] = {"bound": "hbm", "kernel": dom["name"], "achieved": dom["gbs"], "peak": peak,
@@ -256,6 +263,54 @@ def run_ours(args) -> dict:
     for p_ in (host_ptr, p_r, p_m, p_i):
         lib.db2_free_host(p_)
     return line if rank == 0 else {}
+
+
+def normal_equations_leg(ctx, comm, lib, host, world, args) -> dict:
+    """Second workload, reported beside the headline: the per-GPU shard of the sharded normal equations
+    (8,388,608 x 512 over 8 GPUs = 1,048,576 x 512 f64 = 4 GiB per GPU, U[-1,1)): t(X)X by syrk, t(X)y by gemv, both
+    combined across ranks, then solve.  FLOP convention: BLAS syrk count n*d*(d+1) for t(X)X."""
+    import daphne_b200.kernels as K
+    from daphne_b200 import pipelines
+    from daphne_b200.lib import check
+    n, d = (1_048_576, 512) if args.rows >= ROWS_PER_GPU else (max(args.rows // 16, 1024), 512)
+    x = host.reshape(-1)[: n * d].reshape(n, d)  # reuse the pinned buffer
+    rng = np.random.default_rng(5 + comm.rank)
+    step = 1 << 14
+    for lo in range(0, n, step):
+        hi = min(n, lo + step)
+        x[lo:hi] = rng.random((hi - lo, d)) * 2.0 - 1.0
+    w = np.random.default_rng(55).standard_normal((d, 1))
+    y = x @ w + 0.01 * np.random.default_rng(56 + comm.rank).standard_normal((n, 1))
+    X, Y = K.DenseMatrix.from_numpy(ctx, x), K.DenseMatrix.from_numpy(ctx, y)
+    X.device_ptr()
+    Y.device_ptr()
+    stream = C.c_void_p(ctx.stream)
+    probe = pipelines.Probe(lib, stream)
+    for _ in range(2):
+        res = pipelines.normal_equations(ctx, X, Y, 0.001, comm)
+    comm.barrier()
+    check(lib.db2_device_sync())
+    e0, e1 = C.c_void_p(), C.c_void_p()
+    check(lib.db2_event_create(C.byref(e0)))
+    check(lib.db2_event_create(C.byref(e1)))
+    reps = 5
+    check(lib.db2_event_record(e0, stream))
+    for _ in range(reps):
+        res = pipelines.normal_equations(ctx, X, Y, 0.001, comm, probe=probe)
+    check(lib.db2_event_record(e1, stream))
+    comm.barrier()
+    check(lib.db2_device_sync())
+    ms = C.c_float()
+    check(lib.db2_event_elapsed_ms(e0, e1, C.byref(ms)))
+    step_ms = comm.max_float(ms.value / reps)
+    syrk = probe.summary()
+    beta = res.beta.to_numpy()
+    flop = float(n) * d * (d + 1)
+    return {"workload": f"t(X)X + lambda I, t(X)y, solve on f64 {n} x {d} per GPU (U[-1,1)), combined over {world} GPU(s)",
+            "ms_per_step": step_ms, "rows_per_s": n * world / (step_ms * 1e-3),
+            "syrk_ms": syrk["avg_ms"], "syrk_tflops_syrk_count": flop / (syrk["avg_ms"] * 1e-3) / 1e12,
+            "syrk_frac_of_fp64_peak": flop / (syrk["avg_ms"] * 1e-3) / 1e12 / FP64_PEAK_TFLOPS,
+            "fp64_peak_tflops": FP64_PEAK_TFLOPS, "beta_max_abs_err_vs_w": float(np.abs(beta - w).max())}
 
 
 def cpu_baseline(rows: int, cols: int, steps: int = 3, threads: int | None = None) -> dict:
@@ -302,6 +357,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--rows", type=int, default=ROWS_PER_GPU, help="rows per GPU (default: the 4 GiB configuration)")
+    ap.add_argument("--no-extra", action="store_true", help="skip the normal-equations leg reported under `extra`")
     ap.add_argument("--cpu-rows", type=int, default=1 << 20, help="rows of the bounded CPU-baseline sample")
     args = ap.parse_args()
     if args.warmup < 3 and args.impl == "ours":

@@ -1,4 +1,4 @@
-// Small helper kernels called between the hot operators: transpose, fill, seq, diagMatrix, ctable, solve.
+// Small helper kernels called between the hot operators: transpose, fill, seq, diagMatrix, ctable.
 #include "common.cuh"
 
 namespace db2 {
@@ -82,101 +82,6 @@ __global__ void max_i64_kernel(const int64_t *__restrict__ v, int64_t ld, int64_
         m = max(m, __shfl_xor_sync(0xffffffffu, m, o));
     if (threadIdx.x % 32 == 0)
         atomicMax(out, m);
-}
-
-// ---------------------------------------------------------------------------
-// solve: LU with partial pivoting, one right-hand side, one CTA (the systems are d x d with d <= a few hundred).
-// Works on a copy of A in global memory (row-major); pivot = first row with the largest |a_ik| (LAPACK's idamax).
-// status: 0 ok, k+1 = U(k,k) is exactly zero.
-// ---------------------------------------------------------------------------
-__global__ void __launch_bounds__(1024)
-    solve_lu_kernel(double *__restrict__ A, int64_t n, double *__restrict__ x, int32_t *__restrict__ status) {
-    __shared__ double s_val[32];
-    __shared__ int s_idx[32];
-    __shared__ int s_piv;
-    __shared__ double s_pivval;
-    const int tid = threadIdx.x, nt = blockDim.x;
-    for (int64_t k = 0; k < n; k++) {
-        // pivot search over column k, rows k..n-1
-        double best = -1.0;
-        int bi = (int)n;
-        for (int64_t i = k + tid; i < n; i += nt) {
-            const double v = fabs(A[i * n + k]);
-            if (v > best || (v == best && (int)i < bi)) {
-                best = v;
-                bi = (int)i;
-            }
-        }
-        for (int o = 16; o >= 1; o >>= 1) {
-            const double ov = __shfl_xor_sync(0xffffffffu, best, o);
-            const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-            if (ov > best || (ov == best && oi < bi)) {
-                best = ov;
-                bi = oi;
-            }
-        }
-        if (tid % 32 == 0) {
-            s_val[tid / 32] = best;
-            s_idx[tid / 32] = bi;
-        }
-        __syncthreads();
-        if (tid == 0) {
-            double b = s_val[0];
-            int ix = s_idx[0];
-            for (int w = 1; w < (nt + 31) / 32; w++)
-                if (s_val[w] > b || (s_val[w] == b && s_idx[w] < ix)) {
-                    b = s_val[w];
-                    ix = s_idx[w];
-                }
-            s_piv = ix;
-            s_pivval = b;
-        }
-        __syncthreads();
-        const int piv = s_piv;
-        if (s_pivval == 0.0) {
-            if (tid == 0)
-                *status = (int32_t)(k + 1);
-            return;
-        }
-        if (piv != (int)k) { // swap rows k and piv (and the right-hand side)
-            for (int64_t c = tid; c < n; c += nt) {
-                const double t = A[k * n + c];
-                A[k * n + c] = A[(int64_t)piv * n + c];
-                A[(int64_t)piv * n + c] = t;
-            }
-            if (tid == 0) {
-                const double t = x[k];
-                x[k] = x[piv];
-                x[piv] = t;
-            }
-        }
-        __syncthreads();
-        const double inv_free_pivot = A[k * n + k];
-        // multipliers l_ik = a_ik / a_kk, then the rank-1 update of the trailing block and of the right-hand side
-        for (int64_t i = k + 1 + tid; i < n; i += nt)
-            A[i * n + k] = __ddiv_rn(A[i * n + k], inv_free_pivot);
-        __syncthreads();
-        const int64_t m = n - k - 1;
-        for (int64_t e = tid; e < m * m; e += nt) {
-            const int64_t i = k + 1 + e / m, j = k + 1 + e % m;
-            A[i * n + j] = __fma_rn(-A[i * n + k], A[k * n + j], A[i * n + j]);
-        }
-        for (int64_t i = k + 1 + tid; i < n; i += nt)
-            x[i] = __fma_rn(-A[i * n + k], x[k], x[i]);
-        __syncthreads();
-    }
-    // back substitution
-    for (int64_t k = n - 1; k >= 0; k--) {
-        if (tid == 0)
-            x[k] = __ddiv_rn(x[k], A[k * n + k]);
-        __syncthreads();
-        const double xk = x[k];
-        for (int64_t i = tid; i < k; i += nt)
-            x[i] = __fma_rn(-A[i * n + k], xk, x[i]);
-        __syncthreads();
-    }
-    if (tid == 0)
-        *status = 0;
 }
 
 static int grid_for(int64_t n, int threads) {
@@ -277,17 +182,4 @@ extern "C" int db2k_ctable(const void *lhs, int64_t lhs_ld, const void *rhs, int
         return after_launch("ctable_kernel");
     }
     return DB2_OK;
-}
-
-extern "C" int db2k_solve(int dtype, void *a_work, int64_t n, void *x_inout, int32_t *dev_status, void *stream) {
-    DB2_CHECK(dtype == DB2_F64, DB2_EUNSUPPORTED, "solve: only double is implemented on the device");
-    DB2_CHECK(a_work && x_inout && dev_status, DB2_EINVAL, "null argument");
-    if (n == 0)
-        return DB2_OK;
-    int threads = 1024;
-    if (n * n < 1024 * 4)
-        threads = 256;
-    solve_lu_kernel<<<1, threads, 0, as_stream(stream)>>>(static_cast<double *>(a_work), n,
-                                                         static_cast<double *>(x_inout), dev_status);
-    return after_launch("solve_lu_kernel");
 }

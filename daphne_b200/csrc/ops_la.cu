@@ -137,7 +137,9 @@ int db2_solve(db2_context *ctx, db2_matrix **res, db2_matrix *lhs, db2_matrix *r
                                (size_t)n, cudaMemcpyDeviceToDevice, ctx->stream));
     DB2_CUDA(cudaMemcpy2DAsync(r->dev_ptr(), 8, rhs->dev_ptr(), (size_t)rhs->dev_ld * 8, 8, (size_t)n,
                                cudaMemcpyDeviceToDevice, ctx->stream));
-    DB2_TRY(db2k_solve(DB2_F64, work->ptr, n, r->dev_ptr(), ctx->dev_status + 8, ctx->stream));
+    auto pivots = make_devbuf(ctx, db2k_solve_scratch_bytes(n));
+    DB2_TRY(db2k_solve(DB2_F64, work->ptr, n, r->dev_ptr(), ctx->dev_status + 8, pivots->ptr, pivots->bytes,
+                       ctx->stream));
     count(ctx, before);
     // the reference throws from inside the call when a pivot is exactly zero: check synchronously
     DB2_CUDA(cudaMemcpyAsync(ctx->host_status + 8, ctx->dev_status + 8, sizeof(int32_t), cudaMemcpyDeviceToHost,

@@ -79,7 +79,8 @@ _SIGS = {
     "db2k_diag_matrix": (i32, [i32, vp, i64, i64, vp, i64, vp]),
     "db2k_max_i64": (i32, [vp, i64, i64, vp, vp]),
     "db2k_ctable": (i32, [vp, i64, vp, i64, i64, C.c_double, vp, i64, i64, i64, i32, vp]),
-    "db2k_solve": (i32, [i32, vp, i64, vp, vp, vp]),
+    "db2k_solve_scratch_bytes": (sz, [i64]),
+    "db2k_solve": (i32, [i32, vp, i64, vp, vp, vp, sz, vp]),
     # runtime
     "db2_context_create": (i32, [i32, _P(vp)]),
     "db2_context_destroy": (i32, [vp]),

@@ -195,10 +195,13 @@ int db2k_max_i64(const void *vec, int64_t ld, int64_t n, void *dev_out, void *st
  * Replaces CTable<Dense<double>,Dense<int64>,Dense<int64>,double> (src/runtime/local/kernels/CTable.h:55-106). */
 int db2k_ctable(const void *lhs, int64_t lhs_ld, const void *rhs, int64_t rhs_ld, int64_t n, double weight, void *res,
                 int64_t res_rows, int64_t res_cols, int64_t res_ld, int lhs_is_row_index, void *stream);
-/* Solves A x = b by LU with partial pivoting.  a_work: n x n row-major COPY of A (destroyed); x_inout: b on entry,
- * x on exit; *dev_status (device int32) = 0, or k+1 if U(k,k) is exactly zero.  Replaces Solve<Dense,Dense,Dense>
+/* Solves A x = b by blocked LU with partial pivoting.  a_work: n x n row-major COPY of A (destroyed); x_inout: b on
+ * entry, x on exit; *dev_status (device int32) = 0, or k+1 if U(k,k) is exactly zero; scratch: device memory of
+ * db2k_solve_scratch_bytes(n) bytes (pivot indices).  Replaces Solve<Dense,Dense,Dense>
  * (src/runtime/local/kernels/Solve.h:86-116: LAPACKE_dgesv; CUDA twin kernels/CUDA/Solve.cpp:75-151). */
-int db2k_solve(int dtype, void *a_work, int64_t n, void *x_inout, int32_t *dev_status, void *stream);
+size_t db2k_solve_scratch_bytes(int64_t n);
+int db2k_solve(int dtype, void *a_work, int64_t n, void *x_inout, int32_t *dev_status, void *scratch,
+               size_t scratch_bytes, void *stream);
 
 /* ------------------------------------------------------------------------- */
 /* db2_*: runtime -- context, matrix handles with residency, operator calls   */
