@@ -378,12 +378,20 @@ static int run_gemm(bool ta, bool tb, GemmArgs g, cudaStream_t st, void *scratch
     return dispatch_tiles<true, true>(g, p, st);
 }
 
+// f32 path (gemm_tf32.cu): tcgen05 kind::tf32 with split operands
+namespace tc {
+size_t tf32_scratch_bytes(int64_t M, int64_t N, int64_t K, bool syrk);
+int tf32_gemm(const float *A, int64_t lda, bool ta, const float *B, int64_t ldb, bool tb, float *C, int64_t ldc,
+              int64_t M, int64_t N, int64_t K, bool syrk, void *scratch, size_t scratch_bytes, cudaStream_t st);
+} // namespace tc
+
 } // namespace db2
 
 using namespace db2;
 
 extern "C" size_t db2k_matmul_scratch_bytes(int dtype, int64_t m, int64_t n, int64_t k) {
-    (void)dtype;
+    if (dtype == DB2_F32)
+        return tc::tf32_scratch_bytes(m, n, k, false);
     size_t worst = 0;
     for (int c = 0; c < 4; c++) {
         const size_t b = plan_gemm(m, n, k, false, c & 1, c & 2).scratch;
@@ -395,12 +403,17 @@ extern "C" size_t db2k_matmul_scratch_bytes(int dtype, int64_t m, int64_t n, int
 extern "C" int db2k_matmul(int dtype, const void *lhs, int64_t lhs_rows, int64_t lhs_cols, int64_t lhs_ld,
                            const void *rhs, int64_t rhs_rows, int64_t rhs_cols, int64_t rhs_ld, int transa, int transb,
                            void *res, int64_t res_ld, void *scratch, size_t scratch_bytes, void *stream) {
-    DB2_CHECK(dtype == DB2_F64, DB2_EUNSUPPORTED, "matMul: only double is implemented on the device");
+    DB2_CHECK(dtype == DB2_F64 || dtype == DB2_F32, DB2_EUNSUPPORTED,
+              "matMul: only double and float are implemented on the device");
     const int64_t m = transa ? lhs_cols : lhs_rows, k = transa ? lhs_rows : lhs_cols;
     const int64_t k2 = transb ? rhs_cols : rhs_rows, n = transb ? rhs_rows : rhs_cols;
     DB2_CHECK(k == k2, DB2_EINVAL, "MatMul - #cols of lhs and #rows of rhs must be the same, but got%lldand%lld",
               (long long)k, (long long)k2);
     DB2_CHECK((lhs && rhs && res) || m * n == 0, DB2_EINVAL, "null operand");
+    if (dtype == DB2_F32)
+        return tc::tf32_gemm(static_cast<const float *>(lhs), lhs_ld, transa != 0, static_cast<const float *>(rhs),
+                             rhs_ld, transb != 0, static_cast<float *>(res), res_ld, m, n, k, false, scratch,
+                             scratch_bytes, as_stream(stream));
     GemmArgs g{};
     g.A = static_cast<const double *>(lhs);
     g.B = static_cast<const double *>(rhs);
@@ -416,15 +429,23 @@ extern "C" int db2k_matmul(int dtype, const void *lhs, int64_t lhs_rows, int64_t
 }
 
 extern "C" size_t db2k_syrk_scratch_bytes(int dtype, int64_t rows, int64_t cols, int trans_left) {
-    (void)dtype;
     const int64_t n = trans_left ? cols : rows, k = trans_left ? rows : cols;
+    if (dtype == DB2_F32)
+        return tc::tf32_scratch_bytes(n, n, k, true);
     return plan_gemm(n, n, k, true, trans_left != 0, trans_left == 0).scratch + 256;
 }
 
 extern "C" int db2k_syrk(int dtype, const void *arg, int64_t rows, int64_t cols, int64_t ld, int trans_left, void *res,
                          int64_t res_ld, void *scratch, size_t scratch_bytes, void *stream) {
-    DB2_CHECK(dtype == DB2_F64, DB2_EUNSUPPORTED, "syrk: only double is implemented on the device");
+    DB2_CHECK(dtype == DB2_F64 || dtype == DB2_F32, DB2_EUNSUPPORTED,
+              "syrk: only double and float are implemented on the device");
     DB2_CHECK((arg && res) || rows * cols == 0, DB2_EINVAL, "null operand");
+    if (dtype == DB2_F32) {
+        const int64_t n = trans_left ? cols : rows, k = trans_left ? rows : cols;
+        const float *x = static_cast<const float *>(arg);
+        return tc::tf32_gemm(x, ld, trans_left != 0, x, ld, trans_left == 0, static_cast<float *>(res), res_ld, n, n, k,
+                             true, scratch, scratch_bytes, as_stream(stream));
+    }
     GemmArgs g{};
     g.A = g.B = static_cast<const double *>(arg);
     g.C = static_cast<double *>(res);

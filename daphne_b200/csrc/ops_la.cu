@@ -20,6 +20,18 @@ static void count(db2_context *ctx, uint64_t before) {
     ctx->stats.launches += g_launches.load(std::memory_order_relaxed) - before;
 }
 
+// The f32 contraction (tensor-core kernel with bounded waits) leaves a status word at the start of its scratch area;
+// a non-zero word means a wait expired and the result is not valid.
+static int check_contraction_status(db2_context *ctx, int dtype, const void *scratch) {
+    if (dtype != DB2_F32)
+        return DB2_OK;
+    int32_t st = 0;
+    DB2_CUDA(cudaMemcpyAsync(&st, scratch, sizeof(st), cudaMemcpyDeviceToHost, ctx->stream));
+    DB2_CUDA(cudaStreamSynchronize(ctx->stream));
+    DB2_CHECK(st == 0, DB2_ECUDA, "f32 contraction kernel gave up waiting (status %d); result discarded", (int)st);
+    return DB2_OK;
+}
+
 } // namespace db2
 
 using namespace db2;
@@ -29,7 +41,9 @@ extern "C" {
 int db2_matMul(db2_context *ctx, db2_matrix **res, db2_matrix *lhs, db2_matrix *rhs, int transa, int transb) {
     DB2_API_BEGIN
     DB2_CHECK(ctx && res && lhs && rhs, DB2_EINVAL, "null argument");
-    DB2_CHECK(lhs->dtype == DB2_F64 && rhs->dtype == DB2_F64, DB2_EUNSUPPORTED, "matMul: only double on the device");
+    const int dt = lhs->dtype;
+    DB2_CHECK((dt == DB2_F64 || dt == DB2_F32) && rhs->dtype == dt, DB2_EUNSUPPORTED,
+              "matMul: double or float operands of one type on the device");
     const int64_t m = transa ? lhs->cols : lhs->rows, k = transa ? lhs->rows : lhs->cols;
     const int64_t k2 = transb ? rhs->cols : rhs->rows, n = transb ? rhs->rows : rhs->cols;
     DB2_CHECK(k == k2, DB2_EINVAL, "MatMul - #cols of lhs and #rows of rhs must be the same, but got%lldand%lld",
@@ -38,32 +52,33 @@ int db2_matMul(db2_context *ctx, db2_matrix **res, db2_matrix *lhs, db2_matrix *
     const uint64_t before = g_launches.load();
     DB2_TRY(ensure_device(lhs));
     DB2_TRY(ensure_device(rhs));
-    DB2_TRY(prepare_result(ctx, res, DB2_F64, m, n));
+    DB2_TRY(prepare_result(ctx, res, dt, m, n));
     void *scratch = nullptr;
-    DB2_TRY(ctx_scratch(ctx, db2k_matmul_scratch_bytes(DB2_F64, m, n, k), &scratch));
-    DB2_TRY(db2k_matmul(DB2_F64, lhs->dev_ptr(), lhs->rows, lhs->cols, lhs->dev_ld, rhs->dev_ptr(), rhs->rows,
+    DB2_TRY(ctx_scratch(ctx, db2k_matmul_scratch_bytes(dt, m, n, k), &scratch));
+    DB2_TRY(db2k_matmul(dt, lhs->dev_ptr(), lhs->rows, lhs->cols, lhs->dev_ld, rhs->dev_ptr(), rhs->rows,
                         rhs->cols, rhs->dev_ld, transa, transb, (*res)->dev_ptr(), (*res)->dev_ld, scratch,
                         ctx->scratch_bytes, ctx->stream));
     count(ctx, before);
-    return DB2_OK;
+    return check_contraction_status(ctx, dt, scratch);
     DB2_API_END
 }
 
 int db2_syrk(db2_context *ctx, db2_matrix **res, db2_matrix *arg, int trans_left) {
     DB2_API_BEGIN
     DB2_CHECK(ctx && res && arg, DB2_EINVAL, "null argument");
-    DB2_CHECK(arg->dtype == DB2_F64, DB2_EUNSUPPORTED, "syrk: only double on the device");
+    const int dt = arg->dtype;
+    DB2_CHECK(dt == DB2_F64 || dt == DB2_F32, DB2_EUNSUPPORTED, "syrk: double or float on the device");
     const int64_t n = trans_left ? arg->cols : arg->rows;
     bind_device(ctx);
     const uint64_t before = g_launches.load();
     DB2_TRY(ensure_device(arg));
-    DB2_TRY(prepare_result(ctx, res, DB2_F64, n, n));
+    DB2_TRY(prepare_result(ctx, res, dt, n, n));
     void *scratch = nullptr;
-    DB2_TRY(ctx_scratch(ctx, db2k_syrk_scratch_bytes(DB2_F64, arg->rows, arg->cols, trans_left), &scratch));
-    DB2_TRY(db2k_syrk(DB2_F64, arg->dev_ptr(), arg->rows, arg->cols, arg->dev_ld, trans_left, (*res)->dev_ptr(),
+    DB2_TRY(ctx_scratch(ctx, db2k_syrk_scratch_bytes(dt, arg->rows, arg->cols, trans_left), &scratch));
+    DB2_TRY(db2k_syrk(dt, arg->dev_ptr(), arg->rows, arg->cols, arg->dev_ld, trans_left, (*res)->dev_ptr(),
                       (*res)->dev_ld, scratch, ctx->scratch_bytes, ctx->stream));
     count(ctx, before);
-    return DB2_OK;
+    return check_contraction_status(ctx, dt, scratch);
     DB2_API_END
 }
 
