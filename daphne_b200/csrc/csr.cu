@@ -23,6 +23,7 @@ struct db2_csr {
     // device placement
     std::shared_ptr<db2::DevBuf> d_val, d_col, d_off;
     bool idx32 = true;
+    bool unit_vals = false; // every stored value is exactly 1.0: kernels need not read the value array
     bool dev_valid = false;
     // deferred product lhs (.) rhs
     db2_csr *lazy_lhs = nullptr;
@@ -53,65 +54,96 @@ __device__ __forceinline__ double scale_at(int skind, const double *sc, int64_t 
 }
 
 // Row aggregation of val[i] * scale(r, col[i]); entries whose scale is exactly zero do not exist in the product
-// (EwBinaryMat.h:295-302) and therefore count as implicit zeros.  G lanes per row.
-template <int G, typename IT>
+// (EwBinaryMat.h:295-302) and therefore count as implicit zeros.  G lanes per row; every lane group works on U rows
+// at a time so that the dependent loads of a row (offsets -> column index -> gathered operand) of U rows overlap.
+// UNIT: every stored value is exactly 1.0 (adjacency matrices), the value array is not read.
+template <int G, typename IT, bool UNIT>
 __global__ void __launch_bounds__(256)
     csr_agg_row_kernel(int op, const double *__restrict__ val, const IT *__restrict__ col,
                        const uint64_t *__restrict__ off, int64_t rows, int64_t cols, int skind,
                        const double *__restrict__ sc, int64_t sc_ld, double *__restrict__ out) {
-    constexpr int RPC = 256 / G;
+    constexpr int RPC = 256 / G, U = 4;
     const int lane = threadIdx.x % G, grp = threadIdx.x / G;
     const int64_t stride = (int64_t)gridDim.x * RPC;
     const int64_t rows_padded = (rows + RPC - 1) / RPC * RPC;
-    for (int64_t r = (int64_t)blockIdx.x * RPC + grp; r < rows_padded; r += stride) {
-        const bool live = r < rows;
-        double acc = (op == DB2_AGG_MAX) ? -INFINITY : (op == DB2_AGG_MIN) ? INFINITY : (op == DB2_AGG_PROD) ? 1.0 : 0.0;
-        long long kept = 0;
-        if (live) {
-            const uint64_t b = off[r], e = off[r + 1];
-            for (uint64_t i = b + lane; i < e; i += G) {
+    const double init = (op == DB2_AGG_MAX) ? -INFINITY : (op == DB2_AGG_MIN) ? INFINITY : (op == DB2_AGG_PROD) ? 1.0 : 0.0;
+    auto combine = [&](double a, double x) {
+        if (op == DB2_AGG_SUM)
+            return __dadd_rn(a, x);
+        if (op == DB2_AGG_PROD)
+            return __dmul_rn(a, x);
+        if (op == DB2_AGG_MAX)
+            return (a < x) ? x : a;
+        return (x < a) ? x : a;
+    };
+    for (int64_t r0 = (int64_t)blockIdx.x * RPC + grp; r0 < rows_padded; r0 += stride * U) {
+        uint64_t b[U], e[U];
+        double acc[U];
+        long long kept[U];
+#pragma unroll
+        for (int u = 0; u < U; u++) {
+            const int64_t r = r0 + u * stride;
+            const bool live = r < rows;
+            b[u] = live ? off[r] : 0;
+            e[u] = live ? off[r + 1] : 0;
+            acc[u] = init;
+            kept[u] = 0;
+        }
+        // first entry of every lane: the loads of the U rows are issued back to back
+        int64_t cc[U];
+        double xx[U], ss[U];
+        bool have[U];
+#pragma unroll
+        for (int u = 0; u < U; u++) {
+            const uint64_t i = b[u] + lane;
+            have[u] = i < e[u];
+            cc[u] = have[u] ? (int64_t)col[i] : 0;
+            xx[u] = (UNIT || !have[u]) ? 1.0 : val[i];
+        }
+#pragma unroll
+        for (int u = 0; u < U; u++)
+            ss[u] = (have[u] && skind != SK_NONE) ? scale_at(skind, sc, sc_ld, r0 + u * stride, cc[u]) : 1.0;
+#pragma unroll
+        for (int u = 0; u < U; u++)
+            if (have[u] && !(skind != SK_NONE && ss[u] == 0.0)) {
+                kept[u]++;
+                acc[u] = combine(acc[u], skind != SK_NONE ? __dmul_rn(xx[u], ss[u]) : xx[u]);
+            }
+        // rows with more than G entries
+#pragma unroll
+        for (int u = 0; u < U; u++)
+            for (uint64_t i = b[u] + lane + G; i < e[u]; i += G) {
                 const int64_t c = (int64_t)col[i];
-                double x = val[i];
+                double x = UNIT ? 1.0 : val[i];
                 if (skind != SK_NONE) {
-                    const double s = scale_at(skind, sc, sc_ld, r, c);
+                    const double s = scale_at(skind, sc, sc_ld, r0 + u * stride, c);
                     if (s == 0.0)
                         continue;
                     x = __dmul_rn(x, s);
                 }
-                kept++;
-                if (op == DB2_AGG_SUM)
-                    acc = __dadd_rn(acc, x);
-                else if (op == DB2_AGG_PROD)
-                    acc = __dmul_rn(acc, x);
-                else if (op == DB2_AGG_MAX)
-                    acc = (acc < x) ? x : acc;
-                else
-                    acc = (x < acc) ? x : acc;
+                kept[u]++;
+                acc[u] = combine(acc[u], x);
             }
-        }
 #pragma unroll
-        for (int m = G / 2; m >= 1; m >>= 1) {
-            const double o = shfl_xor(acc, m);
-            kept += __shfl_xor_sync(0xffffffffu, kept, m);
-            if (op == DB2_AGG_SUM)
-                acc = __dadd_rn(acc, o);
-            else if (op == DB2_AGG_PROD)
-                acc = __dmul_rn(acc, o);
-            else if (op == DB2_AGG_MAX)
-                acc = (acc < o) ? o : acc;
-            else
-                acc = (o < acc) ? o : acc;
-        }
-        if (live && lane == 0) {
-            if (op != DB2_AGG_SUM && kept < cols) { // one implicit zero takes part (AggRow.h:167-176)
-                if (op == DB2_AGG_MAX)
-                    acc = (acc < 0.0) ? 0.0 : acc;
-                else if (op == DB2_AGG_MIN)
-                    acc = (0.0 < acc) ? 0.0 : acc;
-                else
-                    acc = __dmul_rn(acc, 0.0);
+        for (int u = 0; u < U; u++) {
+#pragma unroll
+            for (int m = G / 2; m >= 1; m >>= 1) {
+                acc[u] = combine(acc[u], shfl_xor(acc[u], m));
+                kept[u] += __shfl_xor_sync(0xffffffffu, kept[u], m);
             }
-            out[r] = acc;
+            const int64_t r = r0 + u * stride;
+            if (r < rows && lane == 0) {
+                double a = acc[u];
+                if (op != DB2_AGG_SUM && kept[u] < cols) { // one implicit zero takes part (AggRow.h:167-176)
+                    if (op == DB2_AGG_MAX)
+                        a = (a < 0.0) ? 0.0 : a;
+                    else if (op == DB2_AGG_MIN)
+                        a = (0.0 < a) ? 0.0 : a;
+                    else
+                        a = __dmul_rn(a, 0.0);
+                }
+                out[r] = a;
+            }
         }
     }
 }
@@ -205,19 +237,29 @@ static int launch_agg(db2_context *ctx, int op, const db2_csr *m, int skind, con
     const IT *col = static_cast<const IT *>(m->d_col->ptr);
     const double avg = (double)m->nnz / (double)(m->rows > 0 ? m->rows : 1); // a view inherits its parent's count
     const int64_t rows = m->rows;
-    if (avg <= 6.0) {
-        const int64_t want = (rows + 63) / 64, cap = (int64_t)sm_count() * 8;
-        csr_agg_row_kernel<4, IT><<<(int)(want < cap ? (want ? want : 1) : cap), 256, 0, ctx->stream>>>(
-            op, val, col, m->off_ptr(), rows, m->cols, skind, sc, ld, out);
-    } else if (avg <= 24.0) {
-        const int64_t want = (rows + 31) / 32, cap = (int64_t)sm_count() * 8;
-        csr_agg_row_kernel<8, IT><<<(int)(want < cap ? (want ? want : 1) : cap), 256, 0, ctx->stream>>>(
-            op, val, col, m->off_ptr(), rows, m->cols, skind, sc, ld, out);
+    const int lanes = avg <= 6.0 ? 4 : (avg <= 24.0 ? 8 : 32);
+    // every lane group takes 4 rows per turn
+    const int64_t want = (rows + (256 / lanes) * 4 - 1) / ((256 / lanes) * 4), cap = (int64_t)sm_count() * 8;
+    const int grid = (int)(want < cap ? (want ? want : 1) : cap);
+#define DB2_CSR_AGG(G, UNIT)                                                                                           \
+    csr_agg_row_kernel<G, IT, UNIT><<<grid, 256, 0, ctx->stream>>>(op, val, col, m->off_ptr(), rows, m->cols, skind,   \
+                                                                   sc, ld, out)
+    if (m->unit_vals) {
+        if (lanes == 4)
+            DB2_CSR_AGG(4, true);
+        else if (lanes == 8)
+            DB2_CSR_AGG(8, true);
+        else
+            DB2_CSR_AGG(32, true);
     } else {
-        const int64_t want = (rows + 7) / 8, cap = (int64_t)sm_count() * 8;
-        csr_agg_row_kernel<32, IT><<<(int)(want < cap ? (want ? want : 1) : cap), 256, 0, ctx->stream>>>(
-            op, val, col, m->off_ptr(), rows, m->cols, skind, sc, ld, out);
+        if (lanes == 4)
+            DB2_CSR_AGG(4, false);
+        else if (lanes == 8)
+            DB2_CSR_AGG(8, false);
+        else
+            DB2_CSR_AGG(32, false);
     }
+#undef DB2_CSR_AGG
     return after_launch("csr_agg_row_kernel");
 }
 
@@ -280,6 +322,12 @@ static int csr_ensure_device(db2_csr *m) {
     const uint64_t lo = m->h_off[0], hi = m->h_off[m->rows];
     const int64_t n = (int64_t)(hi - lo);
     m->idx32 = m->cols <= (int64_t)UINT32_MAX;
+    {
+        bool unit = n > 0;
+        for (int64_t i = 0; i < n && unit; i++)
+            unit = m->h_val[lo + i] == 1.0;
+        m->unit_vals = unit;
+    }
     m->d_val = devbuf(ctx, (size_t)n * 8);
     m->d_off = devbuf(ctx, (size_t)(m->rows + 1) * 8);
     auto wide = devbuf(ctx, (size_t)n * 8);
@@ -370,6 +418,7 @@ int db2_csr_slice_rows(db2_csr *src, int64_t r0, int64_t r1, db2_csr **view) {
         m->d_col = src->d_col;
         m->d_off = src->d_off;
         m->idx32 = src->idx32;
+        m->unit_vals = src->unit_vals;
         m->row0 = src->row0 + r0;
         m->nnz = src->nnz;
         m->dev_valid = true;

@@ -375,6 +375,150 @@ int fused_row_pass_f64(const FusedProgram &prog, cudaStream_t st) {
 }
 
 // ---------------------------------------------------------------------------
+// flat pass: chains on column vectors (rows x 1) or on contiguous same-shape operands, one element at a time
+// ---------------------------------------------------------------------------
+// The row pass gives every thread one ROW, which for an n x 1 vector means one element per thread and 128 elements
+// per CTA tile.  Such chains (connected components: u = max(rowMaxs(G * t(c)), c); sum(u != c)) are evaluated here
+// over the n elements directly, 4 per thread and iteration.  Optional outputs of one pass: the final values
+// (prog.ew_out), the values after `mid_after` steps (mid_out: a deferred matrix whose chain is a prefix), and the sum
+// of the final values (per-CTA partials, added up in a fixed order by flat_sum_final_kernel).
+constexpr int FLAT_THREADS = 256, FLAT_GV = 4;
+
+bool fused_flat_eligible(const FusedProgram &P) {
+    if (P.ntaps != 0)
+        return false;
+    if (P.cols == 1)
+        return true;
+    if (P.base_ld != P.cols)
+        return false;
+    for (int s = 0; s < P.nsteps; s++) {
+        const int k = P.steps[s].kind;
+        if (k == FK_ROWVEC || k == FK_COLVEC || (k == FK_MATRIX && P.steps[s].ld != P.cols))
+            return false;
+    }
+    return true;
+}
+
+__global__ void __launch_bounds__(FLAT_THREADS)
+    fused_flat_kernel(const __grid_constant__ FusedProgram P, int64_t n, int64_t stride_scale, double *mid_out,
+                      int mid_after, double *partials) {
+    // element i of an operand with leading dimension ld sits at i * ld for a column vector (stride_scale = 1) and at
+    // i for a contiguous matrix (stride_scale = 0)
+    const int64_t base_st = stride_scale ? P.base_ld : 1;
+    const double *__restrict__ base = static_cast<const double *>(P.base);
+    double *__restrict__ ew_out = static_cast<double *>(P.ew_out);
+    const int64_t out_st = stride_scale ? P.ew_out_ld : 1;
+    double sum = 0.0;
+    for (int64_t i0 = ((int64_t)blockIdx.x * FLAT_THREADS + threadIdx.x) * FLAT_GV; i0 < n;
+         i0 += (int64_t)gridDim.x * FLAT_THREADS * FLAT_GV) {
+        const int nv = (n - i0) < FLAT_GV ? (int)(n - i0) : FLAT_GV;
+        double v[FLAT_GV], o[FLAT_GV], y[FLAT_GV];
+#pragma unroll
+        for (int k = 0; k < FLAT_GV; k++)
+            v[k] = k < nv ? base[(i0 + k) * base_st] : 0.0;
+        if (mid_out && mid_after == 0) {
+#pragma unroll
+            for (int k = 0; k < FLAT_GV; k++)
+                if (k < nv)
+                    mid_out[i0 + k] = v[k];
+        }
+        for (int s = 0; s < P.nsteps; s++) {
+            const FusedStep &st = P.steps[s];
+            if (st.kind == FK_MATRIX || st.kind == FK_COLVEC) {
+                const double *__restrict__ op = static_cast<const double *>(st.ptr);
+                const int64_t op_st = stride_scale ? st.ld : 1;
+#pragma unroll
+                for (int k = 0; k < FLAT_GV; k++)
+                    o[k] = k < nv ? op[(i0 + k) * op_st] : 1.0;
+            } else {
+                const double b = st.kind == FK_ROWVEC ? *static_cast<const double *>(st.ptr) : st.imm;
+#pragma unroll
+                for (int k = 0; k < FLAT_GV; k++)
+                    o[k] = b;
+            }
+            const bool div = st.op == FO_DIV && !st.reversed;
+#pragma unroll
+            for (int k = 0; k < FLAT_GV; k++)
+                y[k] = div ? div_helper(o[k]) : 0.0;
+            apply_step<FLAT_GV>(st.op, st.reversed != 0, v, o, y);
+            if (mid_out && mid_after == s + 1) {
+#pragma unroll
+                for (int k = 0; k < FLAT_GV; k++)
+                    if (k < nv)
+                        mid_out[i0 + k] = v[k];
+            }
+        }
+        if (ew_out) {
+#pragma unroll
+            for (int k = 0; k < FLAT_GV; k++)
+                if (k < nv)
+                    ew_out[(i0 + k) * out_st] = v[k];
+        }
+#pragma unroll
+        for (int k = 0; k < FLAT_GV; k++)
+            if (k < nv)
+                sum = __dadd_rn(sum, v[k]);
+    }
+    if (partials) {
+        __shared__ double wsum[FLAT_THREADS / 32];
+        for (int d = 16; d >= 1; d >>= 1)
+            sum = __dadd_rn(sum, shfl_down(sum, d));
+        if (threadIdx.x % 32 == 0)
+            wsum[threadIdx.x / 32] = sum;
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            double t = 0.0;
+            for (int w = 0; w < FLAT_THREADS / 32; w++)
+                t = __dadd_rn(t, wsum[w]);
+            partials[blockIdx.x] = t;
+        }
+    }
+}
+
+__global__ void flat_sum_final_kernel(const double *__restrict__ partials, int n, double *__restrict__ out) {
+    __shared__ double sh[256];
+    double t = 0.0;
+    for (int i = threadIdx.x; i < n; i += 256)
+        t = __dadd_rn(t, partials[i]);
+    sh[threadIdx.x] = t;
+    __syncthreads();
+    for (int d = 128; d >= 1; d >>= 1) {
+        if ((int)threadIdx.x < d)
+            sh[threadIdx.x] = __dadd_rn(sh[threadIdx.x], sh[threadIdx.x + d]);
+        __syncthreads();
+    }
+    if (threadIdx.x == 0)
+        *out = sh[0];
+}
+
+size_t fused_flat_scratch_bytes() { return ((size_t)sm_count() * 8 + 8) * sizeof(double); }
+
+// sum_out (device, may be null): sum of the final values; scratch holds the per-CTA partials behind it
+int fused_flat_pass_f64(const FusedProgram &prog, void *mid_out, int mid_after, double *sum_out, void *scratch,
+                        size_t scratch_bytes, cudaStream_t st) {
+    const int64_t n = prog.rows * prog.cols;
+    if (n == 0) {
+        if (sum_out)
+            DB2_CUDA(cudaMemsetAsync(sum_out, 0, sizeof(double), st));
+        return DB2_OK;
+    }
+    int64_t grid = (n + FLAT_THREADS * FLAT_GV - 1) / (FLAT_THREADS * FLAT_GV);
+    const int64_t cap = (int64_t)sm_count() * 8;
+    grid = grid < cap ? grid : cap;
+    DB2_CHECK(!sum_out || (scratch && scratch_bytes >= (size_t)grid * sizeof(double)), DB2_EINVAL,
+              "flat pass scratch too small");
+    fused_flat_kernel<<<(unsigned)grid, FLAT_THREADS, 0, st>>>(prog, n, prog.cols == 1 ? 1 : 0,
+                                                             static_cast<double *>(mid_out), mid_after,
+                                                             sum_out ? static_cast<double *>(scratch) : nullptr);
+    DB2_TRY(after_launch("fused_flat_kernel"));
+    if (sum_out) {
+        flat_sum_final_kernel<<<1, 256, 0, st>>>(static_cast<const double *>(scratch), (int)grid, sum_out);
+        DB2_TRY(after_launch("flat_sum_final_kernel"));
+    }
+    return DB2_OK;
+}
+
+// ---------------------------------------------------------------------------
 // column pass
 // ---------------------------------------------------------------------------
 constexpr int CT = 256;

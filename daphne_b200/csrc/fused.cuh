@@ -77,5 +77,11 @@ bool fused_col_pass_ct(const FusedProgram &prog, const char *signature, int agg_
 int fused_col_pass_f64(const FusedProgram &prog, int agg_op, void *res, void *scratch, size_t scratch_bytes,
                        cudaStream_t st);
 size_t fused_col_scratch_bytes(int64_t cols);
+// flat pass (fused.cu): chains on column vectors or contiguous same-shape operands; optional prefix output after
+// `mid_after` steps (contiguous, mid_out) and optional sum of the final values (*sum_out on the device)
+bool fused_flat_eligible(const FusedProgram &prog);
+size_t fused_flat_scratch_bytes();
+int fused_flat_pass_f64(const FusedProgram &prog, void *mid_out, int mid_after, double *sum_out, void *scratch,
+                        size_t scratch_bytes, cudaStream_t st);
 
 } // namespace db2

@@ -2,21 +2,25 @@
 //
 // The reference multiplies f32 matrices with cblas_sgemm (src/runtime/local/kernels/MatMul.cpp:31-36,284-288) and
 // cblas_ssyrk (Syrk.h:80-92), i.e. with full single-precision products.  The tensor cores take f32 operands as TF32
-// (10 explicit mantissa bits), so every operand is split on the way into shared memory,
-//      x = hi + lo,   hi = tf32(x) (round to nearest),   lo = tf32(x - hi)   (x - hi is exact in f32),
-// and three MMAs per k-step accumulate  hi*hi + hi*lo + lo*hi  in f32; the dropped lo*lo term and the rounding of lo
-// are below 2^-21 relative per product, the same order as sgemm's own rounding.
+// (10 explicit mantissa bits, the low 13 bits of the f32 pattern are ignored), so every operand is used twice,
+//      x = hi + lo,   hi = x with the low 13 mantissa bits cleared (the raw tile as the tensor core reads it),
+//                     lo = tf32(x - hi)   (x - hi is exact in f32),
+// and three MMAs per k-step accumulate  hi*hi  and  hi*lo + lo*hi  in two f32 accumulators; the dropped lo*lo term
+// and the rounding of lo are about 2^-20 relative per product, the same order as sgemm's own rounding.
 //
 // One CTA computes a 128 x 128 tile of C (or one split-K share of it):
-//   warps 0-7  producers: 16-byte global loads -> hi/lo split -> 16-byte stores into a 3-stage ring of shared-memory
-//              tiles laid out in the tensor core's canonical 128-byte-swizzled form.  Both operand majors are
-//              supported by the MMA, so no transposition is needed: a tile whose contraction index is contiguous in
-//              memory is stored K-major (rows of 32 k = 128 bytes), the other kind MN-major (rows of 32 m = 128 bytes,
-//              4 k per swizzle atom).  Writers fence the async proxy and arrive on the stage's "full" mbarrier.
-//   warp 8     one thread issues tcgen05.mma.kind::tf32 (M 128, N 128, K 8) from shared-memory descriptors; a
-//              tcgen05.commit on the stage's "empty" mbarrier hands the buffer back when the MMAs have read it.
-//   warps 0-3  epilogue: tcgen05.ld of the accumulator (lane = row, 32 columns at a time) and stores to C or to the
-//              split-K partial buffer (summed afterwards in a fixed order: results do not depend on scheduling).
+//   warps 0-7   producers: cp.async (16 bytes, zero-filling) of the raw f32 tiles into a 5-slot ring of shared memory,
+//               directly in the tensor core's canonical 128-byte-swizzled layouts, four k-blocks ahead of their use; then
+//               each thread derives the low tile (2-slot ring) from its own packets, fences the async proxy and arrives
+//               on the "full" mbarrier.  Both operand majors are supported by the MMA, so nothing is transposed: a
+//               tile whose contraction index is contiguous in memory is stored K-major (rows of 32 k = 128 bytes),
+//               the other kind MN-major (rows of 32 m = 128 bytes, 4 k per swizzle atom of 32-byte units).
+//   warp 16     one thread issues tcgen05.mma.kind::tf32 (M 128, N 128, K 8) from shared-memory descriptors; a
+//               tcgen05.commit on the k-block's "done" mbarrier hands the buffers back when the MMAs have read them.
+//   warps 8-15  drain: the tensor core adds into its accumulator with truncation, so after every 64 k the main
+//               accumulator (double-buffered in tensor memory) is read with tcgen05.ld (lane = row) and added to a
+//               register accumulator with round-to-nearest; at the end the cross terms are added and the rows are
+//               stored to C or to the split-K partial buffer (summed afterwards in a fixed order).
 // Every mbarrier wait is bounded (about a second): on expiry the kernel raises a flag in *status, all roles fall
 // through to the common exit and tensor memory is released.
 #include "common.cuh"
@@ -26,11 +30,14 @@ namespace tc {
 
 constexpr int BM = 128, BN = 128, BK = 32; // f32 elements; BK * 4 bytes = one 128-byte swizzle row
 constexpr int TILE_BYTES = BM * BK * 4;    // 16 KB (A and B tiles have the same size)
-constexpr int STAGE_BYTES = 4 * TILE_BYTES; // A hi, A lo, B hi, B lo
-constexpr int STAGES = 3;
-constexpr int PRODUCER_THREADS = 256, THREADS = PRODUCER_THREADS + 32;
-constexpr int TMEM_COLS = 128;
-constexpr size_t SMEM_BYTES = (size_t)STAGES * STAGE_BYTES + 1024 /* alignment slack */ + 256 /* barriers */;
+constexpr int SLOT_BYTES = 2 * TILE_BYTES;  // an A tile and a B tile
+constexpr int RAW_SLOTS = 5, LOOKAHEAD = 4; // ring of raw (= high part) tiles; k-blocks copied ahead of their use
+constexpr int LOW_SLOTS = 2;                // ring of low-part tiles
+constexpr int CHUNK_KB = 2;              // k-blocks (64 k) accumulated in tensor memory between two promotions
+constexpr int PRODUCER_THREADS = 256, DRAIN_THREADS = 256, MMA_WARP = (PRODUCER_THREADS + DRAIN_THREADS) / 32;
+constexpr int THREADS = PRODUCER_THREADS + DRAIN_THREADS + 32;
+constexpr int TMEM_COLS = 512; // two main accumulators and the cross-term accumulator of 128 columns each
+constexpr size_t SMEM_BYTES = (size_t)(RAW_SLOTS + LOW_SLOTS) * SLOT_BYTES + 1024 /* alignment slack */ + 256;
 constexpr long long WAIT_LIMIT_CLOCKS = 2000000000LL;
 
 struct TcArgs {
@@ -106,15 +113,12 @@ __device__ __forceinline__ void mma_tf32(uint32_t tmem_d, uint64_t adesc, uint64
 __device__ __forceinline__ void mma_commit(uint32_t bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
-    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-                 "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-                 "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+                 "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
                  : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
                    "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]),
-                   "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]),
-                   "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]),
-                   "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+                   "=r"(r[15])
                  : "r"(taddr)
                  : "memory");
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
@@ -144,15 +148,38 @@ __host__ __device__ constexpr uint32_t instr_desc(bool a_mn_major, bool b_mn_maj
 // ---------------------------------------------------------------------------
 // A tile is 128 (m or n) x 32 (k) elements = 1024 packets of 16 bytes; thread t handles packets t, t+256, t+512, t+768.
 //
-// KMAJ (k contiguous in global memory; element (r, k) at src[(r0 + r) * ld + k]):
+// KMAJ (k contiguous in global memory; element (r, k) at src[(r0 + r) * ld + k]): rows of 32 k = 128 bytes whose
+// 16-byte units are swizzled with the row;  groups of 8 rows 1024 bytes apart
 //   packet p: r = p / 8, kc = p % 8 (k = 4 kc);   shared offset (r/8)*1024 + (r%8)*128 + ((kc ^ r%8) * 16)
 // MN-major (m contiguous; element (m, k) at src[k * ld + m0 + m]): atoms of 4 k-rows x 128 bytes (32 m), whose
 // 32-byte units are swizzled with the k-row;  4 atoms along m (512 bytes apart), groups of 4 k 2048 bytes apart
 //   packet p: kk = p / 32, mc = p % 32 (m = 4 mc);
 //   offset (kk/4)*2048 + (mc/8)*512 + (kk%4)*128 + (((mc%8)/2 ^ kk%4) * 32) + (mc%2)*16
+template <bool KMAJ> __device__ __forceinline__ uint32_t packet_offset(int p) {
+    if (KMAJ) {
+        const int r = p >> 3, kc = p & 7;
+        return (uint32_t)((r >> 3) * 1024 + (r & 7) * 128 + ((kc ^ (r & 7)) << 4));
+    }
+    const int kk = p >> 5, mc = p & 31;
+    return (uint32_t)((kk >> 2) * 2048 + (mc >> 3) * 512 + (kk & 3) * 128 + ((((mc & 7) >> 1) ^ (kk & 3)) << 5) +
+                      ((mc & 1) << 4));
+}
+
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void *src, uint32_t src_bytes) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async4(uint32_t dst, const void *src, uint32_t src_bytes) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() {
+    asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+
+// Asynchronous copy of this thread's 4 packets of one operand tile (raw f32; missing elements are zero-filled).
 template <bool KMAJ>
-__device__ __forceinline__ void load_tile(const float *__restrict__ src, int64_t ld, int64_t r0, int64_t R, int64_t k0,
-                                          int64_t kend, bool vec, int tid, float4 (&v)[4]) {
+__device__ __forceinline__ void issue_tile(const float *__restrict__ src, int64_t ld, int64_t r0, int64_t R, int64_t k0,
+                                           int64_t kend, bool vec, int tid, uint32_t tile) {
 #pragma unroll
     for (int i = 0; i < 4; i++) {
         const int p = tid + i * PRODUCER_THREADS;
@@ -169,57 +196,78 @@ __device__ __forceinline__ void load_tile(const float *__restrict__ src, int64_t
             row_ok = row < kend;
             col_end = R;
         }
-        float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (row_ok && col < col_end) {
-            const float *g = src + row * ld + col;
-            if (vec && col + 4 <= col_end) {
-                x = __ldg(reinterpret_cast<const float4 *>(g));
-            } else {
-                x.x = g[0];
-                if (col + 1 < col_end)
-                    x.y = g[1];
-                if (col + 2 < col_end)
-                    x.z = g[2];
-                if (col + 3 < col_end)
-                    x.w = g[3];
-            }
+        int64_t valid = row_ok ? col_end - col : 0; // elements of the packet that exist
+        valid = valid < 0 ? 0 : (valid > 4 ? 4 : valid);
+        const float *g = valid > 0 ? src + row * ld + col : src;
+        const uint32_t dst = tile + packet_offset<KMAJ>(p);
+        if (vec) {
+            cp_async16(dst, g, (uint32_t)valid * 4u);
+        } else {
+#pragma unroll
+            for (int e = 0; e < 4; e++)
+                cp_async4(dst + 4 * e, e < valid ? g + e : src, e < valid ? 4u : 0u);
         }
-        v[i] = x;
     }
 }
 
-__device__ __forceinline__ void split_tf32(float x, float &hi, float &lo) {
-    uint32_t h, l;
-    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(h) : "f"(x));
-    hi = __uint_as_float(h);
-    // a non-finite hi (infinite or NaN operand) keeps a zero low part so that the product stays inf / NaN
-    const float d = (fabsf(hi) <= 3.4028234e38f) ? (x - hi) : 0.f;
-    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(l) : "f"(d));
-    lo = __uint_as_float(l);
-}
-
+// Per-thread plan of the 4 packets of an operand tile for k-blocks that lie completely inside the k range and
+// 16-byte-aligned operands: source pointer of the first k-block (advanced by `step` elements per k-block), bytes that
+// exist (0, 4, .. 16; the rest of the packet is zero-filled) and shared-memory offset.
+struct PacketPlan {
+    const float *src[4];
+    uint32_t bytes[4], off[4];
+    int64_t step;
+};
 template <bool KMAJ>
-__device__ __forceinline__ void store_tile(unsigned char *hi_tile, unsigned char *lo_tile, int tid,
-                                           const float4 (&v)[4]) {
+__device__ __forceinline__ void plan_tile(const float *__restrict__ src, int64_t ld, int64_t r0, int64_t R, int64_t k0,
+                                          int tid, PacketPlan &pl) {
+    pl.step = KMAJ ? BK : (int64_t)BK * ld;
 #pragma unroll
     for (int i = 0; i < 4; i++) {
         const int p = tid + i * PRODUCER_THREADS;
-        uint32_t off;
+        pl.off[i] = packet_offset<KMAJ>(p);
+        int64_t valid;
+        const float *g;
         if (KMAJ) {
-            const int r = p >> 3, kc = p & 7;
-            off = (uint32_t)((r >> 3) * 1024 + (r & 7) * 128 + ((kc ^ (r & 7)) << 4));
+            const int64_t row = r0 + (p >> 3);
+            valid = row < R ? 4 : 0;
+            g = src + row * ld + k0 + (p & 7) * 4;
         } else {
-            const int kk = p >> 5, mc = p & 31;
-            off = (uint32_t)((kk >> 2) * 2048 + (mc >> 3) * 512 + (kk & 3) * 128 + ((((mc & 7) >> 1) ^ (kk & 3)) << 5) +
-                             ((mc & 1) << 4));
+            const int64_t col = r0 + (p & 31) * 4;
+            valid = R - col;
+            valid = valid < 0 ? 0 : (valid > 4 ? 4 : valid);
+            g = src + (k0 + (p >> 5)) * ld + col;
         }
-        float4 h, l;
-        split_tf32(v[i].x, h.x, l.x);
-        split_tf32(v[i].y, h.y, l.y);
-        split_tf32(v[i].z, h.z, l.z);
-        split_tf32(v[i].w, h.w, l.w);
-        *reinterpret_cast<float4 *>(hi_tile + off) = h;
-        *reinterpret_cast<float4 *>(lo_tile + off) = l;
+        pl.bytes[i] = (uint32_t)valid * 4u;
+        pl.src[i] = valid > 0 ? g : src; // a zero-byte copy still needs a valid address
+    }
+}
+__device__ __forceinline__ void issue_planned(PacketPlan &pl, uint32_t tile) {
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        cp_async16(tile + pl.off[i], pl.src[i], pl.bytes[i]);
+        if (pl.bytes[i])
+            pl.src[i] += pl.step;
+    }
+}
+
+// The tensor core reads an f32 bit pattern as TF32 by ignoring the low 13 mantissa bits, so the raw tile already is
+// the high part  hi = x with those bits cleared;  lo = tf32(x - hi)  (the difference is exact) goes to a second tile.
+__device__ __forceinline__ float low_part(float x) {
+    const uint32_t b = __float_as_uint(x);
+    if ((b & 0x7F800000u) == 0x7F800000u)
+        return 0.f; // inf / NaN: the high part alone carries it into the product
+    const float d = x - __uint_as_float(b & 0xFFFFE000u);
+    uint32_t l;
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(l) : "f"(d));
+    return __uint_as_float(l);
+}
+template <bool KMAJ> __device__ __forceinline__ void make_low_tile(unsigned char *raw, unsigned char *lo, int tid) {
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        const uint32_t off = packet_offset<KMAJ>(tid + i * PRODUCER_THREADS);
+        const float4 x = *reinterpret_cast<const float4 *>(raw + off);
+        *reinterpret_cast<float4 *>(lo + off) = make_float4(low_part(x.x), low_part(x.y), low_part(x.z), low_part(x.w));
     }
 }
 
@@ -232,125 +280,194 @@ template <bool TA, bool TB> __global__ void __launch_bounds__(THREADS, 1) gemm_t
     extern __shared__ unsigned char smem_raw[];
     // the swizzle pattern is a function of the absolute shared address: tiles start on 1024-byte boundaries
     unsigned char *tiles = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
-    uint64_t *bars = reinterpret_cast<uint64_t *>(tiles + STAGES * STAGE_BYTES);
-    // bars[0..S) full, bars[S..2S) empty, bars[2S] accumulator ready; then the tensor-memory base and the abort flag
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * STAGES + 1);
+    unsigned char *low_tiles = tiles + RAW_SLOTS * SLOT_BYTES;
+    uint64_t *bars = reinterpret_cast<uint64_t *>(low_tiles + LOW_SLOTS * SLOT_BYTES);
+    // full[kb % 2]: low tiles of k-block kb written (and its raw tiles landed);  done[kb % RAW_SLOTS]: MMAs of kb finished
+    uint64_t *full = bars, *done = bars + LOW_SLOTS, *acc_full = done + RAW_SLOTS, *acc_empty = acc_full + 2;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(acc_empty + 2);
     volatile int *abort = reinterpret_cast<volatile int *>(tmem_slot + 1);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int64_t m0 = (int64_t)blockIdx.y * BM, n0 = (int64_t)blockIdx.x * BN;
+    // tile order: bands of 8 tile rows are walked column by column, so that the CTAs resident at one time share
+    // their A and B panels in L2
+    int tile_m, tile_n;
+    {
+        const int tiles_n = gridDim.x, tiles_m = gridDim.y, lin = blockIdx.y * gridDim.x + blockIdx.x;
+        const int band = lin / (8 * tiles_n), first_m = band * 8;
+        const int band_rows = tiles_m - first_m < 8 ? tiles_m - first_m : 8;
+        tile_m = first_m + (lin - band * 8 * tiles_n) % band_rows;
+        tile_n = (lin - band * 8 * tiles_n) / band_rows;
+    }
+    const int64_t m0 = (int64_t)tile_m * BM, n0 = (int64_t)tile_n * BN;
     const int64_t kbeg = (int64_t)blockIdx.z * g.k_per_split;
     const int64_t kend = (kbeg + g.k_per_split < g.K) ? kbeg + g.k_per_split : g.K;
     const int nkb = (int)((kend - kbeg + BK - 1) / BK);
+    const int nch = (nkb + CHUNK_KB - 1) / CHUNK_KB;
 
     if (tid == 0) {
-        for (int s = 0; s < STAGES; s++) {
-            mbar_init(smem_u32(bars + s), PRODUCER_THREADS);
-            mbar_init(smem_u32(bars + STAGES + s), 1);
+        for (int s = 0; s < LOW_SLOTS; s++)
+            mbar_init(smem_u32(full + s), PRODUCER_THREADS);
+        for (int s = 0; s < RAW_SLOTS; s++)
+            mbar_init(smem_u32(done + s), 1);
+        for (int b = 0; b < 2; b++) {
+            mbar_init(smem_u32(acc_full + b), 1);
+            mbar_init(smem_u32(acc_empty + b), DRAIN_THREADS);
         }
-        mbar_init(smem_u32(bars + 2 * STAGES), 1);
         *abort = 0;
         fence_mbar_init();
         fence_proxy_async_smem();
     }
-    if (warp == 8)
+    if (warp == MMA_WARP)
         tmem_alloc(smem_u32(tmem_slot), TMEM_COLS);
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    // tensor-memory columns: [0,128) and [128,256) the two main accumulators, [256,384) the cross terms
+    const uint32_t tmem_cross = tmem_base + 2 * BN;
 
-    if (warp < 8) {
-        // ---------------- producers ----------------
-        float4 a_cur[4], b_cur[4], a_nxt[4], b_nxt[4];
-        if (nkb > 0) {
-            load_tile<A_KMAJ>(g.A, g.lda, m0, g.M, kbeg, kend, g.vec_a != 0, tid, a_cur);
-            load_tile<B_KMAJ>(g.B, g.ldb, n0, g.N, kbeg, kend, g.vec_b != 0, tid, b_cur);
+    if (warp < PRODUCER_THREADS / 32) {
+        // ---------------- producers: cp.async LOOKAHEAD k-blocks ahead, then the low tiles ----------------
+        auto mma_done = [&](int kb) { // the MMAs of k-block kb have completed (their slots may be rewritten)
+            return mbar_wait(smem_u32(done + kb % RAW_SLOTS), (kb / RAW_SLOTS) & 1, abort);
+        };
+        // k-blocks are issued in order, so the planned pointers simply advance; the last, partial k-block and
+        // operands without 16-byte alignment take the general path
+        PacketPlan pa, pb;
+        plan_tile<A_KMAJ>(g.A, g.lda, m0, g.M, kbeg, tid, pa);
+        plan_tile<B_KMAJ>(g.B, g.ldb, n0, g.N, kbeg, tid, pb);
+        const bool fast_a = g.vec_a != 0, fast_b = g.vec_b != 0;
+        auto issue = [&](int kb) {
+            const uint32_t st = smem_u32(tiles + (kb % RAW_SLOTS) * SLOT_BYTES);
+            const int64_t k0 = kbeg + (int64_t)kb * BK;
+            const bool whole = k0 + BK <= kend;
+            if (fast_a && whole)
+                issue_planned(pa, st);
+            else
+                issue_tile<A_KMAJ>(g.A, g.lda, m0, g.M, k0, kend, fast_a, tid, st);
+            if (fast_b && whole)
+                issue_planned(pb, st + TILE_BYTES);
+            else
+                issue_tile<B_KMAJ>(g.B, g.ldb, n0, g.N, k0, kend, fast_b, tid, st + TILE_BYTES);
+        };
+        for (int kb = 0; kb < LOOKAHEAD; kb++) {
+            if (kb < nkb)
+                issue(kb);
+            cp_async_commit();
         }
         for (int kb = 0; kb < nkb; kb++) {
-            const int s = kb % STAGES;
-            if (kb + 1 < nkb) {
-                const int64_t k1 = kbeg + (int64_t)(kb + 1) * BK;
-                load_tile<A_KMAJ>(g.A, g.lda, m0, g.M, k1, kend, g.vec_a != 0, tid, a_nxt);
-                load_tile<B_KMAJ>(g.B, g.ldb, n0, g.N, k1, kend, g.vec_b != 0, tid, b_nxt);
-            }
-            // the slot is free once the MMAs of its previous use have completed (first round: passes at once)
-            if (!mbar_wait(smem_u32(bars + STAGES + s), ((kb / STAGES) & 1) ^ 1, abort))
+            cp_async_wait<LOOKAHEAD - 1>(); // this thread's packets of k-block kb have landed
+            if (kb >= LOW_SLOTS && !mma_done(kb - LOW_SLOTS))
                 break;
-            unsigned char *st = tiles + s * STAGE_BYTES;
-            store_tile<A_KMAJ>(st, st + TILE_BYTES, tid, a_cur);
-            store_tile<B_KMAJ>(st + 2 * TILE_BYTES, st + 3 * TILE_BYTES, tid, b_cur);
-            fence_proxy_async_smem(); // generic-proxy stores -> visible to the tensor core's async proxy
-            mbar_arrive(smem_u32(bars + s));
+            unsigned char *raw = tiles + (kb % RAW_SLOTS) * SLOT_BYTES, *low = low_tiles + (kb % LOW_SLOTS) * SLOT_BYTES;
+            make_low_tile<A_KMAJ>(raw, low, tid);
+            make_low_tile<B_KMAJ>(raw + TILE_BYTES, low + TILE_BYTES, tid);
+            fence_proxy_async_smem(); // own cp.async data and stores -> visible to the tensor core's async proxy
+            mbar_arrive(smem_u32(full + kb % LOW_SLOTS));
+            // refill the raw slot that k-block kb - 1 is leaving (its MMAs ran while this block was prepared)
+            const int kn = kb + LOOKAHEAD;
+            if (kn < nkb) {
+                if (kn >= RAW_SLOTS && !mma_done(kn - RAW_SLOTS))
+                    break;
+                issue(kn);
+            }
+            cp_async_commit();
+        }
+        cp_async_wait<0>();
+    } else if (warp == MMA_WARP) {
+        if (lane == 0) {
+            // ---------------- MMA issuer ----------------
+            constexpr uint32_t idesc = instr_desc(!A_KMAJ, !B_KMAJ);
+            // per k-step of 8: K-major tiles advance 32 bytes inside the swizzle row (8-row groups 1024 bytes apart);
+            // MN-major tiles advance two groups of 4 k (2048 bytes each; the 4 atoms of 32 m of a group 512 apart)
+            constexpr uint32_t A_STEP = A_KMAJ ? 32 : 4096, B_STEP = B_KMAJ ? 32 : 4096;
+            constexpr uint32_t A_LBO = A_KMAJ ? 16 : 512, A_SBO = A_KMAJ ? 1024 : 2048, A_LT = A_KMAJ ? 2 : 1;
+            constexpr uint32_t B_LBO = B_KMAJ ? 16 : 512, B_SBO = B_KMAJ ? 1024 : 2048, B_LT = B_KMAJ ? 2 : 1;
+            bool ok = true;
+            for (int kb = 0; kb < nkb && ok; kb++) {
+                const int c = kb / CHUNK_KB, b = c & 1;
+                const bool chunk_start = kb % CHUNK_KB == 0;
+                if (chunk_start && c >= 2) // the drain warps have taken chunk c - 2 out of this accumulator
+                    ok = mbar_wait(smem_u32(acc_empty + b), ((c >> 1) - 1) & 1, abort);
+                ok = ok && mbar_wait(smem_u32(full + kb % LOW_SLOTS), (kb / LOW_SLOTS) & 1, abort);
+                if (!ok)
+                    break;
+                tc_fence_after();
+                const uint32_t raw = smem_u32(tiles + (kb % RAW_SLOTS) * SLOT_BYTES);
+                const uint32_t low = smem_u32(low_tiles + (kb % LOW_SLOTS) * SLOT_BYTES);
+                const uint32_t tmem_main = tmem_base + (uint32_t)b * BN;
 #pragma unroll
-            for (int i = 0; i < 4; i++) {
-                a_cur[i] = a_nxt[i];
-                b_cur[i] = b_nxt[i];
+                for (int j = 0; j < BK / 8; j++) {
+                    const uint64_t a_hi = smem_desc(raw + j * A_STEP, A_LBO, A_SBO, A_LT);
+                    const uint64_t a_lo = smem_desc(low + j * A_STEP, A_LBO, A_SBO, A_LT);
+                    const uint64_t b_hi = smem_desc(raw + TILE_BYTES + j * B_STEP, B_LBO, B_SBO, B_LT);
+                    const uint64_t b_lo = smem_desc(low + TILE_BYTES + j * B_STEP, B_LBO, B_SBO, B_LT);
+                    mma_tf32(tmem_cross, a_lo, b_hi, idesc, (kb | j) != 0);
+                    mma_tf32(tmem_cross, a_hi, b_lo, idesc, 1);
+                    mma_tf32(tmem_main, a_hi, b_hi, idesc, !(chunk_start && j == 0));
+                }
+                mma_commit(smem_u32(done + kb % RAW_SLOTS));
+                if (kb % CHUNK_KB == CHUNK_KB - 1 || kb == nkb - 1)
+                    mma_commit(smem_u32(acc_full + b));
             }
         }
+        __syncwarp();
     } else {
-      if (lane == 0) {
-        // ---------------- MMA issuer ----------------
-        constexpr uint32_t idesc = instr_desc(!A_KMAJ, !B_KMAJ);
-        // per k-step of 8: K-major tiles advance 32 bytes inside the swizzle row (8-row groups 1024 bytes apart);
-        // MN-major tiles advance two groups of 4 k (2048 bytes each; the 4 atoms of 32 m in a group 512 bytes apart)
-        constexpr uint32_t A_STEP = A_KMAJ ? 32 : 4096, B_STEP = B_KMAJ ? 32 : 4096;
-        constexpr uint32_t A_LBO = A_KMAJ ? 16 : 512, A_SBO = A_KMAJ ? 1024 : 2048, A_LT = A_KMAJ ? 2 : 1;
-        constexpr uint32_t B_LBO = B_KMAJ ? 16 : 512, B_SBO = B_KMAJ ? 1024 : 2048, B_LT = B_KMAJ ? 2 : 1;
+        // ---------------- drain warps: lane of tensor memory = row of the tile ----------------
+        // The tensor core adds into its f32 accumulator with truncation, which drifts with the number of additions;
+        // every CHUNK_KB k-blocks the main accumulator is therefore taken out and added (round to nearest) to a
+        // register accumulator.  The cross terms are 2^-10 of the main ones and stay in tensor memory to the end.
+        // a warp reaches the tensor-memory lanes 32 (warp % 4) .. +31; two warps share a lane quarter and take 64
+        // columns each
+        const int q = warp & 3, half = (warp - PRODUCER_THREADS / 32) >> 2;
+        constexpr int HN = BN / 2;
+        float acc[HN];
+#pragma unroll
+        for (int i = 0; i < HN; i++)
+            acc[i] = 0.f;
         bool ok = true;
-        for (int kb = 0; kb < nkb && ok; kb++) {
-            const int s = kb % STAGES;
-            ok = mbar_wait(smem_u32(bars + s), (kb / STAGES) & 1, abort);
+        for (int c = 0; c <= nch && nch > 0; c++) {
+            const bool cross = c == nch; // last round: the cross-term accumulator (complete with the last chunk)
+            const int b = c & 1;
+            if (!cross)
+                ok = __all_sync(0xffffffffu, ok && mbar_wait(smem_u32(acc_full + b), (c >> 1) & 1, abort)) != 0;
             if (!ok)
                 break;
             tc_fence_after();
-            const uint32_t st = smem_u32(tiles + s * STAGE_BYTES);
+            const uint32_t src =
+                (cross ? tmem_cross : tmem_base + (uint32_t)b * BN) + ((uint32_t)(q * 32) << 16) + (uint32_t)(half * HN);
 #pragma unroll
-            for (int j = 0; j < BK / 8; j++) {
-                const uint64_t a_hi = smem_desc(st + j * A_STEP, A_LBO, A_SBO, A_LT);
-                const uint64_t a_lo = smem_desc(st + TILE_BYTES + j * A_STEP, A_LBO, A_SBO, A_LT);
-                const uint64_t b_hi = smem_desc(st + 2 * TILE_BYTES + j * B_STEP, B_LBO, B_SBO, B_LT);
-                const uint64_t b_lo = smem_desc(st + 3 * TILE_BYTES + j * B_STEP, B_LBO, B_SBO, B_LT);
-                mma_tf32(tmem_base, a_lo, b_hi, idesc, (kb | j) != 0);
-                mma_tf32(tmem_base, a_hi, b_lo, idesc, 1);
-                mma_tf32(tmem_base, a_hi, b_hi, idesc, 1);
+            for (int c4 = 0; c4 < HN / 16; c4++) {
+                uint32_t r[16];
+                tmem_ld16(src + (uint32_t)(c4 * 16), r);
+#pragma unroll
+                for (int i = 0; i < 16; i++)
+                    acc[c4 * 16 + i] += __uint_as_float(r[i]);
             }
-            mma_commit(smem_u32(bars + STAGES + s));
+            if (!cross) {
+                tc_fence_before();
+                mbar_arrive(smem_u32(acc_empty + b));
+            }
         }
-        mma_commit(smem_u32(bars + 2 * STAGES));
-      }
-      __syncwarp();
-    }
-
-    if (warp < 4) {
-        // ---------------- epilogue: lane of tensor memory = row of the tile ----------------
-        __syncwarp();
-        const bool ready =
-            __all_sync(0xffffffffu, nkb > 0 && mbar_wait(smem_u32(bars + 2 * STAGES), 0, abort)) != 0;
-        tc_fence_after();
-        const int64_t row = m0 + warp * 32 + lane;
-        float *out = g.to_part ? g.part + ((int64_t)blockIdx.z * g.M + row) * g.N : g.C + row * g.ldc;
-        const bool vec = g.to_part ? (g.N % 4 == 0) : (g.vec_c != 0);
-        for (int c4 = 0; c4 < BN / 32; c4++) {
-            uint32_t r[32];
-            if (ready) {
-                tmem_ld32(tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)(c4 * 32), r);
-            } else {
+        const int64_t row = m0 + q * 32 + lane;
+        if (ok && row < g.M) {
+            float *out = g.to_part ? g.part + ((int64_t)blockIdx.z * g.M + row) * g.N : g.C + row * g.ldc;
+            const bool vec = g.to_part ? (g.N % 4 == 0) : (g.vec_c != 0);
 #pragma unroll
-                for (int i = 0; i < 32; i++)
-                    r[i] = 0u;
-            }
-            const int64_t c0 = n0 + c4 * 32;
-            if (row < g.M && c0 < g.N && (ready || nkb == 0)) {
+            for (int c4 = 0; c4 < HN / 32; c4++) {
+                const int64_t c0 = n0 + half * HN + c4 * 32;
+                if (c0 >= g.N)
+                    break;
                 if (vec && c0 + 32 <= g.N) {
 #pragma unroll
                     for (int i = 0; i < 32; i += 4)
-                        *reinterpret_cast<uint4 *>(out + c0 + i) = make_uint4(r[i], r[i + 1], r[i + 2], r[i + 3]);
+                        *reinterpret_cast<float4 *>(out + c0 + i) = make_float4(
+                            acc[c4 * 32 + i], acc[c4 * 32 + i + 1], acc[c4 * 32 + i + 2], acc[c4 * 32 + i + 3]);
                 } else {
 #pragma unroll
                     for (int i = 0; i < 32; i++)
                         if (c0 + i < g.N)
-                            out[c0 + i] = __uint_as_float(r[i]);
+                            out[c0 + i] = acc[c4 * 32 + i];
                 }
             }
         }
@@ -360,7 +477,7 @@ template <bool TA, bool TB> __global__ void __launch_bounds__(THREADS, 1) gemm_t
     __syncthreads();
     if (tid == 0 && *abort)
         atomicExch(g.status, 1);
-    if (warp == 8) {
+    if (warp == MMA_WARP) {
         tc_fence_after();
         tmem_dealloc(tmem_base, TMEM_COLS);
     }

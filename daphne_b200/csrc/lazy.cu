@@ -80,6 +80,15 @@ static int chain_of(db2_matrix *m, std::shared_ptr<Expr> *out) {
     return DB2_OK;
 }
 
+static void set_lazy(db2_matrix *r, std::shared_ptr<Expr> e) {
+    r->lazy = std::move(e);
+    r->ctx->lazies.push_back(r);
+}
+static void unlazy(db2_matrix *m) {
+    auto &v = m->ctx->lazies;
+    v.erase(std::remove(v.begin(), v.end(), m), v.end());
+}
+
 static db2_matrix *new_deferred(db2_context *ctx, int dtype, int64_t rows, int64_t cols) {
     db2_matrix *m = new db2_matrix();
     m->ctx = ctx;
@@ -122,7 +131,7 @@ int lazy_try_binary(db2_context *ctx, int op, db2_matrix **res, db2_matrix *lhs,
         return DB2_OK; // chain full: run this operator immediately (its inputs are materialised on demand)
     e->steps.push_back(st);
     db2_matrix *r = new_deferred(ctx, DB2_F64, lhs->rows, lhs->cols);
-    r->lazy = e;
+    set_lazy(r, e);
     *res = r;
     *handled = true;
     return DB2_OK;
@@ -148,7 +157,7 @@ int lazy_try_scalar(db2_context *ctx, int op, db2_matrix **res, db2_matrix *lhs,
     st.imm = s;
     e->steps.push_back(st);
     db2_matrix *r = new_deferred(ctx, DB2_F64, lhs->rows, lhs->cols);
-    r->lazy = e;
+    set_lazy(r, e);
     *res = r;
     *handled = true;
     return DB2_OK;
@@ -168,7 +177,7 @@ int lazy_try_unary(db2_context *ctx, int op, db2_matrix **res, db2_matrix *arg, 
     st.op = fop;
     e->steps.push_back(st);
     db2_matrix *r = new_deferred(ctx, DB2_F64, arg->rows, arg->cols);
-    r->lazy = e;
+    set_lazy(r, e);
     *res = r;
     *handled = true;
     return DB2_OK;
@@ -341,11 +350,14 @@ static int run_row_pass(db2_context *ctx, const Expr &longest, db2_matrix *ew_ta
     }
     int rc = DB2_OK;
     const std::string sig = signature_of(P);
-    if (!fused_row_pass_ct(P, sig.c_str(), ctx->stream, &rc))
+    if (fused_flat_eligible(P))
+        rc = fused_flat_pass_f64(P, nullptr, 0, nullptr, nullptr, 0, ctx->stream);
+    else if (!fused_row_pass_ct(P, sig.c_str(), ctx->stream, &rc))
         rc = fused_row_pass_f64(P, ctx->stream);
     DB2_TRY(rc);
     if (ew_target) {
         ew_target->dev_valid = true;
+        unlazy(ew_target);
         ew_target->lazy.reset();
     }
     for (db2_matrix *g : served) {
@@ -403,6 +415,8 @@ int lazy_flush_all(db2_context *ctx) {
 void lazy_forget(db2_matrix *m) {
     if (m->pend_src && m->ctx)
         unpend(m->ctx, m);
+    if (m->lazy && m->ctx)
+        unlazy(m);
 }
 
 int lazy_try_agg_col(db2_context *ctx, int op, db2_matrix **res, db2_matrix *arg, bool *handled) {
@@ -425,6 +439,53 @@ int lazy_try_agg_col(db2_context *ctx, int op, db2_matrix **res, db2_matrix *arg
     if (!fused_col_pass_ct(P, sig.c_str(), op, (*res)->dev_ptr(), scratch, ctx->scratch_bytes, ctx->stream, &rc))
         rc = fused_col_pass_f64(P, op, (*res)->dev_ptr(), scratch, ctx->scratch_bytes, ctx->stream);
     DB2_TRY(rc);
+    *handled = true;
+    return DB2_OK;
+}
+
+// sum(chain) in one flat pass; a live deferred matrix whose chain is a proper prefix (e.g. u of sum(u != c)) is
+// materialised by the same pass
+int lazy_try_agg_all(db2_context *ctx, int op, double *res_host, db2_matrix *arg, bool *handled) {
+    *handled = false;
+    if (!arg->lazy || ctx->eager || op != DB2_AGG_SUM || arg->dtype != DB2_F64)
+        return DB2_OK;
+    std::shared_ptr<const Expr> e = arg->lazy;
+    FusedProgram P;
+    build_program(*e, e->steps.size(), &P);
+    if (!fused_flat_eligible(P))
+        return DB2_OK;
+    db2_matrix *sibling = nullptr;
+    for (db2_matrix *m : ctx->lazies)
+        if (m != arg && m->lazy && !m->lazy->steps.empty() && m->lazy->steps.size() < e->steps.size() &&
+            is_prefix(*m->lazy, *e) && (!sibling || m->lazy->steps.size() > sibling->lazy->steps.size()))
+            sibling = m;
+    const uint64_t before = g_launches.load();
+    void *scratch = nullptr;
+    DB2_TRY(ctx_scratch(ctx, fused_flat_scratch_bytes() + 64, &scratch));
+    void *mid = nullptr;
+    int mid_after = 0;
+    if (sibling) {
+        sibling->dev = make_devbuf(ctx, (size_t)sibling->rows * sibling->cols * 8);
+        sibling->dev_off = 0;
+        sibling->dev_ld = sibling->cols;
+        mid = sibling->dev->ptr;
+        mid_after = (int)sibling->lazy->steps.size();
+    }
+    // the sum sits in the first 8 bytes of the scratch area, the partials behind it
+    DB2_TRY(fused_flat_pass_f64(P, mid, mid_after, static_cast<double *>(scratch), static_cast<char *>(scratch) + 64,
+                                ctx->scratch_bytes - 64, ctx->stream));
+    if (sibling) {
+        sibling->dev_valid = true;
+        unlazy(sibling);
+        sibling->lazy.reset();
+    }
+    DB2_CUDA(cudaMemcpyAsync(res_host, scratch, sizeof(double), cudaMemcpyDeviceToHost, ctx->stream));
+    DB2_CUDA(cudaStreamSynchronize(ctx->stream));
+    {
+        std::lock_guard<std::mutex> lock(ctx->mu);
+        ctx->stats.launches += g_launches.load() - before;
+        ctx->stats.d2h_bytes += sizeof(double);
+    }
     *handled = true;
     return DB2_OK;
 }

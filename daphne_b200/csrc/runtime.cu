@@ -561,6 +561,12 @@ int db2_aggAll(db2_context *ctx, int op, void *res_host, db2_matrix *arg) {
     DB2_API_BEGIN
     DB2_CHECK(ctx && arg && res_host, DB2_EINVAL, "null argument");
     bind_device(ctx);
+    {
+        bool handled = false;
+        DB2_TRY(lazy_try_agg_all(ctx, op, static_cast<double *>(res_host), arg, &handled));
+        if (handled)
+            return DB2_OK;
+    }
     const uint64_t before = g_launches.load();
     DB2_TRY(ensure_device(arg));
     const size_t sb = db2k_agg_all_scratch_bytes(arg->dtype, op, arg->rows, arg->cols) + 64;

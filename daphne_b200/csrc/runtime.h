@@ -20,6 +20,7 @@ struct db2_context {
     int device = 0;
     // deferred evaluation (lazy.cu): row aggregations waiting to be served by one fused pass
     std::vector<db2_matrix *> pending;
+    std::vector<db2_matrix *> lazies; // live matrices that stand for an unevaluated elementwise chain
     bool eager = false; // DB2_EAGER=1: run every operator call immediately (no fusion)
     cudaStream_t stream = nullptr;
     // caching device allocator: freed blocks are kept by size and handed out again without calling the driver; all
@@ -147,6 +148,8 @@ int lazy_try_scalar(db2_context *ctx, int op, db2_matrix **res, db2_matrix *lhs,
 int lazy_try_unary(db2_context *ctx, int op, db2_matrix **res, db2_matrix *arg, bool *handled);
 int lazy_try_agg_row(db2_context *ctx, int op, db2_matrix **res, db2_matrix *arg, bool *handled);
 int lazy_try_agg_col(db2_context *ctx, int op, db2_matrix **res, db2_matrix *arg, bool *handled);
+// full aggregation of a deferred chain without materialising it (SUM of flat-evaluable chains); *res_host gets the value
+int lazy_try_agg_all(db2_context *ctx, int op, double *res_host, db2_matrix *arg, bool *handled);
 int lazy_force(db2_matrix *m);          // materialises a deferred matrix (and the pending siblings it can serve)
 int lazy_flush_all(db2_context *ctx);   // produces every pending aggregation
 void lazy_forget(db2_matrix *m);        // a deferred matrix is being destroyed
