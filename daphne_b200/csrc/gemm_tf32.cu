@@ -40,6 +40,10 @@ constexpr int TMEM_COLS = 512; // two main accumulators and the cross-term accum
 constexpr size_t SMEM_BYTES = (size_t)(RAW_SLOTS + LOW_SLOTS) * SLOT_BYTES + 1024 /* alignment slack */ + 256;
 constexpr long long WAIT_LIMIT_CLOCKS = 2000000000LL;
 
+// bits of the status word
+constexpr int STATUS_WAIT_EXPIRED = 1; // a bounded wait ran out: the result is not valid
+constexpr int STATUS_NONFINITE = 2;    // an operand held inf / NaN: the result was recomputed by the plain kernel
+
 struct TcArgs {
     const float *A, *B;
     float *C, *part;
@@ -253,21 +257,24 @@ __device__ __forceinline__ void issue_planned(PacketPlan &pl, uint32_t tile) {
 
 // The tensor core reads an f32 bit pattern as TF32 by ignoring the low 13 mantissa bits, so the raw tile already is
 // the high part  hi = x with those bits cleared;  lo = tf32(x - hi)  (the difference is exact) goes to a second tile.
-__device__ __forceinline__ float low_part(float x) {
+__device__ __forceinline__ float low_part(float x, bool &non_finite) {
     const uint32_t b = __float_as_uint(x);
-    if ((b & 0x7F800000u) == 0x7F800000u)
-        return 0.f; // inf / NaN: the high part alone carries it into the product
+    if ((b & 0x7F800000u) == 0x7F800000u) {
+        non_finite = true; // inf / NaN: the split product would turn inf * 1 into inf * 0 = NaN; see STATUS_NONFINITE
+        return 0.f;
+    }
     const float d = x - __uint_as_float(b & 0xFFFFE000u);
     uint32_t l;
     asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(l) : "f"(d));
     return __uint_as_float(l);
 }
-template <bool KMAJ> __device__ __forceinline__ void make_low_tile(unsigned char *raw, unsigned char *lo, int tid) {
+template <bool KMAJ>
+__device__ __forceinline__ void make_low_tile(unsigned char *raw, unsigned char *lo, int tid, bool &nf) {
 #pragma unroll
     for (int i = 0; i < 4; i++) {
         const uint32_t off = packet_offset<KMAJ>(tid + i * PRODUCER_THREADS);
         const float4 x = *reinterpret_cast<const float4 *>(raw + off);
-        *reinterpret_cast<float4 *>(lo + off) = make_float4(low_part(x.x), low_part(x.y), low_part(x.z), low_part(x.w));
+        *reinterpret_cast<float4 *>(lo + off) = make_float4(low_part(x.x, nf), low_part(x.y, nf), low_part(x.z, nf), low_part(x.w, nf));
     }
 }
 
@@ -350,6 +357,7 @@ template <bool TA, bool TB> __global__ void __launch_bounds__(THREADS, 1) gemm_t
             else
                 issue_tile<B_KMAJ>(g.B, g.ldb, n0, g.N, k0, kend, fast_b, tid, st + TILE_BYTES);
         };
+        bool non_finite = false;
         for (int kb = 0; kb < LOOKAHEAD; kb++) {
             if (kb < nkb)
                 issue(kb);
@@ -360,8 +368,8 @@ template <bool TA, bool TB> __global__ void __launch_bounds__(THREADS, 1) gemm_t
             if (kb >= LOW_SLOTS && !mma_done(kb - LOW_SLOTS))
                 break;
             unsigned char *raw = tiles + (kb % RAW_SLOTS) * SLOT_BYTES, *low = low_tiles + (kb % LOW_SLOTS) * SLOT_BYTES;
-            make_low_tile<A_KMAJ>(raw, low, tid);
-            make_low_tile<B_KMAJ>(raw + TILE_BYTES, low + TILE_BYTES, tid);
+            make_low_tile<A_KMAJ>(raw, low, tid, non_finite);
+            make_low_tile<B_KMAJ>(raw + TILE_BYTES, low + TILE_BYTES, tid, non_finite);
             fence_proxy_async_smem(); // own cp.async data and stores -> visible to the tensor core's async proxy
             mbar_arrive(smem_u32(full + kb % LOW_SLOTS));
             // refill the raw slot that k-block kb - 1 is leaving (its MMAs ran while this block was prepared)
@@ -374,6 +382,8 @@ template <bool TA, bool TB> __global__ void __launch_bounds__(THREADS, 1) gemm_t
             cp_async_commit();
         }
         cp_async_wait<0>();
+        if (non_finite)
+            atomicOr(g.status, STATUS_NONFINITE);
     } else if (warp == MMA_WARP) {
         if (lane == 0) {
             // ---------------- MMA issuer ----------------
@@ -476,7 +486,7 @@ template <bool TA, bool TB> __global__ void __launch_bounds__(THREADS, 1) gemm_t
     tc_fence_before();
     __syncthreads();
     if (tid == 0 && *abort)
-        atomicExch(g.status, 1);
+        atomicOr(g.status, STATUS_WAIT_EXPIRED);
     if (warp == MMA_WARP) {
         tc_fence_after();
         tmem_dealloc(tmem_base, TMEM_COLS);
@@ -495,6 +505,26 @@ __global__ void tf32_reduce_kernel(const float *__restrict__ part, float *__rest
         for (int s = 1; s < splits; s++)
             acc += part[(int64_t)s * total + src];
         C[r * ldc + c] = acc;
+    }
+}
+
+// Operands with inf / NaN: the split products cannot keep IEEE semantics (inf * 1 becomes inf * 1 + inf * 0), so the
+// whole product is recomputed with plain f32 FMAs.  Launched after every tensor-core product; returns at once unless
+// the producers raised STATUS_NONFINITE.
+__global__ void __launch_bounds__(256)
+    gemm_f32_plain_kernel(const TcArgs g, int ta, int tb) {
+    if (!(*g.status & STATUS_NONFINITE))
+        return;
+    const int64_t total = g.M * g.N;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t r = i / g.N, c = i % g.N;
+        float acc = 0.f;
+        for (int64_t k = 0; k < g.K; k++) {
+            const float a = ta ? g.A[k * g.lda + r] : g.A[r * g.lda + k];
+            const float b = tb ? g.B[c * g.ldb + k] : g.B[k * g.ldb + c];
+            acc = fmaf(a, b, acc);
+        }
+        g.C[r * g.ldc + c] = acc;
     }
 }
 
@@ -594,7 +624,8 @@ int tf32_gemm(const float *A, int64_t lda, bool ta, const float *B, int64_t ldb,
         tf32_reduce_kernel<<<(unsigned)blocks, 256, 0, st>>>(g.part, C, ldc, M, N, p.splits, syrk ? 1 : 0);
         DB2_TRY(after_launch("tf32_reduce_kernel"));
     }
-    return DB2_OK;
+    gemm_f32_plain_kernel<<<sm_count() * 4, 256, 0, st>>>(g, ta ? 1 : 0, tb ? 1 : 0);
+    return after_launch("gemm_f32_plain_kernel");
 }
 
 } // namespace tc

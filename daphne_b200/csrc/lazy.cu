@@ -372,6 +372,8 @@ static int run_row_pass(db2_context *ctx, const Expr &longest, db2_matrix *ew_ta
 int lazy_force(db2_matrix *m) {
     db2_context *ctx = m->ctx;
     bind_device(ctx);
+    if (m->onehot)
+        return onehot_force(m);
     const uint64_t before = g_launches.load();
     int rc = DB2_OK;
     if (m->lazy) {

@@ -1,0 +1,202 @@
+// One-hot matrices that are never written out.
+//
+// K-means builds the assignment matrix  P = ctable(seq(0, n-1), a, 1.0, n, k)  (CTable.h:55-106: one entry per row) only
+// to multiply it,  t(P) @ X  (MatMul.cpp:284-288: a dense 50 x 1M by 1M x 64 dgemm in the reference), and to count its
+// columns,  sum(P, 1)  (AggCol.h:135-141).  Written out, P is n x k doubles (400 MB for n = 1M, k = 50) that are
+// produced once and read twice per iteration.  Here the result of such a ctable call keeps only (a, weight): a matrix
+// with db2_matrix::onehot set has no placement until something else needs its values (then the dense rows are
+// written by the ordinary ctable kernel).  The two consumers above run directly on the index vector:
+//   t(P) @ X   = per-cluster sums of the rows of X: every warp keeps private k x d accumulators in shared memory and
+//                adds its rows to them (no atomics, fixed row order), warps and CTAs are summed in a fixed order;
+//   sum(P, 1)  = histogram of a (integer counts, exact).
+#include "runtime.h"
+
+namespace db2 {
+
+constexpr int SEG_MAX_WARPS = 8;
+constexpr size_t SEG_SMEM_LIMIT = 200 * 1024;
+
+// accumulators acc[warp][cluster][column]; rows of the CTA's slice are dealt to the warps round robin
+__global__ void __launch_bounds__(SEG_MAX_WARPS * 32)
+    onehot_segsum_kernel(const int64_t *__restrict__ idx, int64_t idx_ld, const double *__restrict__ X, int64_t ldx,
+                         int64_t n, int d, int k, int vec, double *__restrict__ partials) {
+    extern __shared__ double acc[];
+    const int warps = blockDim.x / 32, warp = threadIdx.x / 32, lane = threadIdx.x % 32;
+    const int kd = k * d;
+    for (int e = threadIdx.x; e < warps * kd; e += blockDim.x)
+        acc[e] = 0.0;
+    __syncthreads();
+    double *mine = acc + warp * kd;
+    const int64_t per = (n + gridDim.x - 1) / gridDim.x;
+    const int64_t lo = (int64_t)blockIdx.x * per, hi = lo + per < n ? lo + per : n;
+    constexpr int U = 4; // rows in flight per warp
+    for (int64_t r0 = lo + warp; r0 < hi; r0 += (int64_t)warps * U) {
+        int64_t c[U];
+#pragma unroll
+        for (int u = 0; u < U; u++) {
+            const int64_t r = r0 + (int64_t)u * warps;
+            c[u] = r < hi ? idx[r * idx_ld] : -1;
+        }
+        if (vec && d == 64) {
+            // one row = 32 lanes x 16 bytes
+            double2 x[U];
+#pragma unroll
+            for (int u = 0; u < U; u++) {
+                const int64_t r = r0 + (int64_t)u * warps;
+                x[u] = (c[u] >= 0 && c[u] < k) ? __ldcs(reinterpret_cast<const double2 *>(X + r * ldx) + lane)
+                                                : make_double2(0.0, 0.0);
+            }
+#pragma unroll
+            for (int u = 0; u < U; u++)
+                if (c[u] >= 0 && c[u] < k) {
+                    double2 *a = reinterpret_cast<double2 *>(mine + c[u] * d) + lane;
+                    double2 t = *a;
+                    t.x = __dadd_rn(t.x, x[u].x);
+                    t.y = __dadd_rn(t.y, x[u].y);
+                    *a = t;
+                }
+        } else {
+#pragma unroll
+            for (int u = 0; u < U; u++)
+                if (c[u] >= 0 && c[u] < k) {
+                    const int64_t r = r0 + (int64_t)u * warps;
+                    for (int j = lane; j < d; j += 32)
+                        mine[c[u] * d + j] = __dadd_rn(mine[c[u] * d + j], X[r * ldx + j]);
+                }
+        }
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e < kd; e += blockDim.x) {
+        double t = acc[e];
+        for (int w = 1; w < warps; w++)
+            t = __dadd_rn(t, acc[w * kd + e]);
+        partials[(int64_t)blockIdx.x * kd + e] = t;
+    }
+}
+
+__global__ void onehot_segsum_final_kernel(const double *__restrict__ partials, int parts, int kd, int d,
+                                           double *__restrict__ out, int64_t ldo) {
+    for (int e = blockIdx.x * blockDim.x + threadIdx.x; e < kd; e += gridDim.x * blockDim.x) {
+        double t = partials[e];
+        for (int p = 1; p < parts; p++)
+            t = __dadd_rn(t, partials[(int64_t)p * kd + e]);
+        out[(int64_t)(e / d) * ldo + e % d] = t;
+    }
+}
+
+__global__ void onehot_hist_kernel(const int64_t *__restrict__ idx, int64_t idx_ld, int64_t n, int k,
+                                   unsigned long long *__restrict__ counts) {
+    extern __shared__ unsigned int h[];
+    for (int e = threadIdx.x; e < k; e += blockDim.x)
+        h[e] = 0u;
+    __syncthreads();
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t c = idx[i * idx_ld];
+        if (c >= 0 && c < k)
+            atomicAdd(h + c, 1u);
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e < k; e += blockDim.x)
+        if (h[e])
+            atomicAdd(counts + e, (unsigned long long)h[e]);
+}
+__global__ void onehot_hist_final_kernel(const unsigned long long *__restrict__ counts, int k, double *__restrict__ out) {
+    for (int e = blockIdx.x * blockDim.x + threadIdx.x; e < k; e += gridDim.x * blockDim.x)
+        out[e] = (double)counts[e];
+}
+
+static void count(db2_context *ctx, uint64_t before) {
+    std::lock_guard<std::mutex> lock(ctx->mu);
+    ctx->stats.launches += g_launches.load(std::memory_order_relaxed) - before;
+}
+
+// writes the dense rows of a one-hot matrix (someone needs its values after all)
+int onehot_force(db2_matrix *m) {
+    db2_context *ctx = m->ctx;
+    bind_device(ctx);
+    const uint64_t before = g_launches.load();
+    std::shared_ptr<const OneHot> oh = m->onehot;
+    m->dev = make_devbuf(ctx, (size_t)m->rows * m->cols * 8);
+    m->dev_off = 0;
+    m->dev_ld = m->cols;
+    DB2_TRY(db2k_ctable(nullptr, 1, oh->idx.ptr(8), oh->idx.ld, m->rows, oh->weight, m->dev->ptr, m->rows, m->cols,
+                        m->dev_ld, 1, ctx->stream));
+    m->dev_valid = true;
+    m->onehot.reset();
+    count(ctx, before);
+    return DB2_OK;
+}
+
+// t(P) @ X for a one-hot P (weight 1): *handled stays false when the shapes do not fit the kernel
+int onehot_try_matmul(db2_context *ctx, db2_matrix **res, db2_matrix *lhs, db2_matrix *rhs, int transa, int transb,
+                      bool *handled) {
+    *handled = false;
+    if (!lhs->onehot || lhs->dev_valid || !transa || transb || rhs->dtype != DB2_F64 || lhs->onehot->weight != 1.0)
+        return DB2_OK;
+    const int64_t n = lhs->rows, k = lhs->cols, d = rhs->cols;
+    if (rhs->rows != n || k < 1 || d < 1 || (size_t)k * d * 8 > SEG_SMEM_LIMIT || n < 1)
+        return DB2_OK;
+    int warps = SEG_MAX_WARPS;
+    while ((size_t)warps * k * d * 8 > SEG_SMEM_LIMIT)
+        warps /= 2;
+    const uint64_t before = g_launches.load();
+    DB2_TRY(ensure_device(rhs));
+    DB2_TRY(prepare_result(ctx, res, DB2_F64, k, d));
+    const int grid = sm_count();
+    void *scratch = nullptr;
+    DB2_TRY(ctx_scratch(ctx, (size_t)grid * k * d * 8, &scratch));
+    const size_t smem = (size_t)warps * k * d * 8;
+    static bool attr = false;
+    if (!attr) {
+        DB2_CUDA(cudaFuncSetAttribute(onehot_segsum_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      (int)SEG_SMEM_LIMIT));
+        attr = true;
+    }
+    std::shared_ptr<const OneHot> oh = lhs->onehot;
+    const double *X = static_cast<const double *>(rhs->dev_ptr());
+    const int vec = aligned16(X) && rhs->dev_ld % 2 == 0;
+    onehot_segsum_kernel<<<grid, warps * 32, smem, ctx->stream>>>(static_cast<const int64_t *>(oh->idx.ptr(8)),
+                                                                  oh->idx.ld, X, rhs->dev_ld, n, (int)d, (int)k, vec,
+                                                                  static_cast<double *>(scratch));
+    DB2_TRY(after_launch("onehot_segsum_kernel"));
+    const int kd = (int)(k * d);
+    onehot_segsum_final_kernel<<<(kd + 255) / 256, 256, 0, ctx->stream>>>(
+        static_cast<const double *>(scratch), grid, kd, (int)d, static_cast<double *>((*res)->dev_ptr()),
+        (*res)->dev_ld);
+    DB2_TRY(after_launch("onehot_segsum_final_kernel"));
+    count(ctx, before);
+    *handled = true;
+    return DB2_OK;
+}
+
+// sum(P, 1) for a one-hot P (weight 1): the histogram of the index vector
+int onehot_try_agg_col(db2_context *ctx, int op, db2_matrix **res, db2_matrix *arg, bool *handled) {
+    *handled = false;
+    if (!arg->onehot || arg->dev_valid || op != DB2_AGG_SUM || arg->onehot->weight != 1.0 || arg->cols > 8192 ||
+        arg->rows >= (int64_t)1 << 53)
+        return DB2_OK;
+    const uint64_t before = g_launches.load();
+    const int k = (int)arg->cols;
+    DB2_TRY(prepare_result(ctx, res, DB2_F64, 1, k));
+    DB2_CHECK((*res)->dev_ld >= 1, DB2_EINVAL, "bad result");
+    void *scratch = nullptr;
+    DB2_TRY(ctx_scratch(ctx, (size_t)k * 8, &scratch));
+    DB2_CUDA(cudaMemsetAsync(scratch, 0, (size_t)k * 8, ctx->stream));
+    std::shared_ptr<const OneHot> oh = arg->onehot;
+    if (arg->rows > 0) {
+        int64_t want = (arg->rows + 255) / 256;
+        const int64_t cap = (int64_t)sm_count() * 8;
+        onehot_hist_kernel<<<(unsigned)(want < cap ? want : cap), 256, (size_t)k * 4, ctx->stream>>>(
+            static_cast<const int64_t *>(oh->idx.ptr(8)), oh->idx.ld, arg->rows, k,
+            static_cast<unsigned long long *>(scratch));
+        DB2_TRY(after_launch("onehot_hist_kernel"));
+    }
+    onehot_hist_final_kernel<<<(k + 255) / 256, 256, 0, ctx->stream>>>(
+        static_cast<const unsigned long long *>(scratch), k, static_cast<double *>((*res)->dev_ptr()));
+    DB2_TRY(after_launch("onehot_hist_final_kernel"));
+    count(ctx, before);
+    *handled = true;
+    return DB2_OK;
+}
+
+} // namespace db2

@@ -21,14 +21,15 @@ static void count(db2_context *ctx, uint64_t before) {
 }
 
 // The f32 contraction (tensor-core kernel with bounded waits) leaves a status word at the start of its scratch area;
-// a non-zero word means a wait expired and the result is not valid.
+// bit 0 set means a wait expired and the result is not valid (bit 1: operands held inf / NaN and the
+// product was recomputed by the plain kernel, which is not an error).
 static int check_contraction_status(db2_context *ctx, int dtype, const void *scratch) {
     if (dtype != DB2_F32)
         return DB2_OK;
     int32_t st = 0;
     DB2_CUDA(cudaMemcpyAsync(&st, scratch, sizeof(st), cudaMemcpyDeviceToHost, ctx->stream));
     DB2_CUDA(cudaStreamSynchronize(ctx->stream));
-    DB2_CHECK(st == 0, DB2_ECUDA, "f32 contraction kernel gave up waiting (status %d); result discarded", (int)st);
+    DB2_CHECK((st & 1) == 0, DB2_ECUDA, "f32 contraction kernel gave up waiting (status %d); result discarded", (int)st);
     return DB2_OK;
 }
 
@@ -49,6 +50,12 @@ int db2_matMul(db2_context *ctx, db2_matrix **res, db2_matrix *lhs, db2_matrix *
     DB2_CHECK(k == k2, DB2_EINVAL, "MatMul - #cols of lhs and #rows of rhs must be the same, but got%lldand%lld",
               (long long)k, (long long)k2);
     bind_device(ctx);
+    {
+        bool handled = false;
+        DB2_TRY(onehot_try_matmul(ctx, res, lhs, rhs, transa, transb, &handled));
+        if (handled)
+            return DB2_OK;
+    }
     const uint64_t before = g_launches.load();
     DB2_TRY(ensure_device(lhs));
     DB2_TRY(ensure_device(rhs));
@@ -238,6 +245,11 @@ int db2_seq(db2_context *ctx, db2_matrix **res, int dtype, const void *start_p, 
     const uint64_t before = g_launches.load();
     DB2_TRY(prepare_result(ctx, res, dtype, n, 1));
     DB2_TRY(db2k_seq(dtype, (*res)->dev_ptr(), n, start_p, inc_p, ctx->stream));
+    if (dtype == DB2_I64 && !(*res)->is_view) {
+        (*res)->is_seq = true;
+        (*res)->seq_start = *static_cast<const int64_t *>(start_p);
+        (*res)->seq_inc = *static_cast<const int64_t *>(inc_p);
+    }
     count(ctx, before);
     return DB2_OK;
     DB2_API_END
@@ -270,6 +282,26 @@ int db2_ctable(db2_context *ctx, db2_matrix **res, db2_matrix *lhs, db2_matrix *
     DB2_TRY(ensure_device(lhs));
     DB2_TRY(ensure_device(rhs));
     const int64_t n = lhs->rows;
+    // lhs = seq(0, n - 1): exactly one entry per row, in row order.  The result is kept as (rhs, weight) and written
+    // out only if something other than t(P) @ X or sum(P, 1) asks for its values.
+    if (*res == nullptr && !ctx->eager && lhs->is_seq && lhs->seq_start == 0 && lhs->seq_inc == 1 && n > 0 &&
+        (res_rows == n || res_rows < 0) && res_cols > 0) {
+        db2_matrix *r = new db2_matrix();
+        r->ctx = ctx;
+        r->dtype = DB2_F64;
+        r->rows = n;
+        r->cols = res_cols;
+        auto oh = std::make_shared<OneHot>();
+        oh->idx.buf = rhs->dev;
+        oh->idx.off = rhs->dev_off;
+        oh->idx.ld = rhs->dev_ld;
+        oh->idx.rows = n;
+        oh->idx.cols = 1;
+        oh->weight = weight;
+        r->onehot = oh;
+        *res = r;
+        return DB2_OK;
+    }
     if (res_rows < 0 || res_cols < 0) {
         DB2_CHECK(n > 0, DB2_EINVAL, "ctable: cannot derive the result shape from empty coordinate vectors");
         long long *dmax = reinterpret_cast<long long *>(ctx->dev_status + 16);

@@ -167,7 +167,9 @@ int prepare_result(db2_context *ctx, db2_matrix **res, int dtype, int64_t rows, 
         r->lazy.reset();
         r->pend_src.reset();
         r->pend_op = -1;
+        r->onehot.reset();
     }
+    r->is_seq = false;
     // a buffer that deferred chains (or other handles) still read is not overwritten: the result gets a fresh one.
     // Row views are the exception: writing through a view is how results are placed into a larger matrix.
     if (!r->dev || (!r->is_view && r->dev.use_count() > 1)) {
@@ -539,6 +541,9 @@ int db2_aggCol(db2_context *ctx, int op, db2_matrix **res, db2_matrix *arg) {
     const uint64_t before = g_launches.load();
     DB2_CHECK(res, DB2_EINVAL, "null result slot");
     bool handled = false;
+    DB2_TRY(onehot_try_agg_col(ctx, op, res, arg, &handled));
+    if (handled)
+        return DB2_OK;
     DB2_TRY(lazy_try_agg_col(ctx, op, res, arg, &handled));
     if (handled) {
         count_launches(ctx, before);

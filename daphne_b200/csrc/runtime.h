@@ -11,10 +11,12 @@
 #include <string>
 #include <vector>
 
-struct db2_matrix;
 namespace db2 {
 struct Expr;
-}
+struct OneHot;
+} // namespace db2
+
+struct db2_matrix;
 
 struct db2_context {
     int device = 0;
@@ -102,9 +104,15 @@ struct db2_matrix {
     std::shared_ptr<const db2::Expr> pend_src;
     int pend_op = -1;
 
+    // one-hot rows (r, idx[r]) = weight that have not been written out (onehot.cu)
+    std::shared_ptr<const db2::OneHot> onehot;
+    // the matrix is the int64 sequence seq_start, seq_start + seq_inc, ... (set by db2_seq; values are on the device too)
+    bool is_seq = false;
+    int64_t seq_start = 0, seq_inc = 0;
+
     bool is_view = false; // shares its buffers with a parent (row slice): results written through it stay in place
 
-    bool deferred() const { return (bool)lazy || (bool)pend_src; }
+    bool deferred() const { return (bool)lazy || (bool)pend_src || (bool)onehot; }
     size_t esize() const { return db2::dtype_size(dtype); }
     void *dev_ptr() const { return static_cast<char *>(dev->ptr) + dev_off * (int64_t)esize(); }
     void *host_ptr() const { return static_cast<char *>(host->ptr) + host_off * (int64_t)esize(); }
@@ -142,6 +150,14 @@ struct Expr {
     Operand base;
     std::vector<ExprStep> steps;
 };
+struct OneHot { // rows x cols matrix with one stored entry per row: (r, idx[r]) = weight
+    Operand idx; // int64 column vector
+    double weight = 1.0;
+};
+int onehot_force(db2_matrix *m); // writes the dense rows
+int onehot_try_matmul(db2_context *ctx, db2_matrix **res, db2_matrix *lhs, db2_matrix *rhs, int transa, int transb,
+                      bool *handled);
+int onehot_try_agg_col(db2_context *ctx, int op, db2_matrix **res, db2_matrix *arg, bool *handled);
 // Each returns DB2_OK and sets *handled when the call was recorded instead of executed.
 int lazy_try_binary(db2_context *ctx, int op, db2_matrix **res, db2_matrix *lhs, db2_matrix *rhs, bool *handled);
 int lazy_try_scalar(db2_context *ctx, int op, db2_matrix **res, db2_matrix *lhs, const void *scalar, bool *handled);
