@@ -84,4 +84,18 @@ size_t fused_flat_scratch_bytes();
 int fused_flat_pass_f64(const FusedProgram &prog, void *mid_out, int mid_after, double *sum_out, void *scratch,
                         size_t scratch_bytes, cudaStream_t st);
 
+// tall-skinny product with fused row epilogue (skinny.cu): D = A @ op(B), then prog.steps on D, prog.taps (row MIN /
+// MAX with positions, at the end of the chain) and prog.ew_out (the values after all steps); prog.base is not used
+struct SkinnyArgs {
+    const double *A;
+    int64_t lda, n;
+    const double *B;
+    int64_t ldb;
+    int K, N, tb; // tb: B is stored N x K
+    FusedProgram prog;
+};
+bool skinny_shape_ok(int64_t n, int64_t K, int64_t N, const void *A, int64_t lda);
+bool skinny_op_supported(int fused_op);
+int skinny_gemm(const SkinnyArgs &a, cudaStream_t st);
+
 } // namespace db2

@@ -103,8 +103,9 @@ int lazy_try_binary(db2_context *ctx, int op, db2_matrix **res, db2_matrix *lhs,
     const int fop = fused_binary_op(op);
     if (*res != nullptr || fop < 0 || !lazy_candidate(ctx, lhs) || rhs->dtype != DB2_F64)
         return DB2_OK;
-    if (lhs->pend_src || rhs->pend_src) // pending aggregates are column vectors that have to exist first
+    if (lhs->pend_src) // a pending aggregate is a column vector: it is produced and the operator runs at once
         return DB2_OK;
+    // (a pending rhs is produced by operand_of below and becomes an ordinary operand of the chain)
     int kind;
     if (lhs->rows == rhs->rows && lhs->cols == rhs->cols)
         kind = FK_MATRIX;
@@ -207,7 +208,7 @@ int lazy_try_agg_row(db2_context *ctx, int op, db2_matrix **res, db2_matrix *arg
     // bound the backlog: a full group is produced right away
     int same_base = 0;
     for (db2_matrix *p : ctx->pending)
-        if (p->pend_src->base.same(e->base))
+        if (p->pend_src->same_base(*e))
             same_base++;
     if (same_base >= FUSED_MAX_AGGS)
         return lazy_force(r);
@@ -218,8 +219,8 @@ int lazy_try_agg_row(db2_context *ctx, int op, db2_matrix **res, db2_matrix *arg
 // built above)
 static void build_program(const Expr &e, size_t nsteps, FusedProgram *P) {
     memset(P, 0, sizeof(*P));
-    P->base = e.base.ptr(8);
-    P->base_ld = e.base.ld;
+    P->base = e.gemm ? nullptr : e.base.ptr(8);
+    P->base_ld = e.gemm ? e.cols : e.base.ld;
     P->rows = e.rows;
     P->cols = e.cols;
     P->nsteps = (int)nsteps;
@@ -249,7 +250,7 @@ static void build_program(const Expr &e, size_t nsteps, FusedProgram *P) {
 }
 
 static bool is_prefix(const Expr &a, const Expr &b) { // a's chain is a prefix of b's (same base)
-    if (!a.base.same(b.base) || a.rows != b.rows || a.cols != b.cols || a.steps.size() > b.steps.size())
+    if (!a.same_base(b) || a.rows != b.rows || a.cols != b.cols || a.steps.size() > b.steps.size())
         return false;
     for (size_t i = 0; i < a.steps.size(); i++)
         if (!a.steps[i].same(b.steps[i]))
@@ -309,7 +310,65 @@ static int tap_kind_of(int agg_op) {
 // (members that do not fit the tap slots stay pending).  MIN/IDXMIN and MAX/IDXMAX of the same chain position share
 // one tracker.
 static int run_row_pass(db2_context *ctx, const Expr &longest, db2_matrix *ew_target,
+                        const std::vector<db2_matrix *> &group);
+
+static void fill_skinny(const Expr &e, SkinnyArgs *a) {
+    const GemmSrc &g = *e.gemm;
+    a->A = static_cast<const double *>(g.A.ptr(8));
+    a->lda = g.A.ld;
+    a->n = e.rows;
+    a->B = static_cast<const double *>(g.B.ptr(8));
+    a->ldb = g.B.ld;
+    a->K = (int)g.K;
+    a->N = (int)e.cols;
+    a->tb = g.tb ? 1 : 0;
+}
+
+// can chain and aggregations be applied to the accumulators of the product?
+static bool gemm_pass_fusable(const Expr &e, const std::vector<db2_matrix *> &group) {
+    for (const ExprStep &s : e.steps)
+        if (s.kind == FK_MATRIX || !skinny_op_supported(s.op))
+            return false;
+    std::vector<int> kinds;
+    for (const db2_matrix *g : group) {
+        const int op = g->pend_op;
+        if (g->pend_src->steps.size() != e.steps.size() ||
+            !(op == DB2_AGG_MIN || op == DB2_AGG_MAX || op == DB2_AGG_IDXMIN || op == DB2_AGG_IDXMAX))
+            return false;
+    }
+    return true;
+}
+
+static int run_row_pass(db2_context *ctx, const Expr &longest, db2_matrix *ew_target,
                         const std::vector<db2_matrix *> &group) {
+    if (longest.gemm && !gemm_pass_fusable(longest, group)) {
+        // the product is written out and the ordinary pass runs on it
+        Expr plain = longest;
+        plain.gemm.reset();
+        plain.base.buf = make_devbuf(ctx, (size_t)longest.rows * longest.cols * 8);
+        plain.base.off = 0;
+        plain.base.ld = longest.cols;
+        plain.base.rows = longest.rows;
+        plain.base.cols = longest.cols;
+        SkinnyArgs a;
+        memset(&a, 0, sizeof(a));
+        fill_skinny(longest, &a);
+        a.prog.rows = longest.rows;
+        a.prog.cols = longest.cols;
+        a.prog.ew_out = plain.base.buf->ptr;
+        a.prog.ew_out_ld = longest.cols;
+        DB2_TRY(skinny_gemm(a, ctx->stream));
+        if (plain.steps.empty() && group.empty() && ew_target) { // the product itself was wanted
+            ew_target->dev = plain.base.buf;
+            ew_target->dev_off = 0;
+            ew_target->dev_ld = longest.cols;
+            ew_target->dev_valid = true;
+            unlazy(ew_target);
+            ew_target->lazy.reset();
+            return DB2_OK;
+        }
+        return run_row_pass(ctx, plain, ew_target, group);
+    }
     FusedProgram P;
     build_program(longest, longest.steps.size(), &P);
     if (ew_target) {
@@ -350,7 +409,13 @@ static int run_row_pass(db2_context *ctx, const Expr &longest, db2_matrix *ew_ta
     }
     int rc = DB2_OK;
     const std::string sig = signature_of(P);
-    if (fused_flat_eligible(P))
+    if (longest.gemm) {
+        SkinnyArgs a;
+        memset(&a, 0, sizeof(a));
+        fill_skinny(longest, &a);
+        a.prog = P;
+        rc = skinny_gemm(a, ctx->stream);
+    } else if (fused_flat_eligible(P))
         rc = fused_flat_pass_f64(P, nullptr, 0, nullptr, nullptr, 0, ctx->stream);
     else if (!fused_row_pass_ct(P, sig.c_str(), ctx->stream, &rc))
         rc = fused_row_pass_f64(P, ctx->stream);
@@ -430,6 +495,8 @@ int lazy_try_agg_col(db2_context *ctx, int op, db2_matrix **res, db2_matrix *arg
     if (!ok)
         return DB2_OK; // VAR/STDDEV: the argument is materialised and the two-pass kernels run
     std::shared_ptr<const Expr> e = arg->lazy;
+    if (e->gemm)
+        return DB2_OK; // the deferred product is produced first (ensure_device), then the column kernels run
     const bool idx = op == DB2_AGG_IDXMIN || op == DB2_AGG_IDXMAX;
     DB2_TRY(prepare_result(ctx, res, idx ? DB2_U64 : DB2_F64, 1, arg->cols));
     FusedProgram P;
@@ -445,6 +512,32 @@ int lazy_try_agg_col(db2_context *ctx, int op, db2_matrix **res, db2_matrix *arg
     return DB2_OK;
 }
 
+int lazy_try_matmul(db2_context *ctx, db2_matrix **res, db2_matrix *lhs, db2_matrix *rhs, int transa, int transb,
+                    bool *handled) {
+    *handled = false;
+    if (*res != nullptr || ctx->eager || transa || lhs->dtype != DB2_F64 || rhs->dtype != DB2_F64)
+        return DB2_OK;
+    const int64_t m = lhs->rows, k = lhs->cols, n = transb ? rhs->rows : rhs->cols;
+    if ((transb ? rhs->cols : rhs->rows) != k || m * n < LAZY_MIN_ELEMS || n > 64 || k > 128)
+        return DB2_OK;
+    auto g = std::make_shared<GemmSrc>();
+    DB2_TRY(operand_of(lhs, &g->A));
+    DB2_TRY(operand_of(rhs, &g->B));
+    if (!skinny_shape_ok(m, k, n, g->A.ptr(8), g->A.ld))
+        return DB2_OK;
+    g->tb = transb != 0;
+    g->K = k;
+    auto e = std::make_shared<Expr>();
+    e->rows = m;
+    e->cols = n;
+    e->gemm = g;
+    db2_matrix *r = new_deferred(ctx, DB2_F64, m, n);
+    set_lazy(r, e);
+    *res = r;
+    *handled = true;
+    return DB2_OK;
+}
+
 // sum(chain) in one flat pass; a live deferred matrix whose chain is a proper prefix (e.g. u of sum(u != c)) is
 // materialised by the same pass
 int lazy_try_agg_all(db2_context *ctx, int op, double *res_host, db2_matrix *arg, bool *handled) {
@@ -452,6 +545,8 @@ int lazy_try_agg_all(db2_context *ctx, int op, double *res_host, db2_matrix *arg
     if (!arg->lazy || ctx->eager || op != DB2_AGG_SUM || arg->dtype != DB2_F64)
         return DB2_OK;
     std::shared_ptr<const Expr> e = arg->lazy;
+    if (e->gemm)
+        return DB2_OK;
     FusedProgram P;
     build_program(*e, e->steps.size(), &P);
     if (!fused_flat_eligible(P))

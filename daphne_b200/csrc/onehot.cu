@@ -16,7 +16,7 @@ namespace db2 {
 constexpr int SEG_MAX_WARPS = 8;
 constexpr size_t SEG_SMEM_LIMIT = 200 * 1024;
 
-// accumulators acc[warp][cluster][column]; rows of the CTA's slice are dealt to the warps round robin
+// accumulators acc[warp][cluster][column]
 __global__ void __launch_bounds__(SEG_MAX_WARPS * 32)
     onehot_segsum_kernel(const int64_t *__restrict__ idx, int64_t idx_ld, const double *__restrict__ X, int64_t ldx,
                          int64_t n, int d, int k, int vec, double *__restrict__ partials) {
@@ -27,42 +27,49 @@ __global__ void __launch_bounds__(SEG_MAX_WARPS * 32)
         acc[e] = 0.0;
     __syncthreads();
     double *mine = acc + warp * kd;
-    const int64_t per = (n + gridDim.x - 1) / gridDim.x;
-    const int64_t lo = (int64_t)blockIdx.x * per, hi = lo + per < n ? lo + per : n;
-    constexpr int U = 4; // rows in flight per warp
-    for (int64_t r0 = lo + warp; r0 < hi; r0 += (int64_t)warps * U) {
-        int64_t c[U];
+    // every warp owns a contiguous run of rows and walks it in order, 32 rows per batch: one coalesced load of the 32
+    // cluster numbers (the next batch's is issued before this batch is processed), then 16 rows of X in flight
+    const int64_t total_warps = (int64_t)gridDim.x * warps, gw = (int64_t)blockIdx.x * warps + warp;
+    const int64_t per = (n + total_warps - 1) / total_warps;
+    const int64_t lo = gw * per, hi = lo + per < n ? lo + per : n;
+    constexpr int U = 16;
+    int64_t c_next = (lo + lane < hi) ? idx[(lo + lane) * idx_ld] : -1;
+    for (int64_t b0 = lo; b0 < hi; b0 += 32) {
+        const int64_t c_mine = c_next;
+        c_next = (b0 + 32 + lane < hi) ? idx[(b0 + 32 + lane) * idx_ld] : -1;
 #pragma unroll
-        for (int u = 0; u < U; u++) {
-            const int64_t r = r0 + (int64_t)u * warps;
-            c[u] = r < hi ? idx[r * idx_ld] : -1;
-        }
-        if (vec && d == 64) {
-            // one row = 32 lanes x 16 bytes
-            double2 x[U];
+        for (int h = 0; h < 32; h += U) {
+            if (b0 + h >= hi)
+                break;
+            if (vec && d == 64) {
+                // one row = 32 lanes x 16 bytes
+                double2 x[U];
+                int cu[U];
 #pragma unroll
-            for (int u = 0; u < U; u++) {
-                const int64_t r = r0 + (int64_t)u * warps;
-                x[u] = (c[u] >= 0 && c[u] < k) ? __ldcs(reinterpret_cast<const double2 *>(X + r * ldx) + lane)
-                                                : make_double2(0.0, 0.0);
+                for (int u = 0; u < U; u++) {
+                    const long long c = __shfl_sync(0xffffffffu, (long long)c_mine, h + u);
+                    cu[u] = (c >= 0 && c < k) ? (int)c : -1;
+                    x[u] = cu[u] >= 0 ? __ldcs(reinterpret_cast<const double2 *>(X + (b0 + h + u) * ldx) + lane)
+                                      : make_double2(0.0, 0.0);
+                }
+#pragma unroll
+                for (int u = 0; u < U; u++)
+                    if (cu[u] >= 0) {
+                        double2 *a = reinterpret_cast<double2 *>(mine + cu[u] * d) + lane;
+                        double2 t = *a;
+                        t.x = __dadd_rn(t.x, x[u].x);
+                        t.y = __dadd_rn(t.y, x[u].y);
+                        *a = t;
+                    }
+            } else {
+#pragma unroll 1
+                for (int u = 0; u < U; u++) {
+                    const long long c = __shfl_sync(0xffffffffu, (long long)c_mine, h + u);
+                    if (c >= 0 && c < k)
+                        for (int j = lane; j < d; j += 32)
+                            mine[c * d + j] = __dadd_rn(mine[c * d + j], X[(b0 + h + u) * ldx + j]);
+                }
             }
-#pragma unroll
-            for (int u = 0; u < U; u++)
-                if (c[u] >= 0 && c[u] < k) {
-                    double2 *a = reinterpret_cast<double2 *>(mine + c[u] * d) + lane;
-                    double2 t = *a;
-                    t.x = __dadd_rn(t.x, x[u].x);
-                    t.y = __dadd_rn(t.y, x[u].y);
-                    *a = t;
-                }
-        } else {
-#pragma unroll
-            for (int u = 0; u < U; u++)
-                if (c[u] >= 0 && c[u] < k) {
-                    const int64_t r = r0 + (int64_t)u * warps;
-                    for (int j = lane; j < d; j += 32)
-                        mine[c[u] * d + j] = __dadd_rn(mine[c[u] * d + j], X[r * ldx + j]);
-                }
         }
     }
     __syncthreads();
@@ -74,12 +81,22 @@ __global__ void __launch_bounds__(SEG_MAX_WARPS * 32)
     }
 }
 
-__global__ void onehot_segsum_final_kernel(const double *__restrict__ partials, int parts, int kd, int d,
-                                           double *__restrict__ out, int64_t ldo) {
-    for (int e = blockIdx.x * blockDim.x + threadIdx.x; e < kd; e += gridDim.x * blockDim.x) {
-        double t = partials[e];
-        for (int p = 1; p < parts; p++)
+// out = sum over the CTAs' partial sums in a fixed order: 32 elements per CTA, 8 thread groups each adding every 8th
+// partial, then the 8 group sums in order
+__global__ void __launch_bounds__(256)
+    onehot_segsum_final_kernel(const double *__restrict__ partials, int parts, int kd, int d, double *__restrict__ out,
+                               int64_t ldo) {
+    __shared__ double sh[8][32];
+    const int e = blockIdx.x * 32 + threadIdx.x % 32, grp = threadIdx.x / 32;
+    double t = 0.0;
+    if (e < kd)
+        for (int p = grp; p < parts; p += 8)
             t = __dadd_rn(t, partials[(int64_t)p * kd + e]);
+    sh[grp][threadIdx.x % 32] = t;
+    __syncthreads();
+    if (grp == 0 && e < kd) {
+        for (int q = 1; q < 8; q++)
+            t = __dadd_rn(t, sh[q][threadIdx.x]);
         out[(int64_t)(e / d) * ldo + e % d] = t;
     }
 }
@@ -160,7 +177,7 @@ int onehot_try_matmul(db2_context *ctx, db2_matrix **res, db2_matrix *lhs, db2_m
                                                                   static_cast<double *>(scratch));
     DB2_TRY(after_launch("onehot_segsum_kernel"));
     const int kd = (int)(k * d);
-    onehot_segsum_final_kernel<<<(kd + 255) / 256, 256, 0, ctx->stream>>>(
+    onehot_segsum_final_kernel<<<(kd + 31) / 32, 256, 0, ctx->stream>>>(
         static_cast<const double *>(scratch), grid, kd, (int)d, static_cast<double *>((*res)->dev_ptr()),
         (*res)->dev_ld);
     DB2_TRY(after_launch("onehot_segsum_final_kernel"));

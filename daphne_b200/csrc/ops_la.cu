@@ -55,6 +55,9 @@ int db2_matMul(db2_context *ctx, db2_matrix **res, db2_matrix *lhs, db2_matrix *
         DB2_TRY(onehot_try_matmul(ctx, res, lhs, rhs, transa, transb, &handled));
         if (handled)
             return DB2_OK;
+        DB2_TRY(lazy_try_matmul(ctx, res, lhs, rhs, transa, transb, &handled));
+        if (handled)
+            return DB2_OK;
     }
     const uint64_t before = g_launches.load();
     DB2_TRY(ensure_device(lhs));

@@ -144,11 +144,22 @@ struct ExprStep {
         return operand.same(o.operand);
     }
 };
+struct GemmSrc { // the base values are the product A @ op(B) (tall-skinny, skinny.cu), not yet computed
+    Operand A, B;
+    bool tb = false;
+    int64_t K = 0;
+};
 struct Expr {
     int dtype = DB2_F64;
     int64_t rows = 0, cols = 0;
-    Operand base;
+    Operand base;                        // materialised base operand, unless ...
+    std::shared_ptr<const GemmSrc> gemm; // ... the chain starts from a deferred product
     std::vector<ExprStep> steps;
+    bool same_base(const Expr &o) const {
+        if (gemm || o.gemm)
+            return gemm && o.gemm && gemm->A.same(o.gemm->A) && gemm->B.same(o.gemm->B) && gemm->tb == o.gemm->tb;
+        return base.same(o.base);
+    }
 };
 struct OneHot { // rows x cols matrix with one stored entry per row: (r, idx[r]) = weight
     Operand idx; // int64 column vector
@@ -164,6 +175,10 @@ int lazy_try_scalar(db2_context *ctx, int op, db2_matrix **res, db2_matrix *lhs,
 int lazy_try_unary(db2_context *ctx, int op, db2_matrix **res, db2_matrix *arg, bool *handled);
 int lazy_try_agg_row(db2_context *ctx, int op, db2_matrix **res, db2_matrix *arg, bool *handled);
 int lazy_try_agg_col(db2_context *ctx, int op, db2_matrix **res, db2_matrix *arg, bool *handled);
+// A @ op(B) for a tall lhs and at most 64 result columns: deferred, so that a following chain and row extremum are
+// applied to the accumulators
+int lazy_try_matmul(db2_context *ctx, db2_matrix **res, db2_matrix *lhs, db2_matrix *rhs, int transa, int transb,
+                    bool *handled);
 // full aggregation of a deferred chain without materialising it (SUM of flat-evaluable chains); *res_host gets the value
 int lazy_try_agg_all(db2_context *ctx, int op, double *res_host, db2_matrix *arg, bool *handled);
 int lazy_force(db2_matrix *m);          // materialises a deferred matrix (and the pending siblings it can serve)

@@ -1,0 +1,270 @@
+// Tall-skinny FP64 product  D = A @ op(B)  with a fused row epilogue:  A is n x K (n large, K <= 128, row-major),
+// op(B) is K x N with N <= 64.  This is the distance step of k-means,  X @ t(C)  (MatMul.cpp:284-288 in the reference:
+// one dgemm writing the n x k matrix), followed there by three elementwise kernels and a row idxMin.
+//
+// Persistent CTAs (one per SM) keep op(B) in shared memory for the whole launch and stream A through a double-buffered
+// ring of 128-row tiles (16-byte cp.async, zero fill).  Every warp owns 16 rows x all N columns, so after the DMMAs
+// (mma.sync m16n8k16 f64) a row's values sit in the four lanes of a quad: the recorded elementwise chain (scalar,
+// column-vector and row-vector operands) is applied to the accumulators in registers, the row minimum / maximum and
+// its position are reduced with two shuffles, and the n x N product itself is only written if somebody asked for it.
+#include "fused.cuh"
+#include "runtime.h"
+
+namespace db2 {
+
+constexpr int SK_ROWS = 128, SK_THREADS = 256, SK_MAXN = 64, SK_MAXK = 128;
+
+__device__ __forceinline__ void sk_dmma(double (&c)[4], const double (&a)[8], const double (&b)[4]) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f64.f64.f64.f64 {%0,%1,%2,%3}, {%4,%5,%6,%7,%8,%9,%10,%11}, "
+                 "{%12,%13,%14,%15}, {%0,%1,%2,%3};\n"
+                 : "+d"(c[0]), "+d"(c[1]), "+d"(c[2]), "+d"(c[3])
+                 : "d"(a[0]), "d"(a[1]), "d"(a[2]), "d"(a[3]), "d"(a[4]), "d"(a[5]), "d"(a[6]), "d"(a[7]), "d"(b[0]),
+                   "d"(b[1]), "d"(b[2]), "d"(b[3]));
+}
+
+// value (op) operand on NV values with the exactly rounded semantics of the elementwise kernels; the opcode is
+// dispatched once per step, not per value (the epilogue must stay small: it runs once per 128-row tile)
+template <int NV>
+__device__ __forceinline__ void sk_apply(int op, bool rev, double (&v)[NV], const double (&o)[NV]) {
+#define DB2_SK_STEP(FWD, REV)                                                                                          \
+    if (!rev) {                                                                                                        \
+        _Pragma("unroll") for (int i = 0; i < NV; i++) { const double a = v[i], b = o[i]; (void)b; v[i] = (FWD); }     \
+    } else {                                                                                                           \
+        _Pragma("unroll") for (int i = 0; i < NV; i++) { const double a = v[i], b = o[i]; (void)b; v[i] = (REV); }     \
+    }                                                                                                                  \
+    break;
+    switch (op) {
+    case FO_ADD: DB2_SK_STEP(__dadd_rn(a, b), __dadd_rn(b, a))
+    case FO_SUB: DB2_SK_STEP(__dsub_rn(a, b), __dsub_rn(b, a))
+    case FO_MUL: DB2_SK_STEP(__dmul_rn(a, b), __dmul_rn(b, a))
+    case FO_DIV: DB2_SK_STEP(__ddiv_rn(a, b), __ddiv_rn(b, a))
+    case FO_SQUARE: DB2_SK_STEP(__dmul_rn(a, a), __dmul_rn(a, a))
+    case FO_MIN: DB2_SK_STEP(((b < a) ? b : a), ((a < b) ? a : b))
+    case FO_MAX: DB2_SK_STEP(((a < b) ? b : a), ((b < a) ? a : b))
+    case FO_NEG: DB2_SK_STEP(-a, -a)
+    case FO_ABS: DB2_SK_STEP(fabs(a), fabs(a))
+    default: break;
+    }
+#undef DB2_SK_STEP
+}
+bool skinny_op_supported(int op) {
+    return op == FO_ADD || op == FO_SUB || op == FO_MUL || op == FO_DIV || op == FO_SQUARE || op == FO_MIN ||
+           op == FO_MAX || op == FO_NEG || op == FO_ABS;
+}
+
+template <int NT, bool TB>
+__global__ void __launch_bounds__(SK_THREADS, 1) skinny_gemm_kernel(const __grid_constant__ SkinnyArgs s) {
+    extern __shared__ __align__(16) double sm[];
+    const int KP = (s.K + 15) / 16 * 16, PA = KP + 4; // pitch = 4 mod 16 doubles: conflict-free fragment loads
+    const int PB = TB ? KP + 4 : NT * 8 + 4;
+    double *Bs = sm;                                   // TB: [NT*8][PB] (k contiguous);  else [KP][PB]
+    double *rv = Bs + (TB ? NT * 8 * PB : KP * PB);     // row-vector operands: [step][64]
+    double *As = rv + FUSED_MAX_STEPS * SK_MAXN;        // 2 x [128][PA]
+    const int tid = threadIdx.x, warp = tid / 32, lane = tid % 32, g = lane / 4, t = lane % 4;
+    const FusedProgram &P = s.prog;
+
+    // op(B), zero padded to NT*8 columns and KP rows of k
+    if (TB) {
+        for (int e = tid; e < NT * 8 * KP; e += SK_THREADS) {
+            const int n = e / KP, k = e % KP;
+            Bs[n * PB + k] = (n < s.N && k < s.K) ? s.B[(int64_t)n * s.ldb + k] : 0.0;
+        }
+    } else {
+        for (int e = tid; e < KP * NT * 8; e += SK_THREADS) {
+            const int k = e / (NT * 8), n = e % (NT * 8);
+            Bs[k * PB + n] = (n < s.N && k < s.K) ? s.B[(int64_t)k * s.ldb + n] : 0.0;
+        }
+    }
+    for (int st = 0; st < P.nsteps; st++)
+        if (P.steps[st].kind == FK_ROWVEC)
+            for (int c = tid; c < SK_MAXN; c += SK_THREADS)
+                rv[st * SK_MAXN + c] = c < s.N ? static_cast<const double *>(P.steps[st].ptr)[c] : 0.0;
+
+    const int64_t ntiles = (s.n + SK_ROWS - 1) / SK_ROWS;
+    const int packets = KP / 2; // 16-byte packets per row
+    auto load_tile = [&](int64_t tile, int buf) {
+        double *dst = As + (size_t)buf * SK_ROWS * PA;
+        const int64_t r0 = tile * SK_ROWS;
+        for (int e = tid; e < SK_ROWS * packets; e += SK_THREADS) {
+            const int r = e / packets, p = e % packets;
+            const int64_t row = r0 + r;
+            const int k = 2 * p;
+            int bytes = 0;
+            if (row < s.n && k < s.K)
+                bytes = (s.K - k >= 2) ? 16 : 8;
+            const unsigned d = (unsigned)__cvta_generic_to_shared(dst + r * PA + k);
+            const double *src = bytes ? s.A + row * s.lda + k : s.A;
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(d), "l"(src), "r"(bytes) : "memory");
+        }
+    };
+    int64_t tile = blockIdx.x;
+    if (tile < ntiles)
+        load_tile(tile, 0);
+    asm volatile("cp.async.commit_group;\n" ::: "memory");
+    int buf = 0;
+    for (; tile < ntiles; tile += gridDim.x, buf ^= 1) {
+        asm volatile("cp.async.wait_group 0;\n" ::: "memory");
+        __syncthreads(); // the tile has landed for everyone, and everyone has left the other buffer
+        if (tile + gridDim.x < ntiles)
+            load_tile(tile + gridDim.x, buf ^ 1);
+        asm volatile("cp.async.commit_group;\n" ::: "memory");
+
+        const double *At = As + (size_t)buf * SK_ROWS * PA + (size_t)(warp * 16) * PA;
+        double acc[NT][4];
+#pragma unroll
+        for (int nt = 0; nt < NT; nt++)
+#pragma unroll
+            for (int e = 0; e < 4; e++)
+                acc[nt][e] = 0.0;
+        double af[8];
+#pragma unroll
+        for (int i = 0; i < 8; i++)
+            af[i] = At[(g + 8 * (i & 1)) * PA + t + 4 * (i >> 1)];
+        for (int ks = 0; ks < KP; ks += 16) {
+            // fragments of the next k-step are fetched while this step's DMMAs run
+            double an[8];
+            const int kn = ks + 16 < KP ? ks + 16 : ks;
+#pragma unroll
+            for (int i = 0; i < 8; i++)
+                an[i] = At[(g + 8 * (i & 1)) * PA + kn + t + 4 * (i >> 1)];
+            double bf[NT][4];
+#pragma unroll
+            for (int nt = 0; nt < NT; nt++)
+#pragma unroll
+                for (int i = 0; i < 4; i++)
+                    bf[nt][i] = TB ? Bs[(nt * 8 + g) * PB + ks + t + 4 * i] : Bs[(ks + t + 4 * i) * PB + nt * 8 + g];
+#pragma unroll
+            for (int nt = 0; nt < NT; nt++)
+                sk_dmma(acc[nt], af, bf[nt]);
+#pragma unroll
+            for (int i = 0; i < 8; i++)
+                af[i] = an[i];
+        }
+
+        // ---- epilogue: chain, outputs, row extremum ----
+        const int64_t row_base = tile * SK_ROWS + warp * 16 + g;
+#pragma unroll
+        for (int h = 0; h < 2; h++) {
+            const int64_t r = row_base + 8 * h;
+            const bool live = r < s.n;
+            constexpr int NV = NT * 2; // value 2 * nt + e is column 8 * nt + 2 * t + e
+            double v[NV];
+#pragma unroll
+            for (int nt = 0; nt < NT; nt++) {
+                v[2 * nt] = acc[nt][2 * h];
+                v[2 * nt + 1] = acc[nt][2 * h + 1];
+            }
+#pragma unroll 1
+            for (int st = 0; st < P.nsteps; st++) {
+                const FusedStep &fs = P.steps[st];
+                double o[NV];
+                if (fs.kind == FK_ROWVEC) {
+#pragma unroll
+                    for (int nt = 0; nt < NT; nt++) {
+                        const double2 two = *reinterpret_cast<const double2 *>(rv + st * SK_MAXN + nt * 8 + 2 * t);
+                        o[2 * nt] = two.x;
+                        o[2 * nt + 1] = two.y;
+                    }
+                } else {
+                    double colv = fs.imm;
+                    if (fs.kind == FK_COLVEC)
+                        colv = live ? static_cast<const double *>(fs.ptr)[r * fs.ld] : 0.0;
+#pragma unroll
+                    for (int i = 0; i < NV; i++)
+                        o[i] = colv;
+                }
+                sk_apply<NV>(fs.op, fs.reversed != 0, v, o);
+            }
+            if (P.ew_out && live) {
+                double *out = static_cast<double *>(P.ew_out) + r * P.ew_out_ld;
+#pragma unroll
+                for (int i = 0; i < NV; i++) {
+                    const int c = (i >> 1) * 8 + 2 * t + (i & 1);
+                    if (c < s.N)
+                        out[c] = v[i];
+                }
+            }
+#pragma unroll 1
+            for (int tp = 0; tp < P.ntaps; tp++) {
+                // first extremum in column order among the non-NaN values; a NaN in column 0 stays (the reference's
+                // scan starts from it and no comparison with NaN succeeds: AggRow.h:71-96)
+                const bool want_max = P.taps[tp].kind == FT_MAX;
+                double best = 0.0;
+                int bi = 0x7fffffff;
+#pragma unroll
+                for (int i = 0; i < NV; i++) {
+                    const int c = (i >> 1) * 8 + 2 * t + (i & 1);
+                    const double x = want_max ? -v[i] : v[i]; // the maximum is the minimum of the negated values
+                    if (c < s.N && x == x && (bi == 0x7fffffff || x < best)) {
+                        best = x;
+                        bi = c;
+                    }
+                }
+                const bool nan0 = (t == 0) && !(v[0] == v[0]);
+#pragma unroll
+                for (int m = 1; m <= 2; m <<= 1) {
+                    const double ob = __shfl_xor_sync(0xffffffffu, best, m);
+                    const int oi = __shfl_xor_sync(0xffffffffu, bi, m);
+                    const bool take = oi != 0x7fffffff && (bi == 0x7fffffff || ob < best || (ob == best && oi < bi));
+                    if (take) {
+                        best = ob;
+                        bi = oi;
+                    }
+                }
+                const bool first_nan = __shfl_sync(0xffffffffu, (int)nan0, lane & ~3) != 0;
+                if (live && t == 0) {
+                    double val = want_max ? -best : best;
+                    int pos = bi;
+                    if (first_nan || bi == 0x7fffffff) {
+                        val = v[0]; // column 0 (a NaN), as the sequential scan leaves it
+                        pos = 0;
+                    }
+                    if (P.taps[tp].out)
+                        static_cast<double *>(P.taps[tp].out)[r] = val;
+                    if (P.taps[tp].out_idx)
+                        static_cast<uint64_t *>(P.taps[tp].out_idx)[r] = (uint64_t)pos;
+                }
+            }
+        }
+    }
+    asm volatile("cp.async.wait_group 0;\n" ::: "memory");
+}
+
+static size_t skinny_smem(int K, int nt, bool tb) {
+    const int KP = (K + 15) / 16 * 16, PA = KP + 4, PB = tb ? KP + 4 : nt * 8 + 4;
+    return ((size_t)(tb ? nt * 8 * PB : KP * PB) + FUSED_MAX_STEPS * SK_MAXN + 2 * (size_t)SK_ROWS * PA) * sizeof(double);
+}
+
+bool skinny_shape_ok(int64_t n, int64_t K, int64_t N, const void *A, int64_t lda) {
+    return n >= 4096 && K >= 1 && K <= SK_MAXK && N >= 1 && N <= SK_MAXN && aligned16(A) && lda % 2 == 0 &&
+           skinny_smem((int)K, (int)((N + 7) / 8), true) <= 220 * 1024;
+}
+
+template <int NT, bool TB> static int launch_skinny(const SkinnyArgs &a, cudaStream_t st) {
+    const size_t smem = skinny_smem(a.K, NT, TB);
+    static bool attr = false;
+    if (!attr) {
+        DB2_CUDA(cudaFuncSetAttribute(skinny_gemm_kernel<NT, TB>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      220 * 1024));
+        attr = true;
+    }
+    const int64_t ntiles = (a.n + SK_ROWS - 1) / SK_ROWS;
+    const int grid = (int)(ntiles < sm_count() ? ntiles : sm_count());
+    skinny_gemm_kernel<NT, TB><<<grid, SK_THREADS, smem, st>>>(a);
+    return after_launch("skinny_gemm_kernel");
+}
+
+int skinny_gemm(const SkinnyArgs &a, cudaStream_t st) {
+    if (a.n == 0 || a.N == 0)
+        return DB2_OK;
+    const int nt = (a.N + 7) / 8;
+#define DB2_SK(NTV)                                                                                                    \
+    case NTV: return a.tb ? launch_skinny<NTV, true>(a, st) : launch_skinny<NTV, false>(a, st);
+    switch (nt) {
+        DB2_SK(1) DB2_SK(2) DB2_SK(3) DB2_SK(4) DB2_SK(5) DB2_SK(6) DB2_SK(7) DB2_SK(8)
+    default: return set_error(DB2_EINVAL, "skinny product: more than 64 columns");
+    }
+#undef DB2_SK
+}
+
+} // namespace db2
