@@ -231,7 +231,15 @@ def run_ours(args) -> dict:
 
     extra = {}
     if not args.no_extra:
-        extra["normal_equations_shard"] = normal_equations_leg(ctx, comm, lib, host, world, args)
+        leg_sampler = ClockSampler(local_rank)  # the side legs get their own clock record
+        leg_sampler.start()
+        for name, leg in (("normal_equations_shard", normal_equations_leg), ("kmeans_shard", kmeans_leg),
+                          ("connected_components", components_leg), ("f32_matmul_tcgen05", f32_matmul_leg)):
+            try:
+                extra[name] = leg(ctx, comm, lib, host, world, args)
+            except Exception as e:  # a side leg must not take the headline down with it
+                extra[name] = {"error": f"{type(e).__name__}: {e}"[:300]}
+        extra["clocks"] = leg_sampler.stop()
 
     peak, peak_kind = measured_peaks()
     line = {
@@ -313,6 +321,108 @@ def normal_equations_leg(ctx, comm, lib, host, world, args) -> dict:
             "fp64_peak_tflops": FP64_PEAK_TFLOPS, "beta_max_abs_err_vs_w": float(np.abs(beta - w).max())}
 
 
+def _timed(lib, ctx, comm, fn, reps):
+    """max over ranks of the CUDA-event time of `reps` calls of fn (after one warm-up call), per call, in ms"""
+    from daphne_b200.lib import check
+    stream = C.c_void_p(ctx.stream)
+    out = fn()
+    comm.barrier()
+    check(lib.db2_device_sync())
+    e0, e1 = C.c_void_p(), C.c_void_p()
+    check(lib.db2_event_create(C.byref(e0)))
+    check(lib.db2_event_create(C.byref(e1)))
+    check(lib.db2_event_record(e0, stream))
+    for _ in range(reps):
+        out = fn()
+    check(lib.db2_event_record(e1, stream))
+    comm.barrier()
+    check(lib.db2_device_sync())
+    ms = C.c_float()
+    check(lib.db2_event_elapsed_ms(e0, e1, C.byref(ms)))
+    return comm.max_float(ms.value / reps), out
+
+
+def kmeans_leg(ctx, comm, lib, host, world, args) -> dict:
+    """K-means assignment + update, 10 iterations, on a 1,000,000 x 64 f64 row shard per GPU (U[0,1)), k = 50; the
+    centroid sums and counts are combined across ranks every iteration.  Algorithmic work per row and iteration:
+    520 bytes (the row and its assignment) and 6,464 flop (distances 2 k d + update d)."""
+    import daphne_b200.kernels as K
+    from daphne_b200 import pipelines
+    n, d, k, iters = (1_000_000, 64, 50, 10) if args.rows >= ROWS_PER_GPU else (max(args.rows // 16, 4096), 64, 50, 10)
+    x = host.reshape(-1)[: n * d].reshape(n, d)
+    x[:] = np.random.default_rng(3 + comm.rank).random((n, d))
+    c0 = np.random.default_rng(3).random((n, d))[np.random.default_rng(33).choice(n, k, replace=False)].copy()
+    X, C0 = K.DenseMatrix.from_numpy(ctx, x), K.DenseMatrix.from_numpy(ctx, c0)
+    X.device_ptr()
+    ms, res = _timed(lib, ctx, comm, lambda: pipelines.kmeans(ctx, X, C0, iters, comm), 3)
+    per_iter = ms / iters
+    peak, kind = measured_peaks()
+    return {"workload": f"k-means, {iters} iterations, f64 {n} x {d} per GPU, k = {k}, over {world} GPU(s)",
+            "ms_per_iteration": per_iter, "rows_per_s": n * world * iters / (ms * 1e-3),
+            "hbm_gbs_at_520B_per_row": n * 520 / (per_iter * 1e-3) / 1e9,
+            "hbm_frac_of_" + kind: n * 520 / (per_iter * 1e-3) / 1e9 / peak,
+            "fp64_tflops_at_6464_flop_per_row": n * 6464 / (per_iter * 1e-3) / 1e12,
+            "fp64_frac_of_peak": n * 6464 / (per_iter * 1e-3) / 1e12 / FP64_PEAK_TFLOPS,
+            "centroid_checksum": float(res.C.to_numpy().sum())}
+
+
+def components_leg(ctx, comm, lib, host, world, args) -> dict:
+    """Connected components by label propagation on a symmetric 0/1 CSR graph with 1,000,000 vertices and mean degree 8
+    (seed 4), row-sharded over the ranks; the labels are all-gathered every iteration.  Algorithmic bytes per vertex and
+    iteration on the reference's layout: 160 (8 entries x (8 + 8) + offsets + 3 vector passes)."""
+    import scipy.sparse as sp
+    import daphne_b200.kernels as K
+    from daphne_b200 import pipelines
+    from daphne_b200.dist import row_block
+    n, deg = (1_000_000, 8) if args.rows >= ROWS_PER_GPU else (max(args.rows // 16, 4096), 8)
+    rng = np.random.default_rng(4)
+    m = n * deg // 2
+    i, j = rng.integers(0, n, size=int(1.1 * m)), rng.integers(0, n, size=int(1.1 * m))
+    keep = i != j
+    key = np.unique(np.minimum(i[keep], j[keep]) * n + np.maximum(i[keep], j[keep]))[:m]
+    lo, hi = key // n, key % n
+    g = sp.csr_matrix((np.ones(2 * key.size), (np.concatenate([lo, hi]), np.concatenate([hi, lo]))), shape=(n, n))
+    g.sort_indices()
+    r0, r1 = row_block(n, comm.rank, world)
+    G = K.CSRMatrix.from_scipy(ctx, g[r0:r1])
+    blk = (r0, r1) if world > 1 else None
+    ms, res = _timed(lib, ctx, comm, lambda: pipelines.connected_components(ctx, G, 1000, comm, blk), 3)
+    per_iter = ms / res.iterations
+    labels = res.c.to_numpy().ravel()
+    peak, kind = measured_peaks()
+    return {"workload": f"connected components, {n} vertices, {2 * key.size} stored entries, rows over {world} GPU(s)",
+            "iterations": res.iterations, "ms_per_iteration": per_iter, "ms_total": ms,
+            "vertices_per_s": n * res.iterations / (ms * 1e-3),
+            "gbs_at_160B_per_vertex": n * 160 / (per_iter * 1e-3) / 1e9,
+            "frac_of_" + kind + "_hbm": n * 160 / (per_iter * 1e-3) / 1e9 / peak,
+            "components_in_shard": int(np.unique(labels).size), "label_checksum": float(labels.sum())}
+
+
+def f32_matmul_leg(ctx, comm, lib, host, world, args) -> dict:
+    """f32 matMul through the tensor-core path (tcgen05 kind::tf32; three MMAs per product for single-precision
+    accuracy): 8192^3 per GPU, replicated.  TFLOP/s counts 2 m n k once."""
+    import daphne_b200.kernels as K
+    m = 8192 if args.rows >= ROWS_PER_GPU else 1024
+    rng = np.random.default_rng(7)
+    a, b = rng.standard_normal((m, m), dtype=np.float32), rng.standard_normal((m, m), dtype=np.float32)
+    A, B = K.DenseMatrix.from_numpy(ctx, a), K.DenseMatrix.from_numpy(ctx, b)
+    A.device_ptr()
+    B.device_ptr()
+    keep = []
+
+    def run():
+        keep.clear()
+        keep.append(K.matMul(A, B, False, True))
+        return keep[0]
+    ms, res = _timed(lib, ctx, comm, run, 5)
+    got = res.to_numpy()[:64]
+    ref = a[:64].astype(np.float64) @ b.astype(np.float64).T
+    tf = 2.0 * m * m * m / (ms * 1e-3) / 1e12
+    return {"workload": f"f32 {m} x {m} @ t({m} x {m}) per GPU", "ms": ms, "tflops": tf,
+            "tf32_mma_tflops_issued": 3 * tf, "tf32_mma_frac_of_nominal_1125": 3 * tf / 1125.0,
+            "max_abs_err_vs_f64_64_rows": float(np.abs(got - ref).max())}
+
+
 def cpu_baseline(rows: int, cols: int, steps: int = 3, threads: int | None = None) -> dict:
     from oracle import cpu_pipelines
     k, kind = cpu_pipelines.backend()
@@ -357,7 +467,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--rows", type=int, default=ROWS_PER_GPU, help="rows per GPU (default: the 4 GiB configuration)")
-    ap.add_argument("--no-extra", action="store_true", help="skip the normal-equations leg reported under `extra`")
+    ap.add_argument("--no-extra", action="store_true", help="skip the other workloads reported under `extra`")
     ap.add_argument("--cpu-rows", type=int, default=1 << 20, help="rows of the bounded CPU-baseline sample")
     args = ap.parse_args()
     if args.warmup < 3 and args.impl == "ours":

@@ -59,7 +59,8 @@ __global__ void __launch_bounds__(SK_THREADS, 1) skinny_gemm_kernel(const __grid
     const int PB = TB ? KP + 4 : NT * 8 + 4;
     double *Bs = sm;                                   // TB: [NT*8][PB] (k contiguous);  else [KP][PB]
     double *rv = Bs + (TB ? NT * 8 * PB : KP * PB);     // row-vector operands: [step][64]
-    double *As = rv + FUSED_MAX_STEPS * SK_MAXN;        // 2 x [128][PA]
+    double *cv = rv + FUSED_MAX_STEPS * SK_MAXN;        // column-vector operands of the tile's rows: 2 x [step][128]
+    double *As = cv + 2 * FUSED_MAX_STEPS * SK_ROWS;    // 2 x [128][PA]
     const int tid = threadIdx.x, warp = tid / 32, lane = tid % 32, g = lane / 4, t = lane % 4;
     const FusedProgram &P = s.prog;
 
@@ -96,6 +97,17 @@ __global__ void __launch_bounds__(SK_THREADS, 1) skinny_gemm_kernel(const __grid
             const double *src = bytes ? s.A + row * s.lda + k : s.A;
             asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(d), "l"(src), "r"(bytes) : "memory");
         }
+        // the column-vector operands of these rows travel with the tile (one element per thread and step)
+        if (tid < SK_ROWS)
+            for (int st = 0; st < P.nsteps; st++)
+                if (P.steps[st].kind == FK_COLVEC) {
+                    const int64_t row = r0 + tid;
+                    const double *base = static_cast<const double *>(P.steps[st].ptr);
+                    const unsigned d = (unsigned)__cvta_generic_to_shared(cv + ((size_t)buf * FUSED_MAX_STEPS + st) * SK_ROWS + tid);
+                    const int bytes = row < s.n ? 8 : 0;
+                    const double *src = bytes ? base + row * P.steps[st].ld : base;
+                    asm volatile("cp.async.ca.shared.global [%0], [%1], 8, %2;\n" ::"r"(d), "l"(src), "r"(bytes) : "memory");
+                }
     };
     int64_t tile = blockIdx.x;
     if (tile < ntiles)
@@ -168,7 +180,7 @@ __global__ void __launch_bounds__(SK_THREADS, 1) skinny_gemm_kernel(const __grid
                 } else {
                     double colv = fs.imm;
                     if (fs.kind == FK_COLVEC)
-                        colv = live ? static_cast<const double *>(fs.ptr)[r * fs.ld] : 0.0;
+                        colv = cv[((size_t)buf * FUSED_MAX_STEPS + st) * SK_ROWS + warp * 16 + g + 8 * h];
 #pragma unroll
                     for (int i = 0; i < NV; i++)
                         o[i] = colv;
@@ -232,12 +244,14 @@ __global__ void __launch_bounds__(SK_THREADS, 1) skinny_gemm_kernel(const __grid
 
 static size_t skinny_smem(int K, int nt, bool tb) {
     const int KP = (K + 15) / 16 * 16, PA = KP + 4, PB = tb ? KP + 4 : nt * 8 + 4;
-    return ((size_t)(tb ? nt * 8 * PB : KP * PB) + FUSED_MAX_STEPS * SK_MAXN + 2 * (size_t)SK_ROWS * PA) * sizeof(double);
+    return ((size_t)(tb ? nt * 8 * PB : KP * PB) + FUSED_MAX_STEPS * SK_MAXN + 2 * FUSED_MAX_STEPS * SK_ROWS +
+            2 * (size_t)SK_ROWS * PA) * sizeof(double);
 }
 
 bool skinny_shape_ok(int64_t n, int64_t K, int64_t N, const void *A, int64_t lda) {
     return n >= 4096 && K >= 1 && K <= SK_MAXK && N >= 1 && N <= SK_MAXN && aligned16(A) && lda % 2 == 0 &&
-           skinny_smem((int)K, (int)((N + 7) / 8), true) <= 220 * 1024;
+           skinny_smem((int)K, (int)((N + 7) / 8), true) <= 220 * 1024 &&
+           skinny_smem((int)K, (int)((N + 7) / 8), false) <= 220 * 1024;
 }
 
 template <int NT, bool TB> static int launch_skinny(const SkinnyArgs &a, cudaStream_t st) {
