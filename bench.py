@@ -321,6 +321,27 @@ def normal_equations_leg(ctx, comm, lib, host, world, args) -> dict:
             "fp64_peak_tflops": FP64_PEAK_TFLOPS, "beta_max_abs_err_vs_w": float(np.abs(beta - w).max())}
 
 
+LEGS = {}
+
+
+def run_leg(args) -> dict:
+    """One of the side workloads alone (`--leg NAME`), for profiling a single kernel on a small case: `--rows` below
+    the full configuration scales the leg down (normal equations and k-means to rows / 16 rows)."""
+    import daphne_b200.kernels as K
+    from daphne_b200.dist import Comm
+    from daphne_b200.lib import lib, require_device
+    require_device()
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    comm = Comm.from_env("nccl")
+    ctx = K.Context(local_rank)
+    comm.init_device(ctx)
+    host, host_ptr = pinned_array(lib, max(args.rows // 16, 4096) * 512 // COLS + 1, COLS)
+    out = LEGS[args.leg](ctx, comm, lib, host, world, args)
+    lib.db2_free_host(host_ptr)
+    return {"leg": args.leg, "n_gpus": world, **out} if comm.rank == 0 else {}
+
+
 def _timed(lib, ctx, comm, fn, reps):
     """max over ranks of the CUDA-event time of `reps` calls of fn (after one warm-up call), per call, in ms"""
     from daphne_b200.lib import check
@@ -402,7 +423,7 @@ def f32_matmul_leg(ctx, comm, lib, host, world, args) -> dict:
     """f32 matMul through the tensor-core path (tcgen05 kind::tf32; three MMAs per product for single-precision
     accuracy): 8192^3 per GPU, replicated.  TFLOP/s counts 2 m n k once."""
     import daphne_b200.kernels as K
-    m = 8192 if args.rows >= ROWS_PER_GPU else 1024
+    m = 8192 if args.rows >= ROWS_PER_GPU else 4096
     rng = np.random.default_rng(7)
     a, b = rng.standard_normal((m, m), dtype=np.float32), rng.standard_normal((m, m), dtype=np.float32)
     A, B = K.DenseMatrix.from_numpy(ctx, a), K.DenseMatrix.from_numpy(ctx, b)
@@ -421,6 +442,10 @@ def f32_matmul_leg(ctx, comm, lib, host, world, args) -> dict:
     return {"workload": f"f32 {m} x {m} @ t({m} x {m}) per GPU", "ms": ms, "tflops": tf,
             "tf32_mma_tflops_issued": 3 * tf, "tf32_mma_frac_of_nominal_1125": 3 * tf / 1125.0,
             "max_abs_err_vs_f64_64_rows": float(np.abs(got - ref).max())}
+
+
+LEGS.update({"normal_equations_shard": normal_equations_leg, "kmeans_shard": kmeans_leg,
+             "connected_components": components_leg, "f32_matmul_tcgen05": f32_matmul_leg})
 
 
 def cpu_baseline(rows: int, cols: int, steps: int = 3, threads: int | None = None) -> dict:
@@ -469,10 +494,16 @@ def main():
     ap.add_argument("--rows", type=int, default=ROWS_PER_GPU, help="rows per GPU (default: the 4 GiB configuration)")
     ap.add_argument("--no-extra", action="store_true", help="skip the other workloads reported under `extra`")
     ap.add_argument("--cpu-rows", type=int, default=1 << 20, help="rows of the bounded CPU-baseline sample")
+    ap.add_argument("--leg", default=None, choices=["normal_equations_shard", "kmeans_shard", "connected_components",
+                                                    "f32_matmul_tcgen05"],
+                    help="run only this side workload (profiling aid); prints its own JSON line")
     args = ap.parse_args()
     if args.warmup < 3 and args.impl == "ours":
         args.warmup = 3
-    line = run_reference(args) if args.impl == "reference" else run_ours(args)
+    if args.leg and args.impl == "ours":
+        line = run_leg(args)
+    else:
+        line = run_reference(args) if args.impl == "reference" else run_ours(args)
     if line:
         print(json.dumps(line), flush=True)
     if int(os.environ.get("WORLD_SIZE", "1")) > 1:

@@ -57,9 +57,9 @@ __device__ __forceinline__ double scale_at(int skind, const double *sc, int64_t 
 // (EwBinaryMat.h:295-302) and therefore count as implicit zeros.  G lanes per row; every lane group works on U rows
 // at a time so that the dependent loads of a row (offsets -> column index -> gathered operand) of U rows overlap.
 // UNIT: every stored value is exactly 1.0 (adjacency matrices), the value array is not read.
-template <int G, typename IT, bool UNIT>
+template <int G, typename IT, bool UNIT, int op>
 __global__ void __launch_bounds__(256)
-    csr_agg_row_kernel(int op, const double *__restrict__ val, const IT *__restrict__ col,
+    csr_agg_row_kernel(const double *__restrict__ val, const IT *__restrict__ col,
                        const uint64_t *__restrict__ off, int64_t rows, int64_t cols, int skind,
                        const double *__restrict__ sc, int64_t sc_ld, double *__restrict__ out) {
     constexpr int RPC = 256 / G, U = 4;
@@ -79,7 +79,7 @@ __global__ void __launch_bounds__(256)
     for (int64_t r0 = (int64_t)blockIdx.x * RPC + grp; r0 < rows_padded; r0 += stride * U) {
         uint64_t b[U], e[U];
         double acc[U];
-        long long kept[U];
+        int kept[U]; // entries of the row that exist in the product (only compared with the column count)
 #pragma unroll
         for (int u = 0; u < U; u++) {
             const int64_t r = r0 + u * stride;
@@ -241,25 +241,32 @@ static int launch_agg(db2_context *ctx, int op, const db2_csr *m, int skind, con
     // every lane group takes 4 rows per turn
     const int64_t want = (rows + (256 / lanes) * 4 - 1) / ((256 / lanes) * 4), cap = (int64_t)sm_count() * 8;
     const int grid = (int)(want < cap ? (want ? want : 1) : cap);
-#define DB2_CSR_AGG(G, UNIT)                                                                                           \
-    csr_agg_row_kernel<G, IT, UNIT><<<grid, 256, 0, ctx->stream>>>(op, val, col, m->off_ptr(), rows, m->cols, skind,   \
-                                                                   sc, ld, out)
-    if (m->unit_vals) {
-        if (lanes == 4)
-            DB2_CSR_AGG(4, true);
-        else if (lanes == 8)
-            DB2_CSR_AGG(8, true);
-        else
-            DB2_CSR_AGG(32, true);
+#define DB2_CSR_AGG3(G, UNIT, OP)                                                                                      \
+    csr_agg_row_kernel<G, IT, UNIT, OP><<<grid, 256, 0, ctx->stream>>>(val, col, m->off_ptr(), rows, m->cols, skind,   \
+                                                                       sc, ld, out)
+#define DB2_CSR_AGG2(G, UNIT)                                                                                          \
+    switch (op) {                                                                                                      \
+    case DB2_AGG_SUM: DB2_CSR_AGG3(G, UNIT, DB2_AGG_SUM); break;                                                       \
+    case DB2_AGG_PROD: DB2_CSR_AGG3(G, UNIT, DB2_AGG_PROD); break;                                                     \
+    case DB2_AGG_MIN: DB2_CSR_AGG3(G, UNIT, DB2_AGG_MIN); break;                                                       \
+    default: DB2_CSR_AGG3(G, UNIT, DB2_AGG_MAX); break;                                                                \
+    }
+#define DB2_CSR_AGG(G)                                                                                                 \
+    if (m->unit_vals) {                                                                                                \
+        DB2_CSR_AGG2(G, true)                                                                                          \
+    } else {                                                                                                           \
+        DB2_CSR_AGG2(G, false)                                                                                         \
+    }
+    if (lanes == 4) {
+        DB2_CSR_AGG(4)
+    } else if (lanes == 8) {
+        DB2_CSR_AGG(8)
     } else {
-        if (lanes == 4)
-            DB2_CSR_AGG(4, false);
-        else if (lanes == 8)
-            DB2_CSR_AGG(8, false);
-        else
-            DB2_CSR_AGG(32, false);
+        DB2_CSR_AGG(32)
     }
 #undef DB2_CSR_AGG
+#undef DB2_CSR_AGG2
+#undef DB2_CSR_AGG3
     return after_launch("csr_agg_row_kernel");
 }
 

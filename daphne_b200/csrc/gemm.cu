@@ -53,6 +53,10 @@ struct GemmArgs {
     int64_t M, N, K;
     int splits;
     int64_t k_per_split; // multiple of KC
+    // syrk: tiles on the diagonal run only the warps on or above it, so they get fewer, longer shares of the
+    // contraction range than the full tiles (same time per CTA)
+    int splits_diag;
+    int64_t k_per_split_diag;
     int syrk;            // only tiles with tile_n*BN + BN > tile_m*BM are computed (upper triangle incl. diagonal)
     int aligned;         // operands allow 16-byte copies (bases 16-byte aligned, even leading dimensions)
 };
@@ -155,8 +159,12 @@ __global__ void __launch_bounds__(TileCfg<BM, BN>::THREADS) gemm_f64_kernel(cons
         return; // strictly below the diagonal: mirrored by the reduce step
     const bool warp_active = !ga.syrk || (n0 + wn * WN + WN > m0 + wm * 32);
     const bool same_tile = ga.syrk && BM == BN && m0 == n0 && (TA != TB);
-    const int64_t k_begin = (int64_t)blockIdx.z * ga.k_per_split;
-    const int64_t k_end = (k_begin + ga.k_per_split < ga.K) ? k_begin + ga.k_per_split : ga.K;
+    const bool diag_tile = ga.syrk && BM == BN && m0 == n0;
+    if ((int)blockIdx.z >= (diag_tile ? ga.splits_diag : ga.splits))
+        return;
+    const int64_t kps = diag_tile ? ga.k_per_split_diag : ga.k_per_split;
+    const int64_t k_begin = (int64_t)blockIdx.z * kps;
+    const int64_t k_end = (k_begin + kps < ga.K) ? k_begin + kps : ga.K;
     const int64_t nchunks = (k_end > k_begin) ? (k_end - k_begin + KC - 1) / KC : 0;
 
     double acc[2][NTILES][4];
@@ -253,7 +261,7 @@ __global__ void __launch_bounds__(TileCfg<BM, BN>::THREADS) gemm_f64_kernel(cons
 // of computed ones, and when splits == 1 only the mirroring is done (the tiles were written to C directly).
 template <int BM, int BN>
 __global__ void gemm_reduce_kernel(const double *__restrict__ part, double *__restrict__ C, int64_t ldc, int64_t M,
-                                   int64_t N, int tiles_m, int tiles_n, int splits, int syrk) {
+                                   int64_t N, int tiles_m, int tiles_n, int splits, int splits_diag, int syrk) {
     constexpr int WN = 32;
     const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= M * N)
@@ -268,8 +276,9 @@ __global__ void gemm_reduce_kernel(const double *__restrict__ part, double *__re
         const int64_t tm = si / BM, tn = sj / BN;
         const double *p = part + ((size_t)tm * tiles_n + tn) * (BM * BN) + (si % BM) * BN + (sj % BN);
         const size_t stride = (size_t)tiles_m * tiles_n * (BM * BN);
+        const int mine = (syrk && BM == BN && tm == tn) ? splits_diag : splits;
         double a = p[0];
-        for (int s = 1; s < splits; s++)
+        for (int s = 1; s < mine; s++)
             a = __dadd_rn(a, p[(size_t)s * stride]);
         C[i * ldc + j] = a;
     } else if (si != i) {
@@ -278,8 +287,8 @@ __global__ void gemm_reduce_kernel(const double *__restrict__ part, double *__re
 }
 
 struct GemmPlan {
-    int bm, bn, tiles_m, tiles_n, splits;
-    int64_t k_per_split;
+    int bm, bn, tiles_m, tiles_n, splits, splits_diag;
+    int64_t k_per_split, k_per_split_diag;
     size_t scratch;
 };
 
@@ -317,13 +326,37 @@ static GemmPlan plan_gemm(int64_t M, int64_t N, int64_t K, bool syrk, bool ta, b
     int64_t splits = slots / (tiles > 0 ? tiles : 1);
     if (splits < 1)
         splits = 1;
-    if (splits > chunks / 8)
-        splits = chunks / 8 > 0 ? chunks / 8 : 1; // at least 8 chunks (128 rows) per split
-    if (splits > 512)
-        splits = 512;
-    const int64_t cps = (chunks + splits - 1) / splits;
-    p.k_per_split = cps * KC;
-    p.splits = (int)((chunks + cps - 1) / cps);
+    auto shares = [&](int64_t want, int *count, int64_t *k_per) { // `want` shares of whole chunks
+        if (want > chunks / 8)
+            want = chunks / 8; // at least 8 chunks (128 rows) per share
+        if (want < 1)
+            want = 1;
+        if (want > 512)
+            want = 512;
+        const int64_t cps = (chunks + want - 1) / want;
+        *k_per = cps * KC;
+        *count = (int)((chunks + cps - 1) / cps);
+    };
+    shares(splits, &p.splits, &p.k_per_split);
+    p.splits_diag = p.splits;
+    p.k_per_split_diag = p.k_per_split;
+    const int n_diag = p.tiles_m, n_off = (int)tiles - n_diag;
+    if (syrk && p.bm == p.bn && n_off > 0) {
+        // a diagonal tile keeps w (w + 1) / 2 of its w x w warps busy: give it that fraction of the shares of a full
+        // tile, so that every CTA runs about equally long and all of them fit the SMs at once
+        const int w = p.bm / 32;
+        const double rho = (w + 1) / (2.0 * w);
+        int64_t so = (int64_t)(slots / (n_off + rho * n_diag));
+        int64_t sd = (int64_t)(rho * so + 0.5);
+        while (so > 1 && n_off * so + n_diag * (sd < 1 ? 1 : sd) > slots) {
+            so--;
+            sd = (int64_t)(rho * so + 0.5);
+        }
+        shares(so, &p.splits, &p.k_per_split);
+        shares(sd, &p.splits_diag, &p.k_per_split_diag);
+        if (p.splits_diag > p.splits) // the partial buffer and the grid are sized by p.splits
+            p.splits = p.splits_diag, p.k_per_split = p.k_per_split_diag;
+    }
     p.scratch = p.splits > 1 ? (size_t)p.splits * p.tiles_m * p.tiles_n * p.bm * p.bn * 8 : 0;
     return p;
 }
@@ -343,7 +376,7 @@ static int launch_gemm(const GemmArgs &g, const GemmPlan &p, cudaStream_t st) {
     if (p.splits > 1 || g.syrk) {
         const int64_t total = g.M * g.N;
         gemm_reduce_kernel<BM, BN><<<(unsigned)((total + 255) / 256), 256, 0, st>>>(
-            g.part, g.C, g.ldc, g.M, g.N, p.tiles_m, p.tiles_n, p.splits, g.syrk);
+            g.part, g.C, g.ldc, g.M, g.N, p.tiles_m, p.tiles_n, p.splits, p.splits_diag, g.syrk);
         DB2_TRY(after_launch("gemm_reduce_kernel"));
     }
     return DB2_OK;
@@ -368,6 +401,8 @@ static int run_gemm(bool ta, bool tb, GemmArgs g, cudaStream_t st, void *scratch
     g.part = static_cast<double *>(scratch);
     g.splits = p.splits;
     g.k_per_split = p.k_per_split;
+    g.splits_diag = p.splits_diag;
+    g.k_per_split_diag = p.k_per_split_diag;
     g.aligned = aligned16(g.A) && aligned16(g.B) && (g.lda % 2 == 0) && (g.ldb % 2 == 0);
     if (!ta && !tb)
         return dispatch_tiles<false, false>(g, p, st);
