@@ -96,6 +96,7 @@ struct SkinnyArgs {
 };
 bool skinny_shape_ok(int64_t n, int64_t K, int64_t N, const void *A, int64_t lda);
 bool skinny_op_supported(int fused_op);
+int skinny_vec_slots(); // row-vector / column-vector operands (each kind) a fused chain may have
 int skinny_gemm(const SkinnyArgs &a, cudaStream_t st);
 
 } // namespace db2

@@ -326,9 +326,15 @@ static void fill_skinny(const Expr &e, SkinnyArgs *a) {
 
 // can chain and aggregations be applied to the accumulators of the product?
 static bool gemm_pass_fusable(const Expr &e, const std::vector<db2_matrix *> &group) {
-    for (const ExprStep &s : e.steps)
+    int rowvecs = 0, colvecs = 0;
+    for (const ExprStep &s : e.steps) {
         if (s.kind == FK_MATRIX || !skinny_op_supported(s.op))
             return false;
+        rowvecs += s.kind == FK_ROWVEC;
+        colvecs += s.kind == FK_COLVEC;
+    }
+    if (rowvecs > skinny_vec_slots() || colvecs > skinny_vec_slots())
+        return false;
     std::vector<int> kinds;
     for (const db2_matrix *g : group) {
         const int op = g->pend_op;

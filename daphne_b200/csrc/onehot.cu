@@ -33,50 +33,43 @@ __global__ void __launch_bounds__(SEG_MAX_WARPS * 32)
     const int64_t per = (n + total_warps - 1) / total_warps;
     const int64_t lo = gw * per, hi = lo + per < n ? lo + per : n;
     constexpr int U = 16;
-    if (vec && d == 64) {
-        // one row = 32 lanes x 16 bytes.  Rows are taken 16 at a time; the loads of the next 16 rows are in flight
-        // while the current 16 are added.
-        auto fetch_c = [&](int64_t b) { return (b + lane < hi) ? idx[(b + lane) * idx_ld] : (int64_t)-1; };
-        auto fetch_x = [&](int64_t b, long long cl, int half, double2 (&x)[U], int (&cu)[U]) {
+    int64_t c_next = (lo + lane < hi) ? idx[(lo + lane) * idx_ld] : -1;
+    for (int64_t b0 = lo; b0 < hi; b0 += 32) {
+        const int64_t c_mine = c_next;
+        c_next = (b0 + 32 + lane < hi) ? idx[(b0 + 32 + lane) * idx_ld] : -1;
 #pragma unroll
-            for (int u = 0; u < U; u++) {
-                const long long c = __shfl_sync(0xffffffffu, cl, half * U + u);
-                cu[u] = (c >= 0 && c < k) ? (int)c : -1;
-                x[u] = cu[u] >= 0 ? __ldcs(reinterpret_cast<const double2 *>(X + (b + half * U + u) * ldx) + lane)
-                                  : make_double2(0.0, 0.0);
-            }
-        };
-        auto add = [&](const double2 (&x)[U], const int (&cu)[U]) {
+        for (int h = 0; h < 32; h += U) {
+            if (b0 + h >= hi)
+                break;
+            if (vec && d == 64) {
+                // one row = 32 lanes x 16 bytes
+                double2 x[U];
+                int cu[U];
 #pragma unroll
-            for (int u = 0; u < U; u++)
-                if (cu[u] >= 0) {
-                    double2 *a = reinterpret_cast<double2 *>(mine + cu[u] * d) + lane;
-                    double2 t = *a;
-                    t.x = __dadd_rn(t.x, x[u].x);
-                    t.y = __dadd_rn(t.y, x[u].y);
-                    *a = t;
+                for (int u = 0; u < U; u++) {
+                    const long long c = __shfl_sync(0xffffffffu, (long long)c_mine, h + u);
+                    cu[u] = (c >= 0 && c < k) ? (int)c : -1;
+                    x[u] = cu[u] >= 0 ? __ldcs(reinterpret_cast<const double2 *>(X + (b0 + h + u) * ldx) + lane)
+                                      : make_double2(0.0, 0.0);
                 }
-        };
-        double2 xa[U], xb[U];
-        int ca[U], cb[U];
-        long long c_cur = fetch_c(lo), c_nxt = fetch_c(lo + 32);
-        if (lo < hi)
-            fetch_x(lo, c_cur, 0, xa, ca);
-        for (int64_t b0 = lo; b0 < hi; b0 += 32) {
-            fetch_x(b0, c_cur, 1, xb, cb); // rows b0 + 16 .. b0 + 31 (absent rows have cluster -1)
-            add(xa, ca);
-            c_cur = c_nxt;
-            c_nxt = fetch_c(b0 + 64);
-            if (b0 + 32 < hi)
-                fetch_x(b0 + 32, c_cur, 0, xa, ca);
-            add(xb, cb);
-        }
-    } else {
-        for (int64_t r = lo; r < hi; r++) {
-            const int64_t c = idx[r * idx_ld];
-            if (c >= 0 && c < k)
-                for (int j = lane; j < d; j += 32)
-                    mine[c * d + j] = __dadd_rn(mine[c * d + j], X[r * ldx + j]);
+#pragma unroll
+                for (int u = 0; u < U; u++)
+                    if (cu[u] >= 0) {
+                        double2 *a = reinterpret_cast<double2 *>(mine + cu[u] * d) + lane;
+                        double2 t = *a;
+                        t.x = __dadd_rn(t.x, x[u].x);
+                        t.y = __dadd_rn(t.y, x[u].y);
+                        *a = t;
+                    }
+            } else {
+#pragma unroll 1
+                for (int u = 0; u < U; u++) {
+                    const long long c = __shfl_sync(0xffffffffu, (long long)c_mine, h + u);
+                    if (c >= 0 && c < k)
+                        for (int j = lane; j < d; j += 32)
+                            mine[c * d + j] = __dadd_rn(mine[c * d + j], X[(b0 + h + u) * ldx + j]);
+                }
+            }
         }
     }
     __syncthreads();

@@ -2,8 +2,8 @@
 // op(B) is K x N with N <= 64.  This is the distance step of k-means,  X @ t(C)  (MatMul.cpp:284-288 in the reference:
 // one dgemm writing the n x k matrix), followed there by three elementwise kernels and a row idxMin.
 //
-// Persistent CTAs (one per SM) keep op(B) in shared memory for the whole launch and stream A through a double-buffered
-// ring of 128-row tiles (16-byte cp.async, zero fill).  Every warp owns 16 rows x all N columns, so after the DMMAs
+// Persistent CTAs (two per SM) keep op(B) in shared memory for the whole launch and stream A through a double-buffered
+// ring of 64-row tiles (16-byte cp.async, zero fill).  Every warp owns 16 rows x all N columns, so after the DMMAs
 // (mma.sync m16n8k16 f64) a row's values sit in the four lanes of a quad: the recorded elementwise chain (scalar,
 // column-vector and row-vector operands) is applied to the accumulators in registers, the row minimum / maximum and
 // its position are reduced with two shuffles, and the n x N product itself is only written if somebody asked for it.
@@ -12,7 +12,8 @@
 
 namespace db2 {
 
-constexpr int SK_ROWS = 128, SK_THREADS = 256, SK_MAXN = 64, SK_MAXK = 128;
+constexpr int SK_ROWS = 64, SK_THREADS = SK_ROWS * 2, SK_MAXN = 64, SK_MAXK = 128;
+constexpr int SK_VEC_SLOTS = 4; // row-vector and column-vector operands of a fused chain (each kind)
 
 __device__ __forceinline__ void sk_dmma(double (&c)[4], const double (&a)[8], const double (&b)[4]) {
     asm volatile("mma.sync.aligned.m16n8k16.row.col.f64.f64.f64.f64 {%0,%1,%2,%3}, {%4,%5,%6,%7,%8,%9,%10,%11}, "
@@ -53,14 +54,14 @@ bool skinny_op_supported(int op) {
 }
 
 template <int NT, bool TB>
-__global__ void __launch_bounds__(SK_THREADS, 1) skinny_gemm_kernel(const __grid_constant__ SkinnyArgs s) {
+__global__ void __launch_bounds__(SK_THREADS, 2) skinny_gemm_kernel(const __grid_constant__ SkinnyArgs s) {
     extern __shared__ __align__(16) double sm[];
     const int KP = (s.K + 15) / 16 * 16, PA = KP + 4; // pitch = 4 mod 16 doubles: conflict-free fragment loads
     const int PB = TB ? KP + 4 : NT * 8 + 4;
     double *Bs = sm;                                   // TB: [NT*8][PB] (k contiguous);  else [KP][PB]
-    double *rv = Bs + (TB ? NT * 8 * PB : KP * PB);     // row-vector operands: [step][64]
-    double *cv = rv + FUSED_MAX_STEPS * SK_MAXN;        // column-vector operands of the tile's rows: 2 x [step][128]
-    double *As = cv + 2 * FUSED_MAX_STEPS * SK_ROWS;    // 2 x [128][PA]
+    double *rv = Bs + (TB ? NT * 8 * PB : KP * PB);     // row-vector operands: [slot][64]
+    double *cv = rv + SK_VEC_SLOTS * SK_MAXN;           // column-vector operands of the tile's rows: 2 x [slot][rows]
+    double *As = cv + 2 * SK_VEC_SLOTS * SK_ROWS;       // 2 x [rows][PA]
     const int tid = threadIdx.x, warp = tid / 32, lane = tid % 32, g = lane / 4, t = lane % 4;
     const FusedProgram &P = s.prog;
 
@@ -79,7 +80,7 @@ __global__ void __launch_bounds__(SK_THREADS, 1) skinny_gemm_kernel(const __grid
     for (int st = 0; st < P.nsteps; st++)
         if (P.steps[st].kind == FK_ROWVEC)
             for (int c = tid; c < SK_MAXN; c += SK_THREADS)
-                rv[st * SK_MAXN + c] = c < s.N ? static_cast<const double *>(P.steps[st].ptr)[c] : 0.0;
+                rv[P.steps[st].smem_off * SK_MAXN + c] = c < s.N ? static_cast<const double *>(P.steps[st].ptr)[c] : 0.0;
 
     const int64_t ntiles = (s.n + SK_ROWS - 1) / SK_ROWS;
     const int packets = KP / 2; // 16-byte packets per row
@@ -103,7 +104,7 @@ __global__ void __launch_bounds__(SK_THREADS, 1) skinny_gemm_kernel(const __grid
                 if (P.steps[st].kind == FK_COLVEC) {
                     const int64_t row = r0 + tid;
                     const double *base = static_cast<const double *>(P.steps[st].ptr);
-                    const unsigned d = (unsigned)__cvta_generic_to_shared(cv + ((size_t)buf * FUSED_MAX_STEPS + st) * SK_ROWS + tid);
+                    const unsigned d = (unsigned)__cvta_generic_to_shared(cv + ((size_t)buf * SK_VEC_SLOTS + P.steps[st].smem_off) * SK_ROWS + tid);
                     const int bytes = row < s.n ? 8 : 0;
                     const double *src = bytes ? base + row * P.steps[st].ld : base;
                     asm volatile("cp.async.ca.shared.global [%0], [%1], 8, %2;\n" ::"r"(d), "l"(src), "r"(bytes) : "memory");
@@ -173,14 +174,14 @@ __global__ void __launch_bounds__(SK_THREADS, 1) skinny_gemm_kernel(const __grid
                 if (fs.kind == FK_ROWVEC) {
 #pragma unroll
                     for (int nt = 0; nt < NT; nt++) {
-                        const double2 two = *reinterpret_cast<const double2 *>(rv + st * SK_MAXN + nt * 8 + 2 * t);
+                        const double2 two = *reinterpret_cast<const double2 *>(rv + fs.smem_off * SK_MAXN + nt * 8 + 2 * t);
                         o[2 * nt] = two.x;
                         o[2 * nt + 1] = two.y;
                     }
                 } else {
                     double colv = fs.imm;
                     if (fs.kind == FK_COLVEC)
-                        colv = cv[((size_t)buf * FUSED_MAX_STEPS + st) * SK_ROWS + warp * 16 + g + 8 * h];
+                        colv = cv[((size_t)buf * SK_VEC_SLOTS + fs.smem_off) * SK_ROWS + warp * 16 + g + 8 * h];
 #pragma unroll
                     for (int i = 0; i < NV; i++)
                         o[i] = colv;
@@ -244,7 +245,7 @@ __global__ void __launch_bounds__(SK_THREADS, 1) skinny_gemm_kernel(const __grid
 
 static size_t skinny_smem(int K, int nt, bool tb) {
     const int KP = (K + 15) / 16 * 16, PA = KP + 4, PB = tb ? KP + 4 : nt * 8 + 4;
-    return ((size_t)(tb ? nt * 8 * PB : KP * PB) + FUSED_MAX_STEPS * SK_MAXN + 2 * FUSED_MAX_STEPS * SK_ROWS +
+    return ((size_t)(tb ? nt * 8 * PB : KP * PB) + SK_VEC_SLOTS * SK_MAXN + 2 * SK_VEC_SLOTS * SK_ROWS +
             2 * (size_t)SK_ROWS * PA) * sizeof(double);
 }
 
@@ -263,14 +264,28 @@ template <int NT, bool TB> static int launch_skinny(const SkinnyArgs &a, cudaStr
         attr = true;
     }
     const int64_t ntiles = (a.n + SK_ROWS - 1) / SK_ROWS;
-    const int grid = (int)(ntiles < sm_count() ? ntiles : sm_count());
+    // two CTAs per SM when shared memory allows: while one is in its epilogue the other keeps the DMMA pipe busy
+    const int per_sm = smem <= 110 * 1024 ? 2 : 1;
+    const int64_t slots = (int64_t)sm_count() * per_sm;
+    const int grid = (int)(ntiles < slots ? ntiles : slots);
     skinny_gemm_kernel<NT, TB><<<grid, SK_THREADS, smem, st>>>(a);
     return after_launch("skinny_gemm_kernel");
 }
 
-int skinny_gemm(const SkinnyArgs &a, cudaStream_t st) {
-    if (a.n == 0 || a.N == 0)
+int skinny_vec_slots() { return SK_VEC_SLOTS; }
+
+int skinny_gemm(const SkinnyArgs &args, cudaStream_t st) {
+    if (args.n == 0 || args.N == 0)
         return DB2_OK;
+    SkinnyArgs a = args;
+    int rows = 0, cols = 0; // shared-memory slot of every vector operand
+    for (int i = 0; i < a.prog.nsteps; i++) {
+        if (a.prog.steps[i].kind == FK_ROWVEC)
+            a.prog.steps[i].smem_off = rows++;
+        else if (a.prog.steps[i].kind == FK_COLVEC)
+            a.prog.steps[i].smem_off = cols++;
+    }
+    DB2_CHECK(rows <= SK_VEC_SLOTS && cols <= SK_VEC_SLOTS, DB2_EINVAL, "skinny product: too many vector operands");
     const int nt = (a.N + 7) / 8;
 #define DB2_SK(NTV)                                                                                                    \
     case NTV: return a.tb ? launch_skinny<NTV, true>(a, st) : launch_skinny<NTV, false>(a, st);

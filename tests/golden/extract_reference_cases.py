@@ -23,7 +23,12 @@ FILES = ["AggRowTest.cpp", "AggColTest.cpp", "AggAllTest.cpp", "EwBinaryMatTest.
 SCOPE_RE = re.compile(r"^\s*(TEMPLATE_PRODUCT_TEST_CASE|TEMPLATE_TEST_CASE|TEST_CASE|#define\s+\w+TEST_CASE\w*)\b")
 GEN_RE = re.compile(r"(?:auto|\w+\s*\*)\s*(\w+)\s*=\s*genGivenVals<([^>]*(?:<[^>]*>)?[^>]*)>\(\s*(\w+)\s*,\s*\{(.*?)\}\s*\)\s*;",
                     re.S)
-CHECK_RE = re.compile(r"\b(check\w+)\(\s*(?:(\w+OpCode)::(\w+)\s*,\s*)?([^;]*?)\)\s*;")
+CHECK_RE = re.compile(r"\b(check\w+)(?:<[^>;()]*>)?\(\s*(?:(\w+OpCode)::(\w+)\s*,\s*)?([^;]*?)\)\s*;")
+# assignments inside SECTION blocks (CTableTest, TransposeTest): name = genGivenVals<DT>(rows, {...});
+ASSIGN_RE = re.compile(r"(?<![\w*])(\w+)\s*=\s*genGivenVals<([^>]*(?:<[^>]*>)?[^>]*)>\(\s*(\w+)\s*,\s*\{(.*?)\}\s*\)\s*;", re.S)
+SECTION_RE = re.compile(r"SECTION\(\s*\"([^\"]*)\"\s*\)\s*\{")
+SCALAR_ASSIGN_RE = re.compile(r"\b(weight|resNumRows|resNumCols)\s*=\s*([^;{}]+);")
+IGNORED_TOKENS = {"nullptr", "dctx", "dctx.get()", "ctx", "nullptr)"}
 
 _ENV = {"sqrt": math.sqrt, "exp": math.exp, "log": math.log, "sin": math.sin, "cos": math.cos, "tan": math.tan,
         "asin": math.asin, "acos": math.acos, "atan": math.atan, "sinh": math.sinh, "cosh": math.cosh,
@@ -117,7 +122,7 @@ def extract(root: Path):
                 for tok in [t.strip() for t in re.split(r",(?![^()]*\))", rest) if t.strip()]:
                     if tok in mats and mats[tok]["rows"] is not None:
                         args.append({"matrix": tok, **mats[tok]})
-                    elif tok in ("nullptr",):
+                    elif tok in IGNORED_TOKENS:
                         continue
                     else:
                         try:
@@ -129,6 +134,51 @@ def extract(root: Path):
                     continue
                 cases.append({"file": f"test/runtime/local/kernels/{fname}", "line": line, "test": header[:120],
                               "check": fn, "op": op, "args": args})
+            # SolveTest builds A = t(X) X and b = t(X) (X w) with kernels and checks solve(A, b) against w
+            if fname == "SolveTest.cpp" and "X" in mats and "w" in mats and "checkSolve(" in scope:
+                line = text.count("\n", 0, a + scope.index("checkSolve(A")) + 1 if "checkSolve(A" in scope else 0
+                cases.append({"file": f"test/runtime/local/kernels/{fname}", "line": line, "test": header[:120],
+                              "check": "solveNormalEquations", "op": None,
+                              "args": [{"matrix": "X", **mats["X"]}, {"matrix": "w", **mats["w"]}]})
+            # CTableTest / TransposeTest assign their literals inside SECTION blocks and check once after them
+            if fname in ("CTableTest.cpp", "TransposeTest.cpp"):
+                secs = list(SECTION_RE.finditer(scope))
+                for i, sm in enumerate(secs):
+                    body = scope[sm.end(): secs[i + 1].start() if i + 1 < len(secs) else len(scope)]
+                    depth, end = 1, len(body)
+                    for pos, ch in enumerate(body):
+                        depth += ch == "{"
+                        depth -= ch == "}"
+                        if depth == 0:
+                            end = pos
+                            break
+                    body = body[:end]
+                    local = {}
+                    for m in ASSIGN_RE.finditer(body):
+                        name, dt, nrows, vals = m.groups()
+                        try:
+                            local[name] = {"matrix": name, "dt": re.sub(r"\s+", "", dt),
+                                           "rows": int(nrows) if nrows.isdigit() else None,
+                                           "values": [_enc(v) for v in _split_values(vals)]}
+                        except ValueError:
+                            pass
+                    scal = {}
+                    for m in SCALAR_ASSIGN_RE.finditer(body):
+                        try:
+                            scal[m.group(1)] = _enc(_value(m.group(2)))
+                        except ValueError:
+                            pass
+                    line = text.count("\n", 0, a + sm.start()) + 1
+                    if fname == "CTableTest.cpp" and {"ys", "xs", "exp"} <= set(local) and len(scal) == 3:
+                        cases.append({"file": f"test/runtime/local/kernels/{fname}", "line": line,
+                                      "test": sm.group(1)[:120], "check": "ctableSection", "op": None,
+                                      "args": [local["ys"], local["xs"], {"scalar": scal["weight"]},
+                                               {"scalar": scal["resNumRows"]}, {"scalar": scal["resNumCols"]},
+                                               local["exp"]]})
+                    elif fname == "TransposeTest.cpp" and {"m", "mt"} <= set(local):
+                        cases.append({"file": f"test/runtime/local/kernels/{fname}", "line": line,
+                                      "test": sm.group(1)[:120], "check": "transposeSection", "op": None,
+                                      "args": [local["m"], local["mt"]]})
     return cases, skipped
 
 

@@ -1,8 +1,9 @@
 """Known-answer cases of the reference's own unit tests (tests/golden/reference_cases.json, extracted from
 test/runtime/local/kernels/*Test.cpp by tests/golden/extract_reference_cases.py), run against the CPU oracle (always)
 and against the CUDA library (on a GPU).  Tolerances are the ones the reference's tests use: exact for elementwise
-results, 1e-5 absolute for aggregations (checkEqApprox in AggRowTest.cpp:38), 1e-2 for the *Approx unary checks
-(EwUnaryMatTest.cpp:48)."""
+results, matMul, syrk, ctable and transpose (small integer-valued literals, `*res == *exp`), 1e-5 absolute for
+aggregations (checkEqApprox in AggRowTest.cpp:38), 1e-2 for the *Approx unary checks (EwUnaryMatTest.cpp:48), 1e-6
+for solve (SolveTest.cpp:39)."""
 import json
 from pathlib import Path
 
@@ -18,7 +19,8 @@ UN = {n: i for i, n in enumerate(["MINUS", "ABS", "SIGN", "SQRT", "EXP", "LN", "
 AGG = {n: i for i, n in enumerate(["SUM", "PROD", "MIN", "MAX", "IDXMIN", "IDXMAX", "MEAN", "STDDEV", "VAR"])}
 
 DENSE_CHECKS = {"checkAggRow", "checkAggCol", "checkAggAll", "checkEwBinaryMat", "checkEwUnaryMat",
-                "checkEwUnaryMatApprox", "checkEwUnaryMatThrow"}
+                "checkEwUnaryMatApprox", "checkEwUnaryMatThrow", "checkEwBinaryObjSca", "checkMatMul", "checkSyrk",
+                "solveNormalEquations", "ctableSection", "transposeSection"}
 
 
 def _num(v):
@@ -40,12 +42,15 @@ def _dense_cases():
             continue  # string kernels are outside the numeric hot path
         if any("matrix" in a and not a["values"] for a in c["args"]):
             continue
+        if c["check"] == "checkEwBinaryObjSca" and (len(c["args"]) != 3 or "scalar" not in c["args"][1]):
+            continue  # frame / string variants
         out.append(pytest.param(c, id=f"{Path(c['file']).stem}:{c['line']}:{c['op']}"))
     return out
 
 
 class _OracleBackend:
     name = "oracle"
+    dtypes = (np.float64,)  # the oracle restates the double-precision contractions only
 
     def __init__(self):
         from oracle import pyoracle as o
@@ -57,10 +62,17 @@ class _OracleBackend:
     def agg_row(self, op, a): return self.o.aggRow(op, a)
     def agg_col(self, op, a): return self.o.aggCol(op, a)
     def agg_all(self, op, a): return self.o.aggAll(op, a)
+    def binary_sca(self, op, a, s): return self.o.ewBinaryObjSca(op, a, s)
+    def matmul(self, a, b, ta, tb): return self.o.matMul(a, b, ta, tb)
+    def syrk(self, a, tl): return self.o.syrk(a, tl)
+    def transpose(self, a): return self.o.transpose(a)
+    def solve(self, a, b): return self.o.solve(a, b)
+    def ctable(self, ys, xs, w, nr, nc): return self.o.ctable(ys, xs, w, nr, nc)
 
 
 class _CudaBackend:
     name = "cuda"
+    dtypes = (np.float64, np.float32)  # MatMulTest / SyrkTest are instantiated for float and double
 
     def __init__(self, ctx):
         import daphne_b200.kernels as k
@@ -72,6 +84,14 @@ class _CudaBackend:
     def agg_row(self, op, a): return self.k.aggRow(op, self._m(a)).to_numpy()
     def agg_col(self, op, a): return self.k.aggCol(op, self._m(a)).to_numpy()
     def agg_all(self, op, a): return self.k.aggAll(op, self._m(a))
+    def binary_sca(self, op, a, s): return self.k.ewBinaryObjSca(op, self._m(a), s).to_numpy()
+    def matmul(self, a, b, ta, tb): return self.k.matMul(self._m(a), self._m(b), ta, tb).to_numpy()
+    def syrk(self, a, tl): return self.k.syrk(self._m(a), tl).to_numpy()
+    def transpose(self, a): return self.k.transpose(self._m(a)).to_numpy()
+    def solve(self, a, b): return self.k.solve(self._m(a), self._m(b)).to_numpy()
+
+    def ctable(self, ys, xs, w, nr, nc):
+        return self.k.ctable(self._m(ys.astype(np.int64)), self._m(xs.astype(np.int64)), w, nr, nc).to_numpy()
 
 
 def _run_case(be, c):
@@ -98,12 +118,44 @@ def _run_case(be, c):
         arg, exp = _mat(args[0]), _num(args[1]["scalar"])
         got = float(be.agg_all(AGG[op], arg))
         assert abs(got - exp) <= 1e-5 * max(1.0, abs(exp)), f"{c['file']}:{c['line']}: {got} vs {exp}"
+    elif chk == "checkEwBinaryObjSca":
+        arg, sca, exp = _mat(args[0]), float(_num(args[1]["scalar"])), _mat(args[2])
+        assert np.array_equal(be.binary_sca(BIN[op], arg, sca), exp, equal_nan=True), f"{c['file']}:{c['line']}"
+    elif chk == "checkMatMul":
+        lhs, rhs, exp = (_mat(a) for a in args[:3])
+        flags = [bool(_num(a["scalar"])) for a in args[3:]] + [False, False]
+        for dt in be.dtypes:
+            got = be.matmul(lhs.astype(dt), rhs.astype(dt), flags[0], flags[1])
+            assert got.dtype == dt and np.array_equal(got, exp.astype(dt)), f"{c['file']}:{c['line']} {dt.__name__}"
+    elif chk == "checkSyrk":  # syrk against transpose followed by matMul, both orientations (SyrkTest.cpp:32-58)
+        arg = _mat(args[0])
+        for dt in be.dtypes:
+            a = arg.astype(dt)
+            assert np.array_equal(be.syrk(a, True), be.matmul(be.transpose(a), a, False, False))
+            assert np.array_equal(be.syrk(a, False), be.matmul(a, be.transpose(a), False, False))
+            assert np.array_equal(be.syrk(a, True), (arg.T @ arg).astype(dt))
+    elif chk == "solveNormalEquations":  # SolveTest.cpp:43-60
+        X, w = _mat(args[0]), _mat(args[1])
+        y = be.matmul(X, w, False, False)
+        tX = be.transpose(X)
+        A, b = be.matmul(tX, X, False, False), be.matmul(tX, y, False, False)
+        got = be.solve(A, b)
+        assert got.shape == w.shape
+        np.testing.assert_allclose(got, w, atol=1e-6, rtol=0)
+    elif chk == "ctableSection":
+        ys, xs, exp = _mat(args[0]), _mat(args[1]), _mat(args[5])
+        w, nr, nc = (_num(a["scalar"]) for a in args[2:5])
+        got = be.ctable(ys.reshape(-1, 1), xs.reshape(-1, 1), float(w), int(nr), int(nc))
+        assert got.shape == exp.shape and np.array_equal(got, exp), f"{c['file']}:{c['line']}"
+    elif chk == "transposeSection":
+        m, mt = _mat(args[0]), _mat(args[1])
+        assert np.array_equal(be.transpose(m), mt), f"{c['file']}:{c['line']}"
     else:
         raise AssertionError(chk)
 
 
 def test_fixture_is_not_trivial():
-    assert len(_dense_cases()) >= 80
+    assert len(_dense_cases()) >= 130
 
 
 @pytest.mark.parametrize("case", _dense_cases())
