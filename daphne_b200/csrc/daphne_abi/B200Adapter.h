@@ -178,7 +178,13 @@ class Call {
     // new device-only DenseMatrix around a result handle (takes over the reference)
     template <typename VT> DenseMatrix<VT> *wrap(db2_matrix *h) {
         int64_t r = 0, cc = 0;
-        check(db2_matrix_info(h, nullptr, &r, &cc));
+        int dt = -1;
+        check(db2_matrix_info(h, &dt, &r, &cc));
+        if (dt != dtype_of<VT>()) { // an instantiation whose result type the device kernel does not produce
+            db2_matrix_decref(h);
+            throw std::runtime_error("the B200 kernel returned value type code " + std::to_string(dt) +
+                                     " where the caller expects " + std::to_string(dtype_of<VT>()));
+        }
         AllocationDescriptorB200 desc(c, dtype_of<VT>(), r, cc, h);
         return DataObjectFactory::create<DenseMatrix<VT>>((size_t)r, (size_t)cc, false, &desc);
     }

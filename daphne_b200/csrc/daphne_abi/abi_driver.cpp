@@ -151,4 +151,43 @@ int drv_chain(const double *x, int64_t xr, int64_t xc, const double *mu, double 
         return rc;
     });
 }
+// The backend-"CPP" extension kernels (libB200ExtKernels.so), resolved by their catalog names: S = sqrt(X) stays on the
+// device and feeds idxminRow (size_t result), meanCol and varCol; ctable builds a contingency matrix from int64
+// coordinates.  out = [idxmin (xr) | mean (xc) | var (xc) | ctable (tr x tc)].
+int drv_ext(const double *x, int64_t xr, int64_t xc, const int64_t *ys, const int64_t *xs, int64_t n, double weight,
+            int64_t tr, int64_t tc, double *out) {
+    return guarded([&] {
+        using DM = DenseMatrix<double>;
+        using DI = DenseMatrix<int64_t>;
+        using DS = DenseMatrix<size_t>;
+        auto *X = host_matrix(x, xr, xc);
+        DM *S = nullptr, *M = nullptr, *V = nullptr, *T = nullptr;
+        DS *I = nullptr;
+        reinterpret_cast<void (*)(DM **, const DM *, int, DaphneContext *)>(
+            sym("_ewSqrt__DenseMatrix_double__DenseMatrix_double"))(&S, X, 1, &g_ctx);
+        reinterpret_cast<void (*)(DS **, const DM *, int, DaphneContext *)>(
+            sym("_idxminRow__DenseMatrix_size_t__DenseMatrix_double"))(&I, S, 2, &g_ctx);
+        reinterpret_cast<void (*)(DM **, const DM *, int, DaphneContext *)>(
+            sym("_meanCol__DenseMatrix_double__DenseMatrix_double"))(&M, S, 3, &g_ctx);
+        reinterpret_cast<void (*)(DM **, const DM *, int, DaphneContext *)>(
+            sym("_varCol__DenseMatrix_double__DenseMatrix_double"))(&V, S, 4, &g_ctx);
+        auto *Y = DataObjectFactory::create<DI>((size_t)n, 1, false);
+        auto *Xs = DataObjectFactory::create<DI>((size_t)n, 1, false);
+        memcpy(Y->getValues(), ys, sizeof(int64_t) * n);
+        memcpy(Xs->getValues(), xs, sizeof(int64_t) * n);
+        reinterpret_cast<void (*)(DM **, const DI *, const DI *, double, int64_t, int64_t, int, DaphneContext *)>(
+            sym("_ctable__DenseMatrix_double__DenseMatrix_int64_t__DenseMatrix_int64_t__double__int64_t__int64_t"))(
+            &T, Y, Xs, weight, tr, tc, 5, &g_ctx);
+        const size_t *iv = static_cast<const DS *>(I)->getValues();
+        for (int64_t r = 0; r < xr; r++)
+            out[r] = (double)iv[r];
+        int64_t rr, cc;
+        copy_out(M, out + xr, xc, &rr, &cc);
+        copy_out(V, out + xr + xc, xc, &rr, &cc);
+        copy_out(T, out + xr + 2 * xc, tr * tc, &rr, &cc);
+        DataObjectFactory::destroy(X, S, M, V, T, Y, Xs);
+        DataObjectFactory::destroy(I);
+        return 0;
+    });
+}
 }

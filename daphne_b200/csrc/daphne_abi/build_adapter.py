@@ -9,8 +9,13 @@ Steps:
      catalog JSON for backend "CUDA" -- names, argument order and the kId/ctx tail are therefore exactly DAPHNE's;
   3. the wrappers are compiled against the tree's data-structure headers and the headers in include/ here, which carry
      the reference's header names (runtime/local/kernels/CUDA/AggRow.h, ...) and forward to libdaphne_b200.so.
+  4. the same generator, with API "CPP", emits wrappers for operators that DAPHNE's compiler never tags for the CUDA
+     backend (ewUnaryMat, ctable, and the aggregation opcodes beyond SUM/MIN/MAX): they carry the CPU kernels' names
+     (leading "_") and go into an EXTENSION catalog (daphne --kernel-ext B200ExtCatalog.json:1) so that they are
+     preferred over the built-in CPU kernels and keep device-resident operands on the device.
 Nothing of the tree is copied; generated sources and the outputs live in daphne_b200/_abi_build/ (git-ignored):
-    libCUDAKernels.so   CUDAcatalog.json   (+ libabi_driver.so, the JIT stand-in used by the tests)
+    libCUDAKernels.so   CUDAcatalog.json   libB200ExtKernels.so   B200ExtCatalog.json
+    (+ libabi_driver.so, the JIT stand-in used by the tests)
 Outside a DAPHNE build tree (as here) DaphneContext.h / ErrorHandler.h / KernelInstrumentation.h come from shim/."""
 from __future__ import annotations
 
@@ -25,6 +30,62 @@ PKG = HERE.parents[1]
 OUT = PKG / "_abi_build"
 SUPPORTED_HEADERS = {"AggAll.h", "AggCol.h", "AggRow.h", "EwBinaryMat.h", "EwBinaryObjSca.h", "MatMul.h", "Syrk.h",
                      "Gemv.h", "Solve.h", "Transpose.h", "Fill.h", "CreateCUDAContext.h"}
+
+
+# backend-"CPP" extension: header -> opcodes to register (None: all of the entry's opcodes / no opcode)
+EXT_HEADERS = {"EwUnaryMat.h": None, "CTable.h": None,
+               "AggRow.h": {"IDXMIN", "IDXMAX", "MEAN", "VAR", "STDDEV", "PROD"},
+               "AggCol.h": {"IDXMIN", "IDXMAX", "MEAN", "VAR", "STDDEV", "PROD"},
+               "AggAll.h": {"MEAN", "VAR", "STDDEV", "PROD"}}
+DEVICE_VTS = {"double", "float", "int64_t"}
+
+
+def _ext_instantiation_ok(header: str, inst) -> bool:
+    """Dense matrices of the value types the device kernels implement; index results are size_t."""
+    vts, scalars = [], []
+    for tv in inst:
+        if isinstance(tv, list):
+            if tv[0] != "DenseMatrix":
+                return False
+            vts.append(tv[1])
+        else:
+            scalars.append(tv)
+    if header == "CTable.h":  # DTRes, DTLhs, DTRhs, VTWeight
+        return vts == ["double", "int64_t", "int64_t"]
+    if header == "AggAll.h":  # VTRes, DTArg
+        return len(vts) == 1 and vts[0] in ("double", "float") and scalars == vts
+    res, arg = vts[0], vts[-1]
+    if arg not in DEVICE_VTS:
+        return False
+    return res == arg or (header in ("AggRow.h", "AggCol.h") and res == "size_t")
+
+
+def ext_spec(daphne_src: Path) -> list:
+    spec = json.loads((daphne_src / "src/runtime/local/kernels/kernels.json").read_text())
+    keep = []
+    for k in spec:
+        header = k["kernelTemplate"]["header"]
+        if header not in EXT_HEADERS:
+            continue
+        apis = k["api"] if "api" in k else [{"name": ["CPP"], "instantiations": k["instantiations"],
+                                             **({"opCodes": k["opCodes"]} if "opCodes" in k else {})}]
+        out = []
+        for a in apis:
+            names = a["name"] if isinstance(a["name"], list) else [a["name"]]
+            if "CPP" not in names:
+                continue
+            inst = [i for i in a["instantiations"] if _ext_instantiation_ok(header, i)]
+            b = {"name": ["CPP"], "instantiations": inst}
+            if "opCodes" in a:
+                want = EXT_HEADERS[header]
+                b["opCodes"] = [o for o in a["opCodes"] if want is None or o in want]
+                if not b["opCodes"]:
+                    continue
+            if inst:
+                out.append(b)
+        if out:
+            keep.append({"kernelTemplate": k["kernelTemplate"], "api": out})
+    return keep
 
 
 def _is_cuda(api) -> bool:
@@ -78,6 +139,28 @@ def build(daphne_src: str | Path = "/root/reference") -> Path:
     r = subprocess.run(cmd, capture_output=True, text=True)
     if r.returncode != 0:
         raise RuntimeError("compiling the adapter failed:\n" + r.stdout[-4000:] + r.stderr[-8000:])
+    # ---- backend-"CPP" extension catalog ----
+    for old in OUT.glob("B200Extkernels*.cpp"):
+        old.unlink()
+    ext_path = OUT / "kernels_b200_ext.json"
+    ext_path.write_text(json.dumps(ext_spec(daphne_src)))
+    r = subprocess.run([sys.executable, str(daphne_src / "src/runtime/local/kernels/genKernelInst.py"), str(ext_path),
+                        str(OUT / "B200Extkernels"), str(OUT / "B200ExtCatalog.json"), "CPP"],
+                       capture_output=True, text=True)
+    if r.returncode != 0:
+        raise RuntimeError("genKernelInst.py (extension) failed:\n" + r.stdout + r.stderr)
+    cat = json.loads((OUT / "B200ExtCatalog.json").read_text())
+    for e in cat:
+        e["libPath"] = "libB200ExtKernels.so"  # the generator assumes libAllKernels.so for backend "CPP"
+    (OUT / "B200ExtCatalog.json").write_text(json.dumps(cat, indent=1))
+    ext_lib = OUT / "libB200ExtKernels.so"
+    ext_inc = ["-I", str(HERE / "include_cpp")] + inc  # the CPU kernels' header names resolve to the adapter's
+    cmd = ["g++", *flags, "-shared", "-o", str(ext_lib), *ext_inc, *map(str, sorted(OUT.glob("B200Extkernels*.cpp"))),
+           "-L", str(OUT), "-lCUDAKernels", "-L", str(PKG), "-ldaphne_b200", f"-Wl,-rpath,{OUT}", f"-Wl,-rpath,{PKG}",
+           "-Wl,-rpath,$ORIGIN", "-Wl,-rpath,$ORIGIN/.."]
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    if r.returncode != 0:
+        raise RuntimeError("compiling the extension kernels failed:\n" + r.stdout[-4000:] + r.stderr[-8000:])
     drv = OUT / "libabi_driver.so"
     cmd = ["g++", *flags, "-shared", "-o", str(drv), *inc, str(HERE / "abi_driver.cpp"), "-L", str(OUT),
            "-lCUDAKernels", "-L", str(PKG), "-ldaphne_b200", "-ldl", f"-Wl,-rpath,{OUT}", f"-Wl,-rpath,{PKG}",

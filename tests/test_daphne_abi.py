@@ -38,10 +38,30 @@ def test_catalog_symbols_are_exported_with_the_reference_names():
     assert all(e["backend"] == "CUDA" and e["libPath"] == "libCUDAKernels.so" for e in cat)
 
 
+def test_extension_catalog_registers_cpu_names_for_ops_without_cuda_support():
+    """Operators the reference's compiler never tags for CUDA (no CUDASupport trait) are served through an extension
+    catalog under backend "CPP" (daphne --kernel-ext B200ExtCatalog.json:1)."""
+    cat = json.loads((ABI / "B200ExtCatalog.json").read_text())
+    out = subprocess.run(["nm", "-D", "--defined-only", str(ABI / "libB200ExtKernels.so")], capture_output=True,
+                         text=True, check=True).stdout
+    syms = {ln.split()[-1] for ln in out.splitlines() if " T " in ln}
+    names = {e["kernelFuncName"] for e in cat}
+    assert len(names) >= 100 and not (names - syms)
+    assert all(e["backend"] == "CPP" and e["libPath"] == "libB200ExtKernels.so" for e in cat)
+    for must in ("_ewSqrt__DenseMatrix_double__DenseMatrix_double", "_idxminRow__DenseMatrix_size_t__DenseMatrix_double",
+                 "_idxmaxRow__DenseMatrix_size_t__DenseMatrix_double", "_meanCol__DenseMatrix_double__DenseMatrix_double",
+                 "_varCol__DenseMatrix_double__DenseMatrix_double", "_stddevCol__DenseMatrix_double__DenseMatrix_double",
+                 "_ctable__DenseMatrix_double__DenseMatrix_int64_t__DenseMatrix_int64_t__double__int64_t__int64_t"):
+        assert must in names, must
+    # nothing that the CUDA catalog already serves is shadowed
+    assert not any(e["opMnemonic"] in ("sumRow", "minRow", "maxRow", "sumCol", "sumAll") for e in cat)
+
+
 @pytest.fixture(scope="module")
 def drv():
     C.CDLL(str(ROOT / "daphne_b200" / "libdaphne_b200.so"), mode=C.RTLD_GLOBAL)
     C.CDLL(str(ABI / "libCUDAKernels.so"), mode=C.RTLD_GLOBAL)
+    C.CDLL(str(ABI / "libB200ExtKernels.so"), mode=C.RTLD_GLOBAL)
     d = C.CDLL(str(ABI / "libabi_driver.so"), mode=C.RTLD_GLOBAL)
     d.drv_last_error.restype = C.c_char_p
     assert d.drv_init() == 0, d.drv_last_error()
@@ -133,3 +153,23 @@ def test_errors_surface_as_exceptions_with_the_reference_message(drv):
                         i64(5), _p(b), i64(3), i64(2), _p(out), i64(100), C.byref(r), C.byref(c))
     assert rc == 1
     assert b"lhs and rhs must either have the same dimensions" in drv.drv_last_error()
+
+
+@pytest.mark.gpu
+def test_extension_kernels_by_symbol_name(drv):
+    from oracle import pyoracle as o
+    rng = np.random.default_rng(9)
+    n, d = 3000, 17
+    x = rng.random((n, d)) * 4.0
+    x[5, 3] = x[5, 9] = 0.0  # a tie: the lowest index wins
+    ys = rng.integers(0, 6, size=500).astype(np.int64)
+    xs = rng.integers(0, 4, size=500).astype(np.int64)
+    out = np.empty(n + 2 * d + 24)
+    rc = drv.drv_ext(_p(x), C.c_int64(n), C.c_int64(d), _p(ys), _p(xs), C.c_int64(500), C.c_double(2.0),
+                     C.c_int64(6), C.c_int64(4), _p(out))
+    assert rc == 0, drv.drv_last_error()
+    s = np.sqrt(x)
+    assert np.array_equal(out[:n], o.aggRow(4, s).ravel())          # IDXMIN
+    np.testing.assert_allclose(out[n:n + d], o.aggCol(6, s).ravel(), rtol=1e-12)           # MEAN
+    np.testing.assert_allclose(out[n + d:n + 2 * d], o.aggCol(8, s).ravel(), rtol=1e-11)   # VAR
+    assert np.array_equal(out[n + 2 * d:].reshape(6, 4), o.ctable(ys, xs, 2.0, 6, 4))
