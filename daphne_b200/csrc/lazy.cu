@@ -503,6 +503,11 @@ int lazy_try_agg_col(db2_context *ctx, int op, db2_matrix **res, db2_matrix *arg
     std::shared_ptr<const Expr> e = arg->lazy;
     if (e->gemm)
         return DB2_OK; // the deferred product is produced first (ensure_device), then the column kernels run
+    if (op == DB2_AGG_SUM) { // sum((X - mu)^2) right after the column sums of X: answered from the statistics
+        DB2_TRY(colstats_try_sqdev(ctx, *e, res, handled));
+        if (*handled)
+            return DB2_OK;
+    }
     const bool idx = op == DB2_AGG_IDXMIN || op == DB2_AGG_IDXMAX;
     DB2_TRY(prepare_result(ctx, res, idx ? DB2_U64 : DB2_F64, 1, arg->cols));
     FusedProgram P;

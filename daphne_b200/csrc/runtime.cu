@@ -139,6 +139,8 @@ int ensure_device(db2_matrix *m) {
         m->dev = make_devbuf(ctx, (size_t)m->rows * m->cols * es);
         m->dev_off = 0;
         m->dev_ld = m->cols;
+    } else {
+        m->dev->version++;
     }
     if (m->rows * m->cols > 0) {
         if (m->host_ld == m->cols && m->dev_ld == m->cols)
@@ -172,6 +174,8 @@ int prepare_result(db2_context *ctx, db2_matrix **res, int dtype, int64_t rows, 
     r->is_seq = false;
     // a buffer that deferred chains (or other handles) still read is not overwritten: the result gets a fresh one.
     // Row views are the exception: writing through a view is how results are placed into a larger matrix.
+    if (r->dev)
+        r->dev->version++;
     if (!r->dev || (!r->is_view && r->dev.use_count() > 1)) {
         r->dev = make_devbuf(ctx, (size_t)rows * cols * r->esize());
         r->dev_off = 0;
@@ -542,6 +546,9 @@ int db2_aggCol(db2_context *ctx, int op, db2_matrix **res, db2_matrix *arg) {
     DB2_CHECK(res, DB2_EINVAL, "null result slot");
     bool handled = false;
     DB2_TRY(onehot_try_agg_col(ctx, op, res, arg, &handled));
+    if (handled)
+        return DB2_OK;
+    DB2_TRY(colstats_try_agg_col(ctx, op, res, arg, &handled));
     if (handled)
         return DB2_OK;
     DB2_TRY(lazy_try_agg_col(ctx, op, res, arg, &handled));

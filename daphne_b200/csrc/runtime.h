@@ -14,6 +14,7 @@
 namespace db2 {
 struct Expr;
 struct OneHot;
+struct ColStats;
 } // namespace db2
 
 struct db2_matrix;
@@ -39,6 +40,8 @@ struct db2_context {
     // cross-GPU combine (comm.cu): this context's rank among `world` row shards and its NCCL communicator
     int rank = 0, world = 1;
     void *comm = nullptr;
+    // column statistics of the matrix that was last aggregated by columns (colstats.cu)
+    std::shared_ptr<db2::ColStats> colstats;
     std::mutex mu;
     db2_stats stats{};
     // the handle returned by db2_context_create holds one reference, every pooled buffer another: a context is torn
@@ -59,7 +62,16 @@ struct DevBuf {
     void *ptr;
     size_t bytes;
     bool owned;
+    uint64_t version = 0; // bumped whenever a kernel writes into an existing buffer (results placed through views)
     ~DevBuf();
+};
+
+// (pivot, S1, S2) per column of one device-resident matrix, valid while that buffer lives and is not rewritten
+struct ColStats {
+    std::weak_ptr<DevBuf> buf;
+    uint64_t version = 0;
+    int64_t off = 0, ld = 0, rows = 0, cols = 0;
+    std::shared_ptr<DevBuf> stats; // 3 * cols doubles
 };
 
 struct HostBuf {
@@ -165,6 +177,10 @@ struct OneHot { // rows x cols matrix with one stored entry per row: (r, idx[r])
     Operand idx; // int64 column vector
     double weight = 1.0;
 };
+// column aggregation through the one-pass statistics (colstats.cu): SUM / MEAN fill them, VAR / STDDEV and the
+// deferred  sum((X - mu)^2)  are answered from them
+int colstats_try_agg_col(db2_context *ctx, int op, db2_matrix **res, db2_matrix *arg, bool *handled);
+int colstats_try_sqdev(db2_context *ctx, const Expr &e, db2_matrix **res, bool *handled);
 int onehot_force(db2_matrix *m); // writes the dense rows
 int onehot_try_matmul(db2_context *ctx, db2_matrix **res, db2_matrix *lhs, db2_matrix *rhs, int transa, int transb,
                       bool *handled);

@@ -87,8 +87,10 @@ __global__ void __launch_bounds__(SK_THREADS, 2) skinny_gemm_kernel(const __grid
     auto load_tile = [&](int64_t tile, int buf) {
         double *dst = As + (size_t)buf * SK_ROWS * PA;
         const int64_t r0 = tile * SK_ROWS;
+        // packet e = tid, tid + THREADS, ...: row e / packets, packet e % packets, advanced without divisions
+        const int dr = SK_THREADS / packets, dp = SK_THREADS % packets;
+        int r = tid / packets, p = tid % packets;
         for (int e = tid; e < SK_ROWS * packets; e += SK_THREADS) {
-            const int r = e / packets, p = e % packets;
             const int64_t row = r0 + r;
             const int k = 2 * p;
             int bytes = 0;
@@ -97,6 +99,12 @@ __global__ void __launch_bounds__(SK_THREADS, 2) skinny_gemm_kernel(const __grid
             const unsigned d = (unsigned)__cvta_generic_to_shared(dst + r * PA + k);
             const double *src = bytes ? s.A + row * s.lda + k : s.A;
             asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(d), "l"(src), "r"(bytes) : "memory");
+            r += dr;
+            p += dp;
+            if (p >= packets) {
+                p -= packets;
+                r++;
+            }
         }
         // the column-vector operands of these rows travel with the tile (one element per thread and step)
         if (tid < SK_ROWS)
