@@ -28,14 +28,14 @@ sys.path.insert(0, str(ROOT))
 ROWS_PER_GPU = 16_777_216
 COLS = 32
 SEED = 2
-# algorithmic bytes per row of the whole pipeline with nothing materialised: statistics passes read the row twice,
-# the normalise+aggregate pass once more is folded in the survey's minimum of 2 reads + 3 results = 536 B/row
+# algorithmic bytes per row of the whole pipeline with nothing materialised: one statistics pass and one
+# normalise + aggregate pass read the row (2 x 256 B), three row results are written (24 B) = 536 B/row
 PIPELINE_MIN_BYTES_PER_ROW = 2 * COLS * 8 + 24
 # DRAM traffic of the dominant kernel per row, from the ncu capture of the 2,097,152-row case
-# (dram__bytes_read.sum + dram__bytes_write.sum = 536.92 MB + 44.38 MB; profiles/fused_row_ct_kernel_*.md)
+# (dram__bytes_read.sum + dram__bytes_write.sum = 536.92 MB + 44.54 MB; profiles/fused_row_ct_kernel_*.md)
 # FP64 peak of this pool's B200: cuBLAS DGEMM 8192^3 through torch.mm, measured twice on the GPU box (35.4 / 35.5)
 FP64_PEAK_TFLOPS = 35.4
-DOMINANT_TRAFFIC_BYTES_PER_ROW = (536.92e6 + 44.38e6) / 2_097_152
+DOMINANT_TRAFFIC_BYTES_PER_ROW = (536.92e6 + 44.54e6) / 2_097_152
 
 
 def measured_peaks():
