@@ -95,7 +95,15 @@ int db2_syrk(db2_context *ctx, db2_matrix **res, db2_matrix *arg, int trans_left
 int db2_gemv(db2_context *ctx, db2_matrix **res, db2_matrix *mat, db2_matrix *vec) {
     DB2_API_BEGIN
     DB2_CHECK(ctx && res && mat && vec, DB2_EINVAL, "null argument");
-    DB2_CHECK(mat->dtype == DB2_F64 && vec->dtype == DB2_F64, DB2_EUNSUPPORTED, "gemv: only double on the device");
+    if (mat->dtype == DB2_F32 && vec->dtype == DB2_F32) {
+        // f32: t(mat) @ vec as a tensor-core product with one result column (Gemv.h:51-63 calls cblas_sgemv)
+        DB2_CHECK(vec->rows == mat->rows && vec->cols == 1, DB2_EINVAL,
+                  "Gemv - vec must be a column vector with as many rows as mat (%lld), got (%lld x %lld)",
+                  (long long)mat->rows, (long long)vec->rows, (long long)vec->cols);
+        return db2_matMul(ctx, res, mat, vec, 1, 0);
+    }
+    DB2_CHECK(mat->dtype == DB2_F64 && vec->dtype == DB2_F64, DB2_EUNSUPPORTED,
+              "gemv: double or float operands of one type on the device");
     DB2_CHECK(vec->rows == mat->rows && vec->cols == 1, DB2_EINVAL,
               "Gemv - vec must be a column vector with as many rows as mat (%lld), got (%lld x %lld)",
               (long long)mat->rows, (long long)vec->rows, (long long)vec->cols);

@@ -270,6 +270,19 @@ def diagMatrix(arg: DenseMatrix, ctx: Optional[Context] = None) -> DenseMatrix:
     return _res(ctx, h)
 
 
+def readDaphne(ctx: Context, path) -> DenseMatrix:
+    """ReadDaphne.h:44-46: a dense matrix from a .dbdf file, streamed straight into its device placement."""
+    h = C.c_void_p()
+    check(lib.db2_readDaphne(ctx.handle, C.byref(h), str(path).encode()))
+    return _res(ctx, h)
+
+
+def writeDaphne(arg: DenseMatrix, path, ctx: Optional[Context] = None) -> None:
+    """WriteDaphne.h:48-50."""
+    ctx = ctx or arg.ctx
+    check(lib.db2_writeDaphne(ctx.handle, arg.handle, str(path).encode()))
+
+
 def ctable(lhs: DenseMatrix, rhs: DenseMatrix, weight: float = 1.0, resNumRows: int = -1, resNumCols: int = -1,
            ctx: Optional[Context] = None) -> DenseMatrix:
     """CTable.h:44-48: res[lhs[i], rhs[i]] += weight."""

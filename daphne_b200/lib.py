@@ -119,6 +119,8 @@ _SIGS = {
     "db2_diagMatrix": (i32, [vp, _P(vp), vp]),
     "db2_ctable": (i32, [vp, _P(vp), vp, vp, C.c_double, i64, i64]),
     "db2_castObj": (i32, [vp, _P(vp), vp, i32]),
+    "db2_readDaphne": (i32, [vp, _P(vp), C.c_char_p]),
+    "db2_writeDaphne": (i32, [vp, vp, C.c_char_p]),
     "db2_vectorizedPipeline": (i32, [vp, _P(vp), sz, _P(i32), _P(vp), sz, _P(i64), _P(i64), _P(i64), _P(i64), vp, i64]),
     "db2_csr_wrap_host": (i32, [vp, i32, i64, i64, vp, vp, vp, _P(vp)]),
     "db2_csr_slice_rows": (i32, [vp, i64, i64, _P(vp)]),

@@ -313,6 +313,16 @@ int db2_vectorizedPipeline(db2_context *ctx, db2_matrix **outputs, size_t numOut
                            const int64_t *splits, const int64_t *combines, db2_pipeline_fn fun, int64_t batch_rows);
 
 /* ------------------------------------------------------------------------- */
+/* Matrix files                                                               */
+/* ------------------------------------------------------------------------- */
+/* DAPHNE's binary matrix format (doc/BinaryFormat.md), dense matrices of double / float / int64 / uint64 in one dense
+ * block.  Replaces ReadDaphne<DenseMatrix<VT>> (src/runtime/local/io/ReadDaphne.h:58-100) and
+ * WriteDaphne<DenseMatrix<VT>> (src/runtime/local/io/WriteDaphne.h:62-80) for the device path: the file is streamed
+ * through pinned staging buffers directly into (out of) the device placement; no pageable host copy is made. */
+int db2_readDaphne(db2_context *ctx, db2_matrix **res, const char *path);
+int db2_writeDaphne(db2_context *ctx, db2_matrix *m, const char *path);
+
+/* ------------------------------------------------------------------------- */
 /* CSR matrices                                                               */
 /* ------------------------------------------------------------------------- */
 

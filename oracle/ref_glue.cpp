@@ -327,3 +327,31 @@ extern "C" int ref_csr_gemv_f64(const double *vals, const uint64_t *cidx, const 
         DataObjectFactory::destroy(G);
     });
 }
+
+// ReadDaphne / WriteDaphne for DenseMatrix (src/runtime/local/io/ReadDaphne.h:58-100, WriteDaphne.h:62-80): the
+// reference's own serializer writes / reads the .dbdf file
+#include <runtime/local/io/ReadDaphne.h>
+#include <runtime/local/io/WriteDaphne.h>
+#define REF_DBDF(NAME, VT)                                                                                             \
+    extern "C" int ref_write_dbdf_##NAME(const char *path, const VT *v, int64_t rows, int64_t cols) {                  \
+        return guarded([&] {                                                                                           \
+            auto *m = DataObjectFactory::create<DenseMatrix<VT>>((size_t)rows, (size_t)cols, false);                   \
+            memcpy(m->getValues(), v, sizeof(VT) * rows * cols);                                                       \
+            writeDaphne(m, path);                                                                                      \
+            DataObjectFactory::destroy(m);                                                                             \
+        });                                                                                                            \
+    }                                                                                                                  \
+    extern "C" int ref_read_dbdf_##NAME(const char *path, VT *out, int64_t cap, int64_t *rows, int64_t *cols) {        \
+        return guarded([&] {                                                                                           \
+            DenseMatrix<VT> *m = nullptr;                                                                              \
+            readDaphne(m, path);                                                                                       \
+            *rows = (int64_t)m->getNumRows();                                                                          \
+            *cols = (int64_t)m->getNumCols();                                                                          \
+            if (*rows * *cols <= cap)                                                                                  \
+                memcpy(out, m->getValues(), sizeof(VT) * *rows * *cols);                                               \
+            DataObjectFactory::destroy(m);                                                                             \
+        });                                                                                                            \
+    }
+REF_DBDF(f64, double)
+REF_DBDF(f32, float)
+REF_DBDF(i64, int64_t)

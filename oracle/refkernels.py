@@ -159,3 +159,25 @@ def matMulCsrDense(m, rhs):
 
 
 available()  # load the library at import when it exists
+
+
+_DBDF = {np.dtype(np.float64): "f64", np.dtype(np.float32): "f32", np.dtype(np.int64): "i64"}
+
+
+def writeDaphne(arr, path) -> None:
+    """The reference's own WriteDaphne<DenseMatrix<VT>> (src/runtime/local/io/WriteDaphne.h:62-80)."""
+    a = np.ascontiguousarray(arr)
+    f = _f(f"ref_write_dbdf_{_DBDF[a.dtype]}", [C.c_char_p, C.c_void_p, C.c_int64, C.c_int64])
+    _chk(f(str(path).encode(), C.c_void_p(a.ctypes.data), a.shape[0], a.shape[1]))
+
+
+def readDaphne(path, dtype=np.float64):
+    """The reference's own ReadDaphne<DenseMatrix<VT>> (src/runtime/local/io/ReadDaphne.h:58-100)."""
+    import os
+    dt = np.dtype(dtype)
+    cap = max(1, (os.path.getsize(path) - 45) // dt.itemsize)
+    out = np.empty(cap, dtype=dt)
+    r, c = C.c_int64(), C.c_int64()
+    f = _f(f"ref_read_dbdf_{_DBDF[dt]}", [C.c_char_p, C.c_void_p, C.c_int64, C.POINTER(C.c_int64), C.POINTER(C.c_int64)])
+    _chk(f(str(path).encode(), C.c_void_p(out.ctypes.data), cap, C.byref(r), C.byref(c)))
+    return out[: r.value * c.value].reshape(r.value, c.value)

@@ -105,3 +105,13 @@ def test_f32_non_finite_operands_propagate(ctx):
     a[2, 3] = np.nan
     got = k.matMul(k.DenseMatrix.from_numpy(ctx, a), k.DenseMatrix.from_numpy(ctx, b)).to_numpy()
     assert np.isinf(got[1]).all() and np.isnan(got[2]).all() and (got[0] == 8).all() and (got[3] == 8).all()
+
+
+def test_f32_gemv(ctx):
+    k = _k()
+    rng = np.random.default_rng(16)
+    for n, d in [(1000, 1), (20000, 33), (100000, 100)]:
+        x = rng.random((n, d)).astype(np.float32)
+        y = rng.standard_normal((n, 1)).astype(np.float32)
+        got = k.gemv(k.DenseMatrix.from_numpy(ctx, x), k.DenseMatrix.from_numpy(ctx, y)).to_numpy()
+        _check(got, np.ascontiguousarray(x.T), y, f"gemv f32 {n}x{d}")
