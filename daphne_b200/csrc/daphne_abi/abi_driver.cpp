@@ -190,4 +190,51 @@ int drv_ext(const double *x, int64_t xr, int64_t xc, const int64_t *ys, const in
         return 0;
     });
 }
+// A compiled pipeline body as the JIT would emit it (`_vect_cuda0`): calls kernels by their catalog names on its
+// inputs (X: ROWS split, mu: broadcast row vector, s: scalar in the pointer slot), releases the inputs, returns
+//   out0 = sumRow((X - mu) * s)    (ROWS)        out1 = sumCol(X - mu)    (ADD)
+static void pipeline_body(DenseMatrix<double> ***outs, Structure **ins, DaphneContext *ctx) {
+    using DM = DenseMatrix<double>;
+    auto *X = static_cast<DM *>(ins[0]);
+    auto *MU = static_cast<DM *>(ins[1]);
+    double s;
+    memcpy(&s, &ins[2], sizeof(double));
+    DM *D = nullptr, *S = nullptr;
+    reinterpret_cast<void (*)(DM **, const DM *, const DM *, int, DaphneContext *)>(
+        sym("CUDA_ewSub__DenseMatrix_double__DenseMatrix_double__DenseMatrix_double"))(&D, X, MU, 1, ctx);
+    reinterpret_cast<void (*)(DM **, const DM *, double, int, DaphneContext *)>(
+        sym("CUDA_ewMul__DenseMatrix_double__DenseMatrix_double__double"))(&S, D, s, 2, ctx);
+    reinterpret_cast<void (*)(DM **, const DM *, int, DaphneContext *)>(
+        sym("CUDA_sumRow__DenseMatrix_double__DenseMatrix_double"))(outs[0], S, 3, ctx);
+    reinterpret_cast<void (*)(DM **, const DM *, int, DaphneContext *)>(
+        sym("CUDA_sumCol__DenseMatrix_double__DenseMatrix_double"))(outs[1], D, 4, ctx);
+    DataObjectFactory::destroy(D, S, X, MU);
+}
+// calls the scheduler under DAPHNE's symbol name with that body; out = [out0 (xr) | out1 (xc)]
+int drv_pipeline(const double *x, int64_t xr, int64_t xc, const double *mu, double s, double *out) {
+    return guarded([&] {
+        using DM = DenseMatrix<double>;
+        auto *X = host_matrix(x, xr, xc);
+        auto *MU = host_matrix(mu, 1, xc);
+        Structure *inputs[3] = {X, MU, nullptr};
+        memcpy(&inputs[2], &s, sizeof(double));
+        bool is_scalar[3] = {false, false, true};
+        int64_t splits[3] = {1, 0, 0}, combines[2] = {1, 3}, out_rows[2] = {xr, 1}, out_cols[2] = {1, xc};
+        DM *outputs[2] = {nullptr, nullptr};
+        void *funcs[1] = {reinterpret_cast<void *>(&pipeline_body)};
+        reinterpret_cast<void (*)(DM **, size_t, bool *, Structure **, size_t, int64_t *, int64_t *, int64_t *, int64_t *,
+                                  size_t, void **, int, DaphneContext *)>(
+            sym("_vectorizedPipeline__DenseMatrix_double_variadic__size_t__bool__Structure_variadic__size_t__int64_t__"
+                "int64_t__int64_t__int64_t__size_t__void_variadic"))(outputs, 2, is_scalar, inputs, 3, out_rows, out_cols,
+                                                                     splits, combines, 1, funcs, 11, &g_ctx);
+        int64_t r, c;
+        int rc = copy_out(outputs[0], out, xr, &r, &c);
+        if (rc == 0 && (r != xr || c != 1))
+            rc = 4;
+        if (rc == 0)
+            rc = copy_out(outputs[1], out + xr, xc, &r, &c);
+        DataObjectFactory::destroy(X, MU, outputs[0], outputs[1]);
+        return rc;
+    });
+}
 }

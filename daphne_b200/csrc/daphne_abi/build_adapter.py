@@ -155,8 +155,9 @@ def build(daphne_src: str | Path = "/root/reference") -> Path:
     (OUT / "B200ExtCatalog.json").write_text(json.dumps(cat, indent=1))
     ext_lib = OUT / "libB200ExtKernels.so"
     ext_inc = ["-I", str(HERE / "include_cpp")] + inc  # the CPU kernels' header names resolve to the adapter's
+    # ... plus the scheduler entry point under DAPHNE's name (vectorized_pipeline.cpp)
     cmd = ["g++", *flags, "-shared", "-o", str(ext_lib), *ext_inc, *map(str, sorted(OUT.glob("B200Extkernels*.cpp"))),
-           "-L", str(OUT), "-lCUDAKernels", "-L", str(PKG), "-ldaphne_b200", f"-Wl,-rpath,{OUT}", f"-Wl,-rpath,{PKG}",
+           str(HERE / "vectorized_pipeline.cpp"), "-L", str(OUT), "-lCUDAKernels", "-L", str(PKG), "-ldaphne_b200", f"-Wl,-rpath,{OUT}", f"-Wl,-rpath,{PKG}",
            "-Wl,-rpath,$ORIGIN", "-Wl,-rpath,$ORIGIN/.."]
     r = subprocess.run(cmd, capture_output=True, text=True)
     if r.returncode != 0:

@@ -48,6 +48,8 @@ def test_extension_catalog_registers_cpu_names_for_ops_without_cuda_support():
     names = {e["kernelFuncName"] for e in cat}
     assert len(names) >= 100 and not (names - syms)
     assert all(e["backend"] == "CPP" and e["libPath"] == "libB200ExtKernels.so" for e in cat)
+    assert ("_vectorizedPipeline__DenseMatrix_double_variadic__size_t__bool__Structure_variadic__size_t__int64_t__"
+            "int64_t__int64_t__int64_t__size_t__void_variadic") in syms  # the scheduler under DAPHNE's own name
     for must in ("_ewSqrt__DenseMatrix_double__DenseMatrix_double", "_idxminRow__DenseMatrix_size_t__DenseMatrix_double",
                  "_idxmaxRow__DenseMatrix_size_t__DenseMatrix_double", "_meanCol__DenseMatrix_double__DenseMatrix_double",
                  "_varCol__DenseMatrix_double__DenseMatrix_double", "_stddevCol__DenseMatrix_double__DenseMatrix_double",
@@ -173,3 +175,26 @@ def test_extension_kernels_by_symbol_name(drv):
     np.testing.assert_allclose(out[n:n + d], o.aggCol(6, s).ravel(), rtol=1e-12)           # MEAN
     np.testing.assert_allclose(out[n + d:n + 2 * d], o.aggCol(8, s).ravel(), rtol=1e-11)   # VAR
     assert np.array_equal(out[n + 2 * d:].reshape(6, 4), o.ctable(ys, xs, 2.0, 6, 4))
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("batch", [None, 1000, 7777])
+def test_scheduler_under_daphnes_symbol_name(drv, batch, monkeypatch):
+    """_vectorizedPipeline__DenseMatrix_double_variadic__... with a body that calls CUDA_* kernels by name: one batch
+    (results are the body's objects) and several batches (ROWS results copied into place, ADD results folded)."""
+    import os
+    if batch is None:
+        os.environ.pop("DAPHNE_B200_BATCH_ROWS", None)
+    else:
+        os.environ["DAPHNE_B200_BATCH_ROWS"] = str(batch)
+    try:
+        rng = np.random.default_rng(10)
+        n, d = 20000, 24
+        x, mu, s = rng.standard_normal((n, d)), rng.standard_normal((1, d)), 1.75
+        out = np.empty(n + d)
+        rc = drv.drv_pipeline(_p(x), C.c_int64(n), C.c_int64(d), _p(mu), C.c_double(s), _p(out))
+        assert rc == 0, drv.drv_last_error()
+        np.testing.assert_allclose(out[:n], ((x - mu) * s).sum(1), rtol=1e-12, atol=1e-12)
+        np.testing.assert_allclose(out[n:], (x - mu).sum(0), rtol=1e-10, atol=1e-9)
+    finally:
+        os.environ.pop("DAPHNE_B200_BATCH_ROWS", None)
