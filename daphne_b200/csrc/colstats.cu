@@ -176,12 +176,11 @@ static bool stats_match(const db2_context *ctx, const std::shared_ptr<DevBuf> &b
 }
 
 // runs the answer kernel and reads its flag: false = the identity is ill-conditioned for this data
-static int answer_checked(db2_context *ctx, const double *mu, int kind, int64_t rows, int64_t cols, double *out,
-                          bool *ok) {
+static int answer_checked(db2_context *ctx, const DevBuf &stats, const double *mu, int kind, int64_t rows, int64_t cols,
+                          double *out, bool *ok) {
     int32_t *flag = ctx->dev_status + 24;
     DB2_CUDA(cudaMemsetAsync(flag, 0, sizeof(int32_t), ctx->stream));
-    DB2_TRY(col_stats_answer(static_cast<const double *>(ctx->colstats->stats->ptr), cols, rows, mu, kind, out, flag,
-                             ctx->stream));
+    DB2_TRY(col_stats_answer(static_cast<const double *>(stats.ptr), cols, rows, mu, kind, out, flag, ctx->stream));
     int32_t *h = ctx->host_status + 24;
     DB2_CUDA(cudaMemcpyAsync(h, flag, sizeof(int32_t), cudaMemcpyDeviceToHost, ctx->stream));
     DB2_CUDA(cudaStreamSynchronize(ctx->stream));
@@ -194,13 +193,18 @@ static bool stats_candidate(const db2_context *ctx, const db2_matrix *m) {
            m->rows * m->cols >= ((int64_t)1 << 22);
 }
 
-static int run_stats(db2_context *ctx, db2_matrix *arg, int out_mode, double *out) {
+static int run_stats(db2_context *ctx, db2_matrix *arg, int out_mode, double *out,
+                     std::shared_ptr<DevBuf> *stats_out = nullptr) {
     auto cs = std::make_shared<ColStats>();
     cs->stats = make_devbuf(ctx, (size_t)3 * arg->cols * sizeof(double));
     void *scratch = nullptr;
     DB2_TRY(ctx_scratch(ctx, col_stats_scratch_bytes(arg->cols), &scratch));
     DB2_TRY(col_stats_pass(static_cast<const double *>(arg->dev_ptr()), arg->rows, arg->cols, arg->dev_ld, out_mode, out,
                            static_cast<double *>(cs->stats->ptr), scratch, ctx->scratch_bytes, ctx->stream));
+    if (stats_out)
+        *stats_out = cs->stats;
+    if (!arg->dev->owned) // a caller-owned buffer may be rewritten behind the runtime's back: nothing is remembered
+        return DB2_OK;
     cs->buf = arg->dev;
     cs->version = arg->dev->version;
     cs->off = arg->dev_off;
@@ -226,13 +230,16 @@ int colstats_try_agg_col(db2_context *ctx, int op, db2_matrix **res, db2_matrix 
         *handled = true;
         return DB2_OK;
     }
-    if (!stats_match(ctx, arg->dev, arg->dev_off, arg->dev_ld, arg->rows, arg->cols)) {
+    std::shared_ptr<DevBuf> stats;
+    if (stats_match(ctx, arg->dev, arg->dev_off, arg->dev_ld, arg->rows, arg->cols)) {
+        stats = ctx->colstats->stats;
+    } else {
         auto tmp = make_devbuf(ctx, (size_t)arg->cols * sizeof(double));
-        DB2_TRY(run_stats(ctx, arg, 1, static_cast<double *>(tmp->ptr)));
+        DB2_TRY(run_stats(ctx, arg, 1, static_cast<double *>(tmp->ptr), &stats));
     }
     DB2_TRY(prepare_result(ctx, res, DB2_F64, 1, arg->cols));
     bool ok = false;
-    DB2_TRY(answer_checked(ctx, nullptr, op == DB2_AGG_VAR ? 1 : 2, arg->rows, arg->cols,
+    DB2_TRY(answer_checked(ctx, *stats, nullptr, op == DB2_AGG_VAR ? 1 : 2, arg->rows, arg->cols,
                            static_cast<double *>((*res)->dev_ptr()), &ok));
     count(ctx, before);
     *handled = ok; // not ok: the two-pass kernels overwrite the result
@@ -251,8 +258,8 @@ int colstats_try_sqdev(db2_context *ctx, const Expr &e, db2_matrix **res, bool *
     const uint64_t before = g_launches.load();
     DB2_TRY(prepare_result(ctx, res, DB2_F64, 1, e.cols));
     bool ok = false;
-    DB2_TRY(answer_checked(ctx, static_cast<const double *>(sub.operand.ptr(8)), 0, e.rows, e.cols,
-                           static_cast<double *>((*res)->dev_ptr()), &ok));
+    DB2_TRY(answer_checked(ctx, *ctx->colstats->stats, static_cast<const double *>(sub.operand.ptr(8)), 0, e.rows,
+                           e.cols, static_cast<double *>((*res)->dev_ptr()), &ok));
     count(ctx, before);
     *handled = ok;
     return DB2_OK;
