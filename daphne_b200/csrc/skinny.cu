@@ -121,6 +121,13 @@ __global__ void __launch_bounds__(SK_THREADS, 2) skinny_gemm_kernel(const __grid
     int64_t tile = blockIdx.x;
     if (tile < ntiles)
         load_tile(tile, 0);
+    // Two CTAs share an SM (the second half of the grid lands beside the first).  Both alternate between a DMMA phase
+    // and an epilogue of about the same length; started together they would stay in step -- contending for the FP64
+    // pipe in one phase and leaving it idle in the other.  A head start of one phase for half of the CTAs makes the
+    // phases interleave, and the interleaving is stable (whoever has the pipe alone finishes its phase early and waits
+    // in its epilogue).
+    if (gridDim.x > 1 && blockIdx.x >= gridDim.x / 2)
+        __nanosleep(2500);
     asm volatile("cp.async.commit_group;\n" ::: "memory");
     int buf = 0;
     for (; tile < ntiles; tile += gridDim.x, buf ^= 1) {
@@ -162,82 +169,112 @@ __global__ void __launch_bounds__(SK_THREADS, 2) skinny_gemm_kernel(const __grid
                 af[i] = an[i];
         }
 
-        // ---- epilogue: chain, outputs, row extremum ----
+        // ---- epilogue: chain, outputs, row extremum; both rows of the thread (g and g + 8) side by side ----
+        constexpr int NV = NT * 2; // value h * NV + 2 * nt + e is row g + 8 h, column 8 * nt + 2 * t + e
         const int64_t row_base = tile * SK_ROWS + warp * 16 + g;
+        double v[2 * NV];
 #pragma unroll
-        for (int h = 0; h < 2; h++) {
-            const int64_t r = row_base + 8 * h;
-            const bool live = r < s.n;
-            constexpr int NV = NT * 2; // value 2 * nt + e is column 8 * nt + 2 * t + e
-            double v[NV];
+        for (int h = 0; h < 2; h++)
 #pragma unroll
             for (int nt = 0; nt < NT; nt++) {
-                v[2 * nt] = acc[nt][2 * h];
-                v[2 * nt + 1] = acc[nt][2 * h + 1];
+                v[h * NV + 2 * nt] = acc[nt][2 * h];
+                v[h * NV + 2 * nt + 1] = acc[nt][2 * h + 1];
             }
 #pragma unroll 1
-            for (int st = 0; st < P.nsteps; st++) {
-                const FusedStep &fs = P.steps[st];
-                double o[NV];
-                if (fs.kind == FK_ROWVEC) {
+        for (int st = 0; st < P.nsteps; st++) {
+            const FusedStep &fs = P.steps[st];
+            double o[2 * NV];
+            if (fs.kind == FK_ROWVEC) {
 #pragma unroll
-                    for (int nt = 0; nt < NT; nt++) {
-                        const double2 two = *reinterpret_cast<const double2 *>(rv + fs.smem_off * SK_MAXN + nt * 8 + 2 * t);
-                        o[2 * nt] = two.x;
-                        o[2 * nt + 1] = two.y;
-                    }
-                } else {
-                    double colv = fs.imm;
-                    if (fs.kind == FK_COLVEC)
-                        colv = cv[((size_t)buf * SK_VEC_SLOTS + fs.smem_off) * SK_ROWS + warp * 16 + g + 8 * h];
-#pragma unroll
-                    for (int i = 0; i < NV; i++)
-                        o[i] = colv;
+                for (int nt = 0; nt < NT; nt++) {
+                    const double2 two = *reinterpret_cast<const double2 *>(rv + fs.smem_off * SK_MAXN + nt * 8 + 2 * t);
+                    o[2 * nt] = o[NV + 2 * nt] = two.x;
+                    o[2 * nt + 1] = o[NV + 2 * nt + 1] = two.y;
                 }
-                sk_apply<NV>(fs.op, fs.reversed != 0, v, o);
-            }
-            if (P.ew_out && live) {
-                double *out = static_cast<double *>(P.ew_out) + r * P.ew_out_ld;
+            } else {
+                double c0 = fs.imm, c1 = fs.imm;
+                if (fs.kind == FK_COLVEC) {
+                    const double *col = cv + ((size_t)buf * SK_VEC_SLOTS + fs.smem_off) * SK_ROWS + warp * 16 + g;
+                    c0 = col[0];
+                    c1 = col[8];
+                }
 #pragma unroll
                 for (int i = 0; i < NV; i++) {
-                    const int c = (i >> 1) * 8 + 2 * t + (i & 1);
-                    if (c < s.N)
-                        out[c] = v[i];
+                    o[i] = c0;
+                    o[NV + i] = c1;
                 }
             }
+            sk_apply<2 * NV>(fs.op, fs.reversed != 0, v, o);
+        }
+        if (P.ew_out) {
+#pragma unroll
+            for (int h = 0; h < 2; h++) {
+                const int64_t r = row_base + 8 * h;
+                if (r < s.n) {
+                    double *out = static_cast<double *>(P.ew_out) + r * P.ew_out_ld;
+#pragma unroll
+                    for (int i = 0; i < NV; i++) {
+                        const int c = (i >> 1) * 8 + 2 * t + (i & 1);
+                        if (c < s.N)
+                            out[c] = v[h * NV + i];
+                    }
+                }
+            }
+        }
 #pragma unroll 1
-            for (int tp = 0; tp < P.ntaps; tp++) {
-                // first extremum in column order among the non-NaN values; a NaN in column 0 stays (the reference's
-                // scan starts from it and no comparison with NaN succeeds: AggRow.h:71-96)
-                const bool want_max = P.taps[tp].kind == FT_MAX;
-                double best = 0.0;
-                int bi = 0x7fffffff;
+        for (int tp = 0; tp < P.ntaps; tp++) {
+            // First extremum in column order; the maximum is the minimum of the negated values.  The reference's scan
+            // (AggRow.h:71-96) starts from column 0 and uses strict comparisons: a NaN never replaces the running
+            // extremum, and a NaN in column 0 stays.  Here NaNs and the padding columns take part as +inf: they can
+            // only "win" a row whose every real value is +inf or NaN, and such a row's answer is column 0 anyway.
+            // Within a thread columns grow with the slot number, so a strict "<" tournament (depth 4) keeps the first
+            // extremum; only the two cross-lane rounds need the column tie-break.
+            const bool want_max = P.taps[tp].kind == FT_MAX;
+            double best[2];
+            int bi[2];
 #pragma unroll
-                for (int i = 0; i < NV; i++) {
-                    const int c = (i >> 1) * 8 + 2 * t + (i & 1);
-                    const double x = want_max ? -v[i] : v[i]; // the maximum is the minimum of the negated values
-                    if (c < s.N && x == x && (bi == 0x7fffffff || x < best)) {
-                        best = x;
-                        bi = c;
-                    }
-                }
-                const bool nan0 = (t == 0) && !(v[0] == v[0]);
+            for (int h = 0; h < 2; h++) {
+                double x[16];
+                int c[16];
 #pragma unroll
-                for (int m = 1; m <= 2; m <<= 1) {
-                    const double ob = __shfl_xor_sync(0xffffffffu, best, m);
-                    const int oi = __shfl_xor_sync(0xffffffffu, bi, m);
-                    const bool take = oi != 0x7fffffff && (bi == 0x7fffffff || ob < best || (ob == best && oi < bi));
-                    if (take) {
-                        best = ob;
-                        bi = oi;
-                    }
+                for (int i = 0; i < 16; i++) {
+                    const int col = (i >> 1) * 8 + 2 * t + (i & 1);
+                    const double val = i < NV ? v[h * NV + (i < NV ? i : 0)] : 0.0;
+                    x[i] = (i < NV && col < s.N) ? fmin(want_max ? -val : val, (double)INFINITY) : (double)INFINITY;
+                    c[i] = col;
                 }
-                const bool first_nan = __shfl_sync(0xffffffffu, (int)nan0, lane & ~3) != 0;
-                if (live && t == 0) {
-                    double val = want_max ? -best : best;
-                    int pos = bi;
-                    if (first_nan || bi == 0x7fffffff) {
-                        val = v[0]; // column 0 (a NaN), as the sequential scan leaves it
+                // slot i of a round stands for the slots [i, i + w): every column of the left block is lower than
+                // every column of the right block, so keeping the left candidate on ties keeps the first extremum
+#pragma unroll
+                for (int w = 1; w <= 8; w <<= 1)
+#pragma unroll
+                    for (int i = 0; i < 16; i += 2 * w) {
+                        const bool right = x[i + w] < x[i];
+                        x[i] = right ? x[i + w] : x[i];
+                        c[i] = right ? c[i + w] : c[i];
+                    }
+                best[h] = x[0];
+                bi[h] = c[0];
+            }
+#pragma unroll
+            for (int m = 1; m <= 2; m <<= 1)
+#pragma unroll
+                for (int h = 0; h < 2; h++) {
+                    const double ob = __shfl_xor_sync(0xffffffffu, best[h], m);
+                    const int oi = __shfl_xor_sync(0xffffffffu, bi[h], m);
+                    const bool take = ob < best[h] || (ob == best[h] && oi < bi[h]);
+                    best[h] = take ? ob : best[h];
+                    bi[h] = take ? oi : bi[h];
+                }
+#pragma unroll
+            for (int h = 0; h < 2; h++) {
+                const double v0 = __shfl_sync(0xffffffffu, v[h * NV], lane & ~3); // column 0 lives in lane t = 0
+                const int64_t r = row_base + 8 * h;
+                if (r < s.n && t == 0) {
+                    double val = want_max ? -best[h] : best[h];
+                    int pos = bi[h];
+                    if (best[h] == (double)INFINITY) { // nothing below +inf: the scan never left column 0
+                        val = v0;
                         pos = 0;
                     }
                     if (P.taps[tp].out)
