@@ -2,17 +2,19 @@
 // op(B) is K x N with N <= 64.  This is the distance step of k-means,  X @ t(C)  (MatMul.cpp:284-288 in the reference:
 // one dgemm writing the n x k matrix), followed there by three elementwise kernels and a row idxMin.
 //
-// Persistent CTAs (two per SM) keep op(B) in shared memory for the whole launch and stream A through a double-buffered
-// ring of 64-row tiles (16-byte cp.async, zero fill).  Every warp owns 16 rows x all N columns, so after the DMMAs
-// (mma.sync m16n8k16 f64) a row's values sit in the four lanes of a quad: the recorded elementwise chain (scalar,
-// column-vector and row-vector operands) is applied to the accumulators in registers, the row minimum / maximum and
-// its position are reduced with two shuffles, and the n x N product itself is only written if somebody asked for it.
+// One persistent CTA of 16 warps per SM keeps op(B) in shared memory for the whole launch.  Every WARP owns a private
+// 16-row tile buffer and walks its own sequence of tiles -- copy (16-byte cp.async, zero fill), DMMAs
+// (mma.sync m16n8k16 f64), epilogue -- without block-wide barriers, so the warps of an SM drift apart and the FP64 pipe
+// (which the DMMAs and the epilogue's scalar FP64 arithmetic share) always finds a warp with DMMAs to issue.  A warp's
+// 16 rows x all N columns sit in its accumulators with a row's values in the four lanes of a quad: the recorded
+// elementwise chain (scalar, column-vector and row-vector operands) is applied in registers, the row minimum / maximum
+// and its position are reduced with two shuffles, and the n x N product itself is only written if somebody asked for it.
 #include "fused.cuh"
 #include "runtime.h"
 
 namespace db2 {
 
-constexpr int SK_ROWS = 64, SK_THREADS = SK_ROWS * 2, SK_MAXN = 64, SK_MAXK = 128;
+constexpr int SK_WARPS = 16, SK_WROWS = 16, SK_THREADS = SK_WARPS * 32, SK_MAXN = 64, SK_MAXK = 128;
 constexpr int SK_VEC_SLOTS = 4; // row-vector and column-vector operands of a fused chain (each kind)
 
 __device__ __forceinline__ void sk_dmma(double (&c)[4], const double (&a)[8], const double (&b)[4]) {
@@ -54,15 +56,15 @@ bool skinny_op_supported(int op) {
 }
 
 template <int NT, bool TB>
-__global__ void __launch_bounds__(SK_THREADS, 2) skinny_gemm_kernel(const __grid_constant__ SkinnyArgs s) {
+__global__ void __launch_bounds__(SK_THREADS, 1) skinny_gemm_kernel(const __grid_constant__ SkinnyArgs s) {
     extern __shared__ __align__(16) double sm[];
     const int KP = (s.K + 15) / 16 * 16, PA = KP + 4; // pitch = 4 mod 16 doubles: conflict-free fragment loads
     const int PB = TB ? KP + 4 : NT * 8 + 4;
-    double *Bs = sm;                                   // TB: [NT*8][PB] (k contiguous);  else [KP][PB]
-    double *rv = Bs + (TB ? NT * 8 * PB : KP * PB);     // row-vector operands: [slot][64]
-    double *cv = rv + SK_VEC_SLOTS * SK_MAXN;           // column-vector operands of the tile's rows: 2 x [slot][rows]
-    double *As = cv + 2 * SK_VEC_SLOTS * SK_ROWS;       // 2 x [rows][PA]
     const int tid = threadIdx.x, warp = tid / 32, lane = tid % 32, g = lane / 4, t = lane % 4;
+    double *Bs = sm;                                 // TB: [NT*8][PB] (k contiguous);  else [KP][PB]
+    double *rv = Bs + (TB ? NT * 8 * PB : KP * PB);   // row-vector operands: [slot][64]
+    double *At = rv + SK_VEC_SLOTS * SK_MAXN + (size_t)warp * (SK_WROWS * PA + SK_VEC_SLOTS * SK_WROWS);
+    double *cv = At + SK_WROWS * PA;                  // this warp's column-vector operands: [slot][16]
     const FusedProgram &P = s.prog;
 
     // op(B), zero padded to NT*8 columns and KP rows of k
@@ -81,170 +83,126 @@ __global__ void __launch_bounds__(SK_THREADS, 2) skinny_gemm_kernel(const __grid
         if (P.steps[st].kind == FK_ROWVEC)
             for (int c = tid; c < SK_MAXN; c += SK_THREADS)
                 rv[P.steps[st].smem_off * SK_MAXN + c] = c < s.N ? static_cast<const double *>(P.steps[st].ptr)[c] : 0.0;
+    __syncthreads(); // the only block-wide barrier: from here on every warp runs on its own
 
-    const int64_t ntiles = (s.n + SK_ROWS - 1) / SK_ROWS;
+    // Every warp walks its own sequence of 16-row tiles: copy (cp.async), DMMAs, epilogue.  The 16 warps of the SM
+    // drift apart, so while one waits for its copy or works through its epilogue the others keep the FP64 pipe busy.
+    const int64_t ntiles = (s.n + SK_WROWS - 1) / SK_WROWS;
     const int packets = KP / 2; // 16-byte packets per row
-    auto load_tile = [&](int64_t tile, int buf) {
-        double *dst = As + (size_t)buf * SK_ROWS * PA;
-        const int64_t r0 = tile * SK_ROWS;
-        // packet e = tid, tid + THREADS, ...: row e / packets, packet e % packets, advanced without divisions
-        const int dr = SK_THREADS / packets, dp = SK_THREADS % packets;
-        int r = tid / packets, p = tid % packets;
-        for (int e = tid; e < SK_ROWS * packets; e += SK_THREADS) {
-            const int64_t row = r0 + r;
-            const int k = 2 * p;
-            int bytes = 0;
-            if (row < s.n && k < s.K)
-                bytes = (s.K - k >= 2) ? 16 : 8;
-            const unsigned d = (unsigned)__cvta_generic_to_shared(dst + r * PA + k);
-            const double *src = bytes ? s.A + row * s.lda + k : s.A;
-            asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(d), "l"(src), "r"(bytes) : "memory");
-            r += dr;
-            p += dp;
-            if (p >= packets) {
-                p -= packets;
-                r++;
-            }
-        }
-        // the column-vector operands of these rows travel with the tile (one element per thread and step)
-        if (tid < SK_ROWS)
-            for (int st = 0; st < P.nsteps; st++)
-                if (P.steps[st].kind == FK_COLVEC) {
-                    const int64_t row = r0 + tid;
-                    const double *base = static_cast<const double *>(P.steps[st].ptr);
-                    const unsigned d = (unsigned)__cvta_generic_to_shared(cv + ((size_t)buf * SK_VEC_SLOTS + P.steps[st].smem_off) * SK_ROWS + tid);
-                    const int bytes = row < s.n ? 8 : 0;
-                    const double *src = bytes ? base + row * P.steps[st].ld : base;
-                    asm volatile("cp.async.ca.shared.global [%0], [%1], 8, %2;\n" ::"r"(d), "l"(src), "r"(bytes) : "memory");
+    const int dr = 32 / packets, dp = 32 % packets;
+    for (int64_t tile = (int64_t)blockIdx.x * SK_WARPS + warp; tile < ntiles; tile += (int64_t)gridDim.x * SK_WARPS) {
+        const int64_t r0 = tile * SK_WROWS;
+        {
+            int r = lane / packets, p = lane % packets;
+            for (int e = lane; e < SK_WROWS * packets; e += 32) {
+                const int64_t row = r0 + r;
+                const int k = 2 * p;
+                int bytes = 0;
+                if (row < s.n && k < s.K)
+                    bytes = (s.K - k >= 2) ? 16 : 8;
+                const unsigned d = (unsigned)__cvta_generic_to_shared(At + r * PA + k);
+                const double *src = bytes ? s.A + row * s.lda + k : s.A;
+                asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(d), "l"(src), "r"(bytes) : "memory");
+                r += dr;
+                p += dp;
+                if (p >= packets) {
+                    p -= packets;
+                    r++;
                 }
-    };
-    int64_t tile = blockIdx.x;
-    if (tile < ntiles)
-        load_tile(tile, 0);
-    // Two CTAs share an SM (the second half of the grid lands beside the first).  Both alternate between a DMMA phase
-    // and an epilogue of about the same length; started together they would stay in step -- contending for the FP64
-    // pipe in one phase and leaving it idle in the other.  A head start of one phase for half of the CTAs makes the
-    // phases interleave, and the interleaving is stable (whoever has the pipe alone finishes its phase early and waits
-    // in its epilogue).
-    if (gridDim.x > 1 && blockIdx.x >= gridDim.x / 2)
-        __nanosleep(2500);
-    asm volatile("cp.async.commit_group;\n" ::: "memory");
-    int buf = 0;
-    for (; tile < ntiles; tile += gridDim.x, buf ^= 1) {
-        asm volatile("cp.async.wait_group 0;\n" ::: "memory");
-        __syncthreads(); // the tile has landed for everyone, and everyone has left the other buffer
-        if (tile + gridDim.x < ntiles)
-            load_tile(tile + gridDim.x, buf ^ 1);
-        asm volatile("cp.async.commit_group;\n" ::: "memory");
+            }
+            if (lane < SK_WROWS)
+                for (int st = 0; st < P.nsteps; st++)
+                    if (P.steps[st].kind == FK_COLVEC) {
+                        const int64_t row = r0 + lane;
+                        const double *base = static_cast<const double *>(P.steps[st].ptr);
+                        const unsigned d = (unsigned)__cvta_generic_to_shared(cv + P.steps[st].smem_off * SK_WROWS + lane);
+                        const int bytes = row < s.n ? 8 : 0;
+                        const double *src = bytes ? base + row * P.steps[st].ld : base;
+                        asm volatile("cp.async.ca.shared.global [%0], [%1], 8, %2;\n" ::"r"(d), "l"(src), "r"(bytes) : "memory");
+                    }
+            asm volatile("cp.async.commit_group;\ncp.async.wait_group 0;\n" ::: "memory");
+            __syncwarp();
+        }
 
-        const double *At = As + (size_t)buf * SK_ROWS * PA + (size_t)(warp * 16) * PA;
         double acc[NT][4];
 #pragma unroll
         for (int nt = 0; nt < NT; nt++)
 #pragma unroll
             for (int e = 0; e < 4; e++)
                 acc[nt][e] = 0.0;
-        double af[8];
-#pragma unroll
-        for (int i = 0; i < 8; i++)
-            af[i] = At[(g + 8 * (i & 1)) * PA + t + 4 * (i >> 1)];
         for (int ks = 0; ks < KP; ks += 16) {
-            // fragments of the next k-step are fetched while this step's DMMAs run
-            double an[8];
-            const int kn = ks + 16 < KP ? ks + 16 : ks;
+            double af[8];
 #pragma unroll
             for (int i = 0; i < 8; i++)
-                an[i] = At[(g + 8 * (i & 1)) * PA + kn + t + 4 * (i >> 1)];
-            double bf[NT][4];
-#pragma unroll
-            for (int nt = 0; nt < NT; nt++)
-#pragma unroll
-                for (int i = 0; i < 4; i++)
-                    bf[nt][i] = TB ? Bs[(nt * 8 + g) * PB + ks + t + 4 * i] : Bs[(ks + t + 4 * i) * PB + nt * 8 + g];
-#pragma unroll
-            for (int nt = 0; nt < NT; nt++)
-                sk_dmma(acc[nt], af, bf[nt]);
-#pragma unroll
-            for (int i = 0; i < 8; i++)
-                af[i] = an[i];
-        }
-
-        // ---- epilogue: chain, outputs, row extremum; both rows of the thread (g and g + 8) side by side ----
-        constexpr int NV = NT * 2; // value h * NV + 2 * nt + e is row g + 8 h, column 8 * nt + 2 * t + e
-        const int64_t row_base = tile * SK_ROWS + warp * 16 + g;
-        double v[2 * NV];
-#pragma unroll
-        for (int h = 0; h < 2; h++)
+                af[i] = At[(g + 8 * (i & 1)) * PA + ks + t + 4 * (i >> 1)];
 #pragma unroll
             for (int nt = 0; nt < NT; nt++) {
-                v[h * NV + 2 * nt] = acc[nt][2 * h];
-                v[h * NV + 2 * nt + 1] = acc[nt][2 * h + 1];
+                double bf[4];
+#pragma unroll
+                for (int i = 0; i < 4; i++)
+                    bf[i] = TB ? Bs[(nt * 8 + g) * PB + ks + t + 4 * i] : Bs[(ks + t + 4 * i) * PB + nt * 8 + g];
+                sk_dmma(acc[nt], af, bf);
+            }
+        }
+
+        // ---- epilogue: chain, outputs, row extremum, for the thread's two rows g and g + 8 ----
+        constexpr int NV = NT * 2; // value 2 * nt + e is column 8 * nt + 2 * t + e
+#pragma unroll
+        for (int h = 0; h < 2; h++) {
+            const int64_t r = r0 + g + 8 * h;
+            double v[NV];
+#pragma unroll
+            for (int nt = 0; nt < NT; nt++) {
+                v[2 * nt] = acc[nt][2 * h];
+                v[2 * nt + 1] = acc[nt][2 * h + 1];
             }
 #pragma unroll 1
-        for (int st = 0; st < P.nsteps; st++) {
-            const FusedStep &fs = P.steps[st];
-            double o[2 * NV];
-            if (fs.kind == FK_ROWVEC) {
+            for (int st = 0; st < P.nsteps; st++) {
+                const FusedStep &fs = P.steps[st];
+                double o[NV];
+                if (fs.kind == FK_ROWVEC) {
 #pragma unroll
-                for (int nt = 0; nt < NT; nt++) {
-                    const double2 two = *reinterpret_cast<const double2 *>(rv + fs.smem_off * SK_MAXN + nt * 8 + 2 * t);
-                    o[2 * nt] = o[NV + 2 * nt] = two.x;
-                    o[2 * nt + 1] = o[NV + 2 * nt + 1] = two.y;
+                    for (int nt = 0; nt < NT; nt++) {
+                        const double2 two = *reinterpret_cast<const double2 *>(rv + fs.smem_off * SK_MAXN + nt * 8 + 2 * t);
+                        o[2 * nt] = two.x;
+                        o[2 * nt + 1] = two.y;
+                    }
+                } else {
+                    const double colv = fs.kind == FK_COLVEC ? cv[fs.smem_off * SK_WROWS + g + 8 * h] : fs.imm;
+#pragma unroll
+                    for (int i = 0; i < NV; i++)
+                        o[i] = colv;
                 }
-            } else {
-                double c0 = fs.imm, c1 = fs.imm;
-                if (fs.kind == FK_COLVEC) {
-                    const double *col = cv + ((size_t)buf * SK_VEC_SLOTS + fs.smem_off) * SK_ROWS + warp * 16 + g;
-                    c0 = col[0];
-                    c1 = col[8];
-                }
+                sk_apply<NV>(fs.op, fs.reversed != 0, v, o);
+            }
+            if (P.ew_out && r < s.n) {
+                double *out = static_cast<double *>(P.ew_out) + r * P.ew_out_ld;
 #pragma unroll
                 for (int i = 0; i < NV; i++) {
-                    o[i] = c0;
-                    o[NV + i] = c1;
+                    const int c = (i >> 1) * 8 + 2 * t + (i & 1);
+                    if (c < s.N)
+                        out[c] = v[i];
                 }
             }
-            sk_apply<2 * NV>(fs.op, fs.reversed != 0, v, o);
-        }
-        if (P.ew_out) {
-#pragma unroll
-            for (int h = 0; h < 2; h++) {
-                const int64_t r = row_base + 8 * h;
-                if (r < s.n) {
-                    double *out = static_cast<double *>(P.ew_out) + r * P.ew_out_ld;
-#pragma unroll
-                    for (int i = 0; i < NV; i++) {
-                        const int c = (i >> 1) * 8 + 2 * t + (i & 1);
-                        if (c < s.N)
-                            out[c] = v[h * NV + i];
-                    }
-                }
-            }
-        }
 #pragma unroll 1
-        for (int tp = 0; tp < P.ntaps; tp++) {
-            // First extremum in column order; the maximum is the minimum of the negated values.  The reference's scan
-            // (AggRow.h:71-96) starts from column 0 and uses strict comparisons: a NaN never replaces the running
-            // extremum, and a NaN in column 0 stays.  Here NaNs and the padding columns take part as +inf: they can
-            // only "win" a row whose every real value is +inf or NaN, and such a row's answer is column 0 anyway.
-            // Within a thread columns grow with the slot number, so a strict "<" tournament (depth 4) keeps the first
-            // extremum; only the two cross-lane rounds need the column tie-break.
-            const bool want_max = P.taps[tp].kind == FT_MAX;
-            double best[2];
-            int bi[2];
-#pragma unroll
-            for (int h = 0; h < 2; h++) {
+            for (int tp = 0; tp < P.ntaps; tp++) {
+                // First extremum in column order; the maximum is the minimum of the negated values.  The reference's
+                // scan (AggRow.h:71-96) starts from column 0 and uses strict comparisons: a NaN never replaces the
+                // running extremum, and a NaN in column 0 stays.  Here NaNs and the padding columns take part as
+                // +inf: they can only "win" a row whose every real value is +inf or NaN, and such a row's answer is
+                // column 0 anyway.  Block tournament (depth 4): slot i of a round stands for the slots [i, i + w);
+                // every column of the left block is lower than every column of the right block, so keeping the left
+                // candidate on ties keeps the first extremum.  Only the two cross-lane rounds need a column tie-break.
+                const bool want_max = P.taps[tp].kind == FT_MAX;
                 double x[16];
                 int c[16];
 #pragma unroll
                 for (int i = 0; i < 16; i++) {
                     const int col = (i >> 1) * 8 + 2 * t + (i & 1);
-                    const double val = i < NV ? v[h * NV + (i < NV ? i : 0)] : 0.0;
+                    const double val = i < NV ? v[i < NV ? i : 0] : 0.0;
                     x[i] = (i < NV && col < s.N) ? fmin(want_max ? -val : val, (double)INFINITY) : (double)INFINITY;
                     c[i] = col;
                 }
-                // slot i of a round stands for the slots [i, i + w): every column of the left block is lower than
-                // every column of the right block, so keeping the left candidate on ties keeps the first extremum
 #pragma unroll
                 for (int w = 1; w <= 8; w <<= 1)
 #pragma unroll
@@ -253,27 +211,21 @@ __global__ void __launch_bounds__(SK_THREADS, 2) skinny_gemm_kernel(const __grid
                         x[i] = right ? x[i + w] : x[i];
                         c[i] = right ? c[i + w] : c[i];
                     }
-                best[h] = x[0];
-                bi[h] = c[0];
-            }
+                double best = x[0];
+                int bi = c[0];
 #pragma unroll
-            for (int m = 1; m <= 2; m <<= 1)
-#pragma unroll
-                for (int h = 0; h < 2; h++) {
-                    const double ob = __shfl_xor_sync(0xffffffffu, best[h], m);
-                    const int oi = __shfl_xor_sync(0xffffffffu, bi[h], m);
-                    const bool take = ob < best[h] || (ob == best[h] && oi < bi[h]);
-                    best[h] = take ? ob : best[h];
-                    bi[h] = take ? oi : bi[h];
+                for (int m = 1; m <= 2; m <<= 1) {
+                    const double ob = __shfl_xor_sync(0xffffffffu, best, m);
+                    const int oi = __shfl_xor_sync(0xffffffffu, bi, m);
+                    const bool take = ob < best || (ob == best && oi < bi);
+                    best = take ? ob : best;
+                    bi = take ? oi : bi;
                 }
-#pragma unroll
-            for (int h = 0; h < 2; h++) {
-                const double v0 = __shfl_sync(0xffffffffu, v[h * NV], lane & ~3); // column 0 lives in lane t = 0
-                const int64_t r = row_base + 8 * h;
+                const double v0 = __shfl_sync(0xffffffffu, v[0], lane & ~3); // column 0 lives in lane t = 0
                 if (r < s.n && t == 0) {
-                    double val = want_max ? -best[h] : best[h];
-                    int pos = bi[h];
-                    if (best[h] == (double)INFINITY) { // nothing below +inf: the scan never left column 0
+                    double val = want_max ? -best : best;
+                    int pos = bi;
+                    if (best == (double)INFINITY) { // nothing below +inf: the scan never left column 0
                         val = v0;
                         pos = 0;
                     }
@@ -284,14 +236,14 @@ __global__ void __launch_bounds__(SK_THREADS, 2) skinny_gemm_kernel(const __grid
                 }
             }
         }
+        __syncwarp(); // every lane is done with this tile's shared memory before the next copy overwrites it
     }
-    asm volatile("cp.async.wait_group 0;\n" ::: "memory");
 }
 
 static size_t skinny_smem(int K, int nt, bool tb) {
     const int KP = (K + 15) / 16 * 16, PA = KP + 4, PB = tb ? KP + 4 : nt * 8 + 4;
-    return ((size_t)(tb ? nt * 8 * PB : KP * PB) + SK_VEC_SLOTS * SK_MAXN + 2 * SK_VEC_SLOTS * SK_ROWS +
-            2 * (size_t)SK_ROWS * PA) * sizeof(double);
+    return ((size_t)(tb ? nt * 8 * PB : KP * PB) + SK_VEC_SLOTS * SK_MAXN +
+            (size_t)SK_WARPS * (SK_WROWS * PA + SK_VEC_SLOTS * SK_WROWS)) * sizeof(double);
 }
 
 bool skinny_shape_ok(int64_t n, int64_t K, int64_t N, const void *A, int64_t lda) {
@@ -308,11 +260,8 @@ template <int NT, bool TB> static int launch_skinny(const SkinnyArgs &a, cudaStr
                                       220 * 1024));
         attr = true;
     }
-    const int64_t ntiles = (a.n + SK_ROWS - 1) / SK_ROWS;
-    // two CTAs per SM when shared memory allows: while one is in its epilogue the other keeps the DMMA pipe busy
-    const int per_sm = smem <= 110 * 1024 ? 2 : 1;
-    const int64_t slots = (int64_t)sm_count() * per_sm;
-    const int grid = (int)(ntiles < slots ? ntiles : slots);
+    const int64_t ctas = ((a.n + SK_WROWS - 1) / SK_WROWS + SK_WARPS - 1) / SK_WARPS;
+    const int grid = (int)(ctas < sm_count() ? ctas : sm_count());
     skinny_gemm_kernel<NT, TB><<<grid, SK_THREADS, smem, st>>>(a);
     return after_launch("skinny_gemm_kernel");
 }
