@@ -55,10 +55,13 @@ bool skinny_op_supported(int op) {
            op == FO_MAX || op == FO_NEG || op == FO_ABS;
 }
 
-template <int NT, bool TB>
+// KPT: the contraction length rounded up to 16 as a compile-time constant (0: taken from the arguments).  With it every
+// fragment address is one base register plus an immediate; the general form spends most of its instructions on
+// address arithmetic.
+template <int NT, bool TB, int KPT>
 __global__ void __launch_bounds__(SK_THREADS, 1) skinny_gemm_kernel(const __grid_constant__ SkinnyArgs s) {
     extern __shared__ __align__(16) double sm[];
-    const int KP = (s.K + 15) / 16 * 16, PA = KP + 4; // pitch = 4 mod 16 doubles: conflict-free fragment loads
+    const int KP = KPT ? KPT : (s.K + 15) / 16 * 16, PA = KP + 4; // pitch = 4 mod 16 doubles: conflict-free fragments
     const int PB = TB ? KP + 4 : NT * 8 + 4;
     const int tid = threadIdx.x, warp = tid / 32, lane = tid % 32, g = lane / 4, t = lane % 4;
     double *Bs = sm;                                 // TB: [NT*8][PB] (k contiguous);  else [KP][PB]
@@ -252,18 +255,26 @@ bool skinny_shape_ok(int64_t n, int64_t K, int64_t N, const void *A, int64_t lda
            skinny_smem((int)K, (int)((N + 7) / 8), false) <= 220 * 1024;
 }
 
-template <int NT, bool TB> static int launch_skinny(const SkinnyArgs &a, cudaStream_t st) {
+template <int NT, bool TB, int KPT> static int launch_skinny_k(const SkinnyArgs &a, cudaStream_t st) {
     const size_t smem = skinny_smem(a.K, NT, TB);
     static bool attr = false;
     if (!attr) {
-        DB2_CUDA(cudaFuncSetAttribute(skinny_gemm_kernel<NT, TB>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        DB2_CUDA(cudaFuncSetAttribute(skinny_gemm_kernel<NT, TB, KPT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                       220 * 1024));
         attr = true;
     }
     const int64_t ctas = ((a.n + SK_WROWS - 1) / SK_WROWS + SK_WARPS - 1) / SK_WARPS;
     const int grid = (int)(ctas < sm_count() ? ctas : sm_count());
-    skinny_gemm_kernel<NT, TB><<<grid, SK_THREADS, smem, st>>>(a);
+    skinny_gemm_kernel<NT, TB, KPT><<<grid, SK_THREADS, smem, st>>>(a);
     return after_launch("skinny_gemm_kernel");
+}
+template <int NT, bool TB> static int launch_skinny(const SkinnyArgs &a, cudaStream_t st) {
+    switch ((a.K + 15) / 16 * 16) { // the common contraction lengths get their own instantiation
+    case 16: return launch_skinny_k<NT, TB, 16>(a, st);
+    case 32: return launch_skinny_k<NT, TB, 32>(a, st);
+    case 64: return launch_skinny_k<NT, TB, 64>(a, st);
+    default: return launch_skinny_k<NT, TB, 0>(a, st);
+    }
 }
 
 int skinny_vec_slots() { return SK_VEC_SLOTS; }
