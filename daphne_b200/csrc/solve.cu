@@ -87,6 +87,101 @@ __global__ void __launch_bounds__(LU_THREADS)
         A[(k0 + e / nb) * n + k0 + e % nb] = P[(e / nb) * pitch + e % nb];
 }
 
+// The same factorisation for panels of at most 512 rows: one thread per ROW, the row's 32 panel entries in registers.
+// Per column: block-wide argmax of |a[j]| (shuffles + one barrier), exchange of the pivot row and row j through shared
+// memory (one barrier), then every thread below the diagonal scales its a[j] and updates its remaining entries from
+// the broadcast pivot row -- two barriers per column instead of five, no shared-memory traffic for the updates.
+constexpr int LU_NB = 32, LU_REG_ROWS = 512;
+__global__ void __launch_bounds__(LU_REG_ROWS)
+    lu_panel_reg_kernel(double *__restrict__ A, int64_t n, int64_t k0, int nb, int *__restrict__ piv,
+                        int32_t *__restrict__ status) {
+    __shared__ double rowbuf[2][2][LU_NB]; // [column parity][pivot row / row j][entries]
+    __shared__ double s_val[2][LU_REG_ROWS / 32];
+    __shared__ int s_idx[2][LU_REG_ROWS / 32];
+    const int tid = threadIdx.x, lane = tid % 32, warp = tid / 32, nwarps = blockDim.x / 32;
+    const int m = (int)(n - k0);
+    double a[LU_NB];
+#pragma unroll
+    for (int c = 0; c < LU_NB; c++)
+        a[c] = (tid < m && c < nb) ? A[(k0 + tid) * n + k0 + c] : 0.0;
+#pragma unroll
+    for (int j = 0; j < LU_NB; j++) {
+        if (j >= nb)
+            break;
+        const int par = j & 1;
+        // first largest |a[j]| among the rows j .. m-1 (idamax)
+        double best = (tid >= j && tid < m) ? fabs(a[j]) : -1.0;
+        int bi = tid;
+        if (best != best) // a NaN pivot candidate: treated as "not larger" like the comparison of the scan
+            best = -1.0;
+#pragma unroll
+        for (int o = 16; o >= 1; o >>= 1) {
+            const double ov = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+            if (ov > best || (ov == best && oi < bi)) {
+                best = ov;
+                bi = oi;
+            }
+        }
+        if (lane == 0) {
+            s_val[par][warp] = best;
+            s_idx[par][warp] = bi;
+        }
+        __syncthreads();
+        best = lane < nwarps ? s_val[par][lane] : -1.0;
+        bi = lane < nwarps ? s_idx[par][lane] : 0x7fffffff;
+#pragma unroll
+        for (int o = 16; o >= 1; o >>= 1) {
+            const double ov = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+            if (ov > best || (ov == best && oi < bi)) {
+                best = ov;
+                bi = oi;
+            }
+        }
+        const int p = bi; // every thread has the same answer
+        if (tid == 0) {
+            piv[k0 + j] = (int)k0 + p;
+            if (!(best > 0.0) && *status == 0)
+                *status = (int32_t)(k0 + j + 1); // exactly singular (or NaN) pivot
+        }
+        if (tid == p) {
+#pragma unroll
+            for (int c = 0; c < LU_NB; c++)
+                rowbuf[par][0][c] = a[c];
+        }
+        if (tid == j) {
+#pragma unroll
+            for (int c = 0; c < LU_NB; c++)
+                rowbuf[par][1][c] = a[c];
+        }
+        __syncthreads();
+        if (p != j) { // the two rows change places
+            if (tid == j) {
+#pragma unroll
+                for (int c = 0; c < LU_NB; c++)
+                    a[c] = rowbuf[par][0][c];
+            } else if (tid == p) {
+#pragma unroll
+                for (int c = 0; c < LU_NB; c++)
+                    a[c] = rowbuf[par][1][c];
+            }
+        }
+        if (tid > j && tid < m) {
+            const double l = __ddiv_rn(a[j], rowbuf[par][0][j]);
+            a[j] = l;
+#pragma unroll
+            for (int c = j + 1; c < LU_NB; c++)
+                a[c] = __fma_rn(-l, rowbuf[par][0][c], a[c]);
+        }
+    }
+    if (tid < m)
+#pragma unroll
+        for (int c = 0; c < LU_NB; c++)
+            if (c < nb)
+                A[(k0 + tid) * n + k0 + c] = a[c];
+}
+
 // One thread per column outside the panel (column index n stands for the right-hand side): row exchanges of the
 // panel, then -- right of the panel and for b -- the forward substitution with the panel's unit lower triangle.
 __global__ void lu_swap_trsm_kernel(double *__restrict__ A, double *__restrict__ x, int64_t n, int64_t k0, int nb,
@@ -198,8 +293,14 @@ extern "C" int db2k_solve(int dtype, void *a_work, int64_t n, void *x_inout, int
         const int w = (int)((n - k0 < nb) ? (n - k0) : nb);
         const int64_t m = n - k0;
         const int threads = m * w >= 4096 ? LU_THREADS : 256;
-        lu_panel_kernel<<<1, threads, (size_t)m * (w + 1) * 8, st>>>(A, n, k0, w, piv, dev_status);
-        DB2_TRY(after_launch("lu_panel_kernel"));
+        if (m <= LU_REG_ROWS && w <= LU_NB) {
+            const int rows32 = (int)((m + 31) / 32 * 32);
+            lu_panel_reg_kernel<<<1, rows32, 0, st>>>(A, n, k0, w, piv, dev_status);
+            DB2_TRY(after_launch("lu_panel_reg_kernel"));
+        } else {
+            lu_panel_kernel<<<1, threads, (size_t)m * (w + 1) * 8, st>>>(A, n, k0, w, piv, dev_status);
+            DB2_TRY(after_launch("lu_panel_kernel"));
+        }
         lu_swap_trsm_kernel<<<(unsigned)((n + 1 + 127) / 128), 128, 0, st>>>(A, x, n, k0, w, piv);
         DB2_TRY(after_launch("lu_swap_trsm_kernel"));
         const int64_t rest = n - k0 - w;
