@@ -4,9 +4,9 @@
 // cblas_ssyrk (Syrk.h:80-92), i.e. with full single-precision products.  The tensor cores take f32 operands as TF32
 // (10 explicit mantissa bits, the low 13 bits of the f32 pattern are ignored), so every operand is used twice,
 //      x = hi + lo,   hi = x with the low 13 mantissa bits cleared (the raw tile as the tensor core reads it),
-//                     lo = tf32(x - hi)   (x - hi is exact in f32),
+//                     lo = x - hi   (exact in f32; the tensor core keeps its leading 11 bits),
 // and three MMAs per k-step accumulate  hi*hi  and  hi*lo + lo*hi  in two f32 accumulators; the dropped lo*lo term
-// and the rounding of lo are about 2^-20 relative per product, the same order as sgemm's own rounding.
+// and the truncation of lo are about 2^-20 relative per product, the same order as sgemm's own rounding.
 //
 // One CTA computes a 128 x 128 tile of C (or one split-K share of it):
 //   warps 0-7   producers: cp.async (16 bytes, zero-filling) of the raw f32 tiles into a 5-slot ring of shared memory,
@@ -42,7 +42,7 @@ constexpr long long WAIT_LIMIT_CLOCKS = 2000000000LL;
 
 // bits of the status word
 constexpr int STATUS_WAIT_EXPIRED = 1; // a bounded wait ran out: the result is not valid
-constexpr int STATUS_NONFINITE = 2;    // an operand held inf / NaN: the result was recomputed by the plain kernel
+constexpr int STATUS_NONFINITE = 2;    // a result was inf / NaN (inf / NaN operands, overflow): recomputed by the plain kernel
 
 struct TcArgs {
     const float *A, *B;
@@ -256,25 +256,16 @@ __device__ __forceinline__ void issue_planned(PacketPlan &pl, uint32_t tile) {
 }
 
 // The tensor core reads an f32 bit pattern as TF32 by ignoring the low 13 mantissa bits, so the raw tile already is
-// the high part  hi = x with those bits cleared;  lo = tf32(x - hi)  (the difference is exact) goes to a second tile.
-__device__ __forceinline__ float low_part(float x, bool &non_finite) {
-    const uint32_t b = __float_as_uint(x);
-    if ((b & 0x7F800000u) == 0x7F800000u) {
-        non_finite = true; // inf / NaN: the split product would turn inf * 1 into inf * 0 = NaN; see STATUS_NONFINITE
-        return 0.f;
-    }
-    const float d = x - __uint_as_float(b & 0xFFFFE000u);
-    uint32_t l;
-    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(l) : "f"(d));
-    return __uint_as_float(l);
-}
-template <bool KMAJ>
-__device__ __forceinline__ void make_low_tile(unsigned char *raw, unsigned char *lo, int tid, bool &nf) {
+// the high part  hi = x with those bits cleared;  lo = x - hi  (exact in f32, 13 significant bits of which the tensor
+// core again keeps the leading 11) goes to a second tile.  Two instructions per element: the producers are the
+// kernel's bottleneck.  inf / NaN operands give lo = NaN and therefore non-finite results, which the drain warps detect.
+__device__ __forceinline__ float low_part(float x) { return x - __uint_as_float(__float_as_uint(x) & 0xFFFFE000u); }
+template <bool KMAJ> __device__ __forceinline__ void make_low_tile(unsigned char *raw, unsigned char *lo, int tid) {
 #pragma unroll
     for (int i = 0; i < 4; i++) {
         const uint32_t off = packet_offset<KMAJ>(tid + i * PRODUCER_THREADS);
         const float4 x = *reinterpret_cast<const float4 *>(raw + off);
-        *reinterpret_cast<float4 *>(lo + off) = make_float4(low_part(x.x, nf), low_part(x.y, nf), low_part(x.z, nf), low_part(x.w, nf));
+        *reinterpret_cast<float4 *>(lo + off) = make_float4(low_part(x.x), low_part(x.y), low_part(x.z), low_part(x.w));
     }
 }
 
@@ -357,7 +348,6 @@ template <bool TA, bool TB> __global__ void __launch_bounds__(THREADS, 1) gemm_t
             else
                 issue_tile<B_KMAJ>(g.B, g.ldb, n0, g.N, k0, kend, fast_b, tid, st + TILE_BYTES);
         };
-        bool non_finite = false;
         for (int kb = 0; kb < LOOKAHEAD; kb++) {
             if (kb < nkb)
                 issue(kb);
@@ -368,8 +358,8 @@ template <bool TA, bool TB> __global__ void __launch_bounds__(THREADS, 1) gemm_t
             if (kb >= LOW_SLOTS && !mma_done(kb - LOW_SLOTS))
                 break;
             unsigned char *raw = tiles + (kb % RAW_SLOTS) * SLOT_BYTES, *low = low_tiles + (kb % LOW_SLOTS) * SLOT_BYTES;
-            make_low_tile<A_KMAJ>(raw, low, tid, non_finite);
-            make_low_tile<B_KMAJ>(raw + TILE_BYTES, low + TILE_BYTES, tid, non_finite);
+            make_low_tile<A_KMAJ>(raw, low, tid);
+            make_low_tile<B_KMAJ>(raw + TILE_BYTES, low + TILE_BYTES, tid);
             fence_proxy_async_smem(); // own cp.async data and stores -> visible to the tensor core's async proxy
             mbar_arrive(smem_u32(full + kb % LOW_SLOTS));
             // refill the raw slot that k-block kb - 1 is leaving (its MMAs ran while this block was prepared)
@@ -382,8 +372,6 @@ template <bool TA, bool TB> __global__ void __launch_bounds__(THREADS, 1) gemm_t
             cp_async_commit();
         }
         cp_async_wait<0>();
-        if (non_finite)
-            atomicOr(g.status, STATUS_NONFINITE);
     } else if (warp == MMA_WARP) {
         if (lane == 0) {
             // ---------------- MMA issuer ----------------
@@ -459,6 +447,14 @@ template <bool TA, bool TB> __global__ void __launch_bounds__(THREADS, 1) gemm_t
                 mbar_arrive(smem_u32(acc_empty + b));
             }
         }
+        // inf / NaN anywhere in this row of the tile (an inf or NaN operand, whose low part is NaN, or an overflow):
+        // the split product does not keep IEEE semantics there, the plain kernel recomputes the product
+        bool non_finite = false;
+#pragma unroll
+        for (int i = 0; i < HN; i++)
+            non_finite |= (__float_as_uint(acc[i]) & 0x7F800000u) == 0x7F800000u;
+        if (non_finite)
+            atomicOr(g.status, STATUS_NONFINITE);
         const int64_t row = m0 + q * 32 + lane;
         if (ok && row < g.M) {
             float *out = g.to_part ? g.part + ((int64_t)blockIdx.z * g.M + row) * g.N : g.C + row * g.ldc;
@@ -508,9 +504,9 @@ __global__ void tf32_reduce_kernel(const float *__restrict__ part, float *__rest
     }
 }
 
-// Operands with inf / NaN: the split products cannot keep IEEE semantics (inf * 1 becomes inf * 1 + inf * 0), so the
-// whole product is recomputed with plain f32 FMAs.  Launched after every tensor-core product; returns at once unless
-// the producers raised STATUS_NONFINITE.
+// inf / NaN: the split products cannot keep IEEE semantics (inf * 1 becomes inf * 1 + NaN * 1), so the whole product
+// is recomputed with plain f32 FMAs.  Launched after every tensor-core product; returns at once unless the drain
+// warps saw a non-finite result and raised STATUS_NONFINITE.
 __global__ void __launch_bounds__(256)
     gemm_f32_plain_kernel(const TcArgs g, int ta, int tb) {
     if (!(*g.status & STATUS_NONFINITE))
