@@ -161,8 +161,12 @@ size_t db2k_agg_all_scratch_bytes(int dtype, int op, int64_t rows, int64_t cols)
 int db2k_agg_all(int dtype, int op, const void *arg, int64_t rows, int64_t cols, int64_t ld, void *res,
                  void *scratch, size_t scratch_bytes, void *stream);
 
-/* res (m x n) = op(lhs) op(rhs), op = transpose iff the flag is set; double only.  FP64 tensor-core (DMMA) kernel;
- * contractions over a long row range (t(A) B with tall operands) are split over the grid and reduced in a fixed
+/* res (m x n) = op(lhs) op(rhs), op = transpose iff the flag is set; double or float.  DB2_F64: FP64 tensor-core
+ * (DMMA) kernel.  DB2_F32: tcgen05 kind::tf32 kernel with split operands (three MMAs per product, single-precision
+ * accuracy); `scratch` is then always required, and its first 4 bytes receive a status word when the launch has
+ * finished: bit 0 = a bounded wait inside the kernel expired (the result is not valid), bit 1 = a result was
+ * inf / NaN and the product was recomputed by a plain FMA kernel (not an error).
+ * Contractions over a long row range (t(A) B with tall operands) are split over the grid and reduced in a fixed
  * order through `scratch` (db2k_matmul_scratch_bytes(dtype, m, n, k) bytes, m/n/k = the product's dimensions).
  * Replaces MatMul<Dense,Dense,Dense> (src/runtime/local/kernels/MatMul.cpp:248-290: cblas_ddot / dgemv / dgemm;
  * CUDA twin kernels/CUDA/MatMul.cpp:45-91: cuBLAS gemm). */
@@ -171,8 +175,9 @@ int db2k_matmul(int dtype, const void *lhs, int64_t lhs_rows, int64_t lhs_cols, 
                 int64_t rhs_rows, int64_t rhs_cols, int64_t rhs_ld, int transa, int transb, void *res,
                 int64_t res_ld, void *scratch, size_t scratch_bytes, void *stream);
 
-/* res (n x n, full symmetric) = t(arg) arg if trans_left else arg t(arg).  Only the tiles on and above the diagonal
- * are computed, the rest is mirrored.  Replaces Syrk<Dense,Dense> (src/runtime/local/kernels/Syrk.h:51-71:
+/* res (n x n, full symmetric) = t(arg) arg if trans_left else arg t(arg); double or float (float: the tcgen05
+ * kernel of db2k_matmul on the full square, scratch and status word as there; the lower triangle is the mirror of the
+ * upper one).  For double only the tiles on and above the diagonal are computed, the rest is mirrored.  Replaces Syrk<Dense,Dense> (src/runtime/local/kernels/Syrk.h:51-71:
  * cblas_dsyrk + mirror loop; CUDA twin kernels/CUDA/Syrk.cu:54-87). */
 size_t db2k_syrk_scratch_bytes(int dtype, int64_t rows, int64_t cols, int trans_left);
 int db2k_syrk(int dtype, const void *arg, int64_t rows, int64_t cols, int64_t ld, int trans_left, void *res,
