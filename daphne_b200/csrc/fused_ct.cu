@@ -7,11 +7,14 @@
 // recorded program against the table at the end of this file and falls back to the interpreter otherwise.  Adding a
 // pattern is one table line.
 //
-// Row pass layout: CTA = 128 threads = 128 rows per tile, 32 columns per chunk.  The tile is brought into shared
-// memory with 16-byte cp.async copies (no register staging) into an XOR-swizzled layout -- 16-byte slot p of row r
-// lives at slot p ^ (r & 15) -- so that the cooperative (coalesced) fill and the one-row-per-thread walk are both
-// bank-conflict free without padding.  Every thread then walks its row with 128-bit shared loads, applies the chain
-// and feeds its row trackers; results leave one row per thread (coalesced).  No cross-lane reduction exists.
+// Row pass layout: every warp works on its own: a warp owns tiles of 32 rows and walks them in chunks of 32 columns.
+// A chunk is brought into the warp's shared memory with 16-byte cp.async copies (no register staging) into an
+// XOR-swizzled layout -- 16-byte slot p of row r lives at slot p ^ (r & 15) -- so that the cooperative (coalesced)
+// fill and the one-row-per-lane walk are both bank-conflict free without padding.  Each warp has two chunk buffers:
+// the copies of its next chunk are in flight while it evaluates the current one, so an SM always has 8 KB per warp
+// outstanding and no warp ever waits at a block-wide barrier.  Every lane walks its row with 128-bit shared loads,
+// applies the chain and feeds its row trackers; results leave one row per lane (coalesced).  No cross-lane
+// reduction exists.
 #include "fused.cuh"
 #include "ops.cuh"
 
@@ -20,8 +23,11 @@
 namespace db2 {
 namespace ct {
 
-constexpr int RT = 128;
-constexpr int CK = 32;
+constexpr int RT = 128;        // threads per CTA
+constexpr int WR = 32;         // rows of a warp's tile = lanes
+constexpr int WARPS = RT / 32;
+constexpr int CK = 32;         // columns per chunk
+constexpr int GR = 8;          // elements of a row evaluated together
 constexpr int NO_COL = 0x7fffffff;
 
 template <int OP, int KIND, bool REV = false> struct S {
@@ -51,19 +57,28 @@ __device__ __forceinline__ bool safe_divisor(double d) {
     const bool all_ones = ((hi & 0xfffffu) == 0xfffffu) && (lo == 0xffffffffu);
     return e > 923 && e < 1123 && !all_ones;
 }
-__device__ __forceinline__ double div_helper(double d) { return safe_divisor(d) ? __drcp_rn(d) : 0.0; }
-// a / d from the staged reciprocal y = RN(1/d) (0.0 = not applicable); see fused.cu for the argument
+// RN(1/d) for a divisor fast_div may use, NaN = "take the generic division"
+__device__ __forceinline__ double div_helper(double d) {
+    return safe_divisor(d) ? __drcp_rn(d) : __longlong_as_double(0x7ff8000000000000ll);
+}
+// a / d from the staged helper y.  The three-instruction quotient (see fused.cu for the argument) is computed
+// unconditionally and accepted when its exponent lies in [2^-750, 2^750): with |d| in [2^-99, 2^100) that can only
+// happen for |a| in (2^-850, 2^851), inside the window in which no intermediate over- or underflows; zeros,
+// infinities, NaNs, a NaN helper and everything near the ends of the range fail the one test and are divided
+// generically.  One integer test on the result replaces the tests on both operands.
+constexpr unsigned FAST_DIV_WINDOW = 1500u << 20;
+__device__ __forceinline__ unsigned fast_div_window_pos(double q1) {
+    return ((unsigned)__double2hiint(q1) & 0x7ff00000u) - (273u << 20);
+}
+__device__ __forceinline__ bool in_fast_div_window(double q1) { return fast_div_window_pos(q1) < FAST_DIV_WINDOW; }
 __device__ __forceinline__ double fast_div(double a, double d, double y) {
-    const int ea = (__double2hiint(a) >> 20) & 0x7ff;
-    if (y != 0.0) {
-        if (ea > 123 && ea < 1923) {
-            const double q = __dmul_rn(a, y);
-            const double r = __fma_rn(-q, d, a);
-            return __fma_rn(r, y, q);
-        }
-        if (a == 0.0)
-            return __dmul_rn(a, y);
-    }
+    const double q = __dmul_rn(a, y);
+    const double r = __fma_rn(-q, d, a);
+    const double q1 = __fma_rn(r, y, q);
+    if (in_fast_div_window(q1))
+        return q1;
+    if (a == 0.0 && y == y)
+        return __dmul_rn(a, y); // signed zero
     return __ddiv_rn(a, d);
 }
 
@@ -97,7 +112,8 @@ template <typename TapsT> struct TapState {
     int c[TapsT::n > 0 ? TapsT::n : 1];
 };
 
-template <typename TapsT, int AFTER, int J = 0>
+// C0: the element may be column 0 of its row (only then is the scan's start value recorded)
+template <typename TapsT, int AFTER, bool C0, int J = 0>
 __device__ __forceinline__ void feed(TapState<TapsT> &ts, double v, int c) {
     if constexpr (J < TapsT::n) {
         using Tp = typename At<J, TapsT>::type;
@@ -107,8 +123,9 @@ __device__ __forceinline__ void feed(TapState<TapsT> &ts, double v, int c) {
             else if constexpr (Tp::kind == FT_PROD)
                 ts.v[J] = __dmul_rn(ts.v[J], v);
             else {
-                if (c == 0)
-                    ts.first[J] = v;
+                if constexpr (C0)
+                    if (c == 0)
+                        ts.first[J] = v;
                 const bool better = (Tp::kind == FT_MIN) ? (v < ts.v[J]) : (v > ts.v[J]);
                 if (better) {
                     ts.v[J] = v;
@@ -116,36 +133,90 @@ __device__ __forceinline__ void feed(TapState<TapsT> &ts, double v, int c) {
                 }
             }
         }
-        feed<TapsT, AFTER, J + 1>(ts, v, c);
+        feed<TapsT, AFTER, C0, J + 1>(ts, v, c);
     }
 }
 
-template <typename ChainT, typename TapsT, int I = 0>
-__device__ __forceinline__ double run_chain(double v, const FusedProgram &P, const ChainState<ChainT> &cs,
-                                            TapState<TapsT> &ts, const double *rvs, int64_t row, int64_t c) {
+// The chain on G consecutive elements of one row, step by step: G independent dependency chains for the scheduler to
+// interleave (an element at a time, the latency of the FP64 pipe would be exposed on every step).  The division's
+// range test is folded over the group, so the rare generic division costs one branch per group instead of a branch
+// per element that would fence the chains off from one another.  Taps are fed in element order.
+template <typename TapsT, int AFTER, bool C0, int G>
+__device__ __forceinline__ void feed_group(TapState<TapsT> &ts, const double (&v)[G], int c0) {
+    if constexpr (TapsT::n > 0) {
+        feed<TapsT, AFTER, C0>(ts, v[0], c0);
+#pragma unroll
+        for (int i = 1; i < G; i++)
+            feed<TapsT, AFTER, false>(ts, v[i], c0 + i);
+    }
+}
+template <typename ChainT, typename TapsT, bool C0, int G, int I = 0>
+__device__ __forceinline__ void run_group(double (&v)[G], const FusedProgram &P, const ChainState<ChainT> &cs,
+                                          TapState<TapsT> &ts, const double *rvs, int64_t row, int64_t c) {
     if constexpr (I == 0)
-        feed<TapsT, 0>(ts, v, (int)c);
+        feed_group<TapsT, 0, C0, G>(ts, v, (int)c);
     if constexpr (I < ChainT::n) {
         using St = typename At<I, ChainT>::type;
         const FusedStep &fs = P.steps[I];
-        double o = 0.0, y = 0.0;
+        double o[G], y[G];
         if constexpr (St::kind == FK_ROWVEC) {
-            o = rvs[fs.smem_off + c];
-            if constexpr (St::op == FO_DIV && !St::rev)
-                y = rvs[fs.smem_off + P.cols + c];
-        } else if constexpr (St::kind == FK_SCALAR) {
-            o = fs.imm;
-            y = cs.aux[I];
-        } else if constexpr (St::kind == FK_COLVEC) {
-            o = cs.aux[I];
-        } else if constexpr (St::kind == FK_MATRIX) {
-            o = __ldg(static_cast<const double *>(fs.ptr) + row * fs.ld + c);
+            // staged operands: offsets and c are even (see ct_layout_ok), so pairs are 16-byte aligned
+            const double2 *ov = reinterpret_cast<const double2 *>(rvs + fs.smem_off + c);
+            const double2 *yv = reinterpret_cast<const double2 *>(rvs + fs.smem_off + P.cols + c);
+#pragma unroll
+            for (int i = 0; i < G / 2; i++) {
+                const double2 t = ov[i];
+                o[2 * i] = t.x;
+                o[2 * i + 1] = t.y;
+                y[2 * i] = y[2 * i + 1] = 0.0;
+                if constexpr (St::op == FO_DIV && !St::rev) {
+                    const double2 u = yv[i];
+                    y[2 * i] = u.x;
+                    y[2 * i + 1] = u.y;
+                }
+            }
+        } else {
+#pragma unroll
+            for (int i = 0; i < G; i++) {
+                o[i] = 0.0;
+                y[i] = 0.0;
+                if constexpr (St::kind == FK_SCALAR) {
+                    o[i] = fs.imm;
+                    y[i] = cs.aux[I];
+                } else if constexpr (St::kind == FK_COLVEC) {
+                    o[i] = cs.aux[I];
+                } else if constexpr (St::kind == FK_MATRIX) {
+                    o[i] = __ldg(static_cast<const double *>(fs.ptr) + row * fs.ld + c + i);
+                }
+            }
         }
-        v = apply<St::op, St::rev>(v, o, y);
-        feed<TapsT, I + 1>(ts, v, (int)c);
-        return run_chain<ChainT, TapsT, I + 1>(v, P, cs, ts, rvs, row, c);
-    } else
-        return v;
+        if constexpr (St::op == FO_DIV && !St::rev) {
+            double q1[G];
+            unsigned worst = 0; // the largest distance from the window's lower end, as an unsigned number
+#pragma unroll
+            for (int i = 0; i < G; i++) {
+                const double q = __dmul_rn(v[i], y[i]);
+                const double r = __fma_rn(-q, o[i], v[i]);
+                q1[i] = __fma_rn(r, y[i], q);
+                worst = max(worst, fast_div_window_pos(q1[i]));
+            }
+            if (worst < FAST_DIV_WINDOW) {
+#pragma unroll
+                for (int i = 0; i < G; i++)
+                    v[i] = q1[i];
+            } else {
+#pragma unroll
+                for (int i = 0; i < G; i++)
+                    v[i] = fast_div(v[i], o[i], y[i]);
+            }
+        } else {
+#pragma unroll
+            for (int i = 0; i < G; i++)
+                v[i] = apply<St::op, St::rev>(v[i], o[i], y[i]);
+        }
+        feed_group<TapsT, I + 1, C0, G>(ts, v, (int)c);
+        run_group<ChainT, TapsT, C0, G, I + 1>(v, P, cs, ts, rvs, row, c);
+    }
 }
 
 template <typename ChainT, int I = 0>
@@ -200,20 +271,94 @@ __device__ __forceinline__ void write_taps(const TapState<TapsT> &ts, const Fuse
     }
 }
 
-__device__ __forceinline__ void cp_async16(void *smem_dst, const void *gsrc) {
-    const unsigned s = (unsigned)__cvta_generic_to_shared(smem_dst);
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(s), "l"(gsrc) : "memory");
+__device__ __forceinline__ void cp_async16(unsigned smem_dst, const void *gsrc) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(smem_dst), "l"(gsrc) : "memory");
 }
-__device__ __forceinline__ void cp_async_wait_all() {
-    asm volatile("cp.async.commit_group;\ncp.async.wait_group 0;\n" ::: "memory");
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
+__device__ __forceinline__ void cp_async_wait_but_one() { asm volatile("cp.async.wait_group 1;\n" ::: "memory"); }
+__device__ __forceinline__ double2 lds128(unsigned a) {
+    double2 v;
+    asm volatile("ld.shared.v2.f64 {%0, %1}, [%2];\n" : "=d"(v.x), "=d"(v.y) : "r"(a) : "memory");
+    return v;
+}
+__device__ __forceinline__ void sts128(unsigned a, double x, double y) {
+    asm volatile("st.shared.v2.f64 [%0], {%1, %2};\n" ::"r"(a), "d"(x), "d"(y) : "memory");
+}
+
+// A chunk buffer holds WR rows of 256 bytes and starts on a 256-byte boundary; 16-byte slot p of row r lives at slot
+// p ^ (r & 15).  With the buffer aligned, both address patterns below reduce to one XOR with an immediate:
+//   cooperative (fill, store): lane -> rows r0 + 2 i (r0 = lane / 16), slot p = lane % 16:
+//       address = ((buf + 256 r0 + 16 (p ^ r0)) ^ (16 (2 i % 16))) + 512 i
+//   walk: lane = row, slot p:  address = (buf + 256 lane + 16 (lane % 16)) ^ (16 p)
+__device__ __forceinline__ unsigned coop_addr(unsigned coop0, int i) {
+    return (coop0 ^ (unsigned)(((2 * i) & 15) << 4)) + (unsigned)(512 * i);
+}
+
+// copies of one chunk (rows_here x cw of the WR x CK window at src) by one warp
+template <bool FULL>
+__device__ __forceinline__ void issue_chunk(unsigned coop0, const double *src, int64_t ld, int rows_here, int cw,
+                                            int lane) {
+    const int r0 = lane >> 4, p = lane & 15;
+    const double *s = src + r0 * ld + 2 * p;
+#pragma unroll
+    for (int i = 0; i < CK / 2; i++)
+        if (FULL || (r0 + 2 * i < rows_here && 2 * p < cw))
+            cp_async16(coop_addr(coop0, i), s + (int64_t)(2 * i) * ld);
+}
+
+// one lane walks its row of a chunk (FULL: all CK columns are there)
+template <typename ChainT, typename TapsT, bool EW, bool FULL>
+__device__ __forceinline__ void walk_row(unsigned walk0, const FusedProgram &P, const ChainState<ChainT> &cs,
+                                         TapState<TapsT> &ts, const double *rvs, int64_t row, int64_t cc, int cw) {
+#pragma unroll
+    for (int g = 0; g < CK / GR; g++) {
+        if (FULL || g * GR < cw) { // cw is even; a group that straddles the end loads padding it never uses
+            double v[GR];
+#pragma unroll
+            for (int j = 0; j < GR / 2; j++) {
+                const double2 xy = lds128(walk0 ^ (unsigned)((g * (GR / 2) + j) << 4));
+                v[2 * j] = xy.x;
+                v[2 * j + 1] = xy.y;
+            }
+            if (FULL || g * GR + GR <= cw) {
+                if (g == 0)
+                    run_group<ChainT, TapsT, true, GR>(v, P, cs, ts, rvs, row, cc);
+                else
+                    run_group<ChainT, TapsT, false, GR>(v, P, cs, ts, rvs, row, cc + g * GR);
+            } else { // ragged end of the last chunk: pairs
+#pragma unroll
+                for (int j = 0; j < GR / 2; j++) {
+                    if (g * GR + 2 * j < cw) {
+                        double w[2] = {v[2 * j], v[2 * j + 1]};
+                        if (g == 0 && j == 0)
+                            run_group<ChainT, TapsT, true, 2>(w, P, cs, ts, rvs, row, cc);
+                        else
+                            run_group<ChainT, TapsT, false, 2>(w, P, cs, ts, rvs, row, cc + g * GR + 2 * j);
+                        v[2 * j] = w[0];
+                        v[2 * j + 1] = w[1];
+                    }
+                }
+            }
+            if constexpr (EW) {
+#pragma unroll
+                for (int j = 0; j < GR / 2; j++)
+                    if (FULL || g * GR + 2 * j < cw)
+                        sts128(walk0 ^ (unsigned)((g * (GR / 2) + j) << 4), v[2 * j], v[2 * j + 1]);
+            }
+        }
+    }
 }
 
 template <typename ChainT, typename TapsT, bool EW>
-__global__ void __launch_bounds__(RT, 5) fused_row_ct_kernel(const __grid_constant__ FusedProgram P) {
-    extern __shared__ __align__(16) double smem[];
-    double *tile = smem;           // [RT][CK], 16-byte slots swizzled by row
-    double *rvs = smem + RT * CK;  // staged row-vector operands (+ reciprocal helpers)
-    const int tid = threadIdx.x;
+__global__ void __launch_bounds__(RT, 3) fused_row_ct_kernel(const __grid_constant__ FusedProgram P) {
+    extern __shared__ __align__(16) double smem_raw[];
+    // the chunk buffers start on a 256-byte boundary (the launch reserves the slack)
+    const unsigned raw_s = (unsigned)__cvta_generic_to_shared(smem_raw);
+    const unsigned pad = ((raw_s + 255u) & ~255u) - raw_s;
+    double *smem = smem_raw + pad / 8;
+    double *rvs = smem + WARPS * 2 * WR * CK; // staged row-vector operands (+ reciprocal helpers)
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const unsigned bufs_s = raw_s + pad + (unsigned)(warp * 2 * WR * CK * 8); // this warp's two chunk buffers
     const int64_t rows = P.rows, cols = P.cols;
     for (int s = 0; s < P.nsteps; s++) {
         const FusedStep &st = P.steps[s];
@@ -230,73 +375,94 @@ __global__ void __launch_bounds__(RT, 5) fused_row_ct_kernel(const __grid_consta
     }
     ChainState<ChainT> cs;
     init_scalar_aux<ChainT>(cs, P);
-    __syncthreads();
+    __syncthreads(); // the only block-wide barrier: from here on every warp runs on its own
 
     const double *base = static_cast<const double *>(P.base);
-    const int64_t ntiles = (rows + RT - 1) / RT;
-    const int swz = tid & 15;
-    for (int64_t tile_i = blockIdx.x; tile_i < ntiles; tile_i += gridDim.x) {
-        const int64_t row0 = tile_i * RT;
-        const int64_t row = row0 + tid;
-        const bool live = row < rows;
-        const int rows_here = (rows - row0 < RT) ? (int)(rows - row0) : RT;
-        TapState<TapsT> ts;
-        init_taps<TapsT>(ts);
-        if (live)
-            load_colvec_aux<ChainT>(cs, P, row);
-        for (int64_t cc = 0; cc < cols; cc += CK) {
-            const int cw = (cols - cc < CK) ? (int)(cols - cc) : CK;
-            __syncthreads(); // every reader of the previous chunk is done
+    const int64_t ntiles = (rows + WR - 1) / WR;
+    const int nchunks = (int)((cols + CK - 1) / CK);
+    const int64_t wstride = (int64_t)gridDim.x * WARPS;
+    constexpr unsigned BUF_BYTES = WR * CK * 8;
+    const unsigned coop_off = (unsigned)((lane >> 4) * 256 + (((lane & 15) ^ (lane >> 4)) << 4));
+    const unsigned walk_off = (unsigned)(lane * 256 + ((lane & 15) << 4));
+    int64_t t = (int64_t)blockIdx.x * WARPS + warp;
+    int ch = 0;
+    unsigned b = 0;
+    if (t < ntiles) {
+        const int64_t row0 = t * WR;
+        const int rh = (rows - row0 < WR) ? (int)(rows - row0) : WR, cw = (cols < CK) ? (int)cols : CK;
+        if (rh == WR && cw == CK)
+            issue_chunk<true>(bufs_s + coop_off, base + row0 * P.base_ld, P.base_ld, rh, cw, lane);
+        else
+            issue_chunk<false>(bufs_s + coop_off, base + row0 * P.base_ld, P.base_ld, rh, cw, lane);
+    }
+    cp_async_commit();
+    TapState<TapsT> ts;
+    while (t < ntiles) {
+        // the next chunk of this warp is on its way while this one is evaluated
+        int64_t tn = t;
+        int chn = ch + 1;
+        if (chn == nchunks) {
+            chn = 0;
+            tn = t + wstride;
+        }
+        if (tn < ntiles) {
+            const int64_t row0n = tn * WR, ccn = (int64_t)chn * CK;
+            const int rh = (rows - row0n < WR) ? (int)(rows - row0n) : WR, cw = (cols - ccn < CK) ? (int)(cols - ccn) : CK;
+            const double *src = base + row0n * P.base_ld + ccn;
+            if (rh == WR && cw == CK)
+                issue_chunk<true>(bufs_s + (b ^ BUF_BYTES) + coop_off, src, P.base_ld, rh, cw, lane);
+            else
+                issue_chunk<false>(bufs_s + (b ^ BUF_BYTES) + coop_off, src, P.base_ld, rh, cw, lane);
+        }
+        cp_async_commit();
+        cp_async_wait_but_one();
+        __syncwarp();
+
+        const unsigned tile_s = bufs_s + b;
+        const int64_t row0 = t * WR, row = row0 + lane, cc = (int64_t)ch * CK;
+        const int rows_here = (rows - row0 < WR) ? (int)(rows - row0) : WR;
+        const int cw = (cols - cc < CK) ? (int)(cols - cc) : CK;
+        const bool live = lane < rows_here;
+        if (ch == 0) {
+            init_taps<TapsT>(ts);
+            if (live)
+                load_colvec_aux<ChainT>(cs, P, row);
+        }
+        if (rows_here == WR && cw == CK)
+            walk_row<ChainT, TapsT, EW, true>(tile_s + walk_off, P, cs, ts, rvs, row, cc, cw);
+        else if (live)
+            walk_row<ChainT, TapsT, EW, false>(tile_s + walk_off, P, cs, ts, rvs, row, cc, cw);
+        if constexpr (EW) {
+            __syncwarp();
+            const int r0 = lane >> 4, p = lane & 15;
+            double *out = static_cast<double *>(P.ew_out) + (row0 + r0) * P.ew_out_ld + cc + 2 * p;
+            const bool full = rows_here == WR && cw == CK;
 #pragma unroll
             for (int i = 0; i < CK / 2; i++) {
-                const int idx = tid + i * RT;
-                const int r = idx >> 4, p = idx & 15;
-                if (r < rows_here && 2 * p < cw)
-                    cp_async16(tile + (r * 16 + (p ^ (r & 15))) * 2, base + (row0 + r) * P.base_ld + cc + 2 * p);
-            }
-            cp_async_wait_all();
-            __syncthreads();
-            if (live) {
-#pragma unroll
-                for (int p = 0; p < CK / 2; p++) {
-                    if (2 * p < cw) {
-                        double2 *slot = reinterpret_cast<double2 *>(tile + (tid * 16 + (p ^ swz)) * 2);
-                        double2 xy = *slot;
-                        xy.x = run_chain<ChainT, TapsT>(xy.x, P, cs, ts, rvs, row, cc + 2 * p);
-                        xy.y = run_chain<ChainT, TapsT>(xy.y, P, cs, ts, rvs, row, cc + 2 * p + 1);
-                        if constexpr (EW)
-                            *slot = xy;
-                    }
-                }
-            }
-            if constexpr (EW) {
-                __syncthreads();
-                double *out = static_cast<double *>(P.ew_out);
-#pragma unroll
-                for (int i = 0; i < CK / 2; i++) {
-                    const int idx = tid + i * RT;
-                    const int r = idx >> 4, p = idx & 15;
-                    if (r < rows_here && 2 * p < cw) {
-                        const double2 q = *reinterpret_cast<const double2 *>(tile + (r * 16 + (p ^ (r & 15))) * 2);
-                        __stcs(reinterpret_cast<double2 *>(out + (row0 + r) * P.ew_out_ld + cc + 2 * p), q);
-                    }
+                if (full || (r0 + 2 * i < rows_here && 2 * p < cw)) {
+                    const double2 q = lds128(coop_addr(tile_s + coop_off, i));
+                    __stcs(reinterpret_cast<double2 *>(out + (int64_t)(2 * i) * P.ew_out_ld), q);
                 }
             }
         }
-        if (live)
+        if (ch == nchunks - 1 && live)
             write_taps<TapsT>(ts, P, row);
+        __syncwarp(); // every lane is done with this buffer before the next iteration refills it
+        t = tn;
+        ch = chn;
+        b ^= BUF_BYTES;
     }
 }
 
 template <typename ChainT, typename TapsT, bool EW> static int launch_row(const FusedProgram &prog, cudaStream_t st) {
-    const size_t smem = (size_t)(RT * CK + prog.smem_elems) * sizeof(double);
-    const int64_t ntiles = (prog.rows + RT - 1) / RT;
-    const int64_t cap = (int64_t)sm_count() * 5;
-    const int grid = (int)(ntiles < cap ? ntiles : cap);
+    const size_t smem = (size_t)(WARPS * 2 * WR * CK + prog.smem_elems) * sizeof(double) + 256; // + alignment slack
+    const int64_t nblocks = ((prog.rows + WR - 1) / WR + WARPS - 1) / WARPS;
+    const int64_t cap = (int64_t)sm_count() * 3;
+    const int grid = (int)(nblocks < cap ? nblocks : cap);
     static bool attr = false;
     if (!attr) {
         DB2_CUDA(cudaFuncSetAttribute(fused_row_ct_kernel<ChainT, TapsT, EW>,
-                                      cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024));
+                                      cudaFuncAttributeMaxDynamicSharedMemorySize, 128 * 1024));
         attr = true;
     }
     fused_row_ct_kernel<ChainT, TapsT, EW><<<grid, RT, smem, st>>>(prog);
