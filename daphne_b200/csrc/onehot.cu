@@ -14,7 +14,7 @@
 namespace db2 {
 
 constexpr int SEG_MAX_WARPS = 8;
-constexpr size_t SEG_SMEM_LIMIT = 200 * 1024;
+constexpr size_t SEG_SMEM_LIMIT = 216 * 1024;
 
 // accumulators acc[warp][cluster][column]
 __global__ void __launch_bounds__(SEG_MAX_WARPS * 32)
@@ -77,6 +77,90 @@ __global__ void __launch_bounds__(SEG_MAX_WARPS * 32)
         double t = acc[e];
         for (int w = 1; w < warps; w++)
             t = __dadd_rn(t, acc[w * kd + e]);
+        partials[(int64_t)blockIdx.x * kd + e] = t;
+    }
+}
+
+// The same sums for d = 64 columns of 16-byte aligned rows (one row = 32 lanes x 16 bytes), written for latency:
+//  * eight rows of X per warp are always on their way while the previous eight are added (two register sets);
+//  * two rows are added at a time: when their clusters differ the two read-modify-write chains on shared memory are
+//    independent and overlap, when they agree the accumulator is read and written once for both.  The order of the
+//    additions into any accumulator is the row order, as in the general kernel;
+//  * rows without a valid cluster number (and the rows past the end of a warp's range) are added to a spare
+//    accumulator row, so nothing in the loop is conditional.
+__global__ void __launch_bounds__(SEG_MAX_WARPS * 32)
+    onehot_segsum64_kernel(const int64_t *__restrict__ idx, int64_t idx_ld, const double *__restrict__ X, int64_t ldx,
+                           int64_t n, int k, double *__restrict__ partials) {
+    extern __shared__ __align__(16) double acc[];
+    constexpr int D = 64, U = 8;
+    const int warps = blockDim.x / 32, warp = threadIdx.x / 32, lane = threadIdx.x % 32;
+    const int slots = (k + 1) * D; // per warp; row k is the spare one
+    for (int e = threadIdx.x; e < warps * slots; e += blockDim.x)
+        acc[e] = 0.0;
+    __syncthreads();
+    const unsigned mine_s = (unsigned)__cvta_generic_to_shared(acc + warp * slots) + (unsigned)(lane * 16);
+    const int64_t total_warps = (int64_t)gridDim.x * warps, gw = (int64_t)blockIdx.x * warps + warp;
+    const int64_t per = ((n + total_warps - 1) / total_warps + 31) / 32 * 32;
+    const int64_t lo = gw * per, hi = lo + per < n ? lo + per : n;
+    if (lo < hi) {
+        const double2 *xl = reinterpret_cast<const double2 *>(X) + lane;
+        const int64_t ld2 = ldx / 2;
+        double2 xa[U], xb[U];
+        auto load = [&](double2(&x)[U], int64_t r0) {
+#pragma unroll
+            for (int u = 0; u < U; u++)
+                x[u] = (r0 + u < hi) ? __ldcs(xl + (r0 + u) * ld2) : make_double2(0.0, 0.0);
+        };
+        auto lds = [](unsigned a) {
+            double2 v;
+            asm volatile("ld.shared.v2.f64 {%0, %1}, [%2];\n" : "=d"(v.x), "=d"(v.y) : "r"(a) : "memory");
+            return v;
+        };
+        auto sts = [](unsigned a, double2 v) {
+            asm volatile("st.shared.v2.f64 [%0], {%1, %2};\n" ::"r"(a), "d"(v.x), "d"(v.y) : "memory");
+        };
+        auto add = [&](const double2(&x)[U], int ci, int h) {
+#pragma unroll
+            for (int u = 0; u < U; u += 2) {
+                const int c0 = __shfl_sync(0xffffffffu, ci, h + u), c1 = __shfl_sync(0xffffffffu, ci, h + u + 1);
+                const unsigned a0 = mine_s + (unsigned)(c0 * D * 8), a1 = mine_s + (unsigned)(c1 * D * 8);
+                if (c0 != c1) {
+                    double2 t0 = lds(a0), t1 = lds(a1);
+                    t0.x = __dadd_rn(t0.x, x[u].x);
+                    t0.y = __dadd_rn(t0.y, x[u].y);
+                    t1.x = __dadd_rn(t1.x, x[u + 1].x);
+                    t1.y = __dadd_rn(t1.y, x[u + 1].y);
+                    sts(a0, t0);
+                    sts(a1, t1);
+                } else {
+                    double2 t0 = lds(a0);
+                    t0.x = __dadd_rn(__dadd_rn(t0.x, x[u].x), x[u + 1].x);
+                    t0.y = __dadd_rn(__dadd_rn(t0.y, x[u].y), x[u + 1].y);
+                    sts(a0, t0);
+                }
+            }
+        };
+        load(xa, lo);
+        int64_t c_next = (lo + lane < hi) ? idx[(lo + lane) * idx_ld] : -1;
+        for (int64_t b0 = lo; b0 < hi; b0 += 32) {
+            const int ci = (c_next >= 0 && c_next < k) ? (int)c_next : k;
+            c_next = (b0 + 32 + lane < hi) ? idx[(b0 + 32 + lane) * idx_ld] : -1;
+            load(xb, b0 + 8);
+            add(xa, ci, 0);
+            load(xa, b0 + 16);
+            add(xb, ci, 8);
+            load(xb, b0 + 24);
+            add(xa, ci, 16);
+            load(xa, b0 + 32);
+            add(xb, ci, 24);
+        }
+    }
+    __syncthreads();
+    const int kd = k * D;
+    for (int e = threadIdx.x; e < kd; e += blockDim.x) {
+        double t = acc[e];
+        for (int w = 1; w < warps; w++)
+            t = __dadd_rn(t, acc[w * slots + e]);
         partials[(int64_t)blockIdx.x * kd + e] = t;
     }
 }
@@ -153,28 +237,37 @@ int onehot_try_matmul(db2_context *ctx, db2_matrix **res, db2_matrix *lhs, db2_m
     const int64_t n = lhs->rows, k = lhs->cols, d = rhs->cols;
     if (rhs->rows != n || k < 1 || d < 1 || (size_t)k * d * 8 > SEG_SMEM_LIMIT || n < 1)
         return DB2_OK;
-    int warps = SEG_MAX_WARPS;
-    while ((size_t)warps * k * d * 8 > SEG_SMEM_LIMIT)
-        warps /= 2;
     const uint64_t before = g_launches.load();
     DB2_TRY(ensure_device(rhs));
+    const double *X = static_cast<const double *>(rhs->dev_ptr());
+    const int vec = aligned16(X) && rhs->dev_ld % 2 == 0;
+    const bool k64 = vec && d == 64 && (size_t)(k + 1) * d * 8 <= SEG_SMEM_LIMIT; // the latency-tuned kernel
+    const int64_t acc_rows = k64 ? k + 1 : k;
+    int warps = SEG_MAX_WARPS;
+    while ((size_t)warps * acc_rows * d * 8 > SEG_SMEM_LIMIT)
+        warps /= 2;
     DB2_TRY(prepare_result(ctx, res, DB2_F64, k, d));
     const int grid = sm_count();
     void *scratch = nullptr;
     DB2_TRY(ctx_scratch(ctx, (size_t)grid * k * d * 8, &scratch));
-    const size_t smem = (size_t)warps * k * d * 8;
+    const size_t smem = (size_t)warps * acc_rows * d * 8;
     static bool attr = false;
     if (!attr) {
         DB2_CUDA(cudaFuncSetAttribute(onehot_segsum_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                       (int)SEG_SMEM_LIMIT));
+        DB2_CUDA(cudaFuncSetAttribute(onehot_segsum64_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      (int)SEG_SMEM_LIMIT));
         attr = true;
     }
     std::shared_ptr<const OneHot> oh = lhs->onehot;
-    const double *X = static_cast<const double *>(rhs->dev_ptr());
-    const int vec = aligned16(X) && rhs->dev_ld % 2 == 0;
-    onehot_segsum_kernel<<<grid, warps * 32, smem, ctx->stream>>>(static_cast<const int64_t *>(oh->idx.ptr(8)),
-                                                                  oh->idx.ld, X, rhs->dev_ld, n, (int)d, (int)k, vec,
-                                                                  static_cast<double *>(scratch));
+    if (k64)
+        onehot_segsum64_kernel<<<grid, warps * 32, smem, ctx->stream>>>(static_cast<const int64_t *>(oh->idx.ptr(8)),
+                                                                        oh->idx.ld, X, rhs->dev_ld, n, (int)k,
+                                                                        static_cast<double *>(scratch));
+    else
+        onehot_segsum_kernel<<<grid, warps * 32, smem, ctx->stream>>>(static_cast<const int64_t *>(oh->idx.ptr(8)),
+                                                                      oh->idx.ld, X, rhs->dev_ld, n, (int)d, (int)k, vec,
+                                                                      static_cast<double *>(scratch));
     DB2_TRY(after_launch("onehot_segsum_kernel"));
     const int kd = (int)(k * d);
     onehot_segsum_final_kernel<<<(kd + 31) / 32, 256, 0, ctx->stream>>>(

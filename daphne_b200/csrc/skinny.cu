@@ -4,7 +4,7 @@
 //
 // One persistent CTA of 16 warps per SM keeps op(B) in shared memory for the whole launch.  Every WARP owns a private
 // 16-row tile buffer and walks its own sequence of tiles -- copy (16-byte cp.async, zero fill), DMMAs
-// (mma.sync m16n8k16 f64), epilogue -- without block-wide barriers, so the warps of an SM drift apart and the FP64 pipe
+// (mma.sync m8n8k4 f64), epilogue -- without block-wide barriers, so the warps of an SM drift apart and the FP64 pipe
 // (which the DMMAs and the epilogue's scalar FP64 arithmetic share) always finds a warp with DMMAs to issue.  A warp's
 // 16 rows x all N columns sit in its accumulators with a row's values in the four lanes of a quad: the recorded
 // elementwise chain (scalar, column-vector and row-vector operands) is applied in registers, the row minimum / maximum
@@ -17,12 +17,16 @@ namespace db2 {
 constexpr int SK_WARPS = 16, SK_WROWS = 16, SK_THREADS = SK_WARPS * 32, SK_MAXN = 64, SK_MAXK = 128;
 constexpr int SK_VEC_SLOTS = 4; // row-vector and column-vector operands of a fused chain (each kind)
 
-__device__ __forceinline__ void sk_dmma(double (&c)[4], const double (&a)[8], const double (&b)[4]) {
-    asm volatile("mma.sync.aligned.m16n8k16.row.col.f64.f64.f64.f64 {%0,%1,%2,%3}, {%4,%5,%6,%7,%8,%9,%10,%11}, "
-                 "{%12,%13,%14,%15}, {%0,%1,%2,%3};\n"
-                 : "+d"(c[0]), "+d"(c[1]), "+d"(c[2]), "+d"(c[3])
-                 : "d"(a[0]), "d"(a[1]), "d"(a[2]), "d"(a[3]), "d"(a[4]), "d"(a[5]), "d"(a[6]), "d"(a[7]), "d"(b[0]),
-                   "d"(b[1]), "d"(b[2]), "d"(b[3]));
+// one hardware DMMA: an 8 x 8 tile of C += A (8 x 4) * B (4 x 8); lane (g, t) holds A[g][t], B[t][g], C[g][2t..2t+1]
+__device__ __forceinline__ void sk_dmma(double &c0, double &c1, double a, double b) {
+    asm volatile("mma.sync.aligned.m8n8k4.row.col.f64.f64.f64.f64 {%0,%1}, {%2}, {%3}, {%0,%1};\n"
+                 : "+d"(c0), "+d"(c1)
+                 : "d"(a), "d"(b));
+}
+__device__ __forceinline__ double2 sk_lds128(unsigned a) {
+    double2 v;
+    asm volatile("ld.shared.v2.f64 {%0, %1}, [%2];\n" : "=d"(v.x), "=d"(v.y) : "r"(a) : "memory");
+    return v;
 }
 
 // value (op) operand on NV values with the exactly rounded semantics of the elementwise kernels; the opcode is
@@ -55,32 +59,44 @@ bool skinny_op_supported(int op) {
            op == FO_MAX || op == FO_NEG || op == FO_ABS;
 }
 
-// KPT: the contraction length rounded up to 16 as a compile-time constant (0: taken from the arguments).  With it every
-// fragment address is one base register plus an immediate; the general form spends most of its instructions on
-// address arithmetic.
-template <int NT, bool TB, int KPT>
+// KPT: the contraction length rounded up to 16 as a compile-time constant (0: taken from the arguments).
+// CH:  the fused chain as a compile-time constant: 1 = (* scalar, + column vector, + row vector), 2 = (* scalar, + row
+//      vector) -- the distance step of k-means with and without the rowSums(X^2) term; 0 = interpreted.
+//
+// The FP64 pipe issues one DMMA per 16 cycles and scheduler, and every other instruction of the four warps that share
+// a scheduler costs an issue slot in between, so the kernel is written to keep everything that is not a DMMA short:
+//  * within each block of 16 k the four lanes of a quad take k = 4 t + j (j = 0..3) instead of t + 4 j -- A and B
+//    agree, so the product is the same sum in a different (fixed) order -- which makes a lane's four k values
+//    contiguous: two 128-bit shared loads per fragment instead of four 64-bit ones.  Row pitch = 2 mod 4 doubles: the
+//    eight lanes of a load phase then hit eight different 16-byte columns.
+//  * the tile copy has a fast path for full tiles (no bounds tests, one pointer increment per copy);
+//  * the k-means chains are compiled in; the extremum tournament carries slot numbers (immediates), tests validity
+//    only where padding columns can be, and looks for NaNs once per row instead of once per value.
+template <int NT, int KPT, int CH>
 __global__ void __launch_bounds__(SK_THREADS, 1) skinny_gemm_kernel(const __grid_constant__ SkinnyArgs s) {
     extern __shared__ __align__(16) double sm[];
-    const int KP = KPT ? KPT : (s.K + 15) / 16 * 16, PA = KP + 4; // pitch = 4 mod 16 doubles: conflict-free fragments
-    const int PB = TB ? KP + 4 : NT * 8 + 4;
+    const int KP = KPT ? KPT : (s.K + 15) / 16 * 16, PA = KP + 2, PB = KP + 2;
     const int tid = threadIdx.x, warp = tid / 32, lane = tid % 32, g = lane / 4, t = lane % 4;
-    double *Bs = sm;                                 // TB: [NT*8][PB] (k contiguous);  else [KP][PB]
-    double *rv = Bs + (TB ? NT * 8 * PB : KP * PB);   // row-vector operands: [slot][64]
+    double *Bs = sm;                          // [NT*8][PB]: op(B) transposed, k contiguous
+    double *rv = Bs + NT * 8 * PB;            // row-vector operands: [slot][64]
     double *At = rv + SK_VEC_SLOTS * SK_MAXN + (size_t)warp * (SK_WROWS * PA + SK_VEC_SLOTS * SK_WROWS);
-    double *cv = At + SK_WROWS * PA;                  // this warp's column-vector operands: [slot][16]
+    double *cv = At + SK_WROWS * PA;          // this warp's column-vector operands: [slot][16]
     const FusedProgram &P = s.prog;
 
-    // op(B), zero padded to NT*8 columns and KP rows of k
-    if (TB) {
-        for (int e = tid; e < NT * 8 * KP; e += SK_THREADS) {
-            const int n = e / KP, k = e % KP;
-            Bs[n * PB + k] = (n < s.N && k < s.K) ? s.B[(int64_t)n * s.ldb + k] : 0.0;
+    // op(B) transposed, zero padded to NT*8 columns and KP values of k
+    for (int e = tid; e < NT * 8 * KP; e += SK_THREADS) {
+        int n, k;
+        if (s.tb) {
+            n = e / KP;
+            k = e % KP;
+        } else {
+            k = e / (NT * 8);
+            n = e % (NT * 8);
         }
-    } else {
-        for (int e = tid; e < KP * NT * 8; e += SK_THREADS) {
-            const int k = e / (NT * 8), n = e % (NT * 8);
-            Bs[k * PB + n] = (n < s.N && k < s.K) ? s.B[(int64_t)k * s.ldb + n] : 0.0;
-        }
+        double b = 0.0;
+        if (n < s.N && k < s.K)
+            b = s.tb ? s.B[(int64_t)n * s.ldb + k] : s.B[(int64_t)k * s.ldb + n];
+        Bs[n * PB + k] = b;
     }
     for (int st = 0; st < P.nsteps; st++)
         if (P.steps[st].kind == FK_ROWVEC)
@@ -92,10 +108,29 @@ __global__ void __launch_bounds__(SK_THREADS, 1) skinny_gemm_kernel(const __grid
     // drift apart, so while one waits for its copy or works through its epilogue the others keep the FP64 pipe busy.
     const int64_t ntiles = (s.n + SK_WROWS - 1) / SK_WROWS;
     const int packets = KP / 2; // 16-byte packets per row
-    const int dr = 32 / packets, dp = 32 % packets;
+    bool scale_pow2 = false;    // the compiled chains' scalar factor is +-2^e (normal): multiplying by it is exact
+    if constexpr (CH != 0) {
+        const unsigned hi = (unsigned)__double2hiint(P.steps[0].imm), ex = (hi >> 20) & 0x7ffu;
+        scale_pow2 = __double2loint(P.steps[0].imm) == 0 && (hi & 0xfffffu) == 0 && ex != 0 && ex != 0x7ffu;
+    }
+    const unsigned At_s = (unsigned)__cvta_generic_to_shared(At);
+    const unsigned afrag_s = At_s + (unsigned)((g * PA + 4 * t) * 8);
+    const unsigned bfrag_s = (unsigned)__cvta_generic_to_shared(Bs) + (unsigned)((g * PB + 4 * t) * 8);
     for (int64_t tile = (int64_t)blockIdx.x * SK_WARPS + warp; tile < ntiles; tile += (int64_t)gridDim.x * SK_WARPS) {
         const int64_t r0 = tile * SK_WROWS;
-        {
+        if (KPT != 0 && s.K == KPT && r0 + SK_WROWS <= s.n) {
+            // full tile: lane -> packet p of rows r, r + 32 / packets, ...
+            constexpr int PK = KPT ? KPT / 2 : 1, RSTEP = 32 / PK, NCP = SK_WROWS * PK / 32;
+            const int r = lane / PK, p = lane % PK;
+            const double *src = s.A + (r0 + r) * s.lda + 2 * p;
+            const unsigned d = At_s + (unsigned)((r * PA + 2 * p) * 8);
+#pragma unroll
+            for (int i = 0; i < NCP; i++)
+                asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(d + (unsigned)(i * RSTEP * PA * 8)),
+                             "l"(src + (int64_t)(i * RSTEP) * s.lda)
+                             : "memory");
+        } else {
+            const int dr = 32 / packets, dp = 32 % packets;
             int r = lane / packets, p = lane % packets;
             for (int e = lane; e < SK_WROWS * packets; e += 32) {
                 const int64_t row = r0 + r;
@@ -103,7 +138,7 @@ __global__ void __launch_bounds__(SK_THREADS, 1) skinny_gemm_kernel(const __grid
                 int bytes = 0;
                 if (row < s.n && k < s.K)
                     bytes = (s.K - k >= 2) ? 16 : 8;
-                const unsigned d = (unsigned)__cvta_generic_to_shared(At + r * PA + k);
+                const unsigned d = At_s + (unsigned)((r * PA + k) * 8);
                 const double *src = bytes ? s.A + row * s.lda + k : s.A;
                 asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(d), "l"(src), "r"(bytes) : "memory");
                 r += dr;
@@ -113,19 +148,19 @@ __global__ void __launch_bounds__(SK_THREADS, 1) skinny_gemm_kernel(const __grid
                     r++;
                 }
             }
-            if (lane < SK_WROWS)
-                for (int st = 0; st < P.nsteps; st++)
-                    if (P.steps[st].kind == FK_COLVEC) {
-                        const int64_t row = r0 + lane;
-                        const double *base = static_cast<const double *>(P.steps[st].ptr);
-                        const unsigned d = (unsigned)__cvta_generic_to_shared(cv + P.steps[st].smem_off * SK_WROWS + lane);
-                        const int bytes = row < s.n ? 8 : 0;
-                        const double *src = bytes ? base + row * P.steps[st].ld : base;
-                        asm volatile("cp.async.ca.shared.global [%0], [%1], 8, %2;\n" ::"r"(d), "l"(src), "r"(bytes) : "memory");
-                    }
-            asm volatile("cp.async.commit_group;\ncp.async.wait_group 0;\n" ::: "memory");
-            __syncwarp();
         }
+        if (lane < SK_WROWS)
+            for (int st = 0; st < P.nsteps; st++)
+                if (P.steps[st].kind == FK_COLVEC) {
+                    const int64_t row = r0 + lane;
+                    const double *base = static_cast<const double *>(P.steps[st].ptr);
+                    const unsigned d = (unsigned)__cvta_generic_to_shared(cv + P.steps[st].smem_off * SK_WROWS + lane);
+                    const int bytes = row < s.n ? 8 : 0;
+                    const double *src = bytes ? base + row * P.steps[st].ld : base;
+                    asm volatile("cp.async.ca.shared.global [%0], [%1], 8, %2;\n" ::"r"(d), "l"(src), "r"(bytes) : "memory");
+                }
+        asm volatile("cp.async.commit_group;\ncp.async.wait_group 0;\n" ::: "memory");
+        __syncwarp();
 
         double acc[NT][4];
 #pragma unroll
@@ -133,19 +168,32 @@ __global__ void __launch_bounds__(SK_THREADS, 1) skinny_gemm_kernel(const __grid
 #pragma unroll
             for (int e = 0; e < 4; e++)
                 acc[nt][e] = 0.0;
-        for (int ks = 0; ks < KP; ks += 16) {
-            double af[8];
-#pragma unroll
-            for (int i = 0; i < 8; i++)
-                af[i] = At[(g + 8 * (i & 1)) * PA + ks + t + 4 * (i >> 1)];
+        auto kblock = [&](int ks) { // 16 values of k: 8 DMMAs per 8-column block
+            const unsigned ka = (unsigned)(ks * 8);
+            const double2 a0l = sk_lds128(afrag_s + ka), a0h = sk_lds128(afrag_s + ka + 16);
+            const double2 a1l = sk_lds128(afrag_s + ka + (unsigned)(8 * PA * 8));
+            const double2 a1h = sk_lds128(afrag_s + ka + (unsigned)(8 * PA * 8) + 16);
 #pragma unroll
             for (int nt = 0; nt < NT; nt++) {
-                double bf[4];
-#pragma unroll
-                for (int i = 0; i < 4; i++)
-                    bf[i] = TB ? Bs[(nt * 8 + g) * PB + ks + t + 4 * i] : Bs[(ks + t + 4 * i) * PB + nt * 8 + g];
-                sk_dmma(acc[nt], af, bf);
+                const double2 bl = sk_lds128(bfrag_s + ka + (unsigned)(nt * 8 * PB * 8));
+                const double2 bh = sk_lds128(bfrag_s + ka + (unsigned)(nt * 8 * PB * 8) + 16);
+                sk_dmma(acc[nt][0], acc[nt][1], a0l.x, bl.x);
+                sk_dmma(acc[nt][2], acc[nt][3], a1l.x, bl.x);
+                sk_dmma(acc[nt][0], acc[nt][1], a0l.y, bl.y);
+                sk_dmma(acc[nt][2], acc[nt][3], a1l.y, bl.y);
+                sk_dmma(acc[nt][0], acc[nt][1], a0h.x, bh.x);
+                sk_dmma(acc[nt][2], acc[nt][3], a1h.x, bh.x);
+                sk_dmma(acc[nt][0], acc[nt][1], a0h.y, bh.y);
+                sk_dmma(acc[nt][2], acc[nt][3], a1h.y, bh.y);
             }
+        };
+        if constexpr (KPT != 0) {
+#pragma unroll
+            for (int ks = 0; ks < KPT; ks += 16)
+                kblock(ks);
+        } else {
+            for (int ks = 0; ks < KP; ks += 16)
+                kblock(ks);
         }
 
         // ---- epilogue: chain, outputs, row extremum, for the thread's two rows g and g + 8 ----
@@ -159,24 +207,59 @@ __global__ void __launch_bounds__(SK_THREADS, 1) skinny_gemm_kernel(const __grid
                 v[2 * nt] = acc[nt][2 * h];
                 v[2 * nt + 1] = acc[nt][2 * h + 1];
             }
-#pragma unroll 1
-            for (int st = 0; st < P.nsteps; st++) {
-                const FusedStep &fs = P.steps[st];
-                double o[NV];
-                if (fs.kind == FK_ROWVEC) {
+            if constexpr (CH != 0) {
+                double rvv[NV]; // the row-vector operand, as this lane's columns
+                const double *src = rv + P.steps[CH == 1 ? 2 : 1].smem_off * SK_MAXN + 2 * t;
 #pragma unroll
-                    for (int nt = 0; nt < NT; nt++) {
-                        const double2 two = *reinterpret_cast<const double2 *>(rv + fs.smem_off * SK_MAXN + nt * 8 + 2 * t);
-                        o[2 * nt] = two.x;
-                        o[2 * nt + 1] = two.y;
+                for (int nt = 0; nt < NT; nt++) {
+                    const double2 two = *reinterpret_cast<const double2 *>(src + nt * 8);
+                    rvv[2 * nt] = two.x;
+                    rvv[2 * nt + 1] = two.y;
+                }
+                const double m = P.steps[0].imm;
+                double colv = 0.0;
+                if constexpr (CH == 1)
+                    colv = cv[P.steps[1].smem_off * SK_WROWS + g + 8 * h];
+                if (scale_pow2) {
+                    // v * m is exact, so the multiplication and the first addition are one FMA with the same bits
+                    // (scalar FP64 instructions take the pipe the DMMAs of the other warps are waiting for)
+#pragma unroll
+                    for (int i = 0; i < NV; i++) {
+                        if constexpr (CH == 1)
+                            v[i] = __dadd_rn(__fma_rn(v[i], m, colv), rvv[i]);
+                        else
+                            v[i] = __fma_rn(v[i], m, rvv[i]);
                     }
                 } else {
-                    const double colv = fs.kind == FK_COLVEC ? cv[fs.smem_off * SK_WROWS + g + 8 * h] : fs.imm;
 #pragma unroll
-                    for (int i = 0; i < NV; i++)
-                        o[i] = colv;
+                    for (int i = 0; i < NV; i++) {
+                        v[i] = __dmul_rn(v[i], m);
+                        if constexpr (CH == 1)
+                            v[i] = __dadd_rn(v[i], colv);
+                        v[i] = __dadd_rn(v[i], rvv[i]);
+                    }
                 }
-                sk_apply<NV>(fs.op, fs.reversed != 0, v, o);
+            } else {
+#pragma unroll 1
+                for (int st = 0; st < P.nsteps; st++) {
+                    const FusedStep &fs = P.steps[st];
+                    double o[NV];
+                    if (fs.kind == FK_ROWVEC) {
+#pragma unroll
+                        for (int nt = 0; nt < NT; nt++) {
+                            const double2 two =
+                                *reinterpret_cast<const double2 *>(rv + fs.smem_off * SK_MAXN + nt * 8 + 2 * t);
+                            o[2 * nt] = two.x;
+                            o[2 * nt + 1] = two.y;
+                        }
+                    } else {
+                        const double colv = fs.kind == FK_COLVEC ? cv[fs.smem_off * SK_WROWS + g + 8 * h] : fs.imm;
+#pragma unroll
+                        for (int i = 0; i < NV; i++)
+                            o[i] = colv;
+                    }
+                    sk_apply<NV>(fs.op, fs.reversed != 0, v, o);
+                }
             }
             if (P.ew_out && r < s.n) {
                 double *out = static_cast<double *>(P.ew_out) + r * P.ew_out_ld;
@@ -193,19 +276,39 @@ __global__ void __launch_bounds__(SK_THREADS, 1) skinny_gemm_kernel(const __grid
                 // scan (AggRow.h:71-96) starts from column 0 and uses strict comparisons: a NaN never replaces the
                 // running extremum, and a NaN in column 0 stays.  Here NaNs and the padding columns take part as
                 // +inf: they can only "win" a row whose every real value is +inf or NaN, and such a row's answer is
-                // column 0 anyway.  Block tournament (depth 4): slot i of a round stands for the slots [i, i + w);
-                // every column of the left block is lower than every column of the right block, so keeping the left
-                // candidate on ties keeps the first extremum.  Only the two cross-lane rounds need a column tie-break.
+                // column 0 anyway; a NaN in column 0 is put back at the end.  Block tournament (depth 4): slot i of a
+                // round stands for the slots [i, i + w); every column of the left block is lower than every column
+                // of the right block, so keeping the left candidate on ties keeps the first extremum.  Only the two
+                // cross-lane rounds need a column tie-break.
                 const bool want_max = P.taps[tp].kind == FT_MAX;
                 double x[16];
-                int c[16];
+                int c[16]; // slot numbers (immediates); turned into a column once, for the winner
 #pragma unroll
                 for (int i = 0; i < 16; i++) {
-                    const int col = (i >> 1) * 8 + 2 * t + (i & 1);
-                    const double val = i < NV ? v[i < NV ? i : 0] : 0.0;
-                    x[i] = (i < NV && col < s.N) ? fmin(want_max ? -val : val, (double)INFINITY) : (double)INFINITY;
-                    c[i] = col;
+                    x[i] = i < NV ? v[i < NV ? i : 0] : (double)INFINITY;
+                    c[i] = i;
                 }
+                if (want_max) {
+#pragma unroll
+                    for (int i = 0; i < NV; i++)
+                        x[i] = -x[i];
+                }
+                {
+                    // NaNs are looked for with integer instructions (any exponent of all ones: NaN or infinity)
+                    unsigned spare = 0x7ff00000u; // the smallest  ~exponent  seen: 0 = some exponent is all ones
+#pragma unroll
+                    for (int i = 0; i < NV; i++)
+                        spare = min(spare, ~(unsigned)__double2hiint(x[i]) & 0x7ff00000u);
+                    if (spare == 0) {
+#pragma unroll
+                        for (int i = 0; i < NV; i++)
+                            x[i] = fmin(x[i], (double)INFINITY);
+                    }
+                }
+#pragma unroll
+                for (int i = NV - 2; i < NV; i++) // padding columns exist only in the last 8-column block
+                    if ((i >> 1) * 8 + 2 * t + (i & 1) >= s.N)
+                        x[i] = (double)INFINITY;
 #pragma unroll
                 for (int w = 1; w <= 8; w <<= 1)
 #pragma unroll
@@ -215,7 +318,7 @@ __global__ void __launch_bounds__(SK_THREADS, 1) skinny_gemm_kernel(const __grid
                         c[i] = right ? c[i + w] : c[i];
                     }
                 double best = x[0];
-                int bi = c[0];
+                int bi = (c[0] >> 1) * 8 + 2 * t + (c[0] & 1);
 #pragma unroll
                 for (int m = 1; m <= 2; m <<= 1) {
                     const double ob = __shfl_xor_sync(0xffffffffu, best, m);
@@ -228,7 +331,7 @@ __global__ void __launch_bounds__(SK_THREADS, 1) skinny_gemm_kernel(const __grid
                 if (r < s.n && t == 0) {
                     double val = want_max ? -best : best;
                     int pos = bi;
-                    if (best == (double)INFINITY) { // nothing below +inf: the scan never left column 0
+                    if (best == (double)INFINITY || v0 != v0) { // the scan never left column 0
                         val = v0;
                         pos = 0;
                     }
@@ -243,41 +346,50 @@ __global__ void __launch_bounds__(SK_THREADS, 1) skinny_gemm_kernel(const __grid
     }
 }
 
-static size_t skinny_smem(int K, int nt, bool tb) {
-    const int KP = (K + 15) / 16 * 16, PA = KP + 4, PB = tb ? KP + 4 : nt * 8 + 4;
-    return ((size_t)(tb ? nt * 8 * PB : KP * PB) + SK_VEC_SLOTS * SK_MAXN +
+static size_t skinny_smem(int K, int nt) {
+    const int KP = (K + 15) / 16 * 16, PA = KP + 2, PB = KP + 2;
+    return ((size_t)nt * 8 * PB + SK_VEC_SLOTS * SK_MAXN +
             (size_t)SK_WARPS * (SK_WROWS * PA + SK_VEC_SLOTS * SK_WROWS)) * sizeof(double);
 }
 
 bool skinny_shape_ok(int64_t n, int64_t K, int64_t N, const void *A, int64_t lda) {
     return n >= 4096 && K >= 1 && K <= SK_MAXK && N >= 1 && N <= SK_MAXN && aligned16(A) && lda % 2 == 0 &&
-           skinny_smem((int)K, (int)((N + 7) / 8), true) <= 220 * 1024 &&
-           skinny_smem((int)K, (int)((N + 7) / 8), false) <= 220 * 1024;
+           skinny_smem((int)K, (int)((N + 7) / 8)) <= 220 * 1024;
 }
 
-template <int NT, bool TB, int KPT> static int launch_skinny_k(const SkinnyArgs &a, cudaStream_t st) {
-    const size_t smem = skinny_smem(a.K, NT, TB);
+template <int NT, int KPT, int CH> static int launch_skinny_k(const SkinnyArgs &a, cudaStream_t st) {
+    const size_t smem = skinny_smem(a.K, NT);
     static bool attr = false;
     if (!attr) {
-        DB2_CUDA(cudaFuncSetAttribute(skinny_gemm_kernel<NT, TB, KPT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        DB2_CUDA(cudaFuncSetAttribute(skinny_gemm_kernel<NT, KPT, CH>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                       220 * 1024));
         attr = true;
     }
     const int64_t ctas = ((a.n + SK_WROWS - 1) / SK_WROWS + SK_WARPS - 1) / SK_WARPS;
     const int grid = (int)(ctas < sm_count() ? ctas : sm_count());
-    skinny_gemm_kernel<NT, TB, KPT><<<grid, SK_THREADS, smem, st>>>(a);
+    skinny_gemm_kernel<NT, KPT, CH><<<grid, SK_THREADS, smem, st>>>(a);
     return after_launch("skinny_gemm_kernel");
 }
-template <int NT, bool TB> static int launch_skinny(const SkinnyArgs &a, cudaStream_t st) {
+template <int NT, int CH> static int launch_skinny(const SkinnyArgs &a, cudaStream_t st) {
     switch ((a.K + 15) / 16 * 16) { // the common contraction lengths get their own instantiation
-    case 16: return launch_skinny_k<NT, TB, 16>(a, st);
-    case 32: return launch_skinny_k<NT, TB, 32>(a, st);
-    case 64: return launch_skinny_k<NT, TB, 64>(a, st);
-    default: return launch_skinny_k<NT, TB, 0>(a, st);
+    case 16: return launch_skinny_k<NT, 16, CH>(a, st);
+    case 32: return launch_skinny_k<NT, 32, CH>(a, st);
+    case 64: return launch_skinny_k<NT, 64, CH>(a, st);
+    default: return launch_skinny_k<NT, 0, CH>(a, st);
     }
 }
 
 int skinny_vec_slots() { return SK_VEC_SLOTS; }
+
+// the chains that are compiled in (the CH parameter of the kernel); anything else is interpreted
+static int compiled_chain(const FusedProgram &P) {
+    auto is = [&](int i, int op, int kind) { return P.steps[i].op == op && P.steps[i].kind == kind; };
+    if (P.nsteps == 3 && is(0, FO_MUL, FK_SCALAR) && is(1, FO_ADD, FK_COLVEC) && is(2, FO_ADD, FK_ROWVEC))
+        return 1;
+    if (P.nsteps == 2 && is(0, FO_MUL, FK_SCALAR) && is(1, FO_ADD, FK_ROWVEC))
+        return 2;
+    return 0;
+}
 
 int skinny_gemm(const SkinnyArgs &args, cudaStream_t st) {
     if (args.n == 0 || args.N == 0)
@@ -291,9 +403,10 @@ int skinny_gemm(const SkinnyArgs &args, cudaStream_t st) {
             a.prog.steps[i].smem_off = cols++;
     }
     DB2_CHECK(rows <= SK_VEC_SLOTS && cols <= SK_VEC_SLOTS, DB2_EINVAL, "skinny product: too many vector operands");
-    const int nt = (a.N + 7) / 8;
+    const int nt = (a.N + 7) / 8, ch = compiled_chain(a.prog);
 #define DB2_SK(NTV)                                                                                                    \
-    case NTV: return a.tb ? launch_skinny<NTV, true>(a, st) : launch_skinny<NTV, false>(a, st);
+    case NTV:                                                                                                          \
+        return ch == 1 ? launch_skinny<NTV, 1>(a, st) : (ch == 2 ? launch_skinny<NTV, 2>(a, st) : launch_skinny<NTV, 0>(a, st));
     switch (nt) {
         DB2_SK(1) DB2_SK(2) DB2_SK(3) DB2_SK(4) DB2_SK(5) DB2_SK(6) DB2_SK(7) DB2_SK(8)
     default: return set_error(DB2_EINVAL, "skinny product: more than 64 columns");

@@ -91,6 +91,13 @@ def test_fused_extrema_ties_and_nan(ctx):
     ref3 = x[:65536 + 8] @ c3.T + 1.0
     rows = np.array([r for r in range(ref3.shape[0]) if r != 5])
     assert np.array_equal(got[rows], np.nanargmin(ref3[rows], 1))
+    # NaN in column 0 only: the scan starts there and no comparison with a NaN succeeds, so it stays
+    c4 = c.copy()
+    c4[0, :] = np.nan
+    xc = k.matMul(k.DenseMatrix.from_numpy(ctx, x[:65536 + 8]), k.DenseMatrix.from_numpy(ctx, c4), False, True)
+    D4 = k.ewBinaryObjSca(B.ADD, xc, 1.0)
+    assert (k.aggRow(A.IDXMIN, D4).to_numpy() == 0).all() and (k.aggRow(A.IDXMAX, D4).to_numpy() == 0).all()
+    assert np.isnan(k.aggRow(A.MIN, D4).to_numpy()).all() and np.isnan(k.aggRow(A.MAX, D4).to_numpy()).all()
 
 
 def test_chain_that_cannot_be_fused_falls_back(ctx):
