@@ -2,9 +2,11 @@
 //
 // Blackwell's tcgen05 tensor path has no FP64 kind, so the FP64 contraction is the warp-level DMMA
 // (mma.sync.aligned.m16n8k16.f64), fed from shared memory tiles that are filled with 16-byte cp.async copies in a
-// 4-stage ring.  Tile layouts are chosen so that every fragment load is one conflict-free 64-bit shared load per
-// thread: an operand whose contraction index is contiguous in memory is stored [row][KC + 4], the other kind is stored
-// [k][tile + 4]; both pitches are 4 mod 16 doubles, which spreads every fragment access of a half warp over all banks.
+// 3-stage ring.  Tile layouts are chosen so that every fragment load is a conflict-free 128-bit shared load: an
+// operand whose contraction index is contiguous in memory is stored [row][KC + 2], the other kind is stored
+// [k][tile + 4].  The FP64 pipe takes one DMMA per 16 cycles and scheduler, and every other instruction of the
+// warps on that scheduler needs an issue slot in between, so the loop is kept short: two values per shared load,
+// and a loader without bounds tests for the stages that lie inside the operands.
 //
 // The tall-skinny products of the workloads (t(X) X with 8.4 M x 512, t(P) X with 1 M x 50) contract over the ROWS:
 // the row range is split over gridDim.z, each split accumulates a private tile and writes it to scratch, and a second
@@ -14,15 +16,18 @@
 
 namespace db2 {
 
-constexpr int KC = 16;     // contraction depth per stage
-constexpr int PK = KC + 4; // pitch of a [row][k] tile (doubles)
+constexpr int KC = 32;     // contraction depth per stage (two m16n8k16 steps)
+// pitch of a [row][k] tile (doubles).  When both operands are stored that way (A B^T) their fragments are read with
+// 128-bit loads, which are conflict free at a pitch of 2 mod 4; next to a [k][row] operand the loads are 64 bits wide
+// and want 4 mod 16.
+__host__ __device__ constexpr int pitch_k(bool ta, bool tb) { return (!ta && tb) ? KC + 2 : KC + 4; }
 // CTA tiles: BM x BN in {64,128}^2 with (BM / 32) x (BN / 32) warps of 32 x 32.  128 x 128 (16 warps) gives 16 flop
 // per byte fetched from L2, which is what keeps the FP64 tensor pipe busy (a 64 x 64 tile needs twice the L2 traffic
 // and stalls at about half of peak on this part).
 template <int BM, int BN> struct TileCfg {
     static constexpr int WN = 32;
     static constexpr int THREADS = (BM / 32) * (BN / 32) * 32;
-    static constexpr int STAGES = (BM == 128 && BN == 128) ? 5 : 4;
+    static constexpr int STAGES = 3;
 };
 
 // D (16 x 8) += A (16 x 16, row) * B (16 x 8, col).  With g = lane / 4, t = lane % 4:
@@ -39,6 +44,10 @@ __device__ __forceinline__ void dmma16x8x16(double (&c)[4], const double (&a)[8]
 __device__ __forceinline__ void cp_async16_zfill(void *smem_dst, const void *gsrc, int bytes) {
     const unsigned s = (unsigned)__cvta_generic_to_shared(smem_dst);
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(s), "l"(gsrc), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async16(void *smem_dst, const void *gsrc) {
+    const unsigned s = (unsigned)__cvta_generic_to_shared(smem_dst);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(s), "l"(gsrc) : "memory");
 }
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
 template <int N> __device__ __forceinline__ void cp_async_wait() {
@@ -62,11 +71,39 @@ struct GemmArgs {
 };
 
 // Loads one stage.  TA: A is stored K x M (contraction index = row);  !TA: A is M x K.  Same for TB with N.
-template <bool TA, bool TB, int BM, int BN>
+// FULL: the stage lies inside the operands and 16-byte copies are allowed -- no bounds tests, no zero fill.
+template <bool TA, bool TB, int BM, int BN, bool FULL>
 __device__ __forceinline__ void load_stage(const GemmArgs &g, double *As, double *Bs, int64_t m0, int64_t n0,
-                                           int64_t k0, int64_t k_end, int tid, int nthreads, bool load_b) {
-    constexpr int PA = BM + 4, PB = BN + 4;
-    if (g.aligned) {
+                                           int64_t k0, int64_t k_end, int tid, int nthreads, bool load_b,
+                                           const double *a_src, const double *b_src) {
+    constexpr int PA = BM + 4, PB = BN + 4, PK = pitch_k(TA, TB);
+    if constexpr (FULL) {
+        // a_src / b_src: this thread's first 16 bytes of the stage (see full_src)
+        constexpr int NT = (BM / 32) * (BN / 32) * 32;
+        if constexpr (TA) {
+            double *dst = As + (tid / (BM / 2)) * PA + 2 * (tid % (BM / 2));
+#pragma unroll
+            for (int i = 0; i < KC * (BM / 2) / NT; i++)
+                cp_async16(dst + i * (NT / (BM / 2)) * PA, a_src + (int64_t)(i * (NT / (BM / 2))) * g.lda);
+        } else {
+            double *dst = As + (tid / (KC / 2)) * PK + 2 * (tid % (KC / 2));
+#pragma unroll
+            for (int i = 0; i < BM * (KC / 2) / NT; i++)
+                cp_async16(dst + i * (NT / (KC / 2)) * PK, a_src + (int64_t)(i * (NT / (KC / 2))) * g.lda);
+        }
+        if (!load_b) {
+        } else if constexpr (!TB) {
+            double *dst = Bs + (tid / (BN / 2)) * PB + 2 * (tid % (BN / 2));
+#pragma unroll
+            for (int i = 0; i < KC * (BN / 2) / NT; i++)
+                cp_async16(dst + i * (NT / (BN / 2)) * PB, b_src + (int64_t)(i * (NT / (BN / 2))) * g.ldb);
+        } else {
+            double *dst = Bs + (tid / (KC / 2)) * PK + 2 * (tid % (KC / 2));
+#pragma unroll
+            for (int i = 0; i < BN * (KC / 2) / NT; i++)
+                cp_async16(dst + i * (NT / (KC / 2)) * PK, b_src + (int64_t)(i * (NT / (KC / 2))) * g.ldb);
+        }
+    } else if (g.aligned) {
         if constexpr (TA) { // [KC][BM]: KC rows of BM contiguous doubles
             for (int idx = tid; idx < KC * (BM / 2); idx += nthreads) {
                 const int kk = idx / (BM / 2), p = idx % (BM / 2);
@@ -145,7 +182,8 @@ template <bool TA, bool TB, int BM, int BN>
 __global__ void __launch_bounds__(TileCfg<BM, BN>::THREADS) gemm_f64_kernel(const __grid_constant__ GemmArgs ga) {
     using Cfg = TileCfg<BM, BN>;
     constexpr int NT = Cfg::THREADS, WN = Cfg::WN, STAGES = Cfg::STAGES, NTILES = WN / 8;
-    constexpr int PA = BM + 4, PB = BN + 4;
+    constexpr int PA = BM + 4, PB = BN + 4, PK = pitch_k(TA, TB);
+    constexpr bool K4 = !TA && TB; // both operands [row][k]: lane t takes k = 4 t + j, else k = t + 4 j
     constexpr int A_ELEMS = TA ? KC * PA : BM * PK;
     constexpr int B_ELEMS = TB ? BN * PK : KC * PB;
     extern __shared__ __align__(16) double gsm[];
@@ -180,11 +218,27 @@ __global__ void __launch_bounds__(TileCfg<BM, BN>::THREADS) gemm_f64_kernel(cons
     auto stage_a = [&](int s) { return gsm + (size_t)s * (A_ELEMS + B_ELEMS); };
     auto stage_b = [&](int s) { return same_tile ? stage_a(s) : gsm + (size_t)s * (A_ELEMS + B_ELEMS) + A_ELEMS; };
 
+    // a tile inside the operands takes the loader without bounds tests (all but the last stage of a ragged range)
+    const bool interior = ga.aligned && m0 + BM <= ga.M && n0 + BN <= ga.N;
+    // the thread's first source of a full stage at k_begin, and what one stage adds to it
+    const double *a_src0 = TA ? ga.A + (k_begin + tid / (BM / 2)) * ga.lda + m0 + 2 * (tid % (BM / 2))
+                              : ga.A + (m0 + tid / (KC / 2)) * ga.lda + k_begin + 2 * (tid % (KC / 2));
+    const double *b_src0 = !TB ? ga.B + (k_begin + tid / (BN / 2)) * ga.ldb + n0 + 2 * (tid % (BN / 2))
+                               : ga.B + (n0 + tid / (KC / 2)) * ga.ldb + k_begin + 2 * (tid % (KC / 2));
+    const int64_t a_step = TA ? KC * ga.lda : KC, b_step = !TB ? KC * ga.ldb : KC;
+    auto load = [&](int slot, int64_t chunk) {
+        const int64_t k0 = k_begin + chunk * KC;
+        if (interior && k0 + KC <= k_end)
+            load_stage<TA, TB, BM, BN, true>(ga, stage_a(slot), stage_b(slot), m0, n0, k0, k_end, tid, NT, !same_tile,
+                                             a_src0 + chunk * a_step, b_src0 + chunk * b_step);
+        else
+            load_stage<TA, TB, BM, BN, false>(ga, stage_a(slot), stage_b(slot), m0, n0, k0, k_end, tid, NT, !same_tile,
+                                              nullptr, nullptr);
+    };
 #pragma unroll
     for (int s = 0; s < STAGES - 1; s++) {
         if (s < nchunks)
-            load_stage<TA, TB, BM, BN>(ga, stage_a(s), stage_b(s), m0, n0, k_begin + (int64_t)s * KC, k_end, tid, NT,
-                                       !same_tile);
+            load(s, s);
         cp_async_commit();
     }
     for (int64_t ch = 0; ch < nchunks; ch++) {
@@ -193,67 +247,129 @@ __global__ void __launch_bounds__(TileCfg<BM, BN>::THREADS) gemm_f64_kernel(cons
         {
             const int64_t nx = ch + STAGES - 1;
             if (nx < nchunks)
-                load_stage<TA, TB, BM, BN>(ga, stage_a((int)(nx % STAGES)), stage_b((int)(nx % STAGES)), m0, n0,
-                                           k_begin + nx * KC, k_end, tid, NT, !same_tile);
+                load((int)(nx % STAGES), nx);
             cp_async_commit();
         }
         if (!warp_active)
             continue;
         const double *As = stage_a((int)(ch % STAGES));
         const double *Bs = stage_b((int)(ch % STAGES));
-        static_assert(KC == 16, "one m16n8k16 step per stage");
+        static_assert(KC % 16 == 0, "whole m16n8k16 steps per stage");
+#pragma unroll
+        for (int kk = 0; kk < KC; kk += 16) {
+        // Fragments come in with 128-bit shared loads where the layout allows it.  An operand stored [k][row] yields
+        // the same k of two 8-row blocks per load because its rows are interleaved: block b of a 16-row group holds
+        // the rows 2 g + b (not g + 8 b); the epilogue undoes the interleaving.  When both operands are stored
+        // [row][k], lane t takes k = 4 t + j (j = 0..3) for slot j of both (the product is the same sum in a
+        // different fixed order) and a load yields two slots; next to a [k][row] operand k stays t + 4 j (the order
+        // that spreads the [k][row] rows over the banks) and the [row][k] operand is read 64 bits at a time.
         double af[2][8];
 #pragma unroll
-        for (int mt = 0; mt < 2; mt++)
+        for (int mt = 0; mt < 2; mt++) {
+            if constexpr (TA) {
 #pragma unroll
-            for (int i = 0; i < 8; i++) {
-                const int m = wm * 32 + mt * 16 + g + 8 * (i & 1), k = t + 4 * (i >> 1);
-                af[mt][i] = TA ? As[k * PA + m] : As[m * PK + k];
+                for (int j = 0; j < 4; j++) {
+                    const double2 v = *reinterpret_cast<const double2 *>(As + (kk + t + 4 * j) * PA + wm * 32 + mt * 16 + 2 * g);
+                    af[mt][2 * j] = v.x;
+                    af[mt][2 * j + 1] = v.y;
+                }
+            } else if constexpr (K4) {
+#pragma unroll
+                for (int b = 0; b < 2; b++) {
+                    const double *row = As + (wm * 32 + mt * 16 + g + 8 * b) * PK + kk + 4 * t;
+                    const double2 lo = *reinterpret_cast<const double2 *>(row), hi = *reinterpret_cast<const double2 *>(row + 2);
+                    af[mt][b] = lo.x;
+                    af[mt][2 + b] = lo.y;
+                    af[mt][4 + b] = hi.x;
+                    af[mt][6 + b] = hi.y;
+                }
+            } else {
+#pragma unroll
+                for (int i = 0; i < 8; i++)
+                    af[mt][i] = As[(wm * 32 + mt * 16 + g + 8 * (i & 1)) * PK + kk + t + 4 * (i >> 1)];
             }
-#pragma unroll
-        for (int nt = 0; nt < NTILES; nt++) {
-            double bf[4];
-#pragma unroll
-            for (int i = 0; i < 4; i++) {
-                const int n = wn * WN + nt * 8 + g, k = t + 4 * i;
-                bf[i] = TB ? Bs[n * PK + k] : Bs[k * PB + n];
-            }
-            dmma16x8x16(acc[0][nt], af[0], bf);
-            dmma16x8x16(acc[1][nt], af[1], bf);
         }
+#pragma unroll
+        for (int q = 0; q < NTILES / 2; q++) {
+            double bf[2][4];
+            if constexpr (!TB) {
+#pragma unroll
+                for (int j = 0; j < 4; j++) {
+                    const double2 v = *reinterpret_cast<const double2 *>(Bs + (kk + t + 4 * j) * PB + wn * WN + q * 16 + 2 * g);
+                    bf[0][j] = v.x;
+                    bf[1][j] = v.y;
+                }
+            } else if constexpr (K4) {
+#pragma unroll
+                for (int b = 0; b < 2; b++) {
+                    const double *row = Bs + (wn * WN + q * 16 + 8 * b + g) * PK + kk + 4 * t;
+                    const double2 lo = *reinterpret_cast<const double2 *>(row), hi = *reinterpret_cast<const double2 *>(row + 2);
+                    bf[b][0] = lo.x;
+                    bf[b][1] = lo.y;
+                    bf[b][2] = hi.x;
+                    bf[b][3] = hi.y;
+                }
+            } else {
+#pragma unroll
+                for (int b = 0; b < 2; b++)
+#pragma unroll
+                    for (int i = 0; i < 4; i++)
+                        bf[b][i] = Bs[(wn * WN + q * 16 + 8 * b + g) * PK + kk + t + 4 * i];
+            }
+#pragma unroll
+            for (int b = 0; b < 2; b++) {
+                dmma16x8x16(acc[0][2 * q + b], af[0], bf[b]);
+                dmma16x8x16(acc[1][2 * q + b], af[1], bf[b]);
+            }
+        }
+        } // kk
     }
     cp_async_wait<0>();
     if (!warp_active)
         return;
 
+    // acc[mt][nt][2 h + e]: row block h of the 16-row group mt, column 2 t + e of the 8-column block nt.  Rows: block h
+    // holds the rows 2 g + h when A was stored [k][row], g + 8 h otherwise.  Columns: when B was stored [k][column]
+    // the blocks 2 q and 2 q + 1 interleave, so a lane owns the four adjacent columns 16 q + 4 t .. + 3 =
+    // (block 2q, e 0), (block 2q+1, e 0), (block 2q, e 1), (block 2q+1, e 1).
+    auto row_of = [&](int mt, int h) { return wm * 32 + mt * 16 + (TA ? 2 * g + h : g + 8 * h); };
     if (ga.splits > 1) {
         double *tile =
             ga.part + (((size_t)blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x) * (BM * BN);
 #pragma unroll
         for (int mt = 0; mt < 2; mt++)
 #pragma unroll
-            for (int nt = 0; nt < NTILES; nt++)
+            for (int h = 0; h < 2; h++) {
+                double *out = tile + row_of(mt, h) * BN + wn * WN;
+                if constexpr (!TB) {
 #pragma unroll
-                for (int h = 0; h < 2; h++) {
-                    const int r = wm * 32 + mt * 16 + g + 8 * h, c = wn * WN + nt * 8 + 2 * t;
-                    *reinterpret_cast<double2 *>(tile + r * BN + c) =
-                        make_double2(acc[mt][nt][2 * h], acc[mt][nt][2 * h + 1]);
+                    for (int q = 0; q < NTILES / 2; q++) {
+                        double2 *o = reinterpret_cast<double2 *>(out + q * 16 + 4 * t);
+                        o[0] = make_double2(acc[mt][2 * q][2 * h], acc[mt][2 * q + 1][2 * h]);
+                        o[1] = make_double2(acc[mt][2 * q][2 * h + 1], acc[mt][2 * q + 1][2 * h + 1]);
+                    }
+                } else {
+#pragma unroll
+                    for (int nt = 0; nt < NTILES; nt++)
+                        *reinterpret_cast<double2 *>(out + nt * 8 + 2 * t) =
+                            make_double2(acc[mt][nt][2 * h], acc[mt][nt][2 * h + 1]);
                 }
+            }
     } else {
 #pragma unroll
         for (int mt = 0; mt < 2; mt++)
 #pragma unroll
             for (int nt = 0; nt < NTILES; nt++)
 #pragma unroll
-                for (int h = 0; h < 2; h++) {
-                    const int64_t r = m0 + wm * 32 + mt * 16 + g + 8 * h, c = n0 + wn * WN + nt * 8 + 2 * t;
-                    if (r < ga.M) {
-                        if (c < ga.N)
-                            ga.C[r * ga.ldc + c] = acc[mt][nt][2 * h];
-                        if (c + 1 < ga.N)
-                            ga.C[r * ga.ldc + c + 1] = acc[mt][nt][2 * h + 1];
+                for (int h = 0; h < 2; h++)
+#pragma unroll
+                    for (int e = 0; e < 2; e++) {
+                        const int64_t r = m0 + row_of(mt, h);
+                        const int64_t c =
+                            n0 + wn * WN + (TB ? nt * 8 + 2 * t + e : (nt / 2) * 16 + 4 * t + 2 * e + (nt & 1));
+                        if (r < ga.M && c < ga.N)
+                            ga.C[r * ga.ldc + c] = acc[mt][nt][2 * h + e];
                     }
-                }
     }
 }
 
@@ -293,10 +409,9 @@ struct GemmPlan {
 };
 
 static size_t tile_smem(int bm, int bn, bool ta, bool tb) {
-    const size_t a = ta ? (size_t)KC * (bm + 4) : (size_t)bm * PK;
-    const size_t b = tb ? (size_t)bn * PK : (size_t)KC * (bn + 4);
-    const int stages = (bm == 128 && bn == 128) ? 5 : 4;
-    return stages * (a + b) * 8;
+    const size_t a = ta ? (size_t)KC * (bm + 4) : (size_t)bm * pitch_k(ta, tb);
+    const size_t b = tb ? (size_t)bn * pitch_k(ta, tb) : (size_t)KC * (bn + 4);
+    return 3 * (a + b) * 8; // TileCfg::STAGES
 }
 
 static GemmPlan plan_gemm(int64_t M, int64_t N, int64_t K, bool syrk, bool ta, bool tb) {
@@ -327,8 +442,8 @@ static GemmPlan plan_gemm(int64_t M, int64_t N, int64_t K, bool syrk, bool ta, b
     if (splits < 1)
         splits = 1;
     auto shares = [&](int64_t want, int *count, int64_t *k_per) { // `want` shares of whole chunks
-        if (want > chunks / 8)
-            want = chunks / 8; // at least 8 chunks (128 rows) per share
+        if (want > chunks / 4)
+            want = chunks / 4; // at least 4 chunks (128 rows) per share
         if (want < 1)
             want = 1;
         if (want > 512)
