@@ -91,6 +91,17 @@ def _allreduce_scalar(ctx, x: float, comm: Optional[Comm], combine=COMBINE_ADD) 
     return float(comm.allreduce_numpy(np.array([x], dtype=np.float64), combine)[0])
 
 
+def _sum_over_shards(ctx, K, vec, comm: Optional[Comm]) -> float:
+    """sum(vec) over all row shards for an n x 1 vector.  With a device communicator the shard's sum stays on the
+    device as a 1 x 1 matrix and is combined there (one NCCL call on the compute stream, one read at the end); the
+    generic route reads the shard's scalar and combines it through the host."""
+    if comm is not None and comm.world > 1 and comm.device_collectives(ctx) and vec.cols == 1:
+        part = K.aggCol(A.SUM, vec)
+        comm.allreduce_device(ctx, part, COMBINE_ADD)
+        return float(part.to_numpy()[0, 0])
+    return _allreduce_scalar(ctx, K.aggAll(A.SUM, vec), comm)
+
+
 @dataclass
 class StandardiseResult:
     mu: object        # 1 x c   column means
@@ -135,7 +146,7 @@ def standardise_aggregate(ctx, X, n_total: Optional[int] = None, comm: Optional[
     with probe.section("fused_row_kernel (Z=(X-mu)/sd; rowSums(Z^2), rowMaxs(Z), idxMax(Z))",
                        X.rows * (X.cols * 8 + 24)):
         r.device_ptr()  # the three row aggregations are produced by one pass over X
-    s = _allreduce_scalar(ctx, K.aggAll(A.SUM, r), comm)
+    s = _sum_over_shards(ctx, K, r, comm)
     return StandardiseResult(mu, sd, r, s, m, i)
 
 
