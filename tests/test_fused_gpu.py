@@ -11,7 +11,8 @@ from tests.util import RTOL_REDUCE_F64, assert_bits_equal, assert_close_rel, rng
 
 pytestmark = pytest.mark.gpu
 
-SHAPES = [(70000, 32), (4099, 50), (3000, 33), (2049, 128), (1500, 1000), (66000, 7), (300, 400)]
+SHAPES = [(70000, 32), (4099, 50), (3000, 33), (2049, 128), (1500, 1000), (66000, 7), (300, 400), (70001, 34),
+          (40000, 6), (50000, 2), (3001, 70), (2500, 62)]
 
 
 def _k():

@@ -32,7 +32,7 @@ def test_matmul_all_transpose_combinations(ctx, ta, tb):
     k, o = _k()
     rng = np.random.default_rng(1)
     for (m, n, kk) in [(1, 1, 1), (5, 7, 3), (64, 64, 16), (130, 70, 37), (257, 50, 64), (33, 129, 1000), (8, 8, 5000),
-                       (300, 200, 150)]:
+                       (300, 200, 150), (128, 128, 64), (384, 256, 2000), (130, 258, 96)]:
         a = rng.standard_normal((kk, m) if ta else (m, kk))
         b = rng.standard_normal((n, kk) if tb else (kk, n))
         got = k.matMul(k.DenseMatrix.from_numpy(ctx, a), k.DenseMatrix.from_numpy(ctx, b), ta, tb).to_numpy()
