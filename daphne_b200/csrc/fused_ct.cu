@@ -19,6 +19,7 @@
 #include "ops.cuh"
 
 #include <cstring>
+#include <type_traits>
 
 namespace db2 {
 namespace ct {
@@ -137,6 +138,191 @@ __device__ __forceinline__ void feed(TapState<TapsT> &ts, double v, int c) {
     }
 }
 
+// ---- chains that have no entry in the table: same kernel, steps and taps read from the program at run time ----
+// The data movement, the grouping and the division are those of the compiled chains; what is interpreted is the
+// operand kind and the opcode, once per step and group of G elements (not per element).
+struct AnyChain {
+    static constexpr int n = 0; // no per-thread chain state: scalar helpers sit behind the staged row vectors
+};
+struct AnyTaps {
+    static constexpr int n = FUSED_MAX_AGGS;
+};
+
+template <int G>
+__device__ __forceinline__ void apply_step_rt(int op, bool rev, double (&v)[G], const double (&o)[G]) {
+#define DB2_CT_STEP(FWD, REV)                                                                                          \
+    if (!rev) {                                                                                                        \
+        _Pragma("unroll") for (int i = 0; i < G; i++) { const double a = v[i], b = o[i]; (void)b; v[i] = (FWD); }      \
+    } else {                                                                                                           \
+        _Pragma("unroll") for (int i = 0; i < G; i++) { const double a = v[i], b = o[i]; (void)b; v[i] = (REV); }      \
+    }                                                                                                                  \
+    break;
+    switch (op) {
+    case FO_ADD: DB2_CT_STEP(__dadd_rn(a, b), __dadd_rn(b, a))
+    case FO_SUB: DB2_CT_STEP(__dsub_rn(a, b), __dsub_rn(b, a))
+    case FO_MUL: DB2_CT_STEP(__dmul_rn(a, b), __dmul_rn(b, a))
+    case FO_DIV: DB2_CT_STEP(__ddiv_rn(a, b), __ddiv_rn(b, a))
+    case FO_SQUARE: DB2_CT_STEP(__dmul_rn(a, a), __dmul_rn(a, a))
+    case FO_EQ: DB2_CT_STEP((double)(a == b), (double)(b == a))
+    case FO_NEQ: DB2_CT_STEP((double)(a != b), (double)(b != a))
+    case FO_LT: DB2_CT_STEP((double)(a < b), (double)(b < a))
+    case FO_LE: DB2_CT_STEP((double)(a <= b), (double)(b <= a))
+    case FO_GT: DB2_CT_STEP((double)(a > b), (double)(b > a))
+    case FO_GE: DB2_CT_STEP((double)(a >= b), (double)(b >= a))
+    case FO_MIN: DB2_CT_STEP(((b < a) ? b : a), ((a < b) ? a : b))
+    case FO_MAX: DB2_CT_STEP(((a < b) ? b : a), ((b < a) ? a : b))
+    case FO_AND: DB2_CT_STEP((double)((a != 0.0) && (b != 0.0)), (double)((b != 0.0) && (a != 0.0)))
+    case FO_OR: DB2_CT_STEP((double)((a != 0.0) || (b != 0.0)), (double)((b != 0.0) || (a != 0.0)))
+    case FO_NEG: DB2_CT_STEP(-a, -a)
+    case FO_ABS: DB2_CT_STEP(fabs(a), fabs(a))
+    case FO_SIGN:
+        DB2_CT_STEP(((a == 0) ? 0.0 : ((a < 0) ? -1.0 : ((a > 0) ? 1.0 : (double)NAN))),
+                    ((a == 0) ? 0.0 : ((a < 0) ? -1.0 : ((a > 0) ? 1.0 : (double)NAN))))
+    case FO_FLOOR: DB2_CT_STEP(floor(a), floor(a))
+    case FO_CEIL: DB2_CT_STEP(ceil(a), ceil(a))
+    case FO_ROUND: DB2_CT_STEP(round(a), round(a))
+    case FO_ISNAN: DB2_CT_STEP((double)(a != a), (double)(a != a))
+    default: break;
+    }
+#undef DB2_CT_STEP
+}
+
+template <bool C0, int G>
+__device__ __forceinline__ void feed_rt(TapState<AnyTaps> &ts, const FusedProgram &P, int after, const double (&v)[G],
+                                        int c0) {
+#pragma unroll
+    for (int a = 0; a < FUSED_MAX_AGGS; a++) {
+        if (a < P.ntaps && P.taps[a].after_step == after) {
+            const int kind = P.taps[a].kind;
+            if (kind == FT_SUM || kind == FT_MEAN) {
+#pragma unroll
+                for (int i = 0; i < G; i++)
+                    ts.v[a] = __dadd_rn(ts.v[a], v[i]);
+            } else if (kind == FT_PROD) {
+#pragma unroll
+                for (int i = 0; i < G; i++)
+                    ts.v[a] = __dmul_rn(ts.v[a], v[i]);
+            } else {
+                if constexpr (C0)
+                    if (c0 == 0)
+                        ts.first[a] = v[0];
+                const bool mx = kind == FT_MAX;
+#pragma unroll
+                for (int i = 0; i < G; i++) {
+                    const bool better = mx ? (v[i] > ts.v[a]) : (v[i] < ts.v[a]);
+                    if (better) {
+                        ts.v[a] = v[i];
+                        ts.c[a] = c0 + i;
+                    }
+                }
+            }
+        }
+    }
+}
+__device__ __forceinline__ void init_taps_rt(TapState<AnyTaps> &ts, const FusedProgram &P) {
+#pragma unroll
+    for (int a = 0; a < FUSED_MAX_AGGS; a++) {
+        const int kind = a < P.ntaps ? P.taps[a].kind : FT_SUM;
+        ts.v[a] = (kind == FT_PROD) ? 1.0 : (kind == FT_MIN) ? INFINITY : (kind == FT_MAX) ? -INFINITY : 0.0;
+        ts.first[a] = 0.0;
+        ts.c[a] = NO_COL;
+    }
+}
+__device__ __forceinline__ void write_taps_rt(const TapState<AnyTaps> &ts, const FusedProgram &P, int64_t row) {
+#pragma unroll
+    for (int a = 0; a < FUSED_MAX_AGGS; a++) {
+        if (a < P.ntaps) {
+            const int kind = P.taps[a].kind;
+            double v = ts.v[a];
+            int c = ts.c[a];
+            if (kind == FT_MIN || kind == FT_MAX) {
+                if (c == NO_COL || ts.first[a] != ts.first[a]) { // see write_taps
+                    v = ts.first[a];
+                    c = 0;
+                }
+                if (P.taps[a].out_idx)
+                    static_cast<uint64_t *>(P.taps[a].out_idx)[row] = (uint64_t)c;
+            }
+            if (kind == FT_MEAN)
+                v = __ddiv_rn(v, (double)P.cols);
+            if (P.taps[a].out)
+                static_cast<double *>(P.taps[a].out)[row] = v;
+        }
+    }
+}
+
+template <bool C0, int G>
+__device__ __forceinline__ void run_group_rt(double (&v)[G], const FusedProgram &P, TapState<AnyTaps> &ts,
+                                             const double *rvs, int64_t row, int64_t c) {
+    feed_rt<C0, G>(ts, P, 0, v, (int)c);
+#pragma unroll 1
+    for (int s = 0; s < P.nsteps; s++) {
+        const FusedStep &fs = P.steps[s];
+        const bool fwd_div = fs.op == FO_DIV && !fs.reversed;
+        const double nan = __longlong_as_double(0x7ff8000000000000ll);
+        double o[G], y[G];
+        if (fs.kind == FK_ROWVEC) {
+            const double2 *ov = reinterpret_cast<const double2 *>(rvs + fs.smem_off + c);
+#pragma unroll
+            for (int i = 0; i < G / 2; i++) {
+                const double2 t = ov[i];
+                o[2 * i] = t.x;
+                o[2 * i + 1] = t.y;
+            }
+            if (fwd_div) {
+                const double2 *yv = reinterpret_cast<const double2 *>(rvs + fs.smem_off + P.cols + c);
+#pragma unroll
+                for (int i = 0; i < G / 2; i++) {
+                    const double2 u = yv[i];
+                    y[2 * i] = u.x;
+                    y[2 * i + 1] = u.y;
+                }
+            }
+        } else if (fs.kind == FK_MATRIX) {
+            const double *mp = static_cast<const double *>(fs.ptr) + row * fs.ld + c;
+#pragma unroll
+            for (int i = 0; i < G; i++) {
+                o[i] = __ldg(mp + i);
+                y[i] = nan;
+            }
+        } else {
+            double ov = fs.imm, yv = nan; // SCALAR (helper staged behind the row vectors), UNARY
+            if (fs.kind == FK_SCALAR)
+                yv = rvs[P.smem_elems + s];
+            else if (fs.kind == FK_COLVEC)
+                ov = __ldg(static_cast<const double *>(fs.ptr) + row * fs.ld);
+#pragma unroll
+            for (int i = 0; i < G; i++) {
+                o[i] = ov;
+                y[i] = yv;
+            }
+        }
+        if (fwd_div) {
+            double q1[G];
+            unsigned worst = 0;
+#pragma unroll
+            for (int i = 0; i < G; i++) {
+                const double q = __dmul_rn(v[i], y[i]);
+                const double r = __fma_rn(-q, o[i], v[i]);
+                q1[i] = __fma_rn(r, y[i], q);
+                worst = max(worst, fast_div_window_pos(q1[i]));
+            }
+            if (worst < FAST_DIV_WINDOW) {
+#pragma unroll
+                for (int i = 0; i < G; i++)
+                    v[i] = q1[i];
+            } else {
+#pragma unroll
+                for (int i = 0; i < G; i++)
+                    v[i] = fast_div(v[i], o[i], y[i]);
+            }
+        } else {
+            apply_step_rt<G>(fs.op, fs.reversed != 0, v, o);
+        }
+        feed_rt<C0, G>(ts, P, s + 1, v, (int)c);
+    }
+}
+
 // The chain on G consecutive elements of one row, step by step: G independent dependency chains for the scheduler to
 // interleave (an element at a time, the latency of the FP64 pipe would be exposed on every step).  The division's
 // range test is folded over the group, so the rare generic division costs one branch per group instead of a branch
@@ -153,6 +339,9 @@ __device__ __forceinline__ void feed_group(TapState<TapsT> &ts, const double (&v
 template <typename ChainT, typename TapsT, bool C0, int G, int I = 0>
 __device__ __forceinline__ void run_group(double (&v)[G], const FusedProgram &P, const ChainState<ChainT> &cs,
                                           TapState<TapsT> &ts, const double *rvs, int64_t row, int64_t c) {
+    if constexpr (std::is_same<ChainT, AnyChain>::value) {
+        run_group_rt<C0, G>(v, P, ts, rvs, row, c);
+    } else {
     if constexpr (I == 0)
         feed_group<TapsT, 0, C0, G>(ts, v, (int)c);
     if constexpr (I < ChainT::n) {
@@ -217,6 +406,7 @@ __device__ __forceinline__ void run_group(double (&v)[G], const FusedProgram &P,
         feed_group<TapsT, I + 1, C0, G>(ts, v, (int)c);
         run_group<ChainT, TapsT, C0, G, I + 1>(v, P, cs, ts, rvs, row, c);
     }
+    } // compiled chain
 }
 
 template <typename ChainT, int I = 0>
@@ -373,6 +563,10 @@ __global__ void __launch_bounds__(RT, 3) fused_row_ct_kernel(const __grid_consta
             }
         }
     }
+    if constexpr (std::is_same<ChainT, AnyChain>::value) {
+        if (tid < P.nsteps && P.steps[tid].kind == FK_SCALAR)
+            rvs[P.smem_elems + tid] = div_helper(P.steps[tid].imm);
+    }
     ChainState<ChainT> cs;
     init_scalar_aux<ChainT>(cs, P);
     __syncthreads(); // the only block-wide barrier: from here on every warp runs on its own
@@ -424,7 +618,10 @@ __global__ void __launch_bounds__(RT, 3) fused_row_ct_kernel(const __grid_consta
         const int cw = (cols - cc < CK) ? (int)(cols - cc) : CK;
         const bool live = lane < rows_here;
         if (ch == 0) {
-            init_taps<TapsT>(ts);
+            if constexpr (std::is_same<TapsT, AnyTaps>::value)
+                init_taps_rt(ts, P);
+            else
+                init_taps<TapsT>(ts);
             if (live)
                 load_colvec_aux<ChainT>(cs, P, row);
         }
@@ -445,8 +642,12 @@ __global__ void __launch_bounds__(RT, 3) fused_row_ct_kernel(const __grid_consta
                 }
             }
         }
-        if (ch == nchunks - 1 && live)
-            write_taps<TapsT>(ts, P, row);
+        if (ch == nchunks - 1 && live) {
+            if constexpr (std::is_same<TapsT, AnyTaps>::value)
+                write_taps_rt(ts, P, row);
+            else
+                write_taps<TapsT>(ts, P, row);
+        }
         __syncwarp(); // every lane is done with this buffer before the next iteration refills it
         t = tn;
         ch = chn;
@@ -455,7 +656,7 @@ __global__ void __launch_bounds__(RT, 3) fused_row_ct_kernel(const __grid_consta
 }
 
 template <typename ChainT, typename TapsT, bool EW> static int launch_row(const FusedProgram &prog, cudaStream_t st) {
-    const size_t smem = (size_t)(WARPS * 2 * WR * CK + prog.smem_elems) * sizeof(double) + 256; // + alignment slack
+    const size_t smem = (size_t)(WARPS * 2 * WR * CK + prog.smem_elems + FUSED_MAX_STEPS) * sizeof(double) + 256; // + scalar helpers, alignment slack
     const int64_t nblocks = ((prog.rows + WR - 1) / WR + WARPS - 1) / WARPS;
     const int64_t cap = (int64_t)sm_count() * 3;
     const int grid = (int)(nblocks < cap ? nblocks : cap);
@@ -660,7 +861,10 @@ bool fused_row_pass_ct(const FusedProgram &P, const char *signature, cudaStream_
             *rc = e.launch(P, st);
             return true;
         }
-    return false;
+    // not in the table: the same kernel with the chain read at run time
+    *rc = P.ew_out ? ct::launch_row<ct::AnyChain, ct::AnyTaps, true>(P, st)
+                   : ct::launch_row<ct::AnyChain, ct::AnyTaps, false>(P, st);
+    return true;
 }
 
 bool fused_col_pass_ct(const FusedProgram &P, const char *signature, int agg_op, void *res, void *scratch,
