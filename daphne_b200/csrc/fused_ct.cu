@@ -730,6 +730,27 @@ __global__ void __launch_bounds__(CT_THREADS)
         const double *base = static_cast<const double *>(P.base);
         const int64_t stride = (int64_t)gridDim.x * TY;
         int64_t r = (int64_t)blockIdx.x * TY + ty;
+        // four rows in flight per thread (the pass is bound by memory latency); the adds keep the row order
+        for (; r + 3 * stride < rows; r += 4 * stride) {
+            Pack<double> p[4];
+#pragma unroll
+            for (int u = 0; u < 4; u++)
+                p[u] = ld_pack_stream(base + (r + u * stride) * P.base_ld + c0);
+            double v0[4], v1[4];
+#pragma unroll
+            for (int u = 0; u < 4; u++) {
+                v0[u] = col_chain<ChainT>(p[u].v[0], 0, rv, ry, P, r + u * stride, c0);
+                v1[u] = col_chain<ChainT>(p[u].v[1], 1, rv, ry, P, r + u * stride, c0 + 1);
+            }
+            a0 = __dadd_rn(a0, v0[0]);
+            a1 = __dadd_rn(a1, v1[0]);
+            b0 = __dadd_rn(b0, v0[1]);
+            b1 = __dadd_rn(b1, v1[1]);
+            a0 = __dadd_rn(a0, v0[2]);
+            a1 = __dadd_rn(a1, v1[2]);
+            b0 = __dadd_rn(b0, v0[3]);
+            b1 = __dadd_rn(b1, v1[3]);
+        }
         for (; r + stride < rows; r += 2 * stride) {
             const Pack<double> p = ld_pack_stream(base + r * P.base_ld + c0);
             const Pack<double> q = ld_pack_stream(base + (r + stride) * P.base_ld + c0);
