@@ -187,12 +187,15 @@ __device__ __forceinline__ void apply_step_rt(int op, bool rev, double (&v)[G], 
 #undef DB2_CT_STEP
 }
 
-template <bool C0, int G>
-__device__ __forceinline__ void feed_rt(TapState<AnyTaps> &ts, const FusedProgram &P, int after, const double (&v)[G],
+// `mask`: bit a = tap a sees the values after this step (prepared once per CTA, see the kernel)
+template <int G>
+__device__ __forceinline__ void feed_rt(TapState<AnyTaps> &ts, const FusedProgram &P, unsigned mask, const double (&v)[G],
                                         int c0) {
+    if (mask == 0)
+        return;
 #pragma unroll
     for (int a = 0; a < FUSED_MAX_AGGS; a++) {
-        if (a < P.ntaps && P.taps[a].after_step == after) {
+        if (mask & (1u << a)) {
             const int kind = P.taps[a].kind;
             if (kind == FT_SUM || kind == FT_MEAN) {
 #pragma unroll
@@ -203,9 +206,8 @@ __device__ __forceinline__ void feed_rt(TapState<AnyTaps> &ts, const FusedProgra
                 for (int i = 0; i < G; i++)
                     ts.v[a] = __dmul_rn(ts.v[a], v[i]);
             } else {
-                if constexpr (C0)
-                    if (c0 == 0)
-                        ts.first[a] = v[0];
+                if (c0 == 0)
+                    ts.first[a] = v[0];
                 const bool mx = kind == FT_MAX;
 #pragma unroll
                 for (int i = 0; i < G; i++) {
@@ -251,16 +253,19 @@ __device__ __forceinline__ void write_taps_rt(const TapState<AnyTaps> &ts, const
     }
 }
 
-template <bool C0, int G>
+// scalar helpers and tap masks of a run-time chain sit behind the staged row vectors:
+//   rvs[smem_elems + s]                    division helper of step s (SCALAR operands)
+//   rvs[smem_elems + FUSED_MAX_STEPS + s]  (as bits) mask of the taps that follow s steps
+template <int G>
 __device__ __forceinline__ void run_group_rt(double (&v)[G], const FusedProgram &P, TapState<AnyTaps> &ts,
                                              const double *rvs, int64_t row, int64_t c) {
-    feed_rt<C0, G>(ts, P, 0, v, (int)c);
+    const unsigned *masks = reinterpret_cast<const unsigned *>(rvs + P.smem_elems + FUSED_MAX_STEPS);
+    feed_rt<G>(ts, P, masks[0], v, (int)c);
 #pragma unroll 1
     for (int s = 0; s < P.nsteps; s++) {
         const FusedStep &fs = P.steps[s];
         const bool fwd_div = fs.op == FO_DIV && !fs.reversed;
-        const double nan = __longlong_as_double(0x7ff8000000000000ll);
-        double o[G], y[G];
+        double o[G];
         if (fs.kind == FK_ROWVEC) {
             const double2 *ov = reinterpret_cast<const double2 *>(rvs + fs.smem_off + c);
 #pragma unroll
@@ -269,7 +274,21 @@ __device__ __forceinline__ void run_group_rt(double (&v)[G], const FusedProgram 
                 o[2 * i] = t.x;
                 o[2 * i + 1] = t.y;
             }
-            if (fwd_div) {
+        } else if (fs.kind == FK_MATRIX) {
+            const double *mp = static_cast<const double *>(fs.ptr) + row * fs.ld + c;
+#pragma unroll
+            for (int i = 0; i < G; i++)
+                o[i] = __ldg(mp + i);
+        } else {
+            const double ov =
+                fs.kind == FK_COLVEC ? __ldg(static_cast<const double *>(fs.ptr) + row * fs.ld) : fs.imm; // or UNARY
+#pragma unroll
+            for (int i = 0; i < G; i++)
+                o[i] = ov;
+        }
+        if (fwd_div) {
+            double y[G];
+            if (fs.kind == FK_ROWVEC) {
                 const double2 *yv = reinterpret_cast<const double2 *>(rvs + fs.smem_off + P.cols + c);
 #pragma unroll
                 for (int i = 0; i < G / 2; i++) {
@@ -277,27 +296,13 @@ __device__ __forceinline__ void run_group_rt(double (&v)[G], const FusedProgram 
                     y[2 * i] = u.x;
                     y[2 * i + 1] = u.y;
                 }
-            }
-        } else if (fs.kind == FK_MATRIX) {
-            const double *mp = static_cast<const double *>(fs.ptr) + row * fs.ld + c;
+            } else {
+                // SCALAR: the staged helper; anything else: NaN = generic division
+                const double yv = fs.kind == FK_SCALAR ? rvs[P.smem_elems + s] : __longlong_as_double(0x7ff8000000000000ll);
 #pragma unroll
-            for (int i = 0; i < G; i++) {
-                o[i] = __ldg(mp + i);
-                y[i] = nan;
+                for (int i = 0; i < G; i++)
+                    y[i] = yv;
             }
-        } else {
-            double ov = fs.imm, yv = nan; // SCALAR (helper staged behind the row vectors), UNARY
-            if (fs.kind == FK_SCALAR)
-                yv = rvs[P.smem_elems + s];
-            else if (fs.kind == FK_COLVEC)
-                ov = __ldg(static_cast<const double *>(fs.ptr) + row * fs.ld);
-#pragma unroll
-            for (int i = 0; i < G; i++) {
-                o[i] = ov;
-                y[i] = yv;
-            }
-        }
-        if (fwd_div) {
             double q1[G];
             unsigned worst = 0;
 #pragma unroll
@@ -319,7 +324,7 @@ __device__ __forceinline__ void run_group_rt(double (&v)[G], const FusedProgram 
         } else {
             apply_step_rt<G>(fs.op, fs.reversed != 0, v, o);
         }
-        feed_rt<C0, G>(ts, P, s + 1, v, (int)c);
+        feed_rt<G>(ts, P, masks[s + 1], v, (int)c);
     }
 }
 
@@ -340,7 +345,7 @@ template <typename ChainT, typename TapsT, bool C0, int G, int I = 0>
 __device__ __forceinline__ void run_group(double (&v)[G], const FusedProgram &P, const ChainState<ChainT> &cs,
                                           TapState<TapsT> &ts, const double *rvs, int64_t row, int64_t c) {
     if constexpr (std::is_same<ChainT, AnyChain>::value) {
-        run_group_rt<C0, G>(v, P, ts, rvs, row, c);
+        run_group_rt<G>(v, P, ts, rvs, row, c);
     } else {
     if constexpr (I == 0)
         feed_group<TapsT, 0, C0, G>(ts, v, (int)c);
@@ -566,6 +571,13 @@ __global__ void __launch_bounds__(RT, 3) fused_row_ct_kernel(const __grid_consta
     if constexpr (std::is_same<ChainT, AnyChain>::value) {
         if (tid < P.nsteps && P.steps[tid].kind == FK_SCALAR)
             rvs[P.smem_elems + tid] = div_helper(P.steps[tid].imm);
+        if (tid <= P.nsteps) { // which taps follow `tid` steps
+            unsigned mask = 0;
+            for (int a = 0; a < P.ntaps; a++)
+                if (P.taps[a].after_step == tid)
+                    mask |= 1u << a;
+            reinterpret_cast<unsigned *>(rvs + P.smem_elems + FUSED_MAX_STEPS)[tid] = mask;
+        }
     }
     ChainState<ChainT> cs;
     init_scalar_aux<ChainT>(cs, P);
@@ -656,7 +668,7 @@ __global__ void __launch_bounds__(RT, 3) fused_row_ct_kernel(const __grid_consta
 }
 
 template <typename ChainT, typename TapsT, bool EW> static int launch_row(const FusedProgram &prog, cudaStream_t st) {
-    const size_t smem = (size_t)(WARPS * 2 * WR * CK + prog.smem_elems + FUSED_MAX_STEPS) * sizeof(double) + 256; // + scalar helpers, alignment slack
+    const size_t smem = (size_t)(WARPS * 2 * WR * CK + prog.smem_elems + 2 * FUSED_MAX_STEPS) * sizeof(double) + 256; // + run-time chain tables, alignment slack
     const int64_t nblocks = ((prog.rows + WR - 1) / WR + WARPS - 1) / WARPS;
     const int64_t cap = (int64_t)sm_count() * 3;
     const int grid = (int)(nblocks < cap ? nblocks : cap);
