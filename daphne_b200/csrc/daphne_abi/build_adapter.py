@@ -1,6 +1,6 @@
 """Builds the DAPHNE-facing adapter library from a DAPHNE source tree.
 
-    python daphne_b200/csrc/daphne_abi/build_adapter.py [DAPHNE_SRC]      (default /root/reference)
+    python daphne_b200/csrc/daphne_abi/build_adapter.py [DAPHNE_SRC]
 
 Steps:
   1. the tree's own kernels.json is filtered to the kernel templates this library implements for the CUDA backend

@@ -18,7 +18,7 @@ from pathlib import Path
 
 FILES = ["AggRowTest.cpp", "AggColTest.cpp", "AggAllTest.cpp", "EwBinaryMatTest.cpp", "EwBinaryObjScaTest.cpp",
          "EwUnaryMatTest.cpp", "SyrkTest.cpp", "GemvTest.cpp", "MatMulTest.cpp", "SolveTest.cpp", "CTableTest.cpp",
-         "TransposeTest.cpp"]
+         "TransposeTest.cpp", "DiagMatrixTest.cpp"]
 
 SCOPE_RE = re.compile(r"^\s*(TEMPLATE_PRODUCT_TEST_CASE|TEMPLATE_TEST_CASE|TEST_CASE|#define\s+\w+TEST_CASE\w*)\b")
 GEN_RE = re.compile(r"(?:auto|\w+\s*\*)\s*(\w+)\s*=\s*genGivenVals<([^>]*(?:<[^>]*>)?[^>]*)>\(\s*(\w+)\s*,\s*\{(.*?)\}\s*\)\s*;",
@@ -179,7 +179,36 @@ def extract(root: Path):
                         cases.append({"file": f"test/runtime/local/kernels/{fname}", "line": line,
                                       "test": sm.group(1)[:120], "check": "transposeSection", "op": None,
                                       "args": [local["m"], local["mt"]]})
+    cases += _extract_seq(root)
     return cases, skipped
+
+
+SEQ_RE = re.compile(r"(\w+)\s*=\s*genGivenVals<DT>\(\s*(\d+)\s*,\s*\{(.*?)\}\s*\)\s*;\s*checkSeq\(\s*\w+\s*,([^;]*?),\s*\1\s*\)\s*;",
+                    re.S)
+
+
+def _extract_seq(root: Path):
+    """SeqTest.cpp assigns the expected column to a variable declared earlier and checks it right away:
+    targetMatrix = genGivenVals<DT>(n, {...}); checkSeq(inputMatrix, start, end, inc, targetMatrix);"""
+    path = root / "test/runtime/local/kernels/SeqTest.cpp"
+    if not path.exists():
+        return []
+    text = _clean(path.read_text())
+    out = []
+    for m in SEQ_RE.finditer(text):
+        _, nrows, body, scal = m.groups()
+        try:
+            vals = _split_values(body)
+            sc = [_value(t) for t in scal.split(",")]
+        except ValueError:
+            continue
+        if len(sc) != 3:
+            continue
+        out.append({"file": "test/runtime/local/kernels/SeqTest.cpp", "line": text.count("\n", 0, m.start()) + 1,
+                    "test": "Seq", "check": "checkSeq", "op": None,
+                    "args": [{"scalar": _enc(v)} for v in sc] +
+                            [{"matrix": "targetMatrix", "dt": "DT", "rows": int(nrows), "values": [_enc(v) for v in vals]}]})
+    return out
 
 
 if __name__ == "__main__":

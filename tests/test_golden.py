@@ -1,7 +1,7 @@
 """Known-answer cases of the reference's own unit tests (tests/golden/reference_cases.json, extracted from
 test/runtime/local/kernels/*Test.cpp by tests/golden/extract_reference_cases.py), run against the CPU oracle (always)
 and against the CUDA library (on a GPU).  Tolerances are the ones the reference's tests use: exact for elementwise
-results, matMul, syrk, ctable and transpose (small integer-valued literals, `*res == *exp`), 1e-5 absolute for
+results, matMul, syrk, ctable, seq, diagMatrix and transpose (small integer-valued literals, `*res == *exp`), 1e-5 absolute for
 aggregations (checkEqApprox in AggRowTest.cpp:38), 1e-2 for the *Approx unary checks (EwUnaryMatTest.cpp:48), 1e-6
 for solve (SolveTest.cpp:39)."""
 import json
@@ -20,7 +20,7 @@ AGG = {n: i for i, n in enumerate(["SUM", "PROD", "MIN", "MAX", "IDXMIN", "IDXMA
 
 DENSE_CHECKS = {"checkAggRow", "checkAggCol", "checkAggAll", "checkEwBinaryMat", "checkEwUnaryMat",
                 "checkEwUnaryMatApprox", "checkEwUnaryMatThrow", "checkEwBinaryObjSca", "checkMatMul", "checkSyrk",
-                "solveNormalEquations", "ctableSection", "transposeSection"}
+                "solveNormalEquations", "ctableSection", "transposeSection", "checkSeq", "checkDiagMatrix"}
 
 
 def _num(v):
@@ -68,6 +68,8 @@ class _OracleBackend:
     def transpose(self, a): return self.o.transpose(a)
     def solve(self, a, b): return self.o.solve(a, b)
     def ctable(self, ys, xs, w, nr, nc): return self.o.ctable(ys, xs, w, nr, nc)
+    def seq(self, start, end, inc): return self.o.seq(start, end, inc)
+    diag = None  # DiagMatrix has no restatement in the oracle: a diagonal copy, checked on the device only
 
 
 class _CudaBackend:
@@ -92,6 +94,9 @@ class _CudaBackend:
 
     def ctable(self, ys, xs, w, nr, nc):
         return self.k.ctable(self._m(ys.astype(np.int64)), self._m(xs.astype(np.int64)), w, nr, nc).to_numpy()
+
+    def seq(self, start, end, inc): return self.k.seq(self.ctx, start, end, inc).to_numpy()
+    def diag(self, a): return self.k.diagMatrix(self._m(a)).to_numpy()
 
 
 def _run_case(be, c):
@@ -147,6 +152,16 @@ def _run_case(be, c):
         w, nr, nc = (_num(a["scalar"]) for a in args[2:5])
         got = be.ctable(ys.reshape(-1, 1), xs.reshape(-1, 1), float(w), int(nr), int(nc))
         assert got.shape == exp.shape and np.array_equal(got, exp), f"{c['file']}:{c['line']}"
+    elif chk == "checkSeq":  # SeqTest.cpp:26-29: a column vector start, start + inc, ..., end
+        start, end, inc = (float(_num(a["scalar"])) for a in args[:3])
+        exp = _mat(args[3])
+        got = np.asarray(be.seq(start, end, inc), dtype=np.float64)
+        assert got.shape == exp.shape and np.array_equal(got, exp), f"{c['file']}:{c['line']}"
+    elif chk == "checkDiagMatrix":  # DiagMatrixTest.cpp:30-35
+        if be.diag is not None:
+            arg, exp = _mat(args[0]), _mat(args[1])
+            got = be.diag(arg)
+            assert got.shape == exp.shape and np.array_equal(got, exp), f"{c['file']}:{c['line']}"
     elif chk == "transposeSection":
         m, mt = _mat(args[0]), _mat(args[1])
         assert np.array_equal(be.transpose(m), mt), f"{c['file']}:{c['line']}"

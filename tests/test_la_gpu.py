@@ -161,6 +161,18 @@ def test_transpose_fill_seq_diag_cast(ctx):
     assert_bits_equal(k.castObj(k.DenseMatrix.from_numpy(ctx, u), np.int64).to_numpy(), u.astype(np.int64), "cast")
 
 
+def test_fill_shapes_and_values_of_the_reference_test(ctx):
+    """FillTest.cpp:41-92: empty, vector and rectangular shapes, a zero and a non-zero value, several value types."""
+    k, o = _k()
+    shapes = [(0, 0), (0, 1), (0, 5), (1, 0), (5, 0), (1, 1), (1, 5), (1, 1000), (5, 1), (1000, 1), (3, 4), (1000, 1000)]
+    for dtype in (np.float64, np.int64, np.float32):
+        for rows, cols in shapes:
+            for value in (0, 2.5):
+                got = k.fill(ctx, value, rows, cols, dtype=dtype).to_numpy()
+                exp = np.full((rows, cols), np.array([value]).astype(dtype)[0], dtype=dtype)
+                assert got.shape == exp.shape and got.dtype == exp.dtype and np.array_equal(got, exp), (dtype, rows, cols)
+
+
 def test_ctable(ctx):
     k, o = _k()
     rng = np.random.default_rng(9)
