@@ -4,7 +4,7 @@
 
 Steps:
   1. the tree's own kernels.json is filtered to the kernel templates this library implements for the CUDA backend
-     (the DNN operators and extractCol/colBind are left to DAPHNE's own library);
+     (the DNN operators are left to DAPHNE's own library);
   2. the tree's own generator (src/runtime/local/kernels/genKernelInst.py) emits the extern "C" wrappers and the
      catalog JSON for backend "CUDA" -- names, argument order and the kId/ctx tail are therefore exactly DAPHNE's;
   3. the wrappers are compiled against the tree's data-structure headers and the headers in include/ here, which carry
@@ -29,7 +29,7 @@ HERE = Path(__file__).resolve().parent
 PKG = HERE.parents[1]
 OUT = PKG / "_abi_build"
 SUPPORTED_HEADERS = {"AggAll.h", "AggCol.h", "AggRow.h", "EwBinaryMat.h", "EwBinaryObjSca.h", "MatMul.h", "Syrk.h",
-                     "Gemv.h", "Solve.h", "Transpose.h", "Fill.h", "CreateCUDAContext.h"}
+                     "Gemv.h", "Solve.h", "Transpose.h", "Fill.h", "CreateCUDAContext.h", "ColBind.h", "ExtractCol.h"}
 
 
 # backend-"CPP" extension: header -> opcodes to register (None: all of the entry's opcodes / no opcode)

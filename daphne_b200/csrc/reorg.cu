@@ -1,0 +1,171 @@
+// Reorganisation kernels: ColBind and ExtractCol.
+//
+// Both are pure copies (16 bytes of traffic per 8-byte element), so the only thing that matters is that every warp
+// moves whole rows with its lanes side by side (coalesced on both ends) and has several rows in flight:
+//   ColBind     res = [lhs | rhs]                 (src/runtime/local/kernels/ColBind.h:54-88; CUDA twin CUDA/ColBind.cu:24-44,
+//                                                  one element per thread with a 32-bit index)
+//   ExtractCol  res[:, c] = arg[:, sel[c]]        (src/runtime/local/kernels/ExtractCol.h:64-105; CUDA twin
+//                                                  CUDA/ExtractCol.cu:22-30)
+// A warp owns rows r, r + W, ... (W = warps in the grid) and walks four of them at a time; lane l copies the columns
+// l, l + 32, ...  The column selection of ExtractCol is validated on the host (negative positions count from the end,
+// anything outside [0, cols) is the reference's out_of_range error) and handed to the kernel as resolved positions.
+#include "runtime.h"
+
+#include <string>
+#include <vector>
+
+namespace db2 {
+
+constexpr int RG_THREADS = 256, RG_ROWS = 4;
+
+template <typename VT>
+__global__ void __launch_bounds__(RG_THREADS)
+    col_bind_kernel(const VT *__restrict__ lhs, int64_t ld_l, int64_t cols_l, const VT *__restrict__ rhs, int64_t ld_r,
+                    int64_t cols_r, int64_t rows, VT *__restrict__ res, int64_t ld_o) {
+    const int lane = threadIdx.x % 32;
+    const int64_t warp = ((int64_t)blockIdx.x * RG_THREADS + threadIdx.x) / 32;
+    const int64_t nwarps = (int64_t)gridDim.x * (RG_THREADS / 32);
+    const int64_t cols = cols_l + cols_r;
+    for (int64_t r0 = warp * RG_ROWS; r0 < rows; r0 += nwarps * RG_ROWS) {
+        for (int64_t c = lane; c < cols; c += 32) {
+            VT v[RG_ROWS];
+#pragma unroll
+            for (int u = 0; u < RG_ROWS; u++)
+                if (r0 + u < rows)
+                    v[u] = c < cols_l ? lhs[(r0 + u) * ld_l + c] : rhs[(r0 + u) * ld_r + (c - cols_l)];
+#pragma unroll
+            for (int u = 0; u < RG_ROWS; u++)
+                if (r0 + u < rows)
+                    res[(r0 + u) * ld_o + c] = v[u];
+        }
+    }
+}
+
+template <typename VT>
+__global__ void __launch_bounds__(RG_THREADS)
+    extract_col_kernel(const VT *__restrict__ arg, int64_t ld, int64_t rows, const int64_t *__restrict__ pos,
+                       int64_t nsel, VT *__restrict__ res, int64_t ld_o) {
+    const int lane = threadIdx.x % 32;
+    const int64_t warp = ((int64_t)blockIdx.x * RG_THREADS + threadIdx.x) / 32;
+    const int64_t nwarps = (int64_t)gridDim.x * (RG_THREADS / 32);
+    for (int64_t r0 = warp * RG_ROWS; r0 < rows; r0 += nwarps * RG_ROWS) {
+        for (int64_t c = lane; c < nsel; c += 32) {
+            const int64_t p = pos[c];
+            VT v[RG_ROWS];
+#pragma unroll
+            for (int u = 0; u < RG_ROWS; u++)
+                if (r0 + u < rows)
+                    v[u] = arg[(r0 + u) * ld + p];
+#pragma unroll
+            for (int u = 0; u < RG_ROWS; u++)
+                if (r0 + u < rows)
+                    res[(r0 + u) * ld_o + c] = v[u];
+        }
+    }
+}
+
+static void count(db2_context *ctx, uint64_t before) {
+    std::lock_guard<std::mutex> lock(ctx->mu);
+    ctx->stats.launches += g_launches.load(std::memory_order_relaxed) - before;
+}
+
+static int reorg_grid(int64_t rows) {
+    const int64_t want = (rows + (RG_THREADS / 32) * RG_ROWS - 1) / ((RG_THREADS / 32) * RG_ROWS);
+    const int64_t cap = (int64_t)sm_count() * 8;
+    return (int)(want < 1 ? 1 : (want < cap ? want : cap));
+}
+
+} // namespace db2
+
+using namespace db2;
+
+extern "C" {
+
+int db2k_col_bind(int dtype, const void *lhs, int64_t lhs_ld, int64_t lhs_cols, const void *rhs, int64_t rhs_ld,
+                  int64_t rhs_cols, int64_t rows, void *res, int64_t res_ld, void *stream) {
+    DB2_CHECK(rows >= 0 && lhs_cols >= 0 && rhs_cols >= 0, DB2_EINVAL, "negative shape");
+    if (rows == 0 || lhs_cols + rhs_cols == 0)
+        return DB2_OK;
+    const int grid = reorg_grid(rows);
+    DB2_DISPATCH_DTYPE(dtype, VT,
+                       (col_bind_kernel<VT><<<grid, RG_THREADS, 0, as_stream(stream)>>>(
+                           static_cast<const VT *>(lhs), lhs_ld, lhs_cols, static_cast<const VT *>(rhs), rhs_ld,
+                           rhs_cols, rows, static_cast<VT *>(res), res_ld)));
+    return after_launch("col_bind_kernel");
+}
+
+int db2k_extract_col(int dtype, const void *arg, int64_t ld, int64_t rows, const void *dev_positions, int64_t nsel,
+                     void *res, int64_t res_ld, void *stream) {
+    DB2_CHECK(rows >= 0 && nsel >= 0, DB2_EINVAL, "negative shape");
+    if (rows == 0 || nsel == 0)
+        return DB2_OK;
+    const int grid = reorg_grid(rows);
+    DB2_DISPATCH_DTYPE(dtype, VT,
+                       (extract_col_kernel<VT><<<grid, RG_THREADS, 0, as_stream(stream)>>>(
+                           static_cast<const VT *>(arg), ld, rows, static_cast<const int64_t *>(dev_positions), nsel,
+                           static_cast<VT *>(res), res_ld)));
+    return after_launch("extract_col_kernel");
+}
+
+int db2_colBind(db2_context *ctx, db2_matrix **res, db2_matrix *lhs, db2_matrix *rhs) {
+    DB2_API_BEGIN
+    DB2_CHECK(ctx && res && lhs && rhs, DB2_EINVAL, "null argument");
+    DB2_CHECK(lhs->dtype == rhs->dtype, DB2_EUNSUPPORTED, "ColBind: operands of different value types");
+    DB2_CHECK(lhs->rows == rhs->rows, DB2_EINVAL,
+              "ColBind - the two operands must have the same number of rows, but lhs has %lld and rhs has %lld rows",
+              (long long)lhs->rows, (long long)rhs->rows);
+    bind_device(ctx);
+    const uint64_t before = g_launches.load();
+    DB2_TRY(ensure_device(lhs));
+    DB2_TRY(ensure_device(rhs));
+    DB2_TRY(prepare_result(ctx, res, lhs->dtype, lhs->rows, lhs->cols + rhs->cols));
+    DB2_TRY(db2k_col_bind(lhs->dtype, lhs->dev_ptr(), lhs->dev_ld, lhs->cols, rhs->dev_ptr(), rhs->dev_ld, rhs->cols,
+                          lhs->rows, (*res)->dev_ptr(), (*res)->dev_ld, ctx->stream));
+    count(ctx, before);
+    return DB2_OK;
+    DB2_API_END
+}
+
+int db2_extractCol(db2_context *ctx, db2_matrix **res, db2_matrix *arg, db2_matrix *sel) {
+    DB2_API_BEGIN
+    DB2_CHECK(ctx && res && arg && sel, DB2_EINVAL, "null argument");
+    DB2_CHECK(sel->dtype == DB2_I64, DB2_EUNSUPPORTED, "ExtractCol: the column selection must be an int64 matrix");
+    DB2_CHECK(sel->cols == 1, DB2_EINVAL,
+              "invalid argument passed to ExtractCol: column selection must be given as column matrix but has '%lld' "
+              "columns instead of one",
+              (long long)sel->cols);
+    bind_device(ctx);
+    const uint64_t before = g_launches.load();
+    // the selection is small: it is validated on the host, with the reference's rules and message
+    const int64_t nsel = sel->rows;
+    std::vector<int64_t> pos((size_t)nsel);
+    if (nsel > 0)
+        DB2_TRY(db2_matrix_to_host(sel, pos.data(), 1));
+    for (int64_t c = 0; c < nsel; c++) {
+        const int64_t given = pos[(size_t)c];
+        int64_t p = given;
+        if (p < 0)
+            p += arg->cols;
+        DB2_CHECK(p >= 0 && p < arg->cols, DB2_EDOMAIN,
+                  "invalid argument '%lld' passed to ExtractCol: out of bounds for dense matrix with column boundaries "
+                  "'[0, %lld)'",
+                  (long long)given, (long long)arg->cols);
+        pos[(size_t)c] = p;
+    }
+    DB2_TRY(ensure_device(arg));
+    DB2_TRY(prepare_result(ctx, res, arg->dtype, arg->rows, nsel));
+    if (arg->rows > 0 && nsel > 0) {
+        void *dev_pos = nullptr;
+        DB2_TRY(ctx_scratch(ctx, (size_t)nsel * 8, &dev_pos));
+        DB2_CUDA(cudaMemcpyAsync(dev_pos, pos.data(), (size_t)nsel * 8, cudaMemcpyHostToDevice, ctx->stream));
+        DB2_TRY(db2k_extract_col(arg->dtype, arg->dev_ptr(), arg->dev_ld, arg->rows, dev_pos, nsel, (*res)->dev_ptr(),
+                                 (*res)->dev_ld, ctx->stream));
+        // `pos` is pageable host memory: the copy above has consumed it when the call returns
+        DB2_CUDA(cudaStreamSynchronize(ctx->stream));
+    }
+    count(ctx, before);
+    return DB2_OK;
+    DB2_API_END
+}
+
+} // extern "C"

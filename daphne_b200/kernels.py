@@ -270,6 +270,22 @@ def diagMatrix(arg: DenseMatrix, ctx: Optional[Context] = None) -> DenseMatrix:
     return _res(ctx, h)
 
 
+def colBind(lhs: DenseMatrix, rhs: DenseMatrix, ctx: Optional[Context] = None) -> DenseMatrix:
+    """ColBind.h:41-44: [lhs | rhs]."""
+    ctx = ctx or lhs.ctx
+    h = C.c_void_p()
+    check(lib.db2_colBind(ctx.handle, C.byref(h), lhs.handle, rhs.handle))
+    return _res(ctx, h)
+
+
+def extractCol(arg: DenseMatrix, sel: DenseMatrix, ctx: Optional[Context] = None) -> DenseMatrix:
+    """ExtractCol.h:45-48: the columns of arg at the positions in the int64 column matrix sel."""
+    ctx = ctx or arg.ctx
+    h = C.c_void_p()
+    check(lib.db2_extractCol(ctx.handle, C.byref(h), arg.handle, sel.handle))
+    return _res(ctx, h)
+
+
 def readDaphne(ctx: Context, path) -> DenseMatrix:
     """ReadDaphne.h:44-46: a dense matrix from a .dbdf file, streamed straight into its device placement."""
     h = C.c_void_p()

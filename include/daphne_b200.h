@@ -193,6 +193,16 @@ int db2k_fill(int dtype, void *res, int64_t rows, int64_t cols, int64_t ld, cons
 int db2k_seq(int dtype, void *res, int64_t n, const void *start, const void *inc, void *stream);
 /* n x n matrix with vec on its diagonal (DiagMatrix<Dense,Dense>, src/runtime/local/kernels/DiagMatrix.h:55-78). */
 int db2k_diag_matrix(int dtype, const void *vec, int64_t vec_ld, int64_t n, void *res, int64_t res_ld, void *stream);
+/* res (rows x (lhs_cols + rhs_cols)) = [lhs | rhs].  Replaces ColBind<Dense,Dense,Dense>
+ * (src/runtime/local/kernels/ColBind.h:54-88; CUDA twin kernels/CUDA/ColBind.cu:24-75). */
+int db2k_col_bind(int dtype, const void *lhs, int64_t lhs_ld, int64_t lhs_cols, const void *rhs, int64_t rhs_ld,
+                  int64_t rhs_cols, int64_t rows, void *res, int64_t res_ld, void *stream);
+/* res[:, c] = arg[:, positions[c]] for c < nsel; `dev_positions` are nsel int64 column positions on the device,
+ * already resolved and inside [0, cols) (the caller validates them, see db2_extractCol).  Replaces
+ * ExtractCol<Dense,Dense,Dense<int64>> (src/runtime/local/kernels/ExtractCol.h:64-105; CUDA twin
+ * kernels/CUDA/ExtractCol.cu:22-66). */
+int db2k_extract_col(int dtype, const void *arg, int64_t ld, int64_t rows, const void *dev_positions, int64_t nsel,
+                     void *res, int64_t res_ld, void *stream);
 /* maximum of an int64 vector into a device int64 (used to size ctable results like CTable.h:79-84 does) */
 int db2k_max_i64(const void *vec, int64_t ld, int64_t n, void *dev_out, void *stream);
 /* Contingency table res[lhs[i], rhs[i]] += weight over int64 coordinate vectors (f64 result, overwritten).
@@ -291,6 +301,11 @@ int db2_transpose(db2_context *ctx, db2_matrix **res, db2_matrix *arg);
 int db2_fill(db2_context *ctx, db2_matrix **res, int dtype, const void *value, int64_t rows, int64_t cols);
 int db2_seq(db2_context *ctx, db2_matrix **res, int dtype, const void *start, const void *end, const void *inc);
 int db2_diagMatrix(db2_context *ctx, db2_matrix **res, db2_matrix *arg);
+/* [lhs | rhs]; DB2_EINVAL with the reference's message when the row counts differ (ColBind.h:58-63) */
+int db2_colBind(db2_context *ctx, db2_matrix **res, db2_matrix *lhs, db2_matrix *rhs);
+/* the columns of arg named by the int64 column matrix sel; negative positions count from the end, anything outside
+ * [0, cols) is DB2_EDOMAIN with the reference's out_of_range message (ExtractCol.h:84-96) */
+int db2_extractCol(db2_context *ctx, db2_matrix **res, db2_matrix *arg, db2_matrix *sel);
 /* res_rows / res_cols < 0: derived from the largest coordinate (synchronises) */
 int db2_ctable(db2_context *ctx, db2_matrix **res, db2_matrix *lhs, db2_matrix *rhs, double weight,
                int64_t res_rows, int64_t res_cols);

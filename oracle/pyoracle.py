@@ -216,6 +216,39 @@ def seq(start, end, inc):
     return _seq(_lib, "orc", start, end, inc)
 
 
+def colBind(lhs, rhs) -> np.ndarray:
+    """ColBind<Dense,Dense,Dense> (src/runtime/local/kernels/ColBind.h:54-88): row r of the result is row r of lhs
+    followed by row r of rhs; operands with different row counts are an error."""
+    lhs, rhs = _mat(lhs), _mat(rhs)
+    if lhs.shape[0] != rhs.shape[0]:
+        raise OracleError(f"ColBind - the two operands must have the same number of rows, but lhs has {lhs.shape[0]} "
+                          f"and rhs has {rhs.shape[0]} rows")
+    res = np.empty((lhs.shape[0], lhs.shape[1] + rhs.shape[1]), dtype=lhs.dtype)
+    for r in range(lhs.shape[0]):
+        res[r, : lhs.shape[1]] = lhs[r]
+        res[r, lhs.shape[1]:] = rhs[r]
+    return res
+
+
+def extractCol(arg, sel) -> np.ndarray:
+    """ExtractCol<Dense,Dense,Dense<VTSel>> (src/runtime/local/kernels/ExtractCol.h:64-105): sel is a column matrix of
+    column positions; a negative position counts from the end; anything outside [0, cols) is out_of_range."""
+    arg, sel = _mat(arg), np.asarray(sel)
+    if sel.ndim != 2 or sel.shape[1] != 1:
+        raise OracleError("invalid argument passed to ExtractCol: column selection must be given as column matrix but "
+                          f"has '{sel.shape[1] if sel.ndim == 2 else '?'}' columns instead of one")
+    cols = arg.shape[1]
+    res = np.empty((arg.shape[0], sel.shape[0]), dtype=arg.dtype)
+    for c in range(sel.shape[0]):
+        given = int(sel[c, 0])
+        p = given + cols if given < 0 else given
+        if p < 0 or p >= cols:
+            raise OracleError(f"invalid argument '{given}' passed to ExtractCol: out of bounds for dense matrix with "
+                              f"column boundaries '[0, {cols})'")
+        res[:, c] = arg[:, p]
+    return res
+
+
 def _csr_arrays(m):
     """(values f64, colIdxs u64, rowOffsets u64, rows, cols) from a scipy CSR matrix or an equivalent tuple."""
     if isinstance(m, tuple):

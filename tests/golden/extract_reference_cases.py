@@ -180,7 +180,58 @@ def extract(root: Path):
                                       "test": sm.group(1)[:120], "check": "transposeSection", "op": None,
                                       "args": [local["m"], local["mt"]]})
     cases += _extract_seq(root)
+    cases += _extract_reorg(root)
     return cases, skipped
+
+
+def _extract_reorg(root: Path):
+    """ColBindTest.cpp ("ColBind": m0, m1, exp) and the dense part of ExtractColTest.cpp (one arg, a selection and an
+    expected matrix -- or an expected out_of_range -- per SECTION)."""
+    out = []
+    base = root / "test/runtime/local/kernels"
+    path = base / "ColBindTest.cpp"
+    if path.exists():
+        text = _clean(path.read_text())
+        a = text.find('TEMPLATE_PRODUCT_TEST_CASE("ColBind"')
+        b = text.find("TEST_CASE(", a + 40)
+        scope = text[a:b if b > a else len(text)]
+        mats = {}
+        for m in GEN_RE.finditer(scope):
+            name, dt, nrows, body = m.groups()
+            mats[name] = {"matrix": name, "dt": re.sub(r"\s+", "", dt), "rows": int(nrows),
+                          "values": [_enc(v) for v in _split_values(body)]}
+        if {"m0", "m1", "exp"} <= set(mats):
+            out.append({"file": "test/runtime/local/kernels/ColBindTest.cpp",
+                        "line": text.count("\n", 0, a + scope.find("colBind<")) + 1, "test": "ColBind",
+                        "check": "colBind", "op": None, "args": [mats["m0"], mats["m1"], mats["exp"]]})
+    path = base / "ExtractColTest.cpp"
+    if path.exists():
+        text = _clean(path.read_text())
+        a = text.find('TEST_NAME("Dense/Generic Matrix")')
+        scope = text[a:]
+        m = GEN_RE.search(scope)
+        if a >= 0 and m and m.group(1) == "arg":
+            arg = {"matrix": "arg", "dt": "DT", "rows": int(m.group(3)), "values": [_enc(v) for v in _split_values(m.group(4))]}
+            secs = list(SECTION_RE.finditer(scope))
+            for i, sm in enumerate(secs):
+                body = scope[sm.end(): secs[i + 1].start() if i + 1 < len(secs) else len(scope)]
+                local = {}
+                for am in ASSIGN_RE.finditer(body):
+                    name, dt, nrows, vals = am.groups()
+                    local[name] = {"matrix": name, "dt": "DT", "rows": int(nrows),
+                                   "values": [_enc(v) for v in _split_values(vals)]}
+                if "sel" not in local and "create<DTEmpty>(0, 1" in body:
+                    local["sel"] = {"matrix": "sel", "dt": "DT", "rows": 0, "values": []}
+                line = text.count("\n", 0, a + sm.start()) + 1
+                if "checkExtractColThrow" in body and "sel" in local:
+                    out.append({"file": "test/runtime/local/kernels/ExtractColTest.cpp", "line": line,
+                                "test": sm.group(1)[:120], "check": "extractColThrow", "op": None,
+                                "args": [arg, local["sel"]]})
+                elif "checkExtractCol(" in body and {"sel", "exp"} <= set(local):
+                    out.append({"file": "test/runtime/local/kernels/ExtractColTest.cpp", "line": line,
+                                "test": sm.group(1)[:120], "check": "extractCol", "op": None,
+                                "args": [arg, local["sel"], local["exp"]]})
+    return out
 
 
 SEQ_RE = re.compile(r"(\w+)\s*=\s*genGivenVals<DT>\(\s*(\d+)\s*,\s*\{(.*?)\}\s*\)\s*;\s*checkSeq\(\s*\w+\s*,([^;]*?),\s*\1\s*\)\s*;",

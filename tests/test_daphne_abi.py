@@ -33,7 +33,9 @@ def test_catalog_symbols_are_exported_with_the_reference_names():
                  "CUDA_gemv__DenseMatrix_double__DenseMatrix_double__DenseMatrix_double",
                  "CUDA_solve__DenseMatrix_double__DenseMatrix_double__DenseMatrix_double",
                  "CUDA_transpose__DenseMatrix_double__DenseMatrix_double",
-                 "CUDA_fill__DenseMatrix_double__double__size_t__size_t"):
+                 "CUDA_fill__DenseMatrix_double__double__size_t__size_t",
+                 "CUDA_colBind__DenseMatrix_double__DenseMatrix_double__DenseMatrix_double",
+                 "CUDA_extractCol__DenseMatrix_double__DenseMatrix_double__DenseMatrix_int64_t"):
         assert must in syms, must
     assert all(e["backend"] == "CUDA" and e["libPath"] == "libCUDAKernels.so" for e in cat)
 
@@ -131,6 +133,9 @@ def test_kernels_called_by_symbol_through_daphne_objects(drv):
     got = _call(drv, drv.drv_binary, b"CUDA_solve__DenseMatrix_double__DenseMatrix_double__DenseMatrix_double", _p(s),
                 i64(40), i64(40), _p(rhs), i64(40), i64(1))
     assert np.abs(got - o.solve(s, rhs)).max() <= 1e-9 * np.abs(o.solve(s, rhs)).max()
+    got = _call(drv, drv.drv_binary, b"CUDA_colBind__DenseMatrix_double__DenseMatrix_double__DenseMatrix_double", _p(a),
+                i64(3000), i64(40), _p(y), i64(3000), i64(1))
+    assert np.array_equal(got, np.hstack([a, y]))
 
 
 @pytest.mark.gpu

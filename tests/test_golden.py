@@ -20,7 +20,7 @@ AGG = {n: i for i, n in enumerate(["SUM", "PROD", "MIN", "MAX", "IDXMIN", "IDXMA
 
 DENSE_CHECKS = {"checkAggRow", "checkAggCol", "checkAggAll", "checkEwBinaryMat", "checkEwUnaryMat",
                 "checkEwUnaryMatApprox", "checkEwUnaryMatThrow", "checkEwBinaryObjSca", "checkMatMul", "checkSyrk",
-                "solveNormalEquations", "ctableSection", "transposeSection", "checkSeq", "checkDiagMatrix"}
+                "solveNormalEquations", "ctableSection", "transposeSection", "checkSeq", "checkDiagMatrix", "colBind", "extractCol", "extractColThrow"}
 
 
 def _num(v):
@@ -69,6 +69,8 @@ class _OracleBackend:
     def solve(self, a, b): return self.o.solve(a, b)
     def ctable(self, ys, xs, w, nr, nc): return self.o.ctable(ys, xs, w, nr, nc)
     def seq(self, start, end, inc): return self.o.seq(start, end, inc)
+    def col_bind(self, a, b): return self.o.colBind(a, b)
+    def extract_col(self, a, sel): return self.o.extractCol(a, sel)
     diag = None  # DiagMatrix has no restatement in the oracle: a diagonal copy, checked on the device only
 
 
@@ -96,6 +98,8 @@ class _CudaBackend:
         return self.k.ctable(self._m(ys.astype(np.int64)), self._m(xs.astype(np.int64)), w, nr, nc).to_numpy()
 
     def seq(self, start, end, inc): return self.k.seq(self.ctx, start, end, inc).to_numpy()
+    def col_bind(self, a, b): return self.k.colBind(self._m(a), self._m(b)).to_numpy()
+    def extract_col(self, a, sel): return self.k.extractCol(self._m(a), self._m(sel)).to_numpy()
     def diag(self, a): return self.k.diagMatrix(self._m(a)).to_numpy()
 
 
@@ -161,6 +165,20 @@ def _run_case(be, c):
         if be.diag is not None:
             arg, exp = _mat(args[0]), _mat(args[1])
             got = be.diag(arg)
+            assert got.shape == exp.shape and np.array_equal(got, exp), f"{c['file']}:{c['line']}"
+    elif chk == "colBind":  # ColBindTest.cpp:62-64
+        lhs, rhs, exp = (_mat(a) for a in args)
+        got = be.col_bind(lhs, rhs)
+        assert got.shape == exp.shape and np.array_equal(got, exp), f"{c['file']}:{c['line']}"
+    elif chk in ("extractCol", "extractColThrow"):  # ExtractColTest.cpp:36-44
+        arg = _mat(args[0])
+        sel = np.array([_num(v) for v in args[1]["values"]], dtype=np.int64).reshape(-1, 1)
+        if chk == "extractColThrow":
+            with pytest.raises(be.err):
+                be.extract_col(arg, sel)
+        else:
+            exp = np.array([_num(v) for v in args[2]["values"]], dtype=np.float64).reshape(args[2]["rows"], -1)
+            got = be.extract_col(arg, sel)
             assert got.shape == exp.shape and np.array_equal(got, exp), f"{c['file']}:{c['line']}"
     elif chk == "transposeSection":
         m, mt = _mat(args[0]), _mat(args[1])

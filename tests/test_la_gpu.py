@@ -173,6 +173,43 @@ def test_fill_shapes_and_values_of_the_reference_test(ctx):
                 assert got.shape == exp.shape and got.dtype == exp.dtype and np.array_equal(got, exp), (dtype, rows, cols)
 
 
+def test_col_bind_and_extract_col(ctx):
+    """ColBind.h:54-88 and ExtractCol.h:64-105 against their restatements, incl. views, empty operands, negative
+    positions and the reference's errors."""
+    k, o = _k()
+    rng = np.random.default_rng(12)
+    for dtype in (np.float64, np.float32, np.int64):
+        for rows, cl, cr in [(1, 1, 1), (5, 3, 2), (1000, 32, 1), (70001, 7, 33), (300, 0, 5), (300, 5, 0), (0, 3, 2)]:
+            a = (rng.standard_normal((rows, cl)) * 100).astype(dtype)
+            b = (rng.standard_normal((rows, cr)) * 100).astype(dtype)
+            got = k.colBind(k.DenseMatrix.from_numpy(ctx, a), k.DenseMatrix.from_numpy(ctx, b)).to_numpy()
+            exp = o.colBind(a, b) if rows and cl + cr else np.empty((rows, cl + cr), dtype)
+            assert got.shape == exp.shape and got.dtype == exp.dtype and np.array_equal(got, exp), (dtype, rows, cl, cr)
+        x = (rng.standard_normal((40000, 37)) * 100).astype(dtype)
+        X = k.DenseMatrix.from_numpy(ctx, x)
+        for sel in ([0], [36, 0, 5], [-1, -37, 3, 3, 3], list(range(37)), list(range(36, -1, -1)) * 3, []):
+            s = np.array(sel, dtype=np.int64).reshape(-1, 1)
+            got = k.extractCol(X, k.DenseMatrix.from_numpy(ctx, s)).to_numpy()
+            exp = o.extractCol(x, s)
+            assert got.shape == exp.shape and got.dtype == exp.dtype and np.array_equal(got, exp), (dtype, sel)
+    # row views keep their offset; a deferred elementwise result is a valid operand
+    big = rng.standard_normal((5000, 16))
+    B_ = k.DenseMatrix.from_numpy(ctx, big)
+    v = B_.slice_rows(100, 4100)
+    w = k.ewBinaryObjSca(k.BinaryOpCode.MUL, k.DenseMatrix.from_numpy(ctx, rng.standard_normal((4000, 20))), 2.0)
+    got = k.colBind(v, w).to_numpy()
+    assert np.array_equal(got, np.hstack([big[100:4100], w.to_numpy()]))
+    s = np.array([[15], [0], [-2]], dtype=np.int64)
+    assert np.array_equal(k.extractCol(v, k.DenseMatrix.from_numpy(ctx, s)).to_numpy(), big[100:4100][:, [15, 0, 14]])
+    with pytest.raises(k.Db2Error, match="must have the same number of rows, but lhs has 4000 and rhs has 5000"):
+        k.colBind(v, B_)
+    for bad in ([16], [-17], [3, 99]):
+        with pytest.raises(k.Db2Error, match="out of bounds for dense matrix with column boundaries"):
+            k.extractCol(B_, k.DenseMatrix.from_numpy(ctx, np.array(bad, dtype=np.int64).reshape(-1, 1)))
+    with pytest.raises(k.Db2Error, match="must be given as column matrix"):
+        k.extractCol(B_, k.DenseMatrix.from_numpy(ctx, np.zeros((2, 2), dtype=np.int64)))
+
+
 def test_ctable(ctx):
     k, o = _k()
     rng = np.random.default_rng(9)
