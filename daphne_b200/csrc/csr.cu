@@ -63,6 +63,17 @@ __global__ void __launch_bounds__(256)
                        const uint64_t *__restrict__ off, int64_t rows, int64_t cols, int skind,
                        const double *__restrict__ sc, int64_t sc_ld, double *__restrict__ out) {
     constexpr int RPC = 256 / G, U = 4;
+    // A row much longer than the others would keep its G lanes busy for length / G dependent steps while the rest of
+    // the warp waits (a hub of a power-law graph).  Such rows are only noted here and taken by the whole block at the
+    // end of the kernel; when the list is full they are processed in place after all.
+    constexpr int LONG_ROW = 64 * G, MAX_LONG = 64;
+    __shared__ int64_t long_rows[MAX_LONG];
+    __shared__ int n_long;
+    __shared__ double red_v[8];
+    __shared__ int red_k[8];
+    if (threadIdx.x == 0)
+        n_long = 0;
+    __syncthreads();
     const int lane = threadIdx.x % G, grp = threadIdx.x / G;
     const int64_t stride = (int64_t)gridDim.x * RPC;
     const int64_t rows_padded = (rows + RPC - 1) / RPC * RPC;
@@ -80,6 +91,7 @@ __global__ void __launch_bounds__(256)
         uint64_t b[U], e[U];
         double acc[U];
         int kept[U]; // entries of the row that exist in the product (only compared with the column count)
+        bool deferred[U];
 #pragma unroll
         for (int u = 0; u < U; u++) {
             const int64_t r = r0 + u * stride;
@@ -88,6 +100,42 @@ __global__ void __launch_bounds__(256)
             e[u] = live ? off[r + 1] : 0;
             acc[u] = init;
             kept[u] = 0;
+            deferred[u] = false;
+        }
+        // every warp is converged here (all threads of the block make the same number of turns): the groups that want
+        // a slot for a long row are counted with ballots and the warp takes its slots with one atomic
+        {
+            const int wl = threadIdx.x % 32, leader = wl / G * G;
+            bool want[U], any = false;
+#pragma unroll
+            for (int u = 0; u < U; u++) {
+                want[u] = e[u] - b[u] > (uint64_t)LONG_ROW; // the same in all G lanes of a group
+                any |= want[u];
+            }
+            if (__any_sync(0xffffffffu, any)) { // warp-uniform, rare
+                unsigned leaders[U];
+                int total = 0;
+#pragma unroll
+                for (int u = 0; u < U; u++) {
+                    leaders[u] = __ballot_sync(0xffffffffu, want[u] && lane == 0);
+                    total += __popc(leaders[u]);
+                }
+                int base = 0;
+                if (wl == 0)
+                    base = atomicAdd(&n_long, total);
+                base = __shfl_sync(0xffffffffu, base, 0);
+#pragma unroll
+                for (int u = 0; u < U; u++) {
+                    const int slot = base + __popc(leaders[u] & ((1u << leader) - 1u));
+                    base += __popc(leaders[u]);
+                    if (want[u] && slot < MAX_LONG) {
+                        if (lane == 0)
+                            long_rows[slot] = r0 + u * stride;
+                        deferred[u] = true;
+                        e[u] = b[u]; // nothing to do here
+                    }
+                }
+            }
         }
         // first entry of every lane: the loads of the U rows are issued back to back
         int64_t cc[U];
@@ -132,7 +180,7 @@ __global__ void __launch_bounds__(256)
                 kept[u] += __shfl_xor_sync(0xffffffffu, kept[u], m);
             }
             const int64_t r = r0 + u * stride;
-            if (r < rows && lane == 0) {
+            if (r < rows && lane == 0 && !deferred[u]) {
                 double a = acc[u];
                 if (op != DB2_AGG_SUM && kept[u] < cols) { // one implicit zero takes part (AggRow.h:167-176)
                     if (op == DB2_AGG_MAX)
@@ -145,6 +193,60 @@ __global__ void __launch_bounds__(256)
                 out[r] = a;
             }
         }
+    }
+    // the long rows, one after the other, by the whole block (fixed order of the partial results)
+    __syncthreads();
+    const int listed = n_long < MAX_LONG ? n_long : MAX_LONG;
+    for (int q = 0; q < listed; q++) {
+        const int64_t r = long_rows[q];
+        const uint64_t rb = off[r], re = off[r + 1];
+        double a = init;
+        int k = 0;
+        for (uint64_t i0 = rb + threadIdx.x; i0 < re; i0 += 4 * (uint64_t)blockDim.x) { // four entries in flight
+            int64_t c4[4];
+            double x4[4], s4[4];
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                const uint64_t i = i0 + (uint64_t)j * blockDim.x;
+                c4[j] = i < re ? (int64_t)col[i] : -1;
+                x4[j] = (UNIT || i >= re) ? 1.0 : val[i];
+            }
+#pragma unroll
+            for (int j = 0; j < 4; j++)
+                s4[j] = (c4[j] >= 0 && skind != SK_NONE) ? scale_at(skind, sc, sc_ld, r, c4[j]) : 1.0;
+#pragma unroll
+            for (int j = 0; j < 4; j++)
+                if (c4[j] >= 0 && !(skind != SK_NONE && s4[j] == 0.0)) {
+                    k++;
+                    a = combine(a, skind != SK_NONE ? __dmul_rn(x4[j], s4[j]) : x4[j]);
+                }
+        }
+#pragma unroll
+        for (int m = 16; m >= 1; m >>= 1) {
+            a = combine(a, shfl_xor(a, m));
+            k += __shfl_xor_sync(0xffffffffu, k, m);
+        }
+        if (threadIdx.x % 32 == 0) {
+            red_v[threadIdx.x / 32] = a;
+            red_k[threadIdx.x / 32] = k;
+        }
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            for (int w = 1; w < (int)blockDim.x / 32; w++) {
+                a = combine(a, red_v[w]);
+                k += red_k[w];
+            }
+            if (op != DB2_AGG_SUM && k < cols) { // one implicit zero takes part (AggRow.h:167-176)
+                if (op == DB2_AGG_MAX)
+                    a = (a < 0.0) ? 0.0 : a;
+                else if (op == DB2_AGG_MIN)
+                    a = (0.0 < a) ? 0.0 : a;
+                else
+                    a = __dmul_rn(a, 0.0);
+            }
+            out[r] = a;
+        }
+        __syncthreads();
     }
 }
 

@@ -100,6 +100,51 @@ def test_cfg4_connected_components_bit_exact(ctx):
             assert np.all(c[members, 0] == members.max() + 1)
 
 
+def test_csr_row_aggregation_with_hub_rows(ctx):
+    """Rows far longer than the others (hubs of a power-law graph) are finished by whole thread blocks at the end of the
+    kernel; more hubs than a block's list holds fall back to the ordinary path.  Values, implicit zeros and views."""
+    import daphne_b200.kernels as k
+    from oracle import pyoracle as o
+    rng = np.random.default_rng(5)
+    n, m = 20000, 60000
+    base = sp.random(n, m, 0.0002, format="coo", random_state=2)
+    rr, cc = [base.row], [base.col]
+    hubs = list(range(0, 3000, 20)) + [n - 1]           # 151 hubs: more than one block's list in places
+    for h in hubs:
+        cols = rng.choice(m, size=int(rng.integers(2000, 9000)), replace=False)
+        rr.append(np.full(cols.size, h))
+        cc.append(cols)
+    rr.append(np.full(m, 7))                            # a full row: no implicit zero takes part
+    cc.append(np.arange(m))
+    rr, cc = np.concatenate(rr), np.concatenate(cc)
+    g = sp.csr_matrix((np.ones(rr.size), (rr, cc)), shape=(n, m))
+    g.sum_duplicates()
+    g.data[:] = rng.standard_normal(g.nnz)
+    g.sort_indices()
+    G = k.CSRMatrix.from_scipy(ctx, g)
+    rv = rng.standard_normal((1, m))
+    rv[0, ::9] = 0
+    prod = k.ewMulCsrDense(G, k.DenseMatrix.from_numpy(ctx, rv))
+    exp = o.ewMulCsrDense(g, rv)
+    for op in (0, 2, 3):
+        got, e = k.aggRowCsr(op, prod).to_numpy(), o.aggRowCsr(op, exp)
+        if op == 0:
+            np.testing.assert_allclose(got, e, rtol=1e-11, atol=1e-300)
+        else:
+            assert_bits_equal(got, e, f"hub rows agg {op}")
+    for op in (2, 3):
+        assert_bits_equal(k.aggRowCsr(op, G).to_numpy(), o.aggRowCsr(op, g), f"plain hub rows agg {op}")
+    v = G.slice_rows(5, 2500)
+    assert_bits_equal(k.aggRowCsr(3, v).to_numpy(), o.aggRowCsr(3, g)[5:2500], "view with hubs")
+    # adjacency matrix (every value 1.0: the value array is not read)
+    a = g.copy()
+    a.data[:] = 1.0
+    A_ = k.CSRMatrix.from_scipy(ctx, a)
+    c = rng.integers(1, 1000, size=(1, m)).astype(np.float64)
+    got = k.aggRowCsr(3, k.ewMulCsrDense(A_, k.DenseMatrix.from_numpy(ctx, c))).to_numpy()
+    assert_bits_equal(got, o.aggRowCsr(3, o.ewMulCsrDense(a, c)), "unit values with hubs")
+
+
 def test_csr_kernels_against_oracle(ctx):
     import daphne_b200.kernels as k
     from oracle import pyoracle as o
