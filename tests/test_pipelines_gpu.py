@@ -107,9 +107,8 @@ def test_csr_row_aggregation_with_hub_rows(ctx):
     from oracle import pyoracle as o
     rng = np.random.default_rng(5)
     n, m = 20000, 60000
-    base = sp.random(n, m, 0.0002, format="coo", random_state=2)
-    rr, cc = [base.row], [base.col]
-    hubs = list(range(0, 3000, 20)) + [n - 1]           # 151 hubs: more than one block's list in places
+    rr, cc = [rng.integers(0, n, size=240000)], [rng.integers(0, m, size=240000)]  # the ordinary short rows
+    hubs = list(range(0, 3000, 75)) + [n - 1]
     for h in hubs:
         cols = rng.choice(m, size=int(rng.integers(2000, 9000)), replace=False)
         rr.append(np.full(cols.size, h))
@@ -143,6 +142,14 @@ def test_csr_row_aggregation_with_hub_rows(ctx):
     c = rng.integers(1, 1000, size=(1, m)).astype(np.float64)
     got = k.aggRowCsr(3, k.ewMulCsrDense(A_, k.DenseMatrix.from_numpy(ctx, c))).to_numpy()
     assert_bits_equal(got, o.aggRowCsr(3, o.ewMulCsrDense(a, c)), "unit values with hubs")
+    # every row long, few blocks: more long rows than a block's list holds (the rest is processed in place)
+    d = sp.random(300, 5000, 0.15, format="csr", random_state=3)
+    d.data[:] = rng.standard_normal(d.nnz)
+    d.sort_indices()
+    D = k.CSRMatrix.from_scipy(ctx, d)
+    for op in (2, 3):
+        assert_bits_equal(k.aggRowCsr(op, D).to_numpy(), o.aggRowCsr(op, d), f"all rows long, agg {op}")
+    np.testing.assert_allclose(k.aggRowCsr(0, D).to_numpy(), o.aggRowCsr(0, d), rtol=1e-11, atol=1e-11)  # sums near 0
 
 
 def test_csr_kernels_against_oracle(ctx):
