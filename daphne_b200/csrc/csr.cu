@@ -339,7 +339,9 @@ static int launch_agg(db2_context *ctx, int op, const db2_csr *m, int skind, con
     const IT *col = static_cast<const IT *>(m->d_col->ptr);
     const double avg = (double)m->nnz / (double)(m->rows > 0 ? m->rows : 1); // a view inherits its parent's count
     const int64_t rows = m->rows;
-    const int lanes = avg <= 6.0 ? 4 : (avg <= 24.0 ? 8 : 32);
+    // few lanes per row keep more rows in flight; rows far longer than the average are taken by whole blocks (see the
+    // kernel), so a small group is safe on skewed graphs too
+    const int lanes = avg <= 12.0 ? 2 : (avg <= 24.0 ? 4 : (avg <= 96.0 ? 8 : 32));
     // every lane group takes 4 rows per turn
     const int64_t want = (rows + (256 / lanes) * 4 - 1) / ((256 / lanes) * 4), cap = (int64_t)sm_count() * 8;
     const int grid = (int)(want < cap ? (want ? want : 1) : cap);
@@ -359,7 +361,9 @@ static int launch_agg(db2_context *ctx, int op, const db2_csr *m, int skind, con
     } else {                                                                                                           \
         DB2_CSR_AGG2(G, false)                                                                                         \
     }
-    if (lanes == 4) {
+    if (lanes == 2) {
+        DB2_CSR_AGG(2)
+    } else if (lanes == 4) {
         DB2_CSR_AGG(4)
     } else if (lanes == 8) {
         DB2_CSR_AGG(8)
