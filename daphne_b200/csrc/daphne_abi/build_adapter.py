@@ -33,7 +33,7 @@ SUPPORTED_HEADERS = {"AggAll.h", "AggCol.h", "AggRow.h", "EwBinaryMat.h", "EwBin
 
 
 # backend-"CPP" extension: header -> opcodes to register (None: all of the entry's opcodes / no opcode)
-EXT_HEADERS = {"EwUnaryMat.h": None, "CTable.h": None,
+EXT_HEADERS = {"EwUnaryMat.h": None, "CTable.h": None, "OuterBinary.h": None,
                "AggRow.h": {"IDXMIN", "IDXMAX", "MEAN", "VAR", "STDDEV", "PROD"},
                "AggCol.h": {"IDXMIN", "IDXMAX", "MEAN", "VAR", "STDDEV", "PROD"},
                "AggAll.h": {"MEAN", "VAR", "STDDEV", "PROD"}}
@@ -52,6 +52,8 @@ def _ext_instantiation_ok(header: str, inst) -> bool:
             scalars.append(tv)
     if header == "CTable.h":  # DTRes, DTLhs, DTRhs, VTWeight
         return vts == ["double", "int64_t", "int64_t"]
+    if header == "OuterBinary.h":  # DTRes, DTLhs, DTRhs of one value type
+        return len(vts) == 3 and len(set(vts)) == 1 and vts[0] in DEVICE_VTS
     if header == "AggAll.h":  # VTRes, DTArg
         return len(vts) == 1 and vts[0] in ("double", "float") and scalars == vts
     res, arg = vts[0], vts[-1]

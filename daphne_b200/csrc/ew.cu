@@ -296,9 +296,54 @@ static int ew_binary_impl(const VT *lhs, int64_t lr, int64_t lc, int64_t lld, co
                      (long long)lr, (long long)lc, (long long)rr, (long long)rc);
 }
 
+// res[r][c] = lhs[r] (op) rhs[c]: a warp writes whole rows (coalesced), four rows in flight; nothing but the two
+// vectors is read, so the pass is bound by the write stream
+template <int OP, typename VT>
+__global__ void __launch_bounds__(EW_THREADS)
+    ew_outer_kernel(const VT *__restrict__ lhs, int64_t lld, const VT *__restrict__ rhs, VT *__restrict__ res,
+                    int64_t res_ld, int64_t rows, int64_t cols) {
+    const int lane = threadIdx.x % 32;
+    const int64_t warp = ((int64_t)blockIdx.x * EW_THREADS + threadIdx.x) / 32;
+    const int64_t nwarps = (int64_t)gridDim.x * (EW_THREADS / 32);
+    for (int64_t r0 = warp * 4; r0 < rows; r0 += nwarps * 4) {
+        VT a[4];
+#pragma unroll
+        for (int u = 0; u < 4; u++)
+            a[u] = r0 + u < rows ? lhs[(r0 + u) * lld] : (VT)0;
+        for (int64_t c = lane; c < cols; c += 32) {
+            const VT b = rhs[c];
+#pragma unroll
+            for (int u = 0; u < 4; u++)
+                if (r0 + u < rows)
+                    res[(r0 + u) * res_ld + c] = binary_op<OP>(a[u], b);
+        }
+    }
+}
+
+template <int OP, typename VT>
+static int ew_outer_impl(const VT *lhs, int64_t lld, const VT *rhs, VT *res, int64_t res_ld, int64_t rows,
+                         int64_t cols, cudaStream_t st) {
+    const int64_t want = (rows + 31) / 32, cap = (int64_t)sm_count() * 8;
+    const int grid = (int)(want < 1 ? 1 : (want < cap ? want : cap));
+    ew_outer_kernel<OP, VT><<<grid, EW_THREADS, 0, st>>>(lhs, lld, rhs, res, res_ld, rows, cols);
+    return after_launch("ew_outer_kernel");
+}
+
 } // namespace db2
 
 using namespace db2;
+
+extern "C" int db2k_outer_binary(int dtype, int op, const void *lhs, int64_t lhs_ld, int64_t rows, const void *rhs,
+                                 int64_t cols, void *res, int64_t res_ld, void *stream) {
+    DB2_CHECK(rows >= 0 && cols >= 0, DB2_EINVAL, "negative dimension");
+    if (rows == 0 || cols == 0)
+        return DB2_OK;
+    DB2_CHECK(lhs && rhs && res, DB2_EINVAL, "null operand");
+    DB2_DISPATCH_DTYPE(dtype, VT, DB2_DISPATCH_BINOP(op, OP, return (ew_outer_impl<OP, VT>(
+                                                                 (const VT *)lhs, lhs_ld, (const VT *)rhs, (VT *)res,
+                                                                 res_ld, rows, cols, as_stream(stream)))));
+    return DB2_OK;
+}
 
 extern "C" int db2k_ew_binary(int dtype, int op, const void *lhs, int64_t lhs_rows, int64_t lhs_cols,
                               int64_t lhs_ld, const void *rhs, int64_t rhs_rows, int64_t rhs_cols, int64_t rhs_ld,

@@ -450,6 +450,25 @@ int db2_ewBinaryMat(db2_context *ctx, int op, db2_matrix **res, db2_matrix *lhs,
     DB2_API_END
 }
 
+int db2_outerBinary(db2_context *ctx, int op, db2_matrix **res, db2_matrix *lhs, db2_matrix *rhs) {
+    DB2_API_BEGIN
+    DB2_CHECK(ctx && res && lhs && rhs, DB2_EINVAL, "null argument");
+    DB2_CHECK(lhs->dtype == rhs->dtype, DB2_EUNSUPPORTED, "outerBinary: value types of lhs and rhs differ");
+    DB2_CHECK(lhs->cols == 1, DB2_EINVAL, "outerBinary: lhs must be a column (mx1) matrix");
+    DB2_CHECK(rhs->rows == 1, DB2_EINVAL, "outerBinary: rhs must be a row (1xn) matrix");
+    bind_device(ctx);
+    const uint64_t before = g_launches.load();
+    DB2_TRY(ensure_device(lhs));
+    DB2_TRY(ensure_device(rhs));
+    DB2_TRY(prepare_result(ctx, res, lhs->dtype, lhs->rows, rhs->cols));
+    db2_matrix *r = *res;
+    DB2_TRY(db2k_outer_binary(lhs->dtype, op, lhs->dev_ptr(), lhs->dev_ld, lhs->rows, rhs->dev_ptr(), rhs->cols,
+                              r->dev_ptr(), r->dev_ld, ctx->stream));
+    count_launches(ctx, before);
+    return DB2_OK;
+    DB2_API_END
+}
+
 int db2_ewBinaryObjSca(db2_context *ctx, int op, db2_matrix **res, db2_matrix *lhs, const void *scalar) {
     DB2_API_BEGIN
     DB2_CHECK(ctx && lhs && scalar, DB2_EINVAL, "null argument");

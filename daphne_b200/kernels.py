@@ -270,6 +270,14 @@ def diagMatrix(arg: DenseMatrix, ctx: Optional[Context] = None) -> DenseMatrix:
     return _res(ctx, h)
 
 
+def outerBinary(op, lhs: DenseMatrix, rhs: DenseMatrix, ctx: Optional[Context] = None) -> DenseMatrix:
+    """OuterBinary.h:41-44: res[r][c] = lhs[r] (op) rhs[c] for a column vector lhs and a row vector rhs."""
+    ctx = ctx or lhs.ctx
+    h = C.c_void_p()
+    check(lib.db2_outerBinary(ctx.handle, int(op), C.byref(h), lhs.handle, rhs.handle))
+    return _res(ctx, h)
+
+
 def colBind(lhs: DenseMatrix, rhs: DenseMatrix, ctx: Optional[Context] = None) -> DenseMatrix:
     """ColBind.h:41-44: [lhs | rhs]."""
     ctx = ctx or lhs.ctx

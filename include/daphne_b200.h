@@ -110,6 +110,10 @@ int db2k_ew_binary(int dtype, int op, const void *lhs, int64_t lhs_rows, int64_t
                    const void *rhs, int64_t rhs_rows, int64_t rhs_cols, int64_t rhs_ld, void *res, int64_t res_ld,
                    void *stream);
 
+/* res[r][c] = lhs[r] (op) rhs[c] for a column vector lhs (rows elements, stride lhs_ld) and a row vector rhs (cols
+ * elements).  Replaces OuterBinary<Dense,Dense,Dense> (src/runtime/local/kernels/OuterBinary.h:52-78; no CUDA twin). */
+int db2k_outer_binary(int dtype, int op, const void *lhs, int64_t lhs_ld, int64_t rows, const void *rhs, int64_t cols,
+                      void *res, int64_t res_ld, void *stream);
 /* res = lhs op scalar; `scalar` is a HOST pointer to one value of `dtype`.  Replaces EwBinaryObjSca<Dense,Dense,VT>
  * (src/runtime/local/kernels/EwBinaryObjSca.h:58-79; CUDA twin kernels/CUDA/EwBinaryObjSca.cu:31-88). */
 int db2k_ew_binary_sca(int dtype, int op, const void *lhs, int64_t rows, int64_t cols, int64_t ld,
@@ -301,6 +305,8 @@ int db2_transpose(db2_context *ctx, db2_matrix **res, db2_matrix *arg);
 int db2_fill(db2_context *ctx, db2_matrix **res, int dtype, const void *value, int64_t rows, int64_t cols);
 int db2_seq(db2_context *ctx, db2_matrix **res, int dtype, const void *start, const void *end, const void *inc);
 int db2_diagMatrix(db2_context *ctx, db2_matrix **res, db2_matrix *arg);
+/* lhs (m x 1) (op) rhs (1 x n) -> m x n; the reference's messages for other shapes (OuterBinary.h:56-59) */
+int db2_outerBinary(db2_context *ctx, int op, db2_matrix **res, db2_matrix *lhs, db2_matrix *rhs);
 /* [lhs | rhs]; DB2_EINVAL with the reference's message when the row counts differ (ColBind.h:58-63) */
 int db2_colBind(db2_context *ctx, db2_matrix **res, db2_matrix *lhs, db2_matrix *rhs);
 /* the columns of arg named by the int64 column matrix sel; negative positions count from the end, anything outside

@@ -216,6 +216,18 @@ def seq(start, end, inc):
     return _seq(_lib, "orc", start, end, inc)
 
 
+def outerBinary(op, lhs, rhs) -> np.ndarray:
+    """OuterBinary<Dense,Dense,Dense> (src/runtime/local/kernels/OuterBinary.h:52-78): res[r][c] = f(lhs[r], rhs[c])
+    with f the scalar function EwBinaryMat uses for the same opcode, so row r is EwBinaryMat of lhs[r] repeated
+    against the row vector rhs."""
+    lhs, rhs = _mat(lhs), _mat(rhs)
+    if lhs.shape[1] != 1:
+        raise OracleError("outerBinary: lhs must be a column (mx1) matrix")
+    if rhs.shape[0] != 1:
+        raise OracleError("outerBinary: rhs must be a row (1xn) matrix")
+    return ewBinaryMat(op, np.ascontiguousarray(np.repeat(lhs, rhs.shape[1], axis=1)), rhs)
+
+
 def colBind(lhs, rhs) -> np.ndarray:
     """ColBind<Dense,Dense,Dense> (src/runtime/local/kernels/ColBind.h:54-88): row r of the result is row r of lhs
     followed by row r of rhs; operands with different row counts are an error."""

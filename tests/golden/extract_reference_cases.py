@@ -181,7 +181,29 @@ def extract(root: Path):
                                       "args": [local["m"], local["mt"]]})
     cases += _extract_seq(root)
     cases += _extract_reorg(root)
+    cases += _extract_outer(root)
     return cases, skipped
+
+
+OUTER_RE = re.compile(r"helper<TestType>\(\s*BinaryOpCode::(\w+)\s*,\s*\{([^}]*)\}\s*,\s*\{([^}]*)\}\s*,\s*\{([^}]*)\}\s*\)\s*;")
+
+
+def _extract_outer(root: Path):
+    """OuterBinaryTest.cpp: helper<TestType>(opcode, {lhs column}, {rhs row}, {expected, row-major})."""
+    path = root / "test/runtime/local/kernels/OuterBinaryTest.cpp"
+    if not path.exists():
+        return []
+    text = _clean(path.read_text())
+    out = []
+    for m in OUTER_RE.finditer(text):
+        op, lhs, rhs, exp = m.groups()
+        lv, rv, ev = (_split_values(x) for x in (lhs, rhs, exp))
+        out.append({"file": "test/runtime/local/kernels/OuterBinaryTest.cpp", "line": text.count("\n", 0, m.start()) + 1,
+                    "test": "OuterBinary", "check": "outerBinary", "op": op,
+                    "args": [{"matrix": "lhs", "dt": "DT", "rows": len(lv), "values": [_enc(v) for v in lv]},
+                             {"matrix": "rhs", "dt": "DT", "rows": 1, "values": [_enc(v) for v in rv]},
+                             {"matrix": "exp", "dt": "DT", "rows": len(lv), "values": [_enc(v) for v in ev]}]})
+    return out
 
 
 def _extract_reorg(root: Path):

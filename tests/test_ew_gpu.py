@@ -186,3 +186,36 @@ def test_empty_matrices(ctx):
     assert k.ewBinaryMat(k.BinaryOpCode.ADD, e, e).to_numpy().shape == (0, 5)
     assert k.ewBinaryObjSca(k.BinaryOpCode.MUL, e, 2.0).to_numpy().shape == (0, 5)
     assert k.ewUnaryMat(k.UnaryOpCode.ABS, e).to_numpy().shape == (0, 5)
+
+
+def test_outer_binary_all_opcodes_and_shapes(ctx):
+    """OuterBinary.h:52-78 against its restatement: every opcode EwBinaryMat implements, f64 / f32 / i64, empty and
+    ragged shapes, a row view as lhs, and the reference's shape errors."""
+    import daphne_b200.kernels as k
+    from oracle import pyoracle as o
+    rng = np.random.default_rng(41)
+    B = k.BinaryOpCode
+    ops = [B.ADD, B.SUB, B.MUL, B.DIV, B.MIN, B.MAX, B.EQ, B.NEQ, B.LT, B.LE, B.GT, B.GE, B.AND, B.OR]
+    for dtype in (np.float64, np.float32, np.int64):
+        for m, n in [(1, 1), (5, 3), (1000, 33), (70001, 7), (3, 5000), (0, 4), (4, 0)]:
+            lhs = (rng.integers(-5, 6, size=(m, 1)) if dtype == np.int64 else rng.standard_normal((m, 1))).astype(dtype)
+            rhs = (rng.integers(1, 6, size=(1, n)) if dtype == np.int64 else rng.standard_normal((1, n))).astype(dtype)
+            L, R = k.DenseMatrix.from_numpy(ctx, lhs), k.DenseMatrix.from_numpy(ctx, rhs)
+            for op in ops:
+                got = k.outerBinary(op, L, R).to_numpy()
+                if m == 0 or n == 0:
+                    assert got.shape == (m, n)
+                    continue
+                exp = o.outerBinary(int(op), lhs, rhs)
+                assert got.shape == exp.shape and got.dtype == exp.dtype
+                assert np.array_equal(got, exp, equal_nan=True), (dtype, m, n, op)
+    big = k.DenseMatrix.from_numpy(ctx, rng.standard_normal((3000, 1)))
+    v = big.slice_rows(100, 2100)
+    r = rng.standard_normal((1, 17))
+    got = k.outerBinary(B.SUB, v, k.DenseMatrix.from_numpy(ctx, r)).to_numpy()
+    assert np.array_equal(got, o.outerBinary(int(B.SUB), big.to_numpy()[100:2100], r))
+    M = k.DenseMatrix.from_numpy(ctx, rng.standard_normal((4, 4)))
+    with pytest.raises(k.Db2Error, match="lhs must be a column"):
+        k.outerBinary(B.ADD, M, k.DenseMatrix.from_numpy(ctx, r))
+    with pytest.raises(k.Db2Error, match="rhs must be a row"):
+        k.outerBinary(B.ADD, big, M)
