@@ -1,4 +1,4 @@
-// Reorganisation kernels: ColBind and ExtractCol.
+// Reorganisation kernels: ColBind, ExtractCol and the conditional select (Cond*).
 //
 // Both are pure copies (16 bytes of traffic per 8-byte element), so the only thing that matters is that every warp
 // moves whole rows with its lanes side by side (coalesced on both ends) and has several rows in flight:
@@ -64,6 +64,36 @@ __global__ void __launch_bounds__(RG_THREADS)
     }
 }
 
+// res = cond ? then : else, element by element; `then` / `else` are matrices of the shape of cond or immediates
+// (CondMatMatMat.h, CondMatMatSca.h, CondMatScaMat.h, CondMatScaSca.h: static_cast<bool>(cond) picks, so a NaN
+// condition is true).  Same warp-per-row walk as the copies above.
+template <typename VT, typename CT>
+__global__ void __launch_bounds__(RG_THREADS)
+    cond_kernel(const CT *__restrict__ cond, int64_t ld_c, const VT *__restrict__ then_m, int64_t ld_t, VT then_s,
+                const VT *__restrict__ else_m, int64_t ld_e, VT else_s, int64_t rows, int64_t cols,
+                VT *__restrict__ res, int64_t ld_o) {
+    const int lane = threadIdx.x % 32;
+    const int64_t warp = ((int64_t)blockIdx.x * RG_THREADS + threadIdx.x) / 32;
+    const int64_t nwarps = (int64_t)gridDim.x * (RG_THREADS / 32);
+    for (int64_t r0 = warp * RG_ROWS; r0 < rows; r0 += nwarps * RG_ROWS) {
+        for (int64_t c = lane; c < cols; c += 32) {
+            CT k[RG_ROWS];
+            VT t[RG_ROWS], e[RG_ROWS];
+#pragma unroll
+            for (int u = 0; u < RG_ROWS; u++)
+                if (r0 + u < rows) {
+                    k[u] = cond[(r0 + u) * ld_c + c];
+                    t[u] = then_m ? then_m[(r0 + u) * ld_t + c] : then_s;
+                    e[u] = else_m ? else_m[(r0 + u) * ld_e + c] : else_s;
+                }
+#pragma unroll
+            for (int u = 0; u < RG_ROWS; u++)
+                if (r0 + u < rows)
+                    res[(r0 + u) * ld_o + c] = (k[u] != (CT)0) ? t[u] : e[u];
+        }
+    }
+}
+
 static void count(db2_context *ctx, uint64_t before) {
     std::lock_guard<std::mutex> lock(ctx->mu);
     ctx->stats.launches += g_launches.load(std::memory_order_relaxed) - before;
@@ -105,6 +135,54 @@ int db2k_extract_col(int dtype, const void *arg, int64_t ld, int64_t rows, const
                            static_cast<const VT *>(arg), ld, rows, static_cast<const int64_t *>(dev_positions), nsel,
                            static_cast<VT *>(res), res_ld)));
     return after_launch("extract_col_kernel");
+}
+
+int db2k_cond(int dtype, int cond_dtype, const void *cond, int64_t cond_ld, const void *then_m, int64_t then_ld,
+              const void *then_s, const void *else_m, int64_t else_ld, const void *else_s, int64_t rows, int64_t cols,
+              void *res, int64_t res_ld, void *stream) {
+    DB2_CHECK(rows >= 0 && cols >= 0, DB2_EINVAL, "negative shape");
+    DB2_CHECK((then_m || then_s) && (else_m || else_s), DB2_EINVAL, "then / else need a matrix or a scalar");
+    if (rows == 0 || cols == 0)
+        return DB2_OK;
+    const int grid = reorg_grid(rows);
+    DB2_DISPATCH_DTYPE(
+        dtype, VT,
+        DB2_DISPATCH_DTYPE(cond_dtype, CT,
+                           (cond_kernel<VT, CT><<<grid, RG_THREADS, 0, as_stream(stream)>>>(
+                               static_cast<const CT *>(cond), cond_ld, static_cast<const VT *>(then_m), then_ld,
+                               then_m ? (VT)0 : *static_cast<const VT *>(then_s), static_cast<const VT *>(else_m),
+                               else_ld, else_m ? (VT)0 : *static_cast<const VT *>(else_s), rows, cols,
+                               static_cast<VT *>(res), res_ld))));
+    return after_launch("cond_kernel");
+}
+
+int db2_cond(db2_context *ctx, db2_matrix **res, int dtype, db2_matrix *cond, db2_matrix *then_m, const void *then_s,
+             db2_matrix *else_m, const void *else_s) {
+    DB2_API_BEGIN
+    DB2_CHECK(ctx && res && cond, DB2_EINVAL, "null argument");
+    DB2_CHECK((then_m || then_s) && (else_m || else_s), DB2_EINVAL, "cond: then / else need a matrix or a scalar");
+    const char *name = then_m ? (else_m ? "CondMatMatMat" : "CondMatMatSca") : (else_m ? "CondMatScaMat" : "CondMatScaSca");
+    const char *what = then_m ? (else_m ? "condition/then/else" : "condition/then") : "condition/else";
+    DB2_CHECK((!then_m || (then_m->rows == cond->rows && then_m->cols == cond->cols)) &&
+                  (!else_m || (else_m->rows == cond->rows && else_m->cols == cond->cols)),
+              DB2_EINVAL, "%s: %s matrices must have the same shape", name, what);
+    DB2_CHECK((!then_m || then_m->dtype == dtype) && (!else_m || else_m->dtype == dtype), DB2_EUNSUPPORTED,
+              "cond: then / else are not of the result's value type");
+    bind_device(ctx);
+    const uint64_t before = g_launches.load();
+    DB2_TRY(ensure_device(cond));
+    if (then_m)
+        DB2_TRY(ensure_device(then_m));
+    if (else_m)
+        DB2_TRY(ensure_device(else_m));
+    DB2_TRY(prepare_result(ctx, res, dtype, cond->rows, cond->cols));
+    DB2_TRY(db2k_cond(dtype, cond->dtype, cond->dev_ptr(), cond->dev_ld, then_m ? then_m->dev_ptr() : nullptr,
+                      then_m ? then_m->dev_ld : 0, then_s, else_m ? else_m->dev_ptr() : nullptr,
+                      else_m ? else_m->dev_ld : 0, else_s, cond->rows, cond->cols, (*res)->dev_ptr(), (*res)->dev_ld,
+                      ctx->stream));
+    count(ctx, before);
+    return DB2_OK;
+    DB2_API_END
 }
 
 int db2_colBind(db2_context *ctx, db2_matrix **res, db2_matrix *lhs, db2_matrix *rhs) {

@@ -278,6 +278,22 @@ def outerBinary(op, lhs: DenseMatrix, rhs: DenseMatrix, ctx: Optional[Context] =
     return _res(ctx, h)
 
 
+def cond(cnd: DenseMatrix, then, els, dtype=None, ctx: Optional[Context] = None) -> DenseMatrix:
+    """CondMatMatMat.h / CondMatMatSca.h / CondMatScaMat.h / CondMatScaSca.h: cnd ? then : els element by element;
+    `then` and `els` are matrices of the shape of cnd or scalars (dtype names the value type when both are scalars)."""
+    ctx = ctx or cnd.ctx
+    mats = [x for x in (then, els) if isinstance(x, DenseMatrix)]
+    dt = np.dtype(mats[0].dtype if mats else (dtype or np.float64))
+    tm = then.handle if isinstance(then, DenseMatrix) else None
+    em = els.handle if isinstance(els, DenseMatrix) else None
+    ts = np.array([0 if tm else then], dtype=dt)
+    es = np.array([0 if em else els], dtype=dt)
+    h = C.c_void_p()
+    check(lib.db2_cond(ctx.handle, C.byref(h), _NP2DT[dt], cnd.handle, tm, C.c_void_p(ts.ctypes.data), em,
+                       C.c_void_p(es.ctypes.data)))
+    return _res(ctx, h)
+
+
 def colBind(lhs: DenseMatrix, rhs: DenseMatrix, ctx: Optional[Context] = None) -> DenseMatrix:
     """ColBind.h:41-44: [lhs | rhs]."""
     ctx = ctx or lhs.ctx

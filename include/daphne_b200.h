@@ -207,6 +207,13 @@ int db2k_col_bind(int dtype, const void *lhs, int64_t lhs_ld, int64_t lhs_cols, 
  * kernels/CUDA/ExtractCol.cu:22-66). */
 int db2k_extract_col(int dtype, const void *arg, int64_t ld, int64_t rows, const void *dev_positions, int64_t nsel,
                      void *res, int64_t res_ld, void *stream);
+/* res = cond ? then : else, element by element.  then_m / else_m are matrices of the shape of cond (value type
+ * `dtype`) or NULL, in which case the host scalar then_s / else_s (one element of `dtype`) is used; cond has value
+ * type cond_dtype and picks with static_cast<bool>.  Replaces CondMatMatMat / CondMatMatSca / CondMatScaMat /
+ * CondMatScaSca<Dense...> (src/runtime/local/kernels/CondMatMatMat.h:50-83 and the three siblings; no CUDA twin). */
+int db2k_cond(int dtype, int cond_dtype, const void *cond, int64_t cond_ld, const void *then_m, int64_t then_ld,
+              const void *then_s, const void *else_m, int64_t else_ld, const void *else_s, int64_t rows, int64_t cols,
+              void *res, int64_t res_ld, void *stream);
 /* maximum of an int64 vector into a device int64 (used to size ctable results like CTable.h:79-84 does) */
 int db2k_max_i64(const void *vec, int64_t ld, int64_t n, void *dev_out, void *stream);
 /* Contingency table res[lhs[i], rhs[i]] += weight over int64 coordinate vectors (f64 result, overwritten).
@@ -307,6 +314,10 @@ int db2_seq(db2_context *ctx, db2_matrix **res, int dtype, const void *start, co
 int db2_diagMatrix(db2_context *ctx, db2_matrix **res, db2_matrix *arg);
 /* lhs (m x 1) (op) rhs (1 x n) -> m x n; the reference's messages for other shapes (OuterBinary.h:56-59) */
 int db2_outerBinary(db2_context *ctx, int op, db2_matrix **res, db2_matrix *lhs, db2_matrix *rhs);
+/* the four Cond* kernels in one call: a NULL then_m / else_m means "use the scalar"; `dtype` is the value type of the
+ * result, of the matrices and of the scalars; shape mismatches carry the reference's messages */
+int db2_cond(db2_context *ctx, db2_matrix **res, int dtype, db2_matrix *cond, db2_matrix *then_m, const void *then_s,
+             db2_matrix *else_m, const void *else_s);
 /* [lhs | rhs]; DB2_EINVAL with the reference's message when the row counts differ (ColBind.h:58-63) */
 int db2_colBind(db2_context *ctx, db2_matrix **res, db2_matrix *lhs, db2_matrix *rhs);
 /* the columns of arg named by the int64 column matrix sel; negative positions count from the end, anything outside

@@ -228,6 +228,25 @@ def outerBinary(op, lhs, rhs) -> np.ndarray:
     return ewBinaryMat(op, np.ascontiguousarray(np.repeat(lhs, rhs.shape[1], axis=1)), rhs)
 
 
+def cond(cnd, then, els, dtype=np.float64) -> np.ndarray:
+    """CondMatMatMat / CondMatMatSca / CondMatScaMat / CondMatScaSca<Dense...> (src/runtime/local/kernels/
+    CondMatMatMat.h:50-83 and siblings): res = static_cast<bool>(cond) ? then : else per element; matrix operands
+    must have the shape of cond."""
+    cnd = _mat(cnd)
+    mats = [np.asarray(x) for x in (then, els) if isinstance(x, np.ndarray)]
+    dt = mats[0].dtype if mats else np.dtype(dtype)
+    for x in mats:
+        if _mat(x).shape != cnd.shape:
+            raise OracleError("Cond: condition/then/else matrices must have the same shape")
+    res = np.empty(cnd.shape, dtype=dt)
+    for r in range(cnd.shape[0]):
+        for c in range(cnd.shape[1]):
+            t = _mat(then)[r, c] if isinstance(then, np.ndarray) else dt.type(then)
+            e = _mat(els)[r, c] if isinstance(els, np.ndarray) else dt.type(els)
+            res[r, c] = t if bool(cnd[r, c]) else e
+    return res
+
+
 def colBind(lhs, rhs) -> np.ndarray:
     """ColBind<Dense,Dense,Dense> (src/runtime/local/kernels/ColBind.h:54-88): row r of the result is row r of lhs
     followed by row r of rhs; operands with different row counts are an error."""

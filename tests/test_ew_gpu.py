@@ -219,3 +219,40 @@ def test_outer_binary_all_opcodes_and_shapes(ctx):
         k.outerBinary(B.ADD, M, k.DenseMatrix.from_numpy(ctx, r))
     with pytest.raises(k.Db2Error, match="rhs must be a row"):
         k.outerBinary(B.ADD, big, M)
+
+
+def test_cond_four_operand_forms(ctx):
+    """CondMatMatMat / CondMatMatSca / CondMatScaMat / CondMatScaSca against their restatement: value types f64, f32,
+    i64; conditions f64 (incl. NaN = true, -0.0 = false) and i64; views; the reference's shape errors."""
+    import daphne_b200.kernels as k
+    from oracle import pyoracle as o
+    rng = np.random.default_rng(43)
+    for vt in (np.float64, np.float32, np.int64):
+        for ct in (np.float64, np.int64):
+            for rows, cols in [(1, 1), (7, 5), (1000, 33), (40001, 6), (0, 3)]:
+                cnd = rng.integers(-1, 2, size=(rows, cols)).astype(ct)
+                if ct == np.float64 and cnd.size:
+                    cnd.flat[0] = np.nan
+                    cnd.flat[-1] = -0.0
+                t = (rng.standard_normal((rows, cols)) * 10).astype(vt)
+                e = (rng.standard_normal((rows, cols)) * 10).astype(vt)
+                Cn, T, E = (k.DenseMatrix.from_numpy(ctx, a) for a in (cnd, t, e))
+                for then, els, dthen, dels in ((T, E, t, e), (T, 2, t, 2), (3, E, 3, e), (3, 2, 3, 2)):
+                    got = k.cond(Cn, then, els, dtype=vt).to_numpy()
+                    assert got.dtype == np.dtype(vt) and got.shape == (rows, cols)
+                    if rows * cols and rows * cols <= 40000:
+                        assert np.array_equal(got, o.cond(cnd, dthen, dels, dtype=vt)), (vt, ct, rows, cols)
+                    elif rows * cols:
+                        tt = dthen if isinstance(dthen, np.ndarray) else np.full((rows, cols), dthen, dtype=vt)
+                        ee = dels if isinstance(dels, np.ndarray) else np.full((rows, cols), dels, dtype=vt)
+                        assert np.array_equal(got, np.where(cnd != 0, tt, ee))
+    big = rng.standard_normal((5000, 8))
+    B_ = k.DenseMatrix.from_numpy(ctx, big)
+    v = B_.slice_rows(1000, 3000)
+    cnd = (rng.random((2000, 8)) < 0.5).astype(np.float64)
+    got = k.cond(k.DenseMatrix.from_numpy(ctx, cnd), v, -1.0).to_numpy()
+    assert np.array_equal(got, np.where(cnd != 0, big[1000:3000], -1.0))
+    with pytest.raises(k.Db2Error, match="CondMatMatMat: condition/then/else matrices must have the same shape"):
+        k.cond(k.DenseMatrix.from_numpy(ctx, cnd), B_, B_)
+    with pytest.raises(k.Db2Error, match="CondMatMatSca: condition/then matrices must have the same shape"):
+        k.cond(k.DenseMatrix.from_numpy(ctx, cnd), B_, 1.0)
