@@ -33,7 +33,7 @@ SUPPORTED_HEADERS = {"AggAll.h", "AggCol.h", "AggRow.h", "EwBinaryMat.h", "EwBin
 
 
 # backend-"CPP" extension: header -> opcodes to register (None: all of the entry's opcodes / no opcode)
-EXT_HEADERS = {"EwUnaryMat.h": None, "CTable.h": None, "OuterBinary.h": None, "CondMatMatMat.h": None,
+EXT_HEADERS = {"EwUnaryMat.h": None, "CTable.h": None, "OuterBinary.h": None, "AggCum.h": None, "CondMatMatMat.h": None,
                "CondMatMatSca.h": None, "CondMatScaMat.h": None, "CondMatScaSca.h": None,
                "AggRow.h": {"IDXMIN", "IDXMAX", "MEAN", "VAR", "STDDEV", "PROD"},
                "AggCol.h": {"IDXMIN", "IDXMAX", "MEAN", "VAR", "STDDEV", "PROD"},

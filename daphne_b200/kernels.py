@@ -294,6 +294,14 @@ def cond(cnd: DenseMatrix, then, els, dtype=None, ctx: Optional[Context] = None)
     return _res(ctx, h)
 
 
+def aggCum(op, arg: DenseMatrix, ctx: Optional[Context] = None) -> DenseMatrix:
+    """AggCum.h:39-42: cumulative SUM / PROD / MIN / MAX down the rows of every column."""
+    ctx = ctx or arg.ctx
+    h = C.c_void_p()
+    check(lib.db2_aggCum(ctx.handle, int(op), C.byref(h), arg.handle))
+    return _res(ctx, h)
+
+
 def colBind(lhs: DenseMatrix, rhs: DenseMatrix, ctx: Optional[Context] = None) -> DenseMatrix:
     """ColBind.h:41-44: [lhs | rhs]."""
     ctx = ctx or lhs.ctx

@@ -214,6 +214,14 @@ int db2k_extract_col(int dtype, const void *arg, int64_t ld, int64_t rows, const
 int db2k_cond(int dtype, int cond_dtype, const void *cond, int64_t cond_ld, const void *then_m, int64_t then_ld,
               const void *then_s, const void *else_m, int64_t else_ld, const void *else_s, int64_t rows, int64_t cols,
               void *res, int64_t res_ld, void *stream);
+/* Cumulative aggregation down the rows: res[0] = arg[0], res[r] = f(res[r-1], arg[r]) per column; op is the
+ * AggOpCode SUM (0), PROD (1), MIN (2) or MAX (3).  Blocked scan: floating-point sums / products are rounded in a
+ * different order than the sequential loop, MIN / MAX and integer types are exact.  `scratch`: device memory of
+ * db2k_agg_cum_scratch_bytes(rows, cols).  Replaces AggCum<Dense,Dense> (src/runtime/local/kernels/AggCum.h:48-86;
+ * no CUDA twin). */
+size_t db2k_agg_cum_scratch_bytes(int64_t rows, int64_t cols);
+int db2k_agg_cum(int dtype, int op, const void *arg, int64_t rows, int64_t cols, int64_t ld, void *res, int64_t res_ld,
+                 void *scratch, size_t scratch_bytes, void *stream);
 /* maximum of an int64 vector into a device int64 (used to size ctable results like CTable.h:79-84 does) */
 int db2k_max_i64(const void *vec, int64_t ld, int64_t n, void *dev_out, void *stream);
 /* Contingency table res[lhs[i], rhs[i]] += weight over int64 coordinate vectors (f64 result, overwritten).
@@ -318,6 +326,9 @@ int db2_outerBinary(db2_context *ctx, int op, db2_matrix **res, db2_matrix *lhs,
  * result, of the matrices and of the scalars; shape mismatches carry the reference's messages */
 int db2_cond(db2_context *ctx, db2_matrix **res, int dtype, db2_matrix *cond, db2_matrix *then_m, const void *then_s,
              db2_matrix *else_m, const void *else_s);
+/* cumulative SUM / PROD / MIN / MAX down the rows; any other opcode is the reference's "pure binary reduction" error
+ * (AggCum.h:50-52) */
+int db2_aggCum(db2_context *ctx, int op, db2_matrix **res, db2_matrix *arg);
 /* [lhs | rhs]; DB2_EINVAL with the reference's message when the row counts differ (ColBind.h:58-63) */
 int db2_colBind(db2_context *ctx, db2_matrix **res, db2_matrix *lhs, db2_matrix *rhs);
 /* the columns of arg named by the int64 column matrix sel; negative positions count from the end, anything outside

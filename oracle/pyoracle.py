@@ -247,6 +247,22 @@ def cond(cnd, then, els, dtype=np.float64) -> np.ndarray:
     return res
 
 
+def aggCum(op, arg) -> np.ndarray:
+    """AggCum<Dense,Dense> (src/runtime/local/kernels/AggCum.h:48-86): row 0 is copied, row r is f(result row r - 1,
+    argument row r) with f the scalar function of the opcode's binary twin (SUM -> ADD, PROD -> MUL, MIN, MAX)."""
+    twin = {0: 0, 1: 2, 2: 13, 3: 14}
+    if int(op) not in twin:
+        raise OracleError("the aggregation function used in aggCum must be a pure binary reduction")
+    arg = _mat(arg)
+    res = np.empty_like(arg)
+    if arg.shape[0] == 0:
+        return res
+    res[0] = arg[0]
+    for r in range(1, arg.shape[0]):
+        res[r] = ewBinaryMat(twin[int(op)], np.ascontiguousarray(res[r - 1:r]), np.ascontiguousarray(arg[r:r + 1]))
+    return res
+
+
 def colBind(lhs, rhs) -> np.ndarray:
     """ColBind<Dense,Dense,Dense> (src/runtime/local/kernels/ColBind.h:54-88): row r of the result is row r of lhs
     followed by row r of rhs; operands with different row counts are an error."""

@@ -182,7 +182,39 @@ def extract(root: Path):
     cases += _extract_seq(root)
     cases += _extract_reorg(root)
     cases += _extract_outer(root)
+    cases += _extract_aggcum(root)
     return cases, skipped
+
+
+def _extract_aggcum(root: Path):
+    """AggCumTest.cpp: one test case per opcode; every SECTION assigns arg and exp, the check follows the sections."""
+    path = root / "test/runtime/local/kernels/AggCumTest.cpp"
+    if not path.exists():
+        return []
+    text = _clean(path.read_text())
+    out = []
+    starts = [m.start() for m in re.finditer(r"TEMPLATE_PRODUCT_TEST_CASE\(", text)] + [len(text)]
+    for a, b in zip(starts, starts[1:]):
+        scope = text[a:b]
+        om = re.search(r"checkAggCum\(\s*AggOpCode::(\w+)", scope)
+        if not om:
+            continue
+        secs = list(SECTION_RE.finditer(scope))
+        for i, sm in enumerate(secs):
+            body = scope[sm.end(): secs[i + 1].start() if i + 1 < len(secs) else om.start()]
+            local = {}
+            for am in ASSIGN_RE.finditer(body):
+                name, dt, nrows, vals = am.groups()
+                try:
+                    local[name] = {"matrix": name, "dt": "DT", "rows": int(nrows),
+                                   "values": [_enc(v) for v in _split_values(vals)]}
+                except ValueError:
+                    pass
+            if {"arg", "exp"} <= set(local):
+                out.append({"file": "test/runtime/local/kernels/AggCumTest.cpp",
+                            "line": text.count("\n", 0, a + sm.start()) + 1, "test": sm.group(1)[:120],
+                            "check": "aggCum", "op": om.group(1), "args": [local["arg"], local["exp"]]})
+    return out
 
 
 OUTER_RE = re.compile(r"helper<TestType>\(\s*BinaryOpCode::(\w+)\s*,\s*\{([^}]*)\}\s*,\s*\{([^}]*)\}\s*,\s*\{([^}]*)\}\s*\)\s*;")

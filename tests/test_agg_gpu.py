@@ -157,3 +157,56 @@ def test_reduction_error_is_measured_against_an_exact_sum(ctx):
         exact = math.fsum(a[:, c].tolist())
         assert abs(got[c] - exact) <= RTOL_REDUCE_F64 * abs(exact)
         assert abs(seq[c] - exact) <= RTOL_REDUCE_F64 * abs(exact)
+
+
+def test_agg_cum_against_the_sequential_loop(ctx):
+    """AggCum.h:48-86: MIN / MAX and int64 are exact; f64 / f32 sums and products are blocked on the device, so they
+    are held to the error bound of a sum of that length in any order.  NaN handling of MIN / MAX: a NaN in
+    row 0 stays for the whole column, later NaNs are skipped; -0.0 in row 0 is copied."""
+    import daphne_b200.kernels as k
+    from oracle import pyoracle as o
+    rng = np.random.default_rng(51)
+    A = k.AggOpCode
+    shapes = [(1, 1), (5, 3), (1, 40), (300, 1), (4097, 33), (20000, 7), (70001, 2), (2000, 130)]
+    for dtype in (np.float64, np.int64, np.float32):
+        for rows, cols in shapes:
+            if dtype == np.int64:
+                x = rng.integers(-3, 4, size=(rows, cols)).astype(dtype)
+            else:
+                x = rng.standard_normal((rows, cols)).astype(dtype)
+            X = k.DenseMatrix.from_numpy(ctx, x)
+            for op in (A.SUM, A.MIN, A.MAX, A.PROD):
+                if op == A.PROD:
+                    xp = np.where(rng.random((rows, cols)) < 0.5, 1, -1).astype(dtype) if dtype == np.int64 else \
+                        (1.0 + 0.001 * x).astype(dtype)
+                    got = k.aggCum(op, k.DenseMatrix.from_numpy(ctx, xp)).to_numpy()
+                    exp = o.aggCum(int(op), xp)
+                else:
+                    got, exp = k.aggCum(op, X).to_numpy(), o.aggCum(int(op), x)
+                assert got.shape == exp.shape and got.dtype == exp.dtype
+                if dtype == np.int64 or op in (A.MIN, A.MAX):
+                    assert np.array_equal(got, exp), (dtype, rows, cols, op)
+                else:
+                    # classical bound of a length-n sum / product in any order: n * eps * magnitude, against the
+                    # double-precision result of the same inputs
+                    src = (xp if op == A.PROD else x).astype(np.float64)
+                    exact = np.cumprod(src, axis=0) if op == A.PROD else np.cumsum(src, axis=0)
+                    tol = rows * np.finfo(dtype).eps * max(1.0, np.abs(src).cumsum(axis=0).max() if op == A.SUM
+                                                           else np.abs(exact).max())
+                    assert np.abs(got.astype(np.float64) - exact).max() <= tol, (dtype, rows, cols, op)
+                    assert np.abs(exp.astype(np.float64) - exact).max() <= tol, "the sequential loop meets it too"
+    x = rng.standard_normal((5000, 4))
+    x[0, 1] = np.nan          # whole column NaN for MIN / MAX
+    x[700, 2] = np.nan        # skipped
+    x[0, 3] = -0.0
+    x[1:, 3] = np.abs(x[1:, 3])
+    X = k.DenseMatrix.from_numpy(ctx, x)
+    for op in (A.MIN, A.MAX):
+        got, exp = k.aggCum(op, X).to_numpy(), o.aggCum(int(op), x)
+        assert np.array_equal(np.isnan(got), np.isnan(exp)) and np.array_equal(np.nan_to_num(got), np.nan_to_num(exp))
+    got = k.aggCum(A.SUM, X).to_numpy()
+    assert np.signbit(got[0, 3]) and np.isnan(got[700:, 2]).all() and not np.isnan(got[:700, 2]).any()
+    v = X.slice_rows(1000, 4000)
+    assert np.array_equal(k.aggCum(A.MAX, v).to_numpy()[:, 0], np.maximum.accumulate(x[1000:4000, 0]))
+    with pytest.raises(k.Db2Error, match="pure binary reduction"):
+        k.aggCum(A.MEAN, X)

@@ -20,7 +20,7 @@ AGG = {n: i for i, n in enumerate(["SUM", "PROD", "MIN", "MAX", "IDXMIN", "IDXMA
 
 DENSE_CHECKS = {"checkAggRow", "checkAggCol", "checkAggAll", "checkEwBinaryMat", "checkEwUnaryMat",
                 "checkEwUnaryMatApprox", "checkEwUnaryMatThrow", "checkEwBinaryObjSca", "checkMatMul", "checkSyrk",
-                "solveNormalEquations", "ctableSection", "transposeSection", "checkSeq", "checkDiagMatrix", "colBind", "extractCol", "extractColThrow", "outerBinary"}
+                "solveNormalEquations", "ctableSection", "transposeSection", "checkSeq", "checkDiagMatrix", "colBind", "extractCol", "extractColThrow", "outerBinary", "aggCum"}
 
 
 def _num(v):
@@ -71,6 +71,7 @@ class _OracleBackend:
     def seq(self, start, end, inc): return self.o.seq(start, end, inc)
     def col_bind(self, a, b): return self.o.colBind(a, b)
     def outer(self, op, a, b): return self.o.outerBinary(op, a, b)
+    def agg_cum(self, op, a): return self.o.aggCum(op, a)
     def extract_col(self, a, sel): return self.o.extractCol(a, sel)
     diag = None  # DiagMatrix has no restatement in the oracle: a diagonal copy, checked on the device only
 
@@ -101,6 +102,7 @@ class _CudaBackend:
     def seq(self, start, end, inc): return self.k.seq(self.ctx, start, end, inc).to_numpy()
     def col_bind(self, a, b): return self.k.colBind(self._m(a), self._m(b)).to_numpy()
     def outer(self, op, a, b): return self.k.outerBinary(op, self._m(a), self._m(b)).to_numpy()
+    def agg_cum(self, op, a): return self.k.aggCum(op, self._m(a)).to_numpy()
     def extract_col(self, a, sel): return self.k.extractCol(self._m(a), self._m(sel)).to_numpy()
     def diag(self, a): return self.k.diagMatrix(self._m(a)).to_numpy()
 
@@ -168,6 +170,10 @@ def _run_case(be, c):
             arg, exp = _mat(args[0]), _mat(args[1])
             got = be.diag(arg)
             assert got.shape == exp.shape and np.array_equal(got, exp), f"{c['file']}:{c['line']}"
+    elif chk == "aggCum":  # AggCumTest.cpp:33-37 (small integer-valued literals: exact)
+        arg, exp = (_mat(a) for a in args)
+        got = be.agg_cum(AGG[op], arg)
+        assert got.shape == exp.shape and np.array_equal(got, exp), f"{c['file']}:{c['line']}"
     elif chk == "outerBinary":  # OuterBinaryTest.cpp:39-60
         lhs, rhs, exp = (_mat(a) for a in args)
         got = be.outer(BIN[op], lhs, rhs)
