@@ -8,8 +8,8 @@
 //           registers, folds them, the chunk's TY partial values are scanned through shared memory on top of the
 //           running carry, and the thread writes its 16 results from the registers            (8 B read + 8 B written)
 // Threads of a warp lie along the columns (coalesced rows) for matrices of 32 and more columns; narrower matrices put
-// several row groups into a warp, whose strided 8-byte accesses meet again in L1 (every line is used completely by the
-// 16 loads of a chunk).
+// several row groups into a warp: contiguous ones of a power-of-two width go through shared memory (see STAGE), the
+// others rely on L1 (every line is used completely by the 16 loads of a chunk).
 // Folding is f(running, x) started from the operation's identity: -0.0 for SUM (so that the first row is a copy
 // even of -0.0), 1 for PROD, +-inf / the integer limits for MIN / MAX.  MIN / MAX follow the reference's comparisons
 // (std::min / std::max: a NaN argument never replaces the running value, a NaN in row 0 stays for the whole column).
@@ -35,6 +35,12 @@ template <typename VT, int KIND> struct CumOp {
         else
             return KIND == CUM_MIN ? std::numeric_limits<VT>::max() : std::numeric_limits<VT>::lowest();
     }
+    __device__ static VT nan() {
+        if constexpr (std::is_floating_point<VT>::value)
+            return (VT)NAN;
+        else
+            return (VT)0; // never used: only floating-point columns can start with a NaN
+    }
     __device__ static VT apply(VT run, VT x) {
         if constexpr (KIND == CUM_SUM) {
             if constexpr (std::is_same<VT, double>::value)
@@ -58,13 +64,19 @@ template <typename VT, int KIND> struct CumOp {
 };
 
 // WRITE = false: part[b][c] = fold of CTA b's rows.  WRITE = true: results, starting from the prefixes in part.
-template <typename VT, int KIND, bool WRITE>
+// STAGE: the matrix is contiguous and its width is the power of two tx_n < 32.  A chunk (CUM_THREADS * CUM_LS
+// consecutive elements) then goes through shared memory, so that global loads and stores are consecutive per lane
+// while every thread still owns CUM_LS consecutive rows of its column (one padding slot per thread's run keeps the
+// strided shared accesses conflict free).
+template <typename VT, int KIND, bool WRITE, bool STAGE>
 __global__ void __launch_bounds__(CUM_THREADS)
     agg_cum_kernel(const VT *__restrict__ arg, int64_t rows, int64_t cols, int64_t ld, int64_t rows_per_cta, int tx_n,
                    VT *__restrict__ part, VT *__restrict__ res, int64_t res_ld) {
     using Op = CumOp<VT, KIND>;
     __shared__ VT agg[CUM_THREADS];
     __shared__ VT carry[32];
+    __shared__ VT stage[STAGE ? CUM_THREADS * CUM_LS + CUM_THREADS : 1];
+    auto padded = [&](int e) { return e + e / (CUM_LS * tx_n); };
     const int ty_n = CUM_THREADS / tx_n, tx = threadIdx.x % tx_n, ty = threadIdx.x / tx_n;
     const int64_t r_begin = (int64_t)blockIdx.x * rows_per_cta;
     const int64_t r_end = r_begin + rows_per_cta < rows ? r_begin + rows_per_cta : rows;
@@ -84,9 +96,23 @@ __global__ void __launch_bounds__(CUM_THREADS)
         for (int64_t r0 = r_begin; r0 < r_end; r0 += (int64_t)ty_n * CUM_LS) {
             const int64_t my = r0 + (int64_t)ty * CUM_LS;
             VT x[CUM_LS];
+            if constexpr (STAGE) {
+                const VT *base = arg + r0 * ld; // ld == cols == tx_n: the chunk is one run of elements
+                const int64_t left = (r_end - r0) * tx_n;
 #pragma unroll
-            for (int i = 0; i < CUM_LS; i++)
-                x[i] = (col_ok && my + i < r_end) ? arg[(my + i) * ld + c] : Op::identity();
+                for (int i = 0; i < CUM_LS; i++) {
+                    const int e = i * CUM_THREADS + threadIdx.x;
+                    stage[padded(e)] = e < left ? base[e] : Op::identity();
+                }
+                __syncthreads();
+#pragma unroll
+                for (int i = 0; i < CUM_LS; i++)
+                    x[i] = stage[padded((ty * CUM_LS + i) * tx_n + tx)];
+            } else {
+#pragma unroll
+                for (int i = 0; i < CUM_LS; i++)
+                    x[i] = (col_ok && my + i < r_end) ? arg[(my + i) * ld + c] : Op::identity();
+            }
             VT local = Op::identity();
 #pragma unroll
             for (int i = 0; i < CUM_LS; i++)
@@ -96,16 +122,32 @@ __global__ void __launch_bounds__(CUM_THREADS)
             VT pre = carry[tx];
             for (int j = 0; j < ty; j++)
                 pre = Op::apply(pre, agg[j * tx_n + tx]);
-            if constexpr (WRITE) {
+            if constexpr (WRITE && STAGE) {
+                VT run = pre;
+#pragma unroll
+                for (int i = 0; i < CUM_LS; i++) {
+                    run = Op::apply(run, x[i]);
+                    stage[padded((ty * CUM_LS + i) * tx_n + tx)] = poison ? Op::nan() : run;
+                }
+                __syncthreads();
+                VT *out = res + r0 * res_ld;
+                const int64_t left = (r_end - r0) * tx_n;
+#pragma unroll
+                for (int i = 0; i < CUM_LS; i++) {
+                    const int e = i * CUM_THREADS + threadIdx.x;
+                    if (e < left)
+                        out[e] = stage[padded(e)];
+                }
+            } else if constexpr (WRITE) {
                 VT run = pre;
 #pragma unroll
                 for (int i = 0; i < CUM_LS; i++) {
                     run = Op::apply(run, x[i]);
                     if (col_ok && my + i < r_end)
-                        res[(my + i) * res_ld + c] = poison ? (VT)NAN : run;
+                        res[(my + i) * res_ld + c] = poison ? Op::nan() : run;
                 }
             }
-            __syncthreads(); // everybody has read carry[] and agg[]
+            __syncthreads(); // everybody has read carry[], agg[] and the staged chunk
             if (ty == ty_n - 1)
                 carry[tx] = Op::apply(pre, local);
             // the next turn's barrier (after agg[] is written) orders this store before its readers
@@ -118,19 +160,48 @@ __global__ void __launch_bounds__(CUM_THREADS)
     }
 }
 
-// part[b][c] (fold of CTA b) -> exclusive prefix over b, in place; loads do not depend on the running value
+// part[b][c] (fold of CTA b) -> exclusive prefix over b, in place.  One block per column: thread t owns a run of
+// consecutive b (loaded at once), the runs' folds are scanned through shared memory, then every thread writes the
+// prefixes of its run.  (A single thread walking all b would pay one global round trip per step.)
 template <typename VT, int KIND>
-__global__ void agg_cum_prefix_kernel(VT *__restrict__ part, int nb, int64_t cols) {
+__global__ void __launch_bounds__(256) agg_cum_prefix_kernel(VT *__restrict__ part, int nb, int64_t cols) {
     using Op = CumOp<VT, KIND>;
-    const int64_t c = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (c >= cols)
-        return;
-    VT run = Op::identity();
-#pragma unroll 4
-    for (int b = 0; b < nb; b++) {
-        const VT p = part[(int64_t)b * cols + c];
-        part[(int64_t)b * cols + c] = run;
-        run = Op::apply(run, p);
+    constexpr int MAXS = 8; // nb <= 8 * 148 CTAs of the scan kernels: at most 5 per thread; more are walked in turns
+    __shared__ VT fold[256];
+    __shared__ VT carry;
+    const int64_t c = blockIdx.x;
+    const int t = threadIdx.x;
+    if (t == 0)
+        carry = Op::identity();
+    for (int b0 = 0; b0 < nb; b0 += 256 * MAXS) {
+        const int left = nb - b0 < 256 * MAXS ? nb - b0 : 256 * MAXS;
+        const int per = (left + 255) / 256;
+        VT v[MAXS];
+        VT local = Op::identity();
+#pragma unroll
+        for (int i = 0; i < MAXS; i++) {
+            const int b = b0 + t * per + i;
+            v[i] = (i < per && t * per + i < left) ? part[(int64_t)b * cols + c] : Op::identity();
+        }
+#pragma unroll
+        for (int i = 0; i < MAXS; i++)
+            local = Op::apply(local, v[i]);
+        fold[t] = local;
+        __syncthreads();
+        VT run = carry;
+        for (int j = 0; j < t; j++)
+            run = Op::apply(run, fold[j]);
+#pragma unroll
+        for (int i = 0; i < MAXS; i++) {
+            const int b = b0 + t * per + i;
+            if (i < per && t * per + i < left)
+                part[(int64_t)b * cols + c] = run;
+            run = Op::apply(run, v[i]);
+        }
+        __syncthreads();
+        if (t == 255)
+            carry = run;
+        __syncthreads();
     }
 }
 
@@ -161,13 +232,22 @@ template <typename VT, int KIND>
 static int agg_cum_impl(const VT *arg, int64_t rows, int64_t cols, int64_t ld, VT *res, int64_t res_ld, VT *part,
                         cudaStream_t st) {
     const CumPlan p = cum_plan(rows, cols);
-    agg_cum_kernel<VT, KIND, false><<<p.nb, CUM_THREADS, 0, st>>>(arg, rows, cols, ld, p.rows_per_cta, p.tx_n, part,
-                                                                   nullptr, 0);
+    const bool stage = p.tx_n < 32 && cols == p.tx_n && ld == cols && res_ld == cols;
+    if (stage)
+        agg_cum_kernel<VT, KIND, false, true><<<p.nb, CUM_THREADS, 0, st>>>(arg, rows, cols, ld, p.rows_per_cta, p.tx_n,
+                                                                             part, nullptr, 0);
+    else
+        agg_cum_kernel<VT, KIND, false, false><<<p.nb, CUM_THREADS, 0, st>>>(arg, rows, cols, ld, p.rows_per_cta,
+                                                                              p.tx_n, part, nullptr, 0);
     DB2_TRY(after_launch("agg_cum_kernel"));
-    agg_cum_prefix_kernel<VT, KIND><<<(unsigned)((cols + 127) / 128), 128, 0, st>>>(part, p.nb, cols);
+    agg_cum_prefix_kernel<VT, KIND><<<(unsigned)cols, 256, 0, st>>>(part, p.nb, cols);
     DB2_TRY(after_launch("agg_cum_prefix_kernel"));
-    agg_cum_kernel<VT, KIND, true><<<p.nb, CUM_THREADS, 0, st>>>(arg, rows, cols, ld, p.rows_per_cta, p.tx_n, part, res,
-                                                                  res_ld);
+    if (stage)
+        agg_cum_kernel<VT, KIND, true, true><<<p.nb, CUM_THREADS, 0, st>>>(arg, rows, cols, ld, p.rows_per_cta, p.tx_n,
+                                                                            part, res, res_ld);
+    else
+        agg_cum_kernel<VT, KIND, true, false><<<p.nb, CUM_THREADS, 0, st>>>(arg, rows, cols, ld, p.rows_per_cta, p.tx_n,
+                                                                             part, res, res_ld);
     return after_launch("agg_cum_kernel");
 }
 
