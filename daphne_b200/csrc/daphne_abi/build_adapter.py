@@ -33,7 +33,7 @@ SUPPORTED_HEADERS = {"AggAll.h", "AggCol.h", "AggRow.h", "EwBinaryMat.h", "EwBin
 
 
 # backend-"CPP" extension: header -> opcodes to register (None: all of the entry's opcodes / no opcode)
-EXT_HEADERS = {"EwUnaryMat.h": None, "CTable.h": None, "OuterBinary.h": None, "AggCum.h": None, "CondMatMatMat.h": None,
+EXT_HEADERS = {"EwUnaryMat.h": None, "CTable.h": None, "OuterBinary.h": None, "AggCum.h": None, "OneHot.h": None, "CondMatMatMat.h": None,
                "CondMatMatSca.h": None, "CondMatScaMat.h": None, "CondMatScaSca.h": None,
                "AggRow.h": {"IDXMIN", "IDXMAX", "MEAN", "VAR", "STDDEV", "PROD"},
                "AggCol.h": {"IDXMIN", "IDXMAX", "MEAN", "VAR", "STDDEV", "PROD"},
@@ -57,6 +57,8 @@ def _ext_instantiation_ok(header: str, inst) -> bool:
         if len(vts) < 2 or vts[0] not in DEVICE_VTS or vts[1] not in ("double", "int64_t"):
             return False
         return all(v == vts[0] for v in vts[2:]) and all(sc == vts[0] for sc in scalars)
+    if header == "OneHot.h":  # DTRes, DTArg: double or int64
+        return len(vts) == 2 and vts[0] == vts[1] and vts[0] in ("double", "int64_t")
     if header == "OuterBinary.h":  # DTRes, DTLhs, DTRhs of one value type
         return len(vts) == 3 and len(set(vts)) == 1 and vts[0] in DEVICE_VTS
     if header == "AggAll.h":  # VTRes, DTArg

@@ -1,4 +1,4 @@
-// Reorganisation kernels: ColBind, ExtractCol and the conditional select (Cond*).
+// Reorganisation kernels: ColBind, ExtractCol, the conditional select (Cond*) and OneHot.
 //
 // Both are pure copies (16 bytes of traffic per 8-byte element), so the only thing that matters is that every warp
 // moves whole rows with its lanes side by side (coalesced on both ends) and has several rows in flight:
@@ -94,6 +94,44 @@ __global__ void __launch_bounds__(RG_THREADS)
     }
 }
 
+// One-hot encoding (src/runtime/local/kernels/OneHot.h:54-110): result column j either copies argument column
+// src[j] (hot[j] < 0) or is 1 where the argument value, cut to an integer, equals hot[j] and 0 elsewhere.  `width[j]`
+// is the size of the block column j belongs to (only read where hot[j] == 0: that lane checks the value's range and
+// raises *status, the reference's out_of_range).
+template <typename VT>
+__global__ void __launch_bounds__(RG_THREADS)
+    one_hot_kernel(const VT *__restrict__ arg, int64_t ld, int64_t rows, const int64_t *__restrict__ src,
+                   const int64_t *__restrict__ hot, const int64_t *__restrict__ width, int64_t cols_res,
+                   VT *__restrict__ res, int64_t ld_o, int32_t *__restrict__ status) {
+    const int lane = threadIdx.x % 32;
+    const int64_t warp = ((int64_t)blockIdx.x * RG_THREADS + threadIdx.x) / 32;
+    const int64_t nwarps = (int64_t)gridDim.x * (RG_THREADS / 32);
+    bool bad = false;
+    for (int64_t r0 = warp * RG_ROWS; r0 < rows; r0 += nwarps * RG_ROWS) {
+        for (int64_t c = lane; c < cols_res; c += 32) {
+            const int64_t s = src[c], h = hot[c];
+            const int64_t w = h == 0 ? width[c] : 0;
+#pragma unroll
+            for (int u = 0; u < RG_ROWS; u++)
+                if (r0 + u < rows) {
+                    const VT v = arg[(r0 + u) * ld + s];
+                    VT out = v;
+                    if (h >= 0) {
+                        // the reference converts to size_t: negative values and NaN cannot name a position
+                        const bool in_range = v >= (VT)0 && v < (VT)9.2e18;
+                        const int64_t k = in_range ? (int64_t)v : -1;
+                        out = (k == h) ? (VT)1 : (VT)0;
+                        if (h == 0 && (k < 0 || k >= w))
+                            bad = true;
+                    }
+                    res[(r0 + u) * ld_o + c] = out;
+                }
+        }
+    }
+    if (bad)
+        atomicExch(status, 1);
+}
+
 static void count(db2_context *ctx, uint64_t before) {
     std::lock_guard<std::mutex> lock(ctx->mu);
     ctx->stats.launches += g_launches.load(std::memory_order_relaxed) - before;
@@ -180,6 +218,81 @@ int db2_cond(db2_context *ctx, db2_matrix **res, int dtype, db2_matrix *cond, db
                       then_m ? then_m->dev_ld : 0, then_s, else_m ? else_m->dev_ptr() : nullptr,
                       else_m ? else_m->dev_ld : 0, else_s, cond->rows, cond->cols, (*res)->dev_ptr(), (*res)->dev_ld,
                       ctx->stream));
+    count(ctx, before);
+    return DB2_OK;
+    DB2_API_END
+}
+
+int db2k_one_hot(int dtype, const void *arg, int64_t ld, int64_t rows, const void *dev_src, const void *dev_hot,
+                 const void *dev_width, int64_t cols_res, void *res, int64_t res_ld, void *dev_status, void *stream) {
+    DB2_CHECK(rows >= 0 && cols_res >= 0, DB2_EINVAL, "negative shape");
+    DB2_CHECK(dtype == DB2_F64 || dtype == DB2_I64, DB2_EUNSUPPORTED, "OneHot: double and int64 values only");
+    if (rows == 0 || cols_res == 0)
+        return DB2_OK;
+    const int grid = reorg_grid(rows);
+    if (dtype == DB2_F64)
+        one_hot_kernel<double><<<grid, RG_THREADS, 0, as_stream(stream)>>>(
+            static_cast<const double *>(arg), ld, rows, static_cast<const int64_t *>(dev_src),
+            static_cast<const int64_t *>(dev_hot), static_cast<const int64_t *>(dev_width), cols_res,
+            static_cast<double *>(res), res_ld, static_cast<int32_t *>(dev_status));
+    else
+        one_hot_kernel<int64_t><<<grid, RG_THREADS, 0, as_stream(stream)>>>(
+            static_cast<const int64_t *>(arg), ld, rows, static_cast<const int64_t *>(dev_src),
+            static_cast<const int64_t *>(dev_hot), static_cast<const int64_t *>(dev_width), cols_res,
+            static_cast<int64_t *>(res), res_ld, static_cast<int32_t *>(dev_status));
+    return after_launch("one_hot_kernel");
+}
+
+int db2_oneHot(db2_context *ctx, db2_matrix **res, db2_matrix *arg, db2_matrix *info) {
+    DB2_API_BEGIN
+    DB2_CHECK(ctx && res && arg && info, DB2_EINVAL, "null argument");
+    DB2_CHECK(info->dtype == DB2_I64, DB2_EUNSUPPORTED, "OneHot: parameter 'info' must be an int64 matrix");
+    DB2_CHECK(info->rows == 1, DB2_EINVAL, "OneHot - parameter 'info' must be a row matrix");
+    DB2_CHECK(info->cols == arg->cols, DB2_EINVAL,
+              "OneHot - parameter 'info' must provide information for each column of parameter arg");
+    bind_device(ctx);
+    const uint64_t before = g_launches.load();
+    std::vector<int64_t> inf((size_t)info->cols);
+    if (info->cols > 0)
+        DB2_TRY(db2_matrix_to_host(info, inf.data(), info->cols));
+    std::vector<int64_t> table; // [src | hot | width], cols_res entries each
+    std::vector<int64_t> src, hot, width;
+    for (int64_t c = 0; c < arg->cols; c++) {
+        const int64_t n = inf[(size_t)c];
+        DB2_CHECK(n >= -1, DB2_EINVAL, "OneHot: parameter 'info' must be an integer greater or equal than -1");
+        if (n == -1) {
+            src.push_back(c), hot.push_back(-1), width.push_back(0);
+        } else {
+            DB2_CHECK((int64_t)src.size() + n <= ((int64_t)1 << 31), DB2_EUNSUPPORTED, "OneHot: result too wide");
+            for (int64_t k = 0; k < n; k++)
+                src.push_back(c), hot.push_back(k), width.push_back(n);
+        }
+    }
+    const int64_t cols_res = (int64_t)src.size();
+    DB2_CHECK(cols_res > 0, DB2_EINVAL, "OneHot: parameter 'info' must contain at least one non-zero entry");
+    DB2_TRY(ensure_device(arg));
+    DB2_TRY(prepare_result(ctx, res, arg->dtype, arg->rows, cols_res));
+    if (arg->rows > 0) {
+        table.reserve((size_t)cols_res * 3);
+        table.insert(table.end(), src.begin(), src.end());
+        table.insert(table.end(), hot.begin(), hot.end());
+        table.insert(table.end(), width.begin(), width.end());
+        void *dev = nullptr;
+        const size_t tb = (size_t)cols_res * 3 * 8;
+        DB2_TRY(ctx_scratch(ctx, tb + 16, &dev));
+        int32_t *status = reinterpret_cast<int32_t *>(static_cast<char *>(dev) + tb);
+        DB2_CUDA(cudaMemcpyAsync(dev, table.data(), tb, cudaMemcpyHostToDevice, ctx->stream));
+        DB2_CUDA(cudaMemsetAsync(status, 0, 4, ctx->stream));
+        const int64_t *t = static_cast<const int64_t *>(dev);
+        DB2_TRY(db2k_one_hot(arg->dtype, arg->dev_ptr(), arg->dev_ld, arg->rows, t, t + cols_res, t + 2 * cols_res,
+                             cols_res, (*res)->dev_ptr(), (*res)->dev_ld, status, ctx->stream));
+        int32_t flag = 0; // the reference throws on a value outside its block: the status is read before returning
+        DB2_CUDA(cudaMemcpyAsync(&flag, status, 4, cudaMemcpyDeviceToHost, ctx->stream));
+        DB2_CUDA(cudaStreamSynchronize(ctx->stream));
+        DB2_CHECK(flag == 0, DB2_EDOMAIN,
+                  "OneHot: arg values that are encoded (info value != -1) must be positive and smaller than the "
+                  "corresponding info value");
+    }
     count(ctx, before);
     return DB2_OK;
     DB2_API_END

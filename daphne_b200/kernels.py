@@ -302,6 +302,14 @@ def aggCum(op, arg: DenseMatrix, ctx: Optional[Context] = None) -> DenseMatrix:
     return _res(ctx, h)
 
 
+def oneHot(arg: DenseMatrix, info: DenseMatrix, ctx: Optional[Context] = None) -> DenseMatrix:
+    """OneHot.h:43-46: info (1 x cols, int64) says per column: -1 keep, 0 drop, k > 0 expand into k indicators."""
+    ctx = ctx or arg.ctx
+    h = C.c_void_p()
+    check(lib.db2_oneHot(ctx.handle, C.byref(h), arg.handle, info.handle))
+    return _res(ctx, h)
+
+
 def colBind(lhs: DenseMatrix, rhs: DenseMatrix, ctx: Optional[Context] = None) -> DenseMatrix:
     """ColBind.h:41-44: [lhs | rhs]."""
     ctx = ctx or lhs.ctx

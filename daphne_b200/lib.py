@@ -81,6 +81,7 @@ _SIGS = {
     "db2k_cond": (i32, [i32, i32, vp, i64, vp, i64, vp, vp, i64, vp, i64, i64, vp, i64, vp]),
     "db2k_agg_cum_scratch_bytes": (sz, [i64, i64]),
     "db2k_agg_cum": (i32, [i32, i32, vp, i64, i64, i64, vp, i64, vp, sz, vp]),
+    "db2k_one_hot": (i32, [i32, vp, i64, i64, vp, vp, vp, i64, vp, i64, vp, vp]),
     "db2k_col_bind": (i32, [i32, vp, i64, i64, vp, i64, i64, i64, vp, i64, vp]),
     "db2k_extract_col": (i32, [i32, vp, i64, i64, vp, i64, vp, i64, vp]),
     "db2k_max_i64": (i32, [vp, i64, i64, vp, vp]),
@@ -124,6 +125,7 @@ _SIGS = {
     "db2_seq": (i32, [vp, _P(vp), i32, vp, vp, vp]),
     "db2_diagMatrix": (i32, [vp, _P(vp), vp]),
     "db2_colBind": (i32, [vp, _P(vp), vp, vp]),
+    "db2_oneHot": (i32, [vp, _P(vp), vp, vp]),
     "db2_aggCum": (i32, [vp, i32, _P(vp), vp]),
     "db2_cond": (i32, [vp, _P(vp), i32, vp, vp, vp, vp, vp]),
     "db2_outerBinary": (i32, [vp, i32, _P(vp), vp, vp]),

@@ -222,6 +222,12 @@ int db2k_cond(int dtype, int cond_dtype, const void *cond, int64_t cond_ld, cons
 size_t db2k_agg_cum_scratch_bytes(int64_t rows, int64_t cols);
 int db2k_agg_cum(int dtype, int op, const void *arg, int64_t rows, int64_t cols, int64_t ld, void *res, int64_t res_ld,
                  void *scratch, size_t scratch_bytes, void *stream);
+/* One-hot encoding with a prepared column table on the device: result column j copies argument column src[j] when
+ * hot[j] < 0, else it is (integer part of arg[:, src[j]] == hot[j]); width[j] = size of j's block; *dev_status is set
+ * to 1 when a value lies outside its block.  f64 and int64.  Replaces OneHot<Dense,Dense>
+ * (src/runtime/local/kernels/OneHot.h:54-110; no CUDA twin). */
+int db2k_one_hot(int dtype, const void *arg, int64_t ld, int64_t rows, const void *dev_src, const void *dev_hot,
+                 const void *dev_width, int64_t cols_res, void *res, int64_t res_ld, void *dev_status, void *stream);
 /* maximum of an int64 vector into a device int64 (used to size ctable results like CTable.h:79-84 does) */
 int db2k_max_i64(const void *vec, int64_t ld, int64_t n, void *dev_out, void *stream);
 /* Contingency table res[lhs[i], rhs[i]] += weight over int64 coordinate vectors (f64 result, overwritten).
@@ -329,6 +335,9 @@ int db2_cond(db2_context *ctx, db2_matrix **res, int dtype, db2_matrix *cond, db
 /* cumulative SUM / PROD / MIN / MAX down the rows; any other opcode is the reference's "pure binary reduction" error
  * (AggCum.h:50-52) */
 int db2_aggCum(db2_context *ctx, int op, db2_matrix **res, db2_matrix *arg);
+/* info (1 x cols, int64): -1 keeps a column, 0 drops it, k > 0 expands it into k indicator columns; the reference's
+ * messages for a bad info and for values outside their block (DB2_EDOMAIN; OneHot.h:57-101) */
+int db2_oneHot(db2_context *ctx, db2_matrix **res, db2_matrix *arg, db2_matrix *info);
 /* [lhs | rhs]; DB2_EINVAL with the reference's message when the row counts differ (ColBind.h:58-63) */
 int db2_colBind(db2_context *ctx, db2_matrix **res, db2_matrix *lhs, db2_matrix *rhs);
 /* the columns of arg named by the int64 column matrix sel; negative positions count from the end, anything outside

@@ -263,6 +263,38 @@ def aggCum(op, arg) -> np.ndarray:
     return res
 
 
+def oneHot(arg, info) -> np.ndarray:
+    """OneHot<Dense,Dense> (src/runtime/local/kernels/OneHot.h:54-110)."""
+    arg, info = _mat(arg), np.asarray(info)
+    if info.ndim != 2 or info.shape[0] != 1:
+        raise OracleError("OneHot - parameter 'info' must be a row matrix")
+    if info.shape[1] != arg.shape[1]:
+        raise OracleError("OneHot - parameter 'info' must provide information for each column of parameter arg")
+    if (info < -1).any():
+        raise OracleError("OneHot: parameter 'info' must be an integer greater or equal than -1")
+    width = int(sum(1 if n == -1 else n for n in info[0]))
+    if width == 0:
+        raise OracleError("OneHot: parameter 'info' must contain at least one non-zero entry")
+    res = np.empty((arg.shape[0], width), dtype=arg.dtype)
+    for r in range(arg.shape[0]):
+        c_res = 0
+        for c_arg in range(arg.shape[1]):
+            n = int(info[0, c_arg])
+            if n == -1:
+                res[r, c_res] = arg[r, c_arg]
+                c_res += 1
+            elif n != 0:
+                res[r, c_res:c_res + n] = 0
+                v = arg[r, c_arg]
+                k = int(v) if v == v and v >= 0 else -1  # static_cast<size_t>: negatives / NaN name no position
+                if not 0 <= k < n:
+                    raise OracleError("OneHot: arg values that are encoded (info value != -1) must be positive and "
+                                      "smaller than the corresponding info value")
+                res[r, c_res + k] = 1
+                c_res += n
+    return res
+
+
 def colBind(lhs, rhs) -> np.ndarray:
     """ColBind<Dense,Dense,Dense> (src/runtime/local/kernels/ColBind.h:54-88): row r of the result is row r of lhs
     followed by row r of rhs; operands with different row counts are an error."""

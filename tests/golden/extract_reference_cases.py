@@ -183,7 +183,46 @@ def extract(root: Path):
     cases += _extract_reorg(root)
     cases += _extract_outer(root)
     cases += _extract_aggcum(root)
+    cases += _extract_onehot(root)
     return cases, skipped
+
+
+ANY_GEN_RE = re.compile(r"(\w+)\s*=\s*genGivenVals<([^;(]*)>\(\s*(\d+)\s*,\s*\{(.*?)\}\s*\)\s*;", re.S)
+
+
+def _extract_onehot(root: Path):
+    """OneHotTest.cpp, numeric test case: one arg, per SECTION an info row and either an expected matrix or an
+    expected exception."""
+    path = root / "test/runtime/local/kernels/OneHotTest.cpp"
+    if not path.exists():
+        return []
+    text = _clean(path.read_text())
+    a = text.find('TEMPLATE_PRODUCT_TEST_CASE("OneHot"')
+    b = text.find('TEMPLATE_PRODUCT_TEST_CASE("OneHot"', a + 40)
+    scope = text[a:b if b > a else len(text)]
+    m = ANY_GEN_RE.search(scope)
+    if not m or m.group(1) != "arg":
+        return []
+    arg = {"matrix": "arg", "dt": "DTArg", "rows": int(m.group(3)), "values": [_enc(v) for v in _split_values(m.group(4))]}
+    out = []
+    secs = list(SECTION_RE.finditer(scope))
+    for i, sm in enumerate(secs):
+        body = scope[sm.end(): secs[i + 1].start() if i + 1 < len(secs) else len(scope)]
+        local = {}
+        for am in ANY_GEN_RE.finditer(body):
+            name, dt, nrows, vals = am.groups()
+            local[name] = {"matrix": name, "dt": re.sub(r"\s+", "", dt), "rows": int(nrows),
+                           "values": [_enc(v) for v in _split_values(vals)]}
+        if "info" not in local:
+            continue
+        line = text.count("\n", 0, a + sm.start()) + 1
+        if "REQUIRE_THROWS_AS" in body:
+            out.append({"file": "test/runtime/local/kernels/OneHotTest.cpp", "line": line, "test": sm.group(1)[:120],
+                        "check": "oneHotThrow", "op": None, "args": [arg, local["info"]]})
+        elif "exp" in local:
+            out.append({"file": "test/runtime/local/kernels/OneHotTest.cpp", "line": line, "test": sm.group(1)[:120],
+                        "check": "oneHot", "op": None, "args": [arg, local["info"], local["exp"]]})
+    return out
 
 
 def _extract_aggcum(root: Path):

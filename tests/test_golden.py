@@ -20,7 +20,7 @@ AGG = {n: i for i, n in enumerate(["SUM", "PROD", "MIN", "MAX", "IDXMIN", "IDXMA
 
 DENSE_CHECKS = {"checkAggRow", "checkAggCol", "checkAggAll", "checkEwBinaryMat", "checkEwUnaryMat",
                 "checkEwUnaryMatApprox", "checkEwUnaryMatThrow", "checkEwBinaryObjSca", "checkMatMul", "checkSyrk",
-                "solveNormalEquations", "ctableSection", "transposeSection", "checkSeq", "checkDiagMatrix", "colBind", "extractCol", "extractColThrow", "outerBinary", "aggCum"}
+                "solveNormalEquations", "ctableSection", "transposeSection", "checkSeq", "checkDiagMatrix", "colBind", "extractCol", "extractColThrow", "outerBinary", "aggCum", "oneHot", "oneHotThrow"}
 
 
 def _num(v):
@@ -72,6 +72,7 @@ class _OracleBackend:
     def col_bind(self, a, b): return self.o.colBind(a, b)
     def outer(self, op, a, b): return self.o.outerBinary(op, a, b)
     def agg_cum(self, op, a): return self.o.aggCum(op, a)
+    def one_hot(self, a, info): return self.o.oneHot(a, info)
     def extract_col(self, a, sel): return self.o.extractCol(a, sel)
     diag = None  # DiagMatrix has no restatement in the oracle: a diagonal copy, checked on the device only
 
@@ -103,6 +104,7 @@ class _CudaBackend:
     def col_bind(self, a, b): return self.k.colBind(self._m(a), self._m(b)).to_numpy()
     def outer(self, op, a, b): return self.k.outerBinary(op, self._m(a), self._m(b)).to_numpy()
     def agg_cum(self, op, a): return self.k.aggCum(op, self._m(a)).to_numpy()
+    def one_hot(self, a, info): return self.k.oneHot(self._m(a), self._m(info)).to_numpy()
     def extract_col(self, a, sel): return self.k.extractCol(self._m(a), self._m(sel)).to_numpy()
     def diag(self, a): return self.k.diagMatrix(self._m(a)).to_numpy()
 
@@ -169,6 +171,16 @@ def _run_case(be, c):
         if be.diag is not None:
             arg, exp = _mat(args[0]), _mat(args[1])
             got = be.diag(arg)
+            assert got.shape == exp.shape and np.array_equal(got, exp), f"{c['file']}:{c['line']}"
+    elif chk in ("oneHot", "oneHotThrow"):  # OneHotTest.cpp:29-89, the double instantiation
+        arg = _mat(args[0])
+        info = np.array([_num(v) for v in args[1]["values"]], dtype=np.int64).reshape(args[1]["rows"], -1)
+        if chk == "oneHotThrow":
+            with pytest.raises(be.err):
+                be.one_hot(arg, info)
+        else:
+            exp = _mat(args[2])
+            got = be.one_hot(arg, info)
             assert got.shape == exp.shape and np.array_equal(got, exp), f"{c['file']}:{c['line']}"
     elif chk == "aggCum":  # AggCumTest.cpp:33-37 (small integer-valued literals: exact)
         arg, exp = (_mat(a) for a in args)

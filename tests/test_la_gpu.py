@@ -210,6 +210,50 @@ def test_col_bind_and_extract_col(ctx):
         k.extractCol(B_, k.DenseMatrix.from_numpy(ctx, np.zeros((2, 2), dtype=np.int64)))
 
 
+def test_one_hot(ctx):
+    """OneHot.h:54-110 against its restatement: keep / drop / expand, f64 and int64, fractional values cut to their
+    integer part, views, and the reference's errors (bad info, values outside their block)."""
+    k, o = _k()
+    rng = np.random.default_rng(14)
+    for dtype in (np.float64, np.int64):
+        for rows in (1, 7, 4000, 70001):
+            x = np.empty((rows, 5), dtype=dtype)
+            x[:, 0] = rng.integers(-50, 50, size=rows)
+            x[:, 1] = rng.integers(0, 4, size=rows)
+            x[:, 2] = rng.integers(0, 40, size=rows)
+            x[:, 3] = rng.integers(0, 2, size=rows)
+            x[:, 4] = rng.integers(-5, 5, size=rows)
+            if dtype == np.float64:
+                x[:, 1] += 0.75  # cut to the integer part
+            for info in ([-1, 4, 40, 2, -1], [0, 4, 0, 0, 0], [-1, 0, 0, 0, -1], [0, 0, 40, 2, 0]):
+                inf = np.array([info], dtype=np.int64)
+                got = k.oneHot(k.DenseMatrix.from_numpy(ctx, x), k.DenseMatrix.from_numpy(ctx, inf)).to_numpy()
+                exp = o.oneHot(x, inf) if rows <= 4000 else None
+                if exp is None:  # the restatement is a Python loop: large cases against numpy
+                    cols = []
+                    for c, n in enumerate(info):
+                        if n == -1:
+                            cols.append(x[:, c:c + 1])
+                        elif n > 0:
+                            cols.append((np.trunc(x[:, c:c + 1]) == np.arange(n)[None, :]).astype(dtype))
+                    exp = np.hstack(cols)
+                assert got.shape == exp.shape and got.dtype == exp.dtype and np.array_equal(got, exp), (dtype, rows, info)
+    x = rng.integers(0, 3, size=(3000, 2)).astype(np.float64)
+    X = k.DenseMatrix.from_numpy(ctx, x)
+    v = X.slice_rows(500, 2500)
+    inf = k.DenseMatrix.from_numpy(ctx, np.array([[3, -1]], dtype=np.int64))
+    assert np.array_equal(k.oneHot(v, inf).to_numpy(), o.oneHot(x[500:2500], np.array([[3, -1]])))
+    for bad, msg in (([[2, -1]], "must be positive and smaller"), ([[-2, 1]], "greater or equal than -1"),
+                     ([[0, 0]], "at least one non-zero entry"), ([[3]], "information for each column"),
+                     ([[3], [3]], "must be a row matrix")):
+        with pytest.raises(k.Db2Error, match=msg):
+            k.oneHot(X, k.DenseMatrix.from_numpy(ctx, np.array(bad, dtype=np.int64)))
+    neg = x.copy()
+    neg[17, 0] = -1.0
+    with pytest.raises(k.Db2Error, match="must be positive and smaller"):
+        k.oneHot(k.DenseMatrix.from_numpy(ctx, neg), inf)
+
+
 def test_ctable(ctx):
     k, o = _k()
     rng = np.random.default_rng(9)
