@@ -7,7 +7,7 @@ One "step" = one pass of the column standardisation + aggregation pipeline (16,7
 a seeded synthetic N(5,2) matrix; with N > 1 every rank owns its own 4 GiB row block (weak scaling) and the column
 statistics are combined across ranks.  Prints ONE JSON line (rank 0).  `value` is rows/s with the input resident in
 HBM; `e2e` is the same pipeline through the host-buffer API (H2D of the input and D2H of every result inside the timed
-region).  `--impl reference` times the reference's CPU kernels on the host cores on a bounded sample."""
+region).  `--impl reference` times the reference's own multithreaded CPU engine on the host cores on the same rows."""
 from __future__ import annotations
 
 import argparse
@@ -31,10 +31,10 @@ SEED = 2
 # algorithmic bytes per row of the whole pipeline with nothing materialised: one statistics pass and one
 # normalise + aggregate pass read the row (2 x 256 B), three row results are written (24 B) = 536 B/row
 PIPELINE_MIN_BYTES_PER_ROW = 2 * COLS * 8 + 24
-# DRAM traffic of the dominant kernel per row, from the ncu capture of the 2,097,152-row case
-# (dram__bytes_read.sum + dram__bytes_write.sum = 536.92 MB + 44.54 MB; profiles/fused_row_ct_kernel_*.md)
-# FP64 peak of this pool's B200: cuBLAS DGEMM 8192^3 through torch.mm, measured twice on the GPU box (35.4 / 35.5)
+# FP64 tensor peak used when it is not measured in the same run (cuBLAS DGEMM 8192^3 through torch.mm on a B200)
 FP64_PEAK_TFLOPS = 35.4
+# DRAM traffic of the dominant kernel per row, from an ncu capture of the 2,097,152-row case
+# (dram__bytes_read.sum + dram__bytes_write.sum = 536.92 MB + 44.54 MB), scaled by the rows of a launch
 DOMINANT_TRAFFIC_BYTES_PER_ROW = (536.92e6 + 44.54e6) / 2_097_152
 
 
@@ -267,7 +267,8 @@ def run_ours(args) -> dict:
                             "peak_kind": peak_kind, "launches_timed": dom["launches"],
                             "avg_ms": dom["avg_ms"], "algorithmic_bytes_per_launch": dom["bytes"]}
     if rank == 0:
-        line["cpu_baseline"] = cpu_baseline(min(rows, args.cpu_rows), cols)
+        line["cpu_baseline"] = cpu_baseline(min(rows, args.cpu_rows) if args.cpu_rows > 0 else rows, cols, steps=3,
+                                            budget_s=30.0)
     for p_ in (host_ptr, p_r, p_m, p_i):
         lib.db2_free_host(p_)
     return line if rank == 0 else {}
@@ -454,37 +455,72 @@ LEGS.update({"normal_equations_shard": normal_equations_leg, "kmeans_shard": kme
              "connected_components": components_leg, "f32_matmul_tcgen05": f32_matmul_leg})
 
 
-def cpu_baseline(rows: int, cols: int, steps: int = 3, threads: int | None = None) -> dict:
-    from oracle import cpu_pipelines
-    k, kind = cpu_pipelines.backend()
-    threads = threads or cpu_pipelines.host_threads()
-    X = np.empty((rows, cols))
-    make_input(rows, cols, SEED, X)
-    cpu_pipelines.standardise_aggregate(X, threads, k)
-    ts = []
-    for _ in range(steps):
-        t0 = time.perf_counter()
-        cpu_pipelines.standardise_aggregate(X, threads, k)
-        ts.append(time.perf_counter() - t0)
-    t = float(np.median(ts))
-    return {"value": rows / t, "unit": "rows/s", "cores": threads, "kind": kind,
-            "sample": f"first {rows} rows x {cols} cols of the same N(5,2) input, {steps} runs after 1 warm-up, median; "
-                      f"reference CPU kernels row-partitioned over {threads} threads (STATIC)",
-            "ms_per_step": t * 1e3}
+def cpu_baseline(rows: int, cols: int, steps: int = 3, threads: int | None = None, X=None, budget_s: float = 1e9,
+                 non_vectorized: bool = True) -> dict:
+    """The reference's CPU implementation of the workload on the host cores.  When the reference's vectorized engine
+    was built (oracle/_ref/libdaphne_ref_engine.so) it is that engine -- MTWrapper::executeCpuQueues with DAPHNE's
+    defaults -- driving the reference's CPU kernels, one worker per host CPU, and beside it the same kernels called
+    once on whole matrices (daphne without --vec).  Otherwise the reference's kernels (or their restatement) under a
+    row-partitioning thread pool.  Steps are timed one by one (wall clock); the median is reported; after the first
+    timed step the number of steps is cut so that the baseline stays inside `budget_s` seconds."""
+    from oracle import cpu_pipelines, refengine
+    if X is None:
+        X = np.empty((rows, cols))
+        make_input(rows, cols, SEED, X)
+    if refengine.available():
+        threads = threads or refengine.default_threads()
+        run = lambda: refengine.standardise_aggregate(X, threads, True, results=False)[-1]  # noqa: E731
+        kind, how = "reference", refengine.ENGINE
+    else:
+        k, kind = cpu_pipelines.backend()
+        threads = threads or cpu_pipelines.host_threads()
+
+        def run():
+            t0 = time.perf_counter()
+            cpu_pipelines.standardise_aggregate(X, threads, k)
+            t = (time.perf_counter() - t0) * 1e3
+            return (0.0, 0.0, 0.0, t)
+        how = "the reference's CPU kernels under a row-partitioning thread pool (STATIC), the engine was not built"
+    t_begin = time.perf_counter()
+    run()  # warm-up
+    parts = []
+    for i in range(steps):
+        parts.append(run())
+        per = (time.perf_counter() - t_begin) / (len(parts) + 1)
+        if (time.perf_counter() - t_begin) + per > budget_s:
+            break
+    tot = [p[3] for p in parts]
+    t = float(np.median(tot)) * 1e-3
+    med = parts[int(np.argsort(tot)[len(tot) // 2])]
+    out = {"value": rows / t, "unit": "rows/s", "cores": threads, "kind": kind, "engine": how,
+           "sample": f"first {rows} rows x {cols} cols of the N(5,2) seed-{SEED} input, {len(parts)} timed runs after 1 "
+                     f"warm-up, median wall time",
+           "ms_per_step": t * 1e3, "steps_run": len(parts),
+           "ms_column_statistics": med[0], "ms_pipeline": med[1], "ms_idxmax": med[2]}
+    if non_vectorized and refengine.available():
+        ms = refengine.standardise_aggregate(X, threads, False, results=False)[-1]
+        out["non_vectorized"] = {"value": rows / (ms[3] * 1e-3), "unit": "rows/s", "ms_per_step": ms[3], "cores": 1,
+                                 "what": "the same kernel sequence called once on whole matrices (no --vec), 1 run"}
+    return out
 
 
 def run_reference(args) -> dict:
+    """The reference arm: the reference's CPU engine on the SAME configuration (all rows of one GPU's block).  A step
+    takes seconds on the host, so the number of timed steps is cut to what fits about three minutes; the line says
+    how many ran."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return {}
-    rows = min(args.rows, args.cpu_rows)
-    b = cpu_baseline(rows, COLS, steps=max(1, args.steps), threads=None)
+    rows = args.rows if args.cpu_rows <= 0 else min(args.rows, args.cpu_rows)
+    b = cpu_baseline(rows, COLS, steps=max(1, args.steps), threads=None, budget_s=170.0, non_vectorized=True)
     return {
         "impl": "reference", "metric": "pipeline_rows_per_s", "value": b["value"], "unit": "rows/s",
-        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": b["ms_per_step"],
+        "n_gpus": args.gpus, "steps": b["steps_run"], "steps_requested": args.steps, "warmup": 1,
+        "ms_per_step": b["ms_per_step"],
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f64", "data": "synthetic",
-        "config": {"workload": "cfg2 column standardisation + aggregation on f64 %d x %d (bounded sample of the "
-                               "%d-row workload), CPU" % (rows, COLS, args.rows), "rows": rows, "cols": COLS},
+        "config": {"workload": "cfg2 column standardisation + aggregation (mean, sd, Z=(X-mu)/sd, rowSums(Z^2), "
+                               "sum, rowMaxs, idxMax) on f64 %d x %d, N(5,2) seed %d, host cores" % (rows, COLS, SEED),
+                   "rows_per_gpu": rows, "cols": COLS, "same_rows_as_gpu_arm": rows == args.rows},
         "cpu_baseline": b,
         "e2e": {"value": b["value"], "unit": "rows/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -499,11 +535,15 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--rows", type=int, default=ROWS_PER_GPU, help="rows per GPU (default: the 4 GiB configuration)")
     ap.add_argument("--no-extra", action="store_true", help="skip the other workloads reported under `extra`")
-    ap.add_argument("--cpu-rows", type=int, default=1 << 20, help="rows of the bounded CPU-baseline sample")
+    ap.add_argument("--cpu-rows", type=int, default=None,
+                    help="rows of the CPU run: default 4,194,304 for the cpu_baseline of the GPU arm (a bounded "
+                         "sample), all rows for --impl reference")
     ap.add_argument("--leg", default=None, choices=["normal_equations_shard", "kmeans_shard", "connected_components",
                                                     "f32_matmul_tcgen05"],
                     help="run only this side workload (profiling aid); prints its own JSON line")
     args = ap.parse_args()
+    if args.cpu_rows is None:
+        args.cpu_rows = 0 if args.impl == "reference" else 1 << 22
     if args.warmup < 3 and args.impl == "ours":
         args.warmup = 3
     if args.leg and args.impl == "ours":

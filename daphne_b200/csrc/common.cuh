@@ -57,6 +57,23 @@ inline int after_launch(const char *what) {
 // number of SMs of the current device (cached per device)
 int sm_count();
 
+// Once-per-DEVICE flag.  cudaFuncSetAttribute applies to the device that is current when it is called, and one process
+// may hold contexts on several devices, so the opt-in to large dynamic shared memory is tracked per device (a repeated
+// call by two racing threads is harmless).
+struct PerDeviceOnce {
+    std::atomic<uint64_t> done{0};
+    static int dev() {
+        int d = 0;
+        if (cudaGetDevice(&d) != cudaSuccess || d < 0 || d >= 64) {
+            cudaGetLastError();
+            d = 63;
+        }
+        return d;
+    }
+    bool need() const { return !((done.load(std::memory_order_acquire) >> dev()) & 1u); }
+    void mark() { done.fetch_or(uint64_t(1) << dev(), std::memory_order_release); }
+};
+
 inline size_t dtype_size(int dtype) { return dtype == DB2_F32 ? 4 : 8; }
 
 inline cudaStream_t as_stream(void *s) { return reinterpret_cast<cudaStream_t>(s); }

@@ -41,6 +41,12 @@ EXT_HEADERS = {"EwUnaryMat.h": None, "CTable.h": None, "OuterBinary.h": None, "A
 DEVICE_VTS = {"double", "float", "int64_t"}
 
 
+def default_source() -> Path:
+    """$DAPHNE_ROOT, else a directory `reference` beside the repository."""
+    import os
+    return Path(os.environ.get("DAPHNE_ROOT") or PKG.parents[1] / "reference")
+
+
 def _ext_instantiation_ok(header: str, inst) -> bool:
     """Dense matrices of the value types the device kernels implement; index results are size_t."""
     vts, scalars = [], []
@@ -118,8 +124,8 @@ def filtered_spec(daphne_src: Path) -> list:
     return keep
 
 
-def build(daphne_src: str | Path = "/root/reference") -> Path:
-    daphne_src = Path(daphne_src)
+def build(daphne_src: str | Path | None = None) -> Path:
+    daphne_src = Path(daphne_src or default_source())
     if not (daphne_src / "src/runtime/local/kernels/genKernelInst.py").exists():
         raise RuntimeError(f"no DAPHNE source tree at {daphne_src}")
     from daphne_b200 import build as core
@@ -183,4 +189,4 @@ def build(daphne_src: str | Path = "/root/reference") -> Path:
 
 if __name__ == "__main__":
     sys.path.insert(0, str(PKG.parent))
-    print(build(sys.argv[1] if len(sys.argv) > 1 else "/root/reference"))
+    print(build(sys.argv[1] if len(sys.argv) > 1 else None))

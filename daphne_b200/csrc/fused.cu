@@ -357,15 +357,15 @@ int fused_row_pass_f64(const FusedProgram &prog, cudaStream_t st) {
     // resident CTAs per SM are bounded by shared memory (about 34 KB each) and registers; 6 is a safe upper bound
     const int64_t cap = (int64_t)sm_count() * 6;
     const int grid = (int)(ntiles < cap ? ntiles : cap);
-    static bool attr_set[2] = {false, false};
-    if (smem > 48 * 1024 && !attr_set[aligned]) {
+    static PerDeviceOnce attr_set[2];
+    if (smem > 48 * 1024 && attr_set[aligned].need()) {
         if (aligned)
             DB2_CUDA(cudaFuncSetAttribute(fused_row_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                           100 * 1024));
         else
             DB2_CUDA(cudaFuncSetAttribute(fused_row_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                           100 * 1024));
-        attr_set[aligned] = true;
+        attr_set[aligned].mark();
     }
     if (aligned)
         fused_row_kernel<true><<<grid, RT, smem, st>>>(prog);

@@ -672,11 +672,11 @@ template <typename ChainT, typename TapsT, bool EW> static int launch_row(const 
     const int64_t nblocks = ((prog.rows + WR - 1) / WR + WARPS - 1) / WARPS;
     const int64_t cap = (int64_t)sm_count() * 3;
     const int grid = (int)(nblocks < cap ? nblocks : cap);
-    static bool attr = false;
-    if (!attr) {
+    static PerDeviceOnce attr;
+    if (attr.need()) {
         DB2_CUDA(cudaFuncSetAttribute(fused_row_ct_kernel<ChainT, TapsT, EW>,
                                       cudaFuncAttributeMaxDynamicSharedMemorySize, 128 * 1024));
-        attr = true;
+        attr.mark();
     }
     fused_row_ct_kernel<ChainT, TapsT, EW><<<grid, RT, smem, st>>>(prog);
     return after_launch("fused_row_ct_kernel");

@@ -479,11 +479,11 @@ static GemmPlan plan_gemm(int64_t M, int64_t N, int64_t K, bool syrk, bool ta, b
 template <bool TA, bool TB, int BM, int BN>
 static int launch_gemm(const GemmArgs &g, const GemmPlan &p, cudaStream_t st) {
     const size_t smem = tile_smem(BM, BN, TA, TB);
-    static bool attr = false;
-    if (!attr) {
+    static PerDeviceOnce attr;
+    if (attr.need()) {
         DB2_CUDA(cudaFuncSetAttribute(gemm_f64_kernel<TA, TB, BM, BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                       (int)smem));
-        attr = true;
+        attr.mark();
     }
     dim3 grid(p.tiles_n, p.tiles_m, p.splits);
     gemm_f64_kernel<TA, TB, BM, BN><<<grid, TileCfg<BM, BN>::THREADS, smem, st>>>(g);

@@ -560,11 +560,11 @@ size_t tf32_scratch_bytes(int64_t M, int64_t N, int64_t K, bool syrk) {
 }
 
 template <bool TA, bool TB> static int launch_tc(const TcArgs &g, const TcPlan &p, cudaStream_t st) {
-    static bool attr = false;
-    if (!attr) {
+    static PerDeviceOnce attr;
+    if (attr.need()) {
         DB2_CUDA(cudaFuncSetAttribute(gemm_tf32_kernel<TA, TB>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                       (int)SMEM_BYTES));
-        attr = true;
+        attr.mark();
     }
     dim3 grid(p.tiles_n, p.tiles_m, p.splits);
     gemm_tf32_kernel<TA, TB><<<grid, THREADS, SMEM_BYTES, st>>>(g);

@@ -123,9 +123,13 @@ int db2_readDaphne(db2_context *ctx, db2_matrix **res, const char *path) {
     DB2_CHECK(dtype >= 0, DB2_EUNSUPPORTED, "%s: value type code %d is not implemented on the device", path, (int)h[18]);
     DB2_CHECK(h[43] == 1 && h[44] == h[18], DB2_EUNSUPPORTED, "%s: only one dense block of the matrix' value type",
               path);
-    DB2_CHECK(brows == (uint32_t)rows && bcols == (uint32_t)cols, DB2_EUNSUPPORTED,
-              "%s: the block does not span the matrix", path);
-    const size_t es = dtype_size(dtype), total = (size_t)rows * cols * es;
+    DB2_CHECK(rows <= UINT32_MAX && cols <= UINT32_MAX && brows == (uint32_t)rows && bcols == (uint32_t)cols,
+              DB2_EUNSUPPORTED, "%s: the block does not span the matrix", path);
+    const size_t es = dtype_size(dtype);
+    size_t total = 0;
+    DB2_CHECK(!__builtin_mul_overflow((size_t)rows, (size_t)cols, &total) && !__builtin_mul_overflow(total, es, &total),
+              DB2_EINVAL, "%s: %llu x %llu values do not fit the address space", path, (unsigned long long)rows,
+              (unsigned long long)cols);
     struct stat sb;
     DB2_CHECK(fstat(f.fd, &sb) == 0 && (size_t)sb.st_size >= DBDF_HEADER + total, DB2_EINVAL,
               "%s: %lld x %lld values need %zu bytes after the header, the file has %lld", path, (long long)rows,

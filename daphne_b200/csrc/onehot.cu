@@ -251,13 +251,13 @@ int onehot_try_matmul(db2_context *ctx, db2_matrix **res, db2_matrix *lhs, db2_m
     void *scratch = nullptr;
     DB2_TRY(ctx_scratch(ctx, (size_t)grid * k * d * 8, &scratch));
     const size_t smem = (size_t)warps * acc_rows * d * 8;
-    static bool attr = false;
-    if (!attr) {
+    static PerDeviceOnce attr;
+    if (attr.need()) {
         DB2_CUDA(cudaFuncSetAttribute(onehot_segsum_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                       (int)SEG_SMEM_LIMIT));
         DB2_CUDA(cudaFuncSetAttribute(onehot_segsum64_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                       (int)SEG_SMEM_LIMIT));
-        attr = true;
+        attr.mark();
     }
     std::shared_ptr<const OneHot> oh = lhs->onehot;
     if (k64)

@@ -42,8 +42,10 @@ template <typename VT> __device__ __forceinline__ VT op_div(VT a, VT b) {
         // integer division by zero terminates the reference process (SIGFPE); here it yields 0
         if (b == 0)
             return 0;
-        if (a == INT64_MIN && b == -1)
-            return INT64_MIN;
+        if constexpr (std::is_signed_v<VT>) { // the one quotient that does not fit the type
+            if (a == std::numeric_limits<VT>::min() && b == (VT)-1)
+                return std::numeric_limits<VT>::min();
+        }
         return a / b;
     }
 }

@@ -359,11 +359,11 @@ bool skinny_shape_ok(int64_t n, int64_t K, int64_t N, const void *A, int64_t lda
 
 template <int NT, int KPT, int CH> static int launch_skinny_k(const SkinnyArgs &a, cudaStream_t st) {
     const size_t smem = skinny_smem(a.K, NT);
-    static bool attr = false;
-    if (!attr) {
+    static PerDeviceOnce attr;
+    if (attr.need()) {
         DB2_CUDA(cudaFuncSetAttribute(skinny_gemm_kernel<NT, KPT, CH>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                       220 * 1024));
-        attr = true;
+        attr.mark();
     }
     const int64_t ctas = ((a.n + SK_WROWS - 1) / SK_WROWS + SK_WARPS - 1) / SK_WARPS;
     const int grid = (int)(ctas < sm_count() ? ctas : sm_count());

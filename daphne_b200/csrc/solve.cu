@@ -57,6 +57,8 @@ __global__ void __launch_bounds__(LU_THREADS)
                     b = s_val[w];
                     ix = s_idx[w];
                 }
+            if (ix >= m) // no candidate was accepted (every remaining entry of the column is NaN): keep row j
+                ix = j;
             s_p = ix;
             piv[k0 + j] = (int)k0 + ix;
             if (!(b > 0.0) && *status == 0)
@@ -110,8 +112,9 @@ __global__ void __launch_bounds__(LU_REG_ROWS)
             break;
         const int par = j & 1;
         // first largest |a[j]| among the rows j .. m-1 (idamax)
-        double best = (tid >= j && tid < m) ? fabs(a[j]) : -1.0;
-        int bi = tid;
+        const bool cand = tid >= j && tid < m;
+        double best = cand ? fabs(a[j]) : -1.0;
+        int bi = cand ? tid : 0x7fffffff;
         if (best != best) // a NaN pivot candidate: treated as "not larger" like the comparison of the scan
             best = -1.0;
 #pragma unroll
@@ -139,7 +142,7 @@ __global__ void __launch_bounds__(LU_REG_ROWS)
                 bi = oi;
             }
         }
-        const int p = bi; // every thread has the same answer
+        const int p = bi; // every thread has the same answer; always a row in [j, m): row j is a candidate
         if (tid == 0) {
             piv[k0 + j] = (int)k0 + p;
             if (!(best > 0.0) && *status == 0)
@@ -194,7 +197,7 @@ __global__ void lu_swap_trsm_kernel(double *__restrict__ A, double *__restrict__
     const int64_t st = rhs ? 1 : n;
     for (int j = 0; j < nb; j++) {
         const int64_t p = piv[k0 + j];
-        if (p != k0 + j) {
+        if (p > k0 + j && p < n) { // a pivot row lies below row k0 + j and inside the matrix; anything else is no exchange
             const double t = col[(k0 + j) * st];
             col[(k0 + j) * st] = col[p * st];
             col[p * st] = t;
@@ -283,11 +286,11 @@ extern "C" int db2k_solve(int dtype, void *a_work, int64_t n, void *x_inout, int
     int nb = 32;
     while (nb > 1 && (size_t)n * (nb + 1) * 8 > 200 * 1024)
         nb /= 2;
-    static bool attr = false;
-    if (!attr) {
+    static PerDeviceOnce attr;
+    if (attr.need()) {
         DB2_CUDA(cudaFuncSetAttribute(lu_panel_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
         DB2_CUDA(cudaFuncSetAttribute(lu_backsolve_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
-        attr = true;
+        attr.mark();
     }
     for (int64_t k0 = 0; k0 < n; k0 += nb) {
         const int w = (int)((n - k0 < nb) ? (n - k0) : nb);

@@ -79,6 +79,28 @@ def standardise_aggregate(X: np.ndarray, threads: int = 1, k=None):
     return mu, sd, r, s, m, idx
 
 
+def standardise_tail(X: np.ndarray, mu: np.ndarray, sd: np.ndarray, threads: int = 1, k=None, exact_squares=False):
+    """The row part of standardise_aggregate for GIVEN column statistics: (r, row_max, row_idx_max).  With
+    exact_squares the squares are z * z (one correctly rounded multiplication) instead of the reference's pow(z, 2),
+    which glibc evaluates to within one ulp of it."""
+    k = k or backend()[0]
+    n = X.shape[0]
+    r = np.empty((n, 1), dtype=X.dtype)
+    m = np.empty((n, 1), dtype=X.dtype)
+    idx = np.empty((n, 1), dtype=np.uint64)
+
+    def tail(b):
+        lo, hi = b
+        Z = k.ewBinaryMat(DIV, k.ewBinaryMat(SUB, X[lo:hi], mu), sd)
+        r[lo:hi] = k.aggRow(SUM, Z * Z if exact_squares else k.ewBinaryObjSca(POW, Z, 2.0))
+        m[lo:hi] = k.aggRow(MAX, Z)
+        idx[lo:hi] = k.aggRow(IDXMAX, Z)
+
+    with ThreadPoolExecutor(max_workers=max(1, threads)) as ex:
+        list(ex.map(tail, _blocks(n, max(1, threads) * 4)))
+    return r, m, idx
+
+
 def normal_equations(X: np.ndarray, y: np.ndarray, lam: float = 0.001, k=None):
     """CPU twin of daphne_b200.pipelines.normal_equations: (A, b, beta)."""
     k = k or backend()[0]

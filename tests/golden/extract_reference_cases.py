@@ -356,7 +356,9 @@ def _extract_seq(root: Path):
 
 
 if __name__ == "__main__":
-    root = Path(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    import os
+    root = Path(sys.argv[1] if len(sys.argv) > 1 else
+                os.environ.get("DAPHNE_ROOT") or Path(__file__).resolve().parents[3] / "reference")
     cases, skipped = extract(root)
     json.dump({"source": "daphne-eu/daphne test/runtime/local/kernels (literals of the reference's unit tests)",
                "skipped_unparsed_checks": skipped, "cases": cases}, sys.stdout, indent=None, separators=(",", ":"))
