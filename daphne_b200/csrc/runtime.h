@@ -40,6 +40,9 @@ struct db2_context {
     // cross-GPU combine (comm.cu): this context's rank among `world` row shards and its NCCL communicator
     int rank = 0, world = 1;
     void *comm = nullptr;
+    bool comm_is_fake = false;   // installed by the test hook db2_comm_test_attach: never passed to NCCL's destroy
+    // member of a single-process device group (group.cu): the communicator that ncclCommInitAll made for this device
+    void *group_comm = nullptr;
     // column statistics of the matrix that was last aggregated by columns (colstats.cu)
     std::shared_ptr<db2::ColStats> colstats;
     std::mutex mu;
@@ -200,6 +203,11 @@ int lazy_try_agg_all(db2_context *ctx, int op, double *res_host, db2_matrix *arg
 int lazy_force(db2_matrix *m);          // materialises a deferred matrix (and the pending siblings it can serve)
 int lazy_flush_all(db2_context *ctx);   // produces every pending aggregation
 void lazy_forget(db2_matrix *m);        // a deferred matrix is being destroyed
+
+// device groups (comm.cu): NCCL communicators for the contexts of one process, grouped all-reduce
+int nccl_init_group(const std::vector<db2_context *> &ctxs);
+void nccl_destroy_group(const std::vector<db2_context *> &ctxs);
+int nccl_allreduce_group(const std::vector<db2_context *> &ctxs, const std::vector<db2_matrix *> &ms, int combine);
 
 // makes the device placement current (allocation + async H2D when only the host copy is valid)
 int ensure_device(db2_matrix *m);

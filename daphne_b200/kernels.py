@@ -473,3 +473,158 @@ def vectorizedPipeline(ctx: Context, inputs, splits, combines, body, batch_rows:
     check(lib.db2_vectorizedPipeline(ctx.handle, out_h, n_out, scal, in_h, n_in, neg, neg, sp, cm,
                                      C.cast(cb, C.c_void_p), int(batch_rows)))
     return [DenseMatrix(ctx, C.c_void_p(out_h[o])) for o in range(n_out)]
+
+
+class Group:
+    """Several GPUs in one process (db2_group): one Context per device.  devices=None takes DAPHNE_B200_DEVICES or all
+    visible devices; a device may be listed more than once."""
+
+    def __init__(self, devices=None):
+        self._h = C.c_void_p()
+        if devices is None:
+            check(lib.db2_group_create(None, 0, C.byref(self._h)))
+        else:
+            arr = (C.c_int * len(devices))(*[int(d) for d in devices])
+            check(lib.db2_group_create(arr, len(devices), C.byref(self._h)))
+        n = C.c_int()
+        check(lib.db2_group_size(self._h, C.byref(n)))
+        self.size = n.value
+        self.contexts = []
+        for i in range(self.size):
+            h = C.c_void_p()
+            check(lib.db2_group_context(self._h, i, C.byref(h)))
+            c = Context.__new__(Context)  # borrowed: the group owns the context
+            c._h, c._borrowed = h, True
+            dev = C.c_int()
+            check(lib.db2_context_device(h, C.byref(dev)))
+            c.device = dev.value
+            c.close = lambda: None
+            self.contexts.append(c)
+
+    @property
+    def handle(self):
+        return self._h
+
+    @property
+    def uses_nccl(self) -> bool:
+        y = C.c_int()
+        check(lib.db2_group_uses_nccl(self._h, C.byref(y)))
+        return bool(y.value)
+
+    def sync(self) -> None:
+        check(lib.db2_group_sync(self._h))
+
+    def close(self) -> None:
+        if self._h:
+            lib.db2_group_destroy(self._h)
+            self._h = C.c_void_p()
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *exc):
+        self.close()
+
+
+class DistMatrix:
+    """Handle to a db2_dist: row blocks (axis 0), column blocks (axis 1) or one copy per device (axis -1)."""
+
+    def __init__(self, group: Group, handle, keep=None):
+        self.group, self._h, self._keep = group, handle, keep
+        dt, r, c, ax = C.c_int(), C.c_int64(), C.c_int64(), C.c_int()
+        check(lib.db2_dist_info(self._h, C.byref(dt), C.byref(r), C.byref(c), C.byref(ax)))
+        self.dtype_code, self.rows, self.cols, self.axis = dt.value, r.value, c.value, ax.value
+
+    @property
+    def handle(self):
+        return self._h
+
+    @property
+    def shape(self):
+        return (self.rows, self.cols)
+
+    @staticmethod
+    def from_numpy(group: Group, a: np.ndarray) -> "DistMatrix":
+        """Row blocks of a host array (borrowed): each device fetches its own rows on first use."""
+        if a.ndim == 1:
+            a = a.reshape(-1, 1)
+        if a.ndim != 2 or a.dtype not in _NP2DT:
+            raise Db2Error(1, f"unsupported array: ndim {a.ndim}, dtype {a.dtype}")
+        if a.size and (a.strides[1] != a.itemsize or a.strides[0] % a.itemsize):
+            a = np.ascontiguousarray(a)
+        ld = max(a.strides[0] // a.itemsize if a.shape[0] > 1 and a.size else a.shape[1], a.shape[1])
+        h = C.c_void_p()
+        check(lib.db2_dist_from_host(group.handle, _NP2DT[a.dtype], a.shape[0], a.shape[1], ld,
+                                     C.c_void_p(a.ctypes.data), C.byref(h)))
+        return DistMatrix(group, h, keep=a)
+
+    @staticmethod
+    def from_matrix(group: Group, m: DenseMatrix, replicate: bool = False) -> "DistMatrix":
+        h = C.c_void_p()
+        check(lib.db2_dist_from_matrix(group.handle, m.handle, int(replicate), C.byref(h)))
+        return DistMatrix(group, h, keep=m)
+
+    def shard(self, i: int):
+        """(DenseMatrix, first row / column) of device i's block."""
+        h, off = C.c_void_p(), C.c_int64()
+        check(lib.db2_dist_shard(self._h, i, C.byref(h), C.byref(off)))
+        check(lib.db2_matrix_incref(h))
+        return DenseMatrix(self.group.contexts[i], h, keep=self), off.value
+
+    def to_numpy(self) -> np.ndarray:
+        out = np.empty((self.rows, self.cols), dtype=_DT2NP[self.dtype_code])
+        check(lib.db2_dist_to_host(self._h, C.c_void_p(out.ctypes.data), max(self.cols, 1)))
+        return out
+
+    def gather(self, index: int = 0) -> DenseMatrix:
+        h = C.c_void_p()
+        check(lib.db2_dist_gather(self._h, index, C.byref(h)))
+        return DenseMatrix(self.group.contexts[index], h)
+
+    def free(self) -> None:
+        if self._h:
+            lib.db2_dist_decref(self._h)
+            self._h = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.free()
+        except Exception:
+            pass
+
+
+def vectorizedPipelineGroup(group: Group, inputs, splits, combines, body, batch_rows: int = 0):
+    """The scheduler over all devices of a group (db2_vectorizedPipelineGroup).  `body(ins, ctx) -> outs` is called
+    once per device (and batch), from that device's host thread, with that device's Context."""
+    n_in, n_out = len(inputs), len(combines)
+    by_ptr = {c.handle.value: c for c in group.contexts}
+    keep, errors = [], []
+
+    def trampoline(outs_pp, ins_p, ctx_p):
+        try:
+            ctx = by_ptr[ctx_p]
+            ins = [DenseMatrix(ctx, C.c_void_p(ins_p[i])) for i in range(n_in)]
+            outs = body(ins, ctx)
+            assert len(outs) == n_out
+            for o, m in enumerate(outs):
+                outs_pp[o][0] = m.handle.value
+                m._h = C.c_void_p()  # ownership moves to the scheduler
+            for m in ins:
+                m.free()
+            keep.append(outs)
+        except BaseException as e:  # an exception must not unwind through the C frames of the worker thread
+            errors.append(e)
+
+    cb = PIPELINE_FN(trampoline)
+    out_h = (C.c_void_p * n_out)()
+    in_h = (C.c_void_p * n_in)(*[m.handle.value for m in inputs])
+    sp = (C.c_int64 * n_in)(*[int(x) for x in splits])
+    cm = (C.c_int64 * n_out)(*[int(x) for x in combines])
+    neg = (C.c_int64 * n_out)(*([-1] * n_out))
+    scal = (C.c_int * n_in)(*([0] * n_in))
+    rc = lib.db2_vectorizedPipelineGroup(group.handle, out_h, n_out, scal, in_h, n_in, neg, neg, sp, cm,
+                                         C.cast(cb, C.c_void_p), int(batch_rows))
+    if errors:
+        raise errors[0]
+    check(rc)
+    return [DistMatrix(group, C.c_void_p(out_h[o])) for o in range(n_out)]

@@ -101,6 +101,23 @@ _SIGS = {
     "db2_comm_info": (i32, [vp, _P(i32), _P(i32)]),
     "db2_allreduce": (i32, [vp, vp, i32]),
     "db2_allgather_rows": (i32, [vp, vp, _P(vp)]),
+    "db2_allgatherv_rows": (i32, [vp, vp, i64, _P(vp)]),
+    "db2_group_create": (i32, [_P(i32), i32, _P(vp)]),
+    "db2_group_destroy": (i32, [vp]),
+    "db2_group_size": (i32, [vp, _P(i32)]),
+    "db2_group_context": (i32, [vp, i32, _P(vp)]),
+    "db2_group_uses_nccl": (i32, [vp, _P(i32)]),
+    "db2_group_sync": (i32, [vp]),
+    "db2_dist_from_host": (i32, [vp, i32, i64, i64, i64, vp, _P(vp)]),
+    "db2_dist_from_matrix": (i32, [vp, vp, i32, _P(vp)]),
+    "db2_dist_info": (i32, [vp, _P(i32), _P(i64), _P(i64), _P(i32)]),
+    "db2_dist_shard": (i32, [vp, i32, _P(vp), _P(i64)]),
+    "db2_dist_incref": (i32, [vp]),
+    "db2_dist_decref": (i32, [vp]),
+    "db2_dist_to_host": (i32, [vp, vp, i64]),
+    "db2_dist_gather": (i32, [vp, i32, _P(vp)]),
+    "db2_vectorizedPipelineGroup": (i32, [vp, _P(vp), sz, _P(i32), _P(vp), sz, _P(i64), _P(i64), _P(i64), _P(i64), vp,
+                                         i64]),
     "db2_matrix_create": (i32, [vp, i32, i64, i64, i32, _P(vp)]),
     "db2_matrix_wrap_host": (i32, [vp, i32, i64, i64, i64, vp, _P(vp)]),
     "db2_matrix_wrap_device": (i32, [vp, i32, i64, i64, i64, vp, _P(vp)]),

@@ -285,8 +285,12 @@ int db2_comm_destroy(db2_context *ctx);
 int db2_comm_info(const db2_context *ctx, int *rank, int *world);
 /* in-place combine of a small contiguous partial over all ranks; combine = DB2_COMBINE_ADD / MIN / MAX */
 int db2_allreduce(db2_context *ctx, db2_matrix *m, int combine);
-/* concatenation of equally shaped row shards in rank order */
+/* concatenation of equally tall row shards in rank order */
 int db2_allgather_rows(db2_context *ctx, db2_matrix *local, db2_matrix **full);
+/* concatenation of the row shards of the scheduler's partition: total_rows rows cut into one contiguous block per
+ * rank, the first total_rows % world blocks one row taller.  A shard of any other height is refused (DB2_EINVAL)
+ * before a collective is issued. */
+int db2_allgatherv_rows(db2_context *ctx, db2_matrix *local, int64_t total_rows, db2_matrix **full);
 
 /* device-only matrix (DataObjectFactory::create<DenseMatrix<VT>>(rows, cols, zero, &alloc_desc)) */
 int db2_matrix_create(db2_context *ctx, int dtype, int64_t rows, int64_t cols, int zero, db2_matrix **out);
@@ -368,6 +372,56 @@ typedef void (*db2_pipeline_fn)(db2_matrix ***outputs, db2_matrix **inputs, db2_
 int db2_vectorizedPipeline(db2_context *ctx, db2_matrix **outputs, size_t numOutputs, const int *isScalar,
                            db2_matrix **inputs, size_t numInputs, const int64_t *outRows, const int64_t *outCols,
                            const int64_t *splits, const int64_t *combines, db2_pipeline_fn fun, int64_t batch_rows);
+
+/* ------------------------------------------------------------------------- */
+/* several GPUs in one process                                                */
+/* ------------------------------------------------------------------------- */
+
+/* A device group: one context (stream, pooled memory) per listed device and, when the devices are distinct and NCCL
+ * can be loaded, one communicator per device (ncclCommInitAll).  devices == NULL: the comma-separated list in the
+ * environment variable DAPHNE_B200_DEVICES, default all visible devices.  The reference creates exactly one CUDA
+ * context, for device 0 (src/runtime/local/kernels/CUDA/CreateCUDAContext.cpp:4-9), although its scheduler starts one
+ * GPU worker per entry of DaphneContext::cuda_contexts (src/runtime/local/vectorized/MTWrapper.h:93-98,170-174).
+ * A device may be listed more than once (several contexts share it; partials are then combined without NCCL). */
+typedef struct db2_group db2_group;
+int db2_group_create(const int *devices, int ndev, db2_group **out);
+int db2_group_destroy(db2_group *g);
+int db2_group_size(const db2_group *g, int *n);
+int db2_group_context(db2_group *g, int index, db2_context **ctx); /* borrowed */
+int db2_group_uses_nccl(const db2_group *g, int *yes);
+int db2_group_sync(db2_group *g);
+
+/* A matrix distributed over the devices of a group: contiguous row blocks (axis 0; the first rows % n devices hold one
+ * more row), column blocks (axis 1, the COLS results of a pipeline) or one full copy per device (axis -1, broadcast
+ * inputs and combined ADD/MIN/MAX results).  In the reference's data model this is a MetaDataObject with one
+ * DataPlacement and Range per device (src/runtime/local/datastructures/MetaDataObject.h:39-57, DataPlacement.h:29-42),
+ * which its local runtime never creates. */
+typedef struct db2_dist db2_dist;
+/* row blocks of a host buffer (borrowed): nothing is copied here, each device fetches its rows on first use */
+int db2_dist_from_host(db2_group *g, int dtype, int64_t rows, int64_t cols, int64_t ld, void *host, db2_dist **out);
+/* row blocks (replicate == 0) or full copies (replicate != 0) of a matrix of any context of this process */
+int db2_dist_from_matrix(db2_group *g, db2_matrix *m, int replicate, db2_dist **out);
+int db2_dist_info(const db2_dist *d, int *dtype, int64_t *rows, int64_t *cols, int *axis);
+/* the block held by device `index` (borrowed handle) and its first row / column */
+int db2_dist_shard(db2_dist *d, int index, db2_matrix **shard, int64_t *offset);
+int db2_dist_incref(db2_dist *d);
+int db2_dist_decref(db2_dist *d);
+/* every device copies its block into its rows / columns of dst (rows x cols, leading dimension dst_ld); synchronises */
+int db2_dist_to_host(db2_dist *d, void *dst, int64_t dst_ld);
+/* the whole matrix on device `index` of the group (new reference); other devices' blocks arrive by peer copies */
+int db2_dist_gather(db2_dist *d, int index, db2_matrix **out);
+
+/* The row-partition scheduler over all devices of a group: device i runs db2_vectorizedPipeline on block i of the
+ * ROWS-split inputs (which must share one row partition; broadcast inputs must be replicated) from its own host
+ * thread; ROWS / COLS results stay distributed, ADD / MIN / MAX partials are combined over the devices -- one grouped
+ * ncclAllReduce per result, or peer copies and a fold in device order -- and come back replicated.  Fewer rows than
+ * devices is DB2_EUNSUPPORTED.  Extends VectorizedPipeline::apply -> MTWrapper::executeQueuePerDeviceType
+ * (src/runtime/local/kernels/VectorizedPipeline.h:35-69, vectorized/MTWrapper_dense.cpp:204-336: "ToDo: multi-device
+ * support" at :220) to the 8 GPUs of one box. */
+int db2_vectorizedPipelineGroup(db2_group *g, db2_dist **outputs, size_t numOutputs, const int *isScalar,
+                                db2_dist **inputs, size_t numInputs, const int64_t *outRows, const int64_t *outCols,
+                                const int64_t *splits, const int64_t *combines, db2_pipeline_fn fun,
+                                int64_t batch_rows);
 
 /* ------------------------------------------------------------------------- */
 /* Matrix files                                                               */

@@ -141,6 +141,47 @@ def test_solve_general_and_singular(ctx):
         k.solve(k.DenseMatrix.from_numpy(ctx, np.ones((3, 2))), k.DenseMatrix.from_numpy(ctx, np.ones((3, 1))))
 
 
+@pytest.mark.parametrize("n", [600, 1024])
+def test_solve_with_a_nan_column_stays_inside_its_buffers(ctx, n):
+    """A column of NaNs (what one NaN in X makes of t(X) X after the first update) leaves the pivot search without a
+    candidate.  The factorisation must report the singular / NaN pivot and must not touch memory outside the n x n work
+    matrix and the n-element right-hand side: both are laid out here with guard words around them."""
+    import ctypes as C
+    from daphne_b200.lib import check, lib
+    rng = np.random.default_rng(n)
+    a = rng.standard_normal((n, n)) + n * np.eye(n)
+    a[:, 5] = np.nan
+    a[5, :] = np.nan
+    b = rng.standard_normal((n, 1))
+    guard = 512
+    host = np.full(guard + n * n + guard + n + guard, 7.25)
+    host[guard:guard + n * n] = a.ravel()
+    host[guard + n * n + guard:guard + n * n + guard + n] = b.ravel()
+    dev, scr, st = C.c_void_p(), C.c_void_p(), C.c_void_p()
+    check(lib.db2_malloc(C.byref(dev), host.nbytes))
+    sbytes = lib.db2k_solve_scratch_bytes(n)
+    check(lib.db2_malloc(C.byref(scr), sbytes))
+    check(lib.db2_malloc(C.byref(st), 4))
+    check(lib.db2_memcpy_h2d(dev, host.ctypes.data, host.nbytes, None))
+    a_ptr = C.c_void_p(dev.value + guard * 8)
+    x_ptr = C.c_void_p(dev.value + (guard + n * n + guard) * 8)
+    check(lib.db2k_solve(0, a_ptr, n, x_ptr, st, scr, sbytes, None))
+    check(lib.db2_device_sync())
+    back = np.empty_like(host)
+    status = np.zeros(1, dtype=np.int32)
+    check(lib.db2_memcpy_d2h(back.ctypes.data, dev, host.nbytes, None))
+    check(lib.db2_memcpy_d2h(status.ctypes.data, st, 4, None))
+    check(lib.db2_device_sync())
+    for p in (dev, scr, st):
+        check(lib.db2_free(p))
+    assert status[0] != 0, "a NaN pivot column must be reported"
+    assert np.all(back[:guard] == 7.25) and np.all(back[-guard:] == 7.25)
+    assert np.all(back[guard + n * n:guard + n * n + guard] == 7.25)
+    k, _ = _k()
+    with pytest.raises(k.Db2Error, match="exactly singular"):
+        k.solve(k.DenseMatrix.from_numpy(ctx, a), k.DenseMatrix.from_numpy(ctx, b))
+
+
 def test_transpose_fill_seq_diag_cast(ctx):
     k, o = _k()
     rng = np.random.default_rng(8)
