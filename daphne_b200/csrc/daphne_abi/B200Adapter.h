@@ -18,6 +18,7 @@
 #include <daphne_b200.h>
 
 #include <memory>
+#include <mutex>
 #include <stdexcept>
 #include <string>
 #include <type_traits>
@@ -54,9 +55,20 @@ template <typename VT> void require_supported(const char *kernel) {
         throw std::runtime_error(std::string(kernel) + ": this value type is not implemented by the B200 kernel library");
 }
 
-// the device context of a DaphneContext (created by CUDA::createCUDAContext, or on first use)
+// the device group of a DaphneContext (created by CUDA::createCUDAContext, or on first use) and the context kernels
+// called on this thread run on: the one a scheduler worker bound with ThreadContext, else the group's first
+db2_group *group(DaphneContext *ctx);
 db2_context *context(DaphneContext *ctx);
 void create_context(DaphneContext *ctx);
+struct ThreadContext { // binds the calling thread to one context of the group until it goes out of scope
+    db2_context *prev;
+    explicit ThreadContext(db2_context *c);
+    ~ThreadContext();
+};
+// Placement lists are not synchronised in the reference ("FIXME ... to avoid locking", datastructures/Structure.cpp:25);
+// the workers of the scheduler share their broadcast inputs, so lookups and additions go through a striped lock keyed
+// by the MetaDataObject (row views carry their own clone and do not contend).
+std::mutex &mdo_mutex(const void *mdo);
 
 struct HandleBox {
     db2_matrix *m = nullptr;
@@ -80,11 +92,15 @@ class AllocationDescriptorB200 : public IAllocationDescriptor {
         box->m = preset; // takes over the caller's reference
     }
     [[nodiscard]] ALLOCATION_TYPE getType() const override { return ALLOCATION_TYPE::GPU_CUDA; }
+    // the device id like the reference's descriptor; a further context that shares the device gets a suffix, so that
+    // placements of different contexts (different streams and pools) are never mistaken for one another
     [[nodiscard]] std::string getLocation() const override {
-        int dev = 0;
+        int dev = 0, dup = 0;
         db2_context_device(dctx, &dev);
-        return std::to_string(dev);
+        db2_context_ordinal(dctx, &dup);
+        return dup ? std::to_string(dev) + "+" + std::to_string(dup) : std::to_string(dev);
     }
+    [[nodiscard]] db2_context *context() const { return dctx; }
     void createAllocation(size_t size, bool zero) override {
         if (box->m)
             return; // the placement was created around an existing (possibly deferred) result
@@ -141,22 +157,37 @@ class Call {
     // the host copy.  A row view of a device-resident parent becomes a row slice of the parent's handle.
     template <typename VT> db2_matrix *in(const DenseMatrix<VT> *m) {
         require_supported<VT>("kernel argument");
-        AllocationDescriptorB200 probe(c, dtype_of<VT>(), (int64_t)m->getNumRows(), (int64_t)m->getNumCols());
         auto *mdo = m->getMetaDataObject();
+        std::lock_guard<std::mutex> lock(mdo_mutex(mdo));
+        AllocationDescriptorB200 probe(c, dtype_of<VT>(), (int64_t)m->getNumRows(), (int64_t)m->getNumCols());
         const DataPlacement *dp = mdo->findDataPlacementByType(&probe, nullptr);
         if (!dp || !mdo->isLatestVersion(dp->dp_id)) {
+            // the latest values may live on ANOTHER device of the group (a result of a stand-alone kernel consumed
+            // by a scheduler worker): fetch them with a peer copy instead of a round trip through the host
+            for (size_t id : mdo->getLatest()) {
+                DataPlacement *p = mdo->getDataPlacementByID(id);
+                auto *other = p ? dynamic_cast<AllocationDescriptorB200 *>(p->allocation.get()) : nullptr;
+                if (!other || !other->handle() || other->context() == c)
+                    continue;
+                db2_matrix *mine = nullptr;
+                check(db2_matrix_to_context(c, view_of(other->handle(), m), &mine));
+                temps.push_back(mine);
+                return mine;
+            }
             m->getValues(&probe); // creates/refreshes the placement through AllocationDescriptorB200
             dp = mdo->findDataPlacementByType(&probe, nullptr);
         }
         auto *desc = dynamic_cast<AllocationDescriptorB200 *>(dp ? dp->allocation.get() : nullptr);
         if (!desc || !desc->handle())
             throw std::runtime_error("no B200 device placement for a kernel argument");
-        db2_matrix *h = desc->handle();
+        return view_of(desc->handle(), m);
+    }
+    // the handle itself, or -- for a placement inherited from the parent of a row view -- a row slice of it
+    template <typename VT> db2_matrix *view_of(db2_matrix *h, const DenseMatrix<VT> *m) {
         int64_t hr = 0, hc = 0;
         check(db2_matrix_info(h, nullptr, &hr, &hc));
         if (hr == (int64_t)m->getNumRows() && hc == (int64_t)m->getNumCols())
             return h;
-        // placement inherited from the parent of a view
         const size_t r0 = ViewOffsets::row(m);
         if (hc != (int64_t)m->getNumCols() || ViewOffsets::col(m) != 0)
             throw std::runtime_error("column views of device-resident matrices are not supported");
@@ -167,6 +198,7 @@ class Call {
     }
     // handle of a pre-allocated result (the kernel overwrites it)
     template <typename VT> db2_matrix *out(DenseMatrix<VT> *m) {
+        std::lock_guard<std::mutex> lock(mdo_mutex(m->getMetaDataObject()));
         AllocationDescriptorB200 probe(c, dtype_of<VT>(), (int64_t)m->getNumRows(), (int64_t)m->getNumCols());
         m->getValues(&probe); // non-const access: the device placement becomes the only latest version
         const DataPlacement *dp = m->getMetaDataObject()->findDataPlacementByType(&probe, nullptr);
@@ -189,5 +221,20 @@ class Call {
         return DataObjectFactory::create<DenseMatrix<VT>>((size_t)r, (size_t)cc, false, &desc);
     }
 };
+
+// Produces values that a kernel left deferred in a device placement of m (on the context that owns them), so that
+// other threads can read the finished buffer.
+template <typename VT> void settle(const DenseMatrix<VT> *m) {
+    auto *mdo = m->getMetaDataObject();
+    std::lock_guard<std::mutex> lock(mdo_mutex(mdo));
+    for (size_t id : mdo->getLatest()) {
+        DataPlacement *p = mdo->getDataPlacementByID(id);
+        auto *d = p ? dynamic_cast<AllocationDescriptorB200 *>(p->allocation.get()) : nullptr;
+        if (d && d->handle()) {
+            void *ptr = nullptr;
+            check(db2_matrix_device_ptr(d->handle(), &ptr, nullptr));
+        }
+    }
+}
 
 } // namespace b200

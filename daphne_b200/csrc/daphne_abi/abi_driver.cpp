@@ -3,6 +3,7 @@
 // convention of the generated wrappers (src/runtime/local/kernels/genKernelInst.py:183-262), then reads the results
 // back through DenseMatrix::getValues() -- i.e. through the residency layer.
 #include <B200Adapter.h>
+#include <runtime/local/datastructures/CSRMatrix.h>
 
 #include <dlfcn.h>
 
@@ -234,6 +235,134 @@ int drv_pipeline(const double *x, int64_t xr, int64_t xc, const double *mu, doub
         if (rc == 0)
             rc = copy_out(outputs[1], out + xr, xc, &r, &c);
         DataObjectFactory::destroy(X, MU, outputs[0], outputs[1]);
+        return rc;
+    });
+}
+
+// A second compiled body with every kind of combine:
+//   out0 = sumRow(X * s)  (ROWS)   out1 = sumCol(X) (ADD)   out2 = maxCol(X) (MAX)   out3 = minCol(X) (MIN)
+//   out4 = t(maxRow(X))   (COLS)
+static void pipeline_body_all(DenseMatrix<double> ***outs, Structure **ins, DaphneContext *ctx) {
+    using DM = DenseMatrix<double>;
+    auto *X = static_cast<DM *>(ins[0]);
+    double s;
+    memcpy(&s, &ins[1], sizeof(double));
+    DM *S = nullptr, *M = nullptr;
+    reinterpret_cast<void (*)(DM **, const DM *, double, int, DaphneContext *)>(
+        sym("CUDA_ewMul__DenseMatrix_double__DenseMatrix_double__double"))(&S, X, s, 1, ctx);
+    reinterpret_cast<void (*)(DM **, const DM *, int, DaphneContext *)>(
+        sym("CUDA_sumRow__DenseMatrix_double__DenseMatrix_double"))(outs[0], S, 2, ctx);
+    reinterpret_cast<void (*)(DM **, const DM *, int, DaphneContext *)>(
+        sym("CUDA_sumCol__DenseMatrix_double__DenseMatrix_double"))(outs[1], X, 3, ctx);
+    reinterpret_cast<void (*)(DM **, const DM *, int, DaphneContext *)>(
+        sym("CUDA_maxCol__DenseMatrix_double__DenseMatrix_double"))(outs[2], X, 4, ctx);
+    reinterpret_cast<void (*)(DM **, const DM *, int, DaphneContext *)>(
+        sym("CUDA_minCol__DenseMatrix_double__DenseMatrix_double"))(outs[3], X, 5, ctx);
+    reinterpret_cast<void (*)(DM **, const DM *, int, DaphneContext *)>(
+        sym("CUDA_maxRow__DenseMatrix_double__DenseMatrix_double"))(&M, X, 6, ctx);
+    reinterpret_cast<void (*)(DM **, const DM *, int, DaphneContext *)>(
+        sym("CUDA_transpose__DenseMatrix_double__DenseMatrix_double"))(outs[4], M, 7, ctx);
+    DataObjectFactory::destroy(S, M, X);
+}
+// out = [out0 (xr) | out1 (xc) | out2 (xc) | out3 (xc) | out4 (xr)]; x2 != 0: X is first replaced by X + 0 computed by a
+// stand-alone kernel, so that the scheduler's input is device-resident (on the first device) and still deferred
+int drv_pipeline_all(const double *x, int64_t xr, int64_t xc, double s, int x2, double *out) {
+    return guarded([&] {
+        using DM = DenseMatrix<double>;
+        DM *X = host_matrix(x, xr, xc);
+        if (x2) {
+            DM *X2 = nullptr;
+            reinterpret_cast<void (*)(DM **, const DM *, double, int, DaphneContext *)>(
+                sym("CUDA_ewAdd__DenseMatrix_double__DenseMatrix_double__double"))(&X2, X, 0.0, 1, &g_ctx);
+            DataObjectFactory::destroy(X);
+            X = X2;
+        }
+        Structure *inputs[2] = {X, nullptr};
+        memcpy(&inputs[1], &s, sizeof(double));
+        bool is_scalar[2] = {false, true};
+        int64_t splits[2] = {1, 0}, combines[5] = {1, 3, 5, 4, 2};
+        int64_t out_rows[5] = {xr, 1, 1, 1, 1}, out_cols[5] = {1, xc, xc, xc, xr};
+        DM *outputs[5] = {nullptr, nullptr, nullptr, nullptr, nullptr};
+        void *funcs[1] = {reinterpret_cast<void *>(&pipeline_body_all)};
+        reinterpret_cast<void (*)(DM **, size_t, bool *, Structure **, size_t, int64_t *, int64_t *, int64_t *, int64_t *,
+                                  size_t, void **, int, DaphneContext *)>(
+            sym("_vectorizedPipeline__DenseMatrix_double_variadic__size_t__bool__Structure_variadic__size_t__int64_t__"
+                "int64_t__int64_t__int64_t__size_t__void_variadic"))(outputs, 5, is_scalar, inputs, 2, out_rows, out_cols,
+                                                                     splits, combines, 1, funcs, 12, &g_ctx);
+        const int64_t want_r[5] = {xr, 1, 1, 1, 1}, want_c[5] = {1, xc, xc, xc, xr};
+        int64_t at = 0, r, c;
+        int rc = 0;
+        for (int o = 0; o < 5 && rc == 0; o++) {
+            rc = copy_out(outputs[o], out + at, want_r[o] * want_c[o], &r, &c);
+            if (rc == 0 && (r != want_r[o] || c != want_c[o]))
+                rc = 4;
+            at += want_r[o] * want_c[o];
+        }
+        DataObjectFactory::destroy(X, outputs[0], outputs[1], outputs[2], outputs[3], outputs[4]);
+        return rc;
+    });
+}
+// number of devices the scheduler spreads a pipeline over
+int drv_devices() {
+    int n = 0;
+    db2_group_size(b200::group(&g_ctx), &n);
+    return n;
+}
+
+// Connected components (test/api/cli/algorithms/components.daphne:14-26) as the kernel calls the script lowers to, by
+// symbol name, on a real CSRMatrix:
+//   c = seq(1, n); while (diff > 0 & iter <= maxi) { u = max(aggMax(G * t(c), 0), c); diff = sum(u != c); c = u; }
+// G is given in the reference's layout (values, size_t column indices, size_t row offsets).  labels: n doubles.
+int drv_components(const double *values, const uint64_t *col_idx, const uint64_t *row_off, int64_t n, int64_t maxi,
+                   double *labels, int64_t *iterations) {
+    return guarded([&] {
+        using DM = DenseMatrix<double>;
+        using CM = CSRMatrix<double>;
+        const size_t nnz = (size_t)row_off[n];
+        CM *G = DataObjectFactory::create<CM>((size_t)n, (size_t)n, nnz, false);
+        memcpy(G->getValues(), values, nnz * sizeof(double));
+        memcpy(G->getColIdxs(), col_idx, nnz * sizeof(size_t));
+        memcpy(G->getRowOffsets(), row_off, (size_t)(n + 1) * sizeof(size_t));
+        DM *c = DataObjectFactory::create<DM>((size_t)n, 1, false);
+        for (int64_t i = 0; i < n; i++)
+            c->getValues()[i] = (double)(i + 1);
+        auto transpose = reinterpret_cast<void (*)(DM **, const DM *, int, DaphneContext *)>(
+            sym("CUDA_transpose__DenseMatrix_double__DenseMatrix_double"));
+        auto ew_mul = reinterpret_cast<void (*)(CM **, const CM *, const DM *, int, DaphneContext *)>(
+            sym("_ewMul__CSRMatrix_double__CSRMatrix_double__DenseMatrix_double"));
+        auto max_row = reinterpret_cast<void (*)(DM **, const CM *, int, DaphneContext *)>(
+            sym("_maxRow__DenseMatrix_double__CSRMatrix_double"));
+        auto ew_max = reinterpret_cast<void (*)(DM **, const DM *, const DM *, int, DaphneContext *)>(
+            sym("CUDA_ewMax__DenseMatrix_double__DenseMatrix_double__DenseMatrix_double"));
+        auto ew_neq = reinterpret_cast<void (*)(DM **, const DM *, const DM *, int, DaphneContext *)>(
+            sym("CUDA_ewNeq__DenseMatrix_double__DenseMatrix_double__DenseMatrix_double"));
+        auto sum_all = reinterpret_cast<void (*)(double *, const DM *, int, DaphneContext *)>(
+            sym("CUDA_sumAll__double__DenseMatrix_double"));
+        auto dec_ref = [](Structure *o) { DataObjectFactory::destroy(o); }; // what _decRef__Structure does
+        double diff = 1.0;
+        int64_t it = 1;
+        while (diff > 0.0 && it <= maxi) {
+            DM *tc = nullptr, *mx = nullptr, *u = nullptr, *ne = nullptr;
+            CM *prod = nullptr;
+            transpose(&tc, c, 1, &g_ctx);
+            ew_mul(&prod, G, tc, 2, &g_ctx);
+            max_row(&mx, prod, 3, &g_ctx);
+            ew_max(&u, mx, c, 4, &g_ctx);
+            ew_neq(&ne, u, c, 5, &g_ctx);
+            sum_all(&diff, ne, 6, &g_ctx);
+            dec_ref(tc);
+            dec_ref(prod);
+            dec_ref(mx);
+            dec_ref(ne);
+            dec_ref(c);
+            c = u;
+            it++;
+        }
+        *iterations = it - 1;
+        int64_t r, cc;
+        int rc = copy_out(c, labels, n, &r, &cc);
+        dec_ref(c);
+        dec_ref(G);
         return rc;
     });
 }

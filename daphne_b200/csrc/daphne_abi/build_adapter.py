@@ -37,7 +37,14 @@ EXT_HEADERS = {"EwUnaryMat.h": None, "CTable.h": None, "OuterBinary.h": None, "A
                "CondMatMatSca.h": None, "CondMatScaMat.h": None, "CondMatScaSca.h": None,
                "AggRow.h": {"IDXMIN", "IDXMAX", "MEAN", "VAR", "STDDEV", "PROD"},
                "AggCol.h": {"IDXMIN", "IDXMAX", "MEAN", "VAR", "STDDEV", "PROD"},
-               "AggAll.h": {"MEAN", "VAR", "STDDEV", "PROD"}}
+               "AggAll.h": {"MEAN", "VAR", "STDDEV", "PROD"},
+               # CSRMatrix operands (double): the sparse-times-dense product, its row aggregation, CSR @ dense
+               "EwBinaryMat.h": {"MUL"}, "MatMul.h": None, "Gemv.h": None}
+CSR_HEADERS = {"EwBinaryMat.h": [["CSRMatrix", "double"], ["CSRMatrix", "double"], ["DenseMatrix", "double"]],
+               "MatMul.h": [["DenseMatrix", "double"], ["CSRMatrix", "double"], ["DenseMatrix", "double"]],
+               "Gemv.h": [["DenseMatrix", "double"], ["CSRMatrix", "double"], ["DenseMatrix", "double"]],
+               "AggRow.h": [["DenseMatrix", "double"], ["CSRMatrix", "double"]]}
+CSR_AGG_OPS = ["SUM", "MIN", "MAX"]
 DEVICE_VTS = {"double", "float", "int64_t"}
 
 
@@ -49,6 +56,8 @@ def default_source() -> Path:
 
 def _ext_instantiation_ok(header: str, inst) -> bool:
     """Dense matrices of the value types the device kernels implement; index results are size_t."""
+    if header in ("EwBinaryMat.h", "MatMul.h", "Gemv.h"):
+        return [list(t) for t in inst] == CSR_HEADERS[header]
     vts, scalars = [], []
     for tv in inst:
         if isinstance(tv, list):
@@ -98,6 +107,8 @@ def ext_spec(daphne_src: Path) -> list:
                     continue
             if inst:
                 out.append(b)
+            if header == "AggRow.h" and CSR_HEADERS[header] in [[list(t) for t in i] for i in a["instantiations"]]:
+                out.append({"name": ["CPP"], "instantiations": [CSR_HEADERS[header]], "opCodes": CSR_AGG_OPS})
         if out:
             keep.append({"kernelTemplate": k["kernelTemplate"], "api": out})
     return keep
@@ -146,8 +157,8 @@ def build(daphne_src: str | Path | None = None) -> Path:
            "-I", str(site / "flashinfer/data/spdlog/include"), "-I", str(PKG.parent / "include")]
     flags = ["-std=c++20", "-O2", "-fPIC", "-pthread", "-DFMT_HEADER_ONLY", "-w"]
     gen = sorted(OUT.glob("CUDAkernels*.cpp"))
-    ref_srcs = [ds / n for n in ("Structure.cpp", "MetaDataObject.cpp", "DenseMatrix.cpp", "DataPlacement.cpp",
-                                 "ValueTypeUtils.cpp")]
+    ref_srcs = [ds / n for n in ("Structure.cpp", "MetaDataObject.cpp", "DenseMatrix.cpp", "CSRMatrix.cpp",
+                                 "DataPlacement.cpp", "ValueTypeUtils.cpp")]
     lib = OUT / "libCUDAKernels.so"
     cmd = ["g++", *flags, "-shared", "-o", str(lib), *inc, *map(str, gen), str(HERE / "adapter.cpp"),
            *map(str, ref_srcs), "-L", str(PKG), "-ldaphne_b200", f"-Wl,-rpath,{PKG}", "-Wl,-rpath,$ORIGIN/.."]

@@ -144,6 +144,63 @@ int copy_to_context(db2_context *ctx, db2_matrix *src, db2_matrix **out) {
     return DB2_OK;
 }
 
+// Combines the equally shaped partials parts[d] (one per device of the group, device-resident) with ADD / MIN / MAX.
+// out[d] receives the combined matrix of device d (a new reference: either the partial itself, combined in place by
+// NCCL, or a new matrix folded from copies of all partials in device order); consumed partials are set to NULL in
+// `slots` (the caller releases what is left).
+int combine_partials(db2_group *g, std::vector<std::vector<db2_matrix *>> &slots, size_t o, int cmb,
+                     std::vector<db2_matrix *> &out) {
+    const int n = (int)g->ctxs.size();
+    std::vector<db2_matrix *> parts(n);
+    db2_matrix *r0 = slots[0][o];
+    for (int d = 0; d < n; d++) {
+        parts[d] = slots[d][o];
+        DB2_CHECK(parts[d], DB2_EINVAL, "missing partial result on device index %d", d);
+        bind_device(g->ctxs[d]);
+        DB2_TRY(ensure_device(parts[d]));
+        DB2_CHECK(parts[d]->dev_ld == parts[d]->cols || parts[d]->rows == 1, DB2_EUNSUPPORTED,
+                  "a partial result is a strided view");
+        DB2_CHECK(parts[d]->rows == r0->rows && parts[d]->cols == r0->cols && parts[d]->dtype == r0->dtype, DB2_EINVAL,
+                  "a partial result has different shapes on different devices");
+    }
+    if (n == 1 || g->nccl) {
+        if (n > 1)
+            DB2_TRY(nccl_allreduce_group(g->ctxs, parts, cmb));
+        for (int d = 0; d < n; d++) {
+            out[d] = parts[d];
+            slots[d][o] = nullptr;
+        }
+        return DB2_OK;
+    }
+    // peer copies + fold, in device order on every device
+    const int op = cmb == DB2_COMBINE_ADD ? DB2_ADD : (cmb == DB2_COMBINE_MIN ? DB2_MIN : DB2_MAX);
+    for (int d = 0; d < n; d++) {
+        db2_context *c = g->ctxs[d];
+        db2_matrix *acc = nullptr;
+        for (int e = 0; e < n; e++) {
+            db2_matrix *pe = nullptr;
+            int rc = copy_to_context(c, parts[e], &pe);
+            bind_device(c);
+            if (rc == DB2_OK && acc) {
+                rc = db2_ewBinaryMat(c, op, &acc, acc, pe);
+                db2_matrix_decref(pe);
+            } else if (rc == DB2_OK) {
+                acc = pe;
+            }
+            if (rc != DB2_OK) {
+                if (acc)
+                    db2_matrix_decref(acc);
+                return rc;
+            }
+        }
+        out[d] = acc;
+        std::lock_guard<std::mutex> lock(c->mu);
+        c->stats.collectives++;
+        c->stats.collective_bytes += (uint64_t)r0->rows * r0->cols * dtype_size(r0->dtype) * (n - 1);
+    }
+    return DB2_OK;
+}
+
 } // namespace
 
 extern "C" {
@@ -182,8 +239,10 @@ int db2_group_create(const int *devices, int ndev, db2_group **out) {
         DB2_TRY(db2_context_create(devs[i], &c));
         g->ctxs.push_back(c);
         for (size_t j = 0; j < i; j++)
-            if (devs[j] == devs[i])
+            if (devs[j] == devs[i]) {
                 g->distinct = false;
+                c->dup++;
+            }
     }
     // peer access between all pairs (NVLink through NVSwitch): copies between devices then go directly
     if (g->distinct && devs.size() > 1) {
@@ -497,60 +556,7 @@ int db2_vectorizedPipelineGroup(db2_group *g, db2_dist **outputs, size_t numOutp
         // ADD / MIN / MAX: combine the devices' partials; every device ends up with the combined result
         outs.emplace_back(new_dist(g, -1, r0->dtype, r0->rows, r0->cols), db2_dist_decref);
         db2_dist *od = outs.back().get();
-        std::vector<db2_matrix *> parts(n);
-        for (int d = 0; d < n; d++) {
-            parts[d] = res[d][o];
-            bind_device(g->ctxs[d]);
-            rc = ensure_device(parts[d]);
-            if (rc == DB2_OK && !(parts[d]->dev_ld == parts[d]->cols || parts[d]->rows == 1))
-                rc = set_error(DB2_EUNSUPPORTED, "partial result %zu is a strided view", o);
-            if (rc == DB2_OK && (parts[d]->rows != r0->rows || parts[d]->cols != r0->cols))
-                rc = set_error(DB2_EINVAL, "partial result %zu has different shapes on different devices", o);
-            if (rc != DB2_OK) {
-                release_all();
-                return rc;
-            }
-        }
-        if (n == 1) {
-            od->shard[0] = parts[0];
-            res[0][o] = nullptr;
-            continue;
-        }
-        if (g->nccl) {
-            rc = nccl_allreduce_group(g->ctxs, parts, (int)cmb);
-            if (rc != DB2_OK) {
-                release_all();
-                return rc;
-            }
-            for (int d = 0; d < n; d++) {
-                od->shard[d] = parts[d];
-                res[d][o] = nullptr;
-            }
-            continue;
-        }
-        // peer copies + fold, in device order on every device
-        const int op = cmb == DB2_COMBINE_ADD ? DB2_ADD : (cmb == DB2_COMBINE_MIN ? DB2_MIN : DB2_MAX);
-        for (int d = 0; d < n && rc == DB2_OK; d++) {
-            db2_context *c = g->ctxs[d];
-            db2_matrix *acc = nullptr;
-            for (int e = 0; e < n && rc == DB2_OK; e++) {
-                db2_matrix *pe = nullptr;
-                rc = copy_to_context(c, parts[e], &pe);
-                if (rc != DB2_OK)
-                    break;
-                bind_device(c);
-                if (!acc) {
-                    acc = pe;
-                } else {
-                    rc = db2_ewBinaryMat(c, op, &acc, acc, pe);
-                    db2_matrix_decref(pe);
-                }
-            }
-            od->shard[d] = acc;
-            std::lock_guard<std::mutex> lock(c->mu);
-            c->stats.collectives++;
-            c->stats.collective_bytes += (uint64_t)r0->rows * r0->cols * dtype_size(r0->dtype) * (n - 1);
-        }
+        rc = combine_partials(g, res, o, (int)cmb, od->shard);
         if (rc != DB2_OK) {
             release_all();
             return rc;
@@ -559,6 +565,87 @@ int db2_vectorizedPipelineGroup(db2_group *g, db2_dist **outputs, size_t numOutp
     release_all(); // the partials that were copied (fold path); moved entries are NULL
     for (size_t o = 0; o < numOutputs; o++)
         outputs[o] = outs[o].release();
+    return DB2_OK;
+    DB2_API_END
+}
+
+/* In-place-style combine of one partial per device (ms[d] on device d of the group): on return ms[d] is the combined
+ * matrix of device d (the handle may have been replaced; the old one is released). */
+int db2_group_allreduce(db2_group *g, db2_matrix **ms, int combine) {
+    DB2_API_BEGIN
+    DB2_CHECK(g && ms, DB2_EINVAL, "null argument");
+    DB2_CHECK(combine == DB2_COMBINE_ADD || combine == DB2_COMBINE_MIN || combine == DB2_COMBINE_MAX, DB2_EINVAL,
+              "only ADD, MIN and MAX results are combined");
+    const int n = (int)g->ctxs.size();
+    std::vector<std::vector<db2_matrix *>> slots(n, std::vector<db2_matrix *>(1, nullptr));
+    for (int d = 0; d < n; d++) {
+        DB2_CHECK(ms[d] && ms[d]->ctx == g->ctxs[d], DB2_EINVAL,
+                  "partial %d does not live on device index %d of the group", d, d);
+        slots[d][0] = ms[d];
+    }
+    std::vector<db2_matrix *> out(n, nullptr);
+    DB2_TRY(combine_partials(g, slots, 0, combine, out));
+    for (int d = 0; d < n; d++) {
+        if (slots[d][0]) { // not consumed: a new matrix replaces it
+            bind_device(g->ctxs[d]);
+            db2_matrix_decref(slots[d][0]);
+        }
+        ms[d] = out[d];
+    }
+    return DB2_OK;
+    DB2_API_END
+}
+
+/* a copy of src as a new matrix of ctx (any two contexts of this process; a peer copy when their devices differ) */
+int db2_matrix_to_context(db2_context *ctx, db2_matrix *src, db2_matrix **out) {
+    DB2_API_BEGIN
+    DB2_CHECK(ctx && src && out, DB2_EINVAL, "null argument");
+    return copy_to_context(ctx, src, out);
+    DB2_API_END
+}
+
+/* dst[r0 : r0 + src.rows, c0 : c0 + src.cols] = src; dst and src may live on different devices */
+int db2_matrix_copy_block(db2_matrix *dst, int64_t r0, int64_t c0, db2_matrix *src) {
+    DB2_API_BEGIN
+    DB2_CHECK(dst && src, DB2_EINVAL, "null argument");
+    DB2_CHECK(dst->dtype == src->dtype, DB2_EINVAL, "value types differ");
+    DB2_CHECK(r0 >= 0 && c0 >= 0 && r0 + src->rows <= dst->rows && c0 + src->cols <= dst->cols, DB2_EINVAL,
+              "block (%lld x %lld at %lld, %lld) outside the destination (%lld x %lld)", (long long)src->rows,
+              (long long)src->cols, (long long)r0, (long long)c0, (long long)dst->rows, (long long)dst->cols);
+    if (src->rows * src->cols == 0)
+        return DB2_OK;
+    bind_device(src->ctx);
+    DB2_TRY(ensure_device(src));
+    cudaEvent_t ev;
+    DB2_CUDA(cudaEventCreateWithFlags(&ev, cudaEventDisableTiming));
+    DB2_CUDA(cudaEventRecord(ev, src->ctx->stream));
+    db2_context *ctx = dst->ctx;
+    bind_device(ctx);
+    DB2_TRY(ensure_device(dst));
+    DB2_CUDA(cudaStreamWaitEvent(ctx->stream, ev, 0));
+    DB2_CUDA(cudaEventDestroy(ev));
+    const size_t es = src->esize();
+    cudaMemcpy3DPeerParms p = {};
+    p.srcDevice = src->ctx->device;
+    p.dstDevice = ctx->device;
+    p.srcPtr = make_cudaPitchedPtr(src->dev_ptr(), (size_t)src->dev_ld * es, (size_t)src->cols * es, (size_t)src->rows);
+    p.dstPtr = make_cudaPitchedPtr(static_cast<char *>(dst->dev_ptr()) + ((size_t)r0 * dst->dev_ld + (size_t)c0) * es,
+                                   (size_t)dst->dev_ld * es, (size_t)src->cols * es, (size_t)src->rows);
+    p.extent = make_cudaExtent((size_t)src->cols * es, (size_t)src->rows, 1);
+    DB2_CUDA(cudaMemcpy3DPeerAsync(&p, ctx->stream));
+    dst->dev->version++;
+    dst->host_valid = false;
+    if (src->ctx != ctx) { // the source may be released by its own context right after this call
+        cudaEvent_t done;
+        DB2_CUDA(cudaEventCreateWithFlags(&done, cudaEventDisableTiming));
+        DB2_CUDA(cudaEventRecord(done, ctx->stream));
+        bind_device(src->ctx);
+        DB2_CUDA(cudaStreamWaitEvent(src->ctx->stream, done, 0));
+        DB2_CUDA(cudaEventDestroy(done));
+        bind_device(ctx);
+    }
+    std::lock_guard<std::mutex> lock(ctx->mu);
+    ctx->stats.d2d_bytes += (uint64_t)src->rows * src->cols * es;
     return DB2_OK;
     DB2_API_END
 }

@@ -66,6 +66,10 @@ int ctx_alloc(db2_context *ctx, size_t bytes, void **out) {
         ctx->cached_bytes -= it->first;
         ctx->free_blocks.erase(it);
     } else {
+        if (ctx->mem_budget && ctx->stats.live_bytes + want > ctx->mem_budget)
+            return set_error(DB2_ENOMEM, "out of device memory: %zu more bytes would exceed the budget of %zu bytes of "
+                                         "the context on device %d (%llu in use)",
+                             want, ctx->mem_budget, ctx->device, (unsigned long long)ctx->stats.live_bytes);
         cudaError_t e = cudaMalloc(out, want);
         if (e == cudaErrorMemoryAllocation) {
             cudaGetLastError();
@@ -238,12 +242,23 @@ int db2_context_device(const db2_context *ctx, int *device) {
     *device = ctx->device;
     return DB2_OK;
 }
+int db2_context_ordinal(const db2_context *ctx, int *dup) {
+    DB2_CHECK(ctx && dup, DB2_EINVAL, "null argument");
+    *dup = ctx->dup;
+    return DB2_OK;
+}
 void *db2_context_stream(db2_context *ctx) { return ctx ? ctx->stream : nullptr; }
 int db2_context_sync(db2_context *ctx) {
     DB2_CHECK(ctx, DB2_EINVAL, "null context");
     bind_device(ctx);
     DB2_TRY(lazy_flush_all(ctx));
     DB2_CUDA(cudaStreamSynchronize(ctx->stream));
+    return DB2_OK;
+}
+int db2_context_set_mem_budget(db2_context *ctx, size_t bytes) {
+    DB2_CHECK(ctx, DB2_EINVAL, "null context");
+    std::lock_guard<std::mutex> lock(ctx->mu);
+    ctx->mem_budget = bytes;
     return DB2_OK;
 }
 int db2_context_stats(db2_context *ctx, db2_stats *out) {

@@ -31,6 +31,7 @@ struct db2_context {
     std::multimap<size_t, void *> free_blocks;
     std::unordered_map<void *, size_t> block_size;
     size_t cached_bytes = 0;
+    size_t mem_budget = 0; // > 0: pooled allocations may hold at most this many bytes (db2_context_set_mem_budget)
     // reusable scratch for two-stage reductions (grown on demand, stream-ordered reuse)
     void *scratch = nullptr;
     size_t scratch_bytes = 0;
@@ -43,6 +44,7 @@ struct db2_context {
     bool comm_is_fake = false;   // installed by the test hook db2_comm_test_attach: never passed to NCCL's destroy
     // member of a single-process device group (group.cu): the communicator that ncclCommInitAll made for this device
     void *group_comm = nullptr;
+    int dup = 0; // number of contexts of the same group, listed before this one, that share its physical device
     // column statistics of the matrix that was last aggregated by columns (colstats.cu)
     std::shared_ptr<db2::ColStats> colstats;
     std::mutex mu;

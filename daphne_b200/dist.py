@@ -111,17 +111,22 @@ class Comm:
         from .lib import check, lib
         check(lib.db2_allreduce(ctx.handle, m.handle, int(combine)))
 
-    def allgather_rows(self, ctx, m, k=None):
-        """Concatenates equally sized row shards in rank order."""
+    def allgather_rows(self, ctx, m, total_rows: int, k=None):
+        """Concatenates the row shards of `row_block(total_rows, rank, world)` in rank order; the shards may differ in
+        height by one row.  A shard of any other height is refused before anything is exchanged."""
+        lo, hi = row_block(total_rows, self.rank, self.world)
+        if m.rows != hi - lo:
+            raise ValueError(f"rank {self.rank} of {self.world} holds {m.rows} rows, its block of {total_rows} rows "
+                             f"has {hi - lo}")
         if self.device_collectives(ctx):
             import ctypes as C
 
             from . import kernels as K
             from .lib import check, lib
             h = C.c_void_p()
-            check(lib.db2_allgather_rows(ctx.handle, m.handle, C.byref(h)))
+            check(lib.db2_allgatherv_rows(ctx.handle, m.handle, int(total_rows), C.byref(h)))
             return K.DenseMatrix(ctx, h)
-        return k.DenseMatrix.from_numpy(ctx, self.allgather_numpy(m.to_numpy()))
+        return k.DenseMatrix.from_numpy(ctx, self.allgather_ragged(m.to_numpy()))
 
     def barrier(self):
         if self.world > 1:

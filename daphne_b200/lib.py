@@ -92,9 +92,11 @@ _SIGS = {
     "db2_context_create": (i32, [i32, _P(vp)]),
     "db2_context_destroy": (i32, [vp]),
     "db2_context_device": (i32, [vp, _P(i32)]),
+    "db2_context_ordinal": (i32, [vp, _P(i32)]),
     "db2_context_stream": (vp, [vp]),
     "db2_context_sync": (i32, [vp]),
     "db2_context_stats": (i32, [vp, vp]),
+    "db2_context_set_mem_budget": (i32, [vp, sz]),
     "db2_comm_unique_id": (i32, [vp]),
     "db2_comm_init": (i32, [vp, i32, i32, vp]),
     "db2_comm_destroy": (i32, [vp]),
@@ -116,6 +118,9 @@ _SIGS = {
     "db2_dist_decref": (i32, [vp]),
     "db2_dist_to_host": (i32, [vp, vp, i64]),
     "db2_dist_gather": (i32, [vp, i32, _P(vp)]),
+    "db2_group_allreduce": (i32, [vp, _P(vp), i32]),
+    "db2_matrix_to_context": (i32, [vp, vp, _P(vp)]),
+    "db2_matrix_copy_block": (i32, [vp, i64, i64, vp]),
     "db2_vectorizedPipelineGroup": (i32, [vp, _P(vp), sz, _P(i32), _P(vp), sz, _P(i64), _P(i64), _P(i64), _P(i64), vp,
                                          i64]),
     "db2_matrix_create": (i32, [vp, i32, i64, i64, i32, _P(vp)]),

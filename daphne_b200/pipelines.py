@@ -232,18 +232,30 @@ def connected_components(ctx, G, maxi: int = 1000, comm: Optional[Comm] = None, 
     K = kernels or globals()["K"]
     n = G.cols
     lo, hi = row_block if row_block is not None else (0, G.rows)
+    sharded = comm is not None and comm.world > 1
+    on_device = sharded and comm.device_collectives(ctx)
     c_full = K.seq(ctx, 1.0, float(n), 1.0)
     it, diff = 1, 1.0
     c_loc = c_full.slice_rows(lo, hi)
     while diff > 0.0 and it <= maxi:
         prod = K.ewMulCsrDense(G, K.transpose(c_full))
         u = K.ewBinaryMat(B.MAX, K.aggRowCsr(A.MAX, prod), c_loc)
-        diff = _allreduce_scalar(ctx, K.aggAll(A.SUM, K.ewBinaryMat(B.NEQ, u, c_loc)), comm)
-        if comm is not None and comm.world > 1:
-            c_full = comm.allgather_rows(ctx, u, k=K)
+        changed = K.ewBinaryMat(B.NEQ, u, c_loc)
+        if on_device:
+            # the shard's change count stays on the device and is combined there; the all-gather of the labels is
+            # issued behind it on the same stream, so the one host read below waits for both
+            cnt = K.aggCol(A.SUM, changed)
+            comm.allreduce_device(ctx, cnt, COMBINE_ADD)
+            c_full = comm.allgather_rows(ctx, u, n, k=K)
             c_loc = c_full.slice_rows(lo, hi)
+            diff = float(cnt.to_numpy()[0, 0])
         else:
-            c_full = u
-            c_loc = u
+            diff = _allreduce_scalar(ctx, K.aggAll(A.SUM, changed), comm)
+            if sharded:
+                c_full = comm.allgather_rows(ctx, u, n, k=K)
+                c_loc = c_full.slice_rows(lo, hi)
+            else:
+                c_full = u
+                c_loc = u
         it += 1
     return ComponentsResult(c_loc, it - 1)

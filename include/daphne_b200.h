@@ -270,9 +270,15 @@ typedef struct db2_stats {
 int db2_context_create(int device, db2_context **ctx);
 int db2_context_destroy(db2_context *ctx);
 int db2_context_device(const db2_context *ctx, int *device);
+/* 0 for the first context of a device group on its device, k for the k-th further context that shares the device */
+int db2_context_ordinal(const db2_context *ctx, int *dup);
 void *db2_context_stream(db2_context *ctx);
 int db2_context_sync(db2_context *ctx);
 int db2_context_stats(db2_context *ctx, db2_stats *out);
+/* Upper bound on the bytes the context's matrices and scratch may hold (0 = the device's capacity); an allocation
+ * that would exceed it fails with DB2_ENOMEM.  The reference's context has such a budget too (0.9 x device memory,
+ * src/runtime/local/context/CUDAContext.cpp:41-75) but only consults it when deciding what to place on the GPU. */
+int db2_context_set_mem_budget(db2_context *ctx, size_t bytes);
 
 /* Row-sharded multi-GPU execution: one process (and context) per GPU.  rank 0 creates an id with
  * db2_comm_unique_id, every rank passes the same 128 bytes to db2_comm_init (exchange them with any host-side
@@ -410,6 +416,17 @@ int db2_dist_decref(db2_dist *d);
 int db2_dist_to_host(db2_dist *d, void *dst, int64_t dst_ld);
 /* the whole matrix on device `index` of the group (new reference); other devices' blocks arrive by peer copies */
 int db2_dist_gather(db2_dist *d, int index, db2_matrix **out);
+
+/* Combine of one partial per device (ms[i] lives on device i of the group) with DB2_COMBINE_ADD / MIN / MAX; on return
+ * ms[i] is the combined matrix on device i (a handle may have been replaced by a new one, the old one released).
+ * The device-side twin of the host-side merge under a mutex in src/runtime/local/vectorized/Tasks.cpp:51-82. */
+int db2_group_allreduce(db2_group *g, db2_matrix **ms, int combine);
+/* a copy of src as a new matrix of ctx; any two contexts of this process (a peer copy when their devices differ) */
+int db2_matrix_to_context(db2_context *ctx, db2_matrix *src, db2_matrix **out);
+/* dst[r0 : r0 + src.rows, c0 : c0 + src.cols] = src; dst and src may live on different devices.  How the row blocks
+ * of several devices are put into one result (the reference copies task results into the result at
+ * rowSkip * rowStart, src/runtime/local/vectorized/TasksCUDA.cpp:77-102). */
+int db2_matrix_copy_block(db2_matrix *dst, int64_t r0, int64_t c0, db2_matrix *src);
 
 /* The row-partition scheduler over all devices of a group: device i runs db2_vectorizedPipeline on block i of the
  * ROWS-split inputs (which must share one row partition; broadcast inputs must be replicated) from its own host

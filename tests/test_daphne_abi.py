@@ -58,11 +58,16 @@ def test_extension_catalog_registers_cpu_names_for_ops_without_cuda_support():
                  "_ctable__DenseMatrix_double__DenseMatrix_int64_t__DenseMatrix_int64_t__double__int64_t__int64_t"):
         assert must in names, must
     # nothing that the CUDA catalog already serves is shadowed
-    assert not any(e["opMnemonic"] in ("sumRow", "minRow", "maxRow", "sumCol", "sumAll") for e in cat)
+    assert not any(e["opMnemonic"] in ("sumRow", "minRow", "maxRow", "sumCol", "sumAll") and
+                   not any("CSRMatrix" in t for t in e["argTypes"]) for e in cat)
+    # the sparse operators of connected components: no CUDA instantiation exists in the reference
+    for must in ("_ewMul__CSRMatrix_double__CSRMatrix_double__DenseMatrix_double",
+                 "_maxRow__DenseMatrix_double__CSRMatrix_double",
+                 "_matMul__DenseMatrix_double__CSRMatrix_double__DenseMatrix_double__bool__bool"):
+        assert must in names, must
 
 
-@pytest.fixture(scope="module")
-def drv():
+def _load_driver():
     C.CDLL(str(ROOT / "daphne_b200" / "libdaphne_b200.so"), mode=C.RTLD_GLOBAL)
     C.CDLL(str(ABI / "libCUDAKernels.so"), mode=C.RTLD_GLOBAL)
     C.CDLL(str(ABI / "libB200ExtKernels.so"), mode=C.RTLD_GLOBAL)
@@ -70,6 +75,11 @@ def drv():
     d.drv_last_error.restype = C.c_char_p
     assert d.drv_init() == 0, d.drv_last_error()
     return d
+
+
+@pytest.fixture(scope="module")
+def drv():
+    return _load_driver()
 
 
 def _p(a):
@@ -203,3 +213,83 @@ def test_scheduler_under_daphnes_symbol_name(drv, batch, monkeypatch):
         np.testing.assert_allclose(out[n:], (x - mu).sum(0), rtol=1e-10, atol=1e-9)
     finally:
         os.environ.pop("DAPHNE_B200_BATCH_ROWS", None)
+
+
+def _check_pipeline_all(d, n=20001, cols=12, deferred=0):
+    rng = np.random.default_rng(11)
+    x, s = rng.standard_normal((n, cols)), 0.625
+    out = np.empty(2 * n + 3 * cols)
+    rc = d.drv_pipeline_all(_p(x), C.c_int64(n), C.c_int64(cols), C.c_double(s), C.c_int(deferred), _p(out))
+    assert rc == 0, d.drv_last_error()
+    np.testing.assert_allclose(out[:n], (x * s).sum(1), rtol=1e-12, atol=1e-12)                      # ROWS
+    np.testing.assert_allclose(out[n:n + cols], x.sum(0), rtol=1e-10, atol=1e-9)                     # ADD
+    assert np.array_equal(out[n + cols:n + 2 * cols], x.max(0))                                      # MAX
+    assert np.array_equal(out[n + 2 * cols:n + 3 * cols], x.min(0))                                  # MIN
+    assert np.array_equal(out[n + 3 * cols:], x.max(1))                                              # COLS
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("batch", [None, 3000])
+def test_scheduler_all_combines_under_daphnes_symbol_name(drv, batch):
+    import os
+    if batch is not None:
+        os.environ["DAPHNE_B200_BATCH_ROWS"] = str(batch)
+    try:
+        _check_pipeline_all(drv)
+        _check_pipeline_all(drv, deferred=1)
+    finally:
+        os.environ.pop("DAPHNE_B200_BATCH_ROWS", None)
+
+
+@pytest.mark.gpu
+def test_all_five_scheduler_entry_points_are_exported():
+    out = subprocess.run(["nm", "-D", "--defined-only", str(ABI / "libB200ExtKernels.so")], capture_output=True,
+                         text=True, check=True).stdout
+    for dt in ("DenseMatrix_double", "DenseMatrix_float", "DenseMatrix_int64_t", "CSRMatrix_double", "CSRMatrix_float"):
+        assert (f"_vectorizedPipeline__{dt}_variadic__size_t__bool__Structure_variadic__size_t__int64_t__int64_t__"
+                "int64_t__int64_t__size_t__void_variadic") in out, dt
+
+
+@pytest.mark.gpu
+def test_connected_components_by_symbol_name_on_a_real_csr_matrix(drv):
+    """The cfg4 loop through DAPHNE's names (_ewMul__CSRMatrix..., _maxRow__DenseMatrix_double__CSRMatrix_double, CUDA_ewMax,
+    CUDA_ewNeq, CUDA_sumAll) on CSRMatrix objects: labels bit-equal to the reference's CPU kernels."""
+    from oracle import cpu_pipelines as cpu
+    from tests.test_pipelines_gpu import _graph
+    for n, deg, seed in [(3000, 2, 1), (100000, 8, 4)]:
+        g = _graph(n, deg, seed)
+        vals = np.ascontiguousarray(g.data, dtype=np.float64)
+        cols = np.ascontiguousarray(g.indices, dtype=np.uint64)
+        offs = np.ascontiguousarray(g.indptr, dtype=np.uint64)
+        labels, iters = np.empty(n), C.c_int64()
+        rc = drv.drv_components(_p(vals), _p(cols), _p(offs), C.c_int64(n), C.c_int64(1000), _p(labels),
+                                C.byref(iters))
+        assert rc == 0, drv.drv_last_error()
+        c, it = cpu.connected_components(g)
+        assert iters.value == it
+        assert np.array_equal(labels.view(np.uint64), c[:, 0].view(np.uint64))
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("devices", ["0,0", "0,0,0", "all"])
+def test_scheduler_over_several_devices_in_one_process(devices):
+    """The scheduler under DAPHNE's name with a device group of more than one context (DAPHNE_B200_DEVICES): two or
+    three contexts that share device 0, and every visible device.  A fresh process, because the group is made once."""
+    import os
+    import sys
+    code = "\n".join([
+        "import sys",
+        f"sys.path.insert(0, {str(ROOT)!r})",
+        "from tests import test_daphne_abi as t",
+        "d = t._load_driver()",
+        "n = d.drv_devices()",
+        "t._check_pipeline_all(d)",
+        "t._check_pipeline_all(d, n=4099, deferred=1)",
+        "t._check_pipeline_all(d, n=2, cols=3)",
+        "print('devices', n)"])
+    env = dict(os.environ, DAPHNE_B200_DEVICES=devices)
+    r = subprocess.run([sys.executable, "-c", code.replace("\n", "\n")], capture_output=True, text=True, env=env,
+                       timeout=600)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-4000:]
+    n = int(r.stdout.strip().split()[-1])
+    assert n == (devices.count(",") + 1 if devices != "all" else n) and n >= 1

@@ -55,11 +55,17 @@ def _worker(rank, world, port, out_dir):
     lo, hi = row_block(1200, rank, world)
     km = pipelines.kmeans(None, K.DenseMatrix(xk[lo:hi]), K.DenseMatrix(c0), 4, comm, kernels=K)
     res["C"], res["assign"] = km.C.a, comm.allgather_ragged(km.assign.a)
-    # connected components (equal shards: the label vector is all-gathered)
-    g = _graph(600, 3, 9)
-    lo, hi = row_block(600, rank, world)
+    # connected components (the label vector is all-gathered every iteration; 601 vertices: ragged shards)
+    g = _graph(601, 3, 9)
+    lo, hi = row_block(601, rank, world)
     cc = pipelines.connected_components(None, K.CSRMatrix(g[lo:hi]), 1000, comm, (lo, hi), kernels=K)
     res["c"], res["iters"] = comm.allgather_ragged(cc.c.a), cc.iterations
+    # a shard that is not the rank's block is refused before anything is exchanged
+    try:
+        comm.allgather_rows(None, K.DenseMatrix(np.zeros((hi - lo + 1, 1))), 601, k=K)
+        res["refused"] = 0
+    except ValueError:
+        res["refused"] = 1
     np.savez(os.path.join(out_dir, f"rank{rank}.npz"), **res)
     dist.destroy_process_group()
 
@@ -80,7 +86,7 @@ def test_sharded_pipelines_equal_the_unsharded_ones(tmp_path, world):
     ne = pipelines.normal_equations(None, K.DenseMatrix(xx), K.DenseMatrix(yy), 0.001, kernels=K)
     xk = np.random.default_rng(3).random((1200, 6))
     km = pipelines.kmeans(None, K.DenseMatrix(xk), K.DenseMatrix(xk[:5].copy()), 4, kernels=K)
-    cc = pipelines.connected_components(None, K.CSRMatrix(_graph(600, 3, 9)), kernels=K)
+    cc = pipelines.connected_components(None, K.CSRMatrix(_graph(601, 3, 9)), kernels=K)
     for r in ranks:
         np.testing.assert_allclose(r["mu"], one.mu.a, rtol=1e-12)
         np.testing.assert_allclose(r["sd"], one.sd.a, rtol=1e-12)
@@ -94,6 +100,7 @@ def test_sharded_pipelines_equal_the_unsharded_ones(tmp_path, world):
         assert np.array_equal(r["assign"], km.assign.a)
         assert np.array_equal(r["c"], cc.c.a), "connected components must be bit-identical for every shard count"
         assert int(r["iters"]) == cc.iterations
+        assert int(r["refused"]) == 1
     for r in ranks[1:]:  # every rank ends with the same global values
         for key in ("mu", "sd", "A", "beta", "C"):
             assert np.array_equal(r[key], ranks[0][key])
