@@ -74,7 +74,9 @@ struct PerDeviceOnce {
     void mark() { done.fetch_or(uint64_t(1) << dev(), std::memory_order_release); }
 };
 
-inline size_t dtype_size(int dtype) { return dtype == DB2_F32 ? 4 : 8; }
+inline size_t dtype_size(int dtype) {
+    return dtype == DB2_U8 ? 1 : ((dtype == DB2_F32 || dtype == DB2_I32 || dtype == DB2_U32) ? 4 : 8);
+}
 
 inline cudaStream_t as_stream(void *s) { return reinterpret_cast<cudaStream_t>(s); }
 
@@ -95,6 +97,37 @@ __host__ __device__ inline bool aligned16(const void *p) { return (reinterpret_c
     } break;                                                                                                           \
     case DB2_I64: {                                                                                                    \
         using VT = int64_t;                                                                                            \
+        __VA_ARGS__;                                                                                                   \
+    } break;                                                                                                           \
+    default:                                                                                                           \
+        return ::db2::set_error(DB2_EUNSUPPORTED, "unsupported value type code %d", (int)(dtype));                     \
+    }
+
+// all six value types of the elementwise binary kernels (EwBinaryMat / EwBinaryObjSca)
+#define DB2_DISPATCH_DTYPE_EW(dtype, VT, ...)                                                                          \
+    switch (dtype) {                                                                                                   \
+    case DB2_F64: {                                                                                                    \
+        using VT = double;                                                                                             \
+        __VA_ARGS__;                                                                                                   \
+    } break;                                                                                                           \
+    case DB2_F32: {                                                                                                    \
+        using VT = float;                                                                                              \
+        __VA_ARGS__;                                                                                                   \
+    } break;                                                                                                           \
+    case DB2_I64: {                                                                                                    \
+        using VT = int64_t;                                                                                            \
+        __VA_ARGS__;                                                                                                   \
+    } break;                                                                                                           \
+    case DB2_U64: {                                                                                                    \
+        using VT = uint64_t;                                                                                           \
+        __VA_ARGS__;                                                                                                   \
+    } break;                                                                                                           \
+    case DB2_I32: {                                                                                                    \
+        using VT = int32_t;                                                                                            \
+        __VA_ARGS__;                                                                                                   \
+    } break;                                                                                                           \
+    case DB2_U32: {                                                                                                    \
+        using VT = uint32_t;                                                                                           \
         __VA_ARGS__;                                                                                                   \
     } break;                                                                                                           \
     default:                                                                                                           \

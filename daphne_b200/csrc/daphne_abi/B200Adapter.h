@@ -48,6 +48,12 @@ template <typename VT> constexpr int dtype_of() {
         return DB2_I64;
     if (std::is_same_v<VT, uint64_t> || std::is_same_v<VT, size_t>)
         return DB2_U64;
+    if (std::is_same_v<VT, int32_t>)
+        return DB2_I32;
+    if (std::is_same_v<VT, uint32_t>)
+        return DB2_U32;
+    if (std::is_same_v<VT, uint8_t> || std::is_same_v<VT, bool>)
+        return DB2_U8; // fill only
     return -1;
 }
 template <typename VT> void require_supported(const char *kernel) {
@@ -104,7 +110,7 @@ class AllocationDescriptorB200 : public IAllocationDescriptor {
     void createAllocation(size_t size, bool zero) override {
         if (box->m)
             return; // the placement was created around an existing (possibly deferred) result
-        const size_t es = dtype == DB2_F32 ? 4 : 8;
+        const size_t es = dtype == DB2_U8 ? 1 : ((dtype == DB2_F32 || dtype == DB2_I32 || dtype == DB2_U32) ? 4 : 8);
         if ((size_t)rows * cols * es != size) { // a caller that only knows bytes
             rows = 1;
             cols = (int64_t)(size / es);

@@ -366,4 +366,73 @@ int drv_components(const double *values, const uint64_t *col_idx, const uint64_t
         return rc;
     });
 }
+
+} // extern "C"
+
+namespace {
+template <typename VT> DenseMatrix<VT> *host_matrix_t(const VT *v, int64_t r, int64_t c) {
+    auto *m = DataObjectFactory::create<DenseMatrix<VT>>((size_t)r, (size_t)c, false);
+    memcpy(m->getValues(), v, sizeof(VT) * r * c);
+    return m;
+}
+template <typename VT> void copy_out_t(DenseMatrix<VT> *m, VT *out) {
+    const VT *v = static_cast<const DenseMatrix<VT> *>(m)->getValues();
+    for (size_t i = 0; i < m->getNumRows(); i++)
+        memcpy(out + i * m->getNumCols(), v + i * m->getRowSkip(), sizeof(VT) * m->getNumCols());
+}
+// res = kernel(lhs, rhs) with matrices of value type VT; rhs == nullptr: res = kernel(lhs, scalar)
+template <typename VT>
+int binary_t(const char *name, const VT *a, int64_t ar, int64_t ac, const VT *b, int64_t br, int64_t bc, const VT *s,
+             VT *out) {
+    return guarded([&] {
+        using DM = DenseMatrix<VT>;
+        DM *A = host_matrix_t<VT>(a, ar, ac), *R = nullptr;
+        if (b) {
+            DM *B = host_matrix_t<VT>(b, br, bc);
+            reinterpret_cast<void (*)(DM **, const DM *, const DM *, int, DaphneContext *)>(sym(name))(&R, A, B, 1, &g_ctx);
+            DataObjectFactory::destroy(B);
+        } else {
+            reinterpret_cast<void (*)(DM **, const DM *, VT, int, DaphneContext *)>(sym(name))(&R, A, *s, 1, &g_ctx);
+        }
+        copy_out_t<VT>(R, out);
+        DataObjectFactory::destroy(A, R);
+        return 0;
+    });
+}
+} // namespace
+
+extern "C" {
+// value type codes of include/daphne_b200.h; `out` holds ar * ac values
+int drv_binary_typed(const char *name, int dtype, const void *a, int64_t ar, int64_t ac, const void *b, int64_t br,
+                     int64_t bc, const void *scalar, void *out) {
+    switch (dtype) {
+    case DB2_F32: return binary_t<float>(name, (const float *)a, ar, ac, (const float *)b, br, bc, (const float *)scalar, (float *)out);
+    case DB2_I64: return binary_t<int64_t>(name, (const int64_t *)a, ar, ac, (const int64_t *)b, br, bc, (const int64_t *)scalar, (int64_t *)out);
+    case DB2_U64: return binary_t<uint64_t>(name, (const uint64_t *)a, ar, ac, (const uint64_t *)b, br, bc, (const uint64_t *)scalar, (uint64_t *)out);
+    case DB2_I32: return binary_t<int32_t>(name, (const int32_t *)a, ar, ac, (const int32_t *)b, br, bc, (const int32_t *)scalar, (int32_t *)out);
+    case DB2_U32: return binary_t<uint32_t>(name, (const uint32_t *)a, ar, ac, (const uint32_t *)b, br, bc, (const uint32_t *)scalar, (uint32_t *)out);
+    default: return binary_t<double>(name, (const double *)a, ar, ac, (const double *)b, br, bc, (const double *)scalar, (double *)out);
+    }
+}
+// fill through CUDA_fill__DenseMatrix_<vt>__<vt>__size_t__size_t for the one-byte value types (bool, uint8_t)
+int drv_fill_u8(int as_bool, int value, int64_t rows, int64_t cols, uint8_t *out) {
+    return guarded([&] {
+        if (as_bool) {
+            DenseMatrix<bool> *R = nullptr;
+            reinterpret_cast<void (*)(DenseMatrix<bool> **, bool, size_t, size_t, int, DaphneContext *)>(
+                sym("CUDA_fill__DenseMatrix_bool__bool__size_t__size_t"))(&R, value != 0, rows, cols, 1, &g_ctx);
+            const bool *v = static_cast<const DenseMatrix<bool> *>(R)->getValues();
+            for (int64_t i = 0; i < rows * cols; i++)
+                out[i] = v[i] ? 1 : 0;
+            DataObjectFactory::destroy(R);
+        } else {
+            DenseMatrix<uint8_t> *R = nullptr;
+            reinterpret_cast<void (*)(DenseMatrix<uint8_t> **, uint8_t, size_t, size_t, int, DaphneContext *)>(
+                sym("CUDA_fill__DenseMatrix_uint8_t__uint8_t__size_t__size_t"))(&R, (uint8_t)value, rows, cols, 1, &g_ctx);
+            memcpy(out, static_cast<const DenseMatrix<uint8_t> *>(R)->getValues(), rows * cols);
+            DataObjectFactory::destroy(R);
+        }
+        return 0;
+    });
+}
 }

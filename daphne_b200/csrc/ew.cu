@@ -350,7 +350,7 @@ extern "C" int db2k_ew_binary(int dtype, int op, const void *lhs, int64_t lhs_ro
                               void *res, int64_t res_ld, void *stream) {
     DB2_CHECK(lhs_rows >= 0 && lhs_cols >= 0 && rhs_rows >= 0 && rhs_cols >= 0, DB2_EINVAL, "negative dimension");
     DB2_CHECK((lhs && rhs && res) || lhs_rows * lhs_cols == 0, DB2_EINVAL, "null operand");
-    DB2_DISPATCH_DTYPE(dtype, VT, DB2_DISPATCH_BINOP(op, OP, return (ew_binary_impl<OP, VT>(
+    DB2_DISPATCH_DTYPE_EW(dtype, VT, DB2_DISPATCH_BINOP(op, OP, return (ew_binary_impl<OP, VT>(
                                                                  (const VT *)lhs, lhs_rows, lhs_cols, lhs_ld,
                                                                  (const VT *)rhs, rhs_rows, rhs_cols, rhs_ld, (VT *)res,
                                                                  res_ld, as_stream(stream)))));
@@ -376,7 +376,7 @@ extern "C" int db2k_ew_binary_sca(int dtype, int op, const void *lhs, int64_t ro
     DB2_CHECK(rows >= 0 && cols >= 0, DB2_EINVAL, "negative dimension");
     DB2_CHECK(scalar != nullptr, DB2_EINVAL, "null scalar");
     DB2_CHECK((lhs && res) || rows * cols == 0, DB2_EINVAL, "null operand");
-    DB2_DISPATCH_DTYPE(dtype, VT,
+    DB2_DISPATCH_DTYPE_EW(dtype, VT,
                        DB2_DISPATCH_BINOP(op, OP, return (ew_sca_impl<OP, VT>((const VT *)lhs, rows, cols, ld,
                                                                               *(const VT *)scalar, (VT *)res, res_ld,
                                                                               as_stream(stream)))));

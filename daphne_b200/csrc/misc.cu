@@ -117,7 +117,10 @@ extern "C" int db2k_fill(int dtype, void *res, int64_t rows, int64_t cols, int64
     if (rows * cols == 0)
         return DB2_OK;
     const int grid = grid_for(rows * cols, 256);
-    if (dtype_size(dtype) == 8)
+    if (dtype_size(dtype) == 1)
+        fill_kernel<uint8_t><<<grid, 256, 0, as_stream(stream)>>>(static_cast<uint8_t *>(res), rows, cols, ld,
+                                                                 *static_cast<const uint8_t *>(value));
+    else if (dtype_size(dtype) == 8)
         fill_kernel<uint64_t><<<grid, 256, 0, as_stream(stream)>>>(static_cast<uint64_t *>(res), rows, cols, ld,
                                                                   *static_cast<const uint64_t *>(value));
     else

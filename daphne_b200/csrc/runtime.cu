@@ -272,7 +272,7 @@ int db2_matrix_create(db2_context *ctx, int dtype, int64_t rows, int64_t cols, i
     DB2_API_BEGIN
     DB2_CHECK(ctx && out, DB2_EINVAL, "null argument");
     DB2_CHECK(rows >= 0 && cols >= 0, DB2_EINVAL, "negative dimension");
-    DB2_CHECK(dtype >= DB2_F64 && dtype <= DB2_U64, DB2_EINVAL, "bad value type %d", dtype);
+    DB2_CHECK(dtype >= DB2_F64 && dtype <= DB2_U8, DB2_EINVAL, "bad value type %d", dtype);
     std::unique_ptr<db2_matrix> m(new db2_matrix());
     m->ctx = ctx;
     m->dtype = dtype;
@@ -295,7 +295,7 @@ int db2_matrix_wrap_host(db2_context *ctx, int dtype, int64_t rows, int64_t cols
     DB2_CHECK(rows >= 0 && cols >= 0 && ld >= cols, DB2_EINVAL, "bad shape (%lld x %lld, ld %lld)", (long long)rows,
               (long long)cols, (long long)ld);
     DB2_CHECK(host || rows * cols == 0, DB2_EINVAL, "null host buffer");
-    DB2_CHECK(dtype >= DB2_F64 && dtype <= DB2_U64, DB2_EINVAL, "bad value type %d", dtype);
+    DB2_CHECK(dtype >= DB2_F64 && dtype <= DB2_U8, DB2_EINVAL, "bad value type %d", dtype);
     std::unique_ptr<db2_matrix> m(new db2_matrix());
     m->ctx = ctx;
     m->dtype = dtype;
@@ -315,7 +315,7 @@ int db2_matrix_wrap_device(db2_context *ctx, int dtype, int64_t rows, int64_t co
     DB2_CHECK(ctx && out, DB2_EINVAL, "null argument");
     DB2_CHECK(rows >= 0 && cols >= 0 && ld >= cols, DB2_EINVAL, "bad shape");
     DB2_CHECK(dptr || rows * cols == 0, DB2_EINVAL, "null device buffer");
-    DB2_CHECK(dtype >= DB2_F64 && dtype <= DB2_U64, DB2_EINVAL, "bad value type %d", dtype);
+    DB2_CHECK(dtype >= DB2_F64 && dtype <= DB2_U8, DB2_EINVAL, "bad value type %d", dtype);
     std::unique_ptr<db2_matrix> m(new db2_matrix());
     m->ctx = ctx;
     m->dtype = dtype;

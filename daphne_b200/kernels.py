@@ -16,7 +16,8 @@ from . import lib as _l
 from .lib import Db2Error, check, lib
 
 _NP2DT = {np.dtype(np.float64): _l.F64, np.dtype(np.float32): _l.F32, np.dtype(np.int64): _l.I64,
-          np.dtype(np.uint64): _l.U64}
+          np.dtype(np.uint64): _l.U64, np.dtype(np.int32): _l.I32, np.dtype(np.uint32): _l.U32,
+          np.dtype(np.uint8): _l.U8}
 _DT2NP = {v: k for k, v in _NP2DT.items()}
 
 

@@ -11,7 +11,7 @@ _PKG = Path(__file__).resolve().parent
 LIB_PATH = _PKG / "libdaphne_b200.so"
 
 # value type codes (include/daphne_b200.h)
-F64, F32, I64, U64 = 0, 1, 2, 3
+F64, F32, I64, U64, I32, U32, U8 = 0, 1, 2, 3, 4, 5, 6
 
 
 class Db2Error(RuntimeError):

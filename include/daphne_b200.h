@@ -47,9 +47,11 @@ extern "C" {
 enum { DB2_OK = 0, DB2_EINVAL = 1, DB2_ECUDA = 2, DB2_ENOMEM = 3, DB2_EUNSUPPORTED = 4, DB2_EDOMAIN = 5,
        DB2_ENCCL = 6, DB2_ETIMEOUT = 7 };
 
-/* value types (kernels.json instantiates the hot kernels for double, float, int64_t;
- * size_t is the value type of idxMin/idxMax results, AggRow.h:71-96) */
-enum { DB2_F64 = 0, DB2_F32 = 1, DB2_I64 = 2, DB2_U64 = 3 };
+/* value types (kernels.json instantiates the hot kernels for double, float, int64_t; size_t is the value type of
+ * idxMin/idxMax results, AggRow.h:71-96).  The elementwise binary kernels (matrix and scalar rhs), fill and transpose
+ * also take uint64_t, int32_t and uint32_t like the reference's CUDA instantiations (kernels/CUDA/EwBinaryMat.cu:265-270,
+ * EwBinaryObjSca.cu:89-94); DB2_U8 (uint8_t and bool) exists for fill only (CUDA/Fill.cu:44-49). */
+enum { DB2_F64 = 0, DB2_F32 = 1, DB2_I64 = 2, DB2_U64 = 3, DB2_I32 = 4, DB2_U32 = 5, DB2_U8 = 6 };
 
 /* BinaryOpCode (src/runtime/local/kernels/BinaryOpCode.h:29-56) */
 enum { DB2_ADD = 0, DB2_SUB, DB2_MUL, DB2_DIV, DB2_POW, DB2_MOD, DB2_LOG, DB2_EQ, DB2_NEQ, DB2_LT, DB2_LE, DB2_GT,

@@ -57,6 +57,11 @@ enum { A_SUM = 0, A_PROD, A_MIN, A_MAX, A_IDXMIN, A_IDXMAX, A_MEAN, A_STDDEV, A_
     }
 DEF_BIN(f64, double)
 DEF_BIN(i64, int64_t)
+/* the other integer value types of EwBinaryMat / EwBinaryObjSca (kernels.json: uint64_t, int32_t, uint32_t); pow, fmod
+ * and log promote the integer operands to double as the unqualified calls in the reference do */
+DEF_BIN(u64, uint64_t)
+DEF_BIN(i32, int32_t)
+DEF_BIN(u32, uint32_t)
 /* float: fmodf / logf are what std::fmod(float,float) and std::log(float) resolve to */
 static float bin_f32(int op, float a, float b) {
     switch (op) {
@@ -170,6 +175,13 @@ static int64_t un_i64(int op, int64_t x, int *bad) {
 DEF_EW_BINARY(f64, double)
 DEF_EW_BINARY(f32, float)
 DEF_EW_BINARY(i64, int64_t)
+/* binary forms only (no unary kernel is instantiated for these value types) */
+static uint64_t un_u64(int op, uint64_t x, int *bad) { (void)op; (void)bad; return x; }
+static int32_t un_i32(int op, int32_t x, int *bad) { (void)op; (void)bad; return x; }
+static uint32_t un_u32(int op, uint32_t x, int *bad) { (void)op; (void)bad; return x; }
+DEF_EW_BINARY(u64, uint64_t)
+DEF_EW_BINARY(i32, int32_t)
+DEF_EW_BINARY(u32, uint32_t)
 
 /* ------------------------------------------------------------------------------------------------------------- */
 /* aggregations                                                                                                   */

@@ -11,8 +11,10 @@ from . import build as _build
 
 _lib = C.CDLL(str(_build.build()))
 
-_SUF = {np.dtype(np.float64): "f64", np.dtype(np.float32): "f32", np.dtype(np.int64): "i64"}
-_CT = {"f64": C.c_double, "f32": C.c_float, "i64": C.c_int64}
+_SUF = {np.dtype(np.float64): "f64", np.dtype(np.float32): "f32", np.dtype(np.int64): "i64",
+        np.dtype(np.uint64): "u64", np.dtype(np.int32): "i32", np.dtype(np.uint32): "u32"}
+_CT = {"f64": C.c_double, "f32": C.c_float, "i64": C.c_int64, "u64": C.c_uint64, "i32": C.c_int32,
+       "u32": C.c_uint32}
 i64 = C.c_int64
 
 

@@ -184,6 +184,19 @@ template <typename VT> CSRMatrix<VT> *wrap_csr(const VT *vals, const uint64_t *c
 DEF_TYPED(f64, double)
 DEF_TYPED(f32, float)
 DEF_TYPED(i64, int64_t)
+// the elementwise binary kernels are also instantiated for the other integer value types (kernels.json)
+#define DEF_TYPED_BINARY(NAME, VT)                                                                                     \
+    extern "C" int ref_ew_binary_##NAME(int op, const VT *lhs, int64_t lr, int64_t lc, int64_t lld, const VT *rhs,     \
+                                        int64_t rr, int64_t rc, int64_t rld, VT *res, int64_t res_ld) {                \
+        return ew_binary<VT>(op, lhs, lr, lc, lld, rhs, rr, rc, rld, res, res_ld);                                     \
+    }                                                                                                                  \
+    extern "C" int ref_ew_binary_sca_##NAME(int op, const VT *lhs, int64_t rows, int64_t cols, int64_t ld, VT s,       \
+                                            VT *res, int64_t res_ld) {                                                 \
+        return ew_binary_sca<VT>(op, lhs, rows, cols, ld, s, res, res_ld);                                             \
+    }
+DEF_TYPED_BINARY(u64, uint64_t)
+DEF_TYPED_BINARY(i32, int32_t)
+DEF_TYPED_BINARY(u32, uint32_t)
 
 extern "C" void ref_set_blas_threads(int n) { scipy_openblas_set_num_threads(n); }
 

@@ -293,3 +293,59 @@ def test_scheduler_over_several_devices_in_one_process(devices):
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-4000:]
     n = int(r.stdout.strip().split()[-1])
     assert n == (devices.count(",") + 1 if devices != "all" else n) and n >= 1
+
+
+@pytest.mark.gpu
+def test_every_value_type_of_the_elementwise_catalog_entries_computes(drv):
+    """The CUDA catalog names the elementwise binary kernels for six value types (double, float, int64_t, uint64_t,
+    int32_t, uint32_t) and fill also for bool and uint8_t: every one of them is served by a device kernel, called here
+    by its catalog name on DenseMatrix objects of that type."""
+    from oracle import pyoracle as o
+    from tests.test_oracle_vs_ref import _int_operands
+    cat = json.loads((ABI / "CUDAcatalog.json").read_text())
+    names = {e["kernelFuncName"] for e in cat}
+    types = {"float": (np.float32, 1), "int64_t": (np.int64, 2), "uint64_t": (np.uint64, 3), "int32_t": (np.int32, 4),
+             "uint32_t": (np.uint32, 5)}
+    ops = {"ewAdd": 0, "ewSub": 1, "ewMul": 2, "ewDiv": 3, "ewPow": 4, "ewMod": 5, "ewLog": 6, "ewEq": 7, "ewNeq": 8,
+           "ewLt": 9, "ewLe": 10, "ewGt": 11, "ewGe": 12, "ewMin": 13, "ewMax": 14, "ewAnd": 15, "ewOr": 16,
+           "ewBitwise_and": 17}
+    called = 0
+    for vt, (dtype, code) in types.items():
+        if np.dtype(dtype).kind == "f":
+            rng = np.random.default_rng(3)
+            a = (rng.random((300, 17)) * 5 + 1).astype(dtype)
+            b = (rng.random((300, 17)) * 3 + 1).astype(dtype)
+            rv = b[:1].copy()
+        else:
+            a, b, rv, _ = _int_operands(dtype, 3, 300, 17)
+            a = (np.abs(a.astype(np.int64)) % 5 + 9).astype(dtype)
+        for mn, op in ops.items():
+            x = (a % 5 + 1).astype(dtype) if op == 4 and np.dtype(dtype).kind != "f" else a
+            mat = f"CUDA_{mn}__DenseMatrix_{vt}__DenseMatrix_{vt}__DenseMatrix_{vt}"
+            sca = f"CUDA_{mn}__DenseMatrix_{vt}__DenseMatrix_{vt}__{vt}"
+            out = np.empty_like(x)
+            if mat in names:
+                for rhs in (b, rv):
+                    rc = drv.drv_binary_typed(mat.encode(), code, _p(x), i64(300), i64(17), _p(rhs),
+                                              i64(rhs.shape[0]), i64(17), None, _p(out))
+                    assert rc == 0, (mat, drv.drv_last_error())
+                    exp = o.ewBinaryMat(op, x, rhs)
+                    ok = np.array_equal(out, exp) if op not in (4, 6) or np.dtype(dtype).kind != "f" else \
+                        np.allclose(out, exp, rtol=1e-5)
+                    assert ok, mat
+                    called += 1
+            if sca in names:
+                s = np.array([3], dtype=dtype)
+                rc = drv.drv_binary_typed(sca.encode(), code, _p(x), i64(300), i64(17), None, i64(0), i64(0), _p(s),
+                                          _p(out))
+                assert rc == 0, (sca, drv.drv_last_error())
+                exp = o.ewBinaryObjSca(op, x, s[0])
+                ok = np.array_equal(out, exp) if op not in (4, 6) or np.dtype(dtype).kind != "f" else \
+                    np.allclose(out, exp, rtol=1e-5)
+                assert ok, sca
+                called += 1
+    assert called >= 5 * 35 + 5 * 17  # every ew* entry of the five non-double types, matrix entries twice
+    buf = np.empty(35, dtype=np.uint8)
+    for as_bool, v in ((1, 1), (0, 203)):
+        assert drv.drv_fill_u8(as_bool, v, i64(7), i64(5), _p(buf)) == 0, drv.drv_last_error()
+        assert np.all(buf == v)

@@ -256,3 +256,53 @@ def test_cond_four_operand_forms(ctx):
         k.cond(k.DenseMatrix.from_numpy(ctx, cnd), B_, B_)
     with pytest.raises(k.Db2Error, match="CondMatMatSca: condition/then matrices must have the same shape"):
         k.cond(k.DenseMatrix.from_numpy(ctx, cnd), B_, 1.0)
+
+
+@pytest.mark.parametrize("dtype", [np.uint64, np.int32, np.uint32])
+def test_binary_other_integer_types_bit_exact(ctx, dtype):
+    """uint64_t, int32_t and uint32_t: the value types the reference's CUDA library instantiates besides double, float
+    and int64_t (kernels/CUDA/EwBinaryMat.cu:265-270, EwBinaryObjSca.cu:89-94); all 17 matrix opcodes and the 18
+    scalar opcodes, same shape / row vector / column vector / scalar."""
+    from tests.test_oracle_vs_ref import _int_operands
+    k, o = _k()
+    for i, (r, c) in enumerate([(1, 1), (7, 32), (257, 33), (4099, 50), (1, 100003), (100003, 1)]):
+        a, b, rv, cv = _int_operands(dtype, i, r, c)
+        for op in range(18):
+            x = a
+            if op in (4, 5, 6) or (op == 1 and np.dtype(dtype).kind == "u"):
+                x = (np.abs(a.astype(np.int64)) % 7 + 9).astype(dtype)
+            if op == 4:
+                x = (x % 5 + 1).astype(dtype)
+            X = k.DenseMatrix.from_numpy(ctx, x)
+            if op < 17:
+                for rhs in (b, rv, cv):
+                    got = k.ewBinaryMat(op, X, k.DenseMatrix.from_numpy(ctx, rhs)).to_numpy()
+                    assert got.dtype == np.dtype(dtype)
+                    assert_bits_equal(got, o.ewBinaryMat(op, x, rhs), f"op {op} {np.dtype(dtype).name} {rhs.shape}")
+            assert_bits_equal(k.ewBinaryObjSca(op, X, 3).to_numpy(), o.ewBinaryObjSca(op, x, 3), f"scalar op {op}")
+    # wrap-around of unsigned and 32-bit arithmetic
+    big = np.array([[np.iinfo(dtype).max, 5, 0, 1]], dtype=dtype)
+    one = np.array([[1, 7, 1, 1]], dtype=dtype)
+    for op in (0, 2) + ((1,) if np.dtype(dtype).kind == "u" else ()):
+        with np.errstate(over="ignore"):
+            exp = {0: big + one, 1: big - one * 9, 2: big * (one + 1)}[op]
+        rhs = {0: one, 1: (one * 9).astype(dtype), 2: (one + 1).astype(dtype)}[op]
+        got = k.ewBinaryMat(op, k.DenseMatrix.from_numpy(ctx, big), k.DenseMatrix.from_numpy(ctx, rhs)).to_numpy()
+        assert_bits_equal(got, exp.astype(dtype), f"wrap-around op {op}")
+    # unsigned division has no overflow case: (2^63) / (2^64 - 1) is 0
+    if dtype == np.uint64:
+        a = np.array([[2 ** 63, 2 ** 64 - 1]], dtype=np.uint64)
+        b = np.array([[2 ** 64 - 1, 2 ** 63]], dtype=np.uint64)
+        got = k.ewBinaryMat(3, k.DenseMatrix.from_numpy(ctx, a), k.DenseMatrix.from_numpy(ctx, b)).to_numpy()
+        assert_bits_equal(got, np.array([[0, 1]], dtype=np.uint64), "unsigned division")
+
+
+def test_fill_and_transpose_of_the_other_value_types(ctx):
+    k, _ = _k()
+    for dtype, v in ((np.uint64, 2 ** 64 - 3), (np.int32, -7), (np.uint32, 4000000000), (np.uint8, 200)):
+        got = k.fill(ctx, v, 37, 5, dtype=dtype).to_numpy()
+        assert got.dtype == np.dtype(dtype) and np.all(got == np.array(v, dtype=dtype))
+    for dtype in (np.uint64, np.int32, np.uint32):
+        a = np.random.default_rng(1).integers(0, 1000, size=(70, 33)).astype(dtype)
+        assert_bits_equal(k.transpose(k.DenseMatrix.from_numpy(ctx, a)).to_numpy(), np.ascontiguousarray(a.T),
+                          f"transpose {np.dtype(dtype).name}")

@@ -45,6 +45,35 @@ def test_ew_binary(dtype):
             assert_bits_equal(*_nanfix(o.ewBinaryObjSca(op, x, s), ref.ewBinaryObjSca(op, x, s)), f"sca op {op}")
 
 
+def _int_operands(dtype, seed, r, c):
+    """Operands of the 32-bit / unsigned integer value types inside the range where C++ integer arithmetic is defined
+    (no signed overflow, no out-of-range double -> integer conversion, non-zero divisors)."""
+    rng = np.random.default_rng(seed)
+    lo = 0 if np.dtype(dtype).kind == "u" else -30
+    a = rng.integers(lo, 60, size=(r, c)).astype(dtype)
+    b = rng.integers(1, 9, size=(r, c)).astype(dtype)
+    rv = rng.integers(1, 9, size=(1, c)).astype(dtype)
+    cv = rng.integers(1, 9, size=(r, 1)).astype(dtype)
+    a.reshape(-1)[::5] = b.reshape(-1)[::5]
+    return a, b, rv, cv
+
+
+@pytest.mark.parametrize("dtype", [np.uint64, np.int32, np.uint32])
+def test_ew_binary_other_integer_types(dtype):
+    for i, (r, c) in enumerate(SHAPES):
+        a, b, rv, cv = _int_operands(dtype, i, r, c)
+        for op in range(17):
+            x = a
+            if op in (4, 5, 6) or (op == 1 and np.dtype(dtype).kind == "u"):
+                x = (np.abs(a.astype(np.int64)) % 7 + 9).astype(dtype)  # pow / log / mod / unsigned sub stay in range
+            if op == 4:
+                x = (x % 5 + 1).astype(dtype)
+            for rhs in (b, rv, cv):
+                assert_bits_equal(o.ewBinaryMat(op, x, rhs), ref.ewBinaryMat(op, x, rhs),
+                                  f"op {op} {np.dtype(dtype).name} {x.shape} {rhs.shape}")
+            assert_bits_equal(o.ewBinaryObjSca(op, x, 3), ref.ewBinaryObjSca(op, x, 3), f"sca op {op}")
+
+
 def test_ew_binary_shape_error_matches():
     with pytest.raises(o.OracleError):
         o.ewBinaryMat(0, np.ones((4, 5)), np.ones((3, 2)))
