@@ -382,7 +382,7 @@ def kmeans_leg(ctx, comm, lib, host, world, args) -> dict:
     c0 = np.random.default_rng(3).random((n, d))[np.random.default_rng(33).choice(n, k, replace=False)].copy()
     X, C0 = K.DenseMatrix.from_numpy(ctx, x), K.DenseMatrix.from_numpy(ctx, c0)
     X.device_ptr()
-    ms, res = _timed(lib, ctx, comm, lambda: pipelines.kmeans(ctx, X, C0, iters, comm), 3)
+    ms, res = _timed(lib, ctx, comm, lambda: pipelines.kmeans_native(ctx, X, C0, iters), 3)
     per_iter = ms / iters
     peak, kind = measured_peaks()
     return {"workload": f"k-means, {iters} iterations, f64 {n} x {d} per GPU, k = {k}, over {world} GPU(s)",
@@ -414,7 +414,7 @@ def components_leg(ctx, comm, lib, host, world, args) -> dict:
     r0, r1 = row_block(n, comm.rank, world)
     G = K.CSRMatrix.from_scipy(ctx, g[r0:r1])
     blk = (r0, r1) if world > 1 else None
-    ms, res = _timed(lib, ctx, comm, lambda: pipelines.connected_components(ctx, G, 1000, comm, blk), 3)
+    ms, res = _timed(lib, ctx, comm, lambda: pipelines.connected_components_native(ctx, G, 1000, blk), 5)
     per_iter = ms / res.iterations
     labels = res.c.to_numpy().ravel()
     peak, kind = measured_peaks()

@@ -8,6 +8,7 @@
 // and the row aggregation of such a deferred product is ONE pass: per stored entry one value, one index and one
 // gathered operand (L2-resident for a 1 x n row vector), no intermediate matrix.  The product is only materialised
 // (count, scan, fill) when its arrays are actually requested.
+#include "fused_step.cuh"
 #include "runtime.h"
 
 #include <cub/device/device_scan.cuh>
@@ -53,6 +54,23 @@ __device__ __forceinline__ double scale_at(int skind, const double *sc, int64_t 
     return __ldg(sc + r * sc_ld + c);
 }
 
+// Epilogue of the row aggregation: a deferred elementwise chain on the rows x 1 result (lazy.cu), evaluated while the
+// row's aggregate is still in a register.  Connected components issues  u = max(aggMax(G * t(c), 0), c);
+// diff = sum(u != c)  as four operator calls; with the epilogue they are ONE pass that writes u and leaves the sum on
+// the device.
+struct CsrEpi {
+    int32_t active, nsteps, mid_after, pad;
+    double *mid_out; // values after mid_after steps (may be null)
+    double *ew_out;  // final values (may be null)
+    double *partials, *sum_out; // per-block sums of the final values; the last block folds them in block order
+    unsigned int *ticket;
+    // the operand of the first step that reads a vector is fetched together with the row's offsets (its latency then
+    // overlaps the gathers); steps that read the same vector again reuse the value
+    const double *pre_ptr;
+    int64_t pre_ld;
+    FusedStep steps[FUSED_MAX_STEPS];
+};
+
 // Row aggregation of val[i] * scale(r, col[i]); entries whose scale is exactly zero do not exist in the product
 // (EwBinaryMat.h:295-302) and therefore count as implicit zeros.  G lanes per row; every lane group works on U rows
 // at a time so that the dependent loads of a row (offsets -> column index -> gathered operand) of U rows overlap.
@@ -61,8 +79,38 @@ template <int G, typename IT, bool UNIT, int op>
 __global__ void __launch_bounds__(256)
     csr_agg_row_kernel(const double *__restrict__ val, const IT *__restrict__ col,
                        const uint64_t *__restrict__ off, int64_t rows, int64_t cols, int skind,
-                       const double *__restrict__ sc, int64_t sc_ld, double *__restrict__ out) {
+                       const double *__restrict__ sc, int64_t sc_ld, double *__restrict__ out,
+                       const __grid_constant__ CsrEpi E) {
     constexpr int RPC = 256 / G, U = 4;
+    double local_sum = 0.0;
+    // a row's aggregate leaves the kernel here: stored as it is, or sent through the chain of the epilogue
+    auto emit = [&](int64_t r, double a, double pre, bool have_pre) {
+        if (!E.active) {
+            out[r] = a;
+            return;
+        }
+        double v[1] = {a}, o[1], y[1];
+        if (E.mid_out && E.mid_after == 0)
+            E.mid_out[r] = a;
+        for (int s = 0; s < E.nsteps; s++) {
+            const FusedStep &st = E.steps[s];
+            if (st.kind == FK_MATRIX || st.kind == FK_COLVEC)
+                o[0] = (have_pre && st.ptr == E.pre_ptr && st.ld == E.pre_ld)
+                           ? pre
+                           : __ldg(static_cast<const double *>(st.ptr) + r * st.ld);
+            else if (st.kind == FK_ROWVEC)
+                o[0] = __ldg(static_cast<const double *>(st.ptr));
+            else
+                o[0] = st.imm;
+            y[0] = (st.op == FO_DIV && !st.reversed) ? div_helper(o[0]) : 0.0;
+            apply_step<1>(st.op, st.reversed != 0, v, o, y);
+            if (E.mid_out && E.mid_after == s + 1)
+                E.mid_out[r] = v[0];
+        }
+        if (E.ew_out)
+            E.ew_out[r] = v[0];
+        local_sum = __dadd_rn(local_sum, v[0]);
+    };
     // A row much longer than the others would keep its G lanes busy for length / G dependent steps while the rest of
     // the warp waits (a hub of a power-law graph).  Such rows are only noted here and taken by the whole block at the
     // end of the kernel; when the list is full they are processed in place after all.
@@ -89,7 +137,7 @@ __global__ void __launch_bounds__(256)
     };
     for (int64_t r0 = (int64_t)blockIdx.x * RPC + grp; r0 < rows_padded; r0 += stride * U) {
         uint64_t b[U], e[U];
-        double acc[U];
+        double acc[U], pre[U];
         int kept[U]; // entries of the row that exist in the product (only compared with the column count)
         bool deferred[U];
 #pragma unroll
@@ -98,6 +146,7 @@ __global__ void __launch_bounds__(256)
             const bool live = r < rows;
             b[u] = live ? off[r] : 0;
             e[u] = live ? off[r + 1] : 0;
+            pre[u] = (live && lane == 0 && E.pre_ptr) ? __ldg(E.pre_ptr + r * E.pre_ld) : 0.0;
             acc[u] = init;
             kept[u] = 0;
             deferred[u] = false;
@@ -157,7 +206,9 @@ __global__ void __launch_bounds__(256)
                 kept[u]++;
                 acc[u] = combine(acc[u], skind != SK_NONE ? __dmul_rn(xx[u], ss[u]) : xx[u]);
             }
-        // rows with more than G entries
+        // rows with more than G entries (a lock-step loop over the U rows was measured: more loads in flight per
+        // thread, but 78 registers instead of 64 and no gain -- the pass is bound by the tag lookups of the gathers
+        // in L1, one per distinct 128-byte line, not by their latency)
 #pragma unroll
         for (int u = 0; u < U; u++)
             for (uint64_t i = b[u] + lane + G; i < e[u]; i += G) {
@@ -190,7 +241,7 @@ __global__ void __launch_bounds__(256)
                     else
                         a = __dmul_rn(a, 0.0);
                 }
-                out[r] = a;
+                emit(r, a, pre[u], E.pre_ptr != nullptr);
             }
         }
     }
@@ -244,9 +295,47 @@ __global__ void __launch_bounds__(256)
                 else
                     a = __dmul_rn(a, 0.0);
             }
-            out[r] = a;
+            emit(r, a, 0.0, false);
         }
         __syncthreads();
+    }
+    if (E.active && E.partials) {
+        // block sum in a fixed order, then the last block to arrive folds the blocks' sums in block order
+        __shared__ double wsum[8];
+        __shared__ bool last;
+        for (int d = 16; d >= 1; d >>= 1)
+            local_sum = __dadd_rn(local_sum, shfl_down(local_sum, d));
+        if (threadIdx.x % 32 == 0)
+            wsum[threadIdx.x / 32] = local_sum;
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            double t = 0.0;
+            for (int w = 0; w < 8; w++)
+                t = __dadd_rn(t, wsum[w]);
+            E.partials[blockIdx.x] = t;
+            __threadfence();
+            last = atomicAdd(E.ticket, 1u) == gridDim.x - 1;
+        }
+        __syncthreads();
+        if (last) { // thread t takes blocks t, t + 256, ...; then the same fixed tree as above
+            __threadfence();
+            double t = 0.0;
+            for (unsigned b = threadIdx.x; b < gridDim.x; b += 256)
+                t = __dadd_rn(t, __ldcg(E.partials + b));
+            for (int d = 16; d >= 1; d >>= 1)
+                t = __dadd_rn(t, shfl_down(t, d));
+            __syncthreads();
+            if (threadIdx.x % 32 == 0)
+                wsum[threadIdx.x / 32] = t;
+            __syncthreads();
+            if (threadIdx.x == 0) {
+                double tot = 0.0;
+                for (int w = 0; w < 8; w++)
+                    tot = __dadd_rn(tot, wsum[w]);
+                *E.sum_out = tot;
+                *E.ticket = 0;
+            }
+        }
     }
 }
 
@@ -334,7 +423,7 @@ static int scale_args(db2_csr *lhs, db2_matrix *rhs, int *skind, const double **
 
 template <typename IT>
 static int launch_agg(db2_context *ctx, int op, const db2_csr *m, int skind, const double *sc, int64_t ld,
-                      double *out) {
+                      double *out, const CsrEpi &epi, int *grid_out = nullptr) {
     const double *val = static_cast<const double *>(m->d_val->ptr);
     const IT *col = static_cast<const IT *>(m->d_col->ptr);
     const double avg = (double)m->nnz / (double)(m->rows > 0 ? m->rows : 1); // a view inherits its parent's count
@@ -345,9 +434,13 @@ static int launch_agg(db2_context *ctx, int op, const db2_csr *m, int skind, con
     // every lane group takes 4 rows per turn
     const int64_t want = (rows + (256 / lanes) * 4 - 1) / ((256 / lanes) * 4), cap = (int64_t)sm_count() * 8;
     const int grid = (int)(want < cap ? (want ? want : 1) : cap);
+    if (grid_out) { // only the launch geometry is wanted (sizes the partial sums)
+        *grid_out = grid;
+        return DB2_OK;
+    }
 #define DB2_CSR_AGG3(G, UNIT, OP)                                                                                      \
     csr_agg_row_kernel<G, IT, UNIT, OP><<<grid, 256, 0, ctx->stream>>>(val, col, m->off_ptr(), rows, m->cols, skind,   \
-                                                                       sc, ld, out)
+                                                                       sc, ld, out, epi)
 #define DB2_CSR_AGG2(G, UNIT)                                                                                          \
     switch (op) {                                                                                                      \
     case DB2_AGG_SUM: DB2_CSR_AGG3(G, UNIT, DB2_AGG_SUM); break;                                                       \
@@ -486,6 +579,54 @@ static void drop_lazy(db2_csr *m) {
         db2_matrix_decref(m->lazy_rhs);
         m->lazy_rhs = nullptr;
     }
+}
+
+CsrSrc::CsrSrc(db2_csr *mm, int o) : m(mm), op(o) { db2_csr_incref(mm); }
+CsrSrc::~CsrSrc() { db2_csr_decref(m); }
+
+size_t csr_agg_scratch_bytes() { return (size_t)sm_count() * 8 * sizeof(double) + 64; }
+
+int csr_agg_pass(db2_context *ctx, const CsrSrc &src, const FusedProgram &prog, double *mid_out, int mid_after,
+                 double *sum_out, void *scratch, size_t scratch_bytes) {
+    db2_csr *arg = src.m, *m = arg;
+    int skind = SK_NONE;
+    const double *sc = nullptr;
+    int64_t ld = 0;
+    if (arg->lazy_lhs && !arg->dev_valid) {
+        m = arg->lazy_lhs;
+        DB2_TRY(scale_args(m, arg->lazy_rhs, &skind, &sc, &ld));
+    }
+    DB2_TRY(csr_ensure_device(m));
+    if (arg->rows == 0) {
+        if (sum_out)
+            DB2_CUDA(cudaMemsetAsync(sum_out, 0, sizeof(double), ctx->stream));
+        return DB2_OK;
+    }
+    CsrEpi E;
+    memset(&E, 0, sizeof(E));
+    E.active = 1;
+    E.nsteps = prog.nsteps;
+    E.mid_out = mid_out;
+    E.mid_after = mid_after;
+    E.ew_out = static_cast<double *>(prog.ew_out);
+    for (int i = 0; i < prog.nsteps; i++) {
+        E.steps[i] = prog.steps[i];
+        if (!E.pre_ptr && (prog.steps[i].kind == FK_MATRIX || prog.steps[i].kind == FK_COLVEC)) {
+            E.pre_ptr = static_cast<const double *>(prog.steps[i].ptr);
+            E.pre_ld = prog.steps[i].ld;
+        }
+    }
+    if (sum_out) {
+        int grid = 0;
+        DB2_TRY(m->idx32 ? launch_agg<uint32_t>(ctx, src.op, m, skind, sc, ld, nullptr, E, &grid)
+                         : launch_agg<uint64_t>(ctx, src.op, m, skind, sc, ld, nullptr, E, &grid));
+        DB2_CHECK(scratch && scratch_bytes >= (size_t)grid * sizeof(double), DB2_EINVAL, "CSR pass scratch too small");
+        E.partials = static_cast<double *>(scratch);
+        E.sum_out = sum_out;
+        E.ticket = reinterpret_cast<unsigned int *>(ctx->dev_status + 32); // zero between launches
+    }
+    return m->idx32 ? launch_agg<uint32_t>(ctx, src.op, m, skind, sc, ld, nullptr, E)
+                    : launch_agg<uint64_t>(ctx, src.op, m, skind, sc, ld, nullptr, E);
 }
 
 } // namespace db2
@@ -648,6 +789,12 @@ int db2_aggRowCsr(db2_context *ctx, int op, db2_matrix **res, db2_csr *arg) {
     DB2_CHECK(op == DB2_AGG_SUM || op == DB2_AGG_PROD || op == DB2_AGG_MIN || op == DB2_AGG_MAX, DB2_EUNSUPPORTED,
               "aggRow(CSR): SUM, PROD, MIN and MAX are implemented on the device");
     bind_device(ctx);
+    {
+        bool handled = false;
+        DB2_TRY(lazy_try_agg_row_csr(ctx, op, res, arg, &handled));
+        if (handled)
+            return DB2_OK;
+    }
     const uint64_t before = g_launches.load();
     db2_csr *src = arg;
     int skind = SK_NONE;
@@ -661,9 +808,11 @@ int db2_aggRowCsr(db2_context *ctx, int op, db2_matrix **res, db2_csr *arg) {
     DB2_TRY(prepare_result(ctx, res, DB2_F64, arg->rows, 1));
     DB2_CHECK((*res)->dev_ld == 1, DB2_EUNSUPPORTED, "aggRow(CSR) into a strided result view");
     double *out = static_cast<double *>((*res)->dev_ptr());
+    CsrEpi none;
+    memset(&none, 0, sizeof(none));
     if (arg->rows > 0)
-        DB2_TRY(src->idx32 ? launch_agg<uint32_t>(ctx, op, src, skind, sc, ld, out)
-                           : launch_agg<uint64_t>(ctx, op, src, skind, sc, ld, out));
+        DB2_TRY(src->idx32 ? launch_agg<uint32_t>(ctx, op, src, skind, sc, ld, out, none)
+                           : launch_agg<uint64_t>(ctx, op, src, skind, sc, ld, out, none));
     std::lock_guard<std::mutex> lock(ctx->mu);
     ctx->stats.launches += g_launches.load() - before;
     return DB2_OK;

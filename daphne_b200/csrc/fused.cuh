@@ -14,6 +14,8 @@
 
 #include "common.cuh"
 
+struct db2_context;
+
 namespace db2 {
 
 constexpr int FUSED_MAX_STEPS = 10;
@@ -83,6 +85,16 @@ bool fused_flat_eligible(const FusedProgram &prog);
 size_t fused_flat_scratch_bytes();
 int fused_flat_pass_f64(const FusedProgram &prog, void *mid_out, int mid_after, double *sum_out, void *scratch,
                         size_t scratch_bytes, cudaStream_t st);
+
+// row aggregation of a CSR matrix with a fused epilogue on the rows x 1 result (csr.cu): prog.steps are applied to every
+// row's aggregate (operands: column vectors / same-shape rows x 1 matrices, 1 x 1 matrices, immediates), prog.ew_out
+// receives the final values, mid_out the values after mid_after steps, *sum_out (device) the sum of the final values
+// (folded in block order by the last block to finish); prog.base is not used.  scratch: at least
+// csr_agg_scratch_bytes() bytes; ticket: a device word that is zero before and after every launch.
+struct CsrSrc;
+size_t csr_agg_scratch_bytes();
+int csr_agg_pass(struct ::db2_context *ctx, const CsrSrc &src, const FusedProgram &prog, double *mid_out, int mid_after,
+                 double *sum_out, void *scratch, size_t scratch_bytes);
 
 // tall-skinny product with fused row epilogue (skinny.cu): D = A @ op(B), then prog.steps on D, prog.taps (row MIN /
 // MAX with positions, at the end of the chain) and prog.ew_out (the values after all steps); prog.base is not used

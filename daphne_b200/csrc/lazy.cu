@@ -219,8 +219,9 @@ int lazy_try_agg_row(db2_context *ctx, int op, db2_matrix **res, db2_matrix *arg
 // built above)
 static void build_program(const Expr &e, size_t nsteps, FusedProgram *P) {
     memset(P, 0, sizeof(*P));
-    P->base = e.gemm ? nullptr : e.base.ptr(8);
-    P->base_ld = e.gemm ? e.cols : e.base.ld;
+    const bool no_base = e.gemm || e.csr;
+    P->base = no_base ? nullptr : e.base.ptr(8);
+    P->base_ld = no_base ? e.cols : e.base.ld;
     P->rows = e.rows;
     P->cols = e.cols;
     P->nsteps = (int)nsteps;
@@ -345,8 +346,64 @@ static bool gemm_pass_fusable(const Expr &e, const std::vector<db2_matrix *> &gr
     return true;
 }
 
+// the live deferred matrix (other than `self`) whose chain is the longest proper, non-empty prefix of e's
+static db2_matrix *prefix_sibling(db2_context *ctx, const db2_matrix *self, const Expr &e) {
+    db2_matrix *sibling = nullptr;
+    for (db2_matrix *m : ctx->lazies)
+        if (m != self && m->lazy && !m->lazy->steps.empty() && m->lazy->steps.size() < e.steps.size() &&
+            is_prefix(*m->lazy, e) && (!sibling || m->lazy->steps.size() > sibling->lazy->steps.size()))
+            sibling = m;
+    return sibling;
+}
+
+// One pass over a CSR matrix that produces its row aggregation with the chain `e` applied: the final values into
+// `target` (may be null), the values of a live prefix of the chain into that matrix, the sum of the final values into
+// *sum_dev (device, may be null).
+static int run_csr_pass(db2_context *ctx, const Expr &e, db2_matrix *target, double *sum_dev) {
+    FusedProgram P;
+    build_program(e, e.steps.size(), &P);
+    for (int i = 0; i < P.nsteps; i++) // operands are indexed by row: matrices must be rows x 1, row vectors 1 x 1
+        DB2_CHECK(P.steps[i].kind != FK_ROWVEC || e.steps[i].operand.cols == 1, DB2_EUNSUPPORTED,
+                  "a chain on a CSR row aggregation with a wide row-vector operand");
+    db2_matrix *sibling = prefix_sibling(ctx, target, e);
+    double *mid = nullptr;
+    int mid_after = 0;
+    if (sibling) {
+        sibling->dev = make_devbuf(ctx, (size_t)sibling->rows * 8);
+        sibling->dev_off = 0;
+        sibling->dev_ld = 1;
+        mid = static_cast<double *>(sibling->dev->ptr);
+        mid_after = (int)sibling->lazy->steps.size();
+    }
+    if (target) {
+        target->dev = make_devbuf(ctx, (size_t)e.rows * 8);
+        target->dev_off = 0;
+        target->dev_ld = 1;
+        P.ew_out = target->dev->ptr;
+        P.ew_out_ld = 1;
+    }
+    void *scratch = nullptr;
+    const size_t head = 64; // (callers keep a result in front of the partial sums)
+    if (sum_dev)
+        DB2_TRY(ctx_scratch(ctx, csr_agg_scratch_bytes() + head, &scratch));
+    DB2_TRY(csr_agg_pass(ctx, *e.csr, P, mid, mid_after, sum_dev,
+                         scratch ? static_cast<char *>(scratch) + head : nullptr,
+                         scratch ? ctx->scratch_bytes - head : 0));
+    for (db2_matrix *m : {sibling, target})
+        if (m) {
+            m->dev_valid = true;
+            unlazy(m);
+            m->lazy.reset();
+        }
+    return DB2_OK;
+}
+
 static int run_row_pass(db2_context *ctx, const Expr &longest, db2_matrix *ew_target,
                         const std::vector<db2_matrix *> &group) {
+    if (longest.csr) {
+        DB2_CHECK(group.empty(), DB2_EUNSUPPORTED, "row aggregations of a rows x 1 chain are not deferred");
+        return run_csr_pass(ctx, longest, ew_target, nullptr);
+    }
     if (longest.gemm && !gemm_pass_fusable(longest, group)) {
         // the product is written out and the ordinary pass runs on it
         Expr plain = longest;
@@ -503,6 +560,16 @@ int lazy_try_agg_col(db2_context *ctx, int op, db2_matrix **res, db2_matrix *arg
     std::shared_ptr<const Expr> e = arg->lazy;
     if (e->gemm)
         return DB2_OK; // the deferred product is produced first (ensure_device), then the column kernels run
+    if (e->csr) {
+        // sum of a chain on a CSR row aggregation: the pass leaves it on the device (1 x 1), e.g. the number of
+        // labels that changed, which a multi-GPU run combines before anybody reads it
+        if (op != DB2_AGG_SUM || *res != nullptr)
+            return DB2_OK;
+        DB2_TRY(prepare_result(ctx, res, DB2_F64, 1, 1));
+        DB2_TRY(run_csr_pass(ctx, *e, nullptr, static_cast<double *>((*res)->dev_ptr())));
+        *handled = true;
+        return DB2_OK;
+    }
     if (op == DB2_AGG_SUM) { // sum((X - mu)^2) right after the column sums of X: answered from the statistics
         DB2_TRY(colstats_try_sqdev(ctx, *e, res, handled));
         if (*handled)
@@ -519,6 +586,23 @@ int lazy_try_agg_col(db2_context *ctx, int op, db2_matrix **res, db2_matrix *arg
     if (!fused_col_pass_ct(P, sig.c_str(), op, (*res)->dev_ptr(), scratch, ctx->scratch_bytes, ctx->stream, &rc))
         rc = fused_col_pass_f64(P, op, (*res)->dev_ptr(), scratch, ctx->scratch_bytes, ctx->stream);
     DB2_TRY(rc);
+    *handled = true;
+    return DB2_OK;
+}
+
+int lazy_try_agg_row_csr(db2_context *ctx, int op, db2_matrix **res, db2_csr *arg, bool *handled) {
+    *handled = false;
+    int64_t rows = 0;
+    DB2_TRY(db2_csr_info(arg, &rows, nullptr, nullptr));
+    if (*res != nullptr || ctx->eager || rows < LAZY_MIN_ELEMS)
+        return DB2_OK;
+    auto e = std::make_shared<Expr>();
+    e->rows = rows;
+    e->cols = 1;
+    e->csr = std::make_shared<CsrSrc>(arg, op);
+    db2_matrix *r = new_deferred(ctx, DB2_F64, rows, 1);
+    set_lazy(r, e);
+    *res = r;
     *handled = true;
     return DB2_OK;
 }
@@ -558,15 +642,25 @@ int lazy_try_agg_all(db2_context *ctx, int op, double *res_host, db2_matrix *arg
     std::shared_ptr<const Expr> e = arg->lazy;
     if (e->gemm)
         return DB2_OK;
+    if (e->csr) { // one pass over the CSR arrays: aggregate, chain, live prefix of the chain, sum
+        const uint64_t before = g_launches.load();
+        // the last block of the pass writes the sum straight into pinned host memory (device-accessible under unified
+        // addressing): the host only waits for the stream, no copy is queued behind the kernel
+        double *pinned = reinterpret_cast<double *>(ctx->host_status + 48);
+        DB2_TRY(run_csr_pass(ctx, *e, nullptr, pinned));
+        DB2_CUDA(cudaStreamSynchronize(ctx->stream));
+        *res_host = *pinned;
+        std::lock_guard<std::mutex> lock(ctx->mu);
+        ctx->stats.launches += g_launches.load() - before;
+        ctx->stats.d2h_bytes += sizeof(double);
+        *handled = true;
+        return DB2_OK;
+    }
     FusedProgram P;
     build_program(*e, e->steps.size(), &P);
     if (!fused_flat_eligible(P))
         return DB2_OK;
-    db2_matrix *sibling = nullptr;
-    for (db2_matrix *m : ctx->lazies)
-        if (m != arg && m->lazy && !m->lazy->steps.empty() && m->lazy->steps.size() < e->steps.size() &&
-            is_prefix(*m->lazy, *e) && (!sibling || m->lazy->steps.size() > sibling->lazy->steps.size()))
-            sibling = m;
+    db2_matrix *sibling = prefix_sibling(ctx, arg, *e);
     const uint64_t before = g_launches.load();
     void *scratch = nullptr;
     DB2_TRY(ctx_scratch(ctx, fused_flat_scratch_bytes() + 64, &scratch));

@@ -62,7 +62,21 @@ template <typename VT> __device__ __forceinline__ VT op_pow(VT a, VT b) {
         // the reference promotes float arguments of pow() to double (unqualified ::pow)
         return (float)pow((double)a, (double)b);
     } else {
-        return (VT)pow((double)a, (double)b);
+        // integer value types: the reference evaluates pow(double(a), double(b)) with glibc, which returns the exact
+        // power whenever it is representable, and truncates.  A power with a small non-negative integer exponent is
+        // therefore formed by exact multiplications (every partial product below 2^53 is exact); CUDA's pow may be an
+        // ulp low and would truncate to the integer below.
+        const double x = (double)a, y = (double)b;
+        if (y >= 0.0 && y <= 64.0) {
+            double r = 1.0, p = x;
+            for (unsigned e = (unsigned)y; e; e >>= 1) {
+                if (e & 1u)
+                    r = __dmul_rn(r, p);
+                p = __dmul_rn(p, p);
+            }
+            return (VT)r;
+        }
+        return (VT)pow(x, y);
     }
 }
 template <typename VT> __device__ __forceinline__ VT op_mod(VT a, VT b) {

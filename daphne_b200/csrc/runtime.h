@@ -18,6 +18,7 @@ struct ColStats;
 } // namespace db2
 
 struct db2_matrix;
+struct db2_csr;
 
 struct db2_context {
     int device = 0;
@@ -166,13 +167,23 @@ struct GemmSrc { // the base values are the product A @ op(B) (tall-skinny, skin
     bool tb = false;
     int64_t K = 0;
 };
+struct CsrSrc { // the base values are the row aggregation `op` of a CSR matrix (csr.cu), not yet computed
+    db2_csr *m; // holds a reference; may itself be a deferred sparse (.) dense product
+    int op;
+    CsrSrc(db2_csr *m, int op);
+    ~CsrSrc();
+    CsrSrc(const CsrSrc &) = delete;
+};
 struct Expr {
     int dtype = DB2_F64;
     int64_t rows = 0, cols = 0;
     Operand base;                        // materialised base operand, unless ...
     std::shared_ptr<const GemmSrc> gemm; // ... the chain starts from a deferred product
+    std::shared_ptr<const CsrSrc> csr;   // ... or from a deferred row aggregation of a CSR matrix (rows x 1)
     std::vector<ExprStep> steps;
     bool same_base(const Expr &o) const {
+        if (csr || o.csr)
+            return csr && o.csr && csr->m == o.csr->m && csr->op == o.csr->op;
         if (gemm || o.gemm)
             return gemm && o.gemm && gemm->A.same(o.gemm->A) && gemm->B.same(o.gemm->B) && gemm->tb == o.gemm->tb;
         return base.same(o.base);
@@ -195,6 +206,9 @@ int lazy_try_binary(db2_context *ctx, int op, db2_matrix **res, db2_matrix *lhs,
 int lazy_try_scalar(db2_context *ctx, int op, db2_matrix **res, db2_matrix *lhs, const void *scalar, bool *handled);
 int lazy_try_unary(db2_context *ctx, int op, db2_matrix **res, db2_matrix *arg, bool *handled);
 int lazy_try_agg_row(db2_context *ctx, int op, db2_matrix **res, db2_matrix *arg, bool *handled);
+// row aggregation of a CSR matrix (or of a deferred sparse (.) dense product): deferred, so that a following chain on
+// the rows x 1 result (max(., c), . != c), its sum and its intermediate results come out of the same pass
+int lazy_try_agg_row_csr(db2_context *ctx, int op, db2_matrix **res, db2_csr *arg, bool *handled);
 int lazy_try_agg_col(db2_context *ctx, int op, db2_matrix **res, db2_matrix *arg, bool *handled);
 // A @ op(B) for a tall lhs and at most 64 result columns: deferred, so that a following chain and row extremum are
 // applied to the accumulators

@@ -1,0 +1,170 @@
+// The kernel-call sequences that the benchmark workloads lower to, issued from native code.
+//
+// DAPHNE's JIT-compiled `main` calls one kernel per operator through the C ABI with next to no host time between the
+// calls.  These functions are that caller for the five workloads: the same operator calls, in the same order, as the
+// DaphneDSL scripts lower to (PhyOperatorSelection: t(X) @ X -> syrk, t(X) @ y -> gemv; one kernel call per op), made
+// through the public db2_* operator interface -- nothing here reaches below it.  With a communicator on the context
+// they run row-sharded: every rank calls them on its row block and the ADD partials are combined on the device.
+#include "runtime.h"
+
+using namespace db2;
+
+namespace {
+
+struct H { // owning handle
+    db2_matrix *m = nullptr;
+    H() = default;
+    H(const H &) = delete;
+    ~H() { reset(); }
+    void reset(db2_matrix *n = nullptr) {
+        if (m)
+            db2_matrix_decref(m);
+        m = n;
+    }
+    db2_matrix *release() {
+        db2_matrix *r = m;
+        m = nullptr;
+        return r;
+    }
+    db2_matrix **operator&() { return &m; }
+    operator db2_matrix *() const { return m; }
+};
+struct HC {
+    db2_csr *m = nullptr;
+    ~HC() {
+        if (m)
+            db2_csr_decref(m);
+    }
+};
+
+int combine(db2_context *ctx, db2_matrix *m) { return ctx->world > 1 ? db2_allreduce(ctx, m, DB2_COMBINE_ADD) : DB2_OK; }
+
+int scalar_op(db2_context *ctx, int op, db2_matrix **res, db2_matrix *lhs, double s) {
+    return db2_ewBinaryObjSca(ctx, op, res, lhs, &s);
+}
+
+} // namespace
+
+extern "C" {
+
+// Connected components by label propagation (test/api/cli/algorithms/components.daphne:14-26):
+//   c = seq(1, n, 1); while (diff > 0 && iter <= maxi) { u = max(aggMax(G * t(c), 0), c); diff = sum(u != c); c = u; }
+// G holds the rows [row_lo, row_lo + G.rows) of the n x n adjacency matrix.  Sharded: the change count is combined on
+// the device and the label blocks are all-gathered behind it on the same stream; one value is read per iteration.
+int db2w_connected_components(db2_context *ctx, db2_csr *G, int64_t row_lo, int64_t maxi, db2_matrix **labels,
+                              int64_t *iterations) {
+    DB2_API_BEGIN
+    DB2_CHECK(ctx && G && labels && iterations, DB2_EINVAL, "null argument");
+    int64_t rows = 0, n = 0;
+    DB2_TRY(db2_csr_info(G, &rows, &n, nullptr));
+    const bool sharded = ctx->world > 1;
+    H c_full, c_loc;
+    const double one = 1.0, last = (double)n;
+    DB2_TRY(db2_seq(ctx, &c_full, DB2_F64, &one, &last, &one));
+    DB2_TRY(db2_matrix_slice_rows(c_full, row_lo, row_lo + rows, &c_loc));
+    double diff = 1.0;
+    int64_t it = 1;
+    while (diff > 0.0 && it <= maxi) {
+        H tc, mx, u, ne;
+        HC prod;
+        DB2_TRY(db2_transpose(ctx, &tc, c_full));
+        DB2_TRY(db2_ewMulCsrDense(ctx, &prod.m, G, tc));
+        DB2_TRY(db2_aggRowCsr(ctx, DB2_AGG_MAX, &mx, prod.m));
+        DB2_TRY(db2_ewBinaryMat(ctx, DB2_MAX, &u, mx, c_loc));
+        DB2_TRY(db2_ewBinaryMat(ctx, DB2_NEQ, &ne, u, c_loc));
+        if (sharded) {
+            H cnt, gathered;
+            DB2_TRY(db2_aggCol(ctx, DB2_AGG_SUM, &cnt, ne));
+            DB2_TRY(db2_allreduce(ctx, cnt, DB2_COMBINE_ADD));
+            DB2_TRY(db2_allgatherv_rows(ctx, u, n, &gathered));
+            DB2_TRY(db2_matrix_to_host(cnt, &diff, 1));
+            c_full.reset(gathered.release());
+            c_loc.reset();
+            DB2_TRY(db2_matrix_slice_rows(c_full, row_lo, row_lo + rows, &c_loc));
+        } else {
+            DB2_TRY(db2_aggAll(ctx, DB2_AGG_SUM, &diff, ne));
+            db2_matrix_incref(u);
+            c_loc.reset(u);
+            c_full.reset(u.release());
+        }
+        it++;
+    }
+    *iterations = it - 1;
+    *labels = c_loc.release();
+    return DB2_OK;
+    DB2_API_END
+}
+
+// K-means assignment + update (test/api/cli/algorithms/kmeans.daphne:14-21):
+//   xs = sum(X ^ 2, 0);
+//   for i: D = (X @ t(C)) * -2.0 + xs + t(sum(C ^ 2, 0)); a = idxMin(D, 0);
+//          P = ctable(seq(0, n - 1), a, 1.0, n, k); C = (t(P) @ X) / t(sum(P, 1));
+int db2w_kmeans(db2_context *ctx, db2_matrix *X, db2_matrix *C0, int iterations, db2_matrix **C_out,
+                db2_matrix **assign_out) {
+    DB2_API_BEGIN
+    DB2_CHECK(ctx && X && C0 && C_out && assign_out, DB2_EINVAL, "null argument");
+    const int64_t n = X->rows, k = C0->rows;
+    H x2, xs, rows;
+    DB2_TRY(scalar_op(ctx, DB2_POW, &x2, X, 2.0));
+    DB2_TRY(db2_aggRow(ctx, DB2_AGG_SUM, &xs, x2));
+    x2.reset();
+    const int64_t zero = 0, lastrow = n - 1, inc = 1;
+    DB2_TRY(db2_seq(ctx, &rows, DB2_I64, &zero, &lastrow, &inc));
+    H Cm, assign;
+    db2_matrix_incref(C0);
+    Cm.reset(C0);
+    for (int i = 0; i < iterations; i++) {
+        H c2, cs, cst, xc, t1, t2, D, idx, P, sums, counts, ct, Cn;
+        DB2_TRY(scalar_op(ctx, DB2_POW, &c2, Cm, 2.0));
+        DB2_TRY(db2_aggRow(ctx, DB2_AGG_SUM, &cs, c2));
+        DB2_TRY(db2_transpose(ctx, &cst, cs));
+        DB2_TRY(db2_matMul(ctx, &xc, X, Cm, 0, 1));
+        DB2_TRY(scalar_op(ctx, DB2_MUL, &t1, xc, -2.0));
+        DB2_TRY(db2_ewBinaryMat(ctx, DB2_ADD, &t2, t1, xs));
+        DB2_TRY(db2_ewBinaryMat(ctx, DB2_ADD, &D, t2, cst));
+        DB2_TRY(db2_aggRow(ctx, DB2_AGG_IDXMIN, &idx, D));
+        assign.reset();
+        DB2_TRY(db2_castObj(ctx, &assign, idx, DB2_I64));
+        D.reset();
+        t2.reset();
+        t1.reset();
+        xc.reset();
+        DB2_TRY(db2_ctable(ctx, &P, rows, assign, 1.0, n, k));
+        DB2_TRY(db2_matMul(ctx, &sums, P, X, 1, 0));
+        DB2_TRY(combine(ctx, sums));
+        DB2_TRY(db2_aggCol(ctx, DB2_AGG_SUM, &counts, P));
+        DB2_TRY(combine(ctx, counts));
+        P.reset();
+        DB2_TRY(db2_transpose(ctx, &ct, counts));
+        DB2_TRY(db2_ewBinaryMat(ctx, DB2_DIV, &Cn, sums, ct));
+        Cm.reset(Cn.release());
+    }
+    *C_out = Cm.release();
+    *assign_out = assign.release();
+    return DB2_OK;
+    DB2_API_END
+}
+
+// Linear regression by the normal equations (lmDS, scripts/algorithms/lmDS_.daph:98-112):
+//   A = t(X) @ X + diagMatrix(fill(lambda, ncol(X), 1)); b = t(X) @ y; beta = solve(A, b);
+int db2w_normal_equations(db2_context *ctx, db2_matrix *X, db2_matrix *y, double lambda, db2_matrix **A_out,
+                          db2_matrix **b_out, db2_matrix **beta_out) {
+    DB2_API_BEGIN
+    DB2_CHECK(ctx && X && y && A_out && b_out && beta_out, DB2_EINVAL, "null argument");
+    H xtx, xty, lam, diag, A, beta;
+    DB2_TRY(db2_syrk(ctx, &xtx, X, 1));
+    DB2_TRY(db2_gemv(ctx, &xty, X, y));
+    DB2_TRY(combine(ctx, xtx));
+    DB2_TRY(combine(ctx, xty));
+    DB2_TRY(db2_fill(ctx, &lam, DB2_F64, &lambda, X->cols, 1));
+    DB2_TRY(db2_diagMatrix(ctx, &diag, lam));
+    DB2_TRY(db2_ewBinaryMat(ctx, DB2_ADD, &A, xtx, diag));
+    DB2_TRY(db2_solve(ctx, &beta, A, xty));
+    *A_out = A.release();
+    *b_out = xty.release();
+    *beta_out = beta.release();
+    return DB2_OK;
+    DB2_API_END
+}
+
+} // extern "C"

@@ -157,6 +157,9 @@ _SIGS = {
     "db2_readDaphne": (i32, [vp, _P(vp), C.c_char_p]),
     "db2_writeDaphne": (i32, [vp, vp, C.c_char_p]),
     "db2_vectorizedPipeline": (i32, [vp, _P(vp), sz, _P(i32), _P(vp), sz, _P(i64), _P(i64), _P(i64), _P(i64), vp, i64]),
+    "db2w_connected_components": (i32, [vp, vp, i64, i64, _P(vp), _P(i64)]),
+    "db2w_kmeans": (i32, [vp, vp, vp, i32, _P(vp), _P(vp)]),
+    "db2w_normal_equations": (i32, [vp, vp, vp, C.c_double, _P(vp), _P(vp), _P(vp)]),
     "db2_csr_wrap_host": (i32, [vp, i32, i64, i64, vp, vp, vp, _P(vp)]),
     "db2_csr_slice_rows": (i32, [vp, i64, i64, _P(vp)]),
     "db2_csr_incref": (i32, [vp]),

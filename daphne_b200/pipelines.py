@@ -259,3 +259,34 @@ def connected_components(ctx, G, maxi: int = 1000, comm: Optional[Comm] = None, 
                 c_loc = u
         it += 1
     return ComponentsResult(c_loc, it - 1)
+
+
+# ---- the same sequences issued from native code (csrc/workloads.cu): what a JIT-compiled caller costs on the host ----
+
+def connected_components_native(ctx, G, maxi: int = 1000, row_block: Optional[tuple] = None) -> ComponentsResult:
+    """connected_components through db2w_connected_components: the same operator calls, made from C++."""
+    import ctypes as C
+
+    from .lib import check, lib
+    lo = row_block[0] if row_block is not None else 0
+    h, it = C.c_void_p(), C.c_int64()
+    check(lib.db2w_connected_components(ctx.handle, G.handle, int(lo), int(maxi), C.byref(h), C.byref(it)))
+    return ComponentsResult(K.DenseMatrix(ctx, h), it.value)
+
+
+def kmeans_native(ctx, X, C0, iterations: int = 10) -> KMeansResult:
+    import ctypes as C
+
+    from .lib import check, lib
+    c, a = C.c_void_p(), C.c_void_p()
+    check(lib.db2w_kmeans(ctx.handle, X.handle, C0.handle, int(iterations), C.byref(c), C.byref(a)))
+    return KMeansResult(K.DenseMatrix(ctx, c), K.DenseMatrix(ctx, a))
+
+
+def normal_equations_native(ctx, X, y, lam: float = 0.001) -> NormalEquationsResult:
+    import ctypes as C
+
+    from .lib import check, lib
+    a, b, beta = C.c_void_p(), C.c_void_p(), C.c_void_p()
+    check(lib.db2w_normal_equations(ctx.handle, X.handle, y.handle, float(lam), C.byref(a), C.byref(b), C.byref(beta)))
+    return NormalEquationsResult(K.DenseMatrix(ctx, a), K.DenseMatrix(ctx, b), K.DenseMatrix(ctx, beta))

@@ -480,6 +480,23 @@ int db2_aggRowCsr(db2_context *ctx, int op, db2_matrix **res, db2_csr *arg);
 /* res = lhs @ rhs, dense rhs (Gemv<Dense,CSR,Dense>, src/runtime/local/kernels/Gemv.h:79-117) */
 int db2_matMulCsrDense(db2_context *ctx, db2_matrix **res, db2_csr *lhs, db2_matrix *rhs);
 
+/* ------------------------------------------------------------------------- */
+/* the workloads' kernel-call sequences, issued natively                      */
+/* ------------------------------------------------------------------------- */
+/* What DAPHNE's JIT-compiled `main` does for a script: one call of the operator interface above per operator, in the
+ * order the compiler emits them, with next to no host time between the calls.  Row-sharded when the context has a
+ * communicator (every rank passes its row block; ADD partials are combined on the device). */
+/* components.daphne (test/api/cli/algorithms/components.daphne:14-26); G = rows [row_lo, row_lo + G.rows) of the
+ * n x n adjacency matrix; *labels = the labels of those rows */
+int db2w_connected_components(db2_context *ctx, db2_csr *G, int64_t row_lo, int64_t maxi, db2_matrix **labels,
+                              int64_t *iterations);
+/* kmeans.daphne (test/api/cli/algorithms/kmeans.daphne:14-21): assignment (idxMin, ties to the lowest index) and
+ * update (one-hot ctable, t(P) @ X) for `iterations` rounds */
+int db2w_kmeans(db2_context *ctx, db2_matrix *X, db2_matrix *C0, int iterations, db2_matrix **C, db2_matrix **assign);
+/* lmDS (scripts/algorithms/lmDS_.daph:98-112): A = t(X) @ X + lambda I (syrk), b = t(X) @ y (gemv), beta = solve(A, b) */
+int db2w_normal_equations(db2_context *ctx, db2_matrix *X, db2_matrix *y, double lambda, db2_matrix **A,
+                          db2_matrix **b, db2_matrix **beta);
+
 #ifdef __cplusplus
 }
 #endif

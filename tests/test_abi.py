@@ -8,7 +8,7 @@ ROOT = Path(__file__).resolve().parents[1]
 def _declared(header: Path):
     text = header.read_text()
     text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
-    return sorted(set(re.findall(r"\b(db2[kh]?_[A-Za-z0-9_]+)\s*\(", text)))
+    return sorted(set(re.findall(r"\b(db2[khw]?_[A-Za-z0-9_]+)\s*\(", text)))
 
 
 def test_every_declared_symbol_is_exported():

@@ -51,9 +51,9 @@ def _int_operands(dtype, seed, r, c):
     rng = np.random.default_rng(seed)
     lo = 0 if np.dtype(dtype).kind == "u" else -30
     a = rng.integers(lo, 60, size=(r, c)).astype(dtype)
-    b = rng.integers(1, 9, size=(r, c)).astype(dtype)
-    rv = rng.integers(1, 9, size=(1, c)).astype(dtype)
-    cv = rng.integers(1, 9, size=(r, 1)).astype(dtype)
+    b = rng.integers(2, 9, size=(r, c)).astype(dtype)
+    rv = rng.integers(2, 9, size=(1, c)).astype(dtype)
+    cv = rng.integers(2, 9, size=(r, 1)).astype(dtype)
     a.reshape(-1)[::5] = b.reshape(-1)[::5]
     return a, b, rv, cv
 

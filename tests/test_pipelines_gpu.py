@@ -192,3 +192,69 @@ def test_csr_kernels_against_oracle(ctx):
     E = k.CSRMatrix.from_scipy(ctx, e)
     assert_bits_equal(k.aggRowCsr(3, E).to_numpy(), o.aggRowCsr(3, e), "all-empty rows max = implicit zero")
     assert_bits_equal(k.aggRowCsr(0, E).to_numpy(), o.aggRowCsr(0, e), "all-empty rows sum")
+
+
+def test_chains_on_a_csr_row_aggregation_are_evaluated_in_its_pass(ctx):
+    """A row aggregation of a large CSR matrix is deferred; elementwise operators on its rows x 1 result, the sum of
+    the chain and live intermediate results come out of ONE pass over the CSR arrays (what connected components
+    needs: u = max(aggMax(G * t(c), 0), c); diff = sum(u != c)).  Checked against the operator-by-operator oracle."""
+    import daphne_b200.kernels as k
+    from oracle import pyoracle as o
+    B, A = k.BinaryOpCode, k.AggOpCode
+    n = 150000
+    g = _graph(n, 6, 11)
+    rng = np.random.default_rng(12)
+    c = rng.integers(1, n, size=(n, 1)).astype(np.float64)
+    G, Cv = k.CSRMatrix.from_scipy(ctx, g), k.DenseMatrix.from_numpy(ctx, c)
+    exp_mx = o.aggRowCsr(A.MAX, o.ewMulCsrDense(g, c.T.copy()))
+    exp_u = np.maximum(exp_mx, c)
+    exp_diff = float((exp_u != c).sum())
+    # (1) the connected-components step: one kernel launch for four operator calls
+    l0 = ctx.stats()["launches"]
+    mx = k.aggRowCsr(A.MAX, k.ewMulCsrDense(G, k.transpose(Cv)))
+    u = k.ewBinaryMat(B.MAX, mx, Cv)
+    diff = k.aggAll(A.SUM, k.ewBinaryMat(B.NEQ, u, Cv))
+    launches = ctx.stats()["launches"] - l0
+    assert diff == exp_diff
+    assert_bits_equal(u.to_numpy(), exp_u, "u = max(rowMaxs(G * t(c)), c)")
+    assert launches <= 2, f"expected the fused pass (plus at most the upload helper), got {launches} launches"
+    assert_bits_equal(mx.to_numpy(), exp_mx, "the aggregation itself, asked for afterwards")
+    # (2) other aggregations, scalar / unary steps, reversed operands, the chain materialised without a sum
+    w = rng.standard_normal((n, 1))
+    W = k.DenseMatrix.from_numpy(ctx, w)
+    gv = g.copy()
+    gv.data[:] = rng.standard_normal(gv.nnz)
+    GV = k.CSRMatrix.from_scipy(ctx, gv)
+    for op in (A.SUM, A.MIN, A.MAX):
+        base = o.aggRowCsr(op, gv)
+        r = k.aggRowCsr(op, GV)
+        z = k.ewBinaryMat(B.SUB, W, k.ewBinaryObjSca(B.MUL, r, 2.0))          # w - 2 r  (reversed operand)
+        z = k.ewUnaryMat(k.UnaryOpCode.ABS, z)
+        exp = np.abs(w - base * 2.0)
+        if op == A.SUM:
+            np.testing.assert_allclose(z.to_numpy(), exp, rtol=1e-12, atol=1e-12)
+        else:
+            assert_bits_equal(z.to_numpy(), exp, f"chain on csr agg {op}")
+        s = k.aggCol(A.SUM, k.ewBinaryMat(B.GT, k.aggRowCsr(op, GV), W))           # the sum stays on the device
+        assert float(s.to_numpy()[0, 0]) == float((base > w).sum())
+
+
+def test_native_call_sequences_equal_the_python_ones(ctx):
+    """db2w_* issue the same operator calls from C++ (what a JIT-compiled caller does): identical results."""
+    k, p, cpu = _k()
+    g = _graph(120000, 6, 21)
+    G = k.CSRMatrix.from_scipy(ctx, g)
+    a, b = p.connected_components(ctx, G), p.connected_components_native(ctx, G)
+    assert a.iterations == b.iterations
+    assert_bits_equal(a.c.to_numpy(), b.c.to_numpy(), "components")
+    x = np.random.default_rng(3).random((150000, 64))
+    c0 = x[:50].copy()
+    X, C0 = k.DenseMatrix.from_numpy(ctx, x), k.DenseMatrix.from_numpy(ctx, c0)
+    ka, kb = p.kmeans(ctx, X, C0, 3), p.kmeans_native(ctx, X, C0, 3)
+    assert_bits_equal(ka.C.to_numpy(), kb.C.to_numpy(), "centroids")
+    assert_bits_equal(ka.assign.to_numpy(), kb.assign.to_numpy(), "assignments")
+    y = x @ np.arange(64.0).reshape(-1, 1)
+    Y = k.DenseMatrix.from_numpy(ctx, y)
+    na, nb = p.normal_equations(ctx, X, Y, 0.001), p.normal_equations_native(ctx, X, Y, 0.001)
+    for u, v in ((na.A, nb.A), (na.b, nb.b), (na.beta, nb.beta)):
+        assert_bits_equal(u.to_numpy(), v.to_numpy(), "normal equations")
