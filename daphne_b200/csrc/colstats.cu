@@ -126,6 +126,51 @@ __global__ void col_stats_answer_kernel(const double *__restrict__ stats, int64_
     out[c] = v;
 }
 
+// ---- row-sharded runs: statistics of all ranks ----
+// packet of one rank: [rows | pivot (cols) | S1 (cols) | S2 (cols) | column sums (cols)]
+__global__ void col_stats_pack_kernel(const double *__restrict__ stats, const double *__restrict__ sums, int64_t cols,
+                                      int64_t rows, double *__restrict__ pkt) {
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i == 0)
+        pkt[0] = (double)rows;
+    if (i < 3 * cols)
+        pkt[1 + i] = stats[i];
+    if (i < cols)
+        pkt[1 + 3 * cols + i] = sums[i];
+}
+// the column sums over all ranks, added in rank order (the same bits on every rank)
+__global__ void col_stats_fold_kernel(const double *__restrict__ gathered, int world, int64_t cols,
+                                      double *__restrict__ out) {
+    const int64_t c = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= cols)
+        return;
+    const int64_t P = 1 + 4 * cols;
+    double t = 0.0;
+    for (int r = 0; r < world; r++)
+        t = __dadd_rn(t, gathered[r * P + 1 + 3 * cols + c]);
+    out[c] = t;
+}
+// sum over ALL ranks' rows of (x - mu)^2 from the gathered statistics: every rank's identity around its own pivot
+__global__ void col_stats_answer_all_kernel(const double *__restrict__ gathered, int world, int64_t cols,
+                                            const double *__restrict__ mu, double *__restrict__ out,
+                                            int32_t *__restrict__ flag) {
+    const int64_t c = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= cols)
+        return;
+    const int64_t P = 1 + 4 * cols;
+    double tot = 0.0;
+    for (int r = 0; r < world; r++) {
+        const double *g = gathered + r * P;
+        const double n = g[0], K = g[1 + c], S1 = g[1 + cols + c], S2 = g[1 + 2 * cols + c];
+        const double d = __dsub_rn(mu[c], K);
+        const double v = __fma_rn(__dmul_rn(n, d), d, __fma_rn(__dmul_rn(-2.0, d), S1, S2));
+        if (!(S2 <= 1000.0 * v) && S2 != 0.0)
+            atomicExch(flag, 1);
+        tot = __dadd_rn(tot, v);
+    }
+    out[c] = tot;
+}
+
 size_t col_stats_scratch_bytes(int64_t cols) { return (size_t)sm_count() * 4 * 3 * (size_t)cols * sizeof(double); }
 
 // column sums (out_mode 0) or means (1) of X into `out`, statistics into `stats` (3 * cols doubles)
@@ -226,6 +271,10 @@ int colstats_try_agg_col(db2_context *ctx, int op, db2_matrix **res, db2_matrix 
         DB2_TRY(prepare_result(ctx, res, DB2_F64, 1, arg->cols));
         DB2_CHECK((*res)->dev_ld >= arg->cols, DB2_EINVAL, "bad result");
         DB2_TRY(run_stats(ctx, arg, op == DB2_AGG_MEAN ? 1 : 0, static_cast<double *>((*res)->dev_ptr())));
+        if (op == DB2_AGG_SUM && ctx->colstats && ctx->colstats->buf.lock() == arg->dev) {
+            ctx->colstats->sum_buf = (*res)->dev; // an all-reduce of these sums will carry the statistics along
+            ctx->colstats->sum_version = (*res)->dev->version;
+        }
         count(ctx, before);
         *handled = true;
         return DB2_OK;
@@ -258,10 +307,56 @@ int colstats_try_sqdev(db2_context *ctx, const Expr &e, db2_matrix **res, bool *
     const uint64_t before = g_launches.load();
     DB2_TRY(prepare_result(ctx, res, DB2_F64, 1, e.cols));
     bool ok = false;
-    DB2_TRY(answer_checked(ctx, *ctx->colstats->stats, static_cast<const double *>(sub.operand.ptr(8)), 0, e.rows,
-                           e.cols, static_cast<double *>((*res)->dev_ptr()), &ok));
+    const ColStats &cs = *ctx->colstats;
+    if (cs.gathered && cs.world == ctx->world && ctx->world > 1) {
+        // the statistics of every rank are here: the result is the sum over ALL shards, marked as combined so that
+        // the all-reduce the caller issues next is a no-op
+        int32_t *flag = ctx->dev_status + 24, *h = ctx->host_status + 24;
+        DB2_CUDA(cudaMemsetAsync(flag, 0, sizeof(int32_t), ctx->stream));
+        col_stats_answer_all_kernel<<<(unsigned)((e.cols + 127) / 128), 128, 0, ctx->stream>>>(
+            static_cast<const double *>(cs.gathered->ptr), cs.world, e.cols,
+            static_cast<const double *>(sub.operand.ptr(8)), static_cast<double *>((*res)->dev_ptr()), flag);
+        DB2_TRY(after_launch("col_stats_answer_all_kernel"));
+        DB2_CUDA(cudaMemcpyAsync(h, flag, sizeof(int32_t), cudaMemcpyDeviceToHost, ctx->stream));
+        DB2_CUDA(cudaStreamSynchronize(ctx->stream));
+        // the flag must be the same on every rank (they all evaluate the same gathered numbers), so either all ranks
+        // take this path or none does
+        ok = *h == 0;
+        (*res)->combined = ok;
+    } else {
+        DB2_TRY(answer_checked(ctx, *cs.stats, static_cast<const double *>(sub.operand.ptr(8)), 0, e.rows, e.cols,
+                               static_cast<double *>((*res)->dev_ptr()), &ok));
+    }
     count(ctx, before);
     *handled = ok;
+    return DB2_OK;
+}
+
+int colstats_try_allreduce(db2_context *ctx, db2_matrix *m, bool *handled) {
+    *handled = false;
+    ColStats *cs = ctx->colstats.get();
+    if (!cs || !m->dev || cs->sum_buf.lock() != m->dev || cs->sum_version != m->dev->version || m->rows != 1 ||
+        m->cols != cs->cols || !cs->buf.lock())
+        return DB2_OK;
+    const int64_t cols = cs->cols, P = 1 + 4 * cols;
+    const uint64_t before = g_launches.load();
+    auto pkt = make_devbuf(ctx, (size_t)P * sizeof(double));
+    auto gathered = make_devbuf(ctx, (size_t)P * ctx->world * sizeof(double));
+    col_stats_pack_kernel<<<(unsigned)((3 * cols + 127) / 128), 128, 0, ctx->stream>>>(
+        static_cast<const double *>(cs->stats->ptr), static_cast<const double *>(m->dev_ptr()), cols, cs->rows,
+        static_cast<double *>(pkt->ptr));
+    DB2_TRY(after_launch("col_stats_pack_kernel"));
+    DB2_TRY(comm_allgather_f64(ctx, static_cast<const double *>(pkt->ptr), static_cast<double *>(gathered->ptr),
+                               (size_t)P));
+    col_stats_fold_kernel<<<(unsigned)((cols + 127) / 128), 128, 0, ctx->stream>>>(
+        static_cast<const double *>(gathered->ptr), ctx->world, cols, static_cast<double *>(m->dev_ptr()));
+    DB2_TRY(after_launch("col_stats_fold_kernel"));
+    m->host_valid = false;
+    cs->gathered = gathered;
+    cs->world = ctx->world;
+    cs->sum_buf.reset(); // the buffer now holds the global sums
+    count(ctx, before);
+    *handled = true;
     return DB2_OK;
 }
 

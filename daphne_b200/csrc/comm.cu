@@ -144,6 +144,16 @@ int nccl_allreduce_group(const std::vector<db2_context *> &ctxs, const std::vect
     return DB2_OK;
 }
 
+int comm_allgather_f64(db2_context *ctx, const double *send, double *recv, size_t count) {
+    Nccl *n = nccl();
+    DB2_CHECK(n && ctx->comm, DB2_ENCCL, "no communicator: call db2_comm_init first");
+    DB2_NCCL(n->AllGather(send, recv, count, ncclFloat64, static_cast<ncclComm_t>(ctx->comm), ctx->stream));
+    std::lock_guard<std::mutex> lock(ctx->mu);
+    ctx->stats.collectives++;
+    ctx->stats.collective_bytes += (uint64_t)count * 8 * ctx->world;
+    return DB2_OK;
+}
+
 // rows of rank r when n rows are cut into `world` contiguous blocks (the first n % world blocks hold one more row)
 static void row_block(int64_t n, int r, int world, int64_t *lo, int64_t *hi) {
     const int64_t base = n / world, extra = n % world;
@@ -246,10 +256,20 @@ int db2_allreduce(db2_context *ctx, db2_matrix *m, int combine) {
               "only ADD, MIN and MAX results are combined across row shards");
     if (ctx->world == 1)
         return DB2_OK;
+    if (m->combined) { // answered from exchanged statistics: already the value over all shards
+        m->combined = false;
+        return DB2_OK;
+    }
     DB2_CHECK(ctx->comm, DB2_ENCCL, "no communicator: call db2_comm_init first");
     bind_device(ctx);
     DB2_TRY(ensure_device(m));
     DB2_CHECK(m->dev_ld == m->cols || m->rows == 1, DB2_EUNSUPPORTED, "all-reduce of a strided view");
+    if (combine == DB2_COMBINE_ADD) {
+        bool handled = false;
+        DB2_TRY(colstats_try_allreduce(ctx, m, &handled));
+        if (handled)
+            return DB2_OK;
+    }
     const int op = combine == DB2_COMBINE_ADD ? ncclSum : (combine == DB2_COMBINE_MIN ? ncclMin : ncclMax);
     DB2_NCCL(nccl()->AllReduce(m->dev_ptr(), m->dev_ptr(), (size_t)m->rows * m->cols, nccl_dtype(m->dtype), op,
                                static_cast<ncclComm_t>(ctx->comm), ctx->stream));

@@ -176,6 +176,7 @@ int prepare_result(db2_context *ctx, db2_matrix **res, int dtype, int64_t rows, 
         r->onehot.reset();
     }
     r->is_seq = false;
+    r->combined = false;
     // a buffer that deferred chains (or other handles) still read is not overwritten: the result gets a fresh one.
     // Row views are the exception: writing through a view is how results are placed into a larger matrix.
     if (r->dev)

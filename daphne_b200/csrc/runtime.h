@@ -78,6 +78,13 @@ struct ColStats {
     uint64_t version = 0;
     int64_t off = 0, ld = 0, rows = 0, cols = 0;
     std::shared_ptr<DevBuf> stats; // 3 * cols doubles
+    // row-sharded runs: the buffer the column sums of this shard went to, and -- once that result has been combined
+    // over the ranks -- every rank's (rows, pivot, S1, S2, sums), so that the squared deviations from the GLOBAL mean
+    // are answered for all shards at once, without a second exchange
+    std::weak_ptr<DevBuf> sum_buf;
+    uint64_t sum_version = 0;
+    std::shared_ptr<DevBuf> gathered; // world x (1 + 4 * cols) doubles
+    int world = 1;
 };
 
 struct HostBuf {
@@ -129,6 +136,9 @@ struct db2_matrix {
     int64_t seq_start = 0, seq_inc = 0;
 
     bool is_view = false; // shares its buffers with a parent (row slice): results written through it stay in place
+    // the values already are the combination over the row shards of all ranks (computed from exchanged statistics): the
+    // next all-reduce of this matrix has nothing left to do
+    bool combined = false;
 
     bool deferred() const { return (bool)lazy || (bool)pend_src || (bool)onehot; }
     size_t esize() const { return db2::dtype_size(dtype); }
@@ -197,6 +207,10 @@ struct OneHot { // rows x cols matrix with one stored entry per row: (r, idx[r])
 // deferred  sum((X - mu)^2)  are answered from them
 int colstats_try_agg_col(db2_context *ctx, int op, db2_matrix **res, db2_matrix *arg, bool *handled);
 int colstats_try_sqdev(db2_context *ctx, const Expr &e, db2_matrix **res, bool *handled);
+// all-reduce (ADD) of the column sums that filled the statistics: one all-gather that also carries every rank's
+// statistics (colstats.cu); comm_allgather_f64 is the raw collective (comm.cu)
+int colstats_try_allreduce(db2_context *ctx, db2_matrix *m, bool *handled);
+int comm_allgather_f64(db2_context *ctx, const double *send, double *recv, size_t count);
 int onehot_force(db2_matrix *m); // writes the dense rows
 int onehot_try_matmul(db2_context *ctx, db2_matrix **res, db2_matrix *lhs, db2_matrix *rhs, int transa, int transb,
                       bool *handled);

@@ -91,25 +91,31 @@ def _allreduce_scalar(ctx, x: float, comm: Optional[Comm], combine=COMBINE_ADD) 
     return float(comm.allreduce_numpy(np.array([x], dtype=np.float64), combine)[0])
 
 
-def _sum_over_shards(ctx, K, vec, comm: Optional[Comm]) -> float:
+def _sum_over_shards(ctx, K, vec, comm: Optional[Comm]):
     """sum(vec) over all row shards for an n x 1 vector.  With a device communicator the shard's sum stays on the
-    device as a 1 x 1 matrix and is combined there (one NCCL call on the compute stream, one read at the end); the
-    generic route reads the shard's scalar and combines it through the host."""
+    device as a 1 x 1 matrix and is combined there (one NCCL call on the compute stream, nothing is read: the caller
+    gets the device matrix); the generic route reads the shard's scalar and combines it through the host."""
     if comm is not None and comm.world > 1 and comm.device_collectives(ctx) and vec.cols == 1:
         part = K.aggCol(A.SUM, vec)
         comm.allreduce_device(ctx, part, COMBINE_ADD)
-        return float(part.to_numpy()[0, 0])
+        return part
     return _allreduce_scalar(ctx, K.aggAll(A.SUM, vec), comm)
 
 
-@dataclass
 class StandardiseResult:
-    mu: object        # 1 x c   column means
-    sd: object        # 1 x c   column standard deviations (population)
-    r: object         # n x 1   rowSums(Z^2)
-    s: float                 #         sum(r) over ALL shards
-    row_max: object   # n x 1   rowMaxs(Z)
-    row_idx_max: object  # n x 1 (uint64) idxMax per row of Z
+    """mu, sd: 1 x c column means / population standard deviations; r: n x 1 rowSums(Z^2); row_max: n x 1 rowMaxs(Z);
+    row_idx_max: n x 1 (uint64) idxMax per row of Z; s: sum(r) over ALL shards.  On the device path the sum stays a
+    1 x 1 device matrix (already combined over the ranks) and is read when `s` is first asked for."""
+
+    def __init__(self, mu, sd, r, s, row_max, row_idx_max):
+        self.mu, self.sd, self.r, self.row_max, self.row_idx_max = mu, sd, r, row_max, row_idx_max
+        self._s = s
+
+    @property
+    def s(self) -> float:
+        if not isinstance(self._s, float):
+            self._s = float(self._s.to_numpy()[0, 0])
+        return self._s
 
 
 def standardise_aggregate(ctx, X, n_total: Optional[int] = None, comm: Optional[Comm] = None, probe=None,
