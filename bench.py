@@ -233,7 +233,8 @@ def run_ours(args) -> dict:
     if not args.no_extra:
         leg_sampler = ClockSampler(local_rank)  # the side legs get their own clock record
         leg_sampler.start()
-        for name, leg in (("normal_equations_shard", normal_equations_leg), ("kmeans_shard", kmeans_leg),
+        for name, leg in (("normal_equations_shard", normal_equations_leg),
+                          ("normal_equations_full", normal_equations_full_leg), ("kmeans_shard", kmeans_leg),
                           ("connected_components", components_leg), ("f32_matmul_tcgen05", f32_matmul_leg)):
             try:
                 extra[name] = leg(ctx, comm, lib, host, world, args)
@@ -315,11 +316,112 @@ def normal_equations_leg(ctx, comm, lib, host, world, args) -> dict:
     syrk = probe.summary()
     beta = res.beta.to_numpy()
     flop = float(n) * d * (d + 1)
+    peak = fp64_peak_live(ctx, lib)
     return {"workload": f"t(X)X + lambda I, t(X)y, solve on f64 {n} x {d} per GPU (U[-1,1)), combined over {world} GPU(s)",
             "ms_per_step": step_ms, "rows_per_s": n * world / (step_ms * 1e-3),
             "syrk_ms": syrk["avg_ms"], "syrk_tflops_syrk_count": flop / (syrk["avg_ms"] * 1e-3) / 1e12,
-            "syrk_frac_of_fp64_peak": flop / (syrk["avg_ms"] * 1e-3) / 1e12 / FP64_PEAK_TFLOPS,
-            "fp64_peak_tflops": FP64_PEAK_TFLOPS, "beta_max_abs_err_vs_w": float(np.abs(beta - w).max())}
+            "syrk_frac_of_fp64_peak": flop / (syrk["avg_ms"] * 1e-3) / 1e12 / peak["tflops"],
+            "fp64_peak_measured": peak, "beta_max_abs_err_vs_w": float(np.abs(beta - w).max())}
+
+
+def fp64_peak_live(ctx, lib) -> dict:
+    """FP64 tensor peak measured in this run: cuBLAS DGEMM 8192^3 (2 n^3 flop), called through the library's C API on
+    the context's stream and timed with CUDA events, best of 5 after a warm-up.  It is the denominator of the FP64
+    roofline fractions; a constant is used (and named) when cuBLAS cannot be loaded."""
+    from daphne_b200.lib import check
+    n = 8192
+    try:
+        cublas = None
+        for name in ("libcublas.so.12", "libcublas.so"):
+            try:
+                cublas = C.CDLL(name)
+                break
+            except OSError:
+                continue
+        if cublas is None:
+            import glob
+            import sysconfig
+            hits = glob.glob(sysconfig.get_paths()["purelib"] + "/nvidia/cublas/lib/libcublas.so.*")
+            cublas = C.CDLL(hits[0])
+        handle = C.c_void_p()
+        assert cublas.cublasCreate_v2(C.byref(handle)) == 0
+        stream = C.c_void_p(ctx.stream)
+        assert cublas.cublasSetStream_v2(handle, stream) == 0
+        bufs = [C.c_void_p() for _ in range(3)]
+        for b in bufs:
+            check(lib.db2_malloc(C.byref(b), n * n * 8))
+            check(lib.db2_memset(b, 0, n * n * 8, stream))
+        one, zero = C.c_double(1.0), C.c_double(0.0)
+        cublas.cublasDgemm_v2.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p,
+                                          C.c_void_p, C.c_int, C.c_void_p, C.c_int, C.c_void_p, C.c_void_p, C.c_int]
+
+        def gemm():
+            assert cublas.cublasDgemm_v2(handle, 0, 0, n, n, n, C.byref(one), bufs[0], n, bufs[1], n, C.byref(zero),
+                                         bufs[2], n) == 0
+        gemm()
+        check(lib.db2_device_sync())
+        best = None
+        for _ in range(5):
+            e0, e1 = C.c_void_p(), C.c_void_p()
+            check(lib.db2_event_create(C.byref(e0)))
+            check(lib.db2_event_create(C.byref(e1)))
+            check(lib.db2_event_record(e0, stream))
+            gemm()
+            check(lib.db2_event_record(e1, stream))
+            ms = C.c_float()
+            check(lib.db2_event_elapsed_ms(e0, e1, C.byref(ms)))
+            best = ms.value if best is None else min(best, ms.value)
+        for b in bufs:
+            check(lib.db2_free(b))
+        cublas.cublasDestroy_v2(handle)
+        return {"tflops": 2.0 * n ** 3 / (best * 1e-3) / 1e12, "kind": "measured in this run",
+                "how": f"cuBLAS DGEMM {n}^3, best of 5, CUDA events, {best:.2f} ms"}
+    except Exception as e:  # cuBLAS not loadable: the constant measured earlier on the same kind of GPU
+        return {"tflops": FP64_PEAK_TFLOPS, "kind": "constant", "how": f"cuBLAS unavailable ({type(e).__name__})"}
+
+
+def normal_equations_full_leg(ctx, comm, lib, host, world, args) -> dict:
+    """The sharded normal equations at the size the configuration names: X f64 8,388,608 x 512 (32 GiB, U[-1,1)) in
+    TOTAL, rows split over the ranks (strong scaling: one GPU holds all of it, eight hold 1,048,576 rows each);
+    t(X)X by syrk and t(X)y by gemv combined over the ranks, then solve.  The data are generated in 64 blocks with one
+    seed per block, so every number of ranks works on the same matrix.  FLOP convention: BLAS syrk count n d (d+1)."""
+    import daphne_b200.kernels as K
+    from daphne_b200 import pipelines
+    from daphne_b200.lib import check
+    full = args.rows >= ROWS_PER_GPU
+    n_total, d, blocks = (8_388_608, 512, 64) if full else (max(args.rows // 2, 8192), 512, 8)
+    per_block = n_total // blocks
+    mine = [b for b in range(blocks) if b * world // blocks == comm.rank]
+    n = per_block * len(mine)
+    w = np.random.default_rng(55).standard_normal((d, 1))
+    X = K.DenseMatrix.empty(ctx, n, d)
+    Y = K.DenseMatrix.empty(ctx, n, 1)
+    stage = host.reshape(-1)[: per_block * d].reshape(per_block, d)  # the pinned buffer, one block at a time
+    ybuf = np.empty((per_block, 1))
+    for i, b in enumerate(mine):
+        rng = np.random.default_rng(5000 + b)
+        step = 1 << 13
+        for lo in range(0, per_block, step):
+            hi = min(per_block, lo + step)
+            stage[lo:hi] = rng.random((hi - lo, d)) * 2.0 - 1.0
+        ybuf[:] = stage @ w + 0.01 * rng.standard_normal((per_block, 1))
+        xs, ys = X.slice_rows(i * per_block, (i + 1) * per_block), Y.slice_rows(i * per_block, (i + 1) * per_block)
+        check(lib.db2_memcpy_h2d(C.c_void_p(xs.device_ptr()[0]), C.c_void_p(stage.ctypes.data), stage.nbytes,
+                                 C.c_void_p(ctx.stream)))
+        check(lib.db2_memcpy_h2d(C.c_void_p(ys.device_ptr()[0]), C.c_void_p(ybuf.ctypes.data), ybuf.nbytes,
+                                 C.c_void_p(ctx.stream)))
+        ctx.sync()
+    peak = fp64_peak_live(ctx, lib)
+    ms, res = _timed(lib, ctx, comm, lambda: pipelines.normal_equations_native(ctx, X, Y, 0.001), 3)
+    beta = res.beta.to_numpy()
+    flop = float(n_total) * d * (d + 1) + 2.0 * n_total * d
+    return {"workload": f"t(X)X + lambda I, t(X)y, solve on f64 {n_total} x {d} in total (U[-1,1)), rows over "
+                        f"{world} GPU(s): {n} per GPU", "scaling": "strong", "rows_total": n_total, "rows_per_gpu": n,
+            "ms_per_step": ms, "rows_per_s": n_total / (ms * 1e-3),
+            "tflops_syrk_count": flop / (ms * 1e-3) / 1e12,
+            "frac_of_fp64_peak_all_gpus": flop / (ms * 1e-3) / 1e12 / (peak["tflops"] * world),
+            "fp64_peak_measured": peak, "beta_max_abs_err_vs_w": float(np.abs(beta - w).max()),
+            "beta_checksum": float(beta.sum())}
 
 
 LEGS = {}
@@ -337,7 +439,7 @@ def run_leg(args) -> dict:
     comm = Comm.from_env("nccl")
     ctx = K.Context(local_rank)
     comm.init_device(ctx)
-    host, host_ptr = pinned_array(lib, max(args.rows // 16, 4096) * 512 // COLS + 1, COLS)
+    host, host_ptr = pinned_array(lib, max(args.rows // 16, 8192) * 512 // COLS + 1, COLS)
     out = LEGS[args.leg](ctx, comm, lib, host, world, args)
     lib.db2_free_host(host_ptr)
     return {"leg": args.leg, "n_gpus": world, **out} if comm.rank == 0 else {}
@@ -451,7 +553,8 @@ def f32_matmul_leg(ctx, comm, lib, host, world, args) -> dict:
             "max_abs_err_vs_f64_64_rows": float(np.abs(got - ref).max())}
 
 
-LEGS.update({"normal_equations_shard": normal_equations_leg, "kmeans_shard": kmeans_leg,
+LEGS.update({"normal_equations_shard": normal_equations_leg, "normal_equations_full": normal_equations_full_leg,
+             "kmeans_shard": kmeans_leg,
              "connected_components": components_leg, "f32_matmul_tcgen05": f32_matmul_leg})
 
 
@@ -538,8 +641,8 @@ def main():
     ap.add_argument("--cpu-rows", type=int, default=None,
                     help="rows of the CPU run: default 4,194,304 for the cpu_baseline of the GPU arm (a bounded "
                          "sample), all rows for --impl reference")
-    ap.add_argument("--leg", default=None, choices=["normal_equations_shard", "kmeans_shard", "connected_components",
-                                                    "f32_matmul_tcgen05"],
+    ap.add_argument("--leg", default=None, choices=["normal_equations_shard", "normal_equations_full", "kmeans_shard",
+                                                    "connected_components", "f32_matmul_tcgen05"],
                     help="run only this side workload (profiling aid); prints its own JSON line")
     args = ap.parse_args()
     if args.cpu_rows is None:

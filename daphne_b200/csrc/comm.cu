@@ -248,6 +248,27 @@ int db2_comm_info(const db2_context *ctx, int *rank, int *world) {
     return DB2_OK;
 }
 
+// Collectives issued between begin and end are handed to NCCL as one group: it launches them together, so a count
+// all-reduce and the all-gather that follows it cost one launch on the stream instead of two.
+int db2_comm_group_begin(db2_context *ctx) {
+    DB2_CHECK(ctx, DB2_EINVAL, "null context");
+    if (ctx->world == 1 || !ctx->comm)
+        return DB2_OK;
+    Nccl *n = nccl();
+    DB2_CHECK(n, DB2_ENCCL, "NCCL library (libnccl.so.2) could not be loaded");
+    DB2_NCCL(n->GroupStart());
+    return DB2_OK;
+}
+int db2_comm_group_end(db2_context *ctx) {
+    DB2_CHECK(ctx, DB2_EINVAL, "null context");
+    if (ctx->world == 1 || !ctx->comm)
+        return DB2_OK;
+    Nccl *n = nccl();
+    DB2_CHECK(n, DB2_ENCCL, "NCCL library (libnccl.so.2) could not be loaded");
+    DB2_NCCL(n->GroupEnd());
+    return DB2_OK;
+}
+
 // In-place combine of a (small, contiguous) device-resident partial over all ranks; combine = VectorCombine code.
 int db2_allreduce(db2_context *ctx, db2_matrix *m, int combine) {
     DB2_API_BEGIN

@@ -97,7 +97,13 @@ constexpr int LU_NB = 32, LU_REG_ROWS = 512;
 __global__ void __launch_bounds__(LU_REG_ROWS)
     lu_panel_reg_kernel(double *__restrict__ A, int64_t n, int64_t k0, int nb, int *__restrict__ piv,
                         int32_t *__restrict__ status) {
-    __shared__ double rowbuf[2][2][LU_NB]; // [column parity][pivot row / row j][entries]
+    // ONE barrier per column: before it every warp publishes its best pivot candidate TOGETHER WITH that candidate's
+    // row, and the owner of row j publishes row j; after it every thread folds the warps' candidates to the same
+    // pivot p and finds both rows it may need.  The buffers alternate with the column parity, so the writes of column
+    // j + 1 cannot overtake the reads of column j - 1 (a thread writes them only after the barrier of column j, which
+    // every thread reaches after its reads of column j - 1).
+    __shared__ double cand_row[2][LU_REG_ROWS / 32][LU_NB]; // [parity][warp][entries]: row of the warp's candidate
+    __shared__ double row_j[2][LU_NB];                      // [parity][entries]: row j before the exchange
     __shared__ double s_val[2][LU_REG_ROWS / 32];
     __shared__ int s_idx[2][LU_REG_ROWS / 32];
     const int tid = threadIdx.x, lane = tid % 32, warp = tid / 32, nwarps = blockDim.x / 32;
@@ -126,9 +132,19 @@ __global__ void __launch_bounds__(LU_REG_ROWS)
                 bi = oi;
             }
         }
+        if (tid == bi) { // this warp's candidate publishes its row
+#pragma unroll
+            for (int c = 0; c < LU_NB; c++)
+                cand_row[par][warp][c] = a[c];
+        }
         if (lane == 0) {
             s_val[par][warp] = best;
             s_idx[par][warp] = bi;
+        }
+        if (tid == j) {
+#pragma unroll
+            for (int c = 0; c < LU_NB; c++)
+                row_j[par][c] = a[c];
         }
         __syncthreads();
         best = lane < nwarps ? s_val[par][lane] : -1.0;
@@ -143,39 +159,29 @@ __global__ void __launch_bounds__(LU_REG_ROWS)
             }
         }
         const int p = bi; // every thread has the same answer; always a row in [j, m): row j is a candidate
+        const double *prow = cand_row[par][p / 32];
         if (tid == 0) {
             piv[k0 + j] = (int)k0 + p;
             if (!(best > 0.0) && *status == 0)
                 *status = (int32_t)(k0 + j + 1); // exactly singular (or NaN) pivot
         }
-        if (tid == p) {
-#pragma unroll
-            for (int c = 0; c < LU_NB; c++)
-                rowbuf[par][0][c] = a[c];
-        }
-        if (tid == j) {
-#pragma unroll
-            for (int c = 0; c < LU_NB; c++)
-                rowbuf[par][1][c] = a[c];
-        }
-        __syncthreads();
         if (p != j) { // the two rows change places
             if (tid == j) {
 #pragma unroll
                 for (int c = 0; c < LU_NB; c++)
-                    a[c] = rowbuf[par][0][c];
+                    a[c] = prow[c];
             } else if (tid == p) {
 #pragma unroll
                 for (int c = 0; c < LU_NB; c++)
-                    a[c] = rowbuf[par][1][c];
+                    a[c] = row_j[par][c];
             }
         }
         if (tid > j && tid < m) {
-            const double l = __ddiv_rn(a[j], rowbuf[par][0][j]);
+            const double l = __ddiv_rn(a[j], prow[j]);
             a[j] = l;
 #pragma unroll
             for (int c = j + 1; c < LU_NB; c++)
-                a[c] = __fma_rn(-l, rowbuf[par][0][c], a[c]);
+                a[c] = __fma_rn(-l, prow[c], a[c]);
         }
     }
     if (tid < m)
@@ -187,28 +193,52 @@ __global__ void __launch_bounds__(LU_REG_ROWS)
 
 // One thread per column outside the panel (column index n stands for the right-hand side): row exchanges of the
 // panel, then -- right of the panel and for b -- the forward substitution with the panel's unit lower triangle.
-__global__ void lu_swap_trsm_kernel(double *__restrict__ A, double *__restrict__ x, int64_t n, int64_t k0, int nb,
-                                    const int *__restrict__ piv) {
-    const int64_t c = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+// The column's entries of the block row live in shared memory while this happens (one column of a [32][threads] tile
+// per thread) and the triangle is staged once per block: the 32 exchanges and 496 updates of a column touch global
+// memory only for its 32 entries and for pivot rows below the block row.  (Keeping them in global memory cost a
+// dependent L2 round trip per update: 2 ms of the 2.4 ms a 512 x 512 solve took.)
+constexpr int TRSM_THREADS = 128;
+__global__ void __launch_bounds__(TRSM_THREADS)
+    lu_swap_trsm_kernel(double *__restrict__ A, double *__restrict__ x, int64_t n, int64_t k0, int nb,
+                        const int *__restrict__ piv) {
+    __shared__ double V[LU_NB][TRSM_THREADS + 1];
+    __shared__ double L[LU_NB][LU_NB + 1];
+    __shared__ int P[LU_NB];
+    const int t = threadIdx.x;
+    for (int e = t; e < nb * nb; e += TRSM_THREADS)
+        L[e / nb][e % nb] = A[(k0 + e / nb) * n + k0 + e % nb];
+    if (t < nb)
+        P[t] = piv[k0 + t];
+    __syncthreads();
+    const int64_t c = (int64_t)blockIdx.x * TRSM_THREADS + t;
     if (c > n || (c >= k0 && c < k0 + nb))
         return;
     const bool rhs = (c == n);
     double *col = rhs ? x : A + c;
     const int64_t st = rhs ? 1 : n;
+    for (int j = 0; j < nb; j++)
+        V[j][t] = col[(k0 + j) * st];
     for (int j = 0; j < nb; j++) {
-        const int64_t p = piv[k0 + j];
+        const int64_t p = P[j];
         if (p > k0 + j && p < n) { // a pivot row lies below row k0 + j and inside the matrix; anything else is no exchange
-            const double t = col[(k0 + j) * st];
-            col[(k0 + j) * st] = col[p * st];
-            col[p * st] = t;
+            const double v = V[j][t];
+            if (p < k0 + nb) {
+                V[j][t] = V[p - k0][t];
+                V[p - k0][t] = v;
+            } else {
+                V[j][t] = col[p * st];
+                col[p * st] = v;
+            }
         }
     }
     if (rhs || c >= k0 + nb)
         for (int j = 0; j < nb; j++) {
-            const double v = col[(k0 + j) * st];
+            const double v = V[j][t];
             for (int i = j + 1; i < nb; i++)
-                col[(k0 + i) * st] = __fma_rn(-A[(k0 + i) * n + k0 + j], v, col[(k0 + i) * st]);
+                V[i][t] = __fma_rn(-L[i][j], v, V[i][t]);
         }
+    for (int j = 0; j < nb; j++)
+        col[(k0 + j) * st] = V[j][t];
 }
 
 // A22 -= L21 U12 (and b2 -= L21 b1 as one more column): 32 x 32 tiles
@@ -244,20 +274,45 @@ __global__ void __launch_bounds__(256)
     }
 }
 
+// Back substitution in blocks of 32 unknowns: warp 0 solves the 32 x 32 triangle on the diagonal (its tile sits in
+// shared memory, the unknowns in registers, one shuffle per unknown), then all threads subtract the block's
+// contribution from the rows above, each reading 32 consecutive entries of its row.  Every unknown sees the same
+// operations in the same order as in the column-by-column loop (x_k /= U_kk; x_i -= U_ik x_k for k descending), so the
+// result has the same bits; what changes is that the loop no longer pays two block-wide barriers and a strided pass
+// through L2 per unknown.
 __global__ void __launch_bounds__(LU_THREADS)
     lu_backsolve_kernel(const double *__restrict__ A, double *__restrict__ x, int64_t n) {
     extern __shared__ double xs[];
-    const int tid = threadIdx.x, nt = blockDim.x;
+    __shared__ double T[32][33];
+    const int tid = threadIdx.x, nt = blockDim.x, lane = tid % 32;
     for (int64_t i = tid; i < n; i += nt)
         xs[i] = x[i];
-    __syncthreads();
-    for (int64_t k = n - 1; k >= 0; k--) {
-        if (tid == 0)
-            xs[k] = __ddiv_rn(xs[k], A[k * n + k]);
+    for (int64_t k1 = n; k1 > 0; k1 -= 32) {
+        const int64_t k0 = k1 >= 32 ? k1 - 32 : 0;
+        const int w = (int)(k1 - k0);
+        for (int e = tid; e < w * w; e += nt)
+            T[e / w][e % w] = A[(k0 + e / w) * n + k0 + e % w];
         __syncthreads();
-        const double xk = xs[k];
-        for (int64_t i = tid; i < k; i += nt)
-            xs[i] = __fma_rn(-A[i * n + k], xk, xs[i]);
+        if (tid < 32) {
+            double xi = lane < w ? xs[k0 + lane] : 0.0;
+            for (int j = w - 1; j >= 0; j--) {
+                const double xj = __ddiv_rn(__shfl_sync(0xffffffffu, xi, j), T[j][j]);
+                if (lane == j)
+                    xi = xj;
+                else if (lane < j)
+                    xi = __fma_rn(-T[lane][j], xj, xi);
+            }
+            if (lane < w)
+                xs[k0 + lane] = xi;
+        }
+        __syncthreads();
+        for (int64_t i = tid; i < k0; i += nt) {
+            double acc = xs[i];
+            const double *row = A + i * n + k0;
+            for (int c = w - 1; c >= 0; c--)
+                acc = __fma_rn(-row[c], xs[k0 + c], acc);
+            xs[i] = acc;
+        }
         __syncthreads();
     }
     for (int64_t i = tid; i < n; i += nt)
@@ -304,7 +359,8 @@ extern "C" int db2k_solve(int dtype, void *a_work, int64_t n, void *x_inout, int
             lu_panel_kernel<<<1, threads, (size_t)m * (w + 1) * 8, st>>>(A, n, k0, w, piv, dev_status);
             DB2_TRY(after_launch("lu_panel_kernel"));
         }
-        lu_swap_trsm_kernel<<<(unsigned)((n + 1 + 127) / 128), 128, 0, st>>>(A, x, n, k0, w, piv);
+        lu_swap_trsm_kernel<<<(unsigned)((n + 1 + TRSM_THREADS - 1) / TRSM_THREADS), TRSM_THREADS, 0, st>>>(A, x, n, k0, w,
+                                                                                                        piv);
         DB2_TRY(after_launch("lu_swap_trsm_kernel"));
         const int64_t rest = n - k0 - w;
         if (rest > 0) {

@@ -75,8 +75,12 @@ int db2w_connected_components(db2_context *ctx, db2_csr *G, int64_t row_lo, int6
         if (sharded) {
             H cnt, gathered;
             DB2_TRY(db2_aggCol(ctx, DB2_AGG_SUM, &cnt, ne));
-            DB2_TRY(db2_allreduce(ctx, cnt, DB2_COMBINE_ADD));
-            DB2_TRY(db2_allgatherv_rows(ctx, u, n, &gathered));
+            DB2_TRY(db2_comm_group_begin(ctx)); // the count and the labels travel in one NCCL launch
+            int rc = db2_allreduce(ctx, cnt, DB2_COMBINE_ADD);
+            if (rc == DB2_OK)
+                rc = db2_allgatherv_rows(ctx, u, n, &gathered);
+            const int rc_end = db2_comm_group_end(ctx);
+            DB2_TRY(rc != DB2_OK ? rc : rc_end);
             DB2_TRY(db2_matrix_to_host(cnt, &diff, 1));
             c_full.reset(gathered.release());
             c_loc.reset();

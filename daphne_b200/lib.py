@@ -102,6 +102,8 @@ _SIGS = {
     "db2_comm_destroy": (i32, [vp]),
     "db2_comm_info": (i32, [vp, _P(i32), _P(i32)]),
     "db2_allreduce": (i32, [vp, vp, i32]),
+    "db2_comm_group_begin": (i32, [vp]),
+    "db2_comm_group_end": (i32, [vp]),
     "db2_allgather_rows": (i32, [vp, vp, _P(vp)]),
     "db2_allgatherv_rows": (i32, [vp, vp, i64, _P(vp)]),
     "db2_group_create": (i32, [_P(i32), i32, _P(vp)]),

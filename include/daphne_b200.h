@@ -293,6 +293,9 @@ int db2_comm_destroy(db2_context *ctx);
 int db2_comm_info(const db2_context *ctx, int *rank, int *world);
 /* in-place combine of a small contiguous partial over all ranks; combine = DB2_COMBINE_ADD / MIN / MAX */
 int db2_allreduce(db2_context *ctx, db2_matrix *m, int combine);
+/* collectives issued between the two calls are launched together (one NCCL group) */
+int db2_comm_group_begin(db2_context *ctx);
+int db2_comm_group_end(db2_context *ctx);
 /* concatenation of equally tall row shards in rank order */
 int db2_allgather_rows(db2_context *ctx, db2_matrix *local, db2_matrix **full);
 /* concatenation of the row shards of the scheduler's partition: total_rows rows cut into one contiguous block per
