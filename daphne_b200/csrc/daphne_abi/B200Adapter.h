@@ -188,18 +188,27 @@ class Call {
             throw std::runtime_error("no B200 device placement for a kernel argument");
         return view_of(desc->handle(), m);
     }
-    // the handle itself, or -- for a placement inherited from the parent of a row view -- a row slice of it
+    // the handle itself, or -- for a placement inherited from the parent of a view -- the same rows and columns of it
     template <typename VT> db2_matrix *view_of(db2_matrix *h, const DenseMatrix<VT> *m) {
         int64_t hr = 0, hc = 0;
         check(db2_matrix_info(h, nullptr, &hr, &hc));
-        if (hr == (int64_t)m->getNumRows() && hc == (int64_t)m->getNumCols())
+        const int64_t mr = (int64_t)m->getNumRows(), mc = (int64_t)m->getNumCols();
+        if (hr == mr && hc == mc)
             return h;
-        const size_t r0 = ViewOffsets::row(m);
-        if (hc != (int64_t)m->getNumCols() || ViewOffsets::col(m) != 0)
-            throw std::runtime_error("column views of device-resident matrices are not supported");
-        db2_matrix *v = nullptr;
-        check(db2_matrix_slice_rows(h, (int64_t)r0, (int64_t)(r0 + m->getNumRows()), &v));
-        temps.push_back(v);
+        const int64_t r0 = (int64_t)ViewOffsets::row(m), c0 = (int64_t)ViewOffsets::col(m);
+        if (r0 + mr > hr || c0 + mc > hc)
+            throw std::runtime_error("a view does not fit the device placement it inherited");
+        db2_matrix *v = h;
+        if (mr != hr) {
+            check(db2_matrix_slice_rows(v, r0, r0 + mr, &v));
+            temps.push_back(v);
+        }
+        if (mc != hc) {
+            db2_matrix *w = nullptr;
+            check(db2_matrix_slice_cols(v, c0, c0 + mc, &w));
+            temps.push_back(w);
+            v = w;
+        }
         return v;
     }
     // handle of a pre-allocated result (the kernel overwrites it)

@@ -39,6 +39,12 @@ constexpr int THREADS = PRODUCER_THREADS + DRAIN_THREADS + 32;
 constexpr int TMEM_COLS = 512; // two main accumulators and the cross-term accumulator of 128 columns each
 constexpr size_t SMEM_BYTES = (size_t)(RAW_SLOTS + LOW_SLOTS) * SLOT_BYTES + 1024 /* alignment slack */ + 256;
 constexpr long long WAIT_LIMIT_CLOCKS = 2000000000LL;
+// The limit of every bounded wait, and a switch that keeps the MMA issuer from issuing anything.  Both exist so that a
+// test can make the waits of the other roles run out on purpose (db2k_test_tf32_starve): the barriers they wait on are
+// then never completed, the waits expire after the (shortened) limit, and the kernel must leave through its common
+// exit with the status bit set and its tensor memory released.
+__device__ long long d_wait_limit = WAIT_LIMIT_CLOCKS;
+__device__ int d_starve = 0;
 
 // bits of the status word
 constexpr int STATUS_WAIT_EXPIRED = 1; // a bounded wait ran out: the result is not valid
@@ -80,11 +86,11 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort) {
     if (mbar_try_wait(bar, parity))
         return true;
-    const long long t0 = clock64();
+    const long long t0 = clock64(), limit = d_wait_limit;
     while (!mbar_try_wait(bar, parity)) {
         if (*abort)
             return false;
-        if (clock64() - t0 > WAIT_LIMIT_CLOCKS) {
+        if (clock64() - t0 > limit) {
             *abort = 1;
             return false;
         }
@@ -381,7 +387,7 @@ template <bool TA, bool TB> __global__ void __launch_bounds__(THREADS, 1) gemm_t
             constexpr uint32_t A_STEP = A_KMAJ ? 32 : 4096, B_STEP = B_KMAJ ? 32 : 4096;
             constexpr uint32_t A_LBO = A_KMAJ ? 16 : 512, A_SBO = A_KMAJ ? 1024 : 2048, A_LT = A_KMAJ ? 2 : 1;
             constexpr uint32_t B_LBO = B_KMAJ ? 16 : 512, B_SBO = B_KMAJ ? 1024 : 2048, B_LT = B_KMAJ ? 2 : 1;
-            bool ok = true;
+            bool ok = d_starve == 0; // (test switch: the issuer stays silent and everybody else's wait runs out)
             for (int kb = 0; kb < nkb && ok; kb++) {
                 const int c = kb / CHUNK_KB, b = c & 1;
                 const bool chunk_start = kb % CHUNK_KB == 0;
@@ -626,3 +632,12 @@ int tf32_gemm(const float *A, int64_t lda, bool ta, const float *B, int64_t ldb,
 
 } // namespace tc
 } // namespace db2
+
+// Test hook, not part of the public interface: sets the limit of the kernel's bounded waits (in clock cycles; <= 0
+// restores the default of about a second) and switches the MMA issuer off (starve != 0) or back on, on the current device.
+extern "C" int db2k_test_tf32_starve(long long limit_clocks, int starve) {
+    const long long limit = limit_clocks > 0 ? limit_clocks : db2::tc::WAIT_LIMIT_CLOCKS;
+    DB2_CUDA(cudaMemcpyToSymbol(db2::tc::d_wait_limit, &limit, sizeof(limit)));
+    DB2_CUDA(cudaMemcpyToSymbol(db2::tc::d_starve, &starve, sizeof(starve)));
+    return DB2_OK;
+}

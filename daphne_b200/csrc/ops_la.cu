@@ -29,7 +29,8 @@ static int check_contraction_status(db2_context *ctx, int dtype, const void *scr
     int32_t st = 0;
     DB2_CUDA(cudaMemcpyAsync(&st, scratch, sizeof(st), cudaMemcpyDeviceToHost, ctx->stream));
     DB2_CUDA(cudaStreamSynchronize(ctx->stream));
-    DB2_CHECK((st & 1) == 0, DB2_ECUDA, "f32 contraction kernel gave up waiting (status %d); result discarded", (int)st);
+    DB2_CHECK((st & 1) == 0, DB2_ETIMEOUT, "f32 contraction kernel gave up waiting (status %d); result discarded",
+              (int)st);
     return DB2_OK;
 }
 

@@ -362,6 +362,70 @@ int db2_matrix_slice_rows(db2_matrix *src, int64_t r0, int64_t r1, db2_matrix **
     DB2_API_END
 }
 
+// zero-copy view of the columns [c0, c1): same buffers, same leading dimension, the first column moved
+int db2_matrix_slice_cols(db2_matrix *src, int64_t c0, int64_t c1, db2_matrix **view) {
+    DB2_API_BEGIN
+    DB2_CHECK(src && view, DB2_EINVAL, "null argument");
+    DB2_CHECK(0 <= c0 && c0 <= c1 && c1 <= src->cols, DB2_EINVAL, "column range [%lld, %lld) outside [0, %lld)",
+              (long long)c0, (long long)c1, (long long)src->cols);
+    if (!src->dev_valid && src->ctx)
+        DB2_TRY(ensure_device(src));
+    std::unique_ptr<db2_matrix> m(new db2_matrix());
+    m->ctx = src->ctx;
+    m->dtype = src->dtype;
+    m->rows = src->rows;
+    m->cols = c1 - c0;
+    m->is_view = true;
+    if (src->dev) {
+        m->dev = src->dev;
+        m->dev_off = src->dev_off + c0;
+        m->dev_ld = src->dev_ld;
+        m->dev_valid = src->dev_valid;
+    }
+    if (src->host) {
+        m->host = src->host;
+        m->host_off = src->host_off + c0;
+        m->host_ld = src->host_ld;
+        m->host_valid = src->host_valid;
+    }
+    *view = m.release();
+    return DB2_OK;
+    DB2_API_END
+}
+
+// SliceRow / SliceCol with the reference's index rules (negative bounds count from the end) and messages
+static int resolve_slice(const char *what, const char *dim, int64_t lo, int64_t hi, int64_t n, int64_t *a, int64_t *b) {
+    const int64_t lo_in = lo, hi_in = hi;
+    if (lo < 0) {
+        lo += n;
+        if (hi <= 0)
+            hi += n;
+    } else if (hi < 0) {
+        hi += n;
+    }
+    if (lo < 0 || lo >= n || hi < lo || n < hi)
+        return set_error(DB2_EDOMAIN, "invalid arguments '%lld, %lld' passed to %s: it must hold 0 <= lowerIncl < #%s "
+                                      "and lowerIncl <= upperExcl <= #%s",
+                         (long long)lo_in, (long long)hi_in, what, dim, dim);
+    *a = lo;
+    *b = hi;
+    return DB2_OK;
+}
+int db2_sliceRow(db2_context *ctx, db2_matrix **res, db2_matrix *arg, int64_t lowerIncl, int64_t upperExcl) {
+    DB2_CHECK(ctx && res && arg, DB2_EINVAL, "null argument");
+    DB2_CHECK(*res == nullptr, DB2_EUNSUPPORTED, "sliceRow returns a view: a pre-allocated result is not supported");
+    int64_t a = 0, b = 0;
+    DB2_TRY(resolve_slice("SliceRow", "rows", lowerIncl, upperExcl, arg->rows, &a, &b));
+    return db2_matrix_slice_rows(arg, a, b, res);
+}
+int db2_sliceCol(db2_context *ctx, db2_matrix **res, db2_matrix *arg, int64_t lowerIncl, int64_t upperExcl) {
+    DB2_CHECK(ctx && res && arg, DB2_EINVAL, "null argument");
+    DB2_CHECK(*res == nullptr, DB2_EUNSUPPORTED, "sliceCol returns a view: a pre-allocated result is not supported");
+    int64_t a = 0, b = 0;
+    DB2_TRY(resolve_slice("SliceCol", "columns", lowerIncl, upperExcl, arg->cols, &a, &b));
+    return db2_matrix_slice_cols(arg, a, b, res);
+}
+
 int db2_matrix_incref(db2_matrix *m) {
     DB2_CHECK(m, DB2_EINVAL, "null matrix");
     m->refs.fetch_add(1);

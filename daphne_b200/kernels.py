@@ -340,6 +340,33 @@ def writeDaphne(arg: DenseMatrix, path, ctx: Optional[Context] = None) -> None:
     check(lib.db2_writeDaphne(ctx.handle, arg.handle, str(path).encode()))
 
 
+def sliceRow(arg: DenseMatrix, lowerIncl: int, upperExcl: int, ctx: Optional[Context] = None) -> DenseMatrix:
+    """SliceRow.h:45-82: rows [lowerIncl, upperExcl) as a zero-copy view; negative bounds count from the end."""
+    ctx = ctx or arg.ctx
+    h = C.c_void_p()
+    check(lib.db2_sliceRow(ctx.handle, C.byref(h), arg.handle, int(lowerIncl), int(upperExcl)))
+    return DenseMatrix(ctx, h, keep=arg)
+
+
+def sliceCol(arg: DenseMatrix, lowerIncl: int, upperExcl: int, ctx: Optional[Context] = None) -> DenseMatrix:
+    """SliceCol.h:52-86: columns [lowerIncl, upperExcl) as a zero-copy view."""
+    ctx = ctx or arg.ctx
+    h = C.c_void_p()
+    check(lib.db2_sliceCol(ctx.handle, C.byref(h), arg.handle, int(lowerIncl), int(upperExcl)))
+    return DenseMatrix(ctx, h, keep=arg)
+
+
+def randMatrix(ctx: Context, rows: int, cols: int, lo, hi, sparsity: float = 1.0, seed: int = -1,
+               dtype=np.float64) -> DenseMatrix:
+    """RandMatrix.h:82-161 = DaphneDSL rand(rows, cols, lo, hi, sparsity, seed), device-resident."""
+    dt = np.dtype(dtype)
+    a, b = np.array([lo], dtype=dt), np.array([hi], dtype=dt)
+    h = C.c_void_p()
+    check(lib.db2_randMatrix(ctx.handle, C.byref(h), _NP2DT[dt], int(rows), int(cols), C.c_void_p(a.ctypes.data),
+                             C.c_void_p(b.ctypes.data), float(sparsity), int(seed)))
+    return DenseMatrix(ctx, h)
+
+
 def ctable(lhs: DenseMatrix, rhs: DenseMatrix, weight: float = 1.0, resNumRows: int = -1, resNumCols: int = -1,
            ctx: Optional[Context] = None) -> DenseMatrix:
     """CTable.h:44-48: res[lhs[i], rhs[i]] += weight."""

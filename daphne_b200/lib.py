@@ -129,6 +129,10 @@ _SIGS = {
     "db2_matrix_wrap_host": (i32, [vp, i32, i64, i64, i64, vp, _P(vp)]),
     "db2_matrix_wrap_device": (i32, [vp, i32, i64, i64, i64, vp, _P(vp)]),
     "db2_matrix_slice_rows": (i32, [vp, i64, i64, _P(vp)]),
+    "db2_matrix_slice_cols": (i32, [vp, i64, i64, _P(vp)]),
+    "db2_sliceRow": (i32, [vp, _P(vp), vp, i64, i64]),
+    "db2_sliceCol": (i32, [vp, _P(vp), vp, i64, i64]),
+    "db2_randMatrix": (i32, [vp, _P(vp), i32, i64, i64, vp, vp, C.c_double, i64]),
     "db2_matrix_incref": (i32, [vp]),
     "db2_matrix_decref": (i32, [vp]),
     "db2_matrix_info": (i32, [vp, _P(i32), _P(i64), _P(i64)]),

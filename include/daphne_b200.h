@@ -314,6 +314,9 @@ int db2_matrix_wrap_device(db2_context *ctx, int dtype, int64_t rows, int64_t co
                            db2_matrix **out);
 /* zero-copy view of rows [r0, r1) (DenseMatrix view constructor, DenseMatrix.cpp:98-115) */
 int db2_matrix_slice_rows(db2_matrix *m, int64_t r0, int64_t r1, db2_matrix **view);
+/* zero-copy view of columns [c0, c1) (DenseMatrix view constructor with a column range, DenseMatrix.cpp:98-115):
+ * the view keeps the parent's leading dimension, which every kernel honours */
+int db2_matrix_slice_cols(db2_matrix *m, int64_t c0, int64_t c1, db2_matrix **view);
 int db2_matrix_incref(db2_matrix *m);
 int db2_matrix_decref(db2_matrix *m); /* frees at zero (DataObjectFactory::destroy) */
 int db2_matrix_info(const db2_matrix *m, int *dtype, int64_t *rows, int64_t *cols);
@@ -361,6 +364,17 @@ int db2_extractCol(db2_context *ctx, db2_matrix **res, db2_matrix *arg, db2_matr
 /* res_rows / res_cols < 0: derived from the largest coordinate (synchronises) */
 int db2_ctable(db2_context *ctx, db2_matrix **res, db2_matrix *lhs, db2_matrix *rhs, double weight,
                int64_t res_rows, int64_t res_cols);
+/* Row / column ranges as zero-copy views; negative bounds count from the end; DB2_EDOMAIN with the reference's
+ * out_of_range message otherwise (src/runtime/local/kernels/SliceRow.h:45-82, SliceCol.h:52-86) */
+int db2_sliceRow(db2_context *ctx, db2_matrix **res, db2_matrix *arg, int64_t lowerIncl, int64_t upperExcl);
+int db2_sliceCol(db2_context *ctx, db2_matrix **res, db2_matrix *arg, int64_t lowerIncl, int64_t upperExcl);
+/* rand(rows, cols, min, max, sparsity, seed) for double / float / int64 with the reference's stream: two
+ * std::mt19937 engines (seed, seed * 3), values in row-major order with zeros redrawn, selection sampling of the
+ * positions for sparsity < 1; seed -1 picks a random seed.  The walk is sequential and runs on the host, in row blocks
+ * that are uploaded through pinned staging while the next block is generated.  min / max: host pointers to one value
+ * of `dtype`.  Replaces RandMatrix<DenseMatrix<VT>, VT> (src/runtime/local/kernels/RandMatrix.h:82-161). */
+int db2_randMatrix(db2_context *ctx, db2_matrix **res, int dtype, int64_t rows, int64_t cols, const void *min,
+                   const void *max, double sparsity, int64_t seed);
 /* value-type cast between f64 / i64 / u64 (CastObj, used for idxMin results feeding ctable) */
 int db2_castObj(db2_context *ctx, db2_matrix **res, db2_matrix *arg, int dtype);
 

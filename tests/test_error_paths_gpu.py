@@ -79,3 +79,32 @@ def test_an_exhausted_memory_budget_is_reported_as_enomem():
         small.free()
     finally:
         c.close()
+
+
+def test_a_bounded_wait_that_runs_out_is_reported_as_etimeout():
+    """The tcgen05 kernel of the f32 matMul bounds every mbarrier wait.  With the MMA issuer switched off (a barrier
+    that nothing completes) and the limit shortened to about a millisecond, the waits of the other roles run out: the
+    kernel must leave through its common exit, release its tensor memory and raise the status bit, the call must
+    return DB2_ETIMEOUT, and the next product on the same context must be correct."""
+    import daphne_b200.kernels as k
+    from daphne_b200.lib import lib
+    lib.db2k_test_tf32_starve.argtypes = [C.c_longlong, C.c_int]
+    c = k.Context(0)
+    try:
+        rng = np.random.default_rng(0)
+        a = rng.standard_normal((512, 640)).astype(np.float32)
+        b = rng.standard_normal((640, 384)).astype(np.float32)
+        A, B = k.DenseMatrix.from_numpy(c, a), k.DenseMatrix.from_numpy(c, b)
+        ok = k.matMul(A, B).to_numpy()
+        assert lib.db2k_test_tf32_starve(2_000_000, 1) == 0
+        try:
+            with pytest.raises(k.Db2Error) as e:
+                k.matMul(A, B)
+            assert e.value.code == 7 and "gave up waiting" in str(e.value)
+        finally:
+            assert lib.db2k_test_tf32_starve(0, 0) == 0
+        again = k.matMul(A, B).to_numpy()
+        assert np.array_equal(again, ok), "the context is usable and tensor memory was released"
+        np.testing.assert_allclose(again, a.astype(np.float64) @ b.astype(np.float64), rtol=2e-4, atol=2e-3)
+    finally:
+        c.close()
