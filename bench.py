@@ -235,7 +235,8 @@ def run_ours(args) -> dict:
         leg_sampler.start()
         for name, leg in (("normal_equations_shard", normal_equations_leg),
                           ("normal_equations_full", normal_equations_full_leg), ("kmeans_shard", kmeans_leg),
-                          ("connected_components", components_leg), ("f32_matmul_tcgen05", f32_matmul_leg)):
+                          ("connected_components", components_leg), ("f32_matmul_tcgen05", f32_matmul_leg),
+                          ("scheduler_group", scheduler_group_leg)):
             try:
                 extra[name] = leg(ctx, comm, lib, host, world, args)
             except Exception as e:  # a side leg must not take the headline down with it
@@ -424,6 +425,75 @@ def normal_equations_full_leg(ctx, comm, lib, host, world, args) -> dict:
             "beta_checksum": float(beta.sum())}
 
 
+def scheduler_group_leg(ctx, comm, lib, host, world, args) -> dict:
+    """The scheduler that splits row blocks over the GPUs INSIDE one process (db2_vectorizedPipelineGroup: one host
+    thread and one context per device, partials combined with NCCL or peer copies): the column standardisation
+    workload on 16,777,216 x 32 f64 in TOTAL (strong scaling), through db2w_standardise_group with native pipeline
+    bodies.  Run by rank 0 alone over as many GPUs as the launch has ranks (all visible ones without a launcher); the
+    other ranks wait on the host.  `first_ms` includes every device fetching its row block from pinned host memory
+    (all uploads overlap); `ms_per_step` is with the blocks resident."""
+    import daphne_b200.kernels as K
+    from daphne_b200.lib import check, device_count
+    store = None
+    if world > 1:
+        import torch.distributed as dist
+        store = dist.distributed_c10d._get_default_store()
+        if comm.rank != 0:
+            store.wait(["db2_scheduler_group_leg"])
+            return {}
+    rows_total, cols = (ROWS_PER_GPU, COLS) if args.rows >= ROWS_PER_GPU else (max(args.rows, 1 << 16), COLS)
+    x = host.reshape(-1)[: rows_total * cols].reshape(rows_total, cols)
+    make_input(rows_total, cols, SEED, x)
+    ndev = world if world > 1 else device_count()
+    out = {}
+    try:
+        grp = K.Group(list(range(ndev)))
+        X = K.DistMatrix.from_numpy(grp, x)
+        hs = [C.c_void_p() for _ in range(6)]
+
+        def step():
+            for h in hs:
+                if h.value:
+                    lib.db2_dist_decref(h)
+                    h.value = None
+            check(lib.db2w_standardise_group(grp.handle, X.handle, *[C.byref(h) for h in hs]))
+            grp.sync()
+        t0 = time.perf_counter()
+        step()
+        first_ms = (time.perf_counter() - t0) * 1e3
+        for _ in range(3):
+            step()
+        reps, ts = 20, []
+        for _ in range(reps):
+            t0 = time.perf_counter()
+            step()
+            ts.append((time.perf_counter() - t0) * 1e3)
+        ms = float(np.median(ts))
+        s = K.DistMatrix(grp, hs[5])
+        s_val = float(s.to_numpy()[0, 0])
+        s._h = C.c_void_p()  # (released with the others below)
+        peak, kind = measured_peaks()
+        out = {"workload": f"column standardisation + aggregation on f64 {rows_total} x {cols} in total, rows split "
+                           f"over {ndev} GPU(s) by the scheduler of ONE process",
+               "scaling": "strong", "devices": ndev, "combine": "nccl" if grp.uses_nccl else "peer copies + fold",
+               "ms_per_step": ms, "rows_per_s": rows_total / (ms * 1e-3), "first_ms": first_ms,
+               "first_rows_per_s": rows_total / (first_ms * 1e-3),
+               "hbm_gbs_all_devices": rows_total * PIPELINE_MIN_BYTES_PER_ROW / (ms * 1e-3) / 1e9,
+               "hbm_frac_of_" + kind + "_all_devices":
+                   rows_total * PIPELINE_MIN_BYTES_PER_ROW / (ms * 1e-3) / 1e9 / (peak * ndev),
+               "timing": "wall clock around the call and a synchronisation of every device, median of 20",
+               "checksum_s": s_val}
+        for h in hs:
+            if h.value:
+                lib.db2_dist_decref(h)
+        X.free()
+        grp.close()
+    finally:
+        if store is not None:
+            store.set("db2_scheduler_group_leg", "1")
+    return out
+
+
 LEGS = {}
 
 
@@ -479,11 +549,13 @@ def kmeans_leg(ctx, comm, lib, host, world, args) -> dict:
     import daphne_b200.kernels as K
     from daphne_b200 import pipelines
     n, d, k, iters = (1_000_000, 64, 50, 10) if args.rows >= ROWS_PER_GPU else (max(args.rows // 16, 4096), 64, 50, 10)
-    x = host.reshape(-1)[: n * d].reshape(n, d)
-    x[:] = np.random.default_rng(3 + comm.rank).random((n, d))
-    c0 = np.random.default_rng(3).random((n, d))[np.random.default_rng(33).choice(n, k, replace=False)].copy()
-    X, C0 = K.DenseMatrix.from_numpy(ctx, x), K.DenseMatrix.from_numpy(ctx, c0)
-    X.device_ptr()
+    # X = rand(n, d, 0.0, 1.0, 1, seed) as the DaphneDSL script would produce it (the reference's mt19937 stream),
+    # generated straight into the device placement; the initial centroids are 50 rows of rank 0's block
+    X = K.randMatrix(ctx, n, d, 0.0, 1.0, 1.0, 3 + comm.rank)
+    picks = np.sort(np.random.default_rng(33).choice(n, k, replace=False))
+    x0 = K.randMatrix(ctx, n, d, 0.0, 1.0, 1.0, 3).to_numpy() if comm.rank != 0 else X.to_numpy()
+    C0 = K.DenseMatrix.from_numpy(ctx, np.ascontiguousarray(x0[picks]))
+    del x0
     ms, res = _timed(lib, ctx, comm, lambda: pipelines.kmeans_native(ctx, X, C0, iters), 3)
     per_iter = ms / iters
     peak, kind = measured_peaks()
@@ -555,7 +627,8 @@ def f32_matmul_leg(ctx, comm, lib, host, world, args) -> dict:
 
 LEGS.update({"normal_equations_shard": normal_equations_leg, "normal_equations_full": normal_equations_full_leg,
              "kmeans_shard": kmeans_leg,
-             "connected_components": components_leg, "f32_matmul_tcgen05": f32_matmul_leg})
+             "connected_components": components_leg, "f32_matmul_tcgen05": f32_matmul_leg,
+             "scheduler_group": scheduler_group_leg})
 
 
 def cpu_baseline(rows: int, cols: int, steps: int = 3, threads: int | None = None, X=None, budget_s: float = 1e9,
@@ -642,7 +715,7 @@ def main():
                     help="rows of the CPU run: default 4,194,304 for the cpu_baseline of the GPU arm (a bounded "
                          "sample), all rows for --impl reference")
     ap.add_argument("--leg", default=None, choices=["normal_equations_shard", "normal_equations_full", "kmeans_shard",
-                                                    "connected_components", "f32_matmul_tcgen05"],
+                                                    "connected_components", "f32_matmul_tcgen05", "scheduler_group"],
                     help="run only this side workload (profiling aid); prints its own JSON line")
     args = ap.parse_args()
     if args.cpu_rows is None:

@@ -370,6 +370,47 @@ int db2_dist_from_matrix(db2_group *g, db2_matrix *m, int replicate, db2_dist **
     DB2_API_END
 }
 
+/* a distributed matrix from one matrix per device (shards[i] lives on device i; references are taken): row blocks
+ * (axis 0), column blocks (axis 1) or copies of one matrix (axis -1) */
+int db2_dist_from_shards(db2_group *g, db2_matrix **shards, int axis, db2_dist **out) {
+    DB2_API_BEGIN
+    DB2_CHECK(g && shards && out, DB2_EINVAL, "null argument");
+    DB2_CHECK(axis >= -1 && axis <= 1, DB2_EINVAL, "axis must be -1, 0 or 1");
+    const int n = (int)g->ctxs.size();
+    int64_t rows = 0, cols = 0;
+    for (int i = 0; i < n; i++) {
+        DB2_CHECK(shards[i] && shards[i]->ctx == g->ctxs[i], DB2_EINVAL,
+                  "shard %d does not live on device index %d of the group", i, i);
+        DB2_CHECK(shards[i]->dtype == shards[0]->dtype, DB2_EINVAL, "shards of different value types");
+        if (axis == 0) {
+            DB2_CHECK(shards[i]->cols == shards[0]->cols, DB2_EINVAL, "row blocks of different widths");
+            rows += shards[i]->rows;
+            cols = shards[0]->cols;
+        } else if (axis == 1) {
+            DB2_CHECK(shards[i]->rows == shards[0]->rows, DB2_EINVAL, "column blocks of different heights");
+            cols += shards[i]->cols;
+            rows = shards[0]->rows;
+        } else {
+            DB2_CHECK(shards[i]->rows == shards[0]->rows && shards[i]->cols == shards[0]->cols, DB2_EINVAL,
+                      "copies of different shapes");
+            rows = shards[0]->rows;
+            cols = shards[0]->cols;
+        }
+    }
+    db2_dist *d = new_dist(g, axis, shards[0]->dtype, rows, cols);
+    int64_t at = 0;
+    for (int i = 0; i < n; i++) {
+        db2_matrix_incref(shards[i]);
+        d->shard[i] = shards[i];
+        d->off[i] = at;
+        at += axis == 0 ? shards[i]->rows : (axis == 1 ? shards[i]->cols : 0);
+        d->off[i + 1] = at;
+    }
+    *out = d;
+    return DB2_OK;
+    DB2_API_END
+}
+
 int db2_dist_info(const db2_dist *d, int *dtype, int64_t *rows, int64_t *cols, int *axis) {
     DB2_CHECK(d, DB2_EINVAL, "null argument");
     if (dtype)

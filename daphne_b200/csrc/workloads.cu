@@ -7,6 +7,8 @@
 // they run row-sharded: every rank calls them on its row block and the ADD partials are combined on the device.
 #include "runtime.h"
 
+#include <vector>
+
 using namespace db2;
 
 namespace {
@@ -167,6 +169,130 @@ int db2w_normal_equations(db2_context *ctx, db2_matrix *X, db2_matrix *y, double
     *A_out = A.release();
     *b_out = xty.release();
     *beta_out = beta.release();
+    return DB2_OK;
+    DB2_API_END
+}
+
+} // extern "C"
+
+// ---- column standardisation over a device group (one process, several GPUs) ----
+namespace {
+
+struct HD { // owning handle of a distributed matrix
+    db2_dist *d = nullptr;
+    ~HD() {
+        if (d)
+            db2_dist_decref(d);
+    }
+    db2_dist *release() {
+        db2_dist *r = d;
+        d = nullptr;
+        return r;
+    }
+};
+
+// the compiled bodies (what the lowering outlines as _vect_cudaN): they release their inputs and hand over results
+void body_col_sums(db2_matrix ***outs, db2_matrix **ins, db2_context *ctx) {
+    db2_aggCol(ctx, DB2_AGG_SUM, outs[0], ins[0]);
+    db2_matrix_decref(ins[0]);
+}
+void body_sq_dev(db2_matrix ***outs, db2_matrix **ins, db2_context *ctx) {
+    H d, d2;
+    const double two = 2.0;
+    db2_ewBinaryMat(ctx, DB2_SUB, &d, ins[0], ins[1]);
+    db2_ewBinaryObjSca(ctx, DB2_POW, &d2, d, &two);
+    db2_aggCol(ctx, DB2_AGG_SUM, outs[0], d2);
+    db2_matrix_decref(ins[0]);
+    db2_matrix_decref(ins[1]);
+}
+void body_rows(db2_matrix ***outs, db2_matrix **ins, db2_context *ctx) {
+    H xc, Z, z2;
+    const double two = 2.0;
+    db2_ewBinaryMat(ctx, DB2_SUB, &xc, ins[0], ins[1]);
+    db2_ewBinaryMat(ctx, DB2_DIV, &Z, xc, ins[2]);
+    db2_ewBinaryObjSca(ctx, DB2_POW, &z2, Z, &two);
+    db2_aggRow(ctx, DB2_AGG_SUM, outs[0], z2);
+    db2_aggRow(ctx, DB2_AGG_MAX, outs[1], Z);
+    db2_aggRow(ctx, DB2_AGG_IDXMAX, outs[2], Z);
+    db2_aggCol(ctx, DB2_AGG_SUM, outs[3], *outs[0]);
+    for (int i = 0; i < 3; i++)
+        db2_matrix_decref(ins[i]);
+}
+
+// out = f(in) on every device of the group (small replicated follow-up arithmetic between two pipelines)
+template <typename F> int on_every_device(db2_group *g, db2_dist *in, db2_dist **out, F &&f) {
+    int n = 0;
+    DB2_TRY(db2_group_size(g, &n));
+    std::vector<db2_matrix *> res(n, nullptr);
+    int rc = DB2_OK;
+    for (int d = 0; d < n && rc == DB2_OK; d++) {
+        db2_context *c = nullptr;
+        db2_matrix *shard = nullptr;
+        rc = db2_group_context(g, d, &c);
+        if (rc == DB2_OK)
+            rc = db2_dist_shard(in, d, &shard, nullptr);
+        if (rc == DB2_OK) {
+            bind_device(c);
+            rc = f(c, shard, &res[d]);
+        }
+    }
+    if (rc == DB2_OK)
+        rc = db2_dist_from_shards(g, res.data(), -1, out);
+    for (db2_matrix *m : res)
+        if (m) {
+            bind_device(m->ctx);
+            db2_matrix_decref(m);
+        }
+    return rc;
+}
+
+} // namespace
+
+extern "C" {
+
+int db2w_standardise_group(db2_group *g, db2_dist *X, db2_dist **mu_out, db2_dist **sd_out, db2_dist **r_out,
+                           db2_dist **max_out, db2_dist **idx_out, db2_dist **s_out) {
+    DB2_API_BEGIN
+    DB2_CHECK(g && X && mu_out && sd_out && r_out && max_out && idx_out && s_out, DB2_EINVAL, "null argument");
+    int64_t rows = 0;
+    DB2_TRY(db2_dist_info(X, nullptr, &rows, nullptr, nullptr));
+    const double n = (double)rows;
+    const int64_t rows_split = DB2_SPLIT_ROWS, none = DB2_SPLIT_NONE;
+    HD sums, mu, v, sd;
+    {
+        db2_dist *ins[1] = {X};
+        const int64_t splits[1] = {rows_split}, combines[1] = {DB2_COMBINE_ADD};
+        DB2_TRY(db2_vectorizedPipelineGroup(g, &sums.d, 1, nullptr, ins, 1, nullptr, nullptr, splits, combines,
+                                            body_col_sums, 0));
+    }
+    DB2_TRY(on_every_device(g, sums.d, &mu.d, [&](db2_context *c, db2_matrix *m, db2_matrix **o) {
+        return db2_ewBinaryObjSca(c, DB2_DIV, o, m, &n);
+    }));
+    {
+        db2_dist *ins[2] = {X, mu.d};
+        const int64_t splits[2] = {rows_split, none}, combines[1] = {DB2_COMBINE_ADD};
+        DB2_TRY(db2_vectorizedPipelineGroup(g, &v.d, 1, nullptr, ins, 2, nullptr, nullptr, splits, combines, body_sq_dev,
+                                            0));
+    }
+    DB2_TRY(on_every_device(g, v.d, &sd.d, [&](db2_context *c, db2_matrix *m, db2_matrix **o) {
+        H var;
+        DB2_TRY(db2_ewBinaryObjSca(c, DB2_DIV, &var, m, &n));
+        return db2_ewUnaryMat(c, DB2_U_SQRT, o, var);
+    }));
+    db2_dist *outs[4] = {nullptr, nullptr, nullptr, nullptr};
+    {
+        db2_dist *ins[3] = {X, mu.d, sd.d};
+        const int64_t splits[3] = {rows_split, none, none};
+        const int64_t combines[4] = {DB2_COMBINE_ROWS, DB2_COMBINE_ROWS, DB2_COMBINE_ROWS, DB2_COMBINE_ADD};
+        DB2_TRY(db2_vectorizedPipelineGroup(g, outs, 4, nullptr, ins, 3, nullptr, nullptr, splits, combines, body_rows,
+                                            0));
+    }
+    *mu_out = mu.release();
+    *sd_out = sd.release();
+    *r_out = outs[0];
+    *max_out = outs[1];
+    *idx_out = outs[2];
+    *s_out = outs[3];
     return DB2_OK;
     DB2_API_END
 }

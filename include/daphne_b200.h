@@ -426,6 +426,8 @@ typedef struct db2_dist db2_dist;
 int db2_dist_from_host(db2_group *g, int dtype, int64_t rows, int64_t cols, int64_t ld, void *host, db2_dist **out);
 /* row blocks (replicate == 0) or full copies (replicate != 0) of a matrix of any context of this process */
 int db2_dist_from_matrix(db2_group *g, db2_matrix *m, int replicate, db2_dist **out);
+/* from one matrix per device (shards[i] on device i; references are taken): axis 0 / 1 / -1 as above */
+int db2_dist_from_shards(db2_group *g, db2_matrix **shards, int axis, db2_dist **out);
 int db2_dist_info(const db2_dist *d, int *dtype, int64_t *rows, int64_t *cols, int *axis);
 /* the block held by device `index` (borrowed handle) and its first row / column */
 int db2_dist_shard(db2_dist *d, int index, db2_matrix **shard, int64_t *offset);
@@ -513,6 +515,14 @@ int db2w_kmeans(db2_context *ctx, db2_matrix *X, db2_matrix *C0, int iterations,
 /* lmDS (scripts/algorithms/lmDS_.daph:98-112): A = t(X) @ X + lambda I (syrk), b = t(X) @ y (gemv), beta = solve(A, b) */
 int db2w_normal_equations(db2_context *ctx, db2_matrix *X, db2_matrix *y, double lambda, db2_matrix **A,
                           db2_matrix **b, db2_matrix **beta);
+/* Column standardisation and aggregation over the devices of a group, in ONE process: three pipelines through
+ * db2_vectorizedPipelineGroup (column sums: ADD; squared deviations from the global mean: ADD; the row results: ROWS,
+ * and their sum: ADD) with compiled bodies that issue the operator calls of
+ *   mu = mean(X, 1); sd = sqrt(var(X, 1)); Z = (X - mu) / sd; r = sum(Z ^ 2, 0); s = sum(r); m = aggMax(Z, 0);
+ *   i = idxMax(Z, 0);
+ * X: distributed by rows.  mu, sd, s come back replicated, r, row_max, row_idx_max distributed by rows. */
+int db2w_standardise_group(db2_group *g, db2_dist *X, db2_dist **mu, db2_dist **sd, db2_dist **r, db2_dist **row_max,
+                           db2_dist **row_idx_max, db2_dist **s);
 
 #ifdef __cplusplus
 }
