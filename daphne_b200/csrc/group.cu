@@ -18,7 +18,9 @@
 //     elementwise kernel, which gives bit-identical results on all devices.  No multicast loads of any kind.
 #include "runtime.h"
 
+#include <condition_variable>
 #include <cstdlib>
+#include <functional>
 #include <string>
 #include <thread>
 
@@ -31,6 +33,17 @@ struct db2_group {
     bool distinct = true; // every context on its own physical device
     bool nccl = false;    // the contexts hold communicators made by ncclCommInitAll
     std::atomic<int> refs{1};
+    // one host thread per device, like the reference's WorkerGPU per CUDA context (vectorized/MTWrapper.h:93-98), kept
+    // for the lifetime of the group: a pipeline hands them its per-device task and waits (creating threads per
+    // pipeline cost more than the kernels of a small one)
+    std::vector<std::thread> workers;
+    std::mutex mu;
+    std::condition_variable cv_work, cv_done;
+    std::function<void(int)> task;
+    uint64_t generation = 0;
+    int running = 0;
+    bool stop = false;
+    std::mutex call_mu; // one pipeline at a time per group
 };
 
 struct db2_dist {
@@ -51,9 +64,38 @@ void block_of(int64_t n, int r, int world, int64_t *lo, int64_t *hi) {
     *hi = *lo + base + (r < extra ? 1 : 0);
 }
 
+void worker_loop(db2_group *g, int d) {
+    bind_device(g->ctxs[d]);
+    uint64_t seen = 0;
+    for (;;) {
+        std::function<void(int)> f;
+        {
+            std::unique_lock<std::mutex> lock(g->mu);
+            g->cv_work.wait(lock, [&] { return g->stop || g->generation != seen; });
+            if (g->stop)
+                return;
+            seen = g->generation;
+            f = g->task;
+        }
+        f(d);
+        {
+            std::lock_guard<std::mutex> lock(g->mu);
+            if (--g->running == 0)
+                g->cv_done.notify_all();
+        }
+    }
+}
+
 void group_release(db2_group *g) {
     if (g->refs.fetch_sub(1) != 1)
         return;
+    {
+        std::lock_guard<std::mutex> lock(g->mu);
+        g->stop = true;
+    }
+    g->cv_work.notify_all();
+    for (auto &w : g->workers)
+        w.join();
     if (g->nccl)
         nccl_destroy_group(g->ctxs);
     for (db2_context *c : g->ctxs)
@@ -89,11 +131,17 @@ template <typename F> int for_each_device(db2_group *g, F &&f) {
     if (n == 1) {
         run(0);
     } else {
-        std::vector<std::thread> th;
-        for (int d = 0; d < n; d++)
-            th.emplace_back(run, d);
-        for (auto &t : th)
-            t.join();
+        std::lock_guard<std::mutex> one(g->call_mu);
+        std::unique_lock<std::mutex> lock(g->mu);
+        if (g->workers.empty())
+            for (int d = 0; d < n; d++)
+                g->workers.emplace_back(worker_loop, g, d);
+        g->task = run;
+        g->running = n;
+        g->generation++;
+        g->cv_work.notify_all();
+        g->cv_done.wait(lock, [&] { return g->running == 0; });
+        g->task = nullptr;
     }
     for (int d = 0; d < n; d++)
         if (rc[d] != DB2_OK)

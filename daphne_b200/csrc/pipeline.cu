@@ -61,9 +61,15 @@ extern "C" int db2_vectorizedPipeline(db2_context *ctx, db2_matrix **outputs, si
             row_mem += (size_t)outCols[o] * 8;
     }
     if (batch_rows <= 0) {
-        size_t free_b = 0, total_b = 0;
-        DB2_CUDA(cudaMemGetInfo(&free_b, &total_b));
-        const size_t budget = (free_b + ctx->cached_bytes) / 4;
+        // the free-memory query is a slow driver call: its answer is remembered per context and only refreshed when a
+        // pipeline's footprint comes near the remembered budget
+        const size_t need = row_mem * (size_t)(len > 0 ? len : 1);
+        if (ctx->mem_free_seen == 0 || need > ctx->mem_free_seen / 8) {
+            size_t free_b = 0, total_b = 0;
+            DB2_CUDA(cudaMemGetInfo(&free_b, &total_b));
+            ctx->mem_free_seen = free_b + ctx->cached_bytes;
+        }
+        const size_t budget = ctx->mem_free_seen / 4;
         batch_rows = row_mem ? (int64_t)(budget / row_mem) : len;
         if (batch_rows < 1024)
             batch_rows = 1024;

@@ -32,6 +32,7 @@ struct db2_context {
     std::multimap<size_t, void *> free_blocks;
     std::unordered_map<void *, size_t> block_size;
     size_t cached_bytes = 0;
+    size_t mem_free_seen = 0; // free device memory at the last query (pipeline.cu sizes its batches from it)
     size_t mem_budget = 0; // > 0: pooled allocations may hold at most this many bytes (db2_context_set_mem_budget)
     // reusable scratch for two-stage reductions (grown on demand, stream-ordered reuse)
     void *scratch = nullptr;
