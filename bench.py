@@ -592,12 +592,21 @@ def components_leg(ctx, comm, lib, host, world, args) -> dict:
     per_iter = ms / res.iterations
     labels = res.c.to_numpy().ravel()
     peak, kind = measured_peaks()
+    # the labels of all shards against scipy's connected components of the same graph: every vertex must carry the
+    # largest (1-based) vertex id of its component, so the sums over all vertices must be equal
+    total = float(comm.allreduce_numpy(np.array([labels.sum()]), 3)[0]) if world > 1 else float(labels.sum())
+    from scipy.sparse import csgraph
+    ncomp, comp = csgraph.connected_components(g, directed=False)
+    top = np.zeros(ncomp)
+    np.maximum.at(top, comp, np.arange(1, n + 1, dtype=np.float64))
+    expected = float(top[comp].sum())
     return {"workload": f"connected components, {n} vertices, {2 * key.size} stored entries, rows over {world} GPU(s)",
             "iterations": res.iterations, "ms_per_iteration": per_iter, "ms_total": ms,
             "vertices_per_s": n * res.iterations / (ms * 1e-3),
             "gbs_at_160B_per_vertex": n * 160 / (per_iter * 1e-3) / 1e9,
             "frac_of_" + kind + "_hbm": n * 160 / (per_iter * 1e-3) / 1e9 / peak,
-            "components_in_shard": int(np.unique(labels).size), "label_checksum": float(labels.sum())}
+            "components": int(ncomp), "label_checksum_all_ranks": total, "label_checksum_scipy": expected,
+            "labels_equal_scipy": bool(total == expected and np.array_equal(labels, top[comp][r0:r1]))}
 
 
 def f32_matmul_leg(ctx, comm, lib, host, world, args) -> dict:
