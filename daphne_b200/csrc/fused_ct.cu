@@ -148,13 +148,22 @@ struct AnyTaps {
     static constexpr int n = FUSED_MAX_AGGS;
 };
 
-template <int G>
-__device__ __forceinline__ void apply_step_rt(int op, bool rev, double (&v)[G], const double (&o)[G]) {
+// applies one step to the elements [OFF, OFF + G) of v (compile-time positions: v stays in registers)
+template <int G, int OFF = 0, int N = G>
+__device__ __forceinline__ void apply_step_rt(int op, bool rev, double (&v)[N], const double (&o)[G]) {
 #define DB2_CT_STEP(FWD, REV)                                                                                          \
     if (!rev) {                                                                                                        \
-        _Pragma("unroll") for (int i = 0; i < G; i++) { const double a = v[i], b = o[i]; (void)b; v[i] = (FWD); }      \
+        _Pragma("unroll") for (int i = 0; i < G; i++) {                                                                \
+            const double a = v[OFF + i], b = o[i];                                                                     \
+            (void)b;                                                                                                   \
+            v[OFF + i] = (FWD);                                                                                        \
+        }                                                                                                              \
     } else {                                                                                                           \
-        _Pragma("unroll") for (int i = 0; i < G; i++) { const double a = v[i], b = o[i]; (void)b; v[i] = (REV); }      \
+        _Pragma("unroll") for (int i = 0; i < G; i++) {                                                                \
+            const double a = v[OFF + i], b = o[i];                                                                     \
+            (void)b;                                                                                                   \
+            v[OFF + i] = (REV);                                                                                        \
+        }                                                                                                              \
     }                                                                                                                  \
     break;
     switch (op) {
@@ -544,8 +553,162 @@ __device__ __forceinline__ void walk_row(unsigned walk0, const FusedProgram &P, 
     }
 }
 
+// ---- run-time chains: one lane walks its row of a chunk STEP BY STEP ----
+// All CK elements of the row's chunk stay in registers while the steps are applied one after the other, so a step's
+// description (operand kind, opcode, operand address, tap mask) is read and decoded once per CK elements; evaluating
+// group after group (as the compiled chains do, where the description costs nothing) spent most instructions on that
+// decoding.  Order of the arithmetic and of the taps per element is unchanged.
+template <bool FULL>
+__device__ __forceinline__ void feed_chunk_rt(TapState<AnyTaps> &ts, const FusedProgram &P, unsigned mask,
+                                              const double (&v)[CK], int cc, int cw) {
+    if (mask == 0)
+        return;
+#pragma unroll
+    for (int a = 0; a < FUSED_MAX_AGGS; a++) {
+        if (mask & (1u << a)) {
+            const int kind = P.taps[a].kind;
+            if (kind == FT_SUM || kind == FT_MEAN) {
+                double acc = ts.v[a];
+#pragma unroll
+                for (int i = 0; i < CK; i++)
+                    if (FULL || i < cw)
+                        acc = __dadd_rn(acc, v[i]);
+                ts.v[a] = acc;
+            } else if (kind == FT_PROD) {
+                double acc = ts.v[a];
+#pragma unroll
+                for (int i = 0; i < CK; i++)
+                    if (FULL || i < cw)
+                        acc = __dmul_rn(acc, v[i]);
+                ts.v[a] = acc;
+            } else {
+                if (cc == 0)
+                    ts.first[a] = v[0];
+                const bool mx = kind == FT_MAX;
+                double best = ts.v[a];
+                int bc = ts.c[a];
+#pragma unroll
+                for (int i = 0; i < CK; i++) {
+                    const bool better = (FULL || i < cw) && (mx ? (v[i] > best) : (v[i] < best));
+                    if (better) {
+                        best = v[i];
+                        bc = cc + i;
+                    }
+                }
+                ts.v[a] = best;
+                ts.c[a] = bc;
+            }
+        }
+    }
+}
+
+// one step on the groups G0, G0 + 1, ... of a chunk held in registers
+template <bool FULL, int G0>
+__device__ __forceinline__ void step_groups_rt(double (&v)[CK], int kind, int op, bool rev, bool fwd_div,
+                                               const double *ovec, const double *omat, double oscal, double yscal,
+                                               int64_t cols, int cw) {
+    if constexpr (G0 < CK / GR) {
+        constexpr int OFF = G0 * GR;
+        if (FULL || OFF < cw) {
+            double o[GR];
+            if (kind == FK_ROWVEC) {
+#pragma unroll
+                for (int i = 0; i < GR / 2; i++) {
+                    const double2 t = reinterpret_cast<const double2 *>(ovec + OFF)[i];
+                    o[2 * i] = t.x;
+                    o[2 * i + 1] = t.y;
+                }
+            } else if (kind == FK_MATRIX) {
+#pragma unroll
+                for (int i = 0; i < GR; i++)
+                    o[i] = (FULL || OFF + i < cw) ? __ldg(omat + OFF + i) : 0.0;
+            } else {
+#pragma unroll
+                for (int i = 0; i < GR; i++)
+                    o[i] = oscal;
+            }
+            if (fwd_div) {
+                double y[GR];
+                if (kind == FK_ROWVEC) {
+#pragma unroll
+                    for (int i = 0; i < GR / 2; i++) {
+                        const double2 u = reinterpret_cast<const double2 *>(ovec + cols + OFF)[i];
+                        y[2 * i] = u.x;
+                        y[2 * i + 1] = u.y;
+                    }
+                } else {
+#pragma unroll
+                    for (int i = 0; i < GR; i++)
+                        y[i] = yscal;
+                }
+                double q1[GR];
+                unsigned worst = 0;
+#pragma unroll
+                for (int i = 0; i < GR; i++) {
+                    const double q = __dmul_rn(v[OFF + i], y[i]);
+                    const double r = __fma_rn(-q, o[i], v[OFF + i]);
+                    q1[i] = __fma_rn(r, y[i], q);
+                    worst = max(worst, fast_div_window_pos(q1[i]));
+                }
+                if (worst < FAST_DIV_WINDOW) {
+#pragma unroll
+                    for (int i = 0; i < GR; i++)
+                        v[OFF + i] = q1[i];
+                } else {
+#pragma unroll
+                    for (int i = 0; i < GR; i++)
+                        v[OFF + i] = fast_div(v[OFF + i], o[i], y[i]);
+                }
+            } else {
+                apply_step_rt<GR, OFF, CK>(op, rev, v, o);
+            }
+        }
+        step_groups_rt<FULL, G0 + 1>(v, kind, op, rev, fwd_div, ovec, omat, oscal, yscal, cols, cw);
+    }
+}
+
+template <bool EW, bool FULL>
+__device__ __forceinline__ void walk_row_rt(unsigned walk0, const FusedProgram &P, TapState<AnyTaps> &ts,
+                                            const double *rvs, int64_t row, int64_t cc, int cw) {
+    static_assert(CK % GR == 0, "a chunk is a whole number of groups");
+    double v[CK];
+#pragma unroll
+    for (int j = 0; j < CK / 2; j++) {
+        const double2 xy = lds128(walk0 ^ (unsigned)(j << 4)); // beyond cw: padding that no tap and no store sees
+        v[2 * j] = xy.x;
+        v[2 * j + 1] = xy.y;
+    }
+    const unsigned *masks = reinterpret_cast<const unsigned *>(rvs + P.smem_elems + FUSED_MAX_STEPS);
+    feed_chunk_rt<FULL>(ts, P, masks[0], v, (int)cc, cw);
+#pragma unroll 1
+    for (int s = 0; s < P.nsteps; s++) {
+        const FusedStep &fs = P.steps[s];
+        const int kind = fs.kind, op = fs.op;
+        const bool rev = fs.reversed != 0;
+        const bool fwd_div = op == FO_DIV && !rev;
+        const double *ovec = kind == FK_ROWVEC ? rvs + fs.smem_off + cc : nullptr;
+        const double *omat = kind == FK_MATRIX ? static_cast<const double *>(fs.ptr) + row * fs.ld + cc : nullptr;
+        double oscal = fs.imm; // SCALAR (or unused: UNARY)
+        if (kind == FK_COLVEC)
+            oscal = __ldg(static_cast<const double *>(fs.ptr) + row * fs.ld);
+        // division helper of a SCALAR operand; anything that is not staged: NaN = generic division
+        const double yscal = kind == FK_SCALAR ? rvs[P.smem_elems + s] : __longlong_as_double(0x7ff8000000000000ll);
+        step_groups_rt<FULL, 0>(v, kind, op, rev, fwd_div, ovec, omat, oscal, yscal, P.cols, cw);
+        feed_chunk_rt<FULL>(ts, P, masks[s + 1], v, (int)cc, cw);
+    }
+    if constexpr (EW) {
+#pragma unroll
+        for (int j = 0; j < CK / 2; j++)
+            if (FULL || 2 * j < cw)
+                sts128(walk0 ^ (unsigned)(j << 4), v[2 * j], v[2 * j + 1]);
+    }
+}
+
+// resident CTAs per SM: a run-time chain holds a whole chunk row in registers and gets the larger register budget
+template <typename ChainT> constexpr int row_ctas_per_sm() { return std::is_same<ChainT, AnyChain>::value ? 3 : 3; }
+
 template <typename ChainT, typename TapsT, bool EW>
-__global__ void __launch_bounds__(RT, 3) fused_row_ct_kernel(const __grid_constant__ FusedProgram P) {
+__global__ void __launch_bounds__(RT, row_ctas_per_sm<ChainT>()) fused_row_ct_kernel(const __grid_constant__ FusedProgram P) {
     extern __shared__ __align__(16) double smem_raw[];
     // the chunk buffers start on a 256-byte boundary (the launch reserves the slack)
     const unsigned raw_s = (unsigned)__cvta_generic_to_shared(smem_raw);
@@ -637,10 +800,17 @@ __global__ void __launch_bounds__(RT, 3) fused_row_ct_kernel(const __grid_consta
             if (live)
                 load_colvec_aux<ChainT>(cs, P, row);
         }
-        if (rows_here == WR && cw == CK)
-            walk_row<ChainT, TapsT, EW, true>(tile_s + walk_off, P, cs, ts, rvs, row, cc, cw);
-        else if (live)
-            walk_row<ChainT, TapsT, EW, false>(tile_s + walk_off, P, cs, ts, rvs, row, cc, cw);
+        if constexpr (std::is_same<ChainT, AnyChain>::value) {
+            if (rows_here == WR && cw == CK)
+                walk_row_rt<EW, true>(tile_s + walk_off, P, ts, rvs, row, cc, cw);
+            else if (live)
+                walk_row_rt<EW, false>(tile_s + walk_off, P, ts, rvs, row, cc, cw);
+        } else {
+            if (rows_here == WR && cw == CK)
+                walk_row<ChainT, TapsT, EW, true>(tile_s + walk_off, P, cs, ts, rvs, row, cc, cw);
+            else if (live)
+                walk_row<ChainT, TapsT, EW, false>(tile_s + walk_off, P, cs, ts, rvs, row, cc, cw);
+        }
         if constexpr (EW) {
             __syncwarp();
             const int r0 = lane >> 4, p = lane & 15;
@@ -670,7 +840,7 @@ __global__ void __launch_bounds__(RT, 3) fused_row_ct_kernel(const __grid_consta
 template <typename ChainT, typename TapsT, bool EW> static int launch_row(const FusedProgram &prog, cudaStream_t st) {
     const size_t smem = (size_t)(WARPS * 2 * WR * CK + prog.smem_elems + 2 * FUSED_MAX_STEPS) * sizeof(double) + 256; // + run-time chain tables, alignment slack
     const int64_t nblocks = ((prog.rows + WR - 1) / WR + WARPS - 1) / WARPS;
-    const int64_t cap = (int64_t)sm_count() * 3;
+    const int64_t cap = (int64_t)sm_count() * row_ctas_per_sm<ChainT>();
     const int grid = (int)(nblocks < cap ? nblocks : cap);
     static PerDeviceOnce attr;
     if (attr.need()) {

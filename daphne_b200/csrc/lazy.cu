@@ -635,6 +635,22 @@ int lazy_try_matmul(db2_context *ctx, db2_matrix **res, db2_matrix *lhs, db2_mat
 
 // sum(chain) in one flat pass; a live deferred matrix whose chain is a proper prefix (e.g. u of sum(u != c)) is
 // materialised by the same pass
+int lazy_try_agg_all_start(db2_context *ctx, int op, double *pinned, db2_matrix *arg, bool *handled) {
+    *handled = false;
+    if (!arg->lazy || ctx->eager || op != DB2_AGG_SUM || arg->dtype != DB2_F64)
+        return DB2_OK;
+    std::shared_ptr<const Expr> e = arg->lazy;
+    if (!e->csr)
+        return DB2_OK;
+    const uint64_t before = g_launches.load();
+    DB2_TRY(run_csr_pass(ctx, *e, nullptr, pinned));
+    std::lock_guard<std::mutex> lock(ctx->mu);
+    ctx->stats.launches += g_launches.load() - before;
+    ctx->stats.d2h_bytes += sizeof(double);
+    *handled = true;
+    return DB2_OK;
+}
+
 int lazy_try_agg_all(db2_context *ctx, int op, double *res_host, db2_matrix *arg, bool *handled) {
     *handled = false;
     if (!arg->lazy || ctx->eager || op != DB2_AGG_SUM || arg->dtype != DB2_F64)

@@ -25,6 +25,9 @@ void ctx_release(db2_context *ctx) {
     release_cached(ctx);
     cudaFree(ctx->dev_status);
     cudaFreeHost(ctx->host_status);
+    for (cudaEvent_t ev : ctx->scalar_ev)
+        if (ev)
+            cudaEventDestroy(ev);
     cudaStreamDestroy(ctx->stream);
     delete ctx;
 }
@@ -693,6 +696,64 @@ int db2_aggAll(db2_context *ctx, int op, void *res_host, db2_matrix *arg) {
         std::lock_guard<std::mutex> lock(ctx->mu);
         ctx->stats.d2h_bytes += arg->esize();
     }
+    return DB2_OK;
+    DB2_API_END
+}
+
+// ---- a scalar that the host needs later: start now, wait when it is needed ----
+// The two halves of aggAll (and of reading a 1 x 1 matrix).  Between them the caller may queue more work on the
+// context, so the device does not idle while the host looks at the value: a loop whose condition is a reduction
+// (`while (sum(u != c) > 0)`) queues its next trip before it waits for the previous trip's count.  Two slots.
+static double *scalar_slot(db2_context *ctx, int slot) { return reinterpret_cast<double *>(ctx->host_status + 48) + slot; }
+
+static int scalar_mark(db2_context *ctx, int slot) {
+    if (!ctx->scalar_ev[slot])
+        DB2_CUDA(cudaEventCreateWithFlags(&ctx->scalar_ev[slot], cudaEventDisableTiming));
+    DB2_CUDA(cudaEventRecord(ctx->scalar_ev[slot], ctx->stream));
+    return DB2_OK;
+}
+
+int db2_aggAllStart(db2_context *ctx, int op, db2_matrix *arg, int slot) {
+    DB2_API_BEGIN
+    DB2_CHECK(ctx && arg, DB2_EINVAL, "null argument");
+    DB2_CHECK(slot == 0 || slot == 1, DB2_EINVAL, "scalar slot %d (0 or 1)", slot);
+    DB2_CHECK(arg->dtype == DB2_F64, DB2_EUNSUPPORTED, "aggAllStart: f64 only");
+    bind_device(ctx);
+    bool handled = false;
+    DB2_TRY(lazy_try_agg_all_start(ctx, op, scalar_slot(ctx, slot), arg, &handled));
+    if (!handled) { // any other argument: the complete call now, the value parked in the slot
+        double v = 0.0;
+        DB2_TRY(db2_aggAll(ctx, op, &v, arg));
+        *scalar_slot(ctx, slot) = v;
+    }
+    return scalar_mark(ctx, slot);
+    DB2_API_END
+}
+
+int db2_scalarStart(db2_context *ctx, db2_matrix *m, int slot) {
+    DB2_API_BEGIN
+    DB2_CHECK(ctx && m, DB2_EINVAL, "null argument");
+    DB2_CHECK(slot == 0 || slot == 1, DB2_EINVAL, "scalar slot %d (0 or 1)", slot);
+    DB2_CHECK(m->dtype == DB2_F64 && m->rows == 1 && m->cols == 1, DB2_EINVAL, "scalarStart: a 1 x 1 f64 matrix");
+    bind_device(ctx);
+    DB2_TRY(ensure_device(m));
+    DB2_CUDA(cudaMemcpyAsync(scalar_slot(ctx, slot), m->dev_ptr(), sizeof(double), cudaMemcpyDeviceToHost,
+                             ctx->stream));
+    {
+        std::lock_guard<std::mutex> lock(ctx->mu);
+        ctx->stats.d2h_bytes += sizeof(double);
+    }
+    return scalar_mark(ctx, slot);
+    DB2_API_END
+}
+
+int db2_scalarWait(db2_context *ctx, int slot, double *res) {
+    DB2_API_BEGIN
+    DB2_CHECK(ctx && res, DB2_EINVAL, "null argument");
+    DB2_CHECK((slot == 0 || slot == 1) && ctx->scalar_ev[slot], DB2_EINVAL, "scalar slot %d was not started", slot);
+    bind_device(ctx);
+    DB2_CUDA(cudaEventSynchronize(ctx->scalar_ev[slot]));
+    *res = *scalar_slot(ctx, slot);
     return DB2_OK;
     DB2_API_END
 }

@@ -40,6 +40,8 @@ struct db2_context {
     // device status word for domain errors + pinned host mirror
     int32_t *dev_status = nullptr;
     int32_t *host_status = nullptr;
+    // db2_aggAllStart / db2_scalarStart: one event per outstanding scalar (the values sit in host_status)
+    cudaEvent_t scalar_ev[2] = {nullptr, nullptr};
     // cross-GPU combine (comm.cu): this context's rank among `world` row shards and its NCCL communicator
     int rank = 0, world = 1;
     void *comm = nullptr;
@@ -231,6 +233,8 @@ int lazy_try_matmul(db2_context *ctx, db2_matrix **res, db2_matrix *lhs, db2_mat
                     bool *handled);
 // full aggregation of a deferred chain without materialising it (SUM of flat-evaluable chains); *res_host gets the value
 int lazy_try_agg_all(db2_context *ctx, int op, double *res_host, db2_matrix *arg, bool *handled);
+// the same without the wait: the sum is written to `pinned` (pinned host memory) by the pass that this call queues
+int lazy_try_agg_all_start(db2_context *ctx, int op, double *pinned, db2_matrix *arg, bool *handled);
 int lazy_force(db2_matrix *m);          // materialises a deferred matrix (and the pending siblings it can serve)
 int lazy_flush_all(db2_context *ctx);   // produces every pending aggregation
 void lazy_forget(db2_matrix *m);        // a deferred matrix is being destroyed

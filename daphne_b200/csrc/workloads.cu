@@ -53,6 +53,11 @@ extern "C" {
 //   c = seq(1, n, 1); while (diff > 0 && iter <= maxi) { u = max(aggMax(G * t(c), 0), c); diff = sum(u != c); c = u; }
 // G holds the rows [row_lo, row_lo + G.rows) of the n x n adjacency matrix.  Sharded: the change count is combined on
 // the device and the label blocks are all-gathered behind it on the same stream; one value is read per iteration.
+//
+// The loop condition needs the count of trip k on the host.  Trip k + 1 is queued BEFORE that count is awaited, so
+// the device works on it while the value travels and the host prepares the calls.  Should trip k turn out to have
+// changed nothing, the script would have stopped there: the labels after trip k are returned and trip k + 1 (which
+// reproduces them: c is a fixpoint) is dropped.  Labels and the iteration count are those of the script's loop.
 int db2w_connected_components(db2_context *ctx, db2_csr *G, int64_t row_lo, int64_t maxi, db2_matrix **labels,
                               int64_t *iterations) {
     DB2_API_BEGIN
@@ -60,39 +65,50 @@ int db2w_connected_components(db2_context *ctx, db2_csr *G, int64_t row_lo, int6
     int64_t rows = 0, n = 0;
     DB2_TRY(db2_csr_info(G, &rows, &n, nullptr));
     const bool sharded = ctx->world > 1;
-    H c_full, c_loc;
+    H c_full, c_loc; // the labels after trip it - 1
     const double one = 1.0, last = (double)n;
     DB2_TRY(db2_seq(ctx, &c_full, DB2_F64, &one, &last, &one));
     DB2_TRY(db2_matrix_slice_rows(c_full, row_lo, row_lo + rows, &c_loc));
-    double diff = 1.0;
     int64_t it = 1;
-    while (diff > 0.0 && it <= maxi) {
-        H tc, mx, u, ne;
-        HC prod;
-        DB2_TRY(db2_transpose(ctx, &tc, c_full));
-        DB2_TRY(db2_ewMulCsrDense(ctx, &prod.m, G, tc));
-        DB2_TRY(db2_aggRowCsr(ctx, DB2_AGG_MAX, &mx, prod.m));
-        DB2_TRY(db2_ewBinaryMat(ctx, DB2_MAX, &u, mx, c_loc));
-        DB2_TRY(db2_ewBinaryMat(ctx, DB2_NEQ, &ne, u, c_loc));
-        if (sharded) {
-            H cnt, gathered;
-            DB2_TRY(db2_aggCol(ctx, DB2_AGG_SUM, &cnt, ne));
-            DB2_TRY(db2_comm_group_begin(ctx)); // the count and the labels travel in one NCCL launch
-            int rc = db2_allreduce(ctx, cnt, DB2_COMBINE_ADD);
-            if (rc == DB2_OK)
-                rc = db2_allgatherv_rows(ctx, u, n, &gathered);
-            const int rc_end = db2_comm_group_end(ctx);
-            DB2_TRY(rc != DB2_OK ? rc : rc_end);
-            DB2_TRY(db2_matrix_to_host(cnt, &diff, 1));
-            c_full.reset(gathered.release());
-            c_loc.reset();
-            DB2_TRY(db2_matrix_slice_rows(c_full, row_lo, row_lo + rows, &c_loc));
-        } else {
-            DB2_TRY(db2_aggAll(ctx, DB2_AGG_SUM, &diff, ne));
-            db2_matrix_incref(u);
-            c_loc.reset(u);
-            c_full.reset(u.release());
+    for (;;) {
+        const bool queue = it <= maxi;
+        H n_full, n_loc; // the labels after trip it
+        if (queue) {
+            H tc, mx, u, ne;
+            HC prod;
+            DB2_TRY(db2_transpose(ctx, &tc, c_full));
+            DB2_TRY(db2_ewMulCsrDense(ctx, &prod.m, G, tc));
+            DB2_TRY(db2_aggRowCsr(ctx, DB2_AGG_MAX, &mx, prod.m));
+            DB2_TRY(db2_ewBinaryMat(ctx, DB2_MAX, &u, mx, c_loc));
+            DB2_TRY(db2_ewBinaryMat(ctx, DB2_NEQ, &ne, u, c_loc));
+            if (sharded) {
+                H cnt;
+                DB2_TRY(db2_aggCol(ctx, DB2_AGG_SUM, &cnt, ne));
+                DB2_TRY(db2_comm_group_begin(ctx)); // the count and the labels travel in one NCCL launch
+                int rc = db2_allreduce(ctx, cnt, DB2_COMBINE_ADD);
+                if (rc == DB2_OK)
+                    rc = db2_allgatherv_rows(ctx, u, n, &n_full);
+                const int rc_end = db2_comm_group_end(ctx);
+                DB2_TRY(rc != DB2_OK ? rc : rc_end);
+                DB2_TRY(db2_scalarStart(ctx, cnt, (int)(it & 1)));
+                DB2_TRY(db2_matrix_slice_rows(n_full, row_lo, row_lo + rows, &n_loc));
+            } else {
+                DB2_TRY(db2_aggAllStart(ctx, DB2_AGG_SUM, ne, (int)(it & 1)));
+                db2_matrix_incref(u);
+                n_loc.reset(u);
+                n_full.reset(u.release());
+            }
         }
+        if (it > 1) {
+            double diff = 0.0;
+            DB2_TRY(db2_scalarWait(ctx, (int)((it - 1) & 1), &diff));
+            if (!(diff > 0.0) || !queue)
+                break; // trip it - 1 was the script's last
+        } else if (!queue) {
+            break;
+        }
+        c_full.reset(n_full.release());
+        c_loc.reset(n_loc.release());
         it++;
     }
     *iterations = it - 1;

@@ -207,6 +207,25 @@ def aggAll(op, arg: DenseMatrix, ctx: Optional[Context] = None):
     return out[0]
 
 
+def aggAllStart(op, arg: DenseMatrix, slot: int = 0, ctx: Optional[Context] = None) -> None:
+    """First half of aggAll (f64): queue the reduction; aggAllWait(slot) delivers the value.  What is queued on the
+    context in between runs while the host waits."""
+    ctx = ctx or arg.ctx
+    check(lib.db2_aggAllStart(ctx.handle, int(op), arg.handle, int(slot)))
+
+
+def scalarStart(m: DenseMatrix, slot: int = 0, ctx: Optional[Context] = None) -> None:
+    """Queue the read of a 1 x 1 f64 matrix; aggAllWait(slot) delivers the value."""
+    ctx = ctx or m.ctx
+    check(lib.db2_scalarStart(ctx.handle, m.handle, int(slot)))
+
+
+def aggAllWait(ctx: Context, slot: int = 0) -> float:
+    out = C.c_double()
+    check(lib.db2_scalarWait(ctx.handle, int(slot), C.byref(out)))
+    return out.value
+
+
 def matMul(lhs: DenseMatrix, rhs: DenseMatrix, transa: bool = False, transb: bool = False,
            ctx: Optional[Context] = None) -> DenseMatrix:
     """MatMul.h:44-47: res = op(lhs) @ op(rhs)."""

@@ -146,6 +146,9 @@ _SIGS = {
     "db2_aggRow": (i32, [vp, i32, _P(vp), vp]),
     "db2_aggCol": (i32, [vp, i32, _P(vp), vp]),
     "db2_aggAll": (i32, [vp, i32, vp, vp]),
+    "db2_aggAllStart": (i32, [vp, i32, vp, i32]),
+    "db2_scalarStart": (i32, [vp, vp, i32]),
+    "db2_scalarWait": (i32, [vp, i32, vp]),
     "db2_matMul": (i32, [vp, _P(vp), vp, vp, i32, i32]),
     "db2_syrk": (i32, [vp, _P(vp), vp, i32]),
     "db2_gemv": (i32, [vp, _P(vp), vp, vp]),

@@ -334,6 +334,14 @@ int db2_aggRow(db2_context *ctx, int op, db2_matrix **res, db2_matrix *arg);
 int db2_aggCol(db2_context *ctx, int op, db2_matrix **res, db2_matrix *arg);
 /* res_host: host pointer to one value of the matrix's value type; synchronises */
 int db2_aggAll(db2_context *ctx, int op, void *res_host, db2_matrix *arg);
+/* aggAll in two halves (f64): Start queues the reduction and returns, Wait blocks until its value has arrived.  Work
+ * queued on the context between the two runs while the host waits, so a loop whose condition is a reduction
+ * (components.daphne:21-26: while (sum(u != c) > 0)) can queue its next trip before it looks at the count of the
+ * previous one.  slot is 0 or 1: two values may be outstanding.  db2_scalarStart does the same for a 1 x 1 matrix
+ * that is already on the device (e.g. a count that was combined over the ranks). */
+int db2_aggAllStart(db2_context *ctx, int op, db2_matrix *arg, int slot);
+int db2_scalarStart(db2_context *ctx, db2_matrix *m, int slot);
+int db2_scalarWait(db2_context *ctx, int slot, double *res);
 int db2_matMul(db2_context *ctx, db2_matrix **res, db2_matrix *lhs, db2_matrix *rhs, int transa, int transb);
 int db2_syrk(db2_context *ctx, db2_matrix **res, db2_matrix *arg, int trans_left);
 /* res (cols x 1) = t(mat) vec (Gemv<Dense,Dense,Dense>, src/runtime/local/kernels/Gemv.h:51-63) */

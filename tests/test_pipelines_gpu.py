@@ -247,6 +247,10 @@ def test_native_call_sequences_equal_the_python_ones(ctx):
     a, b = p.connected_components(ctx, G), p.connected_components_native(ctx, G)
     assert a.iterations == b.iterations
     assert_bits_equal(a.c.to_numpy(), b.c.to_numpy(), "components")
+    for maxi in (0, 1, 3):  # the loop's other exit: the trip limit
+        a, b = p.connected_components(ctx, G, maxi=maxi), p.connected_components_native(ctx, G, maxi=maxi)
+        assert a.iterations == b.iterations == maxi
+        assert_bits_equal(a.c.to_numpy(), b.c.to_numpy(), f"components, at most {maxi} trips")
     x = np.random.default_rng(3).random((150000, 64))
     c0 = x[:50].copy()
     X, C0 = k.DenseMatrix.from_numpy(ctx, x), k.DenseMatrix.from_numpy(ctx, c0)
@@ -258,3 +262,27 @@ def test_native_call_sequences_equal_the_python_ones(ctx):
     na, nb = p.normal_equations(ctx, X, Y, 0.001), p.normal_equations_native(ctx, X, Y, 0.001)
     for u, v in ((na.A, nb.A), (na.b, nb.b), (na.beta, nb.beta)):
         assert_bits_equal(u.to_numpy(), v.to_numpy(), "normal equations")
+
+
+def test_agg_all_in_two_halves(ctx):
+    """db2_aggAllStart / db2_scalarStart / db2_scalarWait: the value of the one-call form, two values outstanding."""
+    k, p, cpu = _k()
+    A, B = k.AggOpCode, k.BinaryOpCode
+    rng = np.random.default_rng(8)
+    x = rng.standard_normal((70000, 3))
+    X = k.DenseMatrix.from_numpy(ctx, x)
+    g = _graph(90000, 5, 9)
+    G = k.CSRMatrix.from_scipy(ctx, g)
+    w = rng.random((90000, 1)) * 90000
+    W = k.DenseMatrix.from_numpy(ctx, w)
+    ne = k.ewBinaryMat(B.GT, k.aggRowCsr(A.MAX, k.ewMulCsrDense(G, k.transpose(W))), W)   # deferred CSR chain
+    expect_csr = k.aggAll(A.SUM, k.ewBinaryMat(B.GT, k.aggRowCsr(A.MAX, k.ewMulCsrDense(G, k.transpose(W))), W))
+    k.aggAllStart(A.SUM, ne, 1)
+    k.aggAllStart(A.MAX, X, 0)                      # any other argument: same value, already there
+    one = k.aggCol(A.SUM, k.aggRow(A.SUM, k.ewBinaryObjSca(B.MUL, X, 2.0)))
+    assert k.aggAllWait(ctx, 0) == x.max()
+    assert k.aggAllWait(ctx, 1) == expect_csr
+    k.scalarStart(one, 0)
+    assert k.aggAllWait(ctx, 0) == float(one.to_numpy()[0, 0])
+    with pytest.raises(Exception):
+        k.aggAllStart(A.SUM, X, 2)
