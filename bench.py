@@ -236,7 +236,8 @@ def run_ours(args) -> dict:
         for name, leg in (("normal_equations_shard", normal_equations_leg),
                           ("normal_equations_full", normal_equations_full_leg), ("kmeans_shard", kmeans_leg),
                           ("connected_components", components_leg), ("f32_matmul_tcgen05", f32_matmul_leg),
-                          ("scheduler_group", scheduler_group_leg)):
+                          ("scheduler_group", scheduler_group_leg), ("generic_chain", generic_chain_leg),
+                          ("solve_512", solve_leg)):
             try:
                 extra[name] = leg(ctx, comm, lib, host, world, args)
             except Exception as e:  # a side leg must not take the headline down with it
@@ -634,10 +635,57 @@ def f32_matmul_leg(ctx, comm, lib, host, world, args) -> dict:
             "max_abs_err_vs_f64_64_rows": float(np.abs(got - ref).max())}
 
 
+def generic_chain_leg(ctx, comm, lib, host, world, args) -> dict:
+    """A chain that has no compiled specialisation -- ((X - mu) * w) + 0.5 with rowSums and rowMins -- through the
+    run-time form of the fused row pass.  Bytes: X read once (8 B per element) + two row results."""
+    import daphne_b200.kernels as K
+    from daphne_b200.kernels import AggOpCode as A, BinaryOpCode as B
+    rows = min(args.rows, 1 << 23)
+    cols = 32
+    rng = np.random.default_rng(9)
+    rows = max(1 << 16, rows >> 16 << 16)
+    X = K.DenseMatrix.from_numpy(ctx, np.tile(5.0 + 2.0 * rng.standard_normal((1 << 16, cols)), (rows >> 16, 1)))
+    X.device_ptr()
+    mu = K.DenseMatrix.from_numpy(ctx, rng.standard_normal((1, cols)))
+    w = K.DenseMatrix.from_numpy(ctx, rng.standard_normal((1, cols)) + 3.0)
+
+    def run():
+        Z = K.ewBinaryObjSca(B.ADD, K.ewBinaryMat(B.MUL, K.ewBinaryMat(B.SUB, X, mu), w), 0.5)
+        r, m = K.aggRow(A.SUM, Z), K.aggRow(A.MIN, Z)
+        r.device_ptr()
+        return r, m
+    ms, (r, m) = _timed(lib, ctx, comm, run, 7)
+    nbytes = rows * (cols * 8 + 16)
+    peak, _ = measured_peaks()
+    xs = X.to_numpy()[:4096]
+    z = (xs - mu.to_numpy()) * w.to_numpy() + 0.5
+    return {"workload": f"((X - mu) * w) + 0.5 -> rowSums, rowMins on f64 {rows} x {cols} (no compiled specialisation)",
+            "ms": ms, "hbm_gbs": nbytes / (ms * 1e-3) / 1e9, "hbm_frac_of_measured": nbytes / (ms * 1e-3) / 1e9 / peak,
+            "row_mins_equal_numpy_4096_rows": bool(np.array_equal(m.to_numpy()[:4096, 0], z.min(1))),
+            "row_sums_max_rel_err_4096_rows": float(np.abs(r.to_numpy()[:4096, 0] / z.sum(1) - 1.0).max())}
+
+
+def solve_leg(ctx, comm, lib, host, world, args) -> dict:
+    """solve(A, b) alone on the 512 x 512 system of the normal equations (blocked LU with partial pivoting)."""
+    import daphne_b200.kernels as K
+    n = 512
+    rng = np.random.default_rng(11)
+    g = rng.standard_normal((4 * n, n))
+    a = g.T @ g + 1e-3 * np.eye(n)
+    b = rng.standard_normal((n, 1))
+    Am, Bm = K.DenseMatrix.from_numpy(ctx, a), K.DenseMatrix.from_numpy(ctx, b)
+    Am.device_ptr()
+    Bm.device_ptr()
+    ms, x = _timed(lib, ctx, comm, lambda: K.solve(Am, Bm), 15)
+    xh = x.to_numpy()
+    return {"workload": f"solve, f64 {n} x {n}, one right-hand side", "ms": ms,
+            "residual_max_abs": float(np.abs(a @ xh - b).max()), "launches_per_solve": 3 * (n // 32) }
+
+
 LEGS.update({"normal_equations_shard": normal_equations_leg, "normal_equations_full": normal_equations_full_leg,
              "kmeans_shard": kmeans_leg,
              "connected_components": components_leg, "f32_matmul_tcgen05": f32_matmul_leg,
-             "scheduler_group": scheduler_group_leg})
+             "scheduler_group": scheduler_group_leg, "generic_chain": generic_chain_leg, "solve_512": solve_leg})
 
 
 def cpu_baseline(rows: int, cols: int, steps: int = 3, threads: int | None = None, X=None, budget_s: float = 1e9,
@@ -723,8 +771,7 @@ def main():
     ap.add_argument("--cpu-rows", type=int, default=None,
                     help="rows of the CPU run: default 4,194,304 for the cpu_baseline of the GPU arm (a bounded "
                          "sample), all rows for --impl reference")
-    ap.add_argument("--leg", default=None, choices=["normal_equations_shard", "normal_equations_full", "kmeans_shard",
-                                                    "connected_components", "f32_matmul_tcgen05", "scheduler_group"],
+    ap.add_argument("--leg", default=None, choices=sorted(LEGS),
                     help="run only this side workload (profiling aid); prints its own JSON line")
     args = ap.parse_args()
     if args.cpu_rows is None:

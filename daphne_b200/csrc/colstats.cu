@@ -295,8 +295,9 @@ int colstats_try_agg_col(db2_context *ctx, int op, db2_matrix **res, db2_matrix 
     return DB2_OK;
 }
 
-int colstats_try_sqdev(db2_context *ctx, const Expr &e, db2_matrix **res, bool *handled) {
+int colstats_try_sqdev(db2_context *ctx, const Expr &e, db2_matrix **res, bool *handled, const int32_t **run_if) {
     *handled = false;
+    *run_if = nullptr;
     if (e.gemm || e.steps.size() != 2 || e.dtype != DB2_F64)
         return DB2_OK;
     const ExprStep &sub = e.steps[0], &sq = e.steps[1];
@@ -324,8 +325,16 @@ int colstats_try_sqdev(db2_context *ctx, const Expr &e, db2_matrix **res, bool *
         ok = *h == 0;
         (*res)->combined = ok;
     } else {
-        DB2_TRY(answer_checked(ctx, *cs.stats, static_cast<const double *>(sub.operand.ptr(8)), 0, e.rows, e.cols,
-                               static_cast<double *>((*res)->dev_ptr()), &ok));
+        // one shard: no host decision is needed.  The answer kernel raises the flag for ill-conditioned data and the
+        // caller queues the ordinary pass behind it, to run only if the flag is up
+        int32_t *flag = ctx->dev_status + 24;
+        DB2_CUDA(cudaMemsetAsync(flag, 0, sizeof(int32_t), ctx->stream));
+        DB2_TRY(col_stats_answer(static_cast<const double *>(cs.stats->ptr), e.cols, e.rows,
+                                 static_cast<const double *>(sub.operand.ptr(8)), 0,
+                                 static_cast<double *>((*res)->dev_ptr()), flag, ctx->stream));
+        count(ctx, before);
+        *run_if = flag;
+        return DB2_OK;
     }
     count(ctx, before);
     *handled = ok;

@@ -467,6 +467,8 @@ __global__ void __launch_bounds__(CT)
     fused_col_kernel(const __grid_constant__ FusedProgram P, double *__restrict__ part_v,
                      int64_t *__restrict__ part_i) {
     extern __shared__ __align__(16) double csm[];
+    if (P.run_if && *P.run_if == 0)
+        return;
     double *sv = csm;                                          // [TY][TX*2]
     int64_t *si = reinterpret_cast<int64_t *>(csm + CT * 2);   // same shape
     const int tx = threadIdx.x, ty = threadIdx.y, TX = blockDim.x, TY = blockDim.y;
@@ -572,9 +574,10 @@ __global__ void __launch_bounds__(CT)
 // second stage for the chain column pass: folds the per-CTA partials in order and applies the epilogue
 template <int KIND>
 __global__ void fused_col_final_kernel(const double *__restrict__ part_v, const int64_t *__restrict__ part_i,
-                                       int nparts, int64_t cols, int64_t count, int out_mode, void *__restrict__ res) {
+                                       int nparts, int64_t cols, int64_t count, int out_mode, void *__restrict__ res,
+                                       const int32_t *__restrict__ run_if) {
     const int64_t c = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (c >= cols)
+    if (c >= cols || (run_if && *run_if == 0))
         return;
     double a = part_v[c];
     int64_t p = part_i[c];
@@ -618,7 +621,8 @@ static int fused_col_launch(const FusedProgram &prog, int out_mode, void *res, v
     fused_col_kernel<KIND><<<dim3(gx, gy), dim3(tx, ty), CT * 2 * 16, st>>>(prog, part_v, part_i);
     DB2_TRY(after_launch("fused_col_kernel"));
     fused_col_final_kernel<KIND>
-        <<<(unsigned)((prog.cols + 127) / 128), 128, 0, st>>>(part_v, part_i, gx, prog.cols, prog.rows, out_mode, res);
+        <<<(unsigned)((prog.cols + 127) / 128), 128, 0, st>>>(part_v, part_i, gx, prog.cols, prog.rows, out_mode, res,
+                                                              prog.run_if);
     return after_launch("fused_col_final_kernel");
 }
 

@@ -64,6 +64,9 @@ struct FusedProgram {
     int32_t pad;
     void *ew_out; // if set: the value after all steps is stored here (materialisation)
     int64_t ew_out_ld;
+    // column passes only: if set, the pass runs only when this device word is non-zero at the time the kernel starts
+    // (a fallback that is queued behind a kernel which decides on the device whether it is needed)
+    const int32_t *run_if;
     FusedStep steps[FUSED_MAX_STEPS];
     FusedTap taps[FUSED_MAX_AGGS];
 };

@@ -98,8 +98,15 @@ template <int OP, bool REV> __device__ __forceinline__ double apply(double a, do
     else if constexpr (OP == FO_GE) return (double)(l >= r);
     else if constexpr (OP == FO_MIN) return (r < l) ? r : l;
     else if constexpr (OP == FO_MAX) return (l < r) ? r : l;
+    else if constexpr (OP == FO_AND) return (double)((l != 0.0) && (r != 0.0));
+    else if constexpr (OP == FO_OR) return (double)((l != 0.0) || (r != 0.0));
     else if constexpr (OP == FO_NEG) return -a;
     else if constexpr (OP == FO_ABS) return fabs(a);
+    else if constexpr (OP == FO_SIGN) return (a == 0) ? 0.0 : ((a < 0) ? -1.0 : ((a > 0) ? 1.0 : (double)NAN));
+    else if constexpr (OP == FO_FLOOR) return floor(a);
+    else if constexpr (OP == FO_CEIL) return ceil(a);
+    else if constexpr (OP == FO_ROUND) return round(a);
+    else if constexpr (OP == FO_ISNAN) return (double)(a != a);
     else return a;
 }
 
@@ -148,88 +155,6 @@ struct AnyTaps {
     static constexpr int n = FUSED_MAX_AGGS;
 };
 
-// applies one step to the elements [OFF, OFF + G) of v (compile-time positions: v stays in registers)
-template <int G, int OFF = 0, int N = G>
-__device__ __forceinline__ void apply_step_rt(int op, bool rev, double (&v)[N], const double (&o)[G]) {
-#define DB2_CT_STEP(FWD, REV)                                                                                          \
-    if (!rev) {                                                                                                        \
-        _Pragma("unroll") for (int i = 0; i < G; i++) {                                                                \
-            const double a = v[OFF + i], b = o[i];                                                                     \
-            (void)b;                                                                                                   \
-            v[OFF + i] = (FWD);                                                                                        \
-        }                                                                                                              \
-    } else {                                                                                                           \
-        _Pragma("unroll") for (int i = 0; i < G; i++) {                                                                \
-            const double a = v[OFF + i], b = o[i];                                                                     \
-            (void)b;                                                                                                   \
-            v[OFF + i] = (REV);                                                                                        \
-        }                                                                                                              \
-    }                                                                                                                  \
-    break;
-    switch (op) {
-    case FO_ADD: DB2_CT_STEP(__dadd_rn(a, b), __dadd_rn(b, a))
-    case FO_SUB: DB2_CT_STEP(__dsub_rn(a, b), __dsub_rn(b, a))
-    case FO_MUL: DB2_CT_STEP(__dmul_rn(a, b), __dmul_rn(b, a))
-    case FO_DIV: DB2_CT_STEP(__ddiv_rn(a, b), __ddiv_rn(b, a))
-    case FO_SQUARE: DB2_CT_STEP(__dmul_rn(a, a), __dmul_rn(a, a))
-    case FO_EQ: DB2_CT_STEP((double)(a == b), (double)(b == a))
-    case FO_NEQ: DB2_CT_STEP((double)(a != b), (double)(b != a))
-    case FO_LT: DB2_CT_STEP((double)(a < b), (double)(b < a))
-    case FO_LE: DB2_CT_STEP((double)(a <= b), (double)(b <= a))
-    case FO_GT: DB2_CT_STEP((double)(a > b), (double)(b > a))
-    case FO_GE: DB2_CT_STEP((double)(a >= b), (double)(b >= a))
-    case FO_MIN: DB2_CT_STEP(((b < a) ? b : a), ((a < b) ? a : b))
-    case FO_MAX: DB2_CT_STEP(((a < b) ? b : a), ((b < a) ? a : b))
-    case FO_AND: DB2_CT_STEP((double)((a != 0.0) && (b != 0.0)), (double)((b != 0.0) && (a != 0.0)))
-    case FO_OR: DB2_CT_STEP((double)((a != 0.0) || (b != 0.0)), (double)((b != 0.0) || (a != 0.0)))
-    case FO_NEG: DB2_CT_STEP(-a, -a)
-    case FO_ABS: DB2_CT_STEP(fabs(a), fabs(a))
-    case FO_SIGN:
-        DB2_CT_STEP(((a == 0) ? 0.0 : ((a < 0) ? -1.0 : ((a > 0) ? 1.0 : (double)NAN))),
-                    ((a == 0) ? 0.0 : ((a < 0) ? -1.0 : ((a > 0) ? 1.0 : (double)NAN))))
-    case FO_FLOOR: DB2_CT_STEP(floor(a), floor(a))
-    case FO_CEIL: DB2_CT_STEP(ceil(a), ceil(a))
-    case FO_ROUND: DB2_CT_STEP(round(a), round(a))
-    case FO_ISNAN: DB2_CT_STEP((double)(a != a), (double)(a != a))
-    default: break;
-    }
-#undef DB2_CT_STEP
-}
-
-// `mask`: bit a = tap a sees the values after this step (prepared once per CTA, see the kernel)
-template <int G>
-__device__ __forceinline__ void feed_rt(TapState<AnyTaps> &ts, const FusedProgram &P, unsigned mask, const double (&v)[G],
-                                        int c0) {
-    if (mask == 0)
-        return;
-#pragma unroll
-    for (int a = 0; a < FUSED_MAX_AGGS; a++) {
-        if (mask & (1u << a)) {
-            const int kind = P.taps[a].kind;
-            if (kind == FT_SUM || kind == FT_MEAN) {
-#pragma unroll
-                for (int i = 0; i < G; i++)
-                    ts.v[a] = __dadd_rn(ts.v[a], v[i]);
-            } else if (kind == FT_PROD) {
-#pragma unroll
-                for (int i = 0; i < G; i++)
-                    ts.v[a] = __dmul_rn(ts.v[a], v[i]);
-            } else {
-                if (c0 == 0)
-                    ts.first[a] = v[0];
-                const bool mx = kind == FT_MAX;
-#pragma unroll
-                for (int i = 0; i < G; i++) {
-                    const bool better = mx ? (v[i] > ts.v[a]) : (v[i] < ts.v[a]);
-                    if (better) {
-                        ts.v[a] = v[i];
-                        ts.c[a] = c0 + i;
-                    }
-                }
-            }
-        }
-    }
-}
 __device__ __forceinline__ void init_taps_rt(TapState<AnyTaps> &ts, const FusedProgram &P) {
 #pragma unroll
     for (int a = 0; a < FUSED_MAX_AGGS; a++) {
@@ -262,81 +187,6 @@ __device__ __forceinline__ void write_taps_rt(const TapState<AnyTaps> &ts, const
     }
 }
 
-// scalar helpers and tap masks of a run-time chain sit behind the staged row vectors:
-//   rvs[smem_elems + s]                    division helper of step s (SCALAR operands)
-//   rvs[smem_elems + FUSED_MAX_STEPS + s]  (as bits) mask of the taps that follow s steps
-template <int G>
-__device__ __forceinline__ void run_group_rt(double (&v)[G], const FusedProgram &P, TapState<AnyTaps> &ts,
-                                             const double *rvs, int64_t row, int64_t c) {
-    const unsigned *masks = reinterpret_cast<const unsigned *>(rvs + P.smem_elems + FUSED_MAX_STEPS);
-    feed_rt<G>(ts, P, masks[0], v, (int)c);
-#pragma unroll 1
-    for (int s = 0; s < P.nsteps; s++) {
-        const FusedStep &fs = P.steps[s];
-        const bool fwd_div = fs.op == FO_DIV && !fs.reversed;
-        double o[G];
-        if (fs.kind == FK_ROWVEC) {
-            const double2 *ov = reinterpret_cast<const double2 *>(rvs + fs.smem_off + c);
-#pragma unroll
-            for (int i = 0; i < G / 2; i++) {
-                const double2 t = ov[i];
-                o[2 * i] = t.x;
-                o[2 * i + 1] = t.y;
-            }
-        } else if (fs.kind == FK_MATRIX) {
-            const double *mp = static_cast<const double *>(fs.ptr) + row * fs.ld + c;
-#pragma unroll
-            for (int i = 0; i < G; i++)
-                o[i] = __ldg(mp + i);
-        } else {
-            const double ov =
-                fs.kind == FK_COLVEC ? __ldg(static_cast<const double *>(fs.ptr) + row * fs.ld) : fs.imm; // or UNARY
-#pragma unroll
-            for (int i = 0; i < G; i++)
-                o[i] = ov;
-        }
-        if (fwd_div) {
-            double y[G];
-            if (fs.kind == FK_ROWVEC) {
-                const double2 *yv = reinterpret_cast<const double2 *>(rvs + fs.smem_off + P.cols + c);
-#pragma unroll
-                for (int i = 0; i < G / 2; i++) {
-                    const double2 u = yv[i];
-                    y[2 * i] = u.x;
-                    y[2 * i + 1] = u.y;
-                }
-            } else {
-                // SCALAR: the staged helper; anything else: NaN = generic division
-                const double yv = fs.kind == FK_SCALAR ? rvs[P.smem_elems + s] : __longlong_as_double(0x7ff8000000000000ll);
-#pragma unroll
-                for (int i = 0; i < G; i++)
-                    y[i] = yv;
-            }
-            double q1[G];
-            unsigned worst = 0;
-#pragma unroll
-            for (int i = 0; i < G; i++) {
-                const double q = __dmul_rn(v[i], y[i]);
-                const double r = __fma_rn(-q, o[i], v[i]);
-                q1[i] = __fma_rn(r, y[i], q);
-                worst = max(worst, fast_div_window_pos(q1[i]));
-            }
-            if (worst < FAST_DIV_WINDOW) {
-#pragma unroll
-                for (int i = 0; i < G; i++)
-                    v[i] = q1[i];
-            } else {
-#pragma unroll
-                for (int i = 0; i < G; i++)
-                    v[i] = fast_div(v[i], o[i], y[i]);
-            }
-        } else {
-            apply_step_rt<G>(fs.op, fs.reversed != 0, v, o);
-        }
-        feed_rt<G>(ts, P, masks[s + 1], v, (int)c);
-    }
-}
-
 // The chain on G consecutive elements of one row, step by step: G independent dependency chains for the scheduler to
 // interleave (an element at a time, the latency of the FP64 pipe would be exposed on every step).  The division's
 // range test is folded over the group, so the rare generic division costs one branch per group instead of a branch
@@ -353,9 +203,7 @@ __device__ __forceinline__ void feed_group(TapState<TapsT> &ts, const double (&v
 template <typename ChainT, typename TapsT, bool C0, int G, int I = 0>
 __device__ __forceinline__ void run_group(double (&v)[G], const FusedProgram &P, const ChainState<ChainT> &cs,
                                           TapState<TapsT> &ts, const double *rvs, int64_t row, int64_t c) {
-    if constexpr (std::is_same<ChainT, AnyChain>::value) {
-        run_group_rt<G>(v, P, ts, rvs, row, c);
-    } else {
+    {
     if constexpr (I == 0)
         feed_group<TapsT, 0, C0, G>(ts, v, (int)c);
     if constexpr (I < ChainT::n) {
@@ -553,16 +401,158 @@ __device__ __forceinline__ void walk_row(unsigned walk0, const FusedProgram &P, 
     }
 }
 
-// ---- run-time chains: one lane walks its row of a chunk STEP BY STEP ----
-// All CK elements of the row's chunk stay in registers while the steps are applied one after the other, so a step's
-// description (operand kind, opcode, operand address, tap mask) is read and decoded once per CK elements; evaluating
-// group after group (as the compiled chains do, where the description costs nothing) spent most instructions on that
-// decoding.  Order of the arithmetic and of the taps per element is unchanged.
-template <bool FULL>
-__device__ __forceinline__ void feed_chunk_rt(TapState<AnyTaps> &ts, const FusedProgram &P, unsigned mask,
-                                              const double (&v)[CK], int cc, int cw) {
+// ---- run-time chains: one lane applies the steps to its row of a chunk IN PLACE, step by step ----
+// The row's CK elements sit in the warp's chunk buffer in shared memory.  A step is a function of its own per
+// (opcode, operand order, operand kind): it reads the row 8 elements at a time, applies the operation and writes
+// the row back, so nothing is live in registers from one step to the next and no two steps share code paths that
+// would have to agree on registers.  (Holding the row in registers through one `switch` per step cost 48
+// instructions per element, 14 of them register moves where the cases meet; this form costs a third of that.)
+// A step's description -- opcode, operand kind, operand address -- is decoded once per CK elements.  Scalar helpers
+// and tap masks sit behind the staged row vectors:
+//   rvs[smem_elems + s]                    division helper of step s (SCALAR operands)
+//   rvs[smem_elems + FUSED_MAX_STEPS + s]  (as bits) mask of the taps that follow s steps
+struct RtOperand {
+    unsigned vec;       // ROWVEC: shared-memory address of the staged operand at this chunk's first column (its
+                        // division helpers follow `cols` elements further on)
+    const double *mat;  // MATRIX: this row's operand at the chunk's first column
+    double scal, yscal; // SCALAR / COLVEC operand and its division helper
+    int64_t cols;
+    int cw; // columns of the chunk that exist (even)
+};
+
+template <int OP, bool REV, int KIND>
+__device__ __noinline__ void rt_step(unsigned walk0, const RtOperand so) {
+#pragma unroll
+    for (int g = 0; g < CK / GR; g++) {
+        if (g * GR < so.cw) { // a group that straddles the end works on padding nobody reads
+            double v[GR], o[GR], y[GR];
+#pragma unroll
+            for (int j = 0; j < GR / 2; j++) {
+                const double2 xy = lds128(walk0 ^ (unsigned)((g * (GR / 2) + j) << 4));
+                v[2 * j] = xy.x;
+                v[2 * j + 1] = xy.y;
+            }
+#pragma unroll
+            for (int i = 0; i < GR; i++)
+                o[i] = y[i] = 0.0;
+            if constexpr (KIND == FK_ROWVEC) {
+#pragma unroll
+                for (int j = 0; j < GR / 2; j++) {
+                    if (g * GR + 2 * j < so.cw) {
+                        const double2 t = lds128(so.vec + (unsigned)((g * GR + 2 * j) * 8));
+                        o[2 * j] = t.x;
+                        o[2 * j + 1] = t.y;
+                        if constexpr (OP == FO_DIV && !REV) {
+                            const double2 u = lds128(so.vec + (unsigned)((so.cols + g * GR + 2 * j) * 8));
+                            y[2 * j] = u.x;
+                            y[2 * j + 1] = u.y;
+                        }
+                    }
+                }
+            } else if constexpr (KIND == FK_MATRIX) {
+#pragma unroll
+                for (int i = 0; i < GR; i++) {
+                    if (g * GR + i < so.cw)
+                        o[i] = __ldg(so.mat + g * GR + i);
+                    y[i] = __longlong_as_double(0x7ff8000000000000ll); // no helper: generic division
+                }
+            } else if constexpr (KIND == FK_SCALAR) {
+#pragma unroll
+                for (int i = 0; i < GR; i++) {
+                    o[i] = so.scal;
+                    y[i] = so.yscal;
+                }
+            }
+            if constexpr (OP == FO_DIV && !REV) {
+                double q1[GR];
+                unsigned worst = 0;
+#pragma unroll
+                for (int i = 0; i < GR; i++) {
+                    const double q = __dmul_rn(v[i], y[i]);
+                    const double r = __fma_rn(-q, o[i], v[i]);
+                    q1[i] = __fma_rn(r, y[i], q);
+                    worst = max(worst, fast_div_window_pos(q1[i]));
+                }
+                if (worst < FAST_DIV_WINDOW) {
+#pragma unroll
+                    for (int i = 0; i < GR; i++)
+                        v[i] = q1[i];
+                } else {
+#pragma unroll
+                    for (int i = 0; i < GR; i++)
+                        v[i] = fast_div(v[i], o[i], y[i]);
+                }
+            } else {
+#pragma unroll
+                for (int i = 0; i < GR; i++)
+                    v[i] = apply<OP, REV>(v[i], o[i], 0.0);
+            }
+#pragma unroll
+            for (int j = 0; j < GR / 2; j++)
+                sts128(walk0 ^ (unsigned)((g * (GR / 2) + j) << 4), v[2 * j], v[2 * j + 1]);
+        }
+    }
+}
+
+template <int OP, bool REV>
+__device__ __forceinline__ void rt_step_kind(int kind, unsigned walk0, const RtOperand &so) {
+    if (kind == FK_ROWVEC)
+        rt_step<OP, REV, FK_ROWVEC>(walk0, so);
+    else if (kind == FK_MATRIX)
+        rt_step<OP, REV, FK_MATRIX>(walk0, so);
+    else
+        rt_step<OP, REV, FK_SCALAR>(walk0, so); // SCALAR, or COLVEC: this row's value
+}
+template <int OP> __device__ __forceinline__ void rt_step_rev(bool rev, int kind, unsigned walk0, const RtOperand &so) {
+    if (rev)
+        rt_step_kind<OP, true>(kind, walk0, so);
+    else
+        rt_step_kind<OP, false>(kind, walk0, so);
+}
+
+__device__ __forceinline__ void rt_dispatch(int op, bool rev, int kind, unsigned walk0, const RtOperand &so) {
+    switch (op) {
+    // the order of the operands does not matter
+    case FO_ADD: rt_step_kind<FO_ADD, false>(kind, walk0, so); break;
+    case FO_MUL: rt_step_kind<FO_MUL, false>(kind, walk0, so); break;
+    case FO_EQ: rt_step_kind<FO_EQ, false>(kind, walk0, so); break;
+    case FO_NEQ: rt_step_kind<FO_NEQ, false>(kind, walk0, so); break;
+    case FO_AND: rt_step_kind<FO_AND, false>(kind, walk0, so); break;
+    case FO_OR: rt_step_kind<FO_OR, false>(kind, walk0, so); break;
+    // it does (for MIN and MAX: which operand a NaN or a signed zero comes from)
+    case FO_SUB: rt_step_rev<FO_SUB>(rev, kind, walk0, so); break;
+    case FO_DIV: rt_step_rev<FO_DIV>(rev, kind, walk0, so); break;
+    case FO_LT: rt_step_rev<FO_LT>(rev, kind, walk0, so); break;
+    case FO_LE: rt_step_rev<FO_LE>(rev, kind, walk0, so); break;
+    case FO_GT: rt_step_rev<FO_GT>(rev, kind, walk0, so); break;
+    case FO_GE: rt_step_rev<FO_GE>(rev, kind, walk0, so); break;
+    case FO_MIN: rt_step_rev<FO_MIN>(rev, kind, walk0, so); break;
+    case FO_MAX: rt_step_rev<FO_MAX>(rev, kind, walk0, so); break;
+    // no operand
+    case FO_SQUARE: rt_step<FO_SQUARE, false, FK_UNARY>(walk0, so); break;
+    case FO_NEG: rt_step<FO_NEG, false, FK_UNARY>(walk0, so); break;
+    case FO_ABS: rt_step<FO_ABS, false, FK_UNARY>(walk0, so); break;
+    case FO_SIGN: rt_step<FO_SIGN, false, FK_UNARY>(walk0, so); break;
+    case FO_FLOOR: rt_step<FO_FLOOR, false, FK_UNARY>(walk0, so); break;
+    case FO_CEIL: rt_step<FO_CEIL, false, FK_UNARY>(walk0, so); break;
+    case FO_ROUND: rt_step<FO_ROUND, false, FK_UNARY>(walk0, so); break;
+    case FO_ISNAN: rt_step<FO_ISNAN, false, FK_UNARY>(walk0, so); break;
+    default: break;
+    }
+}
+
+// the taps that see the row as it stands now (bit a of mask = tap a), fed in element order
+__device__ __forceinline__ void rt_feed(unsigned walk0, TapState<AnyTaps> &ts, const FusedProgram &P, unsigned mask,
+                                        int cc, int cw) {
     if (mask == 0)
         return;
+    double v[CK];
+#pragma unroll
+    for (int j = 0; j < CK / 2; j++) {
+        const double2 xy = lds128(walk0 ^ (unsigned)(j << 4));
+        v[2 * j] = xy.x;
+        v[2 * j + 1] = xy.y;
+    }
 #pragma unroll
     for (int a = 0; a < FUSED_MAX_AGGS; a++) {
         if (mask & (1u << a)) {
@@ -571,28 +561,32 @@ __device__ __forceinline__ void feed_chunk_rt(TapState<AnyTaps> &ts, const Fused
                 double acc = ts.v[a];
 #pragma unroll
                 for (int i = 0; i < CK; i++)
-                    if (FULL || i < cw)
-                        acc = __dadd_rn(acc, v[i]);
+                    acc = (i < cw) ? __dadd_rn(acc, v[i]) : acc;
                 ts.v[a] = acc;
             } else if (kind == FT_PROD) {
                 double acc = ts.v[a];
 #pragma unroll
                 for (int i = 0; i < CK; i++)
-                    if (FULL || i < cw)
-                        acc = __dmul_rn(acc, v[i]);
+                    acc = (i < cw) ? __dmul_rn(acc, v[i]) : acc;
                 ts.v[a] = acc;
             } else {
                 if (cc == 0)
                     ts.first[a] = v[0];
-                const bool mx = kind == FT_MAX;
                 double best = ts.v[a];
                 int bc = ts.c[a];
+                if (kind == FT_MAX) {
 #pragma unroll
-                for (int i = 0; i < CK; i++) {
-                    const bool better = (FULL || i < cw) && (mx ? (v[i] > best) : (v[i] < best));
-                    if (better) {
-                        best = v[i];
-                        bc = cc + i;
+                    for (int i = 0; i < CK; i++) {
+                        const bool better = (i < cw) & (v[i] > best);
+                        best = better ? v[i] : best;
+                        bc = better ? cc + i : bc;
+                    }
+                } else {
+#pragma unroll
+                    for (int i = 0; i < CK; i++) {
+                        const bool better = (i < cw) & (v[i] < best);
+                        best = better ? v[i] : best;
+                        bc = better ? cc + i : bc;
                     }
                 }
                 ts.v[a] = best;
@@ -602,105 +596,28 @@ __device__ __forceinline__ void feed_chunk_rt(TapState<AnyTaps> &ts, const Fused
     }
 }
 
-// one step on the groups G0, G0 + 1, ... of a chunk held in registers
-template <bool FULL, int G0>
-__device__ __forceinline__ void step_groups_rt(double (&v)[CK], int kind, int op, bool rev, bool fwd_div,
-                                               const double *ovec, const double *omat, double oscal, double yscal,
-                                               int64_t cols, int cw) {
-    if constexpr (G0 < CK / GR) {
-        constexpr int OFF = G0 * GR;
-        if (FULL || OFF < cw) {
-            double o[GR];
-            if (kind == FK_ROWVEC) {
-#pragma unroll
-                for (int i = 0; i < GR / 2; i++) {
-                    const double2 t = reinterpret_cast<const double2 *>(ovec + OFF)[i];
-                    o[2 * i] = t.x;
-                    o[2 * i + 1] = t.y;
-                }
-            } else if (kind == FK_MATRIX) {
-#pragma unroll
-                for (int i = 0; i < GR; i++)
-                    o[i] = (FULL || OFF + i < cw) ? __ldg(omat + OFF + i) : 0.0;
-            } else {
-#pragma unroll
-                for (int i = 0; i < GR; i++)
-                    o[i] = oscal;
-            }
-            if (fwd_div) {
-                double y[GR];
-                if (kind == FK_ROWVEC) {
-#pragma unroll
-                    for (int i = 0; i < GR / 2; i++) {
-                        const double2 u = reinterpret_cast<const double2 *>(ovec + cols + OFF)[i];
-                        y[2 * i] = u.x;
-                        y[2 * i + 1] = u.y;
-                    }
-                } else {
-#pragma unroll
-                    for (int i = 0; i < GR; i++)
-                        y[i] = yscal;
-                }
-                double q1[GR];
-                unsigned worst = 0;
-#pragma unroll
-                for (int i = 0; i < GR; i++) {
-                    const double q = __dmul_rn(v[OFF + i], y[i]);
-                    const double r = __fma_rn(-q, o[i], v[OFF + i]);
-                    q1[i] = __fma_rn(r, y[i], q);
-                    worst = max(worst, fast_div_window_pos(q1[i]));
-                }
-                if (worst < FAST_DIV_WINDOW) {
-#pragma unroll
-                    for (int i = 0; i < GR; i++)
-                        v[OFF + i] = q1[i];
-                } else {
-#pragma unroll
-                    for (int i = 0; i < GR; i++)
-                        v[OFF + i] = fast_div(v[OFF + i], o[i], y[i]);
-                }
-            } else {
-                apply_step_rt<GR, OFF, CK>(op, rev, v, o);
-            }
-        }
-        step_groups_rt<FULL, G0 + 1>(v, kind, op, rev, fwd_div, ovec, omat, oscal, yscal, cols, cw);
-    }
-}
-
-template <bool EW, bool FULL>
 __device__ __forceinline__ void walk_row_rt(unsigned walk0, const FusedProgram &P, TapState<AnyTaps> &ts,
                                             const double *rvs, int64_t row, int64_t cc, int cw) {
     static_assert(CK % GR == 0, "a chunk is a whole number of groups");
-    double v[CK];
-#pragma unroll
-    for (int j = 0; j < CK / 2; j++) {
-        const double2 xy = lds128(walk0 ^ (unsigned)(j << 4)); // beyond cw: padding that no tap and no store sees
-        v[2 * j] = xy.x;
-        v[2 * j + 1] = xy.y;
-    }
     const unsigned *masks = reinterpret_cast<const unsigned *>(rvs + P.smem_elems + FUSED_MAX_STEPS);
-    feed_chunk_rt<FULL>(ts, P, masks[0], v, (int)cc, cw);
+    rt_feed(walk0, ts, P, masks[0], (int)cc, cw);
 #pragma unroll 1
     for (int s = 0; s < P.nsteps; s++) {
         const FusedStep &fs = P.steps[s];
-        const int kind = fs.kind, op = fs.op;
-        const bool rev = fs.reversed != 0;
-        const bool fwd_div = op == FO_DIV && !rev;
-        const double *ovec = kind == FK_ROWVEC ? rvs + fs.smem_off + cc : nullptr;
-        const double *omat = kind == FK_MATRIX ? static_cast<const double *>(fs.ptr) + row * fs.ld + cc : nullptr;
-        double oscal = fs.imm; // SCALAR (or unused: UNARY)
-        if (kind == FK_COLVEC)
-            oscal = __ldg(static_cast<const double *>(fs.ptr) + row * fs.ld);
-        // division helper of a SCALAR operand; anything that is not staged: NaN = generic division
-        const double yscal = kind == FK_SCALAR ? rvs[P.smem_elems + s] : __longlong_as_double(0x7ff8000000000000ll);
-        step_groups_rt<FULL, 0>(v, kind, op, rev, fwd_div, ovec, omat, oscal, yscal, P.cols, cw);
-        feed_chunk_rt<FULL>(ts, P, masks[s + 1], v, (int)cc, cw);
-    }
-    if constexpr (EW) {
-#pragma unroll
-        for (int j = 0; j < CK / 2; j++)
-            if (FULL || 2 * j < cw)
-                sts128(walk0 ^ (unsigned)(j << 4), v[2 * j], v[2 * j + 1]);
+        const int kind = fs.kind;
+        RtOperand so;
+        so.vec = kind == FK_ROWVEC ? (unsigned)__cvta_generic_to_shared(rvs + fs.smem_off + cc) : 0u;
+        so.mat = kind == FK_MATRIX ? static_cast<const double *>(fs.ptr) + row * fs.ld + cc : nullptr;
+        so.scal = fs.imm;
+        so.yscal = rvs[P.smem_elems + s]; // helper of a SCALAR divisor (staged once per CTA)
+        if (kind == FK_COLVEC) {
+            so.scal = __ldg(static_cast<const double *>(fs.ptr) + row * fs.ld);
+            so.yscal = (fs.op == FO_DIV && !fs.reversed) ? div_helper(so.scal) : 0.0;
+        }
+        so.cols = P.cols;
+        so.cw = cw;
+        rt_dispatch(fs.op, fs.reversed != 0, kind, walk0, so);
+        rt_feed(walk0, ts, P, masks[s + 1], (int)cc, cw);
     }
 }
 
@@ -732,8 +649,9 @@ __global__ void __launch_bounds__(RT, row_ctas_per_sm<ChainT>()) fused_row_ct_ke
         }
     }
     if constexpr (std::is_same<ChainT, AnyChain>::value) {
-        if (tid < P.nsteps && P.steps[tid].kind == FK_SCALAR)
-            rvs[P.smem_elems + tid] = div_helper(P.steps[tid].imm);
+        if (tid < P.nsteps) // NaN: no helper, the generic division
+            rvs[P.smem_elems + tid] = P.steps[tid].kind == FK_SCALAR ? div_helper(P.steps[tid].imm)
+                                                                      : __longlong_as_double(0x7ff8000000000000ll);
         if (tid <= P.nsteps) { // which taps follow `tid` steps
             unsigned mask = 0;
             for (int a = 0; a < P.ntaps; a++)
@@ -801,10 +719,8 @@ __global__ void __launch_bounds__(RT, row_ctas_per_sm<ChainT>()) fused_row_ct_ke
                 load_colvec_aux<ChainT>(cs, P, row);
         }
         if constexpr (std::is_same<ChainT, AnyChain>::value) {
-            if (rows_here == WR && cw == CK)
-                walk_row_rt<EW, true>(tile_s + walk_off, P, ts, rvs, row, cc, cw);
-            else if (live)
-                walk_row_rt<EW, false>(tile_s + walk_off, P, ts, rvs, row, cc, cw);
+            if (live) // in place: the elementwise result, if wanted, is the tile itself
+                walk_row_rt(tile_s + walk_off, P, ts, rvs, row, cc, cw);
         } else {
             if (rows_here == WR && cw == CK)
                 walk_row<ChainT, TapsT, EW, true>(tile_s + walk_off, P, cs, ts, rvs, row, cc, cw);
@@ -902,6 +818,8 @@ template <typename ChainT>
 __global__ void __launch_bounds__(CT_THREADS)
     fused_col_sum_ct_kernel(const __grid_constant__ FusedProgram P, double *__restrict__ part) {
     __shared__ double sv[CT_THREADS * 2];
+    if (P.run_if && *P.run_if == 0)
+        return;
     const int tx = threadIdx.x, ty = threadIdx.y, TX = blockDim.x, TY = blockDim.y;
     const int64_t rows = P.rows, cols = P.cols;
     const int64_t c0 = ((int64_t)blockIdx.y * TX + tx) * 2;
@@ -961,7 +879,9 @@ __global__ void __launch_bounds__(CT_THREADS)
 }
 
 __global__ void col_sum_final_kernel(const double *__restrict__ part, int nparts, int64_t cols, int64_t count,
-                                     int mean, double *__restrict__ res) {
+                                     int mean, double *__restrict__ res, const int32_t *__restrict__ run_if) {
+    if (run_if && *run_if == 0)
+        return;
     // one warp per column: lane l adds partials l, l + 32, ... in order, then a fixed shuffle tree (deterministic)
     const int lane = threadIdx.x % 32;
     const int64_t c = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) / 32;
@@ -994,7 +914,7 @@ static int launch_col_sum(const FusedProgram &prog, int mean, void *res, void *s
     fused_col_sum_ct_kernel<ChainT><<<dim3(gx, gy), dim3(tx, ty), 0, st>>>(prog, part);
     DB2_TRY(after_launch("fused_col_sum_ct_kernel"));
     col_sum_final_kernel<<<(unsigned)((prog.cols * 32 + 255) / 256), 256, 0, st>>>(part, gx, prog.cols, prog.rows, mean,
-                                                                            static_cast<double *>(res));
+                                                                            static_cast<double *>(res), prog.run_if);
     return after_launch("col_sum_final_kernel");
 }
 

@@ -570,8 +570,9 @@ int lazy_try_agg_col(db2_context *ctx, int op, db2_matrix **res, db2_matrix *arg
         *handled = true;
         return DB2_OK;
     }
+    const int32_t *run_if = nullptr;
     if (op == DB2_AGG_SUM) { // sum((X - mu)^2) right after the column sums of X: answered from the statistics
-        DB2_TRY(colstats_try_sqdev(ctx, *e, res, handled));
+        DB2_TRY(colstats_try_sqdev(ctx, *e, res, handled, &run_if));
         if (*handled)
             return DB2_OK;
     }
@@ -579,6 +580,7 @@ int lazy_try_agg_col(db2_context *ctx, int op, db2_matrix **res, db2_matrix *arg
     DB2_TRY(prepare_result(ctx, res, idx ? DB2_U64 : DB2_F64, 1, arg->cols));
     FusedProgram P;
     build_program(*e, e->steps.size(), &P);
+    P.run_if = run_if;
     void *scratch = nullptr;
     DB2_TRY(ctx_scratch(ctx, fused_col_scratch_bytes(arg->cols), &scratch));
     int rc = DB2_OK;

@@ -151,7 +151,24 @@ int db2_gemv(db2_context *ctx, db2_matrix **res, db2_matrix *mat, db2_matrix *ve
 int db2_solve(db2_context *ctx, db2_matrix **res, db2_matrix *lhs, db2_matrix *rhs) {
     DB2_API_BEGIN
     DB2_CHECK(ctx && res && lhs && rhs, DB2_EINVAL, "null argument");
-    DB2_CHECK(lhs->dtype == DB2_F64 && rhs->dtype == DB2_F64, DB2_EUNSUPPORTED, "solve: only double on the device");
+    if (lhs->dtype == DB2_F32 && rhs->dtype == DB2_F32) {
+        // float systems (LAPACKE_sgesv in the reference, Solve.h:66-84) are solved in double and the solution is
+        // rounded once: every float is a double, so this is the same system, solved at least as accurately
+        db2_matrix *l64 = nullptr, *r64 = nullptr, *x64 = nullptr;
+        int rc = db2_castObj(ctx, &l64, lhs, DB2_F64);
+        if (rc == DB2_OK)
+            rc = db2_castObj(ctx, &r64, rhs, DB2_F64);
+        if (rc == DB2_OK)
+            rc = db2_solve(ctx, &x64, l64, r64);
+        if (rc == DB2_OK)
+            rc = db2_castObj(ctx, res, x64, DB2_F32);
+        for (db2_matrix *m : {l64, r64, x64})
+            if (m)
+                db2_matrix_decref(m);
+        return rc;
+    }
+    DB2_CHECK(lhs->dtype == DB2_F64 && rhs->dtype == DB2_F64, DB2_EUNSUPPORTED,
+              "solve: double or float operands of one type on the device");
     // checks and messages of Solve.h:90-99
     DB2_CHECK(lhs->rows == rhs->rows, DB2_EINVAL, "#rows of lhs and #rows of rhs must be the same");
     DB2_CHECK(lhs->rows == lhs->cols, DB2_EINVAL, "#rows and #cols of lhs must be the same");

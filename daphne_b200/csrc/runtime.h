@@ -209,7 +209,10 @@ struct OneHot { // rows x cols matrix with one stored entry per row: (r, idx[r])
 // column aggregation through the one-pass statistics (colstats.cu): SUM / MEAN fill them, VAR / STDDEV and the
 // deferred  sum((X - mu)^2)  are answered from them
 int colstats_try_agg_col(db2_context *ctx, int op, db2_matrix **res, db2_matrix *arg, bool *handled);
-int colstats_try_sqdev(db2_context *ctx, const Expr &e, db2_matrix **res, bool *handled);
+// handled: the result is complete.  Otherwise, with *run_if set: the result was written from the statistics and the
+// device word *run_if says whether the data turned out ill-conditioned for that (non-zero) -- the caller queues the
+// ordinary pass with that word as its condition, and nobody waits for the host to look at it.
+int colstats_try_sqdev(db2_context *ctx, const Expr &e, db2_matrix **res, bool *handled, const int32_t **run_if);
 // all-reduce (ADD) of the column sums that filled the statistics: one all-gather that also carries every rank's
 // statistics (colstats.cu); comm_allgather_f64 is the raw collective (comm.cu)
 int colstats_try_allreduce(db2_context *ctx, db2_matrix *m, bool *handled);

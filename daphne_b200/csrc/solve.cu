@@ -8,6 +8,7 @@
 // does the back substitution.  About 3 launches per 32 columns instead of a single CTA walking the whole trailing
 // matrix through L2 for every column (23 ms for d = 512 before, about 1.5 ms now).
 #include "common.cuh"
+#include "fused_step.cuh"
 
 namespace db2 {
 
@@ -90,155 +91,217 @@ __global__ void __launch_bounds__(LU_THREADS)
 }
 
 // The same factorisation for panels of at most 512 rows: one thread per ROW, the row's 32 panel entries in registers.
-// Per column: block-wide argmax of |a[j]| (shuffles + one barrier), exchange of the pivot row and row j through shared
-// memory (one barrier), then every thread below the diagonal scales its a[j] and updates its remaining entries from
-// the broadcast pivot row -- two barriers per column instead of five, no shared-memory traffic for the updates.
+// Per column: block-wide argmax of |a[j]|, exchange of the pivot row and row j through shared memory, then every
+// thread below the diagonal scales its a[j] and updates its remaining entries from the broadcast pivot row -- one
+// barrier per column, no shared-memory traffic for the updates.
+//
+// What bounds the kernel is the chain of dependent operations per column, so that chain is kept short:
+//   * |a| is compared as an integer (the bit pattern of a non-negative double orders like its value), which lets the
+//     argmax run on the warp-reduce instructions: three of them per level (high word, low word, lowest row among the
+//     equals) instead of five rounds of 64-bit shuffles and FP64 compares;
+//   * the division by the pivot is a / p exactly (correctly rounded), but computed from the pivot's reciprocal, which
+//     every candidate row prepares for its own entry BEFORE the search -- off the critical path -- and the winner
+//     publishes with its row; after the barrier a multiplication and two fused multiply-adds remain (fast_div).
 constexpr int LU_NB = 32, LU_REG_ROWS = 512;
+
+// order of |a| as an integer: 0 for "no candidate" and for a NaN (which the scan's comparison never prefers),
+// 1 + bits(|a|) for a candidate
+__device__ __forceinline__ unsigned long long pivot_key(double a, bool cand) {
+    const unsigned long long bits = (unsigned long long)__double_as_longlong(fabs(a));
+    return (cand && bits <= 0x7ff0000000000000ull) ? bits + 1ull : 0ull;
+}
+// the largest key of the warp and the lowest row that has it
+__device__ __forceinline__ void warp_first_largest(unsigned long long key, int row, unsigned long long &kmax, int &rmin) {
+    const unsigned hi = (unsigned)(key >> 32);
+    const unsigned mh = __reduce_max_sync(0xffffffffu, hi);
+    const unsigned lo = hi == mh ? (unsigned)key : 0u;
+    const unsigned ml = __reduce_max_sync(0xffffffffu, lo);
+    const bool top = hi == mh && lo == ml;
+    rmin = (int)__reduce_min_sync(0xffffffffu, top ? (unsigned)row : 0x7fffffffu);
+    kmax = ((unsigned long long)mh << 32) | ml;
+}
+
+// Layout of the dynamic shared memory of lu_panel_reg_kernel (doubles): the multipliers every row has collected,
+// [LU_REG_ROWS][LU_NB + 1]; the pivot rows, [LU_NB][LU_NB]; the candidates' rows, [2][LU_REG_ROWS / 32][LU_NB]
+constexpr int LU_PANEL_SMEM = (LU_REG_ROWS * (LU_NB + 1) + LU_NB * LU_NB + 2 * (LU_REG_ROWS / 32) * LU_NB) * 8;
+
 __global__ void __launch_bounds__(LU_REG_ROWS)
     lu_panel_reg_kernel(double *__restrict__ A, int64_t n, int64_t k0, int nb, int *__restrict__ piv,
                         int32_t *__restrict__ status) {
+    // The loop over the columns is a REAL loop: the part of the row that is still being eliminated lives in
+    // a[0 .. 31 - j] -- the update of column j writes entry c to a[c - 1] -- so the code of every column is the same
+    // and stays in the instruction cache.  (Unrolled over the columns, with fixed register positions, the kernel was
+    // 32 different pieces of code that each ran once: it waited for instruction fetches more than for anything
+    // else.)  Rows are not exchanged either: a thread keeps its row and only the row's POSITION changes hands.  A row
+    // that becomes a pivot row leaves its remaining entries in `urow`, every other row notes its multiplier in
+    // `lmul`; the rows are written to their final positions at the end.
+    //
     // ONE barrier per column: before it every warp publishes its best pivot candidate TOGETHER WITH that candidate's
-    // row, and the owner of row j publishes row j; after it every thread folds the warps' candidates to the same
-    // pivot p and finds both rows it may need.  The buffers alternate with the column parity, so the writes of column
-    // j + 1 cannot overtake the reads of column j - 1 (a thread writes them only after the barrier of column j, which
-    // every thread reaches after its reads of column j - 1).
-    __shared__ double cand_row[2][LU_REG_ROWS / 32][LU_NB]; // [parity][warp][entries]: row of the warp's candidate
-    __shared__ double row_j[2][LU_NB];                      // [parity][entries]: row j before the exchange
-    __shared__ double s_val[2][LU_REG_ROWS / 32];
-    __shared__ int s_idx[2][LU_REG_ROWS / 32];
+    // row; after it every thread folds the warps' candidates to the same pivot.  The buffers alternate with the column
+    // parity, so the writes of column j + 1 cannot overtake the reads of column j - 1.
+    extern __shared__ double lu_sm[];
+    double(*lmul)[LU_NB + 1] = reinterpret_cast<double(*)[LU_NB + 1]>(lu_sm);
+    double(*urow)[LU_NB] = reinterpret_cast<double(*)[LU_NB]>(lu_sm + LU_REG_ROWS * (LU_NB + 1));
+    double(*cand_row)[LU_REG_ROWS / 32][LU_NB] =
+        reinterpret_cast<double(*)[LU_REG_ROWS / 32][LU_NB]>(lu_sm + LU_REG_ROWS * (LU_NB + 1) + LU_NB * LU_NB);
+    __shared__ double cand_rcp[2][LU_REG_ROWS / 32]; // reciprocal of the candidate's entry (0: none usable)
+    __shared__ unsigned long long s_key[2][LU_REG_ROWS / 32];
+    __shared__ int s_pos[2][LU_REG_ROWS / 32];
     const int tid = threadIdx.x, lane = tid % 32, warp = tid / 32, nwarps = blockDim.x / 32;
     const int m = (int)(n - k0);
     double a[LU_NB];
 #pragma unroll
     for (int c = 0; c < LU_NB; c++)
         a[c] = (tid < m && c < nb) ? A[(k0 + tid) * n + k0 + c] : 0.0;
-#pragma unroll
-    for (int j = 0; j < LU_NB; j++) {
-        if (j >= nb)
-            break;
+    int pos = tid;      // the position (row of the panel) this thread's row holds at the moment
+    int pivoted_at = -1; // the column at which it became the pivot row
+#pragma unroll 1
+    for (int j = 0; j < nb; j++) {
         const int par = j & 1;
-        // first largest |a[j]| among the rows j .. m-1 (idamax)
-        const bool cand = tid >= j && tid < m;
-        double best = cand ? fabs(a[j]) : -1.0;
-        int bi = cand ? tid : 0x7fffffff;
-        if (best != best) // a NaN pivot candidate: treated as "not larger" like the comparison of the scan
-            best = -1.0;
-#pragma unroll
-        for (int o = 16; o >= 1; o >>= 1) {
-            const double ov = __shfl_xor_sync(0xffffffffu, best, o);
-            const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-            if (ov > best || (ov == best && oi < bi)) {
-                best = ov;
-                bi = oi;
-            }
-        }
-        if (tid == bi) { // this warp's candidate publishes its row
+        // first largest |a| of column j among the rows at positions j .. m-1 (idamax)
+        const bool cand = pivoted_at < 0 && tid < m;
+        const double rcp = cand ? div_helper(a[0]) : 0.0;
+        unsigned long long key;
+        int bp;
+        warp_first_largest(pivot_key(a[0], cand), cand ? pos : 0x7fffffff, key, bp);
+        if (cand && pos == bp) { // this warp's candidate publishes its row
 #pragma unroll
             for (int c = 0; c < LU_NB; c++)
                 cand_row[par][warp][c] = a[c];
+            cand_rcp[par][warp] = rcp;
         }
         if (lane == 0) {
-            s_val[par][warp] = best;
-            s_idx[par][warp] = bi;
-        }
-        if (tid == j) {
-#pragma unroll
-            for (int c = 0; c < LU_NB; c++)
-                row_j[par][c] = a[c];
+            s_key[par][warp] = key;
+            s_pos[par][warp] = bp;
         }
         __syncthreads();
-        best = lane < nwarps ? s_val[par][lane] : -1.0;
-        bi = lane < nwarps ? s_idx[par][lane] : 0x7fffffff;
-#pragma unroll
-        for (int o = 16; o >= 1; o >>= 1) {
-            const double ov = __shfl_xor_sync(0xffffffffu, best, o);
-            const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-            if (ov > best || (ov == best && oi < bi)) {
-                best = ov;
-                bi = oi;
-            }
-        }
-        const int p = bi; // every thread has the same answer; always a row in [j, m): row j is a candidate
-        const double *prow = cand_row[par][p / 32];
+        const int wpos = lane < nwarps ? s_pos[par][lane] : 0x7fffffff;
+        warp_first_largest(lane < nwarps ? s_key[par][lane] : 0ull, wpos, key, bp);
+        const int p = bp; // the same in every thread; always a position in [j, m): the row at position j is a candidate
+        const int pw = __ffs(__ballot_sync(0xffffffffu, wpos == p)) - 1; // the warp whose candidate it is
+        const double *prow = cand_row[par][pw];
         if (tid == 0) {
             piv[k0 + j] = (int)k0 + p;
-            if (!(best > 0.0) && *status == 0)
+            if (key <= 1ull && *status == 0)
                 *status = (int32_t)(k0 + j + 1); // exactly singular (or NaN) pivot
         }
-        if (p != j) { // the two rows change places
-            if (tid == j) {
+        if (tid < LU_NB)
+            urow[j][tid] = prow[tid]; // entries j .. of the pivot row (entry j + c at index c)
+        if (cand) {
+            if (pos == p) { // this row is the pivot row: it moves to position j and is finished
+                pos = j;
+                pivoted_at = j;
+            } else {
+                if (pos == j)
+                    pos = p; // the row that sat at position j takes the pivot row's place
+                const double l = fast_div(a[0], prow[0], cand_rcp[par][pw]);
+                lmul[tid][j] = l;
 #pragma unroll
-                for (int c = 0; c < LU_NB; c++)
-                    a[c] = prow[c];
-            } else if (tid == p) {
-#pragma unroll
-                for (int c = 0; c < LU_NB; c++)
-                    a[c] = row_j[par][c];
+                for (int c = 1; c < LU_NB; c++)
+                    a[c - 1] = __fma_rn(-l, prow[c], a[c]);
+                a[LU_NB - 1] = 0.0;
             }
         }
-        if (tid > j && tid < m) {
-            const double l = __ddiv_rn(a[j], prow[j]);
-            a[j] = l;
-#pragma unroll
-            for (int c = j + 1; c < LU_NB; c++)
-                a[c] = __fma_rn(-l, prow[c], a[c]);
-        }
     }
-    if (tid < m)
-#pragma unroll
-        for (int c = 0; c < LU_NB; c++)
-            if (c < nb)
-                A[(k0 + tid) * n + k0 + c] = a[c];
+    __syncthreads(); // urow is complete
+    if (tid < m) {
+        double *dst = A + (k0 + pos) * n + k0;
+        const int from_pivot_row = pivoted_at >= 0 ? pivoted_at : nb; // the first column that is not a multiplier
+        for (int c = 0; c < from_pivot_row; c++)
+            dst[c] = lmul[tid][c];
+        for (int c = from_pivot_row; c < nb; c++)
+            dst[c] = urow[pivoted_at][c - pivoted_at];
+    }
 }
 
-// One thread per column outside the panel (column index n stands for the right-hand side): row exchanges of the
-// panel, then -- right of the panel and for b -- the forward substitution with the panel's unit lower triangle.
-// The column's entries of the block row live in shared memory while this happens (one column of a [32][threads] tile
-// per thread) and the triangle is staged once per block: the 32 exchanges and 496 updates of a column touch global
-// memory only for its 32 entries and for pivot rows below the block row.  (Keeping them in global memory cost a
-// dependent L2 round trip per update: 2 ms of the 2.4 ms a 512 x 512 solve took.)
+// One thread per column right of the panel (column index n stands for the right-hand side): row exchanges of the
+// panel, then the forward substitution with the panel's unit lower triangle.  (Columns left of the panel hold
+// multipliers that nothing reads again -- the right-hand side is carried along as a column -- so they are left alone.)
+//
+// The 32 exchanges of a panel are one permutation.  Warp 0 composes it once per block -- lane j follows which original
+// row ends up in row k0 + j of the block row, and the lanes also keep the list of rows below the block row that
+// receive a row -- so every thread can fetch all its sources with INDEPENDENT loads and then write the displaced rows,
+// instead of 32 dependent read-modify-write round trips through L2.  The column's 32 entries of the block row stay
+// in registers through the substitution; the triangle is staged in shared memory once per block.
 constexpr int TRSM_THREADS = 128;
 __global__ void __launch_bounds__(TRSM_THREADS)
     lu_swap_trsm_kernel(double *__restrict__ A, double *__restrict__ x, int64_t n, int64_t k0, int nb,
                         const int *__restrict__ piv) {
-    __shared__ double V[LU_NB][TRSM_THREADS + 1];
-    __shared__ double L[LU_NB][LU_NB + 1];
-    __shared__ int P[LU_NB];
+    __shared__ double L[2 * LU_NB][LU_NB + 1]; // rows nb .. stay zero: the substitution loop needs no bounds
+    __shared__ int src_blk[LU_NB];               // original row whose entry ends up in row k0 + j
+    __shared__ int out_row[LU_NB], out_src[LU_NB]; // rows below the block row that receive original row out_src
+    __shared__ int out_cnt;
     const int t = threadIdx.x;
-    for (int e = t; e < nb * nb; e += TRSM_THREADS)
-        L[e / nb][e % nb] = A[(k0 + e / nb) * n + k0 + e % nb];
-    if (t < nb)
-        P[t] = piv[k0 + t];
+    if (t < 32) {
+        // lane j: cur = original row now in position k0 + j; lane e < cnt: (orow, osrc) of the e-th outside row
+        int cur = (int)k0 + t, orow = -1, osrc = -1, cnt = 0;
+        for (int j = 0; j < nb; j++) {
+            const int p = piv[k0 + j];
+            if (p > k0 + j && p < n) { // a pivot row below row k0 + j and inside the matrix; anything else: no exchange
+                const int cj = __shfl_sync(0xffffffffu, cur, j);
+                if (p < k0 + nb) {
+                    const int cp = __shfl_sync(0xffffffffu, cur, p - (int)k0);
+                    if (t == j)
+                        cur = cp;
+                    else if (t == p - (int)k0)
+                        cur = cj;
+                } else {
+                    const unsigned hit = __ballot_sync(0xffffffffu, t < cnt && orow == p);
+                    int e = hit ? __ffs(hit) - 1 : cnt;
+                    const int prev = hit ? __shfl_sync(0xffffffffu, osrc, e) : p; // what row p holds right now
+                    if (!hit) {
+                        if (t == cnt)
+                            orow = p;
+                        cnt++;
+                    }
+                    if (t == e)
+                        osrc = cj;
+                    if (t == j)
+                        cur = prev;
+                }
+            }
+        }
+        src_blk[t] = cur;
+        out_row[t] = orow;
+        out_src[t] = osrc;
+        if (t == 0)
+            out_cnt = cnt;
+    }
+    for (int e = t; e < 2 * LU_NB * LU_NB; e += TRSM_THREADS) {
+        const int i = e / LU_NB, j = e % LU_NB;
+        L[i][j] = (i < nb && j < nb) ? A[(k0 + i) * n + k0 + j] : 0.0;
+    }
     __syncthreads();
-    const int64_t c = (int64_t)blockIdx.x * TRSM_THREADS + t;
-    if (c > n || (c >= k0 && c < k0 + nb))
+    const int64_t c0 = (int64_t)blockIdx.x * TRSM_THREADS + t;
+    const int64_t c = k0 + nb + c0; // columns k0 + nb .. n - 1, then the right-hand side
+    if (c > n)
         return;
     const bool rhs = (c == n);
     double *col = rhs ? x : A + c;
     const int64_t st = rhs ? 1 : n;
-    for (int j = 0; j < nb; j++)
-        V[j][t] = col[(k0 + j) * st];
+    const int cnt = out_cnt;
+    double v[LU_NB], w[LU_NB];
+#pragma unroll
+    for (int j = 0; j < LU_NB; j++)
+        v[j] = j < nb ? col[(int64_t)src_blk[j] * st] : 0.0;
+#pragma unroll
+    for (int e = 0; e < LU_NB; e++)
+        w[e] = e < cnt ? col[(int64_t)out_src[e] * st] : 0.0;
+#pragma unroll
+    for (int e = 0; e < LU_NB; e++)
+        if (e < cnt)
+            col[(int64_t)out_row[e] * st] = w[e];
+    // forward substitution as a loop with one body: the entries still to be updated move down one register per
+    // column (entry j + i sits in v[i]), so that x_j is always v[0]
+#pragma unroll 1
     for (int j = 0; j < nb; j++) {
-        const int64_t p = P[j];
-        if (p > k0 + j && p < n) { // a pivot row lies below row k0 + j and inside the matrix; anything else is no exchange
-            const double v = V[j][t];
-            if (p < k0 + nb) {
-                V[j][t] = V[p - k0][t];
-                V[p - k0][t] = v;
-            } else {
-                V[j][t] = col[p * st];
-                col[p * st] = v;
-            }
-        }
+        const double xj = v[0];
+        col[(k0 + j) * st] = xj;
+#pragma unroll
+        for (int i = 1; i < LU_NB; i++)
+            v[i - 1] = __fma_rn(-L[j + i][j], xj, v[i]);
+        v[LU_NB - 1] = 0.0;
     }
-    if (rhs || c >= k0 + nb)
-        for (int j = 0; j < nb; j++) {
-            const double v = V[j][t];
-            for (int i = j + 1; i < nb; i++)
-                V[i][t] = __fma_rn(-L[i][j], v, V[i][t]);
-        }
-    for (int j = 0; j < nb; j++)
-        col[(k0 + j) * st] = V[j][t];
 }
 
 // A22 -= L21 U12 (and b2 -= L21 b1 as one more column): 32 x 32 tiles
@@ -295,8 +358,12 @@ __global__ void __launch_bounds__(LU_THREADS)
         __syncthreads();
         if (tid < 32) {
             double xi = lane < w ? xs[k0 + lane] : 0.0;
+            // x_j / U_jj is the exact quotient, taken from the diagonal's reciprocal (prepared by all lanes at once,
+            // ahead of the dependent chain of the 32 unknowns)
+            const double dg = lane < w ? T[lane][lane] : 1.0, ry = div_helper(dg);
             for (int j = w - 1; j >= 0; j--) {
-                const double xj = __ddiv_rn(__shfl_sync(0xffffffffu, xi, j), T[j][j]);
+                const double xj = fast_div(__shfl_sync(0xffffffffu, xi, j), __shfl_sync(0xffffffffu, dg, j),
+                                           __shfl_sync(0xffffffffu, ry, j));
                 if (lane == j)
                     xi = xj;
                 else if (lane < j)
@@ -309,8 +376,14 @@ __global__ void __launch_bounds__(LU_THREADS)
         for (int64_t i = tid; i < k0; i += nt) {
             double acc = xs[i];
             const double *row = A + i * n + k0;
-            for (int c = w - 1; c >= 0; c--)
-                acc = __fma_rn(-row[c], xs[k0 + c], acc);
+            double rv[32]; // the row's 32 entries are fetched together, then used in the order of the column loop
+#pragma unroll
+            for (int c = 0; c < 32; c++)
+                rv[c] = c < w ? row[c] : 0.0;
+#pragma unroll
+            for (int c = 31; c >= 0; c--)
+                if (c < w)
+                    acc = __fma_rn(-rv[c], xs[k0 + c], acc);
             xs[i] = acc;
         }
         __syncthreads();
@@ -344,6 +417,8 @@ extern "C" int db2k_solve(int dtype, void *a_work, int64_t n, void *x_inout, int
     static PerDeviceOnce attr;
     if (attr.need()) {
         DB2_CUDA(cudaFuncSetAttribute(lu_panel_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+        DB2_CUDA(cudaFuncSetAttribute(lu_panel_reg_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      LU_PANEL_SMEM));
         DB2_CUDA(cudaFuncSetAttribute(lu_backsolve_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
         attr.mark();
     }
@@ -353,14 +428,15 @@ extern "C" int db2k_solve(int dtype, void *a_work, int64_t n, void *x_inout, int
         const int threads = m * w >= 4096 ? LU_THREADS : 256;
         if (m <= LU_REG_ROWS && w <= LU_NB) {
             const int rows32 = (int)((m + 31) / 32 * 32);
-            lu_panel_reg_kernel<<<1, rows32, 0, st>>>(A, n, k0, w, piv, dev_status);
+            lu_panel_reg_kernel<<<1, rows32, LU_PANEL_SMEM, st>>>(A, n, k0, w, piv, dev_status);
             DB2_TRY(after_launch("lu_panel_reg_kernel"));
         } else {
             lu_panel_kernel<<<1, threads, (size_t)m * (w + 1) * 8, st>>>(A, n, k0, w, piv, dev_status);
             DB2_TRY(after_launch("lu_panel_kernel"));
         }
-        lu_swap_trsm_kernel<<<(unsigned)((n + 1 + TRSM_THREADS - 1) / TRSM_THREADS), TRSM_THREADS, 0, st>>>(A, x, n, k0, w,
-                                                                                                        piv);
+        const int64_t right = n - k0 - w + 1; // columns right of the panel and the right-hand side
+        lu_swap_trsm_kernel<<<(unsigned)((right + TRSM_THREADS - 1) / TRSM_THREADS), TRSM_THREADS, 0, st>>>(A, x, n, k0, w,
+                                                                                                       piv);
         DB2_TRY(after_launch("lu_swap_trsm_kernel"));
         const int64_t rest = n - k0 - w;
         if (rest > 0) {

@@ -92,7 +92,9 @@ def test_deferred_sum_of_squared_deviations(ctx):
     mu = k.ewBinaryObjSca(B.DIV, s1, float(n))
     s0 = ctx.stats()["launches"]
     v = k.aggCol(A.SUM, k.ewBinaryObjSca(B.POW, k.ewBinaryMat(B.SUB, X, mu), 2.0)).to_numpy()
-    assert ctx.stats()["launches"] - s0 <= 2
+    # the answer from the statistics, and behind it the two kernels of the ordinary pass, which look at the device
+    # flag and return at once: no pass over X, no wait for the host
+    assert ctx.stats()["launches"] - s0 <= 4
     mu_h = mu.to_numpy()
     assert _rel(v, ((x - mu_h) ** 2).sum(0, keepdims=True)) <= RTOL
     # any other row vector (the global mean of a sharded run differs from the shard's own)

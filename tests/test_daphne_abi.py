@@ -356,3 +356,32 @@ def test_every_value_type_of_the_elementwise_catalog_entries_computes(drv):
     for as_bool, v in ((1, 1), (0, 203)):
         assert drv.drv_fill_u8(as_bool, v, i64(7), i64(5), _p(buf)) == 0, drv.drv_last_error()
         assert np.all(buf == v)
+
+
+@pytest.mark.gpu
+def test_float_entries_of_the_contraction_kernels_compute(drv):
+    """CUDA_solve / CUDA_gemv / CUDA_matMul / CUDA_syrk are registered for float as well as double: the float names
+    compute too (solve in double with one final rounding, the products on the tf32 tensor-core path)."""
+    cat = json.loads((ABI / "CUDAcatalog.json").read_text())
+    names = {e["kernelFuncName"] for e in cat}
+    rng = np.random.default_rng(12)
+    n = 96
+    a = (rng.standard_normal((n, n)) + n * np.eye(n)).astype(np.float32)
+    a[[0, n - 1]] = a[[n - 1, 0]]
+    b = rng.standard_normal((n, 1)).astype(np.float32)
+    solve = "CUDA_solve__DenseMatrix_float__DenseMatrix_float__DenseMatrix_float"
+    gemv = "CUDA_gemv__DenseMatrix_float__DenseMatrix_float__DenseMatrix_float"
+    assert solve in names and gemv in names
+    out = np.empty((n, 1), dtype=np.float32)
+    rc = drv.drv_binary_typed(solve.encode(), 1, _p(a), i64(n), i64(n), _p(b), i64(n), i64(1), None, _p(out))
+    assert rc == 0, drv.drv_last_error()
+    exact = np.linalg.solve(a.astype(np.float64), b.astype(np.float64))
+    assert np.abs(out - exact).max() <= 2.0 ** -22 * np.abs(exact).max()      # one float rounding of the exact solution
+    m = rng.standard_normal((500, 40)).astype(np.float32)
+    v = rng.standard_normal((500, 1)).astype(np.float32)
+    out = np.empty((40, 1), dtype=np.float32)
+    rc = drv.drv_binary_typed(gemv.encode(), 1, _p(m), i64(500), i64(40), _p(v), i64(500), i64(1), None, _p(out))
+    assert rc == 0, drv.drv_last_error()
+    exact = m.astype(np.float64).T @ v.astype(np.float64)
+    bound = (500 * 2.0 ** -24 + 2.0 ** -19) * (np.abs(m).astype(np.float64).T @ np.abs(v).astype(np.float64))
+    assert np.all(np.abs(out - exact) <= bound)

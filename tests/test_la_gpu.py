@@ -131,6 +131,20 @@ def test_solve_general_and_singular(ctx):
         got = k.solve(k.DenseMatrix.from_numpy(ctx, a), k.DenseMatrix.from_numpy(ctx, b)).to_numpy()
         ref = o.solve(a, b)
         assert np.abs(got - ref).max() <= 1e-10 * np.abs(ref).max(), n
+    # pivots that sit below the block row of their panel, several exchanges with the same row, n not a multiple of 32
+    for n in (97, 200, 512, 515):
+        a = rng.standard_normal((n, n))
+        a[: n // 2] *= 1e-3                           # the large entries, hence the pivots, are in the lower half
+        b = rng.standard_normal((n, 1))
+        got = k.solve(k.DenseMatrix.from_numpy(ctx, a), k.DenseMatrix.from_numpy(ctx, b)).to_numpy()
+        ref = o.solve(a, b)
+        assert np.abs(got - ref).max() <= 1e-7 * np.abs(ref).max(), n
+        assert np.abs(a @ got - b).max() <= 1e-9 * max(1.0, np.abs(got).max()) * np.abs(a).max() * n, n
+    a32 = (rng.standard_normal((150, 150)) + 150 * np.eye(150)).astype(np.float32)
+    b32 = rng.standard_normal((150, 1)).astype(np.float32)
+    got = k.solve(k.DenseMatrix.from_numpy(ctx, a32), k.DenseMatrix.from_numpy(ctx, b32)).to_numpy()
+    exact = np.linalg.solve(a32.astype(np.float64), b32.astype(np.float64))
+    assert got.dtype == np.float32 and np.abs(got - exact).max() <= 2.0 ** -22 * np.abs(exact).max()
     sing = np.zeros((3, 3))
     sing[0, 0] = 1.0
     with pytest.raises(k.Db2Error, match="exactly singular"):
