@@ -117,6 +117,58 @@ int db2w_connected_components(db2_context *ctx, db2_csr *G, int64_t row_lo, int6
     DB2_API_END
 }
 
+// Column standardisation and aggregation, the memory-bound pipeline of the benchmark:
+//   mu = mean(X, 1); sd = sqrt(var(X, 1)); Z = (X - mu) / sd;
+//   r = sum(Z ^ 2, 0); s = sum(r); m = aggMax(Z, 0); i = idxMax(Z, 0);
+// with mean / var issued as their ADD-combinable forms (column sums over the global row count n_total), so that row
+// shards on several GPUs give the global statistics.  s is returned as a 1 x 1 matrix on the device (combined over
+// the ranks): nothing in here waits for the host.  ev_rows_begin / ev_rows_end (optional, db2_event_create) are
+// recorded around the pass that produces r, m and i.
+int db2w_standardise(db2_context *ctx, db2_matrix *X, int64_t n_total, db2_matrix **mu_out, db2_matrix **sd_out,
+                     db2_matrix **r_out, db2_matrix **max_out, db2_matrix **idx_out, db2_matrix **s_out,
+                     void *ev_rows_begin, void *ev_rows_end) {
+    DB2_API_BEGIN
+    DB2_CHECK(ctx && X && mu_out && sd_out && r_out && max_out && idx_out && s_out, DB2_EINVAL, "null argument");
+    const double n = (double)(n_total > 0 ? n_total : X->rows), two = 2.0;
+    H s1, mu, d, d2, v, var, sd, xc, Z, z2, r, m, idx, s;
+    DB2_TRY(db2_aggCol(ctx, DB2_AGG_SUM, &s1, X));
+    DB2_TRY(combine(ctx, s1));
+    DB2_TRY(db2_ewBinaryObjSca(ctx, DB2_DIV, &mu, s1, &n));
+    DB2_TRY(db2_ewBinaryMat(ctx, DB2_SUB, &d, X, mu));
+    DB2_TRY(db2_ewBinaryObjSca(ctx, DB2_POW, &d2, d, &two));
+    d.reset();
+    DB2_TRY(db2_aggCol(ctx, DB2_AGG_SUM, &v, d2));
+    d2.reset();
+    DB2_TRY(combine(ctx, v));
+    DB2_TRY(db2_ewBinaryObjSca(ctx, DB2_DIV, &var, v, &n));
+    DB2_TRY(db2_ewUnaryMat(ctx, DB2_U_SQRT, &sd, var));
+    DB2_TRY(db2_ewBinaryMat(ctx, DB2_SUB, &xc, X, mu));
+    DB2_TRY(db2_ewBinaryMat(ctx, DB2_DIV, &Z, xc, sd));
+    xc.reset();
+    DB2_TRY(db2_ewBinaryObjSca(ctx, DB2_POW, &z2, Z, &two));
+    DB2_TRY(db2_aggRow(ctx, DB2_AGG_SUM, &r, z2));
+    z2.reset();
+    DB2_TRY(db2_aggRow(ctx, DB2_AGG_MAX, &m, Z));
+    DB2_TRY(db2_aggRow(ctx, DB2_AGG_IDXMAX, &idx, Z));
+    Z.reset();
+    if (ev_rows_begin)
+        DB2_TRY(db2_event_record(ev_rows_begin, ctx->stream));
+    void *unused = nullptr;
+    DB2_TRY(db2_matrix_device_ptr(r, &unused, nullptr)); // the three row aggregations come out of one pass over X
+    if (ev_rows_end)
+        DB2_TRY(db2_event_record(ev_rows_end, ctx->stream));
+    DB2_TRY(db2_aggCol(ctx, DB2_AGG_SUM, &s, r));
+    DB2_TRY(combine(ctx, s));
+    *mu_out = mu.release();
+    *sd_out = sd.release();
+    *r_out = r.release();
+    *max_out = m.release();
+    *idx_out = idx.release();
+    *s_out = s.release();
+    return DB2_OK;
+    DB2_API_END
+}
+
 // K-means assignment + update (test/api/cli/algorithms/kmeans.daphne:14-21):
 //   xs = sum(X ^ 2, 0);
 //   for i: D = (X @ t(C)) * -2.0 + xs + t(sum(C ^ 2, 0)); a = idxMin(D, 0);

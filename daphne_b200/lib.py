@@ -115,6 +115,7 @@ _SIGS = {
     "db2_dist_from_host": (i32, [vp, i32, i64, i64, i64, vp, _P(vp)]),
     "db2_dist_from_matrix": (i32, [vp, vp, i32, _P(vp)]),
     "db2_dist_from_shards": (i32, [vp, _P(vp), i32, _P(vp)]),
+    "db2w_standardise": (i32, [vp, vp, i64, vp, vp, vp, vp, vp, vp, vp, vp]),
     "db2w_standardise_group": (i32, [vp, vp, _P(vp), _P(vp), _P(vp), _P(vp), _P(vp), _P(vp)]),
     "db2_dist_info": (i32, [vp, _P(i32), _P(i64), _P(i64), _P(i32)]),
     "db2_dist_shard": (i32, [vp, i32, _P(vp), _P(i64)]),

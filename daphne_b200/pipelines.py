@@ -46,6 +46,15 @@ class Probe:
 
         return _S()
 
+    def pair(self, name: str, nbytes: int):
+        """Two fresh events for a caller that records them itself (native code): (begin, end)."""
+        import ctypes as C
+        e0, e1 = C.c_void_p(), C.c_void_p()
+        self._lib.db2_event_create(C.byref(e0))
+        self._lib.db2_event_create(C.byref(e1))
+        self._pairs.setdefault(name, []).append((e0, e1, nbytes))
+        return e0, e1
+
     def summary(self):
         """The section with the largest total time: name, launches, average ms, algorithmic GB/s."""
         import ctypes as C
@@ -278,6 +287,23 @@ def connected_components_native(ctx, G, maxi: int = 1000, row_block: Optional[tu
     h, it = C.c_void_p(), C.c_int64()
     check(lib.db2w_connected_components(ctx.handle, G.handle, int(lo), int(maxi), C.byref(h), C.byref(it)))
     return ComponentsResult(K.DenseMatrix(ctx, h), it.value)
+
+
+def standardise_aggregate_native(ctx, X, n_total: Optional[int] = None, probe=None) -> StandardiseResult:
+    """standardise_aggregate through db2w_standardise: the same operator calls, made from C++.  Row shards are
+    combined through the communicator of the context; s stays a 1 x 1 device matrix until it is read."""
+    import ctypes as C
+
+    from .lib import check, lib
+    e0 = e1 = None
+    if probe is not None:
+        e0, e1 = probe.pair("fused_row_kernel (Z=(X-mu)/sd; rowSums(Z^2), rowMaxs(Z), idxMax(Z))",
+                            X.rows * (X.cols * 8 + 24))
+    h = [C.c_void_p() for _ in range(6)]
+    check(lib.db2w_standardise(ctx.handle, X.handle, int(X.rows if n_total is None else n_total),
+                               *[C.byref(x) for x in h], e0, e1))
+    mu, sd, r, m, i, s = (K.DenseMatrix(ctx, x) for x in h)
+    return StandardiseResult(mu, sd, r, s, m, i)
 
 
 def kmeans_native(ctx, X, C0, iterations: int = 10) -> KMeansResult:

@@ -523,6 +523,13 @@ int db2w_kmeans(db2_context *ctx, db2_matrix *X, db2_matrix *C0, int iterations,
 /* lmDS (scripts/algorithms/lmDS_.daph:98-112): A = t(X) @ X + lambda I (syrk), b = t(X) @ y (gemv), beta = solve(A, b) */
 int db2w_normal_equations(db2_context *ctx, db2_matrix *X, db2_matrix *y, double lambda, db2_matrix **A,
                           db2_matrix **b, db2_matrix **beta);
+/* The column standardisation + aggregation pipeline (cfg2) on one context; with a communicator on the context every
+ * rank calls it on its row shard with n_total = the global row count.  *s_out is a 1 x 1 matrix on the device (the
+ * sum over all shards).  ev_rows_begin / ev_rows_end: optional events recorded around the pass over X that produces
+ * the three row results (for measurements). */
+int db2w_standardise(db2_context *ctx, db2_matrix *X, int64_t n_total, db2_matrix **mu_out, db2_matrix **sd_out,
+                     db2_matrix **r_out, db2_matrix **max_out, db2_matrix **idx_out, db2_matrix **s_out,
+                     void *ev_rows_begin, void *ev_rows_end);
 /* Column standardisation and aggregation over the devices of a group, in ONE process: three pipelines through
  * db2_vectorizedPipelineGroup (column sums: ADD; squared deviations from the global mean: ADD; the row results: ROWS,
  * and their sum: ADD) with compiled bodies that issue the operator calls of

@@ -65,6 +65,14 @@ def _worker(rank, world, port, out_dir):
     res["collectives"] = ctx.stats()["collectives"] - c0
     res["mu"], res["sd"], res["s"] = r.mu.to_numpy(), r.sd.to_numpy(), r.s
     res["r"], res["m"], res["i"] = (comm.allgather_ragged(v.to_numpy()) for v in (r.r, r.row_max, r.row_idx_max))
+    lo, hi = row_block(x.shape[0], rank, world)
+    c0 = ctx.stats()["collectives"]
+    rn = pipelines.standardise_aggregate_native(ctx, K.DenseMatrix.from_numpy(ctx, np.ascontiguousarray(x[lo:hi])),
+                                                x.shape[0])
+    res["collectives_native"] = ctx.stats()["collectives"] - c0
+    res["native_equal"] = all(np.array_equal(a.to_numpy(), b.to_numpy()) for a, b in
+                              ((r.mu, rn.mu), (r.sd, rn.sd), (r.r, rn.r), (r.row_max, rn.row_max),
+                               (r.row_idx_max, rn.row_idx_max))) and rn.s == r.s
     lo, hi = row_block(g.shape[0], rank, world)
     G = K.CSRMatrix.from_scipy(ctx, g[lo:hi])
     cc = pipelines.connected_components_native(ctx, G, 1000, (lo, hi))
@@ -95,6 +103,7 @@ def test_two_gpus_equal_one_gpu(tmp_path, ctx):
     for r in ranks:
         # one exchange for the statistics and one for the final scalar
         assert int(r["collectives"]) == 2, f"collectives per standardisation pipeline: {int(r['collectives'])}"
+        assert int(r["collectives_native"]) == 2 and bool(r["native_equal"])  # the same calls, made from C++
         np.testing.assert_allclose(r["mu"], one.mu.to_numpy(), rtol=1e-13)
         np.testing.assert_allclose(r["sd"], one.sd.to_numpy(), rtol=1e-12)
         assert abs(float(r["s"]) - one.s) <= 1e-10 * abs(one.s)

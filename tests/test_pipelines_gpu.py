@@ -251,6 +251,12 @@ def test_native_call_sequences_equal_the_python_ones(ctx):
         a, b = p.connected_components(ctx, G, maxi=maxi), p.connected_components_native(ctx, G, maxi=maxi)
         assert a.iterations == b.iterations == maxi
         assert_bits_equal(a.c.to_numpy(), b.c.to_numpy(), f"components, at most {maxi} trips")
+    xs = 5.0 + 2.0 * np.random.default_rng(4).standard_normal((300000, 32))
+    Xs = k.DenseMatrix.from_numpy(ctx, xs)
+    sa, sb = p.standardise_aggregate(ctx, Xs), p.standardise_aggregate_native(ctx, Xs)
+    for u, v in ((sa.mu, sb.mu), (sa.sd, sb.sd), (sa.r, sb.r), (sa.row_max, sb.row_max), (sa.row_idx_max, sb.row_idx_max)):
+        assert_bits_equal(u.to_numpy(), v.to_numpy(), "standardise")
+    assert abs(sa.s - sb.s) <= 1e-12 * abs(sa.s)          # one is a full aggregation, the other a column sum of r
     x = np.random.default_rng(3).random((150000, 64))
     c0 = x[:50].copy()
     X, C0 = k.DenseMatrix.from_numpy(ctx, x), k.DenseMatrix.from_numpy(ctx, c0)
