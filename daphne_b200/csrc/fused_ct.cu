@@ -420,77 +420,83 @@ struct RtOperand {
     int cw; // columns of the chunk that exist (even)
 };
 
-template <int OP, bool REV, int KIND>
-__device__ __noinline__ void rt_step(unsigned walk0, const RtOperand so) {
+// one group of GR elements of the row; WHOLE: all of them exist (no column tests)
+template <int OP, bool REV, int KIND, bool WHOLE>
+__device__ __forceinline__ void rt_step_group(unsigned walk0, const RtOperand &so, int g) {
+    double v[GR], o[GR], y[GR];
 #pragma unroll
-    for (int g = 0; g < CK / GR; g++) {
-        if (g * GR < so.cw) { // a group that straddles the end works on padding nobody reads
-            double v[GR], o[GR], y[GR];
+    for (int j = 0; j < GR / 2; j++) {
+        const double2 xy = lds128(walk0 ^ (unsigned)((g * (GR / 2) + j) << 4));
+        v[2 * j] = xy.x;
+        v[2 * j + 1] = xy.y;
+    }
+    if constexpr (KIND == FK_ROWVEC) {
 #pragma unroll
-            for (int j = 0; j < GR / 2; j++) {
-                const double2 xy = lds128(walk0 ^ (unsigned)((g * (GR / 2) + j) << 4));
-                v[2 * j] = xy.x;
-                v[2 * j + 1] = xy.y;
+        for (int j = 0; j < GR / 2; j++) {
+            o[2 * j] = o[2 * j + 1] = y[2 * j] = y[2 * j + 1] = 0.0;
+            if (WHOLE || g * GR + 2 * j < so.cw) {
+                const double2 t = lds128(so.vec + (unsigned)((g * GR + 2 * j) * 8));
+                o[2 * j] = t.x;
+                o[2 * j + 1] = t.y;
+                if constexpr (OP == FO_DIV && !REV) {
+                    const double2 u = lds128(so.vec + (unsigned)((so.cols + g * GR + 2 * j) * 8));
+                    y[2 * j] = u.x;
+                    y[2 * j + 1] = u.y;
+                }
             }
+        }
+    } else if constexpr (KIND == FK_MATRIX) {
+#pragma unroll
+        for (int i = 0; i < GR; i++) {
+            o[i] = (WHOLE || g * GR + i < so.cw) ? __ldg(so.mat + g * GR + i) : 0.0;
+            y[i] = __longlong_as_double(0x7ff8000000000000ll); // no helper: generic division
+        }
+    } else {
+#pragma unroll
+        for (int i = 0; i < GR; i++) {
+            o[i] = so.scal;
+            y[i] = so.yscal;
+        }
+    }
+    if constexpr (OP == FO_DIV && !REV) {
+        double q1[GR];
+        unsigned worst = 0;
+#pragma unroll
+        for (int i = 0; i < GR; i++) {
+            const double q = __dmul_rn(v[i], y[i]);
+            const double r = __fma_rn(-q, o[i], v[i]);
+            q1[i] = __fma_rn(r, y[i], q);
+            worst = max(worst, fast_div_window_pos(q1[i]));
+        }
+        if (worst < FAST_DIV_WINDOW) {
 #pragma unroll
             for (int i = 0; i < GR; i++)
-                o[i] = y[i] = 0.0;
-            if constexpr (KIND == FK_ROWVEC) {
+                v[i] = q1[i];
+        } else {
 #pragma unroll
-                for (int j = 0; j < GR / 2; j++) {
-                    if (g * GR + 2 * j < so.cw) {
-                        const double2 t = lds128(so.vec + (unsigned)((g * GR + 2 * j) * 8));
-                        o[2 * j] = t.x;
-                        o[2 * j + 1] = t.y;
-                        if constexpr (OP == FO_DIV && !REV) {
-                            const double2 u = lds128(so.vec + (unsigned)((so.cols + g * GR + 2 * j) * 8));
-                            y[2 * j] = u.x;
-                            y[2 * j + 1] = u.y;
-                        }
-                    }
-                }
-            } else if constexpr (KIND == FK_MATRIX) {
-#pragma unroll
-                for (int i = 0; i < GR; i++) {
-                    if (g * GR + i < so.cw)
-                        o[i] = __ldg(so.mat + g * GR + i);
-                    y[i] = __longlong_as_double(0x7ff8000000000000ll); // no helper: generic division
-                }
-            } else if constexpr (KIND == FK_SCALAR) {
-#pragma unroll
-                for (int i = 0; i < GR; i++) {
-                    o[i] = so.scal;
-                    y[i] = so.yscal;
-                }
-            }
-            if constexpr (OP == FO_DIV && !REV) {
-                double q1[GR];
-                unsigned worst = 0;
-#pragma unroll
-                for (int i = 0; i < GR; i++) {
-                    const double q = __dmul_rn(v[i], y[i]);
-                    const double r = __fma_rn(-q, o[i], v[i]);
-                    q1[i] = __fma_rn(r, y[i], q);
-                    worst = max(worst, fast_div_window_pos(q1[i]));
-                }
-                if (worst < FAST_DIV_WINDOW) {
-#pragma unroll
-                    for (int i = 0; i < GR; i++)
-                        v[i] = q1[i];
-                } else {
-#pragma unroll
-                    for (int i = 0; i < GR; i++)
-                        v[i] = fast_div(v[i], o[i], y[i]);
-                }
-            } else {
-#pragma unroll
-                for (int i = 0; i < GR; i++)
-                    v[i] = apply<OP, REV>(v[i], o[i], 0.0);
-            }
-#pragma unroll
-            for (int j = 0; j < GR / 2; j++)
-                sts128(walk0 ^ (unsigned)((g * (GR / 2) + j) << 4), v[2 * j], v[2 * j + 1]);
+            for (int i = 0; i < GR; i++)
+                v[i] = fast_div(v[i], o[i], y[i]);
         }
+    } else {
+#pragma unroll
+        for (int i = 0; i < GR; i++)
+            v[i] = apply<OP, REV>(v[i], o[i], 0.0);
+    }
+#pragma unroll
+    for (int j = 0; j < GR / 2; j++)
+        sts128(walk0 ^ (unsigned)((g * (GR / 2) + j) << 4), v[2 * j], v[2 * j + 1]);
+}
+
+template <int OP, bool REV, int KIND>
+__device__ __noinline__ void rt_step(unsigned walk0, const RtOperand so) {
+    if (so.cw == CK) { // the usual case: all columns of the chunk exist
+#pragma unroll
+        for (int g = 0; g < CK / GR; g++)
+            rt_step_group<OP, REV, KIND, true>(walk0, so, g);
+    } else {
+#pragma unroll 1
+        for (int g = 0; g * GR < so.cw; g++) // a group that straddles the end works on padding nobody reads
+            rt_step_group<OP, REV, KIND, false>(walk0, so, g);
     }
 }
 
@@ -541,11 +547,10 @@ __device__ __forceinline__ void rt_dispatch(int op, bool rev, int kind, unsigned
     }
 }
 
-// the taps that see the row as it stands now (bit a of mask = tap a), fed in element order
-__device__ __forceinline__ void rt_feed(unsigned walk0, TapState<AnyTaps> &ts, const FusedProgram &P, unsigned mask,
-                                        int cc, int cw) {
-    if (mask == 0)
-        return;
+// the taps that see the row as it stands now (bit a of mask = tap a), fed in element order; FULL: all CK columns exist
+template <bool FULL>
+__device__ __forceinline__ void rt_feed_chunk(unsigned walk0, TapState<AnyTaps> &ts, const FusedProgram &P,
+                                              unsigned mask, int cc, int cw) {
     double v[CK];
 #pragma unroll
     for (int j = 0; j < CK / 2; j++) {
@@ -561,13 +566,15 @@ __device__ __forceinline__ void rt_feed(unsigned walk0, TapState<AnyTaps> &ts, c
                 double acc = ts.v[a];
 #pragma unroll
                 for (int i = 0; i < CK; i++)
-                    acc = (i < cw) ? __dadd_rn(acc, v[i]) : acc;
+                    if (FULL || i < cw)
+                        acc = __dadd_rn(acc, v[i]);
                 ts.v[a] = acc;
             } else if (kind == FT_PROD) {
                 double acc = ts.v[a];
 #pragma unroll
                 for (int i = 0; i < CK; i++)
-                    acc = (i < cw) ? __dmul_rn(acc, v[i]) : acc;
+                    if (FULL || i < cw)
+                        acc = __dmul_rn(acc, v[i]);
                 ts.v[a] = acc;
             } else {
                 if (cc == 0)
@@ -577,14 +584,14 @@ __device__ __forceinline__ void rt_feed(unsigned walk0, TapState<AnyTaps> &ts, c
                 if (kind == FT_MAX) {
 #pragma unroll
                     for (int i = 0; i < CK; i++) {
-                        const bool better = (i < cw) & (v[i] > best);
+                        const bool better = (FULL || i < cw) && (v[i] > best);
                         best = better ? v[i] : best;
                         bc = better ? cc + i : bc;
                     }
                 } else {
 #pragma unroll
                     for (int i = 0; i < CK; i++) {
-                        const bool better = (i < cw) & (v[i] < best);
+                        const bool better = (FULL || i < cw) && (v[i] < best);
                         best = better ? v[i] : best;
                         bc = better ? cc + i : bc;
                     }
@@ -594,6 +601,15 @@ __device__ __forceinline__ void rt_feed(unsigned walk0, TapState<AnyTaps> &ts, c
             }
         }
     }
+}
+__device__ __forceinline__ void rt_feed(unsigned walk0, TapState<AnyTaps> &ts, const FusedProgram &P, unsigned mask,
+                                        int cc, int cw) {
+    if (mask == 0)
+        return;
+    if (cw == CK)
+        rt_feed_chunk<true>(walk0, ts, P, mask, cc, cw);
+    else
+        rt_feed_chunk<false>(walk0, ts, P, mask, cc, cw);
 }
 
 __device__ __forceinline__ void walk_row_rt(unsigned walk0, const FusedProgram &P, TapState<AnyTaps> &ts,
