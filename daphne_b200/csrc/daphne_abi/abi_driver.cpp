@@ -414,6 +414,24 @@ int drv_binary_typed(const char *name, int dtype, const void *a, int64_t ar, int
     default: return binary_t<double>(name, (const double *)a, ar, ac, (const double *)b, br, bc, (const double *)scalar, (double *)out);
     }
 }
+// res = matMul(lhs, rhs, transa, transb) by catalog name for an integer value type (DB2_I64 or DB2_I32); `out` holds
+// the m x n result
+int drv_matmul_int(const char *name, int dtype, const void *a, int64_t ar, int64_t ac, const void *b, int64_t br,
+                   int64_t bc, int ta, int tb, void *out) {
+    auto run = [&](auto zero) {
+        using VT = decltype(zero);
+        using DM = DenseMatrix<VT>;
+        return guarded([&] {
+            DM *A = host_matrix_t<VT>((const VT *)a, ar, ac), *B = host_matrix_t<VT>((const VT *)b, br, bc), *R = nullptr;
+            reinterpret_cast<void (*)(DM **, const DM *, const DM *, bool, bool, int, DaphneContext *)>(sym(name))(
+                &R, A, B, ta != 0, tb != 0, 1, &g_ctx);
+            copy_out_t<VT>(R, (VT *)out);
+            DataObjectFactory::destroy(A, B, R);
+            return 0;
+        });
+    };
+    return dtype == DB2_I32 ? run(int32_t{}) : run(int64_t{});
+}
 // fill through CUDA_fill__DenseMatrix_<vt>__<vt>__size_t__size_t for the one-byte value types (bool, uint8_t)
 int drv_fill_u8(int as_bool, int value, int64_t rows, int64_t cols, uint8_t *out) {
     return guarded([&] {

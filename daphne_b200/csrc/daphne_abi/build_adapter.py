@@ -56,6 +56,8 @@ def default_source() -> Path:
 
 def _ext_instantiation_ok(header: str, inst) -> bool:
     """Dense matrices of the value types the device kernels implement; index results are size_t."""
+    if header == "MatMul.h" and all(list(t) in (["DenseMatrix", "int64_t"], ["DenseMatrix", "int32_t"]) for t in inst):
+        return len({t[1] for t in inst}) == 1  # dense integer products (the reference's Eigen path)
     if header in ("EwBinaryMat.h", "MatMul.h", "Gemv.h"):
         return [list(t) for t in inst] == CSR_HEADERS[header]
     vts, scalars = [], []

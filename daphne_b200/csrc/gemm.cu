@@ -539,7 +539,18 @@ int tf32_gemm(const float *A, int64_t lda, bool ta, const float *B, int64_t ldb,
 
 using namespace db2;
 
+namespace db2 {
+int gemm_int(int dtype, const void *lhs, int64_t lhs_ld, bool ta, const void *rhs, int64_t rhs_ld, bool tb, void *res,
+             int64_t ldc, int64_t m, int64_t n, int64_t k, cudaStream_t st); // gemm_int.cu
+}
+
+static bool int_matmul_type(int dtype) {
+    return dtype == DB2_I64 || dtype == DB2_I32 || dtype == DB2_U64 || dtype == DB2_U32;
+}
+
 extern "C" size_t db2k_matmul_scratch_bytes(int dtype, int64_t m, int64_t n, int64_t k) {
+    if (int_matmul_type(dtype))
+        return 256;
     if (dtype == DB2_F32)
         return tc::tf32_scratch_bytes(m, n, k, false);
     size_t worst = 0;
@@ -553,13 +564,16 @@ extern "C" size_t db2k_matmul_scratch_bytes(int dtype, int64_t m, int64_t n, int
 extern "C" int db2k_matmul(int dtype, const void *lhs, int64_t lhs_rows, int64_t lhs_cols, int64_t lhs_ld,
                            const void *rhs, int64_t rhs_rows, int64_t rhs_cols, int64_t rhs_ld, int transa, int transb,
                            void *res, int64_t res_ld, void *scratch, size_t scratch_bytes, void *stream) {
-    DB2_CHECK(dtype == DB2_F64 || dtype == DB2_F32, DB2_EUNSUPPORTED,
-              "matMul: only double and float are implemented on the device");
+    DB2_CHECK(dtype == DB2_F64 || dtype == DB2_F32 || int_matmul_type(dtype), DB2_EUNSUPPORTED,
+              "matMul: value type %d is not implemented on the device", dtype);
     const int64_t m = transa ? lhs_cols : lhs_rows, k = transa ? lhs_rows : lhs_cols;
     const int64_t k2 = transb ? rhs_cols : rhs_rows, n = transb ? rhs_rows : rhs_cols;
     DB2_CHECK(k == k2, DB2_EINVAL, "MatMul - #cols of lhs and #rows of rhs must be the same, but got%lldand%lld",
               (long long)k, (long long)k2);
     DB2_CHECK((lhs && rhs && res) || m * n == 0, DB2_EINVAL, "null operand");
+    if (int_matmul_type(dtype))
+        return gemm_int(dtype, lhs, lhs_ld, transa != 0, rhs, rhs_ld, transb != 0, res, res_ld, m, n, k,
+                        as_stream(stream));
     if (dtype == DB2_F32)
         return tc::tf32_gemm(static_cast<const float *>(lhs), lhs_ld, transa != 0, static_cast<const float *>(rhs),
                              rhs_ld, transb != 0, static_cast<float *>(res), res_ld, m, n, k, false, scratch,

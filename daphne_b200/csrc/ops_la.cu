@@ -44,8 +44,9 @@ int db2_matMul(db2_context *ctx, db2_matrix **res, db2_matrix *lhs, db2_matrix *
     DB2_API_BEGIN
     DB2_CHECK(ctx && res && lhs && rhs, DB2_EINVAL, "null argument");
     const int dt = lhs->dtype;
-    DB2_CHECK((dt == DB2_F64 || dt == DB2_F32) && rhs->dtype == dt, DB2_EUNSUPPORTED,
-              "matMul: double or float operands of one type on the device");
+    DB2_CHECK((dt == DB2_F64 || dt == DB2_F32 || dt == DB2_I64 || dt == DB2_I32 || dt == DB2_U64 || dt == DB2_U32) &&
+                  rhs->dtype == dt,
+              DB2_EUNSUPPORTED, "matMul: operands of one value type (double, float or an integer type) on the device");
     const int64_t m = transa ? lhs->cols : lhs->rows, k = transa ? lhs->rows : lhs->cols;
     const int64_t k2 = transb ? rhs->cols : rhs->rows, n = transb ? rhs->rows : rhs->cols;
     DB2_CHECK(k == k2, DB2_EINVAL, "MatMul - #cols of lhs and #rows of rhs must be the same, but got%lldand%lld",

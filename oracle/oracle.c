@@ -383,6 +383,44 @@ int orc_matmul_f64(const double *a, int64_t ar, int64_t ac, int64_t lda, const d
         }
     return 0;
 }
+
+/* MatMul for int64_t / int32_t (MatMul.cpp:40-57, 78-134 and the gemm specialisations below them: Eigen products, a
+ * third-party dependency that is not part of the reference tree).  Integer products and sums wrap and are associative,
+ * so every evaluation order gives these bits; the arithmetic is done on the unsigned type to stay defined. */
+int orc_matmul_i64(const int64_t *a, int64_t ar, int64_t ac, int64_t lda, const int64_t *b, int64_t br, int64_t bc,
+                   int64_t ldb, int transa, int transb, int64_t *res, int64_t ldc) {
+    const int64_t m = transa ? ac : ar, k = transa ? ar : ac, k2 = transb ? bc : br, n = transb ? br : bc;
+    if (k != k2)
+        return 1;
+    for (int64_t i = 0; i < m; i++)
+        for (int64_t j = 0; j < n; j++) {
+            uint64_t s = 0;
+            for (int64_t l = 0; l < k; l++) {
+                const uint64_t x = (uint64_t)(transa ? a[l * lda + i] : a[i * lda + l]);
+                const uint64_t y = (uint64_t)(transb ? b[j * ldb + l] : b[l * ldb + j]);
+                s += x * y;
+            }
+            res[i * ldc + j] = (int64_t)s;
+        }
+    return 0;
+}
+int orc_matmul_i32(const int32_t *a, int64_t ar, int64_t ac, int64_t lda, const int32_t *b, int64_t br, int64_t bc,
+                   int64_t ldb, int transa, int transb, int32_t *res, int64_t ldc) {
+    const int64_t m = transa ? ac : ar, k = transa ? ar : ac, k2 = transb ? bc : br, n = transb ? br : bc;
+    if (k != k2)
+        return 1;
+    for (int64_t i = 0; i < m; i++)
+        for (int64_t j = 0; j < n; j++) {
+            uint32_t s = 0;
+            for (int64_t l = 0; l < k; l++) {
+                const uint32_t x = (uint32_t)(transa ? a[l * lda + i] : a[i * lda + l]);
+                const uint32_t y = (uint32_t)(transb ? b[j * ldb + l] : b[l * ldb + j]);
+                s += x * y;
+            }
+            res[i * ldc + j] = (int32_t)s;
+        }
+    return 0;
+}
 /* Syrk<Dense,Dense> (Syrk.h:51-71): cblas_dsyrk on the upper triangle, then the mirror loop (:65-69) */
 int orc_syrk_f64(const double *arg, int64_t rows, int64_t cols, int64_t ld, int trans_left, double *res) {
     const int64_t n = trans_left ? cols : rows, k = trans_left ? rows : cols;

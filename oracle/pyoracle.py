@@ -138,7 +138,23 @@ def _matmul(lib, prefix, lhs, rhs, transa=False, transb=False):
 
 
 def matMul(lhs, rhs, transa=False, transb=False):
+    if np.asarray(lhs).dtype in (np.int64, np.int32):
+        return _matmul_int(lhs, rhs, transa, transb)
     return _matmul(_lib, "orc", lhs, rhs, transa, transb)
+
+
+def _matmul_int(lhs, rhs, transa=False, transb=False):
+    """The integer forms (int64, int32): wrapping products and sums."""
+    dt = np.asarray(lhs).dtype
+    lhs, rhs = _mat(np.asarray(lhs, dtype=dt)), _mat(np.asarray(rhs, dtype=dt))
+    m = lhs.shape[1] if transa else lhs.shape[0]
+    n = rhs.shape[0] if transb else rhs.shape[1]
+    res = np.empty((m, n), dtype=dt)
+    f = getattr(_lib, "orc_matmul_i64" if dt == np.int64 else "orc_matmul_i32")
+    f.argtypes = [C.c_void_p, i64, i64, i64, C.c_void_p, i64, i64, i64, C.c_int, C.c_int, C.c_void_p, i64]
+    _chk(f(_p(lhs), lhs.shape[0], lhs.shape[1], _ld(lhs), _p(rhs), rhs.shape[0], rhs.shape[1], _ld(rhs),
+           int(transa), int(transb), _p(res), max(n, 1)))
+    return res
 
 
 def _syrk(lib, prefix, arg, transLeft=True):

@@ -385,3 +385,25 @@ def test_float_entries_of_the_contraction_kernels_compute(drv):
     exact = m.astype(np.float64).T @ v.astype(np.float64)
     bound = (500 * 2.0 ** -24 + 2.0 ** -19) * (np.abs(m).astype(np.float64).T @ np.abs(v).astype(np.float64))
     assert np.all(np.abs(out - exact) <= bound)
+
+
+@pytest.mark.gpu
+def test_integer_matmul_by_its_catalog_name(drv):
+    """_matMul__DenseMatrix_int64_t__... / _int32_t__... (the reference's Eigen path) are served by the extension
+    catalog: bit-exact against the wrapping triple loop, all transpose combinations."""
+    from oracle import pyoracle as o
+    ext = json.loads((ABI / "B200ExtCatalog.json").read_text())
+    names = {e["kernelFuncName"] for e in ext}
+    rng = np.random.default_rng(5)
+    for vt, dtype, code in (("int64_t", np.int64, 2), ("int32_t", np.int32, 4)):
+        name = f"_matMul__DenseMatrix_{vt}__DenseMatrix_{vt}__DenseMatrix_{vt}__bool__bool"
+        assert name in names
+        for ta in (0, 1):
+            for tb in (0, 1):
+                a = rng.integers(-2000, 2000, size=(33, 70) if ta else (70, 33)).astype(dtype)
+                b = rng.integers(-2000, 2000, size=(45, 33) if tb else (33, 45)).astype(dtype)
+                out = np.empty((70, 45), dtype=dtype)
+                rc = drv.drv_matmul_int(name.encode(), code, _p(a), i64(a.shape[0]), i64(a.shape[1]), _p(b),
+                                        i64(b.shape[0]), i64(b.shape[1]), ta, tb, _p(out))
+                assert rc == 0, drv.drv_last_error()
+                assert np.array_equal(out, o.matMul(a, b, bool(ta), bool(tb))), (vt, ta, tb)

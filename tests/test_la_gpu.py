@@ -324,3 +324,30 @@ def test_ctable(ctx):
     assert_bits_equal(k.ctable(A, B, 3.0, 5, 20).to_numpy(), o.ctable(a, b, 3.0, 5, 20), "ctable, given shape")
     with pytest.raises(k.Db2Error, match="same number of rows"):
         k.ctable(A, R)
+
+
+@pytest.mark.parametrize("dtype", [np.int64, np.int32])
+def test_integer_matmul_bit_exact(ctx, dtype):
+    """MatMul for the integer value types (the reference's Eigen path): wrapping arithmetic, so bit-exact against the
+    triple loop for every transpose combination, ragged tile edges and values that overflow."""
+    k, o = _k()
+    rng = np.random.default_rng(17)
+    info = np.iinfo(dtype)
+    for (m, n, kk) in [(1, 1, 1), (3, 5, 7), (64, 64, 16), (65, 130, 33), (200, 1, 300), (1, 257, 129)]:
+        for ta in (False, True):
+            for tb in (False, True):
+                a = rng.integers(-50, 50, size=(kk, m) if ta else (m, kk)).astype(dtype)
+                b = rng.integers(-50, 50, size=(n, kk) if tb else (kk, n)).astype(dtype)
+                got = k.matMul(k.DenseMatrix.from_numpy(ctx, a), k.DenseMatrix.from_numpy(ctx, b), ta, tb).to_numpy()
+                exp = o.matMul(a, b, ta, tb)
+                assert got.dtype == dtype and np.array_equal(got, exp), (m, n, kk, ta, tb)
+                la, lb = (a.T if ta else a), (b.T if tb else b)
+                assert np.array_equal(got, (la.astype(np.int64) @ lb.astype(np.int64)).astype(dtype))
+    a = rng.integers(info.min, info.max, size=(70, 90), dtype=dtype)      # products and sums wrap
+    b = rng.integers(info.min, info.max, size=(90, 40), dtype=dtype)
+    got = k.matMul(k.DenseMatrix.from_numpy(ctx, a), k.DenseMatrix.from_numpy(ctx, b)).to_numpy()
+    assert np.array_equal(got, o.matMul(a, b))
+    A = k.DenseMatrix.from_numpy(ctx, rng.integers(-9, 9, size=(500, 20)).astype(dtype))
+    v = k.sliceRow(A, 100, 300)                                            # a row view keeps its offset
+    c = rng.integers(-9, 9, size=(20, 6)).astype(dtype)
+    assert np.array_equal(k.matMul(v, k.DenseMatrix.from_numpy(ctx, c)).to_numpy(), o.matMul(A.to_numpy()[100:300], c))
