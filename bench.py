@@ -318,11 +318,12 @@ def normal_equations_leg(ctx, comm, lib, host, world, args) -> dict:
     step_ms = comm.max_float(ms.value / reps)
     syrk = probe.summary()
     beta = res.beta.to_numpy()
-    flop = float(n) * d * (d + 1)
+    flop = float(n) * d * (d + 1) + 2.0 * n * d  # BLAS syrk count + t(X) y
     peak = fp64_peak_live(ctx, lib)
     return {"workload": f"t(X)X + lambda I, t(X)y, solve on f64 {n} x {d} per GPU (U[-1,1)), combined over {world} GPU(s)",
             "ms_per_step": step_ms, "rows_per_s": n * world / (step_ms * 1e-3),
-            "syrk_ms": syrk["avg_ms"], "syrk_tflops_syrk_count": flop / (syrk["avg_ms"] * 1e-3) / 1e12,
+            "syrk_gemv_ms": syrk["avg_ms"], "syrk_gemv_kernel": syrk["name"],
+            "syrk_tflops_syrk_count": flop / (syrk["avg_ms"] * 1e-3) / 1e12,
             "syrk_frac_of_fp64_peak": flop / (syrk["avg_ms"] * 1e-3) / 1e12 / peak["tflops"],
             "fp64_peak_measured": peak, "beta_max_abs_err_vs_w": float(np.abs(beta - w).max())}
 

@@ -68,6 +68,12 @@ struct GemmArgs {
     int64_t k_per_split_diag;
     int syrk;            // only tiles with tile_n*BN + BN > tile_m*BM are computed (upper triangle incl. diagonal)
     int aligned;         // operands allow 16-byte copies (bases 16-byte aligned, even leading dimensions)
+    // t(X) y next to t(X) X (syrk with A = B = X stored K x M): the warps of a diagonal tile that have no sub-tile to
+    // compute form the products of their tile's columns with y from the operand stages that pass through shared
+    // memory anyway, so X is read once for both results.  yv: K contiguous doubles, 16-byte aligned;
+    // ypart: [splits_diag][M] partial sums, added up in split order by gemv_fold_kernel.
+    const double *yv;
+    double *ypart;
 };
 
 // Loads one stage.  TA: A is stored K x M (contraction index = row);  !TA: A is M x K.  Same for TB with N.
@@ -187,6 +193,7 @@ __global__ void __launch_bounds__(TileCfg<BM, BN>::THREADS) gemm_f64_kernel(cons
     constexpr int A_ELEMS = TA ? KC * PA : BM * PK;
     constexpr int B_ELEMS = TB ? BN * PK : KC * PB;
     extern __shared__ __align__(16) double gsm[];
+    double *ysm = gsm + (size_t)STAGES * (A_ELEMS + B_ELEMS); // [STAGES][KC]: the stage's piece of y (fold only)
     const int tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
     // warp -> sub-tile: rotating the column by the row spreads the warps that stay active in a diagonal syrk tile
     // (column block >= row block) evenly over the four scheduler partitions (warp id mod 4)
@@ -200,6 +207,10 @@ __global__ void __launch_bounds__(TileCfg<BM, BN>::THREADS) gemm_f64_kernel(cons
     const bool diag_tile = ga.syrk && BM == BN && m0 == n0;
     if ((int)blockIdx.z >= (diag_tile ? ga.splits_diag : ga.splits))
         return;
+    // fold: this CTA also forms t(X) y for its 128 columns; four of the six idle warps take 32 columns each
+    const bool fold = TA && !TB && BM == 128 && BN == 128 && diag_tile && ga.yv != nullptr;
+    const int yrank = wm * (wm - 1) / 2 + wn; // 0..5 over the warps below the diagonal (wn < wm)
+    double ysum = 0.0;
     const int64_t kps = diag_tile ? ga.k_per_split_diag : ga.k_per_split;
     const int64_t k_begin = (int64_t)blockIdx.z * kps;
     const int64_t k_end = (k_begin + kps < ga.K) ? k_begin + kps : ga.K;
@@ -234,6 +245,11 @@ __global__ void __launch_bounds__(TileCfg<BM, BN>::THREADS) gemm_f64_kernel(cons
         else
             load_stage<TA, TB, BM, BN, false>(ga, stage_a(slot), stage_b(slot), m0, n0, k0, k_end, tid, NT, !same_tile,
                                               nullptr, nullptr);
+        if (fold && tid < KC / 2) { // the rows' entries of y travel with the stage (zeros beyond the range)
+            const int64_t k = k0 + 2 * tid;
+            const int bytes = k + 2 <= k_end ? 16 : (k < k_end ? 8 : 0);
+            cp_async16_zfill(ysm + slot * KC + 2 * tid, bytes ? ga.yv + k : ga.yv, bytes);
+        }
     };
 #pragma unroll
     for (int s = 0; s < STAGES - 1; s++) {
@@ -250,8 +266,19 @@ __global__ void __launch_bounds__(TileCfg<BM, BN>::THREADS) gemm_f64_kernel(cons
                 load((int)(nx % STAGES), nx);
             cp_async_commit();
         }
-        if (!warp_active)
+        if (!warp_active) {
+            if (fold && yrank < 4) { // column yrank * 32 + lane of the tile: its 32 entries of this stage, in row order
+                const double *col = stage_a((int)(ch % STAGES)) + yrank * 32 + lane;
+                const double *ys = ysm + (int)(ch % STAGES) * KC;
+#pragma unroll
+                for (int kk = 0; kk < KC; kk += 2) {
+                    const double2 yy = *reinterpret_cast<const double2 *>(ys + kk);
+                    ysum = __fma_rn(col[kk * PA], yy.x, ysum);
+                    ysum = __fma_rn(col[(kk + 1) * PA], yy.y, ysum);
+                }
+            }
             continue;
+        }
         const double *As = stage_a((int)(ch % STAGES));
         const double *Bs = stage_b((int)(ch % STAGES));
         static_assert(KC % 16 == 0, "whole m16n8k16 steps per stage");
@@ -325,8 +352,11 @@ __global__ void __launch_bounds__(TileCfg<BM, BN>::THREADS) gemm_f64_kernel(cons
         } // kk
     }
     cp_async_wait<0>();
-    if (!warp_active)
+    if (!warp_active) {
+        if (fold && yrank < 4 && m0 + yrank * 32 + lane < ga.M)
+            ga.ypart[(size_t)blockIdx.z * ga.M + m0 + yrank * 32 + lane] = ysum;
         return;
+    }
 
     // acc[mt][nt][2 h + e]: row block h of the 16-row group mt, column 2 t + e of the 8-column block nt.  Rows: block h
     // holds the rows 2 g + h when A was stored [k][row], g + 8 h otherwise.  Columns: when B was stored [k][column]
@@ -402,6 +432,17 @@ __global__ void gemm_reduce_kernel(const double *__restrict__ part, double *__re
     }
 }
 
+// t(X) y: the diagonal tiles' partial sums, added in split order
+__global__ void gemv_fold_kernel(const double *__restrict__ ypart, int64_t n, int splits, double *__restrict__ out) {
+    const int64_t c = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= n)
+        return;
+    double a = ypart[c];
+    for (int s = 1; s < splits; s++)
+        a = __dadd_rn(a, ypart[(size_t)s * n + c]);
+    out[c] = a;
+}
+
 struct GemmPlan {
     int bm, bn, tiles_m, tiles_n, splits, splits_diag;
     int64_t k_per_split, k_per_split_diag;
@@ -411,7 +452,7 @@ struct GemmPlan {
 static size_t tile_smem(int bm, int bn, bool ta, bool tb) {
     const size_t a = ta ? (size_t)KC * (bm + 4) : (size_t)bm * pitch_k(ta, tb);
     const size_t b = tb ? (size_t)bn * pitch_k(ta, tb) : (size_t)KC * (bn + 4);
-    return 3 * (a + b) * 8; // TileCfg::STAGES
+    return 3 * (a + b + KC) * 8; // TileCfg::STAGES stages of both operands and of a piece of y
 }
 
 static GemmPlan plan_gemm(int64_t M, int64_t N, int64_t K, bool syrk, bool ta, bool tb) {
@@ -511,6 +552,15 @@ static int run_gemm(bool ta, bool tb, GemmArgs g, cudaStream_t st, void *scratch
     if (g.M == 0 || g.N == 0)
         return DB2_OK;
     const GemmPlan p = plan_gemm(g.M, g.N, g.K, g.syrk != 0, ta, tb);
+    double *yout = nullptr;
+    if (g.yv) { // t(X) y folded into the syrk: partial sums behind the partial tiles; g.ypart carries the result pointer in
+        DB2_CHECK(g.syrk && ta && !tb && p.bm == 128 && p.bn == 128 && aligned16(g.yv), DB2_EINVAL,
+                  "t(X) y can only ride along with t(X) X on 128 x 128 tiles");
+        DB2_CHECK(scratch && scratch_bytes >= p.scratch + (size_t)p.splits_diag * g.M * 8, DB2_EINVAL,
+                  "syrk + gemv scratch too small");
+        yout = g.ypart;
+        g.ypart = reinterpret_cast<double *>(static_cast<char *>(scratch) + p.scratch);
+    }
     DB2_CHECK(p.scratch == 0 || (scratch && scratch_bytes >= p.scratch), DB2_EINVAL,
               "matMul/syrk scratch too small: %zu < %zu", scratch_bytes, p.scratch);
     g.part = static_cast<double *>(scratch);
@@ -523,8 +573,14 @@ static int run_gemm(bool ta, bool tb, GemmArgs g, cudaStream_t st, void *scratch
         return dispatch_tiles<false, false>(g, p, st);
     if (!ta && tb)
         return dispatch_tiles<false, true>(g, p, st);
-    if (ta && !tb)
-        return dispatch_tiles<true, false>(g, p, st);
+    if (ta && !tb) {
+        DB2_TRY((dispatch_tiles<true, false>(g, p, st)));
+        if (yout) {
+            gemv_fold_kernel<<<(unsigned)((g.M + 255) / 256), 256, 0, st>>>(g.ypart, g.M, p.splits_diag, yout);
+            DB2_TRY(after_launch("gemv_fold_kernel"));
+        }
+        return DB2_OK;
+    }
     return dispatch_tiles<true, true>(g, p, st);
 }
 
@@ -597,6 +653,33 @@ extern "C" size_t db2k_syrk_scratch_bytes(int dtype, int64_t rows, int64_t cols,
     if (dtype == DB2_F32)
         return tc::tf32_scratch_bytes(n, n, k, true);
     return plan_gemm(n, n, k, true, trans_left != 0, trans_left == 0).scratch + 256;
+}
+
+// t(X) X and t(X) y in one pass over X (f64; the reference issues syrk and gemv, Syrk.h:40-43 and Gemv.h:51-63, and
+// reads X for each).  res: cols x cols, yres: cols contiguous doubles; yvec: rows contiguous doubles.
+extern "C" size_t db2k_syrk_gemv_scratch_bytes(int64_t rows, int64_t cols) {
+    const GemmPlan p = plan_gemm(cols, cols, rows, true, true, false);
+    return p.scratch + (size_t)p.splits_diag * cols * 8 + 256;
+}
+extern "C" int db2k_syrk_gemv_supported(int64_t rows, int64_t cols) {
+    const GemmPlan p = plan_gemm(cols, cols, rows, true, true, false);
+    return rows > 0 && p.bm == 128 && p.bn == 128;
+}
+extern "C" int db2k_syrk_gemv(const void *arg, int64_t rows, int64_t cols, int64_t ld, const void *yvec, void *res,
+                              int64_t res_ld, void *yres, void *scratch, size_t scratch_bytes, void *stream) {
+    DB2_CHECK(arg && yvec && res && yres, DB2_EINVAL, "null operand");
+    DB2_CHECK(db2k_syrk_gemv_supported(rows, cols), DB2_EUNSUPPORTED, "syrk + gemv: needs more than 64 columns");
+    GemmArgs g{};
+    g.A = g.B = static_cast<const double *>(arg);
+    g.C = static_cast<double *>(res);
+    g.lda = g.ldb = ld;
+    g.ldc = res_ld;
+    g.M = g.N = cols;
+    g.K = rows;
+    g.syrk = 1;
+    g.yv = static_cast<const double *>(yvec);
+    g.ypart = static_cast<double *>(yres); // run_gemm moves it to the scratch area and folds into yres
+    return run_gemm(true, false, g, as_stream(stream), scratch, scratch_bytes);
 }
 
 extern "C" int db2k_syrk(int dtype, const void *arg, int64_t rows, int64_t cols, int64_t ld, int trans_left, void *res,

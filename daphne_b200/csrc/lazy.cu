@@ -502,6 +502,8 @@ int lazy_force(db2_matrix *m) {
     bind_device(ctx);
     if (m->onehot)
         return onehot_force(m);
+    if (m->syrk_of)
+        return syrk_force(m);
     const uint64_t before = g_launches.load();
     int rc = DB2_OK;
     if (m->lazy) {
@@ -543,6 +545,8 @@ int lazy_flush_all(db2_context *ctx) {
 }
 
 void lazy_forget(db2_matrix *m) {
+    if (m->syrk_of && m->ctx && m->ctx->syrk_waiting == m)
+        m->ctx->syrk_waiting = nullptr;
     if (m->pend_src && m->ctx)
         unpend(m->ctx, m);
     if (m->lazy && m->ctx)

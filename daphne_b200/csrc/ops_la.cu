@@ -34,6 +34,27 @@ static int check_contraction_status(db2_context *ctx, int dtype, const void *scr
     return DB2_OK;
 }
 
+// a deferred t(X) X that something other than the matching gemv needs: the product alone
+int syrk_force(db2_matrix *m) {
+    db2_context *ctx = m->ctx;
+    bind_device(ctx);
+    const uint64_t before = g_launches.load();
+    const Operand x = *m->syrk_of;
+    m->dev = make_devbuf(ctx, (size_t)m->rows * m->cols * 8);
+    m->dev_off = 0;
+    m->dev_ld = m->cols;
+    void *scratch = nullptr;
+    DB2_TRY(ctx_scratch(ctx, db2k_syrk_scratch_bytes(DB2_F64, x.rows, x.cols, 1), &scratch));
+    DB2_TRY(db2k_syrk(DB2_F64, x.ptr(8), x.rows, x.cols, x.ld, 1, m->dev_ptr(), m->dev_ld, scratch,
+                      ctx->scratch_bytes, ctx->stream));
+    m->dev_valid = true;
+    m->syrk_of.reset();
+    if (ctx->syrk_waiting == m)
+        ctx->syrk_waiting = nullptr;
+    count(ctx, before);
+    return DB2_OK;
+}
+
 } // namespace db2
 
 using namespace db2;
@@ -84,6 +105,27 @@ int db2_syrk(db2_context *ctx, db2_matrix **res, db2_matrix *arg, int trans_left
     bind_device(ctx);
     const uint64_t before = g_launches.load();
     DB2_TRY(ensure_device(arg));
+    // t(X) X of a large X whose result nobody has looked at yet: the normal equations ask for t(X) y next
+    // (lmDS_.daph:98-112; one pipeline with two ADD results under --vec), and both come out of one pass over X
+    if (dt == DB2_F64 && trans_left && *res == nullptr && !ctx->eager && arg->rows * arg->cols >= ((int64_t)1 << 22) &&
+        db2k_syrk_gemv_supported(arg->rows, arg->cols)) {
+        auto x = std::make_shared<Operand>();
+        x->buf = arg->dev;
+        x->off = arg->dev_off;
+        x->ld = arg->dev_ld;
+        x->rows = arg->rows;
+        x->cols = arg->cols;
+        db2_matrix *r = new db2_matrix(); // no placement yet
+        r->ctx = ctx;
+        r->dtype = DB2_F64;
+        r->rows = r->cols = n;
+        r->syrk_of = x;
+        if (ctx->syrk_waiting && ctx->syrk_waiting->syrk_of) // one at a time: the older one is computed now
+            DB2_TRY(syrk_force(ctx->syrk_waiting));
+        ctx->syrk_waiting = r;
+        *res = r;
+        return DB2_OK;
+    }
     DB2_TRY(prepare_result(ctx, res, dt, n, n));
     void *scratch = nullptr;
     DB2_TRY(ctx_scratch(ctx, db2k_syrk_scratch_bytes(dt, arg->rows, arg->cols, trans_left), &scratch));
@@ -97,6 +139,35 @@ int db2_syrk(db2_context *ctx, db2_matrix **res, db2_matrix *arg, int trans_left
 int db2_gemv(db2_context *ctx, db2_matrix **res, db2_matrix *mat, db2_matrix *vec) {
     DB2_API_BEGIN
     DB2_CHECK(ctx && res && mat && vec, DB2_EINVAL, "null argument");
+    if (ctx->syrk_waiting && mat->dtype == DB2_F64 && vec->dtype == DB2_F64 && mat->dev_valid) {
+        // t(X) X of this very X is waiting: one pass over X gives both
+        db2_matrix *w = ctx->syrk_waiting;
+        const Operand &x = *w->syrk_of;
+        if (x.buf == mat->dev && x.off == mat->dev_off && x.ld == mat->dev_ld && x.rows == mat->rows &&
+            x.cols == mat->cols && vec->rows == mat->rows && vec->cols == 1) {
+            bind_device(ctx);
+            const uint64_t before = g_launches.load();
+            DB2_TRY(ensure_device(vec));
+            if (vec->dev_ld == 1 && aligned16(vec->dev_ptr())) {
+                DB2_TRY(prepare_result(ctx, res, DB2_F64, mat->cols, 1));
+                if ((*res)->dev_ld == 1) {
+                    w->dev = make_devbuf(ctx, (size_t)w->rows * w->cols * 8);
+                    w->dev_off = 0;
+                    w->dev_ld = w->cols;
+                    void *scratch = nullptr;
+                    DB2_TRY(ctx_scratch(ctx, db2k_syrk_gemv_scratch_bytes(mat->rows, mat->cols), &scratch));
+                    DB2_TRY(db2k_syrk_gemv(mat->dev_ptr(), mat->rows, mat->cols, mat->dev_ld, vec->dev_ptr(),
+                                           w->dev_ptr(), w->dev_ld, (*res)->dev_ptr(), scratch, ctx->scratch_bytes,
+                                           ctx->stream));
+                    w->dev_valid = true;
+                    w->syrk_of.reset();
+                    ctx->syrk_waiting = nullptr;
+                    count(ctx, before);
+                    return DB2_OK;
+                }
+            }
+        }
+    }
     if (mat->dtype == DB2_F32 && vec->dtype == DB2_F32) {
         // f32: t(mat) @ vec as a tensor-core product with one result column (Gemv.h:51-63 calls cblas_sgemv)
         DB2_CHECK(vec->rows == mat->rows && vec->cols == 1, DB2_EINVAL,

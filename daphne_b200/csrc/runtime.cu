@@ -177,6 +177,7 @@ int prepare_result(db2_context *ctx, db2_matrix **res, int dtype, int64_t rows, 
         r->pend_src.reset();
         r->pend_op = -1;
         r->onehot.reset();
+        r->syrk_of.reset();
     }
     r->is_seq = false;
     r->combined = false;

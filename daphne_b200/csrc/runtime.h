@@ -15,6 +15,7 @@ namespace db2 {
 struct Expr;
 struct OneHot;
 struct ColStats;
+struct Operand;
 } // namespace db2
 
 struct db2_matrix;
@@ -51,6 +52,8 @@ struct db2_context {
     int dup = 0; // number of contexts of the same group, listed before this one, that share its physical device
     // column statistics of the matrix that was last aggregated by columns (colstats.cu)
     std::shared_ptr<db2::ColStats> colstats;
+    // the t(X) X that was asked for last and has not been computed yet (db2_matrix::syrk_of)
+    db2_matrix *syrk_waiting = nullptr;
     std::mutex mu;
     db2_stats stats{};
     // the handle returned by db2_context_create holds one reference, every pooled buffer another: a context is torn
@@ -134,6 +137,9 @@ struct db2_matrix {
 
     // one-hot rows (r, idx[r]) = weight that have not been written out (onehot.cu)
     std::shared_ptr<const db2::OneHot> onehot;
+    // t(X) X that has not been computed yet (ops_la.cu): a gemv on the same X that arrives first is computed in the
+    // same pass over X; any other use computes the product alone
+    std::shared_ptr<const db2::Operand> syrk_of;
     // the matrix is the int64 sequence seq_start, seq_start + seq_inc, ... (set by db2_seq; values are on the device too)
     bool is_seq = false;
     int64_t seq_start = 0, seq_inc = 0;
@@ -143,7 +149,7 @@ struct db2_matrix {
     // next all-reduce of this matrix has nothing left to do
     bool combined = false;
 
-    bool deferred() const { return (bool)lazy || (bool)pend_src || (bool)onehot; }
+    bool deferred() const { return (bool)lazy || (bool)pend_src || (bool)onehot || (bool)syrk_of; }
     size_t esize() const { return db2::dtype_size(dtype); }
     void *dev_ptr() const { return static_cast<char *>(dev->ptr) + dev_off * (int64_t)esize(); }
     void *host_ptr() const { return static_cast<char *>(host->ptr) + host_off * (int64_t)esize(); }
@@ -235,6 +241,7 @@ int lazy_try_agg_col(db2_context *ctx, int op, db2_matrix **res, db2_matrix *arg
 int lazy_try_matmul(db2_context *ctx, db2_matrix **res, db2_matrix *lhs, db2_matrix *rhs, int transa, int transb,
                     bool *handled);
 // full aggregation of a deferred chain without materialising it (SUM of flat-evaluable chains); *res_host gets the value
+int syrk_force(db2_matrix *m); // ops_la.cu: computes a deferred t(X) X on its own
 int lazy_try_agg_all(db2_context *ctx, int op, double *res_host, db2_matrix *arg, bool *handled);
 // the same without the wait: the sum is written to `pinned` (pinned host memory) by the pass that this call queues
 int lazy_try_agg_all_start(db2_context *ctx, int op, double *pinned, db2_matrix *arg, bool *handled);

@@ -73,6 +73,9 @@ _SIGS = {
     "db2k_matmul": (i32, [i32, vp, i64, i64, i64, vp, i64, i64, i64, i32, i32, vp, i64, vp, sz, vp]),
     "db2k_syrk_scratch_bytes": (sz, [i32, i64, i64, i32]),
     "db2k_syrk": (i32, [i32, vp, i64, i64, i64, i32, vp, i64, vp, sz, vp]),
+    "db2k_syrk_gemv_scratch_bytes": (sz, [i64, i64]),
+    "db2k_syrk_gemv_supported": (i32, [i64, i64]),
+    "db2k_syrk_gemv": (i32, [vp, i64, i64, i64, vp, vp, i64, vp, vp, sz, vp]),
     "db2k_transpose": (i32, [i32, vp, i64, i64, i64, vp, i64, vp]),
     "db2k_fill": (i32, [i32, vp, i64, i64, i64, vp, vp]),
     "db2k_seq": (i32, [i32, vp, i64, vp, vp, vp]),

@@ -183,9 +183,10 @@ def normal_equations(ctx, X, y, lam: float = 0.001, comm: Optional[Comm] = None,
     K = kernels or globals()["K"]
     probe = probe or _NoProbe()
     d = X.cols
-    with probe.section("gemm_f64_kernel syrk t(X)X", X.rows * d * 8):
+    # t(X) X is deferred until t(X) y arrives: both come out of one pass over X (the fold into the syrk kernel)
+    with probe.section("gemm_f64_kernel syrk t(X)X with t(X)y folded in", X.rows * (d + 1) * 8):
         xtx = K.syrk(X, True)
-    xty = K.gemv(X, y)
+        xty = K.gemv(X, y)
     xtx = _allreduce_matrix(ctx, xtx, comm, k=K)
     xty = _allreduce_matrix(ctx, xty, comm, k=K)
     A = K.ewBinaryMat(B.ADD, xtx, K.diagMatrix(K.fill(ctx, lam, d, 1)))

@@ -188,6 +188,14 @@ int db2k_matmul(int dtype, const void *lhs, int64_t lhs_rows, int64_t lhs_cols, 
 size_t db2k_syrk_scratch_bytes(int dtype, int64_t rows, int64_t cols, int trans_left);
 int db2k_syrk(int dtype, const void *arg, int64_t rows, int64_t cols, int64_t ld, int trans_left, void *res,
               int64_t res_ld, void *scratch, size_t scratch_bytes, void *stream);
+/* t(X) X and t(X) y in ONE pass over X (f64, more than 64 columns; the reference calls syrk and gemv, Syrk.h:40-43 and
+ * Gemv.h:51-63, and reads X for each): the warps of the diagonal tiles that have no sub-tile to compute form the products
+ * with y from the operand stages that pass through shared memory anyway.  res: cols x cols; yvec: rows contiguous
+ * doubles (16-byte aligned); yres: cols contiguous doubles. */
+size_t db2k_syrk_gemv_scratch_bytes(int64_t rows, int64_t cols);
+int db2k_syrk_gemv_supported(int64_t rows, int64_t cols);
+int db2k_syrk_gemv(const void *arg, int64_t rows, int64_t cols, int64_t ld, const void *yvec, void *res, int64_t res_ld,
+                   void *yres, void *scratch, size_t scratch_bytes, void *stream);
 
 /* Out-of-place transpose (any 4- or 8-byte value type).  Replaces Transpose<Dense,Dense>
  * (src/runtime/local/kernels/Transpose.h:51-76; CUDA twin kernels/CUDA/Transpose.cpp:70-90: cuBLAS geam). */
@@ -344,6 +352,9 @@ int db2_scalarStart(db2_context *ctx, db2_matrix *m, int slot);
 int db2_scalarWait(db2_context *ctx, int slot, double *res);
 int db2_matMul(db2_context *ctx, db2_matrix **res, db2_matrix *lhs, db2_matrix *rhs, int transa, int transb);
 int db2_syrk(db2_context *ctx, db2_matrix **res, db2_matrix *arg, int trans_left);
+/* (For a large f64 argument with trans_left the result handle is returned before anything is computed: a db2_gemv on
+ * the same argument that follows is computed in the same pass over it -- t(X) X and t(X) y of the normal equations,
+ * lmDS_.daph:98-112 -- and any other use of the handle computes the product alone.) */
 /* res (cols x 1) = t(mat) vec (Gemv<Dense,Dense,Dense>, src/runtime/local/kernels/Gemv.h:51-63) */
 int db2_gemv(db2_context *ctx, db2_matrix **res, db2_matrix *mat, db2_matrix *vec);
 int db2_solve(db2_context *ctx, db2_matrix **res, db2_matrix *lhs, db2_matrix *rhs);

@@ -351,3 +351,45 @@ def test_integer_matmul_bit_exact(ctx, dtype):
     v = k.sliceRow(A, 100, 300)                                            # a row view keeps its offset
     c = rng.integers(-9, 9, size=(20, 6)).astype(dtype)
     assert np.array_equal(k.matMul(v, k.DenseMatrix.from_numpy(ctx, c)).to_numpy(), o.matMul(A.to_numpy()[100:300], c))
+
+
+def test_syrk_followed_by_gemv_is_one_pass(ctx):
+    """t(X) X is deferred for a large X; a gemv on the same X that follows is computed by the same kernel (the idle
+    warps of the diagonal tiles form t(X) y from the stages in shared memory).  The syrk part is the unchanged
+    arithmetic (bit-identical to the product computed alone); t(X) y within the reduction tolerance."""
+    k, o = _k()
+    rng = np.random.default_rng(23)
+    for n, d in [(40000, 128), (9000, 512), (50000, 100), (33000, 130)]:
+        x = rng.random((n, d)) * 2.0 - 1.0
+        y = rng.standard_normal((n, 1))
+        X, Y = k.DenseMatrix.from_numpy(ctx, x), k.DenseMatrix.from_numpy(ctx, y)
+        X.device_ptr()
+        alone = k.syrk(X, True).to_numpy()                 # looked at right away: the product alone
+        b_alone = k.gemv(X, Y).to_numpy()                  # no t(X) X waiting: the ordinary column pass
+        s0 = ctx.stats()["launches"]
+        A = k.syrk(X, True)
+        assert ctx.stats()["launches"] == s0               # nothing has run yet
+        b = k.gemv(X, Y)
+        fused_launches = ctx.stats()["launches"] - s0
+        assert fused_launches <= 3                         # product kernel, reduce of the splits, fold of t(X) y
+        assert_bits_equal(A.to_numpy(), alone, f"t(X) X with t(X) y folded in, {n} x {d}")
+        exact = x.T @ y
+        scale = np.abs(x).T @ np.abs(y)
+        assert np.all(np.abs(b.to_numpy() - exact) <= 1e-12 * scale), (n, d)
+        assert np.all(np.abs(b_alone - exact) <= 1e-12 * scale)
+    # the deferred product is computed alone when something else needs it first, or never when it is dropped
+    x = rng.random((40000, 128))
+    X = k.DenseMatrix.from_numpy(ctx, x)
+    X.device_ptr()
+    A1 = k.syrk(X, True)
+    A2 = k.syrk(X, True)                                   # one waits at a time: A1 is computed here
+    yv = k.DenseMatrix.from_numpy(ctx, rng.standard_normal((40000, 3)))
+    col = k.sliceCol(yv, 1, 2)                             # a strided column: the ordinary gemv, A2 keeps waiting
+    b = k.gemv(X, col).to_numpy()
+    assert np.all(np.abs(b - x.T @ yv.to_numpy()[:, 1:2]) <= 1e-11 * (np.abs(x).T @ np.abs(yv.to_numpy()[:, 1:2])))
+    assert_bits_equal(A1.to_numpy(), A2.to_numpy(), "both deferred products")
+    A3 = k.syrk(X, True)
+    del A3                                                 # dropped: never computed, and nothing left behind
+    other = k.DenseMatrix.from_numpy(ctx, rng.random((40000, 128)))
+    b2 = k.gemv(other, k.DenseMatrix.from_numpy(ctx, np.ones((40000, 1)))).to_numpy()
+    assert np.allclose(b2[:, 0], other.to_numpy().sum(0), rtol=1e-12)
