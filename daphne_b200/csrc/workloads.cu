@@ -41,6 +41,18 @@ struct HC {
 
 int combine(db2_context *ctx, db2_matrix *m) { return ctx->world > 1 ? db2_allreduce(ctx, m, DB2_COMBINE_ADD) : DB2_OK; }
 
+// two ADD partials of one step, combined by one NCCL launch
+int combine2(db2_context *ctx, db2_matrix *a, db2_matrix *b) {
+    if (ctx->world == 1)
+        return DB2_OK;
+    DB2_TRY(db2_comm_group_begin(ctx));
+    int rc = db2_allreduce(ctx, a, DB2_COMBINE_ADD);
+    if (rc == DB2_OK)
+        rc = db2_allreduce(ctx, b, DB2_COMBINE_ADD);
+    const int rc_end = db2_comm_group_end(ctx);
+    return rc != DB2_OK ? rc : rc_end;
+}
+
 int scalar_op(db2_context *ctx, int op, db2_matrix **res, db2_matrix *lhs, double s) {
     return db2_ewBinaryObjSca(ctx, op, res, lhs, &s);
 }
@@ -205,9 +217,8 @@ int db2w_kmeans(db2_context *ctx, db2_matrix *X, db2_matrix *C0, int iterations,
         xc.reset();
         DB2_TRY(db2_ctable(ctx, &P, rows, assign, 1.0, n, k));
         DB2_TRY(db2_matMul(ctx, &sums, P, X, 1, 0));
-        DB2_TRY(combine(ctx, sums));
         DB2_TRY(db2_aggCol(ctx, DB2_AGG_SUM, &counts, P));
-        DB2_TRY(combine(ctx, counts));
+        DB2_TRY(combine2(ctx, sums, counts));
         P.reset();
         DB2_TRY(db2_transpose(ctx, &ct, counts));
         DB2_TRY(db2_ewBinaryMat(ctx, DB2_DIV, &Cn, sums, ct));
@@ -228,8 +239,7 @@ int db2w_normal_equations(db2_context *ctx, db2_matrix *X, db2_matrix *y, double
     H xtx, xty, lam, diag, A, beta;
     DB2_TRY(db2_syrk(ctx, &xtx, X, 1));
     DB2_TRY(db2_gemv(ctx, &xty, X, y));
-    DB2_TRY(combine(ctx, xtx));
-    DB2_TRY(combine(ctx, xty));
+    DB2_TRY(combine2(ctx, xtx, xty));
     DB2_TRY(db2_fill(ctx, &lam, DB2_F64, &lambda, X->cols, 1));
     DB2_TRY(db2_diagMatrix(ctx, &diag, lam));
     DB2_TRY(db2_ewBinaryMat(ctx, DB2_ADD, &A, xtx, diag));
