@@ -302,6 +302,44 @@ int db2_allreduce(db2_context *ctx, db2_matrix *m, int combine) {
     DB2_API_END
 }
 
+// The same combine, issued on a stream of its own behind what the context's stream has queued so far: the context's
+// stream goes on at once, and whoever touches m next waits for the combine (DevBuf::ready).  For a partial that
+// nothing on the device needs soon -- the final scalar of a pipeline -- the collective's latency is no longer part
+// of the pipeline's step.
+int db2_allreduce_async(db2_context *ctx, db2_matrix *m, int combine) {
+    DB2_API_BEGIN
+    DB2_CHECK(ctx && m, DB2_EINVAL, "null argument");
+    DB2_CHECK(combine == DB2_COMBINE_ADD || combine == DB2_COMBINE_MIN || combine == DB2_COMBINE_MAX, DB2_EINVAL,
+              "only ADD, MIN and MAX results are combined across row shards");
+    if (ctx->world == 1)
+        return DB2_OK;
+    if (m->combined || g_override) // nothing to do / the test table of stand-ins: the plain path
+        return db2_allreduce(ctx, m, combine);
+    DB2_CHECK(ctx->comm, DB2_ENCCL, "no communicator: call db2_comm_init first");
+    bind_device(ctx);
+    DB2_TRY(ensure_device(m));
+    DB2_CHECK(m->dev_ld == m->cols || m->rows == 1, DB2_EUNSUPPORTED, "all-reduce of a strided view");
+    if (!ctx->side_stream)
+        DB2_CUDA(cudaStreamCreateWithFlags(&ctx->side_stream, cudaStreamNonBlocking));
+    cudaEvent_t queued = nullptr, done = nullptr;
+    DB2_CUDA(cudaEventCreateWithFlags(&queued, cudaEventDisableTiming));
+    DB2_CUDA(cudaEventRecord(queued, ctx->stream));
+    DB2_CUDA(cudaStreamWaitEvent(ctx->side_stream, queued, 0));
+    DB2_CUDA(cudaEventDestroy(queued));
+    const int op = combine == DB2_COMBINE_ADD ? ncclSum : (combine == DB2_COMBINE_MIN ? ncclMin : ncclMax);
+    DB2_NCCL(nccl()->AllReduce(m->dev_ptr(), m->dev_ptr(), (size_t)m->rows * m->cols, nccl_dtype(m->dtype), op,
+                               static_cast<ncclComm_t>(ctx->comm), ctx->side_stream));
+    DB2_CUDA(cudaEventCreateWithFlags(&done, cudaEventDisableTiming));
+    DB2_CUDA(cudaEventRecord(done, ctx->side_stream));
+    m->dev->ready = done;
+    m->host_valid = false;
+    std::lock_guard<std::mutex> lock(ctx->mu);
+    ctx->stats.collectives++;
+    ctx->stats.collective_bytes += (uint64_t)m->rows * m->cols * m->esize();
+    return DB2_OK;
+    DB2_API_END
+}
+
 // Concatenates the row shards of all ranks in rank order (ROWS combine across GPUs).  The shards follow the row
 // partition of the scheduler: `total_rows` rows cut into `world` contiguous blocks, the first total_rows % world of
 // them one row taller.  Every rank can compute every block from total_rows, so no sizes are exchanged; a shard whose

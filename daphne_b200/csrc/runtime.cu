@@ -5,6 +5,10 @@
 namespace db2 {
 
 DevBuf::~DevBuf() {
+    if (ready) { // the block goes back to the pool in the order of the context's stream
+        bind_device(ctx);
+        wait_ready(ctx, this);
+    }
     if (owned) {
         if (ptr)
             ctx_free(ctx, ptr, bytes);
@@ -25,6 +29,10 @@ void ctx_release(db2_context *ctx) {
     release_cached(ctx);
     cudaFree(ctx->dev_status);
     cudaFreeHost(ctx->host_status);
+    if (ctx->side_stream) {
+        cudaStreamSynchronize(ctx->side_stream);
+        cudaStreamDestroy(ctx->side_stream);
+    }
     for (cudaEvent_t ev : ctx->scalar_ev)
         if (ev)
             cudaEventDestroy(ev);
@@ -134,6 +142,10 @@ std::shared_ptr<DevBuf> make_devbuf(db2_context *ctx, size_t bytes) {
 }
 
 int ensure_device(db2_matrix *m) {
+    if (m->dev && m->dev->ready) {
+        bind_device(m->ctx);
+        wait_ready(m->ctx, m->dev.get());
+    }
     if (m->dev_valid)
         return DB2_OK;
     if (m->deferred())
@@ -478,6 +490,7 @@ int db2_matrix_to_host(db2_matrix *m, void *dst, int64_t dst_ld) {
     if (m->dev_valid) {
         db2_context *ctx = m->ctx;
         bind_device(ctx);
+        wait_ready(ctx, m->dev.get());
         if ((dst_ld == m->cols && m->dev_ld == m->cols) || m->rows == 1) // contiguous: one linear copy
             DB2_CUDA(cudaMemcpyAsync(dst, m->dev_ptr(), (size_t)m->rows * m->cols * es, cudaMemcpyDeviceToHost,
                                      ctx->stream));

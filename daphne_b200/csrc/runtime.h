@@ -28,6 +28,7 @@ struct db2_context {
     std::vector<db2_matrix *> lazies; // live matrices that stand for an unevaluated elementwise chain
     bool eager = false; // DB2_EAGER=1: run every operator call immediately (no fusion)
     cudaStream_t stream = nullptr;
+    cudaStream_t side_stream = nullptr; // collectives that run beside the compute stream (db2_allreduce_async)
     // caching device allocator: freed blocks are kept by size and handed out again without calling the driver; all
     // work of a context is ordered on its one stream, so a freed block may be reused immediately
     std::multimap<size_t, void *> free_blocks;
@@ -75,6 +76,9 @@ struct DevBuf {
     size_t bytes;
     bool owned;
     uint64_t version = 0; // bumped whenever a kernel writes into an existing buffer (results placed through views)
+    // set while work on ANOTHER stream than the context's still writes the buffer (db2_allreduce_async): whoever
+    // touches the buffer next makes the context's stream wait for it first (wait_ready)
+    cudaEvent_t ready = nullptr;
     ~DevBuf();
 };
 
@@ -105,6 +109,14 @@ int ctx_free(db2_context *ctx, void *ptr, size_t bytes);
 int ctx_scratch(db2_context *ctx, size_t bytes, void **out);
 void ctx_release(db2_context *ctx);
 std::shared_ptr<DevBuf> make_devbuf(db2_context *ctx, size_t bytes); // throws Error
+
+inline void wait_ready(db2_context *ctx, DevBuf *b) {
+    if (b && b->ready) {
+        cudaStreamWaitEvent(ctx->stream, b->ready, 0);
+        cudaEventDestroy(b->ready);
+        b->ready = nullptr;
+    }
+}
 
 inline void bind_device(const db2_context *ctx) {
     int cur = -1;

@@ -170,7 +170,8 @@ int db2w_standardise(db2_context *ctx, db2_matrix *X, int64_t n_total, db2_matri
     if (ev_rows_end)
         DB2_TRY(db2_event_record(ev_rows_end, ctx->stream));
     DB2_TRY(db2_aggCol(ctx, DB2_AGG_SUM, &s, r));
-    DB2_TRY(combine(ctx, s));
+    if (ctx->world > 1) // nobody on the device needs s: its combine runs beside the stream
+        DB2_TRY(db2_allreduce_async(ctx, s, DB2_COMBINE_ADD));
     *mu_out = mu.release();
     *sd_out = sd.release();
     *r_out = r.release();

@@ -105,6 +105,7 @@ _SIGS = {
     "db2_comm_destroy": (i32, [vp]),
     "db2_comm_info": (i32, [vp, _P(i32), _P(i32)]),
     "db2_allreduce": (i32, [vp, vp, i32]),
+    "db2_allreduce_async": (i32, [vp, vp, i32]),
     "db2_comm_group_begin": (i32, [vp]),
     "db2_comm_group_end": (i32, [vp]),
     "db2_allgather_rows": (i32, [vp, vp, _P(vp)]),

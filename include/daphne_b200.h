@@ -301,6 +301,9 @@ int db2_comm_destroy(db2_context *ctx);
 int db2_comm_info(const db2_context *ctx, int *rank, int *world);
 /* in-place combine of a small contiguous partial over all ranks; combine = DB2_COMBINE_ADD / MIN / MAX */
 int db2_allreduce(db2_context *ctx, db2_matrix *m, int combine);
+/* the same, on a stream of its own behind what the context's stream has queued so far; the context's stream goes on
+ * at once and the next use of m (or its release) waits for the combine */
+int db2_allreduce_async(db2_context *ctx, db2_matrix *m, int combine);
 /* collectives issued between the two calls are launched together (one NCCL group) */
 int db2_comm_group_begin(db2_context *ctx);
 int db2_comm_group_end(db2_context *ctx);
