@@ -658,6 +658,16 @@ int db2_vectorizedPipelineGroup(db2_group *g, db2_dist **outputs, size_t numOutp
     DB2_API_END
 }
 
+/* fn(index, context, user) on every device of the group at once, each call on that device's worker thread with the
+ * device bound (the small replicated arithmetic between two pipelines -- mu = sums / n on every device -- costs one
+ * hand-off instead of a walk over the devices).  Returns the first failure. */
+int db2_group_run(db2_group *g, db2_group_fn fn, void *user) {
+    DB2_API_BEGIN
+    DB2_CHECK(g && fn, DB2_EINVAL, "null argument");
+    return for_each_device(g, [&](int d) -> int { return fn(d, g->ctxs[d], user); });
+    DB2_API_END
+}
+
 /* In-place-style combine of one partial per device (ms[d] on device d of the group): on return ms[d] is the combined
  * matrix of device d (the handle may have been replaced; the old one is released). */
 int db2_group_allreduce(db2_group *g, db2_matrix **ms, int combine) {

@@ -7,6 +7,7 @@
 // they run row-sharded: every rank calls them on its row block and the ADD partials are combined on the device.
 #include "runtime.h"
 
+#include <functional>
 #include <vector>
 
 using namespace db2;
@@ -299,22 +300,23 @@ void body_rows(db2_matrix ***outs, db2_matrix **ins, db2_context *ctx) {
 }
 
 // out = f(in) on every device of the group (small replicated follow-up arithmetic between two pipelines)
+struct EachDevice {
+    std::function<int(db2_context *, db2_matrix *, db2_matrix **)> f;
+    db2_dist *in;
+    std::vector<db2_matrix *> *res;
+};
+int each_device_call(int d, db2_context *c, void *user) {
+    EachDevice *e = static_cast<EachDevice *>(user);
+    db2_matrix *shard = nullptr;
+    DB2_TRY(db2_dist_shard(e->in, d, &shard, nullptr));
+    return e->f(c, shard, &(*e->res)[d]);
+}
 template <typename F> int on_every_device(db2_group *g, db2_dist *in, db2_dist **out, F &&f) {
     int n = 0;
     DB2_TRY(db2_group_size(g, &n));
     std::vector<db2_matrix *> res(n, nullptr);
-    int rc = DB2_OK;
-    for (int d = 0; d < n && rc == DB2_OK; d++) {
-        db2_context *c = nullptr;
-        db2_matrix *shard = nullptr;
-        rc = db2_group_context(g, d, &c);
-        if (rc == DB2_OK)
-            rc = db2_dist_shard(in, d, &shard, nullptr);
-        if (rc == DB2_OK) {
-            bind_device(c);
-            rc = f(c, shard, &res[d]);
-        }
-    }
+    EachDevice each{f, in, &res};
+    int rc = db2_group_run(g, each_device_call, &each); // all devices at once, each on its worker thread
     if (rc == DB2_OK)
         rc = db2_dist_from_shards(g, res.data(), -1, out);
     for (db2_matrix *m : res)

@@ -127,6 +127,7 @@ _SIGS = {
     "db2_dist_decref": (i32, [vp]),
     "db2_dist_to_host": (i32, [vp, vp, i64]),
     "db2_dist_gather": (i32, [vp, i32, _P(vp)]),
+    "db2_group_run": (i32, [vp, vp, vp]),
     "db2_group_allreduce": (i32, [vp, _P(vp), i32]),
     "db2_matrix_to_context": (i32, [vp, vp, _P(vp)]),
     "db2_matrix_copy_block": (i32, [vp, i64, i64, vp]),

@@ -463,6 +463,9 @@ int db2_dist_gather(db2_dist *d, int index, db2_matrix **out);
 /* Combine of one partial per device (ms[i] lives on device i of the group) with DB2_COMBINE_ADD / MIN / MAX; on return
  * ms[i] is the combined matrix on device i (a handle may have been replaced by a new one, the old one released).
  * The device-side twin of the host-side merge under a mutex in src/runtime/local/vectorized/Tasks.cpp:51-82. */
+/* fn(device index, that device's context, user) on all devices of the group at once, each on its device's worker thread */
+typedef int (*db2_group_fn)(int index, db2_context *ctx, void *user);
+int db2_group_run(db2_group *g, db2_group_fn fn, void *user);
 int db2_group_allreduce(db2_group *g, db2_matrix **ms, int combine);
 /* a copy of src as a new matrix of ctx; any two contexts of this process (a peer copy when their devices differ) */
 int db2_matrix_to_context(db2_context *ctx, db2_matrix *src, db2_matrix **out);
