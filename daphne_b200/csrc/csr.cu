@@ -11,7 +11,6 @@
 #include "fused_step.cuh"
 #include "runtime.h"
 
-#include <cub/device/device_scan.cuh>
 
 struct db2_csr {
     std::atomic<int> refs{1};
@@ -485,13 +484,14 @@ template <typename IT> static int materialise_product(db2_csr *m) {
     csr_mul_count_kernel<IT><<<grid1d(rows, 256), 256, 0, ctx->stream>>>(col, lhs->off_ptr(), rows, skind, sc, ld,
                                                                        static_cast<uint64_t *>(counts->ptr));
     DB2_TRY(after_launch("csr_mul_count_kernel"));
-    size_t tmp_bytes = 0;
-    DB2_CUDA(cub::DeviceScan::ExclusiveSum(nullptr, tmp_bytes, static_cast<uint64_t *>(counts->ptr),
-                                           static_cast<uint64_t *>(offs->ptr), (int)(rows + 1), ctx->stream));
-    auto tmp = devbuf(ctx, tmp_bytes);
-    DB2_CUDA(cub::DeviceScan::ExclusiveSum(tmp->ptr, tmp_bytes, static_cast<uint64_t *>(counts->ptr),
-                                           static_cast<uint64_t *>(offs->ptr), (int)(rows + 1), ctx->stream));
-    g_launches.fetch_add(1);
+    // row offsets = exclusive prefix sums of the counts: 0, then the cumulative sums (the blocked scan of AggCum)
+    DB2_CUDA(cudaMemsetAsync(offs->ptr, 0, 8, ctx->stream));
+    if (rows > 0) {
+        const size_t tmp_bytes = db2k_agg_cum_scratch_bytes(rows, 1);
+        auto tmp = devbuf(ctx, tmp_bytes);
+        DB2_TRY(db2k_agg_cum(DB2_I64, DB2_AGG_SUM, counts->ptr, rows, 1, 1, static_cast<uint64_t *>(offs->ptr) + 1, 1,
+                             tmp->ptr, tmp_bytes, ctx->stream));
+    }
     uint64_t total = 0;
     DB2_CUDA(cudaMemcpyAsync(&total, static_cast<uint64_t *>(offs->ptr) + rows, 8, cudaMemcpyDeviceToHost,
                              ctx->stream));
