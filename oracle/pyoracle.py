@@ -346,6 +346,36 @@ def extractCol(arg, sel) -> np.ndarray:
     return res
 
 
+def _slice_bounds(what, lower, upper, extent):
+    """The bounds rule shared by SliceRow and SliceCol (src/runtime/local/kernels/SliceRow.h:55-82,
+    SliceCol.h:55-84): a negative lower bound counts from the end (and takes an upper bound <= 0 with it), a negative
+    upper bound alone counts from the end; then 0 <= lower < extent and lower <= upper <= extent must hold."""
+    lo, up = int(lower), int(upper)
+    if lo < 0:
+        lo += extent
+        if up <= 0:
+            up += extent
+    elif up < 0:
+        up += extent
+    if lo < 0 or lo >= extent or up < lo or extent < up:
+        raise OracleError(f"invalid arguments '{lo}, {up}' passed to {what}")
+    return lo, up
+
+
+def sliceRow(arg, lowerIncl, upperExcl) -> np.ndarray:
+    """SliceRow<Dense,Dense,VTSel> (src/runtime/local/kernels/SliceRow.h:71-82): rows [lowerIncl, upperExcl)."""
+    arg = _mat(arg)
+    lo, up = _slice_bounds("SliceRow", lowerIncl, upperExcl, arg.shape[0])
+    return arg[lo:up, :]
+
+
+def sliceCol(arg, lowerIncl, upperExcl) -> np.ndarray:
+    """SliceCol<Dense,Dense,VTSel> (src/runtime/local/kernels/SliceCol.h:73-86): columns [lowerIncl, upperExcl)."""
+    arg = _mat(arg)
+    lo, up = _slice_bounds("SliceCol", lowerIncl, upperExcl, arg.shape[1])
+    return arg[:, lo:up]
+
+
 def _csr_arrays(m):
     """(values f64, colIdxs u64, rowOffsets u64, rows, cols) from a scipy CSR matrix or an equivalent tuple."""
     if isinstance(m, tuple):

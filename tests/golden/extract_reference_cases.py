@@ -38,7 +38,7 @@ _ENV = {"sqrt": math.sqrt, "exp": math.exp, "log": math.log, "sin": math.sin, "c
 
 def _clean(text: str) -> str:
     text = re.sub(r"//[^\n]*", "", text)
-    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    text = re.sub(r"/\*.*?\*/", lambda m: "\n" * m.group().count("\n"), text, flags=re.S)  # keeps line numbers
     return text.replace("\\\n", "\n")
 
 
@@ -184,6 +184,8 @@ def extract(root: Path):
     cases += _extract_outer(root)
     cases += _extract_aggcum(root)
     cases += _extract_onehot(root)
+    cases += _extract_cond(root)
+    cases += _extract_slice(root)
     return cases, skipped
 
 
@@ -352,6 +354,86 @@ def _extract_seq(root: Path):
                     "test": "Seq", "check": "checkSeq", "op": None,
                     "args": [{"scalar": _enc(v)} for v in sc] +
                             [{"matrix": "targetMatrix", "dt": "DT", "rows": int(nrows), "values": [_enc(v) for v in vals]}]})
+    return out
+
+
+COND_SCALAR_RE = re.compile(r"\b(argThen|argElse)\s*=\s*(VT\([^()]*\))\s*;")
+
+
+def _extract_cond(root: Path):
+    """CondMatMatMatTest.cpp, CondMatMatScaTest.cpp, CondMatScaMatTest.cpp and CondMatScaScaTest.cpp: one SECTION
+    ("example 1") assigns argCond and exp as literal 3 x 3 matrices and argThen / argElse as literal matrices or as
+    scalars VT(x); the expected literal may name the scalars.  The test is instantiated for int64_t and double, and
+    VT(x) truncates for the former, so one case is written per value type."""
+    out = []
+    for fname in ("CondMatMatMatTest.cpp", "CondMatMatScaTest.cpp", "CondMatScaMatTest.cpp", "CondMatScaScaTest.cpp"):
+        path = root / "test/runtime/local/kernels" / fname
+        if not path.exists():
+            continue
+        text = _clean(path.read_text())
+        sm = SECTION_RE.search(text)
+        if not sm:
+            continue
+        end = text.find("DT *res = nullptr;", sm.end())
+        body = text[sm.end(): end if end > 0 else len(text)]
+        line = text.count("\n", 0, text.find(fname[0].lower() + fname[1:-8] + "(res", sm.end())) + 1
+        for vt in ("double", "int64_t"):
+            conv = (lambda x: float(x)) if vt == "double" else (lambda x: int(x))
+            scalars = {n: conv(_value(v)) for n, v in COND_SCALAR_RE.findall(body)}
+            local = {}
+            for am in ASSIGN_RE.finditer(body):
+                name, _, nrows, vals = am.groups()
+                toks = re.sub(r"\b(argThen|argElse)\b", lambda m: repr(scalars[m.group(1)]), vals)
+                toks = re.sub(r"\bVT\(([^()]*)\)", lambda m: repr(conv(_value(m.group(1)))), toks)
+                local[name] = {"matrix": name, "dt": f"DenseMatrix<{vt}>", "rows": int(nrows),
+                               "values": [_enc(v) for v in _split_values(toks)]}
+            args = []
+            for name in ("argCond", "argThen", "argElse", "exp"):
+                if name in local:
+                    args.append(local[name])
+                elif name in scalars:
+                    args.append({"scalar": _enc(scalars[name])})
+            if len(args) == 4:
+                out.append({"file": f"test/runtime/local/kernels/{fname}", "line": line, "test": sm.group(1),
+                            "check": "cond", "op": vt, "args": args})
+    return out
+
+
+VECTOR_RE = re.compile(r"std::vector<[^;=]*>\s*(\w+)\s*=\s*\{(.*?)\}\s*;", re.S)
+SLICE_CALL_RE = re.compile(r"\b(sliceRow|sliceCol)\(\s*res\s*,\s*arg\s*,\s*([^,]+),\s*([^,]+),\s*nullptr\s*\)")
+
+
+def _extract_slice(root: Path):
+    """SliceRowTest.cpp and SliceColTest.cpp, the numeric DenseMatrix parts: one case that slices [1, 3) of a literal
+    4 x 6 matrix and three bound pairs that must raise out_of_range."""
+    out = []
+    for fname, kernel in (("SliceRowTest.cpp", "sliceRow"), ("SliceColTest.cpp", "sliceCol")):
+        path = root / "test/runtime/local/kernels" / fname
+        if not path.exists():
+            continue
+        text = _clean(path.read_text())
+        scopes = [m.start() for m in re.finditer(r"TEMPLATE_(?:PRODUCT_)?TEST_CASE\(", text)] + [len(text)]
+        for a, b in zip(scopes, scopes[1:]):
+            scope = text[a:b]
+            if "ALL_STRING_VALUE_TYPES" in scope or "(Frame)" in scope.split("{", 1)[0]:
+                continue
+            vecs = {n: [_enc(v) for v in _split_values(body)] for n, body in VECTOR_RE.findall(scope)}
+            mats = {}
+            for m in re.finditer(r"auto\s+(\w+)\s*=\s*genGivenVals<DT>\(\s*(\d+)\s*,\s*(\w+|\{.*?\})\s*\)\s*;", scope, re.S):
+                name, nrows, src = m.groups()
+                vals = vecs.get(src) if not src.startswith("{") else [_enc(v) for v in _split_values(src[1:-1])]
+                if vals is not None:
+                    mats[name] = {"matrix": name, "dt": "DT", "rows": int(nrows), "values": vals}
+            if "arg" not in mats:
+                continue
+            for cm in SLICE_CALL_RE.finditer(scope):
+                lo, up = (int(_value(t)) for t in cm.group(2, 3))  # VTSel of the throwing calls truncates like VT(x)
+                throws = "REQUIRE_THROWS_AS" in scope[max(0, cm.start() - 24): cm.start()]
+                if not throws and "exp" not in mats:
+                    continue
+                out.append({"file": f"test/runtime/local/kernels/{fname}", "line": text.count("\n", 0, a + cm.start()) + 1,
+                            "test": kernel, "check": kernel + ("Throw" if throws else ""), "op": None,
+                            "args": [mats["arg"], {"scalar": lo}, {"scalar": up}] + ([] if throws else [mats["exp"]])})
     return out
 
 

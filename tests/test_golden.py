@@ -20,7 +20,7 @@ AGG = {n: i for i, n in enumerate(["SUM", "PROD", "MIN", "MAX", "IDXMIN", "IDXMA
 
 DENSE_CHECKS = {"checkAggRow", "checkAggCol", "checkAggAll", "checkEwBinaryMat", "checkEwUnaryMat",
                 "checkEwUnaryMatApprox", "checkEwUnaryMatThrow", "checkEwBinaryObjSca", "checkMatMul", "checkSyrk",
-                "solveNormalEquations", "ctableSection", "transposeSection", "checkSeq", "checkDiagMatrix", "colBind", "extractCol", "extractColThrow", "outerBinary", "aggCum", "oneHot", "oneHotThrow"}
+                "solveNormalEquations", "ctableSection", "transposeSection", "checkSeq", "checkDiagMatrix", "colBind", "extractCol", "extractColThrow", "outerBinary", "aggCum", "oneHot", "oneHotThrow", "cond", "sliceRow", "sliceRowThrow", "sliceCol", "sliceColThrow"}
 
 
 def _num(v):
@@ -37,6 +37,9 @@ def _dense_cases():
     out = []
     for c in CASES:
         if c["check"] not in DENSE_CHECKS:
+            continue
+        if c["check"] == "cond":
+            out.append(pytest.param(c, id=f"{Path(c['file']).stem}:{c['line']}:{c['op']}"))
             continue
         if c["op"] in ("CONCAT", "UPPER", "LOWER"):
             continue  # string kernels are outside the numeric hot path
@@ -74,6 +77,9 @@ class _OracleBackend:
     def agg_cum(self, op, a): return self.o.aggCum(op, a)
     def one_hot(self, a, info): return self.o.oneHot(a, info)
     def extract_col(self, a, sel): return self.o.extractCol(a, sel)
+    def cond(self, c, t, e, dt): return self.o.cond(c, t, e, dtype=dt)
+    def slice_row(self, a, lo, up): return self.o.sliceRow(a, lo, up)
+    def slice_col(self, a, lo, up): return self.o.sliceCol(a, lo, up)
     diag = None  # DiagMatrix has no restatement in the oracle: a diagonal copy, checked on the device only
 
 
@@ -107,6 +113,12 @@ class _CudaBackend:
     def one_hot(self, a, info): return self.k.oneHot(self._m(a), self._m(info)).to_numpy()
     def extract_col(self, a, sel): return self.k.extractCol(self._m(a), self._m(sel)).to_numpy()
     def diag(self, a): return self.k.diagMatrix(self._m(a)).to_numpy()
+    def slice_row(self, a, lo, up): return self.k.sliceRow(self._m(a), lo, up).to_numpy()
+    def slice_col(self, a, lo, up): return self.k.sliceCol(self._m(a), lo, up).to_numpy()
+
+    def cond(self, c, t, e, dt):
+        t, e = (self._m(x) if isinstance(x, np.ndarray) else x for x in (t, e))
+        return self.k.cond(self._m(c), t, e, dtype=dt).to_numpy()
 
 
 def _run_case(be, c):
@@ -204,6 +216,25 @@ def _run_case(be, c):
             exp = np.array([_num(v) for v in args[2]["values"]], dtype=np.float64).reshape(args[2]["rows"], -1)
             got = be.extract_col(arg, sel)
             assert got.shape == exp.shape and np.array_equal(got, exp), f"{c['file']}:{c['line']}"
+    elif chk == "cond":  # CondMatMatMatTest.cpp:35-52 and its three siblings; op names the value type
+        dt = np.float64 if op == "double" else np.int64
+        cnd = _mat(args[0]).astype(dt)
+        then, els = (dt(_num(a["scalar"])) if "scalar" in a else _mat(a).astype(dt) for a in args[1:3])
+        exp = _mat(args[3]).astype(dt)
+        got = be.cond(cnd, then, els, dt)
+        assert got.dtype == dt and got.shape == exp.shape and np.array_equal(got, exp), f"{c['file']}:{c['line']}"
+    elif chk in ("sliceRow", "sliceCol", "sliceRowThrow", "sliceColThrow"):  # SliceRowTest.cpp:31-82, SliceColTest.cpp
+        arg = _mat(args[0])
+        lo, up = (int(_num(a["scalar"])) for a in args[1:3])
+        f = be.slice_row if chk.startswith("sliceRow") else be.slice_col
+        for dt in (np.float64, np.int64, np.uint32):
+            if chk.endswith("Throw"):
+                with pytest.raises(be.err):
+                    f(arg.astype(dt), lo, up)
+            else:
+                exp = _mat(args[3]).astype(dt)
+                got = f(arg.astype(dt), lo, up)
+                assert got.dtype == dt and got.shape == exp.shape and np.array_equal(got, exp), f"{c['file']}:{c['line']}"
     elif chk == "transposeSection":
         m, mt = _mat(args[0]), _mat(args[1])
         assert np.array_equal(be.transpose(m), mt), f"{c['file']}:{c['line']}"
@@ -212,7 +243,7 @@ def _run_case(be, c):
 
 
 def test_fixture_is_not_trivial():
-    assert len(_dense_cases()) >= 130
+    assert len(_dense_cases()) >= 146
 
 
 @pytest.mark.parametrize("case", _dense_cases())
