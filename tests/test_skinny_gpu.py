@@ -139,3 +139,67 @@ def test_one_hot_ctable_consumers(ctx):
         x2 = rng.random((n, dd))
         P2 = k.ctable(rows, Av, 1.0, n, kc)
         _close(k.matMul(P2, k.DenseMatrix.from_numpy(ctx, x2), True, False).to_numpy(), p.T @ x2, f"d={dd}")
+
+
+def _assign_and_sums(k, A, B, ctx, x, c, bump=None):
+    """One k-means step by operator calls: nearest centroid of every row, then t(P) @ X and sum(P, 1)."""
+    n, kc = x.shape[0], c.shape[0]
+    X, C = k.DenseMatrix.from_numpy(ctx, x), k.DenseMatrix.from_numpy(ctx, c)
+    xs = k.aggRow(A.SUM, k.ewBinaryObjSca(B.POW, X, 2.0))
+    cs = k.transpose(k.aggRow(A.SUM, k.ewBinaryObjSca(B.POW, C, 2.0)))
+    xc = k.matMul(X, C, False, True)
+    D = k.ewBinaryMat(B.ADD, k.ewBinaryMat(B.ADD, k.ewBinaryObjSca(B.MUL, xc, -2.0), xs), cs)
+    a = k.castObj(k.aggRow(A.IDXMIN, D), np.int64)
+    P = k.ctable(k.seq(ctx, 0, n - 1, 1, dtype=np.int64), a, 1.0, n, kc)
+    Y = X if bump is None else bump(X)
+    sums = k.matMul(P, Y, True, False)
+    counts = k.aggCol(A.SUM, P)
+    return a.to_numpy().ravel(), sums.to_numpy(), counts.to_numpy().ravel()
+
+
+@pytest.mark.parametrize("n,kc", [(200003, 50), (70000, 64), (4100, 3), (148 * 256 * 3 + 17, 50)])
+def test_cluster_sums_of_integer_valued_rows_are_exact(ctx, n, kc):
+    """t(P) @ X and sum(P, 1) for the one-hot P of a k-means step that is never written out.  Integer-valued X: every
+    order of summation gives the same bits, so the sums must equal numpy's exactly, and a second run must repeat."""
+    k, A, B = _k()
+    rng = np.random.default_rng(31)
+    x = rng.integers(-8, 9, size=(n, 64)).astype(np.float64)
+    c = x[rng.choice(n, kc, replace=False)].copy() + 0.25
+    a, sums, counts = _assign_and_sums(k, A, B, ctx, x, c)
+    ref = np.zeros((kc, 64))
+    np.add.at(ref, a, x)
+    assert_bits_equal(sums, ref, "per-cluster sums of integer-valued rows")
+    assert np.array_equal(counts, np.bincount(a, minlength=kc).astype(np.float64))
+    a2, sums2, _ = _assign_and_sums(k, A, B, ctx, x, c)
+    assert np.array_equal(a, a2)
+    assert_bits_equal(sums2, sums, "repeatable")
+
+
+def test_cluster_sums_of_real_valued_rows_repeat_bit_for_bit(ctx):
+    """No atomics and a fixed order of additions: the sums of real-valued rows are the same bits in every run."""
+    k, A, B = _k()
+    rng = np.random.default_rng(32)
+    n, kc = 300000, 50
+    x = rng.random((n, 64))
+    c = x[rng.choice(n, kc, replace=False)].copy()
+    a, sums, _ = _assign_and_sums(k, A, B, ctx, x, c)
+    ref = np.zeros((kc, 64))
+    np.add.at(ref, a, x)
+    _close(sums, ref, "per-cluster sums", 1e-13)
+    for _ in range(3):
+        a2, sums2, _ = _assign_and_sums(k, A, B, ctx, x, c)
+        assert np.array_equal(a, a2)
+        assert_bits_equal(sums2, sums, "same order of additions in every run")
+
+
+def test_cluster_sums_of_another_matrix_than_the_distances_came_from(ctx):
+    """t(P) @ Y for a Y that is not the X the distances were computed from."""
+    k, A, B = _k()
+    rng = np.random.default_rng(33)
+    n, kc = 50000, 20
+    x = rng.integers(-8, 9, size=(n, 64)).astype(np.float64)
+    c = x[rng.choice(n, kc, replace=False)].copy() + 0.25
+    a, sums, _ = _assign_and_sums(k, A, B, ctx, x, c, bump=lambda X: k.ewBinaryObjSca(B.ADD, X, 1.0))
+    ref = np.zeros((kc, 64))
+    np.add.at(ref, a, x + 1.0)
+    assert_bits_equal(sums, ref, "sums of the other matrix")
