@@ -1,0 +1,310 @@
+// Row passes for chains that have no compiled-in specialisation: the kernel template of fused_ct_dev.cuh is
+// instantiated for the recorded chain by the run-time compiler (NVRTC, found with dlopen), once per chain and
+// process, and the resulting kernel is launched like the compiled-in ones.
+//
+// DAPHNE generates one kernel call per operator and knows no fused kernels, so there is no counterpart in the
+// reference; the compiled-in table (fused_ct.cu) covers the chains of the benchmark pipelines, this file every other
+// DaphneDSL expression that the deferred evaluation turns into a chain.
+//
+// The compilation (about a second) runs on a background thread: the calls that arrive meanwhile are served by the
+// run-time chain interpreter of the same kernel, and the first call after the compilation has finished loads the
+// binary and uses it from then on.  DB2_RTC=sync compiles on the calling thread instead, DB2_RTC=0 switches the
+// mechanism off (as does a missing libnvrtc); db2_rtc_set_mode does the same at run time.
+#include "fused.cuh"
+#include "fused_ct_dev.cuh"
+
+#include "_build/fused_rtc_src.h"
+
+#include <dlfcn.h>
+
+#include <condition_variable>
+#include <map>
+#include <memory>
+#include <mutex>
+#include <string>
+#include <thread>
+#include <vector>
+
+namespace db2 {
+namespace {
+
+enum Mode { RTC_OFF = 0, RTC_ASYNC = 1, RTC_SYNC = 2 };
+enum State { COMPILING = 0, COMPILED, LOADED, FAILED };
+
+struct Nvrtc {
+    typedef void *Program;
+    int (*create)(Program *, const char *, const char *, int, const char *const *, const char *const *) = nullptr;
+    int (*destroy)(Program *) = nullptr;
+    int (*add_name)(Program, const char *) = nullptr;
+    int (*compile)(Program, int, const char *const *) = nullptr;
+    int (*cubin_size)(Program, size_t *) = nullptr;
+    int (*cubin)(Program, char *) = nullptr;
+    int (*lowered)(Program, const char *, const char **) = nullptr;
+    int (*log_size)(Program, size_t *) = nullptr;
+    int (*log)(Program, char *) = nullptr;
+    bool ok = false;
+};
+
+const Nvrtc &nvrtc() {
+    static const Nvrtc n = [] {
+        Nvrtc r;
+        void *h = nullptr;
+        for (const char *name : {"libnvrtc.so.12", "libnvrtc.so", "/usr/local/cuda/lib64/libnvrtc.so.12"})
+            if ((h = dlopen(name, RTLD_NOW | RTLD_LOCAL)))
+                break;
+        if (!h)
+            return r;
+        auto sym = [&](const char *s) { return dlsym(h, s); };
+        r.create = reinterpret_cast<decltype(r.create)>(sym("nvrtcCreateProgram"));
+        r.destroy = reinterpret_cast<decltype(r.destroy)>(sym("nvrtcDestroyProgram"));
+        r.add_name = reinterpret_cast<decltype(r.add_name)>(sym("nvrtcAddNameExpression"));
+        r.compile = reinterpret_cast<decltype(r.compile)>(sym("nvrtcCompileProgram"));
+        r.cubin_size = reinterpret_cast<decltype(r.cubin_size)>(sym("nvrtcGetCUBINSize"));
+        r.cubin = reinterpret_cast<decltype(r.cubin)>(sym("nvrtcGetCUBIN"));
+        r.lowered = reinterpret_cast<decltype(r.lowered)>(sym("nvrtcGetLoweredName"));
+        r.log_size = reinterpret_cast<decltype(r.log_size)>(sym("nvrtcGetProgramLogSize"));
+        r.log = reinterpret_cast<decltype(r.log)>(sym("nvrtcGetProgramLog"));
+        r.ok = r.create && r.destroy && r.add_name && r.compile && r.cubin_size && r.cubin && r.lowered && r.log_size &&
+               r.log;
+        return r;
+    }();
+    return n;
+}
+
+struct Entry {
+    State state = COMPILING;
+    std::vector<char> cubin;
+    std::string lowered, log;
+    cudaLibrary_t lib = nullptr;
+    cudaKernel_t kernel = nullptr;
+    PerDeviceOnce attr;
+};
+
+// never destroyed: a compilation may still be running on its background thread when the process ends
+struct Globals {
+    std::mutex mu;
+    std::condition_variable cv;
+    std::map<std::string, std::shared_ptr<Entry>> cache; // by instantiation expression; entries are never removed
+    int pending = 0;
+    int mode = -1; // -1: not read from the environment yet
+};
+Globals &globals() {
+    static Globals *g = new Globals;
+    return *g;
+}
+#define g_mu (globals().mu)
+#define g_cv (globals().cv)
+#define g_cache (globals().cache)
+#define g_pending (globals().pending)
+#define g_mode (globals().mode)
+
+int mode_locked() {
+    if (g_mode < 0) {
+        const char *e = getenv("DB2_RTC");
+        g_mode = !e ? RTC_ASYNC : (e[0] == '0' ? RTC_OFF : (strcmp(e, "sync") == 0 ? RTC_SYNC : RTC_ASYNC));
+    }
+    return g_mode;
+}
+
+// fused_row_ct_kernel<Chain<S<op, kind, rev>...>, Taps<T<after, kind>...>, EW>
+std::string expression_of(const FusedProgram &P) {
+    std::string e = "db2::ct::fused_row_ct_kernel<db2::ct::Chain<";
+    for (int i = 0; i < P.nsteps; i++)
+        e += std::string(i ? "," : "") + "db2::ct::S<" + std::to_string(P.steps[i].op) + "," +
+             std::to_string(P.steps[i].kind) + "," + (P.steps[i].reversed ? "true" : "false") + ">";
+    e += ">,db2::ct::Taps<";
+    for (int i = 0; i < P.ntaps; i++)
+        e += std::string(i ? "," : "") + "db2::ct::T<" + std::to_string(P.taps[i].after_step) + "," +
+             std::to_string(P.taps[i].kind) + ">";
+    e += std::string(">,") + (P.ew_out ? "true" : "false") + ">";
+    return e;
+}
+
+// compiles one instantiation to a cubin for sm_100a; on failure the compiler's log is left in *log
+bool compile(const std::string &expr, std::vector<char> *cubin, std::string *lowered, std::string *log) {
+    const Nvrtc &n = nvrtc();
+    if (!n.ok) {
+        *log = "libnvrtc not found";
+        return false;
+    }
+    std::string src;
+    for (const char *piece : FUSED_RTC_SRC)
+        src += piece;
+    Nvrtc::Program prog = nullptr;
+    if (n.create(&prog, src.c_str(), "fused_ct_dev.cu", 0, nullptr, nullptr) != 0) {
+        *log = "nvrtcCreateProgram failed";
+        return false;
+    }
+    const char *opts[] = {"--gpu-architecture=sm_100a", "-std=c++17", "-lineinfo"};
+    bool ok = n.add_name(prog, expr.c_str()) == 0 && n.compile(prog, 3, opts) == 0;
+    size_t sz = 0;
+    if (!ok && n.log_size(prog, &sz) == 0 && sz > 1) {
+        log->resize(sz);
+        n.log(prog, &(*log)[0]);
+    }
+    const char *name = nullptr;
+    ok = ok && n.lowered(prog, expr.c_str(), &name) == 0 && name;
+    if (ok)
+        *lowered = name;
+    ok = ok && n.cubin_size(prog, &sz) == 0 && sz > 0;
+    if (ok) {
+        cubin->resize(sz);
+        ok = n.cubin(prog, cubin->data()) == 0;
+    }
+    n.destroy(&prog);
+    if (!ok && log->empty())
+        *log = "the run-time compiler returned no binary";
+    return ok;
+}
+
+void compile_entry(const std::string expr, std::shared_ptr<Entry> e) {
+    std::vector<char> cubin;
+    std::string lowered, log;
+    const bool ok = compile(expr, &cubin, &lowered, &log);
+    {
+        std::lock_guard<std::mutex> lock(g_mu);
+        e->cubin.swap(cubin);
+        e->lowered.swap(lowered);
+        e->log.swap(log);
+        e->state = ok ? COMPILED : FAILED;
+        g_pending--;
+    }
+    g_cv.notify_all();
+}
+
+} // namespace
+
+// Launches the run-time compiled specialisation of P's chain if it is ready (true; *rc is the launch's result).
+// Otherwise starts its compilation, if that has not happened yet, and returns false: the caller runs the interpreter.
+bool fused_row_pass_rtc(const FusedProgram &P, cudaStream_t st, int *rc) {
+    std::shared_ptr<Entry> e;
+    const std::string expr = expression_of(P);
+    {
+        std::unique_lock<std::mutex> lock(g_mu);
+        const int mode = mode_locked();
+        if (mode == RTC_OFF)
+            return false;
+        auto it = g_cache.find(expr);
+        if (it == g_cache.end()) {
+            e = std::make_shared<Entry>();
+            g_cache[expr] = e;
+            g_pending++;
+            lock.unlock();
+            if (mode == RTC_SYNC)
+                compile_entry(expr, e);
+            else
+                std::thread(compile_entry, expr, e).detach();
+            lock.lock();
+        } else {
+            e = it->second;
+        }
+        if (e->state == COMPILED) { // first call after the compiler finished: load the binary
+            cudaError_t err = cudaLibraryLoadData(&e->lib, e->cubin.data(), nullptr, nullptr, 0, nullptr, nullptr, 0);
+            if (err == cudaSuccess)
+                err = cudaLibraryGetKernel(&e->kernel, e->lib, e->lowered.c_str());
+            if (err != cudaSuccess) {
+                cudaGetLastError();
+                e->log = std::string("loading the compiled kernel failed: ") + cudaGetErrorString(err);
+                e->state = FAILED;
+            } else {
+                e->state = LOADED;
+                std::vector<char>().swap(e->cubin);
+            }
+        }
+        if (e->state != LOADED)
+            return false;
+    }
+    using namespace ct;
+    const size_t smem = (size_t)(WARPS * 2 * WR * CK + P.smem_elems + 2 * FUSED_MAX_STEPS) * sizeof(double) + 256;
+    const int64_t nblocks = ((P.rows + WR - 1) / WR + WARPS - 1) / WARPS;
+    const int64_t cap = (int64_t)sm_count() * 3; // RowCtasPerSm
+    const int grid = (int)(nblocks < cap ? nblocks : cap);
+    const void *fn = reinterpret_cast<const void *>(e->kernel);
+    if (e->attr.need()) {
+        const cudaError_t err = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, 128 * 1024);
+        if (err != cudaSuccess) {
+            cudaGetLastError();
+            return false;
+        }
+        e->attr.mark();
+    }
+    void *args[] = {const_cast<FusedProgram *>(&P)};
+    const cudaError_t err = cudaLaunchKernel(fn, dim3((unsigned)grid), dim3(RT), args, smem, st);
+    if (err != cudaSuccess) {
+        cudaGetLastError();
+        *rc = set_error(DB2_ECUDA, "launch of a run-time compiled row pass failed: %s", cudaGetErrorString(err));
+        return true;
+    }
+    *rc = after_launch("fused_row_ct_kernel (run-time compiled)");
+    return true;
+}
+
+} // namespace db2
+
+using namespace db2;
+
+extern "C" {
+
+int db2_rtc_set_mode(int mode) {
+    DB2_CHECK(mode >= RTC_OFF && mode <= RTC_SYNC, DB2_EINVAL, "mode must be 0 (off), 1 (background) or 2 (blocking)");
+    std::lock_guard<std::mutex> lock(g_mu);
+    g_mode = mode;
+    return DB2_OK;
+}
+
+int db2_rtc_wait(void) {
+    std::unique_lock<std::mutex> lock(g_mu);
+    g_cv.wait(lock, [] { return g_pending == 0; });
+    return DB2_OK;
+}
+
+int db2_rtc_counts(int *ready, int *pending, int *failed) {
+    std::lock_guard<std::mutex> lock(g_mu);
+    int r = 0, f = 0;
+    for (const auto &kv : g_cache) {
+        r += kv.second->state == COMPILED || kv.second->state == LOADED;
+        f += kv.second->state == FAILED;
+    }
+    if (ready)
+        *ready = r;
+    if (pending)
+        *pending = g_pending;
+    if (failed)
+        *failed = f;
+    return DB2_OK;
+}
+
+int db2_rtc_compile(const int *ops, const int *kinds, const int *reversed, int nsteps, const int *tap_after,
+                    const int *tap_kinds, int ntaps, int ew, size_t *binary_bytes) {
+    DB2_CHECK(nsteps >= 0 && nsteps <= FUSED_MAX_STEPS && ntaps >= 0 && ntaps <= FUSED_MAX_AGGS, DB2_EINVAL,
+              "at most %d steps and %d aggregations", FUSED_MAX_STEPS, FUSED_MAX_AGGS);
+    DB2_CHECK((nsteps == 0 || (ops && kinds && reversed)) && (ntaps == 0 || (tap_after && tap_kinds)), DB2_EINVAL,
+              "null argument");
+    FusedProgram P;
+    memset(&P, 0, sizeof(P));
+    P.nsteps = nsteps;
+    P.ntaps = ntaps;
+    for (int i = 0; i < nsteps; i++) {
+        DB2_CHECK(ops[i] >= 0 && ops[i] < FO_COUNT && kinds[i] >= FK_MATRIX && kinds[i] <= FK_UNARY, DB2_EINVAL,
+                  "step %d: unknown operation or operand kind", i);
+        P.steps[i].op = ops[i];
+        P.steps[i].kind = kinds[i];
+        P.steps[i].reversed = reversed[i] != 0;
+    }
+    for (int i = 0; i < ntaps; i++) {
+        DB2_CHECK(tap_after[i] >= 0 && tap_after[i] <= nsteps && tap_kinds[i] >= FT_SUM && tap_kinds[i] <= FT_MEAN,
+                  DB2_EINVAL, "aggregation %d: unknown kind or position", i);
+        P.taps[i].after_step = tap_after[i];
+        P.taps[i].kind = tap_kinds[i];
+    }
+    P.ew_out = ew ? &P : nullptr; // only its presence matters here
+    std::vector<char> cubin;
+    std::string lowered, log;
+    if (!compile(expression_of(P), &cubin, &lowered, &log))
+        return set_error(DB2_EUNSUPPORTED, "run-time compilation failed: %.900s", log.c_str());
+    if (binary_bytes)
+        *binary_bytes = cubin.size();
+    return DB2_OK;
+}
+
+} // extern "C"

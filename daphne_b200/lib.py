@@ -128,6 +128,10 @@ _SIGS = {
     "db2_dist_to_host": (i32, [vp, vp, i64]),
     "db2_dist_gather": (i32, [vp, i32, _P(vp)]),
     "db2_group_run": (i32, [vp, vp, vp]),
+    "db2_rtc_set_mode": (i32, [i32]),
+    "db2_rtc_wait": (i32, []),
+    "db2_rtc_counts": (i32, [_P(i32), _P(i32), _P(i32)]),
+    "db2_rtc_compile": (i32, [_P(i32), _P(i32), _P(i32), i32, _P(i32), _P(i32), i32, i32, _P(sz)]),
     "db2_group_allreduce": (i32, [vp, _P(vp), i32]),
     "db2_matrix_to_context": (i32, [vp, vp, _P(vp)]),
     "db2_matrix_copy_block": (i32, [vp, i64, i64, vp]),

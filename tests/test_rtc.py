@@ -1,0 +1,149 @@
+"""Chains without a compiled-in specialisation: the kernel template is instantiated by the run-time compiler.
+
+CPU part: every combination the deferred evaluation can record must compile for sm_100a (the compiler needs no device).
+GPU part: the compiled kernel must give the bits of the kernel that reads the chain at run time, and of the oracle."""
+import ctypes as C
+
+import numpy as np
+import pytest
+
+from daphne_b200.lib import lib, check, Db2Error
+
+OPS = ["ADD", "SUB", "MUL", "DIV", "SQUARE", "EQ", "NEQ", "LT", "LE", "GT", "GE", "MIN", "MAX", "AND", "OR", "NEG", "ABS",
+       "SIGN", "FLOOR", "CEIL", "ROUND", "ISNAN"]
+KINDS = {"M": 0, "R": 1, "C": 2, "S": 3, "U": 4}
+TAPS = {"SUM": 0, "PROD": 1, "MIN": 2, "MAX": 3, "MEAN": 4}
+
+
+def _compile(steps, taps, ew):
+    """steps: [("SUB", "R", False), ...]; taps: [("SUM", after), ...]"""
+    arr = lambda xs: (C.c_int * max(len(xs), 1))(*xs)
+    ops, kinds, rev = arr([OPS.index(s[0]) for s in steps]), arr([KINDS[s[1]] for s in steps]), arr([int(s[2]) for s in steps])
+    after, tk = arr([t[1] for t in taps]), arr([TAPS[t[0]] for t in taps])
+    n = C.c_size_t(0)
+    check(lib.db2_rtc_compile(ops, kinds, rev, len(steps), after, tk, len(taps), int(ew), C.byref(n)))
+    return n.value
+
+
+def _have_nvrtc():
+    try:
+        _compile([], [("SUM", 0)], False)
+        return True
+    except Db2Error as e:
+        if "libnvrtc not found" in str(e):
+            return False
+        raise
+
+
+needs_nvrtc = pytest.mark.skipif(not _have_nvrtc(), reason="libnvrtc is not installed")
+
+
+@needs_nvrtc
+@pytest.mark.parametrize("steps,taps,ew", [
+    ([("SUB", "R", False), ("MUL", "R", False), ("ADD", "S", False)], [("SUM", 3)], False),
+    ([("SUB", "R", False), ("MUL", "R", False), ("ADD", "S", False)], [], True),
+    ([("DIV", "C", False), ("DIV", "S", True), ("ABS", "U", False)], [("MIN", 1), ("MAX", 3), ("MEAN", 3)], True),
+    ([("MUL", "M", False), ("GT", "S", False), ("AND", "M", True), ("FLOOR", "U", False), ("ISNAN", "U", False)],
+     [("PROD", 0), ("SUM", 5)], False),
+    ([(op, "R", False) for op in OPS[:10]], [("SUM", 10), ("MIN", 4), ("MAX", 7), ("MEAN", 0)], True),
+])
+def test_chains_compile_for_sm_100a(steps, taps, ew):
+    assert _compile(steps, taps, ew) > 10_000  # a device binary, not an empty one
+
+
+@needs_nvrtc
+def test_every_operation_and_operand_kind_compiles():
+    for op in OPS:
+        unary = op in ("SQUARE", "NEG", "ABS", "SIGN", "FLOOR", "CEIL", "ROUND", "ISNAN")
+        for kind in (["U", "S"] if unary else ["M", "R", "C", "S"]):
+            for rev in ([False] if unary else [False, True]):
+                assert _compile([(op, kind, rev)], [("SUM", 1)], False) > 10_000, (op, kind, rev)
+
+
+def test_bad_arguments_are_refused():
+    with pytest.raises(Db2Error):
+        _compile([("ADD", "R", False)] * 11, [], True)       # more steps than a program holds
+    with pytest.raises(Db2Error):
+        _compile([("ADD", "R", False)], [("SUM", 2)], False)  # an aggregation after a step that does not exist
+    with pytest.raises(Db2Error):
+        check(lib.db2_rtc_set_mode(7))
+
+
+@pytest.mark.gpu
+@needs_nvrtc
+@pytest.mark.parametrize("shape", [(70000, 48), (4099, 50), (2049, 128), (300, 400)])
+def test_compiled_chain_gives_the_bits_of_the_run_time_kernel_and_of_the_oracle(ctx, shape):
+    import daphne_b200.kernels as k
+    from oracle import pyoracle as o
+    from tests.util import RTOL_REDUCE_F64, assert_bits_equal, assert_close_rel, rng_matrix
+    B, U, A = k.BinaryOpCode, k.UnaryOpCode, k.AggOpCode
+    r, c = shape
+    x, y = rng_matrix(3, r, c) - 5.0, rng_matrix(4, r, c) - 5.0
+    rv, cv = rng_matrix(5, 1, c) - 4.0, rng_matrix(6, r, 1) - 4.0
+    y[::7] = x[::7]
+    x[3, :4] = [0.0, -0.0, np.inf, np.nan]   # zeros, infinities and NaNs through every division
+    x[5, 0], cv[9, 0], rv[0, 2] = -0.0, 0.0, 1e-310
+
+    def run(kk, mk):
+        X, Y, RV, CV = mk(x), mk(y), mk(rv), mk(cv)
+        t = kk.ewBinaryMat(B.SUB, X, RV)            # row vector
+        t = kk.ewBinaryMat(B.DIV, t, CV)            # division by a column vector (no staged reciprocal)
+        t = kk.ewBinaryMat(B.DIV, t, RV)            # division by a row vector (staged reciprocal)
+        t = kk.ewBinaryObjSca(B.DIV, t, 3.7)        # by a scalar
+        t = kk.ewBinaryMat(B.DIV, t, Y)             # by a matrix
+        u = kk.ewUnaryMat(U.ABS, kk.ewBinaryMat(B.MAX, t, Y))
+        w = kk.ewBinaryMat(B.DIV, X, kk.ewBinaryMat(B.SUB, Y, u))  # reversed steps
+        z = kk.ewBinaryObjSca(B.ADD, kk.ewBinaryMat(B.MUL, kk.ewBinaryMat(B.SUB, X, RV), RV), 0.5)
+        return t, u, w, z
+
+    cpu = run(type("O", (), {"ewBinaryMat": staticmethod(o.ewBinaryMat), "ewBinaryObjSca": staticmethod(o.ewBinaryObjSca),
+                             "ewUnaryMat": staticmethod(o.ewUnaryMat)}), lambda a: a)
+    ready0 = C.c_int()
+    check(lib.db2_rtc_counts(C.byref(ready0), None, None))
+    try:
+        for mode, name in ((0, "run-time chain"), (2, "compiled chain")):
+            check(lib.db2_rtc_set_mode(mode))
+            dev = run(k, lambda a: k.DenseMatrix.from_numpy(ctx, a))
+            for i, (g, e) in enumerate(zip(dev, cpu)):
+                with np.errstate(all="ignore"):
+                    assert_bits_equal(k.aggRow(A.MIN, g).to_numpy(), o.aggRow(A.MIN, e), f"{name}: rowMin {i}")
+                    assert_bits_equal(k.aggRow(A.IDXMAX, g).to_numpy(), o.aggRow(A.IDXMAX, e), f"{name}: idxMax {i}")
+                    assert_bits_equal(g.to_numpy(), e, f"{name}: values {i}")
+            ok = ~np.isnan(cpu[3]).any(1) & ~np.isinf(cpu[3]).any(1)
+            got = k.aggRow(A.SUM, dev[3]).to_numpy()[ok]
+            assert_close_rel(got, o.aggRow(A.SUM, cpu[3])[ok], RTOL_REDUCE_F64, f"{name}: rowSum", scale=1e-9)
+        ready, pending, failed = C.c_int(), C.c_int(), C.c_int()
+        check(lib.db2_rtc_counts(C.byref(ready), C.byref(pending), C.byref(failed)))
+        assert failed.value == 0 and pending.value == 0
+        if c % 2 == 0:  # odd widths go through the general interpreter and are never compiled
+            assert ready.value > ready0.value or ready0.value > 0
+    finally:
+        check(lib.db2_rtc_set_mode(1))
+
+
+@pytest.mark.gpu
+@needs_nvrtc
+def test_background_compilation_takes_over_after_it_finishes(ctx):
+    """Default mode: the first call is served by the run-time kernel while the compiler works; after db2_rtc_wait the
+    same chain runs compiled.  Both must give the same bits."""
+    import daphne_b200.kernels as k
+    from tests.util import assert_bits_equal
+    B, A = k.BinaryOpCode, k.AggOpCode
+    rng = np.random.default_rng(77)
+    x, rv = rng.standard_normal((50000, 32)), rng.standard_normal((1, 32)) + 3.0
+    X, RV = k.DenseMatrix.from_numpy(ctx, x), k.DenseMatrix.from_numpy(ctx, rv)
+
+    def run():
+        z = k.ewBinaryObjSca(B.SUB, k.ewBinaryMat(B.DIV, k.ewBinaryMat(B.ADD, X, RV), RV), 0.125)
+        return k.aggRow(A.MAX, z).to_numpy(), k.aggRow(A.SUM, z).to_numpy()
+    check(lib.db2_rtc_set_mode(1))
+    first = run()
+    check(lib.db2_rtc_wait())
+    pending = C.c_int()
+    check(lib.db2_rtc_counts(None, C.byref(pending), None))
+    assert pending.value == 0
+    second = run()
+    for a, b in zip(first, second):
+        assert_bits_equal(b, a, "compiled against run-time chain")
+    ref = (x + rv) / rv - 0.125
+    assert_bits_equal(second[0], ref.max(1, keepdims=True), "row maximum")
