@@ -26,6 +26,10 @@ int fused_row_pass_f64(const FusedProgram &prog, cudaStream_t st);
 bool fused_row_pass_ct(const FusedProgram &prog, const char *signature, cudaStream_t st, int *rc);
 // the specialisation of prog's chain compiled at run time (fused_rtc.cu): true if it was launched
 bool fused_row_pass_rtc(const FusedProgram &prog, cudaStream_t st, int *rc);
+bool fused_col_pass_rtc(const FusedProgram &prog, int mean, void *res, void *scratch, cudaStream_t st, int *rc);
+// geometry and last step of the compile-time column pass (fused_ct.cu), shared with the kernels compiled at run time
+void fused_col_geometry(const FusedProgram &prog, unsigned (&grid)[2], unsigned (&block)[2]);
+int fused_col_finish(const FusedProgram &prog, unsigned parts, int mean, void *res, void *scratch, cudaStream_t st);
 bool fused_col_pass_ct(const FusedProgram &prog, const char *signature, int agg_op, void *res, void *scratch,
                        size_t scratch_bytes, cudaStream_t st, int *rc);
 // column aggregation of a chain: kind = K_SUM / K_MIN / K_MAX / K_PROD of agg.cu, epilogue like db2k_agg_col

@@ -41,116 +41,6 @@ template <typename ChainT, typename TapsT, bool EW> static int launch_row(const 
     return after_launch("fused_row_ct_kernel");
 }
 
-// ---------------------------------------------------------------------------
-// column pass with a compile-time chain (SUM only: the squared-deviation and plain column sums)
-// ---------------------------------------------------------------------------
-constexpr int CT_THREADS = 256;
-
-template <typename ChainT, int I = 0>
-__device__ __forceinline__ void load_rowvec_regs(double (&rv)[ChainT::n > 0 ? ChainT::n : 1][2],
-                                                 double (&ry)[ChainT::n > 0 ? ChainT::n : 1][2],
-                                                 const FusedProgram &P, int64_t c0) {
-    if constexpr (I < ChainT::n) {
-        using St = typename At<I, ChainT>::type;
-        rv[I][0] = rv[I][1] = ry[I][0] = ry[I][1] = 0.0;
-        if constexpr (St::kind == FK_ROWVEC) {
-            const double *src = static_cast<const double *>(P.steps[I].ptr) + c0;
-            rv[I][0] = src[0];
-            rv[I][1] = src[1];
-            if constexpr (St::op == FO_DIV && !St::rev) {
-                ry[I][0] = div_helper(rv[I][0]);
-                ry[I][1] = div_helper(rv[I][1]);
-            }
-        } else if constexpr (St::kind == FK_SCALAR) {
-            rv[I][0] = rv[I][1] = P.steps[I].imm;
-            if constexpr (St::op == FO_DIV && !St::rev)
-                ry[I][0] = ry[I][1] = div_helper(P.steps[I].imm);
-        }
-        load_rowvec_regs<ChainT, I + 1>(rv, ry, P, c0);
-    }
-}
-template <typename ChainT, int I = 0>
-__device__ __forceinline__ double col_chain(double v, int k, const double (&rv)[ChainT::n > 0 ? ChainT::n : 1][2],
-                                            const double (&ry)[ChainT::n > 0 ? ChainT::n : 1][2],
-                                            const FusedProgram &P, int64_t r, int64_t c) {
-    if constexpr (I < ChainT::n) {
-        using St = typename At<I, ChainT>::type;
-        double o = rv[I][k], y = ry[I][k];
-        if constexpr (St::kind == FK_COLVEC)
-            o = __ldg(static_cast<const double *>(P.steps[I].ptr) + r * P.steps[I].ld);
-        else if constexpr (St::kind == FK_MATRIX)
-            o = __ldg(static_cast<const double *>(P.steps[I].ptr) + r * P.steps[I].ld + c);
-        v = apply<St::op, St::rev>(v, o, y);
-        return col_chain<ChainT, I + 1>(v, k, rv, ry, P, r, c);
-    } else
-        return v;
-}
-
-// blockDim = (TX, 256 / TX); requires even cols, 16-byte aligned base and even ld
-template <typename ChainT>
-__global__ void __launch_bounds__(CT_THREADS)
-    fused_col_sum_ct_kernel(const __grid_constant__ FusedProgram P, double *__restrict__ part) {
-    __shared__ double sv[CT_THREADS * 2];
-    if (P.run_if && *P.run_if == 0)
-        return;
-    const int tx = threadIdx.x, ty = threadIdx.y, TX = blockDim.x, TY = blockDim.y;
-    const int64_t rows = P.rows, cols = P.cols;
-    const int64_t c0 = ((int64_t)blockIdx.y * TX + tx) * 2;
-    double a0 = 0.0, a1 = 0.0, b0 = 0.0, b1 = 0.0;
-    if (c0 < cols) {
-        double rv[ChainT::n > 0 ? ChainT::n : 1][2], ry[ChainT::n > 0 ? ChainT::n : 1][2];
-        load_rowvec_regs<ChainT>(rv, ry, P, c0);
-        const double *base = static_cast<const double *>(P.base);
-        const int64_t stride = (int64_t)gridDim.x * TY;
-        int64_t r = (int64_t)blockIdx.x * TY + ty;
-        // four rows in flight per thread (the pass is bound by memory latency); the adds keep the row order
-        for (; r + 3 * stride < rows; r += 4 * stride) {
-            Pack<double> p[4];
-#pragma unroll
-            for (int u = 0; u < 4; u++)
-                p[u] = ld_pack_stream(base + (r + u * stride) * P.base_ld + c0);
-            double v0[4], v1[4];
-#pragma unroll
-            for (int u = 0; u < 4; u++) {
-                v0[u] = col_chain<ChainT>(p[u].v[0], 0, rv, ry, P, r + u * stride, c0);
-                v1[u] = col_chain<ChainT>(p[u].v[1], 1, rv, ry, P, r + u * stride, c0 + 1);
-            }
-            a0 = __dadd_rn(a0, v0[0]);
-            a1 = __dadd_rn(a1, v1[0]);
-            b0 = __dadd_rn(b0, v0[1]);
-            b1 = __dadd_rn(b1, v1[1]);
-            a0 = __dadd_rn(a0, v0[2]);
-            a1 = __dadd_rn(a1, v1[2]);
-            b0 = __dadd_rn(b0, v0[3]);
-            b1 = __dadd_rn(b1, v1[3]);
-        }
-        for (; r + stride < rows; r += 2 * stride) {
-            const Pack<double> p = ld_pack_stream(base + r * P.base_ld + c0);
-            const Pack<double> q = ld_pack_stream(base + (r + stride) * P.base_ld + c0);
-            a0 = __dadd_rn(a0, col_chain<ChainT>(p.v[0], 0, rv, ry, P, r, c0));
-            a1 = __dadd_rn(a1, col_chain<ChainT>(p.v[1], 1, rv, ry, P, r, c0 + 1));
-            b0 = __dadd_rn(b0, col_chain<ChainT>(q.v[0], 0, rv, ry, P, r + stride, c0));
-            b1 = __dadd_rn(b1, col_chain<ChainT>(q.v[1], 1, rv, ry, P, r + stride, c0 + 1));
-        }
-        for (; r < rows; r += stride) {
-            const Pack<double> p = ld_pack_stream(base + r * P.base_ld + c0);
-            a0 = __dadd_rn(a0, col_chain<ChainT>(p.v[0], 0, rv, ry, P, r, c0));
-            a1 = __dadd_rn(a1, col_chain<ChainT>(p.v[1], 1, rv, ry, P, r, c0 + 1));
-        }
-    }
-    sv[(ty * TX + tx) * 2] = __dadd_rn(a0, b0);
-    sv[(ty * TX + tx) * 2 + 1] = __dadd_rn(a1, b1);
-    __syncthreads();
-    for (int k = ty; k < 2; k += TY) {
-        if (c0 + k < cols) {
-            double a = sv[tx * 2 + k];
-            for (int y = 1; y < TY; y++)
-                a = __dadd_rn(a, sv[(y * TX + tx) * 2 + k]);
-            part[(int64_t)blockIdx.x * cols + c0 + k] = a;
-        }
-    }
-}
-
 __global__ void col_sum_final_kernel(const double *__restrict__ part, int nparts, int64_t cols, int64_t count,
                                      int mean, double *__restrict__ res, const int32_t *__restrict__ run_if) {
     if (run_if && *run_if == 0)
@@ -170,25 +60,43 @@ __global__ void col_sum_final_kernel(const double *__restrict__ part, int nparts
         res[c] = mean ? __ddiv_rn(a, (double)count) : a;
 }
 
-template <typename ChainT>
-static int launch_col_sum(const FusedProgram &prog, int mean, void *res, void *scratch, cudaStream_t st) {
+} // namespace ct
+
+// launch geometry of the column pass: blockDim = (tx, 256 / tx), grid = (gx row slices, gy column slices)
+void fused_col_geometry(const FusedProgram &prog, unsigned (&grid)[2], unsigned (&block)[2]) {
     const int64_t packets = prog.cols / 2;
     int tx = next_pow2(packets);
     if (tx > 32)
         tx = 32;
-    const int ty = CT_THREADS / tx;
+    const int ty = ct::CT_THREADS / tx;
     const int gy = (int)((packets + tx - 1) / tx);
     int64_t cap = ((int64_t)sm_count() * 8 + gy - 1) / gy;
     int64_t want = (prog.rows + (int64_t)ty * 8 - 1) / ((int64_t)ty * 8);
     if (want < 1)
         want = 1;
-    const int gx = (int)(want < cap ? want : cap);
-    double *part = static_cast<double *>(scratch);
-    fused_col_sum_ct_kernel<ChainT><<<dim3(gx, gy), dim3(tx, ty), 0, st>>>(prog, part);
-    DB2_TRY(after_launch("fused_col_sum_ct_kernel"));
-    col_sum_final_kernel<<<(unsigned)((prog.cols * 32 + 255) / 256), 256, 0, st>>>(part, gx, prog.cols, prog.rows, mean,
-                                                                            static_cast<double *>(res), prog.run_if);
+    grid[0] = (unsigned)(want < cap ? want : cap);
+    grid[1] = (unsigned)gy;
+    block[0] = (unsigned)tx;
+    block[1] = (unsigned)ty;
+}
+// the partial sums of `parts` row slices (scratch) -> res
+int fused_col_finish(const FusedProgram &prog, unsigned parts, int mean, void *res, void *scratch, cudaStream_t st) {
+    ct::col_sum_final_kernel<<<(unsigned)((prog.cols * 32 + 255) / 256), 256, 0, st>>>(
+        static_cast<const double *>(scratch), (int)parts, prog.cols, prog.rows, mean, static_cast<double *>(res),
+        prog.run_if);
     return after_launch("col_sum_final_kernel");
+}
+
+namespace ct {
+
+template <typename ChainT>
+static int launch_col_sum(const FusedProgram &prog, int mean, void *res, void *scratch, cudaStream_t st) {
+    unsigned grid[2], block[2];
+    fused_col_geometry(prog, grid, block);
+    fused_col_sum_ct_kernel<ChainT><<<dim3(grid[0], grid[1]), dim3(block[0], block[1]), 0, st>>>(
+        prog, static_cast<double *>(scratch));
+    DB2_TRY(after_launch("fused_col_sum_ct_kernel"));
+    return fused_col_finish(prog, grid[0], mean, res, scratch, st);
 }
 
 // ---------------------------------------------------------------------------
@@ -277,7 +185,8 @@ bool fused_col_pass_ct(const FusedProgram &P, const char *signature, int agg_op,
             *rc = e.launch(P, agg_op == DB2_AGG_MEAN ? 1 : 0, res, scratch, st);
             return true;
         }
-    return false;
+    // not in the table: the kernel compiled for this chain at run time, once it exists; until then the general pass
+    return fused_col_pass_rtc(P, agg_op == DB2_AGG_MEAN ? 1 : 0, res, scratch, st, rc);
 }
 
 } // namespace db2

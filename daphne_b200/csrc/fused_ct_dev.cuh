@@ -768,5 +768,120 @@ __global__ void __launch_bounds__(RT, RowCtasPerSm<ChainT>::value) fused_row_ct_
     }
 }
 
+// ---------------------------------------------------------------------------
+// column pass with a compile-time chain (SUM only: the squared-deviation and plain column sums)
+// ---------------------------------------------------------------------------
+constexpr int CT_THREADS = 256;
+// streaming load of two neighbouring values: read once, not kept in L1
+__device__ __forceinline__ double2 ld_pair_stream(const double *p) { return __ldcs(reinterpret_cast<const double2 *>(p)); }
+
+template <typename ChainT, int I = 0>
+__device__ __forceinline__ void load_rowvec_regs(double (&rv)[ChainT::n > 0 ? ChainT::n : 1][2],
+                                                 double (&ry)[ChainT::n > 0 ? ChainT::n : 1][2],
+                                                 const FusedProgram &P, int64_t c0) {
+    if constexpr (I < ChainT::n) {
+        using St = typename At<I, ChainT>::type;
+        rv[I][0] = rv[I][1] = ry[I][0] = ry[I][1] = 0.0;
+        if constexpr (St::kind == FK_ROWVEC) {
+            const double *src = static_cast<const double *>(P.steps[I].ptr) + c0;
+            rv[I][0] = src[0];
+            rv[I][1] = src[1];
+            if constexpr (St::op == FO_DIV && !St::rev) {
+                ry[I][0] = div_helper(rv[I][0]);
+                ry[I][1] = div_helper(rv[I][1]);
+            }
+        } else if constexpr (St::kind == FK_SCALAR) {
+            rv[I][0] = rv[I][1] = P.steps[I].imm;
+            if constexpr (St::op == FO_DIV && !St::rev)
+                ry[I][0] = ry[I][1] = div_helper(P.steps[I].imm);
+        }
+        load_rowvec_regs<ChainT, I + 1>(rv, ry, P, c0);
+    }
+}
+template <typename ChainT, int I = 0>
+__device__ __forceinline__ double col_chain(double v, int k, const double (&rv)[ChainT::n > 0 ? ChainT::n : 1][2],
+                                            const double (&ry)[ChainT::n > 0 ? ChainT::n : 1][2],
+                                            const FusedProgram &P, int64_t r, int64_t c) {
+    if constexpr (I < ChainT::n) {
+        using St = typename At<I, ChainT>::type;
+        double o = rv[I][k], y = ry[I][k];
+        if constexpr (St::kind == FK_COLVEC)
+            o = __ldg(static_cast<const double *>(P.steps[I].ptr) + r * P.steps[I].ld);
+        else if constexpr (St::kind == FK_MATRIX)
+            o = __ldg(static_cast<const double *>(P.steps[I].ptr) + r * P.steps[I].ld + c);
+        if constexpr (St::op == FO_DIV && !St::rev && St::kind != FK_ROWVEC && St::kind != FK_SCALAR)
+            v = __ddiv_rn(v, o); // no reciprocal helper exists for a column-vector or matrix divisor
+        else
+            v = apply<St::op, St::rev>(v, o, y);
+        return col_chain<ChainT, I + 1>(v, k, rv, ry, P, r, c);
+    } else
+        return v;
+}
+
+// blockDim = (TX, 256 / TX); requires even cols, 16-byte aligned base and even ld
+template <typename ChainT>
+__global__ void __launch_bounds__(CT_THREADS)
+    fused_col_sum_ct_kernel(const __grid_constant__ FusedProgram P, double *__restrict__ part) {
+    __shared__ double sv[CT_THREADS * 2];
+    if (P.run_if && *P.run_if == 0)
+        return;
+    const int tx = threadIdx.x, ty = threadIdx.y, TX = blockDim.x, TY = blockDim.y;
+    const int64_t rows = P.rows, cols = P.cols;
+    const int64_t c0 = ((int64_t)blockIdx.y * TX + tx) * 2;
+    double a0 = 0.0, a1 = 0.0, b0 = 0.0, b1 = 0.0;
+    if (c0 < cols) {
+        double rv[ChainT::n > 0 ? ChainT::n : 1][2], ry[ChainT::n > 0 ? ChainT::n : 1][2];
+        load_rowvec_regs<ChainT>(rv, ry, P, c0);
+        const double *base = static_cast<const double *>(P.base);
+        const int64_t stride = (int64_t)gridDim.x * TY;
+        int64_t r = (int64_t)blockIdx.x * TY + ty;
+        // four rows in flight per thread (the pass is bound by memory latency); the adds keep the row order
+        for (; r + 3 * stride < rows; r += 4 * stride) {
+            double2 p[4];
+#pragma unroll
+            for (int u = 0; u < 4; u++)
+                p[u] = ld_pair_stream(base + (r + u * stride) * P.base_ld + c0);
+            double v0[4], v1[4];
+#pragma unroll
+            for (int u = 0; u < 4; u++) {
+                v0[u] = col_chain<ChainT>(p[u].x, 0, rv, ry, P, r + u * stride, c0);
+                v1[u] = col_chain<ChainT>(p[u].y, 1, rv, ry, P, r + u * stride, c0 + 1);
+            }
+            a0 = __dadd_rn(a0, v0[0]);
+            a1 = __dadd_rn(a1, v1[0]);
+            b0 = __dadd_rn(b0, v0[1]);
+            b1 = __dadd_rn(b1, v1[1]);
+            a0 = __dadd_rn(a0, v0[2]);
+            a1 = __dadd_rn(a1, v1[2]);
+            b0 = __dadd_rn(b0, v0[3]);
+            b1 = __dadd_rn(b1, v1[3]);
+        }
+        for (; r + stride < rows; r += 2 * stride) {
+            const double2 p = ld_pair_stream(base + r * P.base_ld + c0);
+            const double2 q = ld_pair_stream(base + (r + stride) * P.base_ld + c0);
+            a0 = __dadd_rn(a0, col_chain<ChainT>(p.x, 0, rv, ry, P, r, c0));
+            a1 = __dadd_rn(a1, col_chain<ChainT>(p.y, 1, rv, ry, P, r, c0 + 1));
+            b0 = __dadd_rn(b0, col_chain<ChainT>(q.x, 0, rv, ry, P, r + stride, c0));
+            b1 = __dadd_rn(b1, col_chain<ChainT>(q.y, 1, rv, ry, P, r + stride, c0 + 1));
+        }
+        for (; r < rows; r += stride) {
+            const double2 p = ld_pair_stream(base + r * P.base_ld + c0);
+            a0 = __dadd_rn(a0, col_chain<ChainT>(p.x, 0, rv, ry, P, r, c0));
+            a1 = __dadd_rn(a1, col_chain<ChainT>(p.y, 1, rv, ry, P, r, c0 + 1));
+        }
+    }
+    sv[(ty * TX + tx) * 2] = __dadd_rn(a0, b0);
+    sv[(ty * TX + tx) * 2 + 1] = __dadd_rn(a1, b1);
+    __syncthreads();
+    for (int k = ty; k < 2; k += TY) {
+        if (c0 + k < cols) {
+            double a = sv[tx * 2 + k];
+            for (int y = 1; y < TY; y++)
+                a = __dadd_rn(a, sv[(y * TX + tx) * 2 + k]);
+            part[(int64_t)blockIdx.x * cols + c0 + k] = a;
+        }
+    }
+}
+
 } // namespace ct
 } // namespace db2

@@ -6,10 +6,12 @@
 // reference; the compiled-in table (fused_ct.cu) covers the chains of the benchmark pipelines, this file every other
 // DaphneDSL expression that the deferred evaluation turns into a chain.
 //
-// The compilation (about a second) runs on a background thread: the calls that arrive meanwhile are served by the
-// run-time chain interpreter of the same kernel, and the first call after the compilation has finished loads the
-// binary and uses it from then on.  DB2_RTC=sync compiles on the calling thread instead, DB2_RTC=0 switches the
-// mechanism off (as does a missing libnvrtc); db2_rtc_set_mode does the same at run time.
+// The compilation takes 0.4 to 0.8 s per chain.  By default it runs on the calling thread, the first time a chain is
+// evaluated.  DB2_RTC=async (or db2_rtc_set_mode(1)) moves it to a background thread: the calls that arrive meanwhile
+// are served by the run-time chain interpreter of the same kernel, and the first call after the compilation has
+// finished loads the binary and uses it from then on.  A process in that mode must not end while a compilation is
+// running (the compiler's own static objects would be destroyed under it): db2_context_destroy and db2_rtc_wait
+// wait for it.  DB2_RTC=0 switches the mechanism off, as does a missing libnvrtc.
 #include "fused.cuh"
 #include "fused_ct_dev.cuh"
 
@@ -101,24 +103,30 @@ Globals &globals() {
 int mode_locked() {
     if (g_mode < 0) {
         const char *e = getenv("DB2_RTC");
-        g_mode = !e ? RTC_ASYNC : (e[0] == '0' ? RTC_OFF : (strcmp(e, "sync") == 0 ? RTC_SYNC : RTC_ASYNC));
+        g_mode = !e ? RTC_SYNC : (e[0] == '0' ? RTC_OFF : (strcmp(e, "async") == 0 ? RTC_ASYNC : RTC_SYNC));
     }
     return g_mode;
 }
 
-// fused_row_ct_kernel<Chain<S<op, kind, rev>...>, Taps<T<after, kind>...>, EW>
-std::string expression_of(const FusedProgram &P) {
-    std::string e = "db2::ct::fused_row_ct_kernel<db2::ct::Chain<";
+// Chain<S<op, kind, rev>...>
+std::string chain_of(const FusedProgram &P) {
+    std::string e = "db2::ct::Chain<";
     for (int i = 0; i < P.nsteps; i++)
         e += std::string(i ? "," : "") + "db2::ct::S<" + std::to_string(P.steps[i].op) + "," +
              std::to_string(P.steps[i].kind) + "," + (P.steps[i].reversed ? "true" : "false") + ">";
-    e += ">,db2::ct::Taps<";
+    return e + ">";
+}
+// fused_row_ct_kernel<Chain<...>, Taps<T<after, kind>...>, EW>
+std::string expression_of(const FusedProgram &P) {
+    std::string e = "db2::ct::fused_row_ct_kernel<" + chain_of(P) + ",db2::ct::Taps<";
     for (int i = 0; i < P.ntaps; i++)
         e += std::string(i ? "," : "") + "db2::ct::T<" + std::to_string(P.taps[i].after_step) + "," +
              std::to_string(P.taps[i].kind) + ">";
     e += std::string(">,") + (P.ew_out ? "true" : "false") + ">";
     return e;
 }
+// fused_col_sum_ct_kernel<Chain<...>>
+std::string col_expression_of(const FusedProgram &P) { return "db2::ct::fused_col_sum_ct_kernel<" + chain_of(P) + ">"; }
 
 // compiles one instantiation to a cubin for sm_100a; on failure the compiler's log is left in *log
 bool compile(const std::string &expr, std::vector<char> *cubin, std::string *lowered, std::string *log) {
@@ -174,46 +182,52 @@ void compile_entry(const std::string expr, std::shared_ptr<Entry> e) {
 
 } // namespace
 
+namespace {
+// The loaded kernel of an instantiation, or null: not ready yet (its compilation is started if it has not been), failed
+// or switched off.
+std::shared_ptr<Entry> kernel_of(const std::string &expr) {
+    std::shared_ptr<Entry> e;
+    std::unique_lock<std::mutex> lock(g_mu);
+    const int mode = mode_locked();
+    if (mode == RTC_OFF)
+        return nullptr;
+    auto it = g_cache.find(expr);
+    if (it == g_cache.end()) {
+        e = std::make_shared<Entry>();
+        g_cache[expr] = e;
+        g_pending++;
+        lock.unlock();
+        if (mode == RTC_SYNC)
+            compile_entry(expr, e);
+        else
+            std::thread(compile_entry, expr, e).detach();
+        lock.lock();
+    } else {
+        e = it->second;
+    }
+    if (e->state == COMPILED) { // first call after the compiler finished: load the binary
+        cudaError_t err = cudaLibraryLoadData(&e->lib, e->cubin.data(), nullptr, nullptr, 0, nullptr, nullptr, 0);
+        if (err == cudaSuccess)
+            err = cudaLibraryGetKernel(&e->kernel, e->lib, e->lowered.c_str());
+        if (err != cudaSuccess) {
+            cudaGetLastError();
+            e->log = std::string("loading the compiled kernel failed: ") + cudaGetErrorString(err);
+            e->state = FAILED;
+        } else {
+            e->state = LOADED;
+            std::vector<char>().swap(e->cubin);
+        }
+    }
+    return e->state == LOADED ? e : nullptr;
+}
+} // namespace
+
 // Launches the run-time compiled specialisation of P's chain if it is ready (true; *rc is the launch's result).
 // Otherwise starts its compilation, if that has not happened yet, and returns false: the caller runs the interpreter.
 bool fused_row_pass_rtc(const FusedProgram &P, cudaStream_t st, int *rc) {
-    std::shared_ptr<Entry> e;
-    const std::string expr = expression_of(P);
-    {
-        std::unique_lock<std::mutex> lock(g_mu);
-        const int mode = mode_locked();
-        if (mode == RTC_OFF)
-            return false;
-        auto it = g_cache.find(expr);
-        if (it == g_cache.end()) {
-            e = std::make_shared<Entry>();
-            g_cache[expr] = e;
-            g_pending++;
-            lock.unlock();
-            if (mode == RTC_SYNC)
-                compile_entry(expr, e);
-            else
-                std::thread(compile_entry, expr, e).detach();
-            lock.lock();
-        } else {
-            e = it->second;
-        }
-        if (e->state == COMPILED) { // first call after the compiler finished: load the binary
-            cudaError_t err = cudaLibraryLoadData(&e->lib, e->cubin.data(), nullptr, nullptr, 0, nullptr, nullptr, 0);
-            if (err == cudaSuccess)
-                err = cudaLibraryGetKernel(&e->kernel, e->lib, e->lowered.c_str());
-            if (err != cudaSuccess) {
-                cudaGetLastError();
-                e->log = std::string("loading the compiled kernel failed: ") + cudaGetErrorString(err);
-                e->state = FAILED;
-            } else {
-                e->state = LOADED;
-                std::vector<char>().swap(e->cubin);
-            }
-        }
-        if (e->state != LOADED)
-            return false;
-    }
+    std::shared_ptr<Entry> e = kernel_of(expression_of(P));
+    if (!e)
+        return false;
     using namespace ct;
     const size_t smem = (size_t)(WARPS * 2 * WR * CK + P.smem_elems + 2 * FUSED_MAX_STEPS) * sizeof(double) + 256;
     const int64_t nblocks = ((P.rows + WR - 1) / WR + WARPS - 1) / WARPS;
@@ -236,6 +250,28 @@ bool fused_row_pass_rtc(const FusedProgram &P, cudaStream_t st, int *rc) {
         return true;
     }
     *rc = after_launch("fused_row_ct_kernel (run-time compiled)");
+    return true;
+}
+
+// The same for the column sums / means of a chain; until the kernel exists the caller runs the general column pass.
+bool fused_col_pass_rtc(const FusedProgram &P, int mean, void *res, void *scratch, cudaStream_t st, int *rc) {
+    std::shared_ptr<Entry> e = kernel_of(col_expression_of(P));
+    if (!e)
+        return false;
+    unsigned grid[2], block[2];
+    fused_col_geometry(P, grid, block);
+    double *part = static_cast<double *>(scratch);
+    void *args[] = {const_cast<FusedProgram *>(&P), &part};
+    const cudaError_t err = cudaLaunchKernel(reinterpret_cast<const void *>(e->kernel), dim3(grid[0], grid[1]),
+                                             dim3(block[0], block[1]), args, 0, st);
+    if (err != cudaSuccess) {
+        cudaGetLastError();
+        *rc = set_error(DB2_ECUDA, "launch of a run-time compiled column pass failed: %s", cudaGetErrorString(err));
+        return true;
+    }
+    *rc = after_launch("fused_col_sum_ct_kernel (run-time compiled)");
+    if (*rc == DB2_OK)
+        *rc = fused_col_finish(P, grid[0], mean, res, scratch, st);
     return true;
 }
 
@@ -276,7 +312,10 @@ int db2_rtc_counts(int *ready, int *pending, int *failed) {
 
 int db2_rtc_compile(const int *ops, const int *kinds, const int *reversed, int nsteps, const int *tap_after,
                     const int *tap_kinds, int ntaps, int ew, size_t *binary_bytes) {
-    DB2_CHECK(nsteps >= 0 && nsteps <= FUSED_MAX_STEPS && ntaps >= 0 && ntaps <= FUSED_MAX_AGGS, DB2_EINVAL,
+    const bool column_pass = ntaps < 0; // column sums of the chain instead of row aggregations
+    if (column_pass)
+        ntaps = 0;
+    DB2_CHECK(nsteps >= 0 && nsteps <= FUSED_MAX_STEPS && ntaps <= FUSED_MAX_AGGS, DB2_EINVAL,
               "at most %d steps and %d aggregations", FUSED_MAX_STEPS, FUSED_MAX_AGGS);
     DB2_CHECK((nsteps == 0 || (ops && kinds && reversed)) && (ntaps == 0 || (tap_after && tap_kinds)), DB2_EINVAL,
               "null argument");
@@ -300,7 +339,7 @@ int db2_rtc_compile(const int *ops, const int *kinds, const int *reversed, int n
     P.ew_out = ew ? &P : nullptr; // only its presence matters here
     std::vector<char> cubin;
     std::string lowered, log;
-    if (!compile(expression_of(P), &cubin, &lowered, &log))
+    if (!compile(column_pass ? col_expression_of(P) : expression_of(P), &cubin, &lowered, &log))
         return set_error(DB2_EUNSUPPORTED, "run-time compilation failed: %.900s", log.c_str());
     if (binary_bytes)
         *binary_bytes = cubin.size();

@@ -250,6 +250,7 @@ int db2_context_destroy(db2_context *ctx) {
         return DB2_OK;
     bind_device(ctx);
     cudaStreamSynchronize(ctx->stream);
+    db2_rtc_wait(); // a background compilation of a chain's kernel (fused_rtc.cu) must not outlive the process
     ctx_release(ctx);
     return DB2_OK;
 }

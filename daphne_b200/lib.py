@@ -4,6 +4,7 @@ There is no CPU fallback: if the shared library is missing the import fails with
 and every compute call needs a CUDA device."""
 from __future__ import annotations
 
+import atexit
 import ctypes as C
 from pathlib import Path
 
@@ -208,6 +209,9 @@ def declare(sigs: dict) -> None:
 
 
 declare(_SIGS)
+
+# a background compilation of a chain's kernel (db2_rtc_set_mode(1)) must have finished before the process ends
+atexit.register(lib.db2_rtc_wait)
 
 
 def exported_symbols() -> list[str]:

@@ -466,8 +466,10 @@ int db2_dist_gather(db2_dist *d, int index, db2_matrix **out);
 /* Elementwise chains that have no specialised kernel compiled into the library get one from the run-time compiler
  * (NVRTC), once per chain and process; until it is ready such chains are evaluated by a kernel that reads the chain at
  * run time.  DAPHNE has no counterpart (it launches one kernel per operator, e.g. src/runtime/local/kernels/CUDA/
- * EwBinaryMat.cu:97-263 for every binary step).  mode: 0 = never compile, 1 = compile on a background thread (the
- * default; environment DB2_RTC=0 / sync overrides it), 2 = compile on the calling thread. */
+ * EwBinaryMat.cu:97-263 for every binary step).  mode: 0 = never compile, 2 = compile on the calling thread when a
+ * chain is first evaluated (0.4 - 0.8 s; the default), 1 = compile on a background thread while the run-time kernel
+ * serves the calls (the process must not end while a compilation runs: db2_context_destroy and db2_rtc_wait wait
+ * for it).  Environment: DB2_RTC=0 / async. */
 int db2_rtc_set_mode(int mode);
 /* returns when no compilation is running any more */
 int db2_rtc_wait(void);
@@ -477,7 +479,8 @@ int db2_rtc_counts(int *ready, int *pending, int *failed);
  * BinaryOpCode ADD SUB MUL DIV, then SQUARE EQ NEQ LT LE GT GE MIN MAX AND OR NEG ABS SIGN FLOOR CEIL ROUND ISNAN =
  * 0..21) with an operand of kinds[i] (0 matrix, 1 row vector, 2 column vector, 3 scalar, 4 none), operands swapped if
  * reversed[i]; row aggregation j of tap_kinds[j] (0 SUM 1 PROD 2 MIN 3 MAX 4 MEAN) sees the values after tap_after[j]
- * steps; ew != 0: the final values are stored.  Needs no device.  *binary_bytes: size of the device binary. */
+ * steps; ew != 0: the final values are stored; ntaps < 0: the kernel of the column sums of the chain instead.  Needs no
+ * device.  *binary_bytes: size of the device binary. */
 int db2_rtc_compile(const int *ops, const int *kinds, const int *reversed, int nsteps, const int *tap_after,
                     const int *tap_kinds, int ntaps, int ew, size_t *binary_bytes);
 /* fn(device index, that device's context, user) on all devices of the group at once, each on its device's worker thread */

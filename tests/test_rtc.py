@@ -15,13 +15,14 @@ KINDS = {"M": 0, "R": 1, "C": 2, "S": 3, "U": 4}
 TAPS = {"SUM": 0, "PROD": 1, "MIN": 2, "MAX": 3, "MEAN": 4}
 
 
-def _compile(steps, taps, ew):
-    """steps: [("SUB", "R", False), ...]; taps: [("SUM", after), ...]"""
+def _compile(steps, taps, ew, column_pass=False):
+    """steps: [("SUB", "R", False), ...]; taps: [("SUM", after), ...]; column_pass: the column sums of the chain"""
     arr = lambda xs: (C.c_int * max(len(xs), 1))(*xs)
     ops, kinds, rev = arr([OPS.index(s[0]) for s in steps]), arr([KINDS[s[1]] for s in steps]), arr([int(s[2]) for s in steps])
     after, tk = arr([t[1] for t in taps]), arr([TAPS[t[0]] for t in taps])
     n = C.c_size_t(0)
-    check(lib.db2_rtc_compile(ops, kinds, rev, len(steps), after, tk, len(taps), int(ew), C.byref(n)))
+    check(lib.db2_rtc_compile(ops, kinds, rev, len(steps), after, tk, -1 if column_pass else len(taps), int(ew),
+                              C.byref(n)))
     return n.value
 
 
@@ -58,6 +59,13 @@ def test_every_operation_and_operand_kind_compiles():
         for kind in (["U", "S"] if unary else ["M", "R", "C", "S"]):
             for rev in ([False] if unary else [False, True]):
                 assert _compile([(op, kind, rev)], [("SUM", 1)], False) > 10_000, (op, kind, rev)
+
+
+@needs_nvrtc
+def test_column_sums_of_a_chain_compile():
+    assert _compile([("SUB", "R", False), ("MUL", "C", False), ("DIV", "M", False), ("ABS", "U", False)], [], False,
+                    column_pass=True) > 5_000
+    assert _compile([("DIV", "R", False), ("DIV", "S", True)], [], False, column_pass=True) > 5_000
 
 
 def test_bad_arguments_are_refused():
@@ -147,3 +155,34 @@ def test_background_compilation_takes_over_after_it_finishes(ctx):
         assert_bits_equal(b, a, "compiled against run-time chain")
     ref = (x + rv) / rv - 0.125
     assert_bits_equal(second[0], ref.max(1, keepdims=True), "row maximum")
+
+
+@pytest.mark.gpu
+@needs_nvrtc
+@pytest.mark.parametrize("shape", [(70000, 48), (4099, 50), (100001, 6)])
+def test_column_sums_of_a_chain_without_compiled_in_kernel(ctx, shape):
+    """colSums / colMeans of ((X - mu) / cv) * Y: general column pass, then the kernel compiled for the chain; the two
+    sum in different orders, so they agree with the oracle within the reduction tolerance, not bit for bit."""
+    import daphne_b200.kernels as k
+    from oracle import pyoracle as o
+    from tests.util import RTOL_REDUCE_F64, assert_close_rel, rng_matrix
+    B, A = k.BinaryOpCode, k.AggOpCode
+    r, c = shape
+    x, y = rng_matrix(13, r, c) - 5.0, rng_matrix(14, r, c) + 1.0
+    mu, cv = rng_matrix(15, 1, c), rng_matrix(16, r, 1) + 2.0
+    ref = o.ewBinaryMat(B.MUL, o.ewBinaryMat(B.DIV, o.ewBinaryMat(B.SUB, x, mu), cv), y)
+    ready, failed = C.c_int(), C.c_int()
+    try:
+        for mode in (0, 2):
+            check(lib.db2_rtc_set_mode(mode))
+            X, Y, MU, CV = (k.DenseMatrix.from_numpy(ctx, a) for a in (x, y, mu, cv))
+            z = k.ewBinaryMat(B.MUL, k.ewBinaryMat(B.DIV, k.ewBinaryMat(B.SUB, X, MU), CV), Y)
+            assert_close_rel(k.aggCol(A.SUM, z).to_numpy(), o.aggCol(A.SUM, ref), RTOL_REDUCE_F64, f"colSums mode {mode}",
+                             scale=float(np.abs(ref).sum(0).max()))
+            z = k.ewBinaryMat(B.MUL, k.ewBinaryMat(B.DIV, k.ewBinaryMat(B.SUB, X, MU), CV), Y)
+            assert_close_rel(k.aggCol(A.MEAN, z).to_numpy(), o.aggCol(A.MEAN, ref), RTOL_REDUCE_F64,
+                             f"colMeans mode {mode}", scale=float(np.abs(ref).mean(0).max()))
+        check(lib.db2_rtc_counts(C.byref(ready), None, C.byref(failed)))
+        assert failed.value == 0 and ready.value > 0
+    finally:
+        check(lib.db2_rtc_set_mode(1))
