@@ -82,7 +82,11 @@ __global__ void __launch_bounds__(SEG_MAX_WARPS * 32)
 }
 
 // The same sums for d = 64 columns of 16-byte aligned rows (one row = 32 lanes x 16 bytes), written for latency:
-//  * eight rows of X per warp are always on their way while the previous eight are added (two register sets);
+//  * 32 rows of X per warp (16 KB) are on their way at any time: a row's registers are refilled with the row 32
+//    further on as soon as the row has been added, so the loads are spread evenly over the additions (with two
+//    register sets filled in turns -- 8 rows each: 108 us for 1 M rows, 16 rows each: 124 us -- no load is issued
+//    while a whole set is being added; this form: 101 us with 16 rows, 96 us with 32).  Eight warps per SM keep
+//    128 KB in flight; the block is alone on its SM, so the 158 registers cost nothing;
 //  * two rows are added at a time: when their clusters differ the two read-modify-write chains on shared memory are
 //    independent and overlap, when they agree the accumulator is read and written once for both.  The order of the
 //    additions into any accumulator is the row order, as in the general kernel;
@@ -92,7 +96,7 @@ __global__ void __launch_bounds__(SEG_MAX_WARPS * 32)
     onehot_segsum64_kernel(const int64_t *__restrict__ idx, int64_t idx_ld, const double *__restrict__ X, int64_t ldx,
                            int64_t n, int k, double *__restrict__ partials) {
     extern __shared__ __align__(16) double acc[];
-    constexpr int D = 64, U = 8;
+    constexpr int D = 64, U = 32;
     const int warps = blockDim.x / 32, warp = threadIdx.x / 32, lane = threadIdx.x % 32;
     const int slots = (k + 1) * D; // per warp; row k is the spare one
     for (int e = threadIdx.x; e < warps * slots; e += blockDim.x)
@@ -105,12 +109,10 @@ __global__ void __launch_bounds__(SEG_MAX_WARPS * 32)
     if (lo < hi) {
         const double2 *xl = reinterpret_cast<const double2 *>(X) + lane;
         const int64_t ld2 = ldx / 2;
-        double2 xa[U], xb[U];
-        auto load = [&](double2(&x)[U], int64_t r0) {
-#pragma unroll
-            for (int u = 0; u < U; u++)
-                x[u] = (r0 + u < hi) ? __ldcs(xl + (r0 + u) * ld2) : make_double2(0.0, 0.0);
-        };
+        // x[u]: the next row of this warp whose number is u modulo U; a row's register pair is refilled with the
+        // row U further on as soon as the row has been added
+        double2 x[U];
+        auto ldrow = [&](int64_t r) { return (r < hi) ? __ldcs(xl + r * ld2) : make_double2(0.0, 0.0); };
         auto lds = [](unsigned a) {
             double2 v;
             asm volatile("ld.shared.v2.f64 {%0, %1}, [%2];\n" : "=d"(v.x), "=d"(v.y) : "r"(a) : "memory");
@@ -119,40 +121,37 @@ __global__ void __launch_bounds__(SEG_MAX_WARPS * 32)
         auto sts = [](unsigned a, double2 v) {
             asm volatile("st.shared.v2.f64 [%0], {%1, %2};\n" ::"r"(a), "d"(v.x), "d"(v.y) : "memory");
         };
-        auto add = [&](const double2(&x)[U], int ci, int h) {
 #pragma unroll
-            for (int u = 0; u < U; u += 2) {
-                const int c0 = __shfl_sync(0xffffffffu, ci, h + u), c1 = __shfl_sync(0xffffffffu, ci, h + u + 1);
-                const unsigned a0 = mine_s + (unsigned)(c0 * D * 8), a1 = mine_s + (unsigned)(c1 * D * 8);
-                if (c0 != c1) {
-                    double2 t0 = lds(a0), t1 = lds(a1);
-                    t0.x = __dadd_rn(t0.x, x[u].x);
-                    t0.y = __dadd_rn(t0.y, x[u].y);
-                    t1.x = __dadd_rn(t1.x, x[u + 1].x);
-                    t1.y = __dadd_rn(t1.y, x[u + 1].y);
-                    sts(a0, t0);
-                    sts(a1, t1);
-                } else {
-                    double2 t0 = lds(a0);
-                    t0.x = __dadd_rn(__dadd_rn(t0.x, x[u].x), x[u + 1].x);
-                    t0.y = __dadd_rn(__dadd_rn(t0.y, x[u].y), x[u + 1].y);
-                    sts(a0, t0);
-                }
-            }
-        };
-        load(xa, lo);
+        for (int u = 0; u < U; u++)
+            x[u] = ldrow(lo + u);
         int64_t c_next = (lo + lane < hi) ? idx[(lo + lane) * idx_ld] : -1;
         for (int64_t b0 = lo; b0 < hi; b0 += 32) {
             const int ci = (c_next >= 0 && c_next < k) ? (int)c_next : k;
             c_next = (b0 + 32 + lane < hi) ? idx[(b0 + 32 + lane) * idx_ld] : -1;
-            load(xb, b0 + 8);
-            add(xa, ci, 0);
-            load(xa, b0 + 16);
-            add(xb, ci, 8);
-            load(xb, b0 + 24);
-            add(xa, ci, 16);
-            load(xa, b0 + 32);
-            add(xb, ci, 24);
+#pragma unroll
+            for (int h = 0; h < 32; h += U) {
+#pragma unroll
+                for (int u = 0; u < U; u += 2) {
+                    const int c0 = __shfl_sync(0xffffffffu, ci, h + u), c1 = __shfl_sync(0xffffffffu, ci, h + u + 1);
+                    const unsigned a0 = mine_s + (unsigned)(c0 * D * 8), a1 = mine_s + (unsigned)(c1 * D * 8);
+                    if (c0 != c1) {
+                        double2 t0 = lds(a0), t1 = lds(a1);
+                        t0.x = __dadd_rn(t0.x, x[u].x);
+                        t0.y = __dadd_rn(t0.y, x[u].y);
+                        t1.x = __dadd_rn(t1.x, x[u + 1].x);
+                        t1.y = __dadd_rn(t1.y, x[u + 1].y);
+                        sts(a0, t0);
+                        sts(a1, t1);
+                    } else {
+                        double2 t0 = lds(a0);
+                        t0.x = __dadd_rn(__dadd_rn(t0.x, x[u].x), x[u + 1].x);
+                        t0.y = __dadd_rn(__dadd_rn(t0.y, x[u].y), x[u + 1].y);
+                        sts(a0, t0);
+                    }
+                    x[u] = ldrow(b0 + h + u + U);
+                    x[u + 1] = ldrow(b0 + h + u + 1 + U);
+                }
+            }
         }
     }
     __syncthreads();

@@ -434,6 +434,23 @@ int db2_castObj(db2_context *ctx, db2_matrix **res, db2_matrix *arg, int dtype) 
     bind_device(ctx);
     const uint64_t before = g_launches.load();
     DB2_TRY(ensure_device(arg));
+    // The two 64-bit integer types hold the same bits (the conversion wraps): the result is a second handle on the
+    // same device buffer.  A later write through either handle gets a buffer of its own (prepare_result), so the two
+    // matrices stay independent values.  K-means casts a million row positions per iteration this way.
+    if (*res == nullptr && arg->dev && arg->dev_valid && !arg->is_view &&
+        ((arg->dtype == DB2_U64 && dtype == DB2_I64) || (arg->dtype == DB2_I64 && dtype == DB2_U64))) {
+        db2_matrix *r = new db2_matrix();
+        r->ctx = ctx;
+        r->dtype = dtype;
+        r->rows = arg->rows;
+        r->cols = arg->cols;
+        r->dev = arg->dev;
+        r->dev_off = arg->dev_off;
+        r->dev_ld = arg->dev_ld;
+        r->dev_valid = true;
+        *res = r;
+        return DB2_OK;
+    }
     DB2_TRY(prepare_result(ctx, res, dtype, arg->rows, arg->cols));
     db2_matrix *r = *res;
     const int64_t n = arg->rows * arg->cols;

@@ -203,3 +203,23 @@ def test_cluster_sums_of_another_matrix_than_the_distances_came_from(ctx):
     ref = np.zeros((kc, 64))
     np.add.at(ref, a, x + 1.0)
     assert_bits_equal(sums, ref, "sums of the other matrix")
+
+
+def test_cast_between_the_64_bit_integer_types_shares_the_buffer_but_not_later_writes(ctx):
+    """castObj ui64 <-> si64 hands out a second handle on the same device buffer (no kernel, no copy); overwriting one
+    of the two matrices afterwards must leave the other one as it was."""
+    k, A, B = _k()
+    from daphne_b200.lib import lib
+    a = np.array([[0], [5], [2 ** 63 + 7], [2 ** 64 - 1]], dtype=np.uint64)
+    U = k.DenseMatrix.from_numpy(ctx, a)
+    U.device_ptr()
+    before = lib.db2_launch_count()
+    S = k.castObj(U, np.int64)
+    assert lib.db2_launch_count() == before
+    assert S.dtype == np.int64 and np.array_equal(S.to_numpy(), a.astype(np.int64))
+    back = k.castObj(S, np.uint64)
+    assert np.array_equal(back.to_numpy(), a)
+    # a result written "into" U (pre-allocated result) must not show through S
+    T = k.ewBinaryObjSca(B.ADD, S, 1)
+    assert np.array_equal(S.to_numpy(), a.astype(np.int64))
+    assert np.array_equal(T.to_numpy(), a.astype(np.int64) + 1)
