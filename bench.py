@@ -669,6 +669,24 @@ def generic_chain_leg(ctx, comm, lib, host, world, args) -> dict:
     ms, (r, m) = _timed(lib, ctx, comm, run, 7)
     ready, failed = C.c_int(), C.c_int()
     check(lib.db2_rtc_counts(C.byref(ready), None, C.byref(failed)))
+    # the same chain on 33 columns: rows that do not start on 16-byte boundaries (chunks copied element by element);
+    # without the run-time compiler such layouts are served by the general interpreter
+    rows33 = rows // 2
+    X33 = K.DenseMatrix.from_numpy(ctx, np.tile(5.0 + 2.0 * rng.standard_normal((1 << 16, 33)), (rows33 >> 16, 1)))
+    X33.device_ptr()
+    mu33, w33 = (K.DenseMatrix.from_numpy(ctx, rng.standard_normal((1, 33)) + 3.0) for _ in range(2))
+
+    def run33():
+        Z = K.ewBinaryObjSca(B.ADD, K.ewBinaryMat(B.MUL, K.ewBinaryMat(B.SUB, X33, mu33), w33), 0.5)
+        r33, m33 = K.aggRow(A.SUM, Z), K.aggRow(A.MIN, Z)
+        r33.device_ptr()
+        return r33, m33
+    check(lib.db2_rtc_set_mode(0))
+    ms33_interp, _ = _timed(lib, ctx, comm, run33, 5)
+    check(lib.db2_rtc_set_mode(2))
+    ms33, (r33, m33) = _timed(lib, ctx, comm, run33, 7)
+    z33 = (X33.to_numpy()[:4096] - mu33.to_numpy()) * w33.to_numpy() + 0.5
+    nbytes33 = rows33 * (33 * 8 + 16)
     nbytes = rows * (cols * 8 + 16)
     peak, _ = measured_peaks()
     xs = X.to_numpy()[:4096]
@@ -678,6 +696,10 @@ def generic_chain_leg(ctx, comm, lib, host, world, args) -> dict:
             "kernel": "compiled at run time for this chain" if ready.value and not failed.value else "chain read at run time",
             "background_compile_s": compile_s,
             "ms_chain_read_at_run_time": ms_rt, "hbm_frac_chain_read_at_run_time": nbytes / (ms_rt * 1e-3) / 1e9 / peak,
+            "columns_33": {"rows": rows33, "ms": ms33, "hbm_frac_of_measured": nbytes33 / (ms33 * 1e-3) / 1e9 / peak,
+                           "ms_general_interpreter": ms33_interp,
+                           "hbm_frac_general_interpreter": nbytes33 / (ms33_interp * 1e-3) / 1e9 / peak,
+                           "row_mins_equal_numpy_4096_rows": bool(np.array_equal(m33.to_numpy()[:4096, 0], z33.min(1)))},
             "row_mins_equal_numpy_4096_rows": bool(np.array_equal(m.to_numpy()[:4096, 0], z.min(1))),
             "row_sums_max_rel_err_4096_rows": float(np.abs(r.to_numpy()[:4096, 0] / z.sum(1) - 1.0).max())}
 

@@ -103,7 +103,7 @@ __global__ void __launch_bounds__(RT)
                 const double d = src[c];
                 rvs[st.smem_off + c] = d;
                 if (helper)
-                    rvs[st.smem_off + cols + c] = div_helper(d);
+                    rvs[st.smem_off + ((cols + 1) & ~(int64_t)1) + c] = div_helper(d);
             }
         }
     }
@@ -176,7 +176,7 @@ __global__ void __launch_bounds__(RT)
                             if (st.op == FO_DIV && !st.reversed) {
 #pragma unroll
                                 for (int i = 0; i < GV; i++)
-                                    y[i] = (i < nv) ? sv[cols + i] : 0.0;
+                                    y[i] = (i < nv) ? sv[((cols + 1) & ~(int64_t)1) + i] : 0.0;
                             }
                         } else {
                             const double *gv = static_cast<const double *>(st.ptr) + c0;

@@ -25,7 +25,8 @@ int fused_row_pass_f64(const FusedProgram &prog, cudaStream_t st);
 // e.g. "SUB.R|DIV.R|SQ.S#MAX@2,SUM@3"; returns true when a specialised kernel was launched.
 bool fused_row_pass_ct(const FusedProgram &prog, const char *signature, cudaStream_t st, int *rc);
 // the specialisation of prog's chain compiled at run time (fused_rtc.cu): true if it was launched
-bool fused_row_pass_rtc(const FusedProgram &prog, cudaStream_t st, int *rc);
+// aligned: base (and stored result) rows start on 16-byte boundaries and the number of columns is even
+bool fused_row_pass_rtc(const FusedProgram &prog, bool aligned, cudaStream_t st, int *rc);
 bool fused_col_pass_rtc(const FusedProgram &prog, int mean, void *res, void *scratch, cudaStream_t st, int *rc);
 // geometry and last step of the compile-time column pass (fused_ct.cu), shared with the kernels compiled at run time
 void fused_col_geometry(const FusedProgram &prog, unsigned (&grid)[2], unsigned (&block)[2]);

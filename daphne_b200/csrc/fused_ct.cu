@@ -146,27 +146,34 @@ static const ColEntry COL_TABLE[] = {
 
 } // namespace ct
 
-static bool ct_layout_ok(const FusedProgram &P) {
-    if (!aligned16(P.base) || (P.base_ld & 1) || (P.cols & 1) || P.rows <= 0 || P.cols <= 0)
+static bool ct_staged(const FusedProgram &P) {
+    if (P.rows <= 0 || P.cols <= 0)
         return false;
     for (int i = 0; i < P.nsteps; i++)
         if (P.steps[i].kind == FK_ROWVEC && P.steps[i].smem_off < 0)
             return false; // row vectors too large to stage
     return true;
 }
+// rows start on 16-byte boundaries and hold an even number of values: the 16-byte copies of the compiled-in kernels
+static bool ct_layout_ok(const FusedProgram &P) {
+    return ct_staged(P) && aligned16(P.base) && !(P.base_ld & 1) && !(P.cols & 1);
+}
 
 bool fused_row_pass_ct(const FusedProgram &P, const char *signature, cudaStream_t st, int *rc) {
-    if (!ct_layout_ok(P))
+    if (!ct_staged(P))
         return false;
-    if (P.ew_out && (!aligned16(P.ew_out) || (P.ew_out_ld & 1)))
-        return false;
+    if (!ct_layout_ok(P) || (P.ew_out && (!aligned16(P.ew_out) || (P.ew_out_ld & 1)))) {
+        // any other layout (odd number of columns, odd leading dimension, a view that starts at an odd column): the
+        // kernel compiled at run time in its copy-by-element form; until that exists, the general interpreter
+        return (reinterpret_cast<uintptr_t>(P.base) & 7) == 0 && fused_row_pass_rtc(P, false, st, rc);
+    }
     for (const auto &e : ct::ROW_TABLE)
         if (strcmp(e.sig, signature) == 0) {
             *rc = e.launch(P, st);
             return true;
         }
     // not in the table: the kernel compiled for this chain at run time, once that exists (fused_rtc.cu) ...
-    if (fused_row_pass_rtc(P, st, rc))
+    if (fused_row_pass_rtc(P, true, st, rc))
         return true;
     // ... and until then the same kernel with the chain read at run time
     *rc = P.ew_out ? ct::launch_row<ct::AnyChain, ct::AnyTaps, true>(P, st)

@@ -201,10 +201,15 @@ __device__ __forceinline__ void run_group(double (&v)[G], const FusedProgram &P,
         using St = typename At<I, ChainT>::type;
         const FusedStep &fs = P.steps[I];
         double o[G], y[G];
-        if constexpr (St::kind == FK_ROWVEC) {
-            // staged operands: offsets and c are even (see ct_layout_ok), so pairs are 16-byte aligned
+        if constexpr (St::kind == FK_ROWVEC && G == 1) { // the last column of a row with an odd number of columns
+            o[0] = rvs[fs.smem_off + c];
+            y[0] = 0.0;
+            if constexpr (St::op == FO_DIV && !St::rev)
+                y[0] = rvs[fs.smem_off + ((P.cols + 1) & ~(int64_t)1) + c];
+        } else if constexpr (St::kind == FK_ROWVEC) {
+            // staged operands: offsets and c are even, so pairs are 16-byte aligned
             const double2 *ov = reinterpret_cast<const double2 *>(rvs + fs.smem_off + c);
-            const double2 *yv = reinterpret_cast<const double2 *>(rvs + fs.smem_off + P.cols + c);
+            const double2 *yv = reinterpret_cast<const double2 *>(rvs + fs.smem_off + ((P.cols + 1) & ~(int64_t)1) + c);
 #pragma unroll
             for (int i = 0; i < G / 2; i++) {
                 const double2 t = ov[i];
@@ -355,13 +360,32 @@ __device__ __forceinline__ void issue_chunk(unsigned coop0, const double *src, i
             cp_async16(coop_addr(coop0, i), s + (int64_t)(2 * i) * ld);
 }
 
+// The same chunk for a source whose rows do not start on 16-byte boundaries (odd leading dimension, odd number of
+// columns, or a base that is only 8-byte aligned): one 8-byte copy per element, lane = column, so that a row of the
+// chunk is still one 256-byte request; element (r, c) lands where the 16-byte form puts it.
+__device__ __forceinline__ void cp_async8(unsigned smem_dst, const void *gsrc) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 8;\n" ::"r"(smem_dst), "l"(gsrc) : "memory");
+}
+__device__ __forceinline__ unsigned elem_addr(unsigned buf, int r, int lane) {
+    return buf + (unsigned)(256 * r + ((((lane >> 1) ^ r) & 15) << 4) + ((lane & 1) << 3));
+}
+template <bool FULL>
+__device__ __forceinline__ void issue_chunk_by_element(unsigned buf, const double *src, int64_t ld, int rows_here, int cw,
+                                                       int lane) {
+    const double *s = src + lane;
+#pragma unroll
+    for (int r = 0; r < WR; r++)
+        if (FULL || (r < rows_here && lane < cw))
+            cp_async8(elem_addr(buf, r, lane), s + (int64_t)r * ld);
+}
+
 // one lane walks its row of a chunk (FULL: all CK columns are there)
 template <typename ChainT, typename TapsT, bool EW, bool FULL>
 __device__ __forceinline__ void walk_row(unsigned walk0, const FusedProgram &P, const ChainState<ChainT> &cs,
                                          TapState<TapsT> &ts, const double *rvs, int64_t row, int64_t cc, int cw) {
 #pragma unroll
     for (int g = 0; g < CK / GR; g++) {
-        if (FULL || g * GR < cw) { // cw is even; a group that straddles the end loads padding it never uses
+        if (FULL || g * GR < cw) { // a group that straddles the end loads padding it never uses
             double v[GR];
 #pragma unroll
             for (int j = 0; j < GR / 2; j++) {
@@ -377,7 +401,7 @@ __device__ __forceinline__ void walk_row(unsigned walk0, const FusedProgram &P, 
             } else { // ragged end of the last chunk: pairs
 #pragma unroll
                 for (int j = 0; j < GR / 2; j++) {
-                    if (g * GR + 2 * j < cw) {
+                    if (g * GR + 2 * j + 1 < cw) {
                         double w[2] = {v[2 * j], v[2 * j + 1]};
                         if (g == 0 && j == 0)
                             run_group<ChainT, TapsT, true, 2>(w, P, cs, ts, rvs, row, cc);
@@ -385,6 +409,13 @@ __device__ __forceinline__ void walk_row(unsigned walk0, const FusedProgram &P, 
                             run_group<ChainT, TapsT, false, 2>(w, P, cs, ts, rvs, row, cc + g * GR + 2 * j);
                         v[2 * j] = w[0];
                         v[2 * j + 1] = w[1];
+                    } else if (g * GR + 2 * j < cw) { // the last column of a row with an odd number of columns
+                        double w[1] = {v[2 * j]};
+                        if (g == 0 && j == 0)
+                            run_group<ChainT, TapsT, true, 1>(w, P, cs, ts, rvs, row, cc);
+                        else
+                            run_group<ChainT, TapsT, false, 1>(w, P, cs, ts, rvs, row, cc + g * GR + 2 * j);
+                        v[2 * j] = w[0];
                     }
                 }
             }
@@ -627,7 +658,7 @@ __device__ __forceinline__ void walk_row_rt(unsigned walk0, const FusedProgram &
             so.scal = __ldg(static_cast<const double *>(fs.ptr) + row * fs.ld);
             so.yscal = (fs.op == FO_DIV && !fs.reversed) ? div_helper(so.scal) : 0.0;
         }
-        so.cols = P.cols;
+        so.cols = (P.cols + 1) & ~(int64_t)1; // where the helpers of a staged divisor start
         so.cw = cw;
         rt_dispatch(fs.op, fs.reversed != 0, kind, walk0, so);
         rt_feed(walk0, ts, P, masks[s + 1], (int)cc, cw);
@@ -639,7 +670,8 @@ template <typename ChainT> struct RowCtasPerSm {
     static constexpr int value = 3;
 };
 
-template <typename ChainT, typename TapsT, bool EW>
+// AL: rows of the base (and of the stored result) start on 16-byte boundaries and have an even number of columns
+template <typename ChainT, typename TapsT, bool EW, bool AL = true>
 __global__ void __launch_bounds__(RT, RowCtasPerSm<ChainT>::value) fused_row_ct_kernel(const __grid_constant__ FusedProgram P) {
     extern __shared__ __align__(16) double smem_raw[];
     // the chunk buffers start on a 256-byte boundary (the launch reserves the slack)
@@ -659,7 +691,7 @@ __global__ void __launch_bounds__(RT, RowCtasPerSm<ChainT>::value) fused_row_ct_
                 const double d = src[c];
                 rvs[st.smem_off + c] = d;
                 if (helper)
-                    rvs[st.smem_off + cols + c] = div_helper(d);
+                    rvs[st.smem_off + ((cols + 1) & ~(int64_t)1) + c] = div_helper(d);
             }
         }
     }
@@ -692,10 +724,17 @@ __global__ void __launch_bounds__(RT, RowCtasPerSm<ChainT>::value) fused_row_ct_
     if (t < ntiles) {
         const int64_t row0 = t * WR;
         const int rh = (rows - row0 < WR) ? (int)(rows - row0) : WR, cw = (cols < CK) ? (int)cols : CK;
-        if (rh == WR && cw == CK)
-            issue_chunk<true>(bufs_s + coop_off, base + row0 * P.base_ld, P.base_ld, rh, cw, lane);
-        else
-            issue_chunk<false>(bufs_s + coop_off, base + row0 * P.base_ld, P.base_ld, rh, cw, lane);
+        if constexpr (AL) {
+            if (rh == WR && cw == CK)
+                issue_chunk<true>(bufs_s + coop_off, base + row0 * P.base_ld, P.base_ld, rh, cw, lane);
+            else
+                issue_chunk<false>(bufs_s + coop_off, base + row0 * P.base_ld, P.base_ld, rh, cw, lane);
+        } else {
+            if (rh == WR && cw == CK)
+                issue_chunk_by_element<true>(bufs_s, base + row0 * P.base_ld, P.base_ld, rh, cw, lane);
+            else
+                issue_chunk_by_element<false>(bufs_s, base + row0 * P.base_ld, P.base_ld, rh, cw, lane);
+        }
     }
     cp_async_commit();
     TapState<TapsT> ts;
@@ -711,10 +750,17 @@ __global__ void __launch_bounds__(RT, RowCtasPerSm<ChainT>::value) fused_row_ct_
             const int64_t row0n = tn * WR, ccn = (int64_t)chn * CK;
             const int rh = (rows - row0n < WR) ? (int)(rows - row0n) : WR, cw = (cols - ccn < CK) ? (int)(cols - ccn) : CK;
             const double *src = base + row0n * P.base_ld + ccn;
-            if (rh == WR && cw == CK)
-                issue_chunk<true>(bufs_s + (b ^ BUF_BYTES) + coop_off, src, P.base_ld, rh, cw, lane);
-            else
-                issue_chunk<false>(bufs_s + (b ^ BUF_BYTES) + coop_off, src, P.base_ld, rh, cw, lane);
+            if constexpr (AL) {
+                if (rh == WR && cw == CK)
+                    issue_chunk<true>(bufs_s + (b ^ BUF_BYTES) + coop_off, src, P.base_ld, rh, cw, lane);
+                else
+                    issue_chunk<false>(bufs_s + (b ^ BUF_BYTES) + coop_off, src, P.base_ld, rh, cw, lane);
+            } else {
+                if (rh == WR && cw == CK)
+                    issue_chunk_by_element<true>(bufs_s + (b ^ BUF_BYTES), src, P.base_ld, rh, cw, lane);
+                else
+                    issue_chunk_by_element<false>(bufs_s + (b ^ BUF_BYTES), src, P.base_ld, rh, cw, lane);
+            }
         }
         cp_async_commit();
         cp_async_wait_but_one();
@@ -742,7 +788,19 @@ __global__ void __launch_bounds__(RT, RowCtasPerSm<ChainT>::value) fused_row_ct_
             else if (live)
                 walk_row<ChainT, TapsT, EW, false>(tile_s + walk_off, P, cs, ts, rvs, row, cc, cw);
         }
-        if constexpr (EW) {
+        if constexpr (EW && !AL) { // one 8-byte store per element, lane = column
+            __syncwarp();
+            double *out = static_cast<double *>(P.ew_out) + row0 * P.ew_out_ld + cc + lane;
+            if (lane < cw) {
+#pragma unroll 4
+                for (int r = 0; r < WR; r++)
+                    if (r < rows_here) {
+                        double q;
+                        asm volatile("ld.shared.f64 %0, [%1];\n" : "=d"(q) : "r"(elem_addr(tile_s, r, lane)) : "memory");
+                        __stcs(out + (int64_t)r * P.ew_out_ld, q);
+                    }
+            }
+        } else if constexpr (EW) {
             __syncwarp();
             const int r0 = lane >> 4, p = lane & 15;
             double *out = static_cast<double *>(P.ew_out) + (row0 + r0) * P.ew_out_ld + cc + 2 * p;

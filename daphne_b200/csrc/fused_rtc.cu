@@ -116,13 +116,13 @@ std::string chain_of(const FusedProgram &P) {
              std::to_string(P.steps[i].kind) + "," + (P.steps[i].reversed ? "true" : "false") + ">";
     return e + ">";
 }
-// fused_row_ct_kernel<Chain<...>, Taps<T<after, kind>...>, EW>
-std::string expression_of(const FusedProgram &P) {
+// fused_row_ct_kernel<Chain<...>, Taps<T<after, kind>...>, EW, AL>
+std::string expression_of(const FusedProgram &P, bool aligned) {
     std::string e = "db2::ct::fused_row_ct_kernel<" + chain_of(P) + ",db2::ct::Taps<";
     for (int i = 0; i < P.ntaps; i++)
         e += std::string(i ? "," : "") + "db2::ct::T<" + std::to_string(P.taps[i].after_step) + "," +
              std::to_string(P.taps[i].kind) + ">";
-    e += std::string(">,") + (P.ew_out ? "true" : "false") + ">";
+    e += std::string(">,") + (P.ew_out ? "true" : "false") + "," + (aligned ? "true" : "false") + ">";
     return e;
 }
 // fused_col_sum_ct_kernel<Chain<...>>
@@ -224,8 +224,8 @@ std::shared_ptr<Entry> kernel_of(const std::string &expr) {
 
 // Launches the run-time compiled specialisation of P's chain if it is ready (true; *rc is the launch's result).
 // Otherwise starts its compilation, if that has not happened yet, and returns false: the caller runs the interpreter.
-bool fused_row_pass_rtc(const FusedProgram &P, cudaStream_t st, int *rc) {
-    std::shared_ptr<Entry> e = kernel_of(expression_of(P));
+bool fused_row_pass_rtc(const FusedProgram &P, bool aligned, cudaStream_t st, int *rc) {
+    std::shared_ptr<Entry> e = kernel_of(expression_of(P, aligned));
     if (!e)
         return false;
     using namespace ct;
@@ -336,10 +336,10 @@ int db2_rtc_compile(const int *ops, const int *kinds, const int *reversed, int n
         P.taps[i].after_step = tap_after[i];
         P.taps[i].kind = tap_kinds[i];
     }
-    P.ew_out = ew ? &P : nullptr; // only its presence matters here
+    P.ew_out = (ew & 1) ? &P : nullptr; // only its presence matters here
     std::vector<char> cubin;
     std::string lowered, log;
-    if (!compile(column_pass ? col_expression_of(P) : expression_of(P), &cubin, &lowered, &log))
+    if (!compile(column_pass ? col_expression_of(P) : expression_of(P, (ew & 2) == 0), &cubin, &lowered, &log))
         return set_error(DB2_EUNSUPPORTED, "run-time compilation failed: %.900s", log.c_str());
     if (binary_bytes)
         *binary_bytes = cubin.size();

@@ -240,7 +240,9 @@ static void build_program(const Expr &e, size_t nsteps, FusedProgram *P) {
             d.ld = s.operand.ld;
         }
         if (s.kind == FK_ROWVEC) {
-            const int need = (int)e.cols * ((s.op == FO_DIV && !s.reversed) ? 2 : 1);
+            // the operand, then (for a divisor) its reciprocal helpers, each padded to an even number of values so
+            // that pairs stay 16-byte aligned for an odd number of columns
+            const int need = (int)((e.cols + 1) & ~(int64_t)1) * ((s.op == FO_DIV && !s.reversed) ? 2 : 1);
             if (smem + need <= smem_budget) {
                 d.smem_off = smem;
                 smem += need;

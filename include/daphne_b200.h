@@ -479,7 +479,7 @@ int db2_rtc_counts(int *ready, int *pending, int *failed);
  * BinaryOpCode ADD SUB MUL DIV, then SQUARE EQ NEQ LT LE GT GE MIN MAX AND OR NEG ABS SIGN FLOOR CEIL ROUND ISNAN =
  * 0..21) with an operand of kinds[i] (0 matrix, 1 row vector, 2 column vector, 3 scalar, 4 none), operands swapped if
  * reversed[i]; row aggregation j of tap_kinds[j] (0 SUM 1 PROD 2 MIN 3 MAX 4 MEAN) sees the values after tap_after[j]
- * steps; ew != 0: the final values are stored; ntaps < 0: the kernel of the column sums of the chain instead.  Needs no
+ * steps; ew bit 0: the final values are stored, bit 1: the form for rows that do not start on 16-byte boundaries; ntaps < 0: the kernel of the column sums of the chain instead.  Needs no
  * device.  *binary_bytes: size of the device binary. */
 int db2_rtc_compile(const int *ops, const int *kinds, const int *reversed, int nsteps, const int *tap_after,
                     const int *tap_kinds, int ntaps, int ew, size_t *binary_bytes);

@@ -62,6 +62,15 @@ def test_every_operation_and_operand_kind_compiles():
 
 
 @needs_nvrtc
+def test_the_form_for_rows_off_16_byte_boundaries_compiles():
+    steps = [("SUB", "R", False), ("DIV", "R", False), ("MUL", "C", False), ("MAX", "M", True), ("ABS", "U", False)]
+    taps = [("SUM", 5), ("MIN", 2), ("MAX", 0)]
+    assert _compile(steps, taps, 2) > 10_000       # row aggregations only
+    assert _compile(steps, taps, 3) > 10_000       # and the values stored
+    assert _compile([], [("MEAN", 0)], 2) > 10_000
+
+
+@needs_nvrtc
 def test_column_sums_of_a_chain_compile():
     assert _compile([("SUB", "R", False), ("MUL", "C", False), ("DIV", "M", False), ("ABS", "U", False)], [], False,
                     column_pass=True) > 5_000
@@ -126,13 +135,13 @@ def test_compiled_chain_gives_the_bits_of_the_run_time_kernel_and_of_the_oracle(
         if c % 2 == 0:  # odd widths go through the general interpreter and are never compiled
             assert ready.value > ready0.value or ready0.value > 0
     finally:
-        check(lib.db2_rtc_set_mode(1))
+        check(lib.db2_rtc_set_mode(2))
 
 
 @pytest.mark.gpu
 @needs_nvrtc
 def test_background_compilation_takes_over_after_it_finishes(ctx):
-    """Default mode: the first call is served by the run-time kernel while the compiler works; after db2_rtc_wait the
+    """Background mode: the first call is served by the run-time kernel while the compiler works; after db2_rtc_wait the
     same chain runs compiled.  Both must give the same bits."""
     import daphne_b200.kernels as k
     from tests.util import assert_bits_equal
@@ -145,12 +154,15 @@ def test_background_compilation_takes_over_after_it_finishes(ctx):
         z = k.ewBinaryObjSca(B.SUB, k.ewBinaryMat(B.DIV, k.ewBinaryMat(B.ADD, X, RV), RV), 0.125)
         return k.aggRow(A.MAX, z).to_numpy(), k.aggRow(A.SUM, z).to_numpy()
     check(lib.db2_rtc_set_mode(1))
-    first = run()
-    check(lib.db2_rtc_wait())
-    pending = C.c_int()
-    check(lib.db2_rtc_counts(None, C.byref(pending), None))
-    assert pending.value == 0
-    second = run()
+    try:
+        first = run()
+        check(lib.db2_rtc_wait())
+        pending = C.c_int()
+        check(lib.db2_rtc_counts(None, C.byref(pending), None))
+        assert pending.value == 0
+        second = run()
+    finally:
+        check(lib.db2_rtc_set_mode(2))
     for a, b in zip(first, second):
         assert_bits_equal(b, a, "compiled against run-time chain")
     ref = (x + rv) / rv - 0.125
@@ -185,4 +197,51 @@ def test_column_sums_of_a_chain_without_compiled_in_kernel(ctx, shape):
         check(lib.db2_rtc_counts(C.byref(ready), None, C.byref(failed)))
         assert failed.value == 0 and ready.value > 0
     finally:
-        check(lib.db2_rtc_set_mode(1))
+        check(lib.db2_rtc_set_mode(2))
+
+
+@pytest.mark.gpu
+@needs_nvrtc
+@pytest.mark.parametrize("shape,view", [((70001, 33), None), ((4099, 7), None), ((3001, 129), None), ((2049, 1), None),
+                                        ((50000, 64), (3, 40)), ((50000, 65), (1, 65)), ((300, 401), (200, 333))])
+def test_rows_off_16_byte_boundaries_take_the_compiled_kernel_too(ctx, shape, view):
+    """Odd numbers of columns, odd leading dimensions and column views that start at an odd column: the kernel copies
+    its chunks element by element.  Values, row extrema with positions and row sums against the oracle, for the
+    kernel compiled at run time and for the general interpreter that serves such layouts without it."""
+    import daphne_b200.kernels as k
+    from oracle import pyoracle as o
+    from tests.util import RTOL_REDUCE_F64, assert_bits_equal, assert_close_rel, rng_matrix
+    B, U, A = k.BinaryOpCode, k.UnaryOpCode, k.AggOpCode
+    r, c = shape
+    full = rng_matrix(23, r, c) - 5.0
+    lo, hi = view if view else (0, c)
+    full[min(3, r - 1), lo] = 0.0
+    x = np.ascontiguousarray(full[:, lo:hi])
+    w = hi - lo
+    rv, cv, y = rng_matrix(24, 1, w) - 4.0, rng_matrix(25, r, 1) + 2.0, rng_matrix(26, r, w)
+
+    def run(kk, X, RV, CV, Y):
+        t = kk.ewBinaryMat(B.DIV, kk.ewBinaryMat(B.SUB, X, RV), RV)   # staged operand and its reciprocals
+        t = kk.ewBinaryMat(B.MUL, t, CV)
+        u = kk.ewUnaryMat(U.ABS, kk.ewBinaryMat(B.MIN, t, Y))
+        return t, u
+
+    cpu = run(type("O", (), {"ewBinaryMat": staticmethod(o.ewBinaryMat), "ewUnaryMat": staticmethod(o.ewUnaryMat)}),
+              x, rv, cv, y)
+    try:
+        for mode, name in ((0, "interpreter"), (2, "compiled")):
+            check(lib.db2_rtc_set_mode(mode))
+            F = k.DenseMatrix.from_numpy(ctx, full)
+            X = k.sliceCol(F, lo, hi) if view else F
+            dev = run(k, X, *(k.DenseMatrix.from_numpy(ctx, a) for a in (rv, cv, y)))
+            for i, (g, e) in enumerate(zip(dev, cpu)):
+                assert_bits_equal(k.aggRow(A.MAX, g).to_numpy(), o.aggRow(A.MAX, e), f"{name}: rowMax {i}")
+                assert_bits_equal(k.aggRow(A.IDXMIN, g).to_numpy(), o.aggRow(A.IDXMIN, e), f"{name}: idxMin {i}")
+                assert_close_rel(k.aggRow(A.SUM, g).to_numpy(), o.aggRow(A.SUM, e), RTOL_REDUCE_F64, f"{name}: rowSum {i}",
+                                 scale=float(np.abs(e).sum(1).max()))
+                assert_bits_equal(g.to_numpy(), e, f"{name}: values {i}")
+        failed = C.c_int()
+        check(lib.db2_rtc_counts(None, None, C.byref(failed)))
+        assert failed.value == 0
+    finally:
+        check(lib.db2_rtc_set_mode(2))
