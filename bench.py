@@ -202,28 +202,31 @@ def run_ours(args) -> dict:
 
     # ---- end to end through host buffers (`e2e`) ----
     # results land in pinned host buffers, like the input leaves from one
-    (out_r, p_r), (out_m, p_m), (out_i8, p_i) = (pinned_array(lib, rows, 1) for _ in range(3))
-    out_i = out_i8.view(np.uint64)
+    # (two sets: a step's three row results travel to the host on the context's second stream while the next step's
+    # input travels to the device -- the link carries both directions at once)
+    pinned = [[pinned_array(lib, rows, 1) for _ in range(3)] for _ in range(2)]
+    outs = [[a for a, _ in trio] for trio in pinned]
     Xd.free()
     e2e_steps = max(1, min(args.steps, 3))
 
-    def e2e_step():
+    def e2e_step(i):
         Xh = K.DenseMatrix.from_numpy(ctx, host)  # host placement only; the first kernel triggers the H2D copy
         r = pipelines.standardise_aggregate_native(ctx, Xh, n_total)
-        check(lib.db2_matrix_to_host(r.r.handle, C.c_void_p(out_r.ctypes.data), 1))
-        check(lib.db2_matrix_to_host(r.row_max.handle, C.c_void_p(out_m.ctypes.data), 1))
-        check(lib.db2_matrix_to_host(r.row_idx_max.handle, C.c_void_p(out_i.ctypes.data), 1))
+        for m, dst in zip((r.r, r.row_max, r.row_idx_max), outs[i % 2]):
+            check(lib.db2_matrix_to_host_async(m.handle, C.c_void_p(dst.ctypes.data), 1))
         mu, sd = r.mu.to_numpy(), r.sd.to_numpy()
         Xh.free()
         return r.s, mu, sd
 
-    e2e_step()
+    e2e_step(0)
+    check(lib.db2_context_side_sync(ctx.handle))
     sync_all()
     t0 = time.perf_counter()
     e2, e3 = ev(), ev()
     check(lib.db2_event_record(e2, stream))
-    for _ in range(e2e_steps):
-        e2e_step()
+    for i in range(e2e_steps):
+        e2e_step(i + 1)
+    check(lib.db2_context_side_sync(ctx.handle))  # the last step's results have arrived
     check(lib.db2_event_record(e3, stream))
     sync_all()
     wall_ms = (time.perf_counter() - t0) * 1e3 / e2e_steps
@@ -273,7 +276,7 @@ def run_ours(args) -> dict:
     if rank == 0:
         line["cpu_baseline"] = cpu_baseline(min(rows, args.cpu_rows) if args.cpu_rows > 0 else rows, cols, steps=3,
                                             budget_s=30.0)
-    for p_ in (host_ptr, p_r, p_m, p_i):
+    for p_ in [host_ptr] + [p for trio in pinned for _, p in trio]:
         lib.db2_free_host(p_)
     return line if rank == 0 else {}
 

@@ -24,6 +24,9 @@ void ctx_release(db2_context *ctx) {
     bind_device(ctx);
     db2_comm_destroy(ctx);
     cudaStreamSynchronize(ctx->stream);
+    if (ctx->side_stream)
+        cudaStreamSynchronize(ctx->side_stream);
+    ctx->side_keep.clear();
     if (ctx->scratch)
         ctx_free(ctx, ctx->scratch, ctx->scratch_bytes);
     release_cached(ctx);
@@ -509,6 +512,56 @@ int db2_matrix_to_host(db2_matrix *m, void *dst, int64_t dst_ld) {
     }
     return DB2_OK;
     DB2_API_END
+}
+
+// The same copy on the context's side stream, ordered after everything queued on the compute stream so far; returns
+// without waiting.  A step's results can so travel to the host while the next step's input travels to the device
+// (PCIe carries both directions at once).  dst must stay valid, and should be pinned, until db2_context_side_sync.
+int db2_matrix_to_host_async(db2_matrix *m, void *dst, int64_t dst_ld) {
+    DB2_API_BEGIN
+    DB2_CHECK(m && (dst || m->rows * m->cols == 0), DB2_EINVAL, "null argument");
+    DB2_CHECK(dst_ld >= m->cols, DB2_EINVAL, "destination leading dimension too small");
+    if (m->rows * m->cols == 0)
+        return DB2_OK;
+    if (m->deferred())
+        DB2_TRY(lazy_force(m));
+    if (!m->dev_valid)
+        return db2_matrix_to_host(m, dst, dst_ld);
+    db2_context *ctx = m->ctx;
+    bind_device(ctx);
+    const size_t es = m->esize();
+    wait_ready(ctx, m->dev.get());
+    if (!ctx->side_stream)
+        DB2_CUDA(cudaStreamCreateWithFlags(&ctx->side_stream, cudaStreamNonBlocking));
+    cudaEvent_t queued;
+    DB2_CUDA(cudaEventCreateWithFlags(&queued, cudaEventDisableTiming));
+    DB2_CUDA(cudaEventRecord(queued, ctx->stream));
+    DB2_CUDA(cudaStreamWaitEvent(ctx->side_stream, queued, 0));
+    DB2_CUDA(cudaEventDestroy(queued));
+    if ((dst_ld == m->cols && m->dev_ld == m->cols) || m->rows == 1)
+        DB2_CUDA(cudaMemcpyAsync(dst, m->dev_ptr(), (size_t)m->rows * m->cols * es, cudaMemcpyDeviceToHost,
+                                 ctx->side_stream));
+    else
+        DB2_CUDA(cudaMemcpy2DAsync(dst, (size_t)dst_ld * es, m->dev_ptr(), (size_t)m->dev_ld * es, (size_t)m->cols * es,
+                                   (size_t)m->rows, cudaMemcpyDeviceToHost, ctx->side_stream));
+    std::lock_guard<std::mutex> lock(ctx->mu);
+    ctx->side_keep.push_back(m->dev);
+    ctx->stats.d2h_bytes += (uint64_t)m->rows * m->cols * es;
+    return DB2_OK;
+    DB2_API_END
+}
+// waits for the copies (and collectives) queued on the side stream
+int db2_context_side_sync(db2_context *ctx) {
+    DB2_CHECK(ctx, DB2_EINVAL, "null context");
+    bind_device(ctx);
+    if (ctx->side_stream)
+        DB2_CUDA(cudaStreamSynchronize(ctx->side_stream));
+    std::vector<std::shared_ptr<DevBuf>> done;
+    {
+        std::lock_guard<std::mutex> lock(ctx->mu);
+        done.swap(ctx->side_keep);
+    }
+    return DB2_OK;
 }
 
 // ---------------------------------------------------------------------------

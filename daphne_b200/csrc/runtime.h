@@ -16,6 +16,7 @@ struct Expr;
 struct OneHot;
 struct ColStats;
 struct Operand;
+struct DevBuf;
 } // namespace db2
 
 struct db2_matrix;
@@ -28,7 +29,10 @@ struct db2_context {
     std::vector<db2_matrix *> lazies; // live matrices that stand for an unevaluated elementwise chain
     bool eager = false; // DB2_EAGER=1: run every operator call immediately (no fusion)
     cudaStream_t stream = nullptr;
-    cudaStream_t side_stream = nullptr; // collectives that run beside the compute stream (db2_allreduce_async)
+    cudaStream_t side_stream = nullptr; // collectives and result copies that run beside the compute stream
+    // device buffers that a copy on the side stream still reads (db2_matrix_to_host_async): kept from the allocator,
+    // which hands freed blocks straight back to the compute stream, until db2_context_side_sync
+    std::vector<std::shared_ptr<db2::DevBuf>> side_keep;
     // caching device allocator: freed blocks are kept by size and handed out again without calling the driver; all
     // work of a context is ordered on its one stream, so a freed block may be reused immediately
     std::multimap<size_t, void *> free_blocks;

@@ -129,6 +129,8 @@ _SIGS = {
     "db2_dist_to_host": (i32, [vp, vp, i64]),
     "db2_dist_gather": (i32, [vp, i32, _P(vp)]),
     "db2_group_run": (i32, [vp, vp, vp]),
+    "db2_matrix_to_host_async": (i32, [vp, vp, i64]),
+    "db2_context_side_sync": (i32, [vp]),
     "db2_rtc_set_mode": (i32, [i32]),
     "db2_rtc_wait": (i32, []),
     "db2_rtc_counts": (i32, [_P(i32), _P(i32), _P(i32)]),

@@ -335,6 +335,12 @@ int db2_matrix_info(const db2_matrix *m, int *dtype, int64_t *rows, int64_t *col
 int db2_matrix_device_ptr(db2_matrix *m, void **dptr, int64_t *ld);
 /* copies the latest values into dst (rows x cols, leading dimension dst_ld); synchronises the stream */
 int db2_matrix_to_host(db2_matrix *m, void *dst, int64_t dst_ld);
+/* The same copy on the context's second stream, ordered after the work queued so far; returns without waiting, so that
+ * the results of one pipeline run travel to the host while the input of the next travels to the device.  dst (pinned
+ * for a true overlap) must stay valid until db2_context_side_sync, which waits for these copies.  The reference copies
+ * results synchronously from pageable memory (src/runtime/local/datastructures/AllocationDescriptorCUDA.h:60-68). */
+int db2_matrix_to_host_async(db2_matrix *m, void *dst, int64_t dst_ld);
+int db2_context_side_sync(db2_context *ctx);
 
 /* Operator calls.  *res == NULL on entry means "the kernel allocates the result" (the reference's convention,
  * e.g. kernels/CUDA/AggRow.cu:121-122); otherwise the given matrix is overwritten. */

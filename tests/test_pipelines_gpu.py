@@ -292,3 +292,28 @@ def test_agg_all_in_two_halves(ctx):
     assert k.aggAllWait(ctx, 0) == float(one.to_numpy()[0, 0])
     with pytest.raises(Exception):
         k.aggAllStart(A.SUM, X, 2)
+
+
+def test_results_copied_to_the_host_beside_the_next_run(ctx):
+    """db2_matrix_to_host_async: the copy runs on the context's second stream; the matrix may be released and the next
+    run queued before db2_context_side_sync, and the bytes are those of the synchronous copy."""
+    import ctypes as C
+    from daphne_b200.lib import lib, check
+    k, p, cpu = _k()
+    rng = np.random.default_rng(91)
+    dsts, refs = [], []
+    for i in range(4):
+        x = rng.standard_normal((200000, 32)) * (i + 1)
+        X = k.DenseMatrix.from_numpy(ctx, x)
+        z = k.ewBinaryObjSca(k.BinaryOpCode.MUL, X, 1.5)       # a deferred chain: forced by the copy
+        r = k.aggRow(k.AggOpCode.SUM, z)
+        dz, dr = np.empty((200000, 40)), np.empty((200000, 1))   # a destination with a larger leading dimension
+        check(lib.db2_matrix_to_host_async(z.handle, C.c_void_p(dz.ctypes.data), 40))
+        check(lib.db2_matrix_to_host_async(r.handle, C.c_void_p(dr.ctypes.data), 1))
+        dsts.append((dz, dr))
+        refs.append((z.to_numpy(), r.to_numpy()))
+        del z, r, X                                               # released while the copies may still be running
+    check(lib.db2_context_side_sync(ctx.handle))
+    for (dz, dr), (z, r) in zip(dsts, refs):
+        assert_bits_equal(dz[:, :32], z, "values copied on the second stream")
+        assert_bits_equal(dr, r, "row sums copied on the second stream")
