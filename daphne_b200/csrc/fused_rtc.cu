@@ -11,13 +11,17 @@
 // are served by the run-time chain interpreter of the same kernel, and the first call after the compilation has
 // finished loads the binary and uses it from then on.  A process in that mode must not end while a compilation is
 // running (the compiler's own static objects would be destroyed under it): db2_context_destroy and db2_rtc_wait
-// wait for it.  DB2_RTC=0 switches the mechanism off, as does a missing libnvrtc.
+// wait for it.  DB2_RTC=0 switches the mechanism off, as does a missing libnvrtc (binaries kept on disk by earlier
+// processes are still used then; DB2_RTC_NO_COMPILER=1 makes a process behave like that).
 #include "fused.cuh"
 #include "fused_ct_dev.cuh"
 
 #include "_build/fused_rtc_src.h"
 
 #include <dlfcn.h>
+#include <sys/stat.h>
+#include <sys/types.h>
+#include <unistd.h>
 
 #include <condition_variable>
 #include <map>
@@ -51,6 +55,8 @@ const Nvrtc &nvrtc() {
     static const Nvrtc n = [] {
         Nvrtc r;
         void *h = nullptr;
+        if (getenv("DB2_RTC_NO_COMPILER")) // behave like a machine without the toolkit: binaries from disk only
+            return r;
         for (const char *name : {"libnvrtc.so.12", "libnvrtc.so", "/usr/local/cuda/lib64/libnvrtc.so.12"})
             if ((h = dlopen(name, RTLD_NOW | RTLD_LOCAL)))
                 break;
@@ -128,16 +134,117 @@ std::string expression_of(const FusedProgram &P, bool aligned) {
 // fused_col_sum_ct_kernel<Chain<...>>
 std::string col_expression_of(const FusedProgram &P) { return "db2::ct::fused_col_sum_ct_kernel<" + chain_of(P) + ">"; }
 
-// compiles one instantiation to a cubin for sm_100a; on failure the compiler's log is left in *log
+// ---- binaries kept on disk ----
+// DAPHNE starts a new process for every script, so a chain's kernel would be compiled again in every run.  The device
+// binary is therefore also written to a directory of the user -- DB2_RTC_CACHE, else $XDG_CACHE_HOME/daphne_b200, else
+// $HOME/.cache/daphne_b200; DB2_RTC_CACHE=0 (or no usable directory) switches this off -- under a name made of hashes
+// of the embedded source and the instantiation, and read back from there (size and checksum verified) before the
+// compiler is asked.  Files are written under a temporary name and renamed, so concurrent processes see whole files.
+uint64_t fnv1a(const void *data, size_t n, uint64_t h) {
+    const unsigned char *p = static_cast<const unsigned char *>(data);
+    for (size_t i = 0; i < n; i++) {
+        h ^= p[i];
+        h *= 1099511628211ull;
+    }
+    return h;
+}
+std::string cache_dir() {
+    const char *e = getenv("DB2_RTC_CACHE");
+    std::string dir;
+    if (e && (e[0] == '\0' || strcmp(e, "0") == 0))
+        return "";
+    if (e) {
+        dir = e;
+    } else {
+        const char *x = getenv("XDG_CACHE_HOME"), *h = getenv("HOME");
+        if (x && x[0] == '/')
+            dir = std::string(x) + "/daphne_b200";
+        else if (h && h[0] == '/') {
+            dir = std::string(h) + "/.cache";
+            mkdir(dir.c_str(), 0700);
+            dir += "/daphne_b200";
+        } else
+            return "";
+    }
+    mkdir(dir.c_str(), 0700);
+    struct stat st;
+    if (stat(dir.c_str(), &st) != 0 || !S_ISDIR(st.st_mode))
+        return "";
+    return dir;
+}
+std::string cache_path(const std::string &src, const std::string &expr) {
+    const std::string dir = cache_dir();
+    if (dir.empty())
+        return "";
+    const char *what = "db2-rtc-1 sm_100a -std=c++17 -lineinfo";
+    uint64_t a = fnv1a(what, strlen(what), 14695981039346656037ull), b = fnv1a(what, strlen(what), 0x9e3779b97f4a7c15ull);
+    a = fnv1a(src.data(), src.size(), a);
+    b = fnv1a(src.data(), src.size(), b);
+    a = fnv1a(expr.data(), expr.size(), a);
+    b = fnv1a(expr.data(), expr.size(), b);
+    char name[64];
+    snprintf(name, sizeof(name), "/%016llx%016llx.cubin", (unsigned long long)a, (unsigned long long)b);
+    return dir + name;
+}
+struct CacheHeader {
+    char magic[8]; // "DB2RTC1"
+    uint64_t cubin_bytes, cubin_hash, name_bytes;
+};
+bool cache_load(const std::string &path, std::vector<char> *cubin, std::string *lowered) {
+    FILE *f = path.empty() ? nullptr : fopen(path.c_str(), "rb");
+    if (!f)
+        return false;
+    CacheHeader h;
+    bool ok = fread(&h, sizeof(h), 1, f) == 1 && memcmp(h.magic, "DB2RTC1", 8) == 0 && h.cubin_bytes > 0 &&
+              h.cubin_bytes < (64u << 20) && h.name_bytes > 0 && h.name_bytes < 65536;
+    if (ok) {
+        lowered->resize(h.name_bytes);
+        cubin->resize(h.cubin_bytes);
+        ok = fread(&(*lowered)[0], 1, h.name_bytes, f) == h.name_bytes &&
+             fread(cubin->data(), 1, h.cubin_bytes, f) == h.cubin_bytes &&
+             fnv1a(cubin->data(), cubin->size(), 14695981039346656037ull) == h.cubin_hash;
+    }
+    fclose(f);
+    if (!ok) {
+        cubin->clear();
+        lowered->clear();
+        remove(path.c_str()); // truncated or foreign file: compile again
+    }
+    return ok;
+}
+void cache_store(const std::string &path, const std::vector<char> &cubin, const std::string &lowered) {
+    if (path.empty())
+        return;
+    const std::string tmp = path + ".tmp" + std::to_string((long long)getpid());
+    FILE *f = fopen(tmp.c_str(), "wb");
+    if (!f)
+        return;
+    CacheHeader h;
+    memset(&h, 0, sizeof(h));
+    memcpy(h.magic, "DB2RTC1", 8);
+    h.cubin_bytes = cubin.size();
+    h.cubin_hash = fnv1a(cubin.data(), cubin.size(), 14695981039346656037ull);
+    h.name_bytes = lowered.size();
+    const bool ok = fwrite(&h, sizeof(h), 1, f) == 1 && fwrite(lowered.data(), 1, lowered.size(), f) == lowered.size() &&
+                    fwrite(cubin.data(), 1, cubin.size(), f) == cubin.size();
+    if (fclose(f) != 0 || !ok || rename(tmp.c_str(), path.c_str()) != 0)
+        remove(tmp.c_str());
+}
+
+// one instantiation as a cubin for sm_100a: from the directory above, else from the compiler (and then stored there);
+// on failure the compiler's log is left in *log
 bool compile(const std::string &expr, std::vector<char> *cubin, std::string *lowered, std::string *log) {
+    std::string src;
+    for (const char *piece : FUSED_RTC_SRC)
+        src += piece;
+    const std::string path = cache_path(src, expr);
+    if (cache_load(path, cubin, lowered))
+        return true;
     const Nvrtc &n = nvrtc();
     if (!n.ok) {
         *log = "libnvrtc not found";
         return false;
     }
-    std::string src;
-    for (const char *piece : FUSED_RTC_SRC)
-        src += piece;
     Nvrtc::Program prog = nullptr;
     if (n.create(&prog, src.c_str(), "fused_ct_dev.cu", 0, nullptr, nullptr) != 0) {
         *log = "nvrtcCreateProgram failed";
@@ -162,6 +269,8 @@ bool compile(const std::string &expr, std::vector<char> *cubin, std::string *low
     n.destroy(&prog);
     if (!ok && log->empty())
         *log = "the run-time compiler returned no binary";
+    if (ok)
+        cache_store(path, *cubin, *lowered);
     return ok;
 }
 
@@ -212,7 +321,13 @@ std::shared_ptr<Entry> kernel_of(const std::string &expr) {
         if (err != cudaSuccess) {
             cudaGetLastError();
             e->log = std::string("loading the compiled kernel failed: ") + cudaGetErrorString(err);
-            e->state = FAILED;
+            e->state = FAILED; // (a binary that came from disk is not trusted again: its file is removed)
+            std::string src;
+            for (const char *piece : FUSED_RTC_SRC)
+                src += piece;
+            const std::string path = cache_path(src, expr);
+            if (!path.empty())
+                remove(path.c_str());
         } else {
             e->state = LOADED;
             std::vector<char>().swap(e->cubin);

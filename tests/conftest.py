@@ -8,6 +8,11 @@ ROOT = Path(__file__).resolve().parents[1]
 if str(ROOT) not in sys.path:
     sys.path.insert(0, str(ROOT))
 
+# kernels compiled at run time are kept on disk between processes: the tests use a directory of their own
+if "DB2_RTC_CACHE" not in os.environ:
+    import tempfile
+    os.environ["DB2_RTC_CACHE"] = tempfile.mkdtemp(prefix="db2_rtc_cache_")
+
 
 def pytest_configure(config):
     config.addinivalue_line("markers", "gpu: needs a CUDA device (run on a B200 with `pytest -m gpu`)")

@@ -77,6 +77,51 @@ def test_column_sums_of_a_chain_compile():
     assert _compile([("DIV", "R", False), ("DIV", "S", True)], [], False, column_pass=True) > 5_000
 
 
+@needs_nvrtc
+def test_binaries_are_kept_on_disk_between_processes(tmp_path, monkeypatch):
+    """The device binary of a chain is written to DB2_RTC_CACHE and read back from there instead of compiling again; a
+    damaged file is thrown away and replaced; DB2_RTC_CACHE=0 writes nothing."""
+    import time
+    monkeypatch.setenv("DB2_RTC_CACHE", str(tmp_path))
+    chain = ([("MUL", "R", False), ("SUB", "S", True), ("CEIL", "U", False)], [("MAX", 3)], False)
+    t0 = time.perf_counter()
+    n1 = _compile(*chain)
+    t_compile = time.perf_counter() - t0
+    files = list(tmp_path.glob("*.cubin"))
+    assert len(files) == 1 and files[0].stat().st_size > n1 and not list(tmp_path.glob("*.tmp*"))
+    t0 = time.perf_counter()
+    n2 = _compile(*chain)
+    t_cached = time.perf_counter() - t0
+    assert n2 == n1 and t_cached < t_compile / 5, (t_compile, t_cached)
+    # another chain, another file; the same chain for the other layout, a third one
+    _compile(chain[0], [("MIN", 3)], False)
+    _compile(chain[0], chain[1], 2)
+    assert len(list(tmp_path.glob("*.cubin"))) == 3
+    # a file that was cut short is not used: compiled again and written again
+    def whole(path):  # a complete file again (the compiler's output is not the same bytes every time)
+        b = path.read_bytes()
+        size, name = int.from_bytes(b[8:16], "little"), int.from_bytes(b[24:32], "little")
+        return b[:8] == b"DB2RTC1\0" and len(b) == 32 + name + size
+    data = files[0].read_bytes()
+    assert whole(files[0])
+    files[0].write_bytes(data[: len(data) // 2])
+    assert not whole(files[0])
+    assert _compile(*chain) > 10_000 and whole(files[0])
+    # a file whose contents were altered fails the checksum
+    files[0].write_bytes(data[:-8] + bytes(8))
+    t0 = time.perf_counter()
+    assert _compile(*chain) > 10_000
+    assert time.perf_counter() - t0 > 5 * t_cached       # it was compiled, not read
+    assert files[0].read_bytes()[-8:] != bytes(8) and whole(files[0])
+    # switched off: nothing is written
+    off = tmp_path / "off"
+    off.mkdir()
+    monkeypatch.setenv("DB2_RTC_CACHE", "0")
+    _compile([("ADD", "S", False)], [("SUM", 1)], False)
+    monkeypatch.setenv("DB2_RTC_CACHE", str(off))
+    assert not list(off.iterdir())
+
+
 def test_bad_arguments_are_refused():
     with pytest.raises(Db2Error):
         _compile([("ADD", "R", False)] * 11, [], True)       # more steps than a program holds
@@ -245,3 +290,52 @@ def test_rows_off_16_byte_boundaries_take_the_compiled_kernel_too(ctx, shape, vi
         assert failed.value == 0
     finally:
         check(lib.db2_rtc_set_mode(2))
+
+
+@pytest.mark.gpu
+@needs_nvrtc
+def test_a_second_process_loads_the_kernel_from_disk(tmp_path):
+    """Process A compiles a chain's kernel and leaves it in DB2_RTC_CACHE; process B, which has no compiler at all
+    (DB2_RTC_NO_COMPILER), runs the same chain with that kernel and gets the same bits; process C, without compiler and
+    with an empty directory, falls back to the kernel that reads the chain at run time."""
+    import os
+    import subprocess
+    import sys
+    from pathlib import Path
+    root = Path(__file__).resolve().parents[1]
+    code = "\n".join([
+        "import sys, ctypes as C, numpy as np",
+        f"sys.path.insert(0, {str(root)!r})",
+        "import daphne_b200.kernels as k",
+        "from daphne_b200.lib import lib, check",
+        "B, A = k.BinaryOpCode, k.AggOpCode",
+        "ctx = k.Context(0)",
+        "rng = np.random.default_rng(5)",
+        "X = k.DenseMatrix.from_numpy(ctx, rng.standard_normal((50000, 32)))",
+        "RV = k.DenseMatrix.from_numpy(ctx, rng.standard_normal((1, 32)) + 3.0)",
+        "z = k.ewBinaryObjSca(B.ADD, k.ewBinaryMat(B.MUL, k.ewBinaryMat(B.SUB, X, RV), RV), 0.25)",
+        "m = k.aggRow(A.MAX, z).to_numpy()",
+        "ready, failed = C.c_int(), C.c_int()",
+        "check(lib.db2_rtc_counts(C.byref(ready), None, C.byref(failed)))",
+        "print(ready.value, failed.value, float(m.sum()).hex(), float(m[777, 0]).hex())",
+        "ctx.close()"])
+
+    def run(cache, no_compiler):
+        env = dict(os.environ, DB2_RTC_CACHE=str(cache))
+        env.pop("DB2_RTC", None)
+        if no_compiler:
+            env["DB2_RTC_NO_COMPILER"] = "1"
+        r = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, env=env, timeout=600)
+        assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-4000:]
+        ready, failed, total, one = r.stdout.strip().split()[-4:]
+        return int(ready), int(failed), total, one
+
+    shared, empty = tmp_path / "shared", tmp_path / "empty"
+    shared.mkdir()
+    empty.mkdir()
+    a = run(shared, False)
+    assert a[0] >= 1 and a[1] == 0 and len(list(shared.glob("*.cubin"))) >= 1
+    b = run(shared, True)
+    assert b[0] >= 1 and b[1] == 0 and b[2:] == a[2:]
+    c = run(empty, True)
+    assert c[0] == 0 and c[1] >= 1 and c[2:] == a[2:] and not list(empty.glob("*.cubin"))
