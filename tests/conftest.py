@@ -10,8 +10,11 @@ if str(ROOT) not in sys.path:
 
 # kernels compiled at run time are kept on disk between processes: the tests use a directory of their own
 if "DB2_RTC_CACHE" not in os.environ:
+    import atexit
+    import shutil
     import tempfile
     os.environ["DB2_RTC_CACHE"] = tempfile.mkdtemp(prefix="db2_rtc_cache_")
+    atexit.register(shutil.rmtree, os.environ["DB2_RTC_CACHE"], ignore_errors=True)
 
 
 def pytest_configure(config):
