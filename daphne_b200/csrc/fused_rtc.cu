@@ -346,7 +346,7 @@ bool fused_row_pass_rtc(const FusedProgram &P, bool aligned, cudaStream_t st, in
     using namespace ct;
     const size_t smem = (size_t)(WARPS * 2 * WR * CK + P.smem_elems + 2 * FUSED_MAX_STEPS) * sizeof(double) + 256;
     const int64_t nblocks = ((P.rows + WR - 1) / WR + WARPS - 1) / WARPS;
-    const int64_t cap = (int64_t)sm_count() * 3; // RowCtasPerSm
+    const int64_t cap = (int64_t)sm_count() * RowCtasPerSm<AnyChain>::value; // the same for every chain
     const int grid = (int)(nblocks < cap ? nblocks : cap);
     const void *fn = reinterpret_cast<const void *>(e->kernel);
     if (e->attr.need()) {
