@@ -544,9 +544,15 @@ int db2_matrix_to_host_async(db2_matrix *m, void *dst, int64_t dst_ld) {
     else
         DB2_CUDA(cudaMemcpy2DAsync(dst, (size_t)dst_ld * es, m->dev_ptr(), (size_t)m->dev_ld * es, (size_t)m->cols * es,
                                    (size_t)m->rows, cudaMemcpyDeviceToHost, ctx->side_stream));
-    std::lock_guard<std::mutex> lock(ctx->mu);
-    ctx->side_keep.push_back(m->dev);
-    ctx->stats.d2h_bytes += (uint64_t)m->rows * m->cols * es;
+    bool drain = false;
+    {
+        std::lock_guard<std::mutex> lock(ctx->mu);
+        ctx->side_keep.push_back(m->dev);
+        ctx->stats.d2h_bytes += (uint64_t)m->rows * m->cols * es;
+        drain = ctx->side_keep.size() >= 256; // a caller that never waits must not pin device memory without bound
+    }
+    if (drain)
+        return db2_context_side_sync(ctx);
     return DB2_OK;
     DB2_API_END
 }
