@@ -54,6 +54,10 @@ class Context:
     def sync(self) -> None:
         check(lib.db2_context_sync(self._h))
 
+    def side_sync(self) -> None:
+        """Waits for the copies queued by DenseMatrix.to_numpy_async (and the collectives of the second stream)."""
+        check(lib.db2_context_side_sync(self._h))
+
     def stats(self) -> dict:
         s = _l.Stats()
         check(lib.db2_context_stats(self._h, C.byref(s)))
@@ -136,6 +140,14 @@ class DenseMatrix:
     def to_numpy(self) -> np.ndarray:
         out = np.empty((self.rows, self.cols), dtype=self.dtype)
         check(lib.db2_matrix_to_host(self._h, C.c_void_p(out.ctypes.data), max(self.cols, 1)))
+        return out
+
+    def to_numpy_async(self, out: np.ndarray) -> np.ndarray:
+        """Queues the copy into `out` (C-contiguous, same shape and value type; pinned memory for a true overlap) on the
+        context's second stream and returns at once; Context.side_sync() waits for it."""
+        if out.shape != (self.rows, self.cols) or out.dtype != self.dtype or not out.flags.c_contiguous:
+            raise ValueError("to_numpy_async needs a C-contiguous array of the matrix's shape and value type")
+        check(lib.db2_matrix_to_host_async(self._h, C.c_void_p(out.ctypes.data), max(self.cols, 1)))
         return out
 
     def free(self) -> None:
@@ -344,6 +356,24 @@ def extractCol(arg: DenseMatrix, sel: DenseMatrix, ctx: Optional[Context] = None
     h = C.c_void_p()
     check(lib.db2_extractCol(ctx.handle, C.byref(h), arg.handle, sel.handle))
     return _res(ctx, h)
+
+
+def rtc_set_mode(mode: int) -> None:
+    """Kernels for elementwise chains without a compiled-in specialisation: 0 = never compile one, 2 = compile on the
+    calling thread when the chain is first evaluated (default), 1 = compile on a background thread (call rtc_wait()
+    before the process ends)."""
+    check(lib.db2_rtc_set_mode(int(mode)))
+
+
+def rtc_wait() -> None:
+    check(lib.db2_rtc_wait())
+
+
+def rtc_counts() -> dict:
+    """Chains with a compiled kernel / being compiled / whose compilation failed."""
+    r, p, f = C.c_int(), C.c_int(), C.c_int()
+    check(lib.db2_rtc_counts(C.byref(r), C.byref(p), C.byref(f)))
+    return {"ready": r.value, "pending": p.value, "failed": f.value}
 
 
 def readDaphne(ctx: Context, path) -> DenseMatrix:
